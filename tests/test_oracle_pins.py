@@ -1,0 +1,156 @@
+"""Pin the CPU oracle to the reference: its known-answer tests restated, and
+fixtures produced by importing the reference's Python (tests/golden/make_golden.py).
+Everything here is bit-exact unless a tolerance is written next to the check."""
+
+import numpy as np
+import torch
+
+import fa4b_oracle as O
+
+
+def _bf16(a):
+    return torch.from_numpy(a.copy()).view(torch.bfloat16)
+
+
+def test_e2m1_rne_midpoints_match_reference_kat(golden_dir):
+    # tests/test_projection_quantization_reference.py:81-95 of the reference
+    fx = np.load(golden_dir / "quantizers.npz")
+    mid = torch.from_numpy(fx["e2m1_midpoints"])
+    want = torch.from_numpy(fx["e2m1_midpoints_rne"])
+    assert want.tolist() == [0.0, 1.0, 1.0, 2.0, 2.0, 4.0, 4.0]
+    assert torch.equal(O.e2m1_decode(O.e2m1_rne_codes(mid)), want)
+    assert torch.equal(O.e2m1_decode(O.e2m1_rne_codes(-mid)), -want)
+    # sign bit is kept when the magnitude rounds to zero
+    # (tests/test_e4m3_to_mxfp4_v_contract.py:465-478 of the reference)
+    assert O.e2m1_rne_codes(torch.tensor([-0.1, -0.0, 0.1])).tolist() == [8, 8, 0]
+    assert O.e2m1_rne_codes(torch.tensor([7.0, -100.0, 6.0])).tolist() == [7, 15, 7]
+
+
+def test_nvfp4_rowwise_matches_reference_fixture(golden_dir):
+    fx = np.load(golden_dir / "quantizers.npz")
+    x = _bf16(fx["x"])
+    q = O.nvfp4_quantize(x)
+    assert torch.equal(q.dequant().bfloat16().view(torch.int16), torch.from_numpy(fx["nvfp4_values"]))
+    assert torch.equal(q.scales.view(torch.float8_e4m3fn).float(), torch.from_numpy(fx["nvfp4_block_scales"]))
+    assert float(q.global_scale) == float(fx["nvfp4_global_decode"])
+    # the stock bucketize payload differs only at exact ties
+    stock = _bf16(fx["nvfp4_stock_values"])
+    differing = (stock != q.dequant().bfloat16()).sum().item()
+    assert 0 < differing <= 64
+
+
+def test_nvfp4_transposed_matches_reference_fixture(golden_dir):
+    fx = np.load(golden_dir / "quantizers.npz")
+    x = _bf16(fx["x"])
+    q = O.nvfp4_quantize_transposed(x)
+    assert q.codes.shape == (256, 64)
+    assert torch.equal(q.dequant().bfloat16().view(torch.int16), torch.from_numpy(fx["nvfp4_t_values"]))
+    assert torch.equal(q.scales.view(torch.float8_e4m3fn).float(), torch.from_numpy(fx["nvfp4_t_block_scales"]))
+
+
+def test_mxfp4_matches_reference_fixture(golden_dir):
+    fx = np.load(golden_dir / "quantizers.npz")
+    x = _bf16(fx["x"])
+    for mode in ("ceil", "rte"):
+        q = O.mxfp4_quantize(x, mode)
+        assert torch.equal(q.dequant().bfloat16().view(torch.int16), torch.from_numpy(fx[f"mxfp4_{mode}_values"]))
+        e = q.scales.float()
+        scale = torch.where(e > 0, torch.exp2(e - 127.0), torch.zeros_like(e))
+        assert torch.equal(scale, torch.from_numpy(fx[f"mxfp4_{mode}_block_scales"]))
+
+
+def test_mxfp4_v_sequence_groups_match_reference_fixture(golden_dir):
+    fx = np.load(golden_dir / "quantizers.npz")
+    v = _bf16(fx["v"])  # [B,S,H,D]
+    codes, scales, deq = O.mxfp4_v_sequence(v.permute(0, 2, 1, 3).contiguous())
+    assert codes.shape == (1, 2, 32, 32) and scales.shape == (1, 2, 32, 2)
+    got = deq.permute(0, 2, 1, 3).bfloat16().contiguous()
+    assert torch.equal(got.view(torch.int16), torch.from_numpy(fx["v_values"]))
+    e = scales.float()
+    assert torch.equal(torch.where(e > 0, torch.exp2(e - 127.0), torch.zeros_like(e)),
+                       torch.from_numpy(fx["v_block_scales"]))
+
+
+def test_scale_page_byte_order():
+    # projection_quantization_reference.py:314-322
+    rows, kb = 256, 8
+    s = torch.arange(rows * kb, dtype=torch.int64).remainder(251).to(torch.uint8).reshape(rows, kb)
+    pages = O.scales_to_pages(s)
+    assert pages.shape == (2, 2, 512)
+    for r, c in ((0, 0), (31, 3), (32, 0), (127, 7), (128, 4), (200, 5), (255, 7)):
+        off = (r % 32) * 16 + ((r % 128) // 32) * 4 + (c % 4)
+        assert pages[r // 128, c // 4, off] == s[r, c]
+    assert torch.equal(O.pages_to_scales(pages), s)
+
+
+def test_nibble_packing_even_element_low():
+    codes = torch.tensor([[1, 2, 15, 0]], dtype=torch.uint8)
+    assert O.pack_nibbles(codes).tolist() == [[0x21, 0x0F]]
+    assert torch.equal(O.unpack_nibbles(O.pack_nibbles(codes)), codes)
+
+
+def test_all_zero_and_saturating_blocks():
+    x = torch.zeros(128, 64).bfloat16()
+    q = O.nvfp4_quantize(x)
+    assert q.codes.sum() == 0 and q.scales.sum() == 0 and float(q.global_scale) == 0.0
+    m = O.mxfp4_quantize(x)
+    assert m.codes.sum() == 0 and m.scales.sum() == 0
+    x[0, 0] = 3.0
+    q = O.nvfp4_quantize(x)
+    # the block holding the tensor maximum gets the E4M3 end point and code 6
+    assert q.scales[0, 0] == 0x7E and (q.codes[0, 0] & 0xF) == 7
+
+
+def test_backward_collapses_to_reference_fp32_backward(golden_dir):
+    """With E4M3 scores and no P/dS rounding the emulation must equal the
+    reference's represented-operand FP32 backward (S=128, one kv group)."""
+    fx = np.load(golden_dir / "backward_s128.npz")
+    def e4(a):  # [B,S,H,D] e4m3 bits of 4*x -> bf16 [B,H,S,D]
+        t = torch.from_numpy(a.copy()).view(torch.float8_e4m3fn).float() / 4.0
+        return t.permute(0, 2, 1, 3).contiguous().bfloat16()
+    q, k, v, do = e4(fx["q"]), e4(fx["k"]), e4(fx["v"]), e4(fx["dout"])
+    lstat = torch.from_numpy(fx["lstat"])[:, :, 0]
+    dstat = torch.from_numpy(fx["dstat"])[:, :, 0]
+    do5 = do.float() * 4.0  # the validator's dO is E4M3-represented; keep it exact (no E5M2 step)
+    dq, dk, dv = O.attn_backward(q, k, v, None, None, do, softmax_scale=float(fx["softmax_scale"]),
+                                 score_operands="e4m3", quantize_p_ds=False, stats=(do5, dstat, lstat))
+    for got, name in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+        want = torch.from_numpy(fx[name]).permute(0, 2, 1, 3)
+        assert O.rel_l2(want, got) < 2e-5, name  # FP32 summation order only
+
+
+def test_backward_quantised_route_stays_close_to_fp32_backward(golden_dir):
+    fx = np.load(golden_dir / "backward_s128.npz")
+    def e4(a):
+        t = torch.from_numpy(a.copy()).view(torch.float8_e4m3fn).float() / 4.0
+        return t.permute(0, 2, 1, 3).contiguous().bfloat16()
+    q, k, v, do = e4(fx["q"]), e4(fx["k"]), e4(fx["v"]), e4(fx["dout"])
+    fwd = O.attn_forward(q, k, v, softmax_scale=float(fx["softmax_scale"]))
+    dq, dk, dv = O.attn_backward(q, k, v, fwd.o, fwd.lse, do, softmax_scale=float(fx["softmax_scale"]))
+    for got, name, tol in ((dq, "dq", 0.25), (dk, "dk", 0.25), (dv, "dv", 0.1)):
+        want = torch.from_numpy(fx[name]).permute(0, 2, 1, 3)
+        assert O.rel_l2(want, got) < tol, (name, O.rel_l2(want, got))
+
+
+def test_forward_tracks_fp32_attention_and_zero_dout_gives_zero_grads():
+    q, k, v, do = O.make_attention_inputs(1, 4, 2, 256, 64, seed=3)
+    fwd = O.attn_forward(q, k, v)
+    ref_o, ref_lse = O.attn_reference_fp32(q, k, v)
+    assert O.rel_l2(ref_o, fwd.o) < 0.12  # NVFP4 scores + FP8 P/V vs exact math
+    assert (fwd.lse - ref_lse).abs().max() < 0.5
+    # validate_native_tk_d128_backward.py:707-738: exact-zero dO => exact-zero gradients
+    dq, dk, dv = O.attn_backward(q, k, v, fwd.o, fwd.lse, torch.zeros_like(do))
+    assert not dq.any() and not dk.any() and not dv.any()
+
+
+def test_forward_rounding_is_invariant_to_the_running_maximum():
+    """The E4M3 probability of 2^(s - mhat + 8) does not depend on which
+    integer mhat a streaming kernel happened to hold when it saw the tile."""
+    g = torch.Generator().manual_seed(1)
+    s2 = torch.randn(64, 256, generator=g) * 3.0
+    mhat = torch.ceil(s2.amax(dim=1, keepdim=True))
+    final = O.e4m3_round(torch.exp2(s2 - mhat + 8.0)).float()
+    early = O.e4m3_round(torch.exp2(s2 - (mhat - 3.0) + 8.0).clamp(max=448.0)).float() / 8.0
+    keep = torch.exp2(s2 - mhat + 8.0) >= 2.0 ** -6  # normal range of the final grid
+    keep &= torch.exp2(s2 - (mhat - 3.0) + 8.0) <= 448.0
+    assert torch.equal(final[keep], early[keep])
