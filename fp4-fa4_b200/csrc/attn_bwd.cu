@@ -1,0 +1,461 @@
+// Causal GQA backward.  One CTA owns a 128-key tile of one kv head: dK and dV of
+// that tile accumulate in TMEM over every query head of the group and every
+// query tile at or after the key tile; dQ contributions leave through FP32
+// reductions into a scratch accumulator that a second kernel rounds to bf16.
+//
+// Per query sub-tile (QT = 64 rows at D = 128, 128 rows at D = 64) five MMAs:
+//   S^T  = Knvfp4 . Qnvfp4^T            block-scaled FP4   -> TMEM St  [key, q]
+//   dP^T = V8 . dO5^T                   E4M3 x E5M2        -> TMEM dPt [key, q]
+//   dV  += P8^T . dO5                   A = P8^T (smem), B = dO5 MN-major
+//   dK  += dS8^T . Q8                   A = dS8^T (smem), B = Q8 MN-major
+//   dQ   = dS8 . K8  (D = 64)  or  dQ^T = K8^T . dS8^T (D = 128), both operands MN-major
+// with P8 = E4M3(2^min(S2 + lstat, 8)) and dS8 = E4M3((dP16 + dstat) * P8 * scale/16)
+// computed by eight warps, two threads per key row.
+//
+// Warps: 0-7 compute, 8-11 drain dQ, 12 TMA producer, 13 MMA issuer.
+#include <mutex>
+
+#include "attn.cuh"
+
+namespace fa4b {
+
+constexpr int kBwdThreads = 448;
+constexpr int kBwdStages = 3;
+
+template <int D>
+struct BwdCfg {
+  static constexpr int QT = (D == 128) ? 64 : 128;  // query rows per iteration
+  static constexpr int kPages = D / 64;
+  static constexpr uint32_t colDK = 0, colDV = D, colSt = 2 * D, colDPt = 2 * D + QT, colDQ = 2 * D + 2 * QT;
+  static constexpr uint32_t colSfa = colDQ + 64, colSfb = colSfa + 8;
+  static_assert(colSfb + 8 <= 512, "TMEM budget");
+};
+
+template <int D>
+struct BwdSmem {
+  using C = BwdCfg<D>;
+  alignas(1024) uint8_t k_codes[128 * D / 2];
+  alignas(1024) uint8_t k8[128 * D];
+  alignas(1024) uint8_t v8[128 * D];
+  alignas(1024) uint8_t q_codes[kBwdStages][C::QT * D / 2];
+  alignas(1024) uint8_t q8[kBwdStages][C::QT * D];
+  alignas(1024) uint8_t do5[kBwdStages][C::QT * D];
+  alignas(1024) uint8_t pt[2][128 * C::QT];   // P8^T  [key][q], rows of QT bytes, swizzled
+  alignas(1024) uint8_t dst[2][128 * C::QT];  // dS8^T [key][q]
+  alignas(16) uint8_t k_sf[C::kPages * 512];
+  alignas(16) uint8_t q_sf[kBwdStages][C::kPages * 512];
+  alignas(16) float lstat[kBwdStages][C::QT];
+  alignas(16) float dstat[kBwdStages][C::QT];
+  alignas(8) uint64_t kv_full, in_full[kBwdStages], in_empty[kBwdStages], st_full, dp_full, pt_ready, ds_ready, dq_full, dq_free,
+      acc_done;
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+struct BwdParams {
+  int B, Hq, Hkv, S;
+  float scale;
+  const uint8_t* q_sf;
+  const uint8_t* k_sf;
+  const float* q_global;
+  const float* k_global;
+  const float* lstat;
+  const float* dstat;
+  float* dq_accum;  // [B*Hq, S, D] f32, zeroed before launch
+  __nv_bfloat16* dk;
+  int64_t dk_sb, dk_sh, dk_ss;
+  __nv_bfloat16* dv;
+  int64_t dv_sb, dv_sh, dv_ss;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ float ex2_approx_b(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float2 e4m3x2_to_f32(uint32_t two_bytes) {
+  uint32_t h2;
+  const uint16_t in = (uint16_t)two_bytes;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(in));
+  return __half22float2(*reinterpret_cast<const __half2*>(&h2));
+}
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, const __grid_constant__ CUtensorMap map_k8,
+                const __grid_constant__ CUtensorMap map_v8, const __grid_constant__ CUtensorMap map_qc,
+                const __grid_constant__ CUtensorMap map_q8, const __grid_constant__ CUtensorMap map_do) {
+  using C = BwdCfg<D>;
+  constexpr int QT = C::QT;
+  constexpr int kPages = C::kPages;
+  extern __shared__ uint8_t raw[];
+  BwdSmem<D>& s = *reinterpret_cast<BwdSmem<D>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+
+  const int n_tiles = p.S / 128;
+  const int heads_kv = p.B * p.Hkv;
+  const int kt = blockIdx.x / heads_kv;  // key tile; low tiles (most query tiles) first
+  const int bhk = blockIdx.x % heads_kv;
+  const int b = bhk / p.Hkv, hk = bhk % p.Hkv;
+  const int G = p.Hq / p.Hkv;
+  const int sub_per_tile = 128 / QT;
+  const int n_sub = (n_tiles - kt) * sub_per_tile;  // query sub-tiles per head
+  const int n_it = G * n_sub;
+  const int sub0 = kt * sub_per_tile;
+
+  if (t == 0) {
+    mbar_init(&s.kv_full, 1);
+    for (int i = 0; i < kBwdStages; ++i) {
+      mbar_init(&s.in_full[i], 1);
+      mbar_init(&s.in_empty[i], 1);
+    }
+    mbar_init(&s.st_full, 1);
+    mbar_init(&s.dp_full, 1);
+    mbar_init(&s.pt_ready, 256);
+    mbar_init(&s.ds_ready, 256);
+    mbar_init(&s.dq_full, 1);
+    mbar_init(&s.dq_free, 128);
+    mbar_init(&s.acc_done, 1);
+    s.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 12) tmem_alloc(&s.tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = s.tmem_base;
+
+  if (warp == 12) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      mbar_expect_tx(&s.kv_full, 128 * D / 2 + kPages * 512 + 2 * 128 * D);
+      tma_load_3d(s.k_codes, &map_kc, 0, kt * 128, bhk, &s.kv_full);
+      bulk_load(s.k_sf, p.k_sf + ((size_t)bhk * n_tiles + kt) * kPages * 512, kPages * 512, &s.kv_full);
+      tma_load_3d(s.k8, &map_k8, 0, kt * 128, bhk, &s.kv_full);
+      tma_load_3d(s.v8, &map_v8, 0, kt * 128, bhk, &s.kv_full);
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it % kBwdStages;
+        if (it >= kBwdStages && !mbar_wait(&s.in_empty[st], ((it / kBwdStages) - 1) & 1, &s.abort_flag, p.status, 110)) break;
+        const int g = it / n_sub, qs = sub0 + it % n_sub;
+        const int bh = b * p.Hq + hk * G + g;
+        const int q0 = qs * QT;
+        mbar_expect_tx(&s.in_full[st], QT * D / 2 + kPages * 512 + 2 * QT * D + 2 * QT * 4);
+        tma_load_3d(s.q_codes[st], &map_qc, 0, q0, bh, &s.in_full[st]);
+        bulk_load(s.q_sf[st], p.q_sf + ((size_t)bh * n_tiles + q0 / 128) * kPages * 512, kPages * 512, &s.in_full[st]);
+        tma_load_3d(s.q8[st], &map_q8, 0, q0, bh, &s.in_full[st]);
+        tma_load_3d(s.do5[st], &map_do, 0, q0, bh, &s.in_full[st]);
+        bulk_load(s.lstat[st], p.lstat + (size_t)bh * p.S + q0, QT * 4, &s.in_full[st]);
+        bulk_load(s.dstat[st], p.dstat + (size_t)bh * p.S + q0, QT * 4, &s.in_full[st]);
+      }
+    }
+  } else if (warp == 13) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t id_s = idesc_fp4(128, QT, 0, 0, 0);
+      constexpr uint32_t id_dp = idesc_f8(128, QT, 0, 1, 0, 0);   // V8 (E4M3, K-major) x dO5 (E5M2, K-major)
+      constexpr uint32_t id_dv = idesc_f8(128, D, 0, 1, 0, 1);    // P8^T (K-major) x dO5 (MN-major)
+      constexpr uint32_t id_dk = idesc_f8(128, D, 0, 0, 0, 1);    // dS8^T (K-major) x Q8 (MN-major)
+      constexpr uint32_t id_dq = idesc_f8(128, 64, 0, 0, 1, 1);   // both MN-major
+      const uint32_t kc = smem_u32(s.k_codes), k8 = smem_u32(s.k8), v8 = smem_u32(s.v8);
+      bool ok = mbar_wait(&s.kv_full, 0, &s.abort_flag, p.status, 120);
+      if (ok) {
+        tc_fence_after();
+        for (int pg = 0; pg < kPages; ++pg) tmem_cp_page(tm + C::colSfa + 4 * pg, make_page_desc(smem_u32(s.k_sf + 512 * pg)));
+      }
+      // S^T and dP^T of iteration `it` (inputs in stage it % kBwdStages)
+      auto issue_scores = [&](int it) -> bool {
+        const int st = it % kBwdStages;
+        if (!mbar_wait(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 121)) return false;
+        tc_fence_after();
+        const int qs = sub0 + it % n_sub;
+        const uint32_t sf_shift = (QT == 64) ? 2u * (uint32_t)(qs & 1) : 0u;  // which 64 rows of the 128-row scale page
+        for (int pg = 0; pg < kPages; ++pg) tmem_cp_page(tm + C::colSfb + 4 * pg, make_page_desc(smem_u32(s.q_sf[st] + 512 * pg)));
+#pragma unroll
+        for (int k = 0; k < D / 64; ++k)
+          mma_nvfp4_ss(tm + C::colSt, make_tile_desc(kc + 32 * k, D / 2), make_tile_desc(smem_u32(s.q_codes[st]) + 32 * k, D / 2), id_s,
+                       tm + C::colSfa + 4 * k, tm + C::colSfb + 4 * k + sf_shift, k > 0);
+        mma_commit(&s.st_full);
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k)
+          mma_f8_ss(tm + C::colDPt, make_tile_desc(v8 + 32 * k, D), make_tile_desc(smem_u32(s.do5[st]) + 32 * k, D), id_dp, k > 0);
+        mma_commit(&s.dp_full);
+        return true;
+      };
+      if (ok) ok = issue_scores(0);
+      for (int it = 0; ok && it < n_it; ++it) {
+        const int st = it % kBwdStages, buf = it & 1;
+        ok = mbar_wait(&s.pt_ready, it & 1, &s.abort_flag, p.status, 122);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < QT / 32; ++k)
+          mma_f8_ss(tm + C::colDV, make_tile_desc(smem_u32(s.pt[buf]) + 32 * k, QT), make_tile_desc(smem_u32(s.do5[st]) + 32 * D * k, D),
+                    id_dv, (it > 0 || k > 0) ? 1u : 0u);
+        ok = mbar_wait(&s.ds_ready, it & 1, &s.abort_flag, p.status, 123);
+        if (!ok) break;
+        tc_fence_after();
+        if (it + 1 < n_it) {
+          ok = issue_scores(it + 1);
+          if (!ok) break;
+        }
+#pragma unroll
+        for (int k = 0; k < QT / 32; ++k)
+          mma_f8_ss(tm + C::colDK, make_tile_desc(smem_u32(s.dst[buf]) + 32 * k, QT), make_tile_desc(smem_u32(s.q8[st]) + 32 * D * k, D),
+                    id_dk, (it > 0 || k > 0) ? 1u : 0u);
+        if (it > 0) {
+          ok = mbar_wait(&s.dq_free, (it - 1) & 1, &s.abort_flag, p.status, 124);
+          if (!ok) break;
+          tc_fence_after();
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {  // 128 keys, 32 per step
+          if (D == 128)  // dQ^T[d, q] = K8^T . dS8^T
+            mma_f8_ss(tm + C::colDQ, make_tile_desc(k8 + 32 * D * k, D), make_tile_desc(smem_u32(s.dst[buf]) + 32 * QT * k, QT), id_dq,
+                      k > 0);
+          else  // dQ[q, d] = dS8 . K8
+            mma_f8_ss(tm + C::colDQ, make_tile_desc(smem_u32(s.dst[buf]) + 32 * QT * k, QT), make_tile_desc(k8 + 32 * D * k, D), id_dq,
+                      k > 0);
+        }
+        mma_commit(&s.dq_full);
+        mma_commit(&s.in_empty[st]);
+      }
+      if (ok) mma_commit(&s.acc_done);
+    }
+  } else if (warp >= 8) {
+    // ------------------------------------------------------------------ dQ drain (warps 8-11)
+    const int w4 = warp & 3;
+    const uint32_t lane_base = tm + ((uint32_t)(w4 * 32) << 16);
+    const int r = w4 * 32 + lane;  // TMEM lane: d (D = 128) or query row (D = 64)
+    for (int it = 0; it < n_it; ++it) {
+      if (!mbar_wait(&s.dq_full, it & 1, &s.abort_flag, p.status, 130)) break;
+      tc_fence_after();
+      const int g = it / n_sub, qs = sub0 + it % n_sub;
+      const int bh = b * p.Hq + hk * G + g;
+      float* base = p.dq_accum + ((size_t)bh * p.S + (size_t)qs * QT) * D;
+#pragma unroll
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + C::colDQ + c0, v);
+        tmem_ld_wait();
+        if (D == 128) {
+          // lane = d, column = query row: one coalesced 128-byte reduction per column
+#pragma unroll
+          for (int i = 0; i < 32; ++i) atomicAdd(base + (size_t)(c0 + i) * D + r, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            red_add_v4(base + (size_t)r * D + c0 + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
+                       __uint_as_float(v[i + 3]));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&s.dq_free);
+    }
+  } else {
+    // ------------------------------------------------------------------ compute (warps 0-7)
+    constexpr int CW = QT / 2;                   // query columns per thread
+    const int half = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;      // key row inside the tile = TMEM lane
+    const uint32_t lane_base = tm + ((uint32_t)((warp & 3) * 32) << 16);
+    const int key = kt * 128 + row;
+    const float beta = p.scale / 16.0f;
+    const float kg = p.k_global[bhk] * p.scale * kLog2e;
+    bool ok = true;
+    for (int it = 0; ok && it < n_it; ++it) {
+      const int st = it % kBwdStages, buf = it & 1;
+      const int g = it / n_sub, qs = sub0 + it % n_sub;
+      const int bh = b * p.Hq + hk * G + g;
+      const float c2 = kg * p.q_global[bh];
+      const int q_first = qs * QT + half * CW;   // global query index of this thread's first column
+      const bool diag = qs * QT < kt * 128 + 128;  // sub-tile overlaps the key tile: mask needed
+      ok = mbar_wait(&s.st_full, it & 1, &s.abort_flag, p.status, 140);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t pk[CW / 4];
+#pragma unroll
+      for (int c0 = 0; c0 < CW; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + C::colSt + half * CW + c0, v);
+        tmem_ld_wait();
+        float pr[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float x = fminf(fmaf(__uint_as_float(v[i]), c2, s.lstat[st][half * CW + c0 + i]), kPLift);
+          pr[i] = ex2_approx_b(x);
+          if (diag && key > q_first + c0 + i) pr[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) pk[c0 / 4 + i] = cvt_e4m3x4(pr[4 * i], pr[4 * i + 1], pr[4 * i + 2], pr[4 * i + 3]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          *reinterpret_cast<uint4*>(&s.pt[buf][swizzled_offset(row, half * CW + c0 + 16 * i, QT)]) =
+              make_uint4(pk[c0 / 4 + 4 * i], pk[c0 / 4 + 4 * i + 1], pk[c0 / 4 + 4 * i + 2], pk[c0 / 4 + 4 * i + 3]);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&s.pt_ready);
+
+      ok = mbar_wait(&s.dp_full, it & 1, &s.abort_flag, p.status, 141);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c0 = 0; c0 < CW; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + C::colDPt + half * CW + c0, v);
+        tmem_ld_wait();
+        uint32_t dk4[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t w = pk[c0 / 4 + i];
+          const float2 p01 = e4m3x2_to_f32(w & 0xffffu), p23 = e4m3x2_to_f32(w >> 16);
+          const float* ds_ = &s.dstat[st][half * CW + c0 + 4 * i];
+          const float d0 = (__uint_as_float(v[4 * i]) + ds_[0]) * p01.x * beta;
+          const float d1 = (__uint_as_float(v[4 * i + 1]) + ds_[1]) * p01.y * beta;
+          const float d2 = (__uint_as_float(v[4 * i + 2]) + ds_[2]) * p23.x * beta;
+          const float d3 = (__uint_as_float(v[4 * i + 3]) + ds_[3]) * p23.y * beta;
+          dk4[i] = cvt_e4m3x4(d0, d1, d2, d3);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          *reinterpret_cast<uint4*>(&s.dst[buf][swizzled_offset(row, half * CW + c0 + 16 * i, QT)]) =
+              make_uint4(dk4[4 * i], dk4[4 * i + 1], dk4[4 * i + 2], dk4[4 * i + 3]);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&s.ds_ready);
+    }
+    // ------------------------------------------------------------------ dK, dV of this key tile
+    if (ok) ok = mbar_wait(&s.acc_done, 0, &s.abort_flag, p.status, 142);
+    if (ok) {
+      tc_fence_after();
+      constexpr float inv = 1.0f / 1024.0f;
+      __nv_bfloat16* dkrow = p.dk + (int64_t)b * p.dk_sb + (int64_t)hk * p.dk_sh + (int64_t)key * p.dk_ss + (D / 2) * half;
+      __nv_bfloat16* dvrow = p.dv + (int64_t)b * p.dv_sb + (int64_t)hk * p.dv_sh + (int64_t)key * p.dv_ss + (D / 2) * half;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* dst = which ? dvrow : dkrow;
+        const uint32_t col = (which ? C::colDV : C::colDK) + (D / 2) * half;
+#pragma unroll
+        for (int c0 = 0; c0 < D / 2; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(lane_base + col + c0, v);
+          tmem_ld_wait();
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[2 * i]) * inv, __uint_as_float(v[2 * i + 1]) * inv);
+            w[i] = *reinterpret_cast<const uint32_t*>(&h2);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<uint4*>(dst + c0 + 8 * i) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 12) tmem_dealloc(tm, 512);
+}
+
+// dQ = bf16(accumulator / 1024) through the caller's strides
+template <int D>
+__global__ void __launch_bounds__(256) dq_convert_kernel(const float* __restrict__ acc, int Hq, int S, int64_t n_rows, __nv_bfloat16* dq,
+                                                         int64_t sb, int64_t sh, int64_t ss) {
+  constexpr int kPerRow = D / 8;
+  for (int64_t c = (int64_t)blockIdx.x * 256 + threadIdx.x; c < n_rows * kPerRow; c += (int64_t)gridDim.x * 256) {
+    const int64_t row = c / kPerRow;
+    const int cb = (int)(c % kPerRow) * 8;
+    const int bh = (int)(row / S), sidx = (int)(row % S);
+    const float4 a = *reinterpret_cast<const float4*>(acc + row * D + cb), bq = *reinterpret_cast<const float4*>(acc + row * D + cb + 4);
+    constexpr float inv = 1.0f / 1024.0f;
+    const __nv_bfloat162 h0 = __floats2bfloat162_rn(a.x * inv, a.y * inv), h1 = __floats2bfloat162_rn(a.z * inv, a.w * inv);
+    const __nv_bfloat162 h2 = __floats2bfloat162_rn(bq.x * inv, bq.y * inv), h3 = __floats2bfloat162_rn(bq.z * inv, bq.w * inv);
+    uint4 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&h0);
+    o.y = *reinterpret_cast<const uint32_t*>(&h1);
+    o.z = *reinterpret_cast<const uint32_t*>(&h2);
+    o.w = *reinterpret_cast<const uint32_t*>(&h3);
+    *reinterpret_cast<uint4*>(dq + (int64_t)(bh / Hq) * sb + (int64_t)(bh % Hq) * sh + (int64_t)sidx * ss + cb) = o;
+  }
+}
+
+template <int D>
+static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
+  using C = BwdCfg<D>;
+  const fa4b_attn_dims& d = a.dims;
+  const fa4b_attn_ws_layout l = make_ws_layout(d);
+  uint8_t* ws = static_cast<uint8_t*>(a.ws);
+  const uint64_t S = d.S, nq = (uint64_t)d.B * d.Hq, nk = (uint64_t)d.B * d.Hkv;
+  CUtensorMap m_kc, m_k8, m_v8, m_qc, m_q8, m_do;
+  if (int s = make_tensor_map(&m_kc, ws + l.k_codes, 1, D / 2, S, nk, D / 2, S * (D / 2), D / 2, 128)) return s;
+  if (int s = make_tensor_map(&m_k8, ws + l.k_fp8, 1, D, S, nk, D, S * D, D, 128)) return s;
+  if (int s = make_tensor_map(&m_v8, ws + l.v_fp8, 1, D, S, nk, D, S * D, D, 128)) return s;
+  if (int s = make_tensor_map(&m_qc, ws + l.q_codes, 1, D / 2, S, nq, D / 2, S * (D / 2), D / 2, C::QT)) return s;
+  if (int s = make_tensor_map(&m_q8, ws + l.q_fp8, 1, D, S, nq, D, S * D, D, C::QT)) return s;
+  if (int s = make_tensor_map(&m_do, ws + l.do_fp8, 1, D, S, nq, D, S * D, D, C::QT)) return s;
+  BwdParams p{};
+  p.B = d.B; p.Hq = d.Hq; p.Hkv = d.Hkv; p.S = d.S;
+  p.scale = resolve_scale(d);
+  p.q_sf = ws + l.q_scales; p.k_sf = ws + l.k_scales;
+  p.q_global = reinterpret_cast<const float*>(ws + l.q_global);
+  p.k_global = reinterpret_cast<const float*>(ws + l.k_global);
+  p.lstat = reinterpret_cast<const float*>(ws + l.lstat);
+  p.dstat = reinterpret_cast<const float*>(ws + l.dstat);
+  p.dq_accum = reinterpret_cast<float*>(ws + l.dq_accum);
+  p.dk = static_cast<__nv_bfloat16*>(a.dk); p.dk_sb = a.dk_strides.batch; p.dk_sh = a.dk_strides.head; p.dk_ss = a.dk_strides.seq;
+  p.dv = static_cast<__nv_bfloat16*>(a.dv); p.dv_sb = a.dv_strides.batch; p.dv_sh = a.dv_strides.head; p.dv_ss = a.dv_strides.seq;
+  p.status = reinterpret_cast<uint32_t*>(ws + l.status);
+  FA4B_CUDA(cudaMemsetAsync(p.status, 0, 16, st));
+  FA4B_CUDA(cudaMemsetAsync(p.dq_accum, 0, nq * S * D * sizeof(float), st));
+  const int smem = (int)sizeof(BwdSmem<D>) + 1024;
+  static std::mutex mu;
+  static bool configured[64] = {};
+  int dev = 0;
+  FA4B_CUDA(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 64 && !configured[dev]) {
+      FA4B_CUDA(cudaFuncSetAttribute(attn_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      configured[dev] = true;
+    }
+  }
+  const unsigned grid = (unsigned)(nk * (S / 128));
+  attn_bwd_kernel<D><<<grid, kBwdThreads, smem, st>>>(p, m_kc, m_k8, m_v8, m_qc, m_q8, m_do);
+  FA4B_CUDA(cudaGetLastError());
+  const int64_t n_rows = (int64_t)nq * S;
+  const unsigned cgrid = (unsigned)std::min<int64_t>((n_rows * (D / 8) + 255) / 256, 148 * 16);
+  dq_convert_kernel<D><<<cgrid, 256, 0, st>>>(p.dq_accum, d.Hq, d.S, n_rows, static_cast<__nv_bfloat16*>(a.dq), a.dq_strides.batch,
+                                              a.dq_strides.head, a.dq_strides.seq);
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
+}
+
+static int check_out(const void* ptr, const fa4b_strides& s, const char* name) {
+  FA4B_REQUIRE(ptr != nullptr, FA4B_BAD_ARG, "%s is NULL", name);
+  FA4B_REQUIRE((reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && s.batch % 8 == 0 && s.head % 8 == 0 && s.seq % 8 == 0, FA4B_BAD_ALIGN,
+               "%s: base must be 16-byte aligned and strides multiples of 8 elements", name);
+  return FA4B_OK;
+}
+
+int launch_attn_bwd(const fa4b_attn_bwd_args& a, cudaStream_t st) {
+  if (int s = check_dims(a.dims)) return s;
+  FA4B_REQUIRE(a.dims.pv_format == FA4B_PV_FP8_E4M3, FA4B_UNSUPPORTED, "the MXFP4 P.V backward is not built");
+  if (int s = check_out(a.dq, a.dq_strides, "dq")) return s;
+  if (int s = check_out(a.dk, a.dk_strides, "dk")) return s;
+  if (int s = check_out(a.dv, a.dv_strides, "dv")) return s;
+  if (int s = launch_attn_bwd_preprocess(a, st)) return s;
+  return a.dims.D == 128 ? bwd_impl<128>(a, st) : bwd_impl<64>(a, st);
+}
+
+void fill_bwd_info(fa4b_info* out) {
+  out->bwd_threads = kBwdThreads;
+  out->bwd_smem_bytes = (int)sizeof(BwdSmem<128>) + 1024;
+  out->bwd_tmem_columns = 512;
+}
+
+}  // namespace fa4b

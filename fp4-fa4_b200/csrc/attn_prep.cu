@@ -1,0 +1,241 @@
+// Memory-bound operand publication for the attention kernels: per-(batch, head)
+// amax, NVFP4 codes + scale pages + E4M3 copies of Q and K, E4M3 V, and the
+// backward's E5M2 dO with its two row statistics.
+#include "attn.cuh"
+
+namespace fa4b {
+
+__device__ __forceinline__ float warp_max_f(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+struct HeadView {
+  const __nv_bfloat16* p;
+  int64_t sb, sh, ss;  // element strides: batch, head, sequence
+  int H;
+  __device__ __forceinline__ const __nv_bfloat16* row(int bh, int s) const {
+    return p + (int64_t)(bh / H) * sb + (int64_t)(bh % H) * sh + (int64_t)s * ss;
+  }
+};
+
+// grid (row chunks, B*H): amax over the [S, D] slice of one head
+template <int D>
+__global__ void __launch_bounds__(256) head_amax_kernel(HeadView x, int S, int rows_per_cta, int* __restrict__ amax_bits) {
+  const int bh = blockIdx.y;
+  constexpr int kVec = D / 8;             // 16-byte chunks per row
+  constexpr int kRowsPerPass = 256 / kVec;
+  const int r0 = blockIdx.x * rows_per_cta;
+  const int sub = threadIdx.x / kVec, c = threadIdx.x % kVec;
+  __nv_bfloat162 acc = __float2bfloat162_rn(0.f);
+  for (int r = r0 + sub; r < min(S, r0 + rows_per_cta); r += kRowsPerPass) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(x.row(bh, r)) + c);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc = __hmax2(acc, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[k])));
+  }
+  float m = warp_max_f(fmaxf(__bfloat162float(acc.x), __bfloat162float(acc.y)));
+  __shared__ float wm[8];
+  if ((threadIdx.x & 31) == 0) wm[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k) m = fmaxf(m, wm[k]);
+    atomicMax(amax_bits + bh, __float_as_int(m));
+  }
+}
+
+// grid (S/128, B*H): NVFP4 codes, scale pages, global scale and (optionally) E4M3(4x) of one 128-row tile
+template <int D>
+__global__ void __launch_bounds__(256) quant_heads_kernel(HeadView x, int S, const int* __restrict__ amax_bits,
+                                                          uint8_t* __restrict__ codes, uint8_t* __restrict__ pages,
+                                                          float* __restrict__ gscale, uint8_t* __restrict__ fp8) {
+  constexpr int kKb = D / 16, kPages = D / 64;
+  __shared__ __align__(16) uint8_t sc[kPages * 512];
+  const int bh = blockIdx.y, tile = blockIdx.x, t = threadIdx.x;
+  const float amax = __int_as_float(amax_bits[bh]);
+  const float g = amax / kNvfp4GlobalDiv;
+  if (tile == 0 && t == 0) gscale[bh] = g;
+  const bool all_zero = !(amax > 0.f);
+#pragma unroll
+  for (int i = 0; i < (128 * kKb) / 256; ++i) {
+    const int b = t + i * 256;
+    const int r = b / kKb, kb = b % kKb;
+    const int s = tile * 128 + r;
+    const uint4* src = reinterpret_cast<const uint4*>(x.row(bh, s) + kb * 16);
+    const uint4 lo = __ldg(src), hi = __ldg(src + 1);
+    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    float xv[16];
+    float bamax = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      xv[2 * k] = bf16_bits_to_f32(w[k] & 0xffffu);
+      xv[2 * k + 1] = bf16_bits_to_f32(w[k] >> 16);
+      bamax = fmaxf(bamax, fmaxf(fabsf(xv[2 * k]), fabsf(xv[2 * k + 1])));
+    }
+    uint32_t packed[2] = {0, 0};
+    uint32_t sbyte = 0;
+    if (!all_zero) {
+      float safe;
+      sbyte = nvfp4_block_scale(bamax, g, safe);
+      quantize_block<16>(xv, safe, packed);
+    }
+    const size_t row_index = (size_t)bh * S + s;
+    *reinterpret_cast<uint2*>(codes + row_index * (D / 2) + kb * 8) = make_uint2(packed[0], packed[1]);
+    sc[(kb >> 2) * 512 + page_offset(r, kb)] = (uint8_t)sbyte;
+    if (fp8) {
+      uint4 o;
+      o.x = cvt_e4m3x4(4.f * xv[0], 4.f * xv[1], 4.f * xv[2], 4.f * xv[3]);
+      o.y = cvt_e4m3x4(4.f * xv[4], 4.f * xv[5], 4.f * xv[6], 4.f * xv[7]);
+      o.z = cvt_e4m3x4(4.f * xv[8], 4.f * xv[9], 4.f * xv[10], 4.f * xv[11]);
+      o.w = cvt_e4m3x4(4.f * xv[12], 4.f * xv[13], 4.f * xv[14], 4.f * xv[15]);
+      *reinterpret_cast<uint4*>(fp8 + row_index * D + kb * 16) = o;
+    }
+  }
+  __syncthreads();
+  if (t < kPages * 32) {
+    uint8_t* dst = pages + (((size_t)bh * (S / 128) + tile) * kPages) * 512 + t * 16;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&sc[t * 16]);
+  }
+}
+
+// E4M3(4x) of [B,H,S,D] through strides into a dense [B*H, S, D]
+template <int D>
+__global__ void __launch_bounds__(256) heads_to_fp8_kernel(HeadView x, int S, int64_t n_chunks, uint8_t* __restrict__ out) {
+  constexpr int kPerRow = D / 16;
+  for (int64_t c = (int64_t)blockIdx.x * 256 + threadIdx.x; c < n_chunks; c += (int64_t)gridDim.x * 256) {
+    const int64_t row = c / kPerRow;
+    const int kb = (int)(c % kPerRow);
+    const uint4* src = reinterpret_cast<const uint4*>(x.row((int)(row / S), (int)(row % S)) + kb * 16);
+    const uint4 lo = __ldg(src), hi = __ldg(src + 1);
+    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      o[k] = cvt_e4m3x4(4.f * bf16_bits_to_f32(w[2 * k] & 0xffffu), 4.f * bf16_bits_to_f32(w[2 * k] >> 16),
+                        4.f * bf16_bits_to_f32(w[2 * k + 1] & 0xffffu), 4.f * bf16_bits_to_f32(w[2 * k + 1] >> 16));
+    *reinterpret_cast<uint4*>(out + row * D + kb * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+__device__ __forceinline__ float e5m2_to_f32(uint32_t byte) { return __half2float(__ushort_as_half((unsigned short)(byte << 8))); }
+
+// dO5 = E5M2(4 dO); dstat = -4 sum_d O * float(dO5); lstat = 8 - LSE * log2e
+template <int D>
+__global__ void __launch_bounds__(256) bwd_preprocess_kernel(HeadView o, HeadView dout, const float* __restrict__ lse, int S,
+                                                             int64_t n_rows, uint8_t* __restrict__ do_fp8,
+                                                             float* __restrict__ dstat, float* __restrict__ lstat) {
+  constexpr int kLanes = D / 8;  // threads per row, 8 elements each
+  const int64_t row = (int64_t)blockIdx.x * (256 / kLanes) + threadIdx.x / kLanes;
+  const int c = threadIdx.x % kLanes;
+  float acc = 0.f;
+  if (row < n_rows) {
+    const int bh = (int)(row / S), s = (int)(row % S);
+    const uint4 ov = __ldg(reinterpret_cast<const uint4*>(o.row(bh, s)) + c);
+    const uint4 dv = __ldg(reinterpret_cast<const uint4*>(dout.row(bh, s)) + c);
+    const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w}, dw[4] = {dv.x, dv.y, dv.z, dv.w};
+    uint32_t packed[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      packed[k] = cvt_e5m2x4(4.f * bf16_bits_to_f32(dw[2 * k] & 0xffffu), 4.f * bf16_bits_to_f32(dw[2 * k] >> 16),
+                             4.f * bf16_bits_to_f32(dw[2 * k + 1] & 0xffffu), 4.f * bf16_bits_to_f32(dw[2 * k + 1] >> 16));
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const uint32_t ob = ow[2 * k + (e >> 1)];
+        const float of = bf16_bits_to_f32((e & 1) ? (ob >> 16) : (ob & 0xffffu));
+        acc = fmaf(of, e5m2_to_f32((packed[k] >> (8 * e)) & 0xffu), acc);
+      }
+    }
+    *reinterpret_cast<uint2*>(do_fp8 + row * D + c * 8) = make_uint2(packed[0], packed[1]);
+  }
+#pragma unroll
+  for (int off = kLanes / 2; off; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (row < n_rows && c == 0) {
+    dstat[row] = -4.0f * acc;
+    lstat[row] = kPLift - lse[row] * kLog2e;
+  }
+}
+
+static int check_view(const void* p, const fa4b_strides& s, const char* name) {
+  FA4B_REQUIRE(p != nullptr, FA4B_BAD_ARG, "%s is NULL", name);
+  FA4B_REQUIRE((reinterpret_cast<uintptr_t>(p) & 15) == 0 && s.batch % 8 == 0 && s.head % 8 == 0 && s.seq % 8 == 0, FA4B_BAD_ALIGN,
+               "%s: base must be 16-byte aligned and strides multiples of 8 elements", name);
+  return FA4B_OK;
+}
+
+static HeadView view(const void* p, const fa4b_strides& s, int H) {
+  return HeadView{static_cast<const __nv_bfloat16*>(p), s.batch, s.head, s.seq, H};
+}
+
+template <int D>
+static int prepare_impl(const fa4b_attn_prepare_args& a, cudaStream_t st) {
+  const fa4b_attn_dims& d = a.dims;
+  const fa4b_attn_ws_layout l = make_ws_layout(d);
+  uint8_t* ws = static_cast<uint8_t*>(a.ws);
+  const int nq = d.B * d.Hq, nk = d.B * d.Hkv;
+  int* amax_bits = reinterpret_cast<int*>(ws + l.amax_bits);
+  FA4B_CUDA(cudaMemsetAsync(amax_bits, 0, (size_t)(nq + nk) * 4, st));
+  const int rows_per_cta = 512;
+  const unsigned chunks = (unsigned)((d.S + rows_per_cta - 1) / rows_per_cta);
+  const HeadView q = view(a.q, a.q_strides, d.Hq), k = view(a.k, a.k_strides, d.Hkv), v = view(a.v, a.v_strides, d.Hkv);
+  head_amax_kernel<D><<<dim3(chunks, nq), 256, 0, st>>>(q, d.S, rows_per_cta, amax_bits);
+  head_amax_kernel<D><<<dim3(chunks, nk), 256, 0, st>>>(k, d.S, rows_per_cta, amax_bits + nq);
+  quant_heads_kernel<D><<<dim3(d.S / 128, nq), 256, 0, st>>>(q, d.S, amax_bits, ws + l.q_codes, ws + l.q_scales,
+                                                             reinterpret_cast<float*>(ws + l.q_global), ws + l.q_fp8);
+  quant_heads_kernel<D><<<dim3(d.S / 128, nk), 256, 0, st>>>(k, d.S, amax_bits + nq, ws + l.k_codes, ws + l.k_scales,
+                                                             reinterpret_cast<float*>(ws + l.k_global), ws + l.k_fp8);
+  const int64_t n_chunks = (int64_t)nk * d.S * (D / 16);
+  const unsigned grid = (unsigned)std::min<int64_t>((n_chunks + 255) / 256, 148 * 16);
+  heads_to_fp8_kernel<D><<<grid, 256, 0, st>>>(v, d.S, n_chunks, ws + l.v_fp8);
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
+}
+
+int launch_attn_prepare(const fa4b_attn_prepare_args& a, cudaStream_t st) {
+  if (int s = check_dims(a.dims)) return s;
+  if (int s = check_view(a.q, a.q_strides, "q")) return s;
+  if (int s = check_view(a.k, a.k_strides, "k")) return s;
+  if (int s = check_view(a.v, a.v_strides, "v")) return s;
+  FA4B_REQUIRE(a.ws != nullptr && (reinterpret_cast<uintptr_t>(a.ws) & 1023) == 0, FA4B_BAD_ALIGN,
+               "workspace must be non-NULL and 1024-byte aligned");
+  return a.dims.D == 128 ? prepare_impl<128>(a, st) : prepare_impl<64>(a, st);
+}
+
+template <int D>
+static int preprocess_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
+  const fa4b_attn_dims& d = a.dims;
+  const fa4b_attn_ws_layout l = make_ws_layout(d);
+  uint8_t* ws = static_cast<uint8_t*>(a.ws);
+  const int64_t n_rows = (int64_t)d.B * d.Hq * d.S;
+  constexpr int kRowsPerCta = 256 / (D / 8);
+  bwd_preprocess_kernel<D><<<(unsigned)((n_rows + kRowsPerCta - 1) / kRowsPerCta), 256, 0, st>>>(
+      view(a.o, a.o_strides, d.Hq), view(a.dout, a.do_strides, d.Hq), a.lse, d.S, n_rows, ws + l.do_fp8,
+      reinterpret_cast<float*>(ws + l.dstat), reinterpret_cast<float*>(ws + l.lstat));
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
+}
+
+int launch_attn_bwd_preprocess(const fa4b_attn_bwd_args& a, cudaStream_t st) {
+  if (int s = check_dims(a.dims)) return s;
+  if (int s = check_view(a.o, a.o_strides, "o")) return s;
+  if (int s = check_view(a.dout, a.do_strides, "dout")) return s;
+  FA4B_REQUIRE(a.lse != nullptr, FA4B_BAD_ARG, "lse is NULL");
+  FA4B_REQUIRE(a.ws != nullptr && (reinterpret_cast<uintptr_t>(a.ws) & 1023) == 0, FA4B_BAD_ALIGN,
+               "workspace must be non-NULL and 1024-byte aligned");
+  return a.dims.D == 128 ? preprocess_impl<128>(a, st) : preprocess_impl<64>(a, st);
+}
+
+}  // namespace fa4b
+
+using namespace fa4b;
+
+extern "C" int fa4b_attn_prepare(const fa4b_attn_prepare_args* a, void* stream) {
+  FA4B_REQUIRE(a != nullptr, FA4B_BAD_ARG, "args is NULL");
+  return launch_attn_prepare(*a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fa4b_attn_bwd_preprocess(const fa4b_attn_bwd_args* a, void* stream) {
+  FA4B_REQUIRE(a != nullptr, FA4B_BAD_ARG, "args is NULL");
+  return launch_attn_bwd_preprocess(*a, static_cast<cudaStream_t>(stream));
+}

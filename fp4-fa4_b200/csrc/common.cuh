@@ -1,0 +1,124 @@
+// Shared device/host helpers: status plumbing, number-format conversions.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/fa4b.h"
+
+namespace fa4b {
+
+void set_error(const char* fmt, ...);
+
+#define FA4B_REQUIRE(cond, status, ...)        \
+  do {                                         \
+    if (!(cond)) {                             \
+      ::fa4b::set_error(__VA_ARGS__);          \
+      return (status);                         \
+    }                                          \
+  } while (0)
+
+#define FA4B_CUDA(call)                                                          \
+  do {                                                                           \
+    cudaError_t e__ = (call);                                                    \
+    if (e__ != cudaSuccess) {                                                    \
+      ::fa4b::set_error("%s failed: %s", #call, cudaGetErrorString(e__));        \
+      return FA4B_CUDA_ERROR;                                                    \
+    }                                                                            \
+  } while (0)
+
+constexpr float kFltMin = 1.17549435e-38f;
+constexpr float kNvfp4GlobalDiv = 2688.0f;  // 6 * 448
+
+// ---- conversions ------------------------------------------------------------
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t b16) { return __uint_as_float(b16 << 16); }
+
+// two f32 -> one byte of two E2M1 codes; `lo` lands in the low nibble
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
+  uint32_t r;
+  asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u32.u8 %0, t; }" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// two f32 -> two E4M3 bytes (lo in bits 0-7)
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ uint32_t cvt_e5m2x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
+  return cvt_e4m3x2(a, b) | (cvt_e4m3x2(c, d) << 16);
+}
+__device__ __forceinline__ uint32_t cvt_e5m2x4(float a, float b, float c, float d) {
+  return cvt_e5m2x2(a, b) | (cvt_e5m2x2(c, d) << 16);
+}
+__device__ __forceinline__ float e4m3_to_f32(uint32_t byte) {
+  uint32_t h2;
+  uint16_t in = (uint16_t)byte;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(in));
+  return __half2float(__ushort_as_half((unsigned short)(h2 & 0xffff)));
+}
+__device__ __forceinline__ float e2m1_to_f32(uint32_t code) {
+  float mag;
+  switch (code & 7u) {
+    case 0: mag = 0.f; break;
+    case 1: mag = .5f; break;
+    case 2: mag = 1.f; break;
+    case 3: mag = 1.5f; break;
+    case 4: mag = 2.f; break;
+    case 5: mag = 3.f; break;
+    case 6: mag = 4.f; break;
+    default: mag = 6.f; break;
+  }
+  return (code & 8u) ? -mag : mag;
+}
+
+// byte offset of the scale of (row, kblock) inside its 512-byte page
+__device__ __host__ __forceinline__ uint32_t page_offset(uint32_t row, uint32_t kblock) {
+  return (row & 31u) * 16u + ((row & 127u) >> 5) * 4u + (kblock & 3u);
+}
+
+// ---- one quantisation block ----------------------------------------------------
+// Codes of n (16 or 32) values divided by `safe`, equal to E2M1_rne(x / safe) with
+// an IEEE division.  The fast path multiplies by the reciprocal; that product is
+// within 3 ulp of the rounded quotient, and every E2M1 rounding threshold has
+// zero low 21 mantissa bits, so a product at least 8 ulp away from such a
+// pattern rounds to the same code.  Blocks with a closer product redo the
+// division exactly.
+template <int N>
+__device__ __forceinline__ void quantize_block(const float (&x)[N], float safe, uint32_t (&packed)[N / 8]) {
+  const float r = 1.0f / safe;
+  float q[N];
+  bool danger = false;
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    q[i] = x[i] * r;
+    danger |= ((__float_as_uint(q[i]) + 8u) & 0x1FFFFFu) <= 16u;
+  }
+  if (danger) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) q[i] = x[i] / safe;
+  }
+#pragma unroll
+  for (int w = 0; w < N / 8; ++w) {
+    uint32_t v = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v |= cvt_e2m1x2(q[w * 8 + 2 * j], q[w * 8 + 2 * j + 1]) << (8 * j);
+    packed[w] = v;
+  }
+}
+
+// NVFP4 block scale: s = E4M3(clamp(bamax / 6 / g)), returns the byte and safe = max(s*g, FLT_MIN)
+__device__ __forceinline__ uint32_t nvfp4_block_scale(float bamax, float g, float& safe) {
+  const float s = (bamax / 6.0f) / g;
+  const uint32_t byte = cvt_e4m3x2(s, 0.f) & 0xffu;
+  safe = fmaxf(e4m3_to_f32(byte) * g, kFltMin);
+  return byte;
+}
+
+}  // namespace fa4b

@@ -1,0 +1,217 @@
+// Tensor-core self tests: one 128x128xK product per launch through the same
+// tcgen05 instruction forms, shared-memory descriptors, swizzles and TMEM
+// layouts that the attention kernels use.  Also home of the tensor-map helper.
+#include <mutex>
+
+#include "common.cuh"
+#include "tc_sm100.cuh"
+
+namespace fa4b {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+int make_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t rows, uint64_t outer,
+                    uint64_t row_stride_bytes, uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  FA4B_REQUIRE(fn != nullptr, FA4B_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from this driver");
+  FA4B_REQUIRE(elem_bytes == 1 || elem_bytes == 2, FA4B_BAD_ARG, "tensor map element size %d", elem_bytes);
+  const uint32_t inner_bytes = box_inner * elem_bytes;
+  CUtensorMapSwizzle swz = inner_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                           : inner_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                           : inner_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                               : CU_TENSOR_MAP_SWIZZLE_NONE;
+  const bool three = outer > 0;  // outer == 0 asks for a 2-D map
+  cuuint64_t dims[3] = {inner, rows, outer ? outer : 1};
+  cuuint64_t strides[2] = {row_stride_bytes, outer_stride_bytes};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, three ? 3 : 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  FA4B_REQUIRE(r == CUDA_SUCCESS, FA4B_CUDA_ERROR, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return FA4B_OK;
+}
+
+struct GateSmem {
+  alignas(1024) uint8_t a[128 * 128];
+  alignas(1024) uint8_t b[128 * 128];
+  alignas(16) uint8_t sfa[2 * 512];
+  alignas(16) uint8_t sfb[2 * 512];
+  alignas(8) uint64_t bar;
+  alignas(8) uint64_t tma_bar;
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+// kinds: see fa4b_microgate in the public header; kind 7 = kind 1 with TMA loads
+__global__ void __launch_bounds__(128, 1) microgate_kernel(int kind, int K, const uint8_t* __restrict__ a, const uint8_t* __restrict__ b,
+                                                           const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb,
+                                                           float* __restrict__ out, uint32_t* status,
+                                                           const __grid_constant__ CUtensorMap map_a,
+                                                           const __grid_constant__ CUtensorMap map_b) {
+  extern __shared__ uint8_t raw[];
+  GateSmem& s = *reinterpret_cast<GateSmem*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  const int t = threadIdx.x, warp = t >> 5;
+  const bool fp4 = kind == 0 || kind == 6;
+  const bool a_mn = kind == 4, b_mn = kind == 3 || kind == 4 || kind == 5;
+  const bool a_tmem = kind == 5;
+  // bytes per operand row in shared memory
+  const uint32_t a_row = a_mn ? 128u : (fp4 ? K / 2 : K), b_row = b_mn ? 128u : (fp4 ? K / 2 : K);
+  const uint32_t a_rows = a_mn ? K : 128u, b_rows = b_mn ? K : 128u;
+
+  if (t == 0) {
+    mbar_init(&s.bar, 1);
+    mbar_init(&s.tma_bar, 1);
+    s.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) tmem_alloc(&s.tmem_base, 256);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = s.tmem_base;
+  const uint32_t tm_d = tm, tm_a = tm + 128, tm_sfa = tm + 192, tm_sfb = tm + 208;
+
+  bool ok = true;
+  if (kind == 7) {
+    if (t == 0) {
+      mbar_expect_tx(&s.tma_bar, 2 * 128 * K);
+      tma_load_2d(s.a, &map_a, 0, 0, &s.tma_bar);
+      tma_load_2d(s.b, &map_b, 0, 0, &s.tma_bar);
+    }
+    ok = mbar_wait(&s.tma_bar, 0, &s.abort_flag, status, 1);
+  } else {
+    // manual swizzled staging, 16-byte chunks
+    if (!a_tmem) {
+      const uint32_t chunks = a_rows * a_row / 16;
+      for (uint32_t c = t; c < chunks; c += 128) {
+        const uint32_t r = (c * 16) / a_row, cb = (c * 16) % a_row;
+        *reinterpret_cast<uint4*>(&s.a[swizzled_offset(r, cb, a_row)]) = *reinterpret_cast<const uint4*>(a + (size_t)r * a_row + cb);
+      }
+    }
+    const uint32_t chunks = b_rows * b_row / 16;
+    for (uint32_t c = t; c < chunks; c += 128) {
+      const uint32_t r = (c * 16) / b_row, cb = (c * 16) % b_row;
+      *reinterpret_cast<uint4*>(&s.b[swizzled_offset(r, cb, b_row)]) = *reinterpret_cast<const uint4*>(b + (size_t)r * b_row + cb);
+    }
+    if (fp4) {
+      const int pages = kind == 0 ? K / 64 : (K + 127) / 128;
+      for (int c = t; c < pages * 32; c += 128) {
+        *reinterpret_cast<uint4*>(&s.sfa[c * 16]) = *reinterpret_cast<const uint4*>(sfa + c * 16);
+        *reinterpret_cast<uint4*>(&s.sfb[c * 16]) = *reinterpret_cast<const uint4*>(sfb + c * 16);
+      }
+    }
+  }
+  if (a_tmem) {
+    // this thread's row of A (K bytes of E4M3) goes to TMEM columns tm_a .. tm_a + K/4
+    const uint32_t lane_addr = tm_a + ((uint32_t)(warp * 32) << 16);
+    for (int k0 = 0; k0 < K; k0 += 32) {
+      uint32_t w[8];
+      const uint4 v0 = *reinterpret_cast<const uint4*>(a + (size_t)t * K + k0);
+      const uint4 v1 = *reinterpret_cast<const uint4*>(a + (size_t)t * K + k0 + 16);
+      w[0] = v0.x; w[1] = v0.y; w[2] = v0.z; w[3] = v0.w; w[4] = v1.x; w[5] = v1.y; w[6] = v1.z; w[7] = v1.w;
+      tmem_st8(lane_addr + k0 / 4, w);
+    }
+    tmem_st_wait();
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  if (t == 0 && ok) {
+    const uint32_t sa = smem_u32(s.a), sb = smem_u32(s.b);
+    if (fp4) {
+      const bool mx = kind == 6;
+      const int pages = mx ? (K + 127) / 128 : K / 64;
+      for (int p = 0; p < pages; ++p) {
+        tmem_cp_page(tm_sfa + 4 * p, make_page_desc(smem_u32(s.sfa + 512 * p)));
+        tmem_cp_page(tm_sfb + 4 * p, make_page_desc(smem_u32(s.sfb + 512 * p)));
+      }
+      for (int k = 0; k < K / 64; ++k) {
+        const uint64_t ad = make_tile_desc(sa + 32 * k, a_row), bd = make_tile_desc(sb + 32 * k, b_row);
+        if (mx) {
+          const uint32_t id = idesc_fp4(128, 128, 1, (k & 1) * 2, (k & 1) * 2);
+          mma_mxfp4_ss(tm_d, ad, bd, id, tm_sfa + 4 * (k / 2), tm_sfb + 4 * (k / 2), k > 0);
+        } else {
+          mma_nvfp4_ss(tm_d, ad, bd, idesc_fp4(128, 128, 0, 0, 0), tm_sfa + 4 * k, tm_sfb + 4 * k, k > 0);
+        }
+      }
+    } else {
+      const uint32_t id = idesc_f8(128, 128, 0, kind == 2 ? 1 : 0, a_mn, b_mn);
+      for (int k = 0; k < K / 32; ++k) {
+        // K-major: 32 bytes further along the row; MN-major: 32 rows further down
+        const uint64_t bd = make_tile_desc(sb + (b_mn ? 32 * 128 * k : 32 * k), b_row);
+        if (a_tmem) {
+          mma_f8_ts(tm_d, tm_a + 8 * k, bd, id, k > 0);
+        } else {
+          const uint64_t ad = make_tile_desc(sa + (a_mn ? 32 * 128 * k : 32 * k), a_row);
+          mma_f8_ss(tm_d, ad, bd, id, k > 0);
+        }
+      }
+    }
+    mma_commit(&s.bar);
+  }
+  if (ok) ok = mbar_wait(&s.bar, 0, &s.abort_flag, status, 2);
+  tc_fence_after();
+  if (ok) {
+    const uint32_t lane_addr = tm_d + ((uint32_t)(warp * 32) << 16);
+#pragma unroll 1
+    for (int c0 = 0; c0 < 128; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(lane_addr + c0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) out[(size_t)t * 128 + c0 + j] = __uint_as_float(r[j]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, 256);
+}
+
+}  // namespace fa4b
+
+using namespace fa4b;
+
+extern "C" int fa4b_microgate(int kind, int K, const void* a, const void* b, const void* sfa, const void* sfb, float* out,
+                              uint32_t* status_out, void* stream) {
+  FA4B_REQUIRE(kind >= 0 && kind <= 7, FA4B_UNSUPPORTED, "microgate kind %d", kind);
+  FA4B_REQUIRE(a && b && out && status_out, FA4B_BAD_ARG, "microgate: NULL pointer");
+  const bool fp4 = kind == 0 || kind == 6;
+  FA4B_REQUIRE(!fp4 || (sfa && sfb), FA4B_BAD_ARG, "microgate: block-scaled kinds need scale pages");
+  const bool mn = kind == 3 || kind == 4 || kind == 5;
+  if (fp4) FA4B_REQUIRE(K == 64 || K == 128, FA4B_BAD_SHAPE, "microgate: FP4 K must be 64 or 128");
+  else if (mn) FA4B_REQUIRE(K % 32 == 0 && K >= 32 && K <= 128, FA4B_BAD_SHAPE, "microgate: K must be 32..128, multiple of 32");
+  else FA4B_REQUIRE(K == 32 || K == 64 || K == 128, FA4B_BAD_SHAPE, "microgate: K must be 32, 64 or 128");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  FA4B_CUDA(cudaMemsetAsync(status_out, 0, 4 * sizeof(uint32_t), st));
+  CUtensorMap ma{}, mb{};
+  if (kind == 7) {
+    if (int s = make_tensor_map(&ma, a, 1, K, 128, 0, K, 0, K, 128)) return s;
+    if (int s = make_tensor_map(&mb, b, 1, K, 128, 0, K, 0, K, 128)) return s;
+  }
+  const int smem = sizeof(GateSmem) + 1024;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(microgate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
+  FA4B_CUDA(attr_err);
+  microgate_kernel<<<1, 128, smem, st>>>(kind, K, static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(b),
+                                         static_cast<const uint8_t*>(sfa), static_cast<const uint8_t*>(sfb), out, status_out, ma, mb);
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
+}

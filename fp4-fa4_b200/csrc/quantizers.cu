@@ -1,0 +1,458 @@
+// Memory-bound block quantizers: amax, NVFP4 (row-wise + transposed), fused
+// RMSNorm + NVFP4, MXFP4, and the decode utilities.  All are HBM-bound byte
+// work: 128-bit loads, warp-shuffle reductions, packed e2m1 stores, one
+// 128x128 tile per CTA staged in shared memory so that the transposed
+// quantisation reads the input once.
+#include <cstdarg>
+
+#include "common.cuh"
+
+namespace fa4b {
+
+static thread_local char g_error[512] = "";
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+const char* last_error() { return g_error; }
+
+// ------------------------------------------------------------------ amax
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ __nv_bfloat162 absmax2(__nv_bfloat162 acc, uint32_t w) {
+  return __hmax2(acc, __habs2(*reinterpret_cast<__nv_bfloat162*>(&w)));
+}
+
+__global__ void __launch_bounds__(256) amax_kernel(const uint4* __restrict__ x, int64_t n_vec, const __nv_bfloat16* tail,
+                                                   int n_tail, float* __restrict__ amax) {
+  __nv_bfloat162 acc = __float2bfloat162_rn(0.f);
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 v = __ldg(x + i);
+    acc = absmax2(absmax2(absmax2(absmax2(acc, v.x), v.y), v.z), v.w);
+  }
+  float m = fmaxf(__bfloat162float(acc.x), __bfloat162float(acc.y));
+  if (blockIdx.x == 0 && threadIdx.x < n_tail) m = fmaxf(m, fabsf(__bfloat162float(tail[threadIdx.x])));
+  m = warp_max(m);
+  __shared__ float wm[8];
+  if ((threadIdx.x & 31) == 0) wm[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    m = warp_max(threadIdx.x < 8 ? wm[threadIdx.x] : 0.f);
+    if (threadIdx.x == 0) atomicMax(reinterpret_cast<int*>(amax), __float_as_int(m));  // non-negative floats order as ints
+  }
+}
+
+// ------------------------------------------------------------------ RMSNorm statistics
+// One CTA per row: inv_rms, and the amax of y = bf16((x*inv_rms)*gamma).  The row stays in
+// registers between the two reductions, so x is read once here.
+template <int VEC_PER_THREAD>
+__global__ void __launch_bounds__(256) rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld, int cols,
+                                                            const __nv_bfloat16* __restrict__ gamma, float eps,
+                                                            float* __restrict__ inv_rms, float* __restrict__ amax) {
+  const int64_t row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * ld);
+  const uint4* gr = reinterpret_cast<const uint4*>(gamma);
+  const int n_vec = cols / 8;
+  uint4 v[VEC_PER_THREAD];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VEC_PER_THREAD; ++j) {
+    const int i = threadIdx.x + j * 256;
+    v[j] = (i < n_vec) ? __ldg(xr + i) : make_uint4(0, 0, 0, 0);
+    const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float a = bf16_bits_to_f32(w[k] & 0xffffu), b = bf16_bits_to_f32(w[k] >> 16);
+      ss = fmaf(a, a, ss);
+      ss = fmaf(b, b, ss);
+    }
+  }
+  __shared__ float red[8];
+  __shared__ float s_inv;
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k];
+    const float inv = 1.0f / sqrtf(t / (float)cols + eps);
+    s_inv = inv;
+    inv_rms[row] = inv;
+  }
+  __syncthreads();
+  const float inv = s_inv;
+  float m = 0.f;
+#pragma unroll
+  for (int j = 0; j < VEC_PER_THREAD; ++j) {
+    const int i = threadIdx.x + j * 256;
+    if (i < n_vec) {
+      const uint4 gv = __ldg(gr + i);
+      const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float a = (bf16_bits_to_f32(w[k] & 0xffffu) * inv) * bf16_bits_to_f32(gw[k] & 0xffffu);
+        const float b = (bf16_bits_to_f32(w[k] >> 16) * inv) * bf16_bits_to_f32(gw[k] >> 16);
+        m = fmaxf(m, fmaxf(fabsf(__bfloat162float(__float2bfloat16_rn(a))), fabsf(__bfloat162float(__float2bfloat16_rn(b)))));
+      }
+    }
+  }
+  m = warp_max(m);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t = fmaxf(t, red[k]);
+    atomicMax(reinterpret_cast<int*>(amax), __float_as_int(t));
+  }
+}
+
+// ------------------------------------------------------------------ NVFP4 tile kernel
+constexpr int kTile = 128;
+constexpr int kPitch = kTile + 8;  // bf16 elements; 272-byte rows keep 16-byte alignment
+
+struct Nvfp4Params {
+  const __nv_bfloat16* x;
+  int64_t ld;
+  int64_t rows, cols;
+  const __nv_bfloat16* gamma;  // NORM only
+  const float* inv_rms;        // NORM only
+  __nv_bfloat16* y_out;        // NORM only, optional
+  const float* amax;
+  float* global_scale;
+  uint8_t* codes_row;
+  uint8_t* scales_row;
+  uint8_t* codes_col;
+  uint8_t* scales_col;
+};
+
+template <bool NORM, bool COL>
+__global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
+  __shared__ __align__(16) __nv_bfloat16 tile[kTile * kPitch];
+  __shared__ __align__(16) uint8_t sc_row[2 * 512];
+  __shared__ __align__(16) uint8_t sc_col[COL ? 2 * 512 : 16];
+  __shared__ __align__(16) uint8_t cb_col[COL ? kTile * 80 : 16];  // [128 columns][64 code bytes + pad]
+
+  const int t = threadIdx.x;
+  const int64_t row0 = (int64_t)blockIdx.y * kTile, col0 = (int64_t)blockIdx.x * kTile;
+  const float amax = *p.amax;
+  const float g = amax / kNvfp4GlobalDiv;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && t == 0) *p.global_scale = g;
+
+  // ---- stage the tile (and apply the norm) -------------------------------------
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int chunk = t + i * 256;  // 2048 chunks of 8 bf16
+    const int r = chunk >> 4, c8 = (chunk & 15) * 8;
+    uint4 v = __ldg(reinterpret_cast<const uint4*>(p.x + (row0 + r) * p.ld + col0 + c8));
+    if (NORM) {
+      const float inv = __ldg(p.inv_rms + row0 + r);
+      const uint4 gv = __ldg(reinterpret_cast<const uint4*>(p.gamma + col0 + c8));
+      uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float a = (bf16_bits_to_f32(w[k] & 0xffffu) * inv) * bf16_bits_to_f32(gw[k] & 0xffffu);
+        const float b = (bf16_bits_to_f32(w[k] >> 16) * inv) * bf16_bits_to_f32(gw[k] >> 16);
+        const __nv_bfloat162 y = __floats2bfloat162_rn(a, b);
+        w[k] = *reinterpret_cast<const uint32_t*>(&y);
+      }
+      v = make_uint4(w[0], w[1], w[2], w[3]);
+      if (p.y_out) *reinterpret_cast<uint4*>(p.y_out + (row0 + r) * p.cols + col0 + c8) = v;
+    }
+    *reinterpret_cast<uint4*>(&tile[r * kPitch + c8]) = v;
+  }
+  __syncthreads();
+
+  const bool all_zero = !(amax > 0.f);
+  // ---- row-wise 1x16 blocks: 1024 per tile, 4 per thread --------------------------
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int b = t + i * 256;
+    const int r = b >> 3, kb = b & 7;
+    const uint4 lo = *reinterpret_cast<const uint4*>(&tile[r * kPitch + kb * 16]);
+    const uint4 hi = *reinterpret_cast<const uint4*>(&tile[r * kPitch + kb * 16 + 8]);
+    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    float xv[16];
+    float bamax = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      xv[2 * k] = bf16_bits_to_f32(w[k] & 0xffffu);
+      xv[2 * k + 1] = bf16_bits_to_f32(w[k] >> 16);
+      bamax = fmaxf(bamax, fmaxf(fabsf(xv[2 * k]), fabsf(xv[2 * k + 1])));
+    }
+    uint32_t packed[2] = {0, 0};
+    uint32_t sbyte = 0;
+    if (!all_zero) {
+      float safe;
+      sbyte = nvfp4_block_scale(bamax, g, safe);
+      quantize_block<16>(xv, safe, packed);
+    }
+    *reinterpret_cast<uint2*>(p.codes_row + (row0 + r) * (p.cols / 2) + (col0 + kb * 16) / 2) = make_uint2(packed[0], packed[1]);
+    sc_row[(kb >> 2) * 512 + page_offset(r, kb)] = (uint8_t)sbyte;
+  }
+  // ---- column-wise 16x1 blocks (transposed output) ----------------------------------
+  if (COL) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int b = t + i * 256;
+      const int c = b & 127, rb = b >> 7;  // column c, row block rb (16 rows)
+      float xv[16];
+      float bamax = 0.f;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        xv[k] = __bfloat162float(tile[(rb * 16 + k) * kPitch + c]);
+        bamax = fmaxf(bamax, fabsf(xv[k]));
+      }
+      uint32_t packed[2] = {0, 0};
+      uint32_t sbyte = 0;
+      if (!all_zero) {
+        float safe;
+        sbyte = nvfp4_block_scale(bamax, g, safe);
+        quantize_block<16>(xv, safe, packed);
+      }
+      *reinterpret_cast<uint2*>(&cb_col[c * 80 + rb * 8]) = make_uint2(packed[0], packed[1]);
+      // transposed tensor: row = c (within this tile's 128 columns), kblock = rb (within 8)
+      sc_col[(rb >> 2) * 512 + page_offset(c, rb)] = (uint8_t)sbyte;
+    }
+  }
+  __syncthreads();
+  // ---- write the staged scale pages and transposed codes ------------------------------
+  if (t < 64) {
+    const int page = t >> 5, off = (t & 31) * 16;
+    uint8_t* dst = p.scales_row + ((row0 / 128) * (p.cols / 64) + col0 / 64 + page) * 512 + off;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&sc_row[page * 512 + off]);
+  } else if (COL && t < 128) {
+    const int u = t - 64;
+    const int page = u >> 5, off = (u & 31) * 16;
+    uint8_t* dst = p.scales_col + ((col0 / 128) * (p.rows / 64) + row0 / 64 + page) * 512 + off;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&sc_col[page * 512 + off]);
+  }
+  if (COL) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int chunk = t + i * 256;  // 512 chunks of 16 bytes
+      const int c = chunk >> 2, q = chunk & 3;
+      *reinterpret_cast<uint4*>(p.codes_col + (col0 + c) * (p.rows / 2) + row0 / 2 + q * 16) =
+          *reinterpret_cast<const uint4*>(&cb_col[c * 80 + q * 16]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ MXFP4
+__device__ __forceinline__ int mx_exponent(float bamax, int mode) {
+  // bamax > 0 is a bf16 value; returns the unbiased power-of-two exponent of the block scale
+  const uint32_t bits = __float_as_uint(fmaxf(bamax, kFltMin));
+  const int e = (int)(bits >> 23) - 127;
+  const uint32_t man = bits & 0x7fffffu;
+  if (mode == FA4B_MX_CEIL) return e + (man != 0);
+  if (mode == FA4B_MX_FLOOR) return e;
+  // mantissa round-to-nearest, a tie keeps an even biased exponent
+  const bool up = man > 0x400000u || (man == 0x400000u && ((e + 127) & 1));
+  return e + up;
+}
+
+__global__ void __launch_bounds__(256) mxfp4_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld, int64_t rows, int64_t cols,
+                                                    int mode, uint8_t* __restrict__ codes, uint8_t* __restrict__ scales) {
+  const int64_t kblocks = cols / 32;
+  const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  const bool live = idx < rows * kblocks;
+  const int64_t row = live ? idx / kblocks : 0, kb = live ? idx % kblocks : 0;
+  float xv[32];
+  float bamax = 0.f;
+  const uint4* src = reinterpret_cast<const uint4*>(x + row * ld + kb * 32);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint4 v = live ? __ldg(src + j) : make_uint4(0, 0, 0, 0);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      xv[j * 8 + 2 * k] = bf16_bits_to_f32(w[k] & 0xffffu);
+      xv[j * 8 + 2 * k + 1] = bf16_bits_to_f32(w[k] >> 16);
+      bamax = fmaxf(bamax, fmaxf(fabsf(xv[j * 8 + 2 * k]), fabsf(xv[j * 8 + 2 * k + 1])));
+    }
+  }
+  uint32_t packed[4] = {0, 0, 0, 0};
+  uint32_t ebyte = 0;
+  if (bamax > 0.f) {
+    const int e = max(mx_exponent(bamax, mode), -126);
+    ebyte = (uint32_t)min(e + 127, 254);
+    const float d = __uint_as_float((uint32_t)(e + 127) << 23) / 6.0f;
+    quantize_block<32>(xv, fmaxf(d, kFltMin), packed);
+  }
+  if (live) *reinterpret_cast<uint4*>(codes + row * (cols / 2) + kb * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  // the four blocks of a 128-column page row are held by four adjacent lanes
+  uint32_t quad = ebyte << (8 * (threadIdx.x & 3));
+  quad |= __shfl_xor_sync(0xffffffffu, quad, 1);
+  quad |= __shfl_xor_sync(0xffffffffu, quad, 2);
+  if (live && (threadIdx.x & 3) == 0) {
+    uint8_t* page = scales + ((row / 128) * (cols / 128) + kb / 4) * 512;
+    *reinterpret_cast<uint32_t*>(page + page_offset((uint32_t)row, 0)) = quad;
+  }
+}
+
+// ------------------------------------------------------------------ decode utilities
+__global__ void dequant_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ pages, const float* g,
+                               int64_t rows, int64_t cols, int block, float* __restrict__ out) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * cols) return;
+  const int64_t r = idx / cols, c = idx % cols;
+  const uint32_t byte = codes[r * (cols / 2) + c / 2];
+  const uint32_t code = (c & 1) ? (byte >> 4) : (byte & 15u);
+  const int64_t kb = c / block;
+  const uint32_t s = pages[((r / 128) * (cols / (4 * block)) + kb / 4) * 512 + page_offset((uint32_t)r, (uint32_t)kb)];
+  float d;
+  if (block == 16) d = e4m3_to_f32(s) * *g;
+  else d = s ? __uint_as_float(s << 23) / 6.0f : 0.f;
+  out[idx] = e2m1_to_f32(code) * d;
+}
+
+static int check_matrix(const void* x, int64_t rows, int64_t cols, int64_t ld) {
+  FA4B_REQUIRE(x != nullptr, FA4B_BAD_ARG, "input pointer is NULL");
+  FA4B_REQUIRE(rows > 0 && cols > 0 && rows % 128 == 0 && cols % 128 == 0, FA4B_BAD_SHAPE,
+               "rows=%lld cols=%lld must be positive multiples of 128", (long long)rows, (long long)cols);
+  FA4B_REQUIRE(ld >= cols && ld % 8 == 0, FA4B_BAD_ALIGN, "row stride %lld must be >= cols and a multiple of 8 elements", (long long)ld);
+  FA4B_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0, FA4B_BAD_ALIGN, "input must be 16-byte aligned");
+  return FA4B_OK;
+}
+
+}  // namespace fa4b
+
+using namespace fa4b;
+
+extern "C" {
+
+const char* fa4b_last_error(void) { return fa4b::last_error(); }
+
+const char* fa4b_status_string(int s) {
+  switch (s) {
+    case FA4B_OK: return "ok";
+    case FA4B_BAD_SHAPE: return "bad shape";
+    case FA4B_BAD_ALIGN: return "bad alignment";
+    case FA4B_UNSUPPORTED: return "unsupported";
+    case FA4B_CUDA_ERROR: return "CUDA error";
+    case FA4B_TIMEOUT: return "device wait timed out";
+    case FA4B_BAD_ARG: return "bad argument";
+    default: return "unknown status";
+  }
+}
+
+int fa4b_amax(const void* x, int64_t n, float* amax, void* stream) {
+  FA4B_REQUIRE(x && amax && n > 0, FA4B_BAD_ARG, "fa4b_amax: NULL pointer or n <= 0");
+  FA4B_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0, FA4B_BAD_ALIGN, "fa4b_amax: input must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  FA4B_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), st));
+  const int64_t n_vec = n / 8;
+  const int n_tail = (int)(n % 8);
+  const int grid = (int)std::min<int64_t>(148 * 8, std::max<int64_t>(1, (n_vec + 255) / 256));
+  amax_kernel<<<grid, 256, 0, st>>>(static_cast<const uint4*>(x), n_vec, static_cast<const __nv_bfloat16*>(x) + n_vec * 8, n_tail, amax);
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
+}
+
+static int launch_nvfp4(const Nvfp4Params& p, bool norm, cudaStream_t st) {
+  dim3 grid((unsigned)(p.cols / 128), (unsigned)(p.rows / 128));
+  const bool col = p.codes_col != nullptr;
+  if (norm) {
+    if (col) nvfp4_tile_kernel<true, true><<<grid, 256, 0, st>>>(p);
+    else nvfp4_tile_kernel<true, false><<<grid, 256, 0, st>>>(p);
+  } else {
+    if (col) nvfp4_tile_kernel<false, true><<<grid, 256, 0, st>>>(p);
+    else nvfp4_tile_kernel<false, false><<<grid, 256, 0, st>>>(p);
+  }
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
+}
+
+int fa4b_quant_nvfp4(const fa4b_quant_nvfp4_args* a, void* stream) {
+  FA4B_REQUIRE(a != nullptr, FA4B_BAD_ARG, "args is NULL");
+  if (int s = check_matrix(a->x, a->rows, a->cols, a->ld)) return s;
+  FA4B_REQUIRE(a->amax && a->global_scale && a->codes_row && a->scales_row, FA4B_BAD_ARG, "fa4b_quant_nvfp4: an output pointer is NULL");
+  FA4B_REQUIRE((a->codes_col == nullptr) == (a->scales_col == nullptr), FA4B_BAD_ARG, "codes_col and scales_col go together");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!a->amax_is_input) {
+    FA4B_REQUIRE(a->ld == a->cols, FA4B_UNSUPPORTED, "computing amax needs a dense matrix (ld == cols); pass amax_is_input");
+    if (int s = fa4b_amax(a->x, a->rows * a->cols, a->amax, stream)) return s;
+  }
+  Nvfp4Params p{};
+  p.x = static_cast<const __nv_bfloat16*>(a->x);
+  p.ld = a->ld; p.rows = a->rows; p.cols = a->cols;
+  p.amax = a->amax; p.global_scale = a->global_scale;
+  p.codes_row = a->codes_row; p.scales_row = a->scales_row;
+  p.codes_col = a->codes_col; p.scales_col = a->scales_col;
+  return launch_nvfp4(p, false, st);
+}
+
+int fa4b_rmsnorm_quant_nvfp4(const fa4b_rmsnorm_quant_nvfp4_args* a, void* stream) {
+  FA4B_REQUIRE(a != nullptr, FA4B_BAD_ARG, "args is NULL");
+  if (int s = check_matrix(a->x, a->rows, a->cols, a->ld)) return s;
+  FA4B_REQUIRE(a->gamma && a->inv_rms && a->amax && a->global_scale && a->codes_row && a->scales_row, FA4B_BAD_ARG,
+               "fa4b_rmsnorm_quant_nvfp4: a required pointer is NULL");
+  FA4B_REQUIRE((a->codes_col == nullptr) == (a->scales_col == nullptr), FA4B_BAD_ARG, "codes_col and scales_col go together");
+  FA4B_REQUIRE(a->cols <= 8 * 256 * 8, FA4B_BAD_SHAPE, "cols=%lld exceeds the 16384-column limit of the row-statistics kernel", (long long)a->cols);
+  FA4B_REQUIRE((reinterpret_cast<uintptr_t>(a->gamma) & 15) == 0, FA4B_BAD_ALIGN, "gamma must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  FA4B_CUDA(cudaMemsetAsync(a->amax, 0, sizeof(float), st));
+  const auto* x = static_cast<const __nv_bfloat16*>(a->x);
+  const auto* gm = static_cast<const __nv_bfloat16*>(a->gamma);
+  const int vec = (int)((a->cols / 8 + 255) / 256);
+  const unsigned rows = (unsigned)a->rows;
+  if (vec <= 1) rmsnorm_stats_kernel<1><<<rows, 256, 0, st>>>(x, a->ld, (int)a->cols, gm, a->eps, a->inv_rms, a->amax);
+  else if (vec <= 2) rmsnorm_stats_kernel<2><<<rows, 256, 0, st>>>(x, a->ld, (int)a->cols, gm, a->eps, a->inv_rms, a->amax);
+  else if (vec <= 4) rmsnorm_stats_kernel<4><<<rows, 256, 0, st>>>(x, a->ld, (int)a->cols, gm, a->eps, a->inv_rms, a->amax);
+  else rmsnorm_stats_kernel<8><<<rows, 256, 0, st>>>(x, a->ld, (int)a->cols, gm, a->eps, a->inv_rms, a->amax);
+  FA4B_CUDA(cudaGetLastError());
+  Nvfp4Params p{};
+  p.x = x; p.ld = a->ld; p.rows = a->rows; p.cols = a->cols;
+  p.gamma = gm; p.inv_rms = a->inv_rms; p.y_out = static_cast<__nv_bfloat16*>(a->y_out);
+  p.amax = a->amax; p.global_scale = a->global_scale;
+  p.codes_row = a->codes_row; p.scales_row = a->scales_row;
+  p.codes_col = a->codes_col; p.scales_col = a->scales_col;
+  return launch_nvfp4(p, true, st);
+}
+
+int fa4b_quant_mxfp4(const fa4b_quant_mxfp4_args* a, void* stream) {
+  FA4B_REQUIRE(a != nullptr, FA4B_BAD_ARG, "args is NULL");
+  if (int s = check_matrix(a->x, a->rows, a->cols, a->ld)) return s;
+  FA4B_REQUIRE(a->codes && a->scales, FA4B_BAD_ARG, "fa4b_quant_mxfp4: an output pointer is NULL");
+  FA4B_REQUIRE(a->mode >= FA4B_MX_CEIL && a->mode <= FA4B_MX_FLOOR, FA4B_UNSUPPORTED, "unknown MXFP4 scale mode %d", a->mode);
+  const int64_t n = a->rows * (a->cols / 32);
+  mxfp4_kernel<<<(unsigned)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(a->x), a->ld, a->rows, a->cols, a->mode, a->codes, a->scales);
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
+}
+
+int fa4b_dequant_nvfp4(const uint8_t* codes, const uint8_t* pages, const float* g, int64_t rows, int64_t cols, float* out, void* stream) {
+  FA4B_REQUIRE(codes && pages && g && out, FA4B_BAD_ARG, "fa4b_dequant_nvfp4: NULL pointer");
+  FA4B_REQUIRE(rows > 0 && cols > 0 && rows % 128 == 0 && cols % 64 == 0, FA4B_BAD_SHAPE, "rows %% 128 and cols %% 64 must be 0");
+  const int64_t n = rows * cols;
+  dequant_kernel<<<(unsigned)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(codes, pages, g, rows, cols, 16, out);
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
+}
+
+int fa4b_dequant_mxfp4(const uint8_t* codes, const uint8_t* pages, int64_t rows, int64_t cols, float* out, void* stream) {
+  FA4B_REQUIRE(codes && pages && out, FA4B_BAD_ARG, "fa4b_dequant_mxfp4: NULL pointer");
+  FA4B_REQUIRE(rows > 0 && cols > 0 && rows % 128 == 0 && cols % 128 == 0, FA4B_BAD_SHAPE, "rows and cols must be multiples of 128");
+  const int64_t n = rows * cols;
+  dequant_kernel<<<(unsigned)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(codes, pages, nullptr, rows, cols, 32, out);
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,120 @@
+"""ctypes binding of libfa4b.so (the C ABI declared in include/fa4b.h).
+
+There is no fallback: if the shared library is missing or a call fails, the
+caller gets an exception.  Build with ``make -C fp4-fa4_b200/csrc``.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import pathlib
+
+_LIB_PATH = pathlib.Path(__file__).resolve().parents[1] / "lib" / "libfa4b.so"
+
+STATUS_EXC = {1: ValueError, 2: ValueError, 3: NotImplementedError, 4: RuntimeError, 5: TimeoutError, 6: ValueError}
+
+
+class Fa4bError(RuntimeError):
+    pass
+
+
+class QuantNvfp4Args(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("rows", C.c_int64), ("cols", C.c_int64), ("ld", C.c_int64),
+                ("amax", C.c_void_p), ("amax_is_input", C.c_int), ("global_scale", C.c_void_p),
+                ("codes_row", C.c_void_p), ("scales_row", C.c_void_p),
+                ("codes_col", C.c_void_p), ("scales_col", C.c_void_p)]
+
+
+class RmsnormQuantArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("gamma", C.c_void_p), ("rows", C.c_int64), ("cols", C.c_int64), ("ld", C.c_int64),
+                ("eps", C.c_float), ("inv_rms", C.c_void_p), ("y_out", C.c_void_p), ("amax", C.c_void_p),
+                ("global_scale", C.c_void_p), ("codes_row", C.c_void_p), ("scales_row", C.c_void_p),
+                ("codes_col", C.c_void_p), ("scales_col", C.c_void_p)]
+
+
+class QuantMxfp4Args(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("rows", C.c_int64), ("cols", C.c_int64), ("ld", C.c_int64),
+                ("mode", C.c_int), ("codes", C.c_void_p), ("scales", C.c_void_p)]
+
+
+class AttnDims(C.Structure):
+    _fields_ = [("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("S", C.c_int32), ("D", C.c_int32),
+                ("softmax_scale", C.c_float), ("pv_format", C.c_int32)]
+
+
+class Strides(C.Structure):
+    _fields_ = [("batch", C.c_int64), ("head", C.c_int64), ("seq", C.c_int64)]
+
+
+class WsLayout(C.Structure):
+    _fields_ = [(n, C.c_size_t) for n in (
+        "q_codes", "q_scales", "q_global", "k_codes", "k_scales", "k_global", "v_fp8", "q_fp8", "k_fp8",
+        "do_fp8", "dstat", "lstat", "dq_accum", "amax_bits", "status", "total")]
+
+
+class AttnPrepareArgs(C.Structure):
+    _fields_ = [("dims", AttnDims), ("q", C.c_void_p), ("q_strides", Strides), ("k", C.c_void_p), ("k_strides", Strides),
+                ("v", C.c_void_p), ("v_strides", Strides), ("ws", C.c_void_p)]
+
+
+class AttnFwdArgs(C.Structure):
+    _fields_ = [("dims", AttnDims), ("q", C.c_void_p), ("q_strides", Strides), ("k", C.c_void_p), ("k_strides", Strides),
+                ("v", C.c_void_p), ("v_strides", Strides), ("o", C.c_void_p), ("o_strides", Strides),
+                ("lse", C.c_void_p), ("ws", C.c_void_p), ("prepared", C.c_int32)]
+
+
+class AttnBwdArgs(C.Structure):
+    _fields_ = [("dims", AttnDims), ("o", C.c_void_p), ("o_strides", Strides), ("dout", C.c_void_p), ("do_strides", Strides),
+                ("lse", C.c_void_p), ("dq", C.c_void_p), ("dq_strides", Strides), ("dk", C.c_void_p), ("dk_strides", Strides),
+                ("dv", C.c_void_p), ("dv_strides", Strides), ("ws", C.c_void_p)]
+
+
+class Info(C.Structure):
+    _fields_ = [(n, C.c_int) for n in (
+        "abi_version", "build_sm", "fwd_threads", "fwd_smem_bytes", "fwd_tmem_columns", "fwd_kv_stages",
+        "bwd_threads", "bwd_smem_bytes", "bwd_tmem_columns", "tile_q", "tile_kv", "wait_limit")]
+
+
+EXPORTS = (
+    "fa4b_status_string", "fa4b_last_error", "fa4b_query", "fa4b_amax", "fa4b_quant_nvfp4",
+    "fa4b_rmsnorm_quant_nvfp4", "fa4b_quant_mxfp4", "fa4b_dequant_nvfp4", "fa4b_dequant_mxfp4",
+    "fa4b_attn_workspace_bytes", "fa4b_attn_ws_layout_query", "fa4b_attn_prepare", "fa4b_attn_fwd",
+    "fa4b_attn_bwd_preprocess", "fa4b_attn_bwd", "fa4b_attn_check_status", "fa4b_microgate",
+)
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise Fa4bError(f"{_LIB_PATH} is missing: build it with `make -C {_LIB_PATH.parents[1] / 'csrc'}`")
+        handle = C.CDLL(str(_LIB_PATH))
+        handle.fa4b_status_string.restype = C.c_char_p
+        handle.fa4b_last_error.restype = C.c_char_p
+        handle.fa4b_attn_workspace_bytes.restype = C.c_size_t
+        for name in EXPORTS:
+            getattr(handle, name)  # AttributeError if the ABI is incomplete
+        _lib = handle
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    handle = lib()
+    reason = handle.fa4b_last_error().decode(errors="replace")
+    kind = handle.fa4b_status_string(status).decode()
+    raise STATUS_EXC.get(status, Fa4bError)(f"{what}: {kind}: {reason}")
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def current_stream() -> int:
+    import torch
+
+    return torch.cuda.current_stream().cuda_stream

@@ -1,0 +1,122 @@
+"""Attention operators over the C ABI: operand publication, forward, backward.
+
+Tensors are ``[B,H,S,D]`` bf16 views (any batch/head/sequence strides, last
+dimension contiguous), the layout ``FA4AttentionWrapper.forward`` receives
+(torchtitan/experiments/fa4/fa4_attention.py:507-548)."""
+
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import check, current_stream, lib, ptr
+
+PV_FORMATS = {"e4m3_fp8": 0, "mxfp4_e8m0_block32": 1}
+
+
+def _strides(t: torch.Tensor) -> _lib.Strides:
+    return _lib.Strides(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _check_bhsd(t: torch.Tensor, name: str) -> None:
+    if not isinstance(t, torch.Tensor) or t.ndim != 4:
+        raise ValueError(f"{name} must be a [B,H,S,D] tensor")
+    if t.dtype != torch.bfloat16:
+        raise TypeError(f"{name} must be bfloat16, got {t.dtype}")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must live on a CUDA device (there is no CPU path)")
+    if t.stride(3) != 1:
+        raise ValueError(f"{name} must have a contiguous head dimension")
+
+
+@dataclass
+class Workspace:
+    """Operand cache of one attention call (see fa4b_attn_ws_layout)."""
+
+    dims: _lib.AttnDims
+    layout: _lib.WsLayout
+    buf: torch.Tensor
+
+    def _view(self, off: int, nbytes: int) -> torch.Tensor:
+        return self.buf[off:off + nbytes]
+
+    def operands(self):
+        d = self.dims
+        nq, nk, S, D = d.B * d.Hq, d.B * d.Hkv, d.S, d.D
+        L = self.layout
+        return {
+            "q_codes": self._view(L.q_codes, nq * S * D // 2).view(d.B, d.Hq, S, D // 2),
+            "q_scales": self._view(L.q_scales, nq * (S // 128) * (D // 64) * 512).view(d.B, d.Hq, S // 128, D // 64, 512),
+            "q_global": self._view(L.q_global, nq * 4).view(torch.float32).view(d.B, d.Hq),
+            "k_codes": self._view(L.k_codes, nk * S * D // 2).view(d.B, d.Hkv, S, D // 2),
+            "k_scales": self._view(L.k_scales, nk * (S // 128) * (D // 64) * 512).view(d.B, d.Hkv, S // 128, D // 64, 512),
+            "k_global": self._view(L.k_global, nk * 4).view(torch.float32).view(d.B, d.Hkv),
+            "v_fp8": self._view(L.v_fp8, nk * S * D).view(torch.float8_e4m3fn).view(d.B, d.Hkv, S, D),
+            "q_fp8": self._view(L.q_fp8, nq * S * D).view(torch.float8_e4m3fn).view(d.B, d.Hq, S, D),
+            "k_fp8": self._view(L.k_fp8, nk * S * D).view(torch.float8_e4m3fn).view(d.B, d.Hkv, S, D),
+            "do_fp8": self._view(L.do_fp8, nq * S * D).view(torch.float8_e5m2).view(d.B, d.Hq, S, D),
+            "dstat": self._view(L.dstat, nq * S * 4).view(torch.float32).view(d.B, d.Hq, S),
+            "lstat": self._view(L.lstat, nq * S * 4).view(torch.float32).view(d.B, d.Hq, S),
+        }
+
+    def check_status(self) -> None:
+        check(lib().fa4b_attn_check_status(C.byref(self.dims), C.c_void_p(ptr(self.buf)), C.c_void_p(current_stream())),
+              "fa4b_attn_check_status")
+
+
+def make_dims(q: torch.Tensor, k: torch.Tensor, softmax_scale: float | None, pv_format: str) -> _lib.AttnDims:
+    if pv_format not in PV_FORMATS:
+        raise ValueError(f"unknown pv_format {pv_format!r}; expected one of {sorted(PV_FORMATS)}")
+    B, Hq, S, D = q.shape
+    return _lib.AttnDims(B, Hq, k.shape[1], S, D, float(softmax_scale) if softmax_scale else 0.0, PV_FORMATS[pv_format])
+
+
+def alloc_workspace(dims: _lib.AttnDims, device) -> Workspace:
+    layout = _lib.WsLayout()
+    check(lib().fa4b_attn_ws_layout_query(C.byref(dims), C.byref(layout)), "fa4b_attn_ws_layout_query")
+    buf = torch.empty(layout.total + 1024, dtype=torch.uint8, device=device)
+    shift = (-buf.data_ptr()) % 1024
+    return Workspace(dims, layout, buf[shift:shift + layout.total])
+
+
+def attn_forward(q, k, v, softmax_scale: float | None = None, pv_format: str = "e4m3_fp8", workspace: Workspace | None = None):
+    """O ``[B,Hq,S,D]`` bf16, LSE ``[B,Hq,S]`` f32 and the workspace holding the quantised operands."""
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _check_bhsd(t, n)
+    if k.shape != v.shape or q.shape[0] != k.shape[0] or q.shape[2:] != k.shape[2:]:
+        raise ValueError(f"inconsistent shapes q{tuple(q.shape)} k{tuple(k.shape)} v{tuple(v.shape)}")
+    dims = make_dims(q, k, softmax_scale, pv_format)
+    ws = workspace or alloc_workspace(dims, q.device)
+    B, Hq, S, D = q.shape
+    o = torch.empty(B, Hq, S, D, dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
+    a = _lib.AttnFwdArgs(dims, ptr(q), _strides(q), ptr(k), _strides(k), ptr(v), _strides(v), ptr(o), _strides(o), ptr(lse),
+                         ptr(ws.buf), 0)
+    check(lib().fa4b_attn_fwd(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_fwd")
+    return o, lse, ws
+
+
+def attn_backward(o, lse, dout, ws: Workspace):
+    """dQ ``[B,Hq,S,D]``, dK, dV ``[B,Hkv,S,D]`` bf16, replaying the operands the forward cached in ``ws``."""
+    for t, n in ((o, "o"), (dout, "dout")):
+        _check_bhsd(t, n)
+    d = ws.dims
+    dq = torch.empty(d.B, d.Hq, d.S, d.D, dtype=torch.bfloat16, device=o.device)
+    dk = torch.empty(d.B, d.Hkv, d.S, d.D, dtype=torch.bfloat16, device=o.device)
+    dv = torch.empty_like(dk)
+    a = _lib.AttnBwdArgs(d, ptr(o), _strides(o), ptr(dout), _strides(dout), ptr(lse), ptr(dq), _strides(dq), ptr(dk), _strides(dk),
+                         ptr(dv), _strides(dv), ptr(ws.buf))
+    check(lib().fa4b_attn_bwd(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_bwd")
+    return dq, dk, dv
+
+
+def attn_bwd_preprocess(o, lse, dout, ws: Workspace):
+    d = ws.dims
+    a = _lib.AttnBwdArgs(d, ptr(o), _strides(o), ptr(dout), _strides(dout), ptr(lse), 0, _lib.Strides(), 0, _lib.Strides(), 0,
+                         _lib.Strides(), ptr(ws.buf))
+    check(lib().fa4b_attn_bwd_preprocess(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_bwd_preprocess")
+    ops = ws.operands()
+    return ops["do_fp8"], ops["dstat"], ops["lstat"]

@@ -1,0 +1,24 @@
+"""Tensor-core self tests (one 128x128xK product per call); see fa4b_microgate."""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ._lib import check, current_stream, lib, ptr
+
+KINDS = {"nvfp4": 0, "e4m3_kk": 1, "e4m3_e5m2_kk": 2, "e4m3_k_mn": 3, "e4m3_mn_mn": 4, "e4m3_ts_mn": 5, "mxfp4": 6,
+         "e4m3_kk_tma": 7}
+
+
+def run(kind: str, K: int, a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor | None = None, sfb: torch.Tensor | None = None):
+    out = torch.zeros(128, 128, dtype=torch.float32, device=a.device)
+    status = torch.zeros(4, dtype=torch.int32, device=a.device)
+    check(lib().fa4b_microgate(C.c_int(KINDS[kind]), C.c_int(K), C.c_void_p(ptr(a)), C.c_void_p(ptr(b)), C.c_void_p(ptr(sfa)),
+                               C.c_void_p(ptr(sfb)), C.c_void_p(ptr(out)), C.c_void_p(ptr(status)), C.c_void_p(current_stream())),
+          "fa4b_microgate")
+    torch.cuda.synchronize()
+    if int(status[0]) != 0:
+        raise TimeoutError(f"microgate {kind}: device wait ran out at site {int(status[1])}")
+    return out

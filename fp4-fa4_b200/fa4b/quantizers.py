@@ -1,0 +1,112 @@
+"""Block quantizer operators, named after the reference's pybind entry points
+(TK_quantisation/nvfp4_v6/tk_quantize.cu:3172-3234,
+TK_quantisation/mxfp4_v3/tk_quantize.cu:2052-2054)."""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import check, current_stream, lib, ptr
+
+MX_MODES = {"ceil": 0, "rte_mantissa": 1, "floor": 2, 0: 0, 1: 1, 2: 2}
+
+
+def _require_matrix(x: torch.Tensor, name: str) -> None:
+    if not isinstance(x, torch.Tensor) or x.ndim != 2:
+        raise ValueError(f"{name} must be a 2-D tensor")
+    if x.dtype != torch.bfloat16:
+        raise TypeError(f"{name} must be bfloat16, got {x.dtype}")
+    if not x.is_cuda:
+        raise RuntimeError(f"{name} must live on a CUDA device (there is no CPU path)")
+    if x.stride(1) != 1:
+        raise ValueError(f"{name} must have a contiguous last dimension")
+    if x.shape[0] % 128 or x.shape[1] % 128:
+        raise ValueError(f"{name} shape {tuple(x.shape)} must be multiples of 128")
+
+
+def amax(x: torch.Tensor) -> torch.Tensor:
+    """max |x| of a contiguous bf16 tensor -> f32 [1]."""
+    if x.dtype != torch.bfloat16 or not x.is_cuda or not x.is_contiguous():
+        raise ValueError("amax needs a contiguous CUDA bfloat16 tensor")
+    out = torch.empty(1, dtype=torch.float32, device=x.device)
+    check(lib().fa4b_amax(C.c_void_p(ptr(x)), C.c_int64(x.numel()), C.c_void_p(ptr(out)), C.c_void_p(current_stream())), "fa4b_amax")
+    return out
+
+
+def _alloc_outputs(rows, cols, transpose, dev, block=16):
+    fp4_row = torch.empty(rows, cols // 2, dtype=torch.uint8, device=dev)
+    sc_row = torch.empty(rows // 128, cols // (4 * block), 512, dtype=torch.uint8, device=dev)
+    fp4_col = sc_col = None
+    if transpose:
+        fp4_col = torch.empty(cols, rows // 2, dtype=torch.uint8, device=dev)
+        sc_col = torch.empty(cols // 128, rows // (4 * block), 512, dtype=torch.uint8, device=dev)
+    return fp4_row, sc_row, fp4_col, sc_col
+
+
+def tk_quantize_for_gemm(input: torch.Tensor, return_transpose: bool = True, amax_in: torch.Tensor | None = None):
+    """NVFP4 of ``input [M,K]``: returns ``(fp4_row [M,K/2], sc_row [M/128,K/64,512],
+    fp4_col [K,M/2] | None, sc_col [K/128,M/64,512] | None, sg [1], amax [1])``.
+    ``sg = amax/2688``; scale bytes are E4M3."""
+    _require_matrix(input, "input")
+    rows, cols = input.shape
+    fp4_row, sc_row, fp4_col, sc_col = _alloc_outputs(rows, cols, return_transpose, input.device)
+    am = torch.empty(1, dtype=torch.float32, device=input.device) if amax_in is None else amax_in
+    sg = torch.empty(1, dtype=torch.float32, device=input.device)
+    a = _lib.QuantNvfp4Args(ptr(input), rows, cols, input.stride(0), ptr(am), int(amax_in is not None), ptr(sg),
+                            ptr(fp4_row), ptr(sc_row), ptr(fp4_col), ptr(sc_col))
+    check(lib().fa4b_quant_nvfp4(C.byref(a), C.c_void_p(current_stream())), "fa4b_quant_nvfp4")
+    return fp4_row, sc_row, fp4_col, sc_col, sg, am
+
+
+def tk_fused_norm_quantize(input: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6, with_silu: bool = False,
+                           return_transpose: bool = True, return_normalized: bool = False):
+    """Fused RMSNorm + NVFP4: returns ``(fp4_row, sc_row, fp4_col, sc_col, sg,
+    inv_rms [M], amax [1])`` (plus the bf16 normalised tensor when asked)."""
+    _require_matrix(input, "input")
+    if with_silu:
+        raise NotImplementedError("the SiLU variant feeds the FFN GEMMs and is outside this attention path")
+    if gamma.dtype != torch.bfloat16 or gamma.ndim != 1 or gamma.shape[0] != input.shape[1] or not gamma.is_cuda:
+        raise ValueError("gamma must be a CUDA bfloat16 vector of length K")
+    rows, cols = input.shape
+    fp4_row, sc_row, fp4_col, sc_col = _alloc_outputs(rows, cols, return_transpose, input.device)
+    dev = input.device
+    inv_rms = torch.empty(rows, dtype=torch.float32, device=dev)
+    am = torch.empty(1, dtype=torch.float32, device=dev)
+    sg = torch.empty(1, dtype=torch.float32, device=dev)
+    y = torch.empty(rows, cols, dtype=torch.bfloat16, device=dev) if return_normalized else None
+    a = _lib.RmsnormQuantArgs(ptr(input), ptr(gamma.contiguous()), rows, cols, input.stride(0), float(eps), ptr(inv_rms), ptr(y),
+                              ptr(am), ptr(sg), ptr(fp4_row), ptr(sc_row), ptr(fp4_col), ptr(sc_col))
+    check(lib().fa4b_rmsnorm_quant_nvfp4(C.byref(a), C.c_void_p(current_stream())), "fa4b_rmsnorm_quant_nvfp4")
+    out = (fp4_row, sc_row, fp4_col, sc_col, sg, inv_rms, am)
+    return out + (y,) if return_normalized else out
+
+
+def mxfp4_quantize_for_gemm(input: torch.Tensor, mode: int | str = "ceil"):
+    """MXFP4 (1x32, E8M0) of ``input [M,K]``: ``(fp4 [M,K/2], scales [M/128,K/128,512])``."""
+    _require_matrix(input, "input")
+    if mode not in MX_MODES:
+        raise ValueError(f"unknown MXFP4 scale mode {mode!r}")
+    rows, cols = input.shape
+    fp4, sc, _, _ = _alloc_outputs(rows, cols, False, input.device, block=32)
+    a = _lib.QuantMxfp4Args(ptr(input), rows, cols, input.stride(0), MX_MODES[mode], ptr(fp4), ptr(sc))
+    check(lib().fa4b_quant_mxfp4(C.byref(a), C.c_void_p(current_stream())), "fa4b_quant_mxfp4")
+    return fp4, sc
+
+
+def dequant_nvfp4(codes: torch.Tensor, scale_pages: torch.Tensor, sg: torch.Tensor) -> torch.Tensor:
+    rows, cols = codes.shape[0], codes.shape[1] * 2
+    out = torch.empty(rows, cols, dtype=torch.float32, device=codes.device)
+    check(lib().fa4b_dequant_nvfp4(C.c_void_p(ptr(codes)), C.c_void_p(ptr(scale_pages)), C.c_void_p(ptr(sg)), C.c_int64(rows),
+                                   C.c_int64(cols), C.c_void_p(ptr(out)), C.c_void_p(current_stream())), "fa4b_dequant_nvfp4")
+    return out
+
+
+def dequant_mxfp4(codes: torch.Tensor, scale_pages: torch.Tensor) -> torch.Tensor:
+    rows, cols = codes.shape[0], codes.shape[1] * 2
+    out = torch.empty(rows, cols, dtype=torch.float32, device=codes.device)
+    check(lib().fa4b_dequant_mxfp4(C.c_void_p(ptr(codes)), C.c_void_p(ptr(scale_pages)), C.c_int64(rows), C.c_int64(cols),
+                                   C.c_void_p(ptr(out)), C.c_void_p(current_stream())), "fa4b_dequant_mxfp4")
+    return out

@@ -1,0 +1,239 @@
+/*
+ * fa4b -- C ABI of the B200 (sm_100a) low-precision attention path.
+ *
+ * Plain pointers and sizes only: every buffer is a CUDA device pointer owned
+ * by the caller unless a comment says "host".  `stream` is a cudaStream_t
+ * passed as void* (NULL = the legacy default stream).  Every entry point
+ * returns an fa4b_status; on failure fa4b_last_error() (thread local) holds a
+ * one-line reason.  Nothing here allocates device memory: scratch space is
+ * passed in and sized by the *_workspace_bytes queries.
+ *
+ * Each entry point names the reference interface it stands in for
+ * (paths are relative to the reference project's root).
+ */
+#ifndef FA4B_H_
+#define FA4B_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA4B_ABI_VERSION 1
+
+typedef enum fa4b_status {
+  FA4B_OK = 0,
+  FA4B_BAD_SHAPE = 1,   /* a dimension the kernels do not cover               */
+  FA4B_BAD_ALIGN = 2,   /* pointer or stride not aligned as documented        */
+  FA4B_UNSUPPORTED = 3, /* format / mode / device not supported               */
+  FA4B_CUDA_ERROR = 4,  /* a CUDA runtime or driver call failed               */
+  FA4B_TIMEOUT = 5,     /* a bounded device-side wait ran out                 */
+  FA4B_BAD_ARG = 6      /* NULL where a buffer is required, overlap, ...      */
+} fa4b_status;
+
+const char* fa4b_status_string(int status);
+const char* fa4b_last_error(void);
+
+/* ---- formats and modes ------------------------------------------------- */
+enum { FA4B_PV_FP8_E4M3 = 0, FA4B_PV_MXFP4_E8M0 = 1 };  /* fa4.exact_pv_format */
+enum { FA4B_MX_CEIL = 0, FA4B_MX_RTE_MANTISSA = 1, FA4B_MX_FLOOR = 2 };
+enum { FA4B_LAYOUT_BHSD = 0, FA4B_LAYOUT_BSHD = 1 };
+
+/* ---- fa4b_query --------------------------------------------------------
+ * Host only.  Replaces read_hao_direct_topology()
+ * (tk_fa4/fp4_fa4_fwd/hao_direct_host.inc:149-261) and
+ * native_tk_d128_backward_metadata()
+ * (tk_fa4/native_gqa_tk_bwd/v509_*bshd.cu:446-522). */
+typedef struct fa4b_info {
+  int abi_version;
+  int build_sm;            /* 100 (compiled for sm_100a)                      */
+  int fwd_threads, fwd_smem_bytes, fwd_tmem_columns, fwd_kv_stages;
+  int bwd_threads, bwd_smem_bytes, bwd_tmem_columns;
+  int tile_q, tile_kv;     /* 128, 128                                        */
+  int wait_limit;          /* iteration cap of every device-side wait         */
+} fa4b_info;
+int fa4b_query(fa4b_info* out);
+
+/* ---- fa4b_amax ----------------------------------------------------------
+ * max |x| of n bf16 values -> amax[0] (f32).  Replaces
+ * fused_amax_pipelined_kernel (TK_quantisation/nvfp4_v6/amax_pipelined.cuh:142). */
+int fa4b_amax(const void* x_bf16, int64_t n, float* amax, void* stream);
+
+/* ---- fa4b_quant_nvfp4 ---------------------------------------------------
+ * Row-wise (1x16) and optionally transposed (16x1) NVFP4 of x[rows, cols]
+ * bf16 (row stride ld elements).  Replaces tk_quantize_for_gemm /
+ * tk_quantize_transpose (TK_quantisation/nvfp4_v6/tk_quantize.cu:3172-3177)
+ * and quantize_nvfp4_projection_operand (tk_fa4/interface.py:991), with the
+ * decode-centric arithmetic of projection_quantization_reference.py:456-470.
+ *   amax         [1] f32: written unless amax_is_input != 0
+ *   global_scale [1] f32: amax / 2688
+ *   codes_row  [rows, cols/2] u8 (even column in the low nibble)
+ *   scales_row [rows/128, cols/64, 512] E4M3 bytes; byte
+ *              (r%32)*16 + ((r%128)/32)*4 + (kblock%4) of page (r/128, kblock/4)
+ *   codes_col  [cols, rows/2], scales_col [cols/128, rows/64, 512]: optional
+ * rows and cols must be multiples of 128. */
+typedef struct fa4b_quant_nvfp4_args {
+  const void* x;
+  int64_t rows, cols, ld;
+  float* amax;
+  int amax_is_input;
+  float* global_scale;
+  uint8_t* codes_row;
+  uint8_t* scales_row;
+  uint8_t* codes_col;  /* NULL = no transposed output */
+  uint8_t* scales_col;
+} fa4b_quant_nvfp4_args;
+int fa4b_quant_nvfp4(const fa4b_quant_nvfp4_args* a, void* stream);
+
+/* ---- fa4b_rmsnorm_quant_nvfp4 -------------------------------------------
+ * y = bf16((x * inv_rms[row]) * gamma[col]), inv_rms = 1/sqrt(mean x^2 + eps);
+ * then fa4b_quant_nvfp4 of y with amax over the bf16 y.  Replaces
+ * tk_fused_norm_quantize (TK_quantisation/nvfp4_v6/tk_quantize.cu:2353-2366)
+ * and quantize_nvfp4_projection_operand_rmsnorm (tk_fa4/interface.py:1056).
+ *   inv_rms [rows] f32 out;  y_out [rows, cols] bf16 optional (NULL = skip). */
+typedef struct fa4b_rmsnorm_quant_nvfp4_args {
+  const void* x;
+  const void* gamma;
+  int64_t rows, cols, ld;
+  float eps;
+  float* inv_rms;
+  void* y_out;
+  float* amax;
+  float* global_scale;
+  uint8_t* codes_row;
+  uint8_t* scales_row;
+  uint8_t* codes_col;
+  uint8_t* scales_col;
+} fa4b_rmsnorm_quant_nvfp4_args;
+int fa4b_rmsnorm_quant_nvfp4(const fa4b_rmsnorm_quant_nvfp4_args* a, void* stream);
+
+/* ---- fa4b_quant_mxfp4 ---------------------------------------------------
+ * Row-wise 1x32 MXFP4 with E8M0 scales.  Replaces mxfp4_quantize_for_gemm
+ * (TK_quantisation/mxfp4_v3/tk_quantize.cu:2052-2054).
+ *   codes [rows, cols/2]; scales [rows/128, cols/128, 512] E8M0 bytes, same
+ *   page byte order as above with kblock = col/32; byte 0 = all-zero block. */
+typedef struct fa4b_quant_mxfp4_args {
+  const void* x;
+  int64_t rows, cols, ld;
+  int mode; /* FA4B_MX_* */
+  uint8_t* codes;
+  uint8_t* scales;
+} fa4b_quant_mxfp4_args;
+int fa4b_quant_mxfp4(const fa4b_quant_mxfp4_args* a, void* stream);
+
+/* ---- fa4b_dequant_* (test utilities) --------------------------------------
+ * Replace tk_reconstruct_row (TK_quantisation/nvfp4_v6/tk_quantize.cu:3225-3234)
+ * and decode_prepared_nvfp4_matrix (projection_quantization_reference.py:293-329). */
+int fa4b_dequant_nvfp4(const uint8_t* codes, const uint8_t* scale_pages, const float* global_scale,
+                       int64_t rows, int64_t cols, float* out_f32, void* stream);
+int fa4b_dequant_mxfp4(const uint8_t* codes, const uint8_t* scale_pages,
+                       int64_t rows, int64_t cols, float* out_f32, void* stream);
+
+/* ---- attention ------------------------------------------------------------
+ * Causal grouped-query attention, NVFP4 Q.K^T and FP8-E4M3 (or MXFP4) P.V.
+ * q/o/do/dq are [B,Hq,S,D], k/v/dk/dv [B,Hkv,S,D] bf16, addressed through
+ * element strides (batch, head, seq); the last dim is contiguous.  S must be a
+ * multiple of 128, D is 64 or 128, Hq a multiple of Hkv.
+ *
+ * The operand cache `ws` (fa4b_attn_workspace_bytes) receives, in this order:
+ *   q NVFP4 codes [B,Hq,S,D/2], scale pages [B,Hq,S/128,D/64,512], global [B,Hq];
+ *   the same for k; v as E4M3(4v) [B,Hkv,S,D]; q and k as E4M3(4x) (backward);
+ * the optional out-pointers of fa4b_attn_fwd_args expose them for parity checks. */
+typedef struct fa4b_attn_dims {
+  int32_t B, Hq, Hkv, S, D;
+  float softmax_scale; /* <= 0: 1/sqrt(D) */
+  int32_t pv_format;   /* FA4B_PV_* */
+} fa4b_attn_dims;
+
+typedef struct fa4b_strides {
+  int64_t batch, head, seq; /* in elements */
+} fa4b_strides;
+
+size_t fa4b_attn_workspace_bytes(const fa4b_attn_dims* d);
+
+/* Offsets (bytes) of the cached operands inside the workspace. */
+typedef struct fa4b_attn_ws_layout {
+  size_t q_codes, q_scales, q_global, k_codes, k_scales, k_global;
+  size_t v_fp8, q_fp8, k_fp8, do_fp8, dstat, lstat, dq_accum, amax_bits, status, total;
+} fa4b_attn_ws_layout;
+int fa4b_attn_ws_layout_query(const fa4b_attn_dims* d, fa4b_attn_ws_layout* out);
+
+/* fa4b_attn_prepare: per-(batch, head) amax, NVFP4 Q/K and E4M3 V/Q/K
+ * publication into `ws`.  Replaces the quantise/publish half of the QKV
+ * projection epilogue (tk_fa4/lowp_fa4_bwd/projection_fp4_epilogue.cuh:
+ * 1453-1579 stage_codes_perblock_qk, 1861-1945 publish_forward_qk_perblock_scales,
+ * 873-983 publish_v_fp8). */
+typedef struct fa4b_attn_prepare_args {
+  fa4b_attn_dims dims;
+  const void* q; fa4b_strides q_strides;
+  const void* k; fa4b_strides k_strides;
+  const void* v; fa4b_strides v_strides;
+  void* ws;
+} fa4b_attn_prepare_args;
+int fa4b_attn_prepare(const fa4b_attn_prepare_args* a, void* stream);
+
+/* fa4b_attn_fwd: O and LSE (natural log, [B,Hq,S] f32).  Replaces
+ * forward_hao_direct_fp8pv / forward_hao_direct_fp4pv
+ * (tk_fa4/fp4_fa4_fwd/hao_direct_host.inc:263-275, 511-521;
+ * hao_direct_fp4pv_host.inc:1141-1237).  Calls fa4b_attn_prepare first unless
+ * `prepared` is non-zero. */
+typedef struct fa4b_attn_fwd_args {
+  fa4b_attn_dims dims;
+  const void* q; fa4b_strides q_strides;
+  const void* k; fa4b_strides k_strides;
+  const void* v; fa4b_strides v_strides;
+  void* o; fa4b_strides o_strides;
+  float* lse;
+  void* ws;
+  int32_t prepared;
+} fa4b_attn_fwd_args;
+int fa4b_attn_fwd(const fa4b_attn_fwd_args* a, void* stream);
+
+/* fa4b_attn_bwd_preprocess: dO5 = E5M2(4 dO), dstat = -4 sum_d O*dO5,
+ * lstat = 8 - LSE*log2e, into `ws`.  Replaces the dO/statistics publisher
+ * project_dout_unified_fp4_nvfp4_v509_e5m2
+ * (tk_fa4/lowp_fa4_bwd/projection_fp4_epilogue.cuh:840-871, 4049-4127). */
+typedef struct fa4b_attn_bwd_args {
+  fa4b_attn_dims dims;
+  const void* o; fa4b_strides o_strides;
+  const void* dout; fa4b_strides do_strides;
+  const float* lse;
+  void* dq; fa4b_strides dq_strides;
+  void* dk; fa4b_strides dk_strides;
+  void* dv; fa4b_strides dv_strides;
+  void* ws; /* the workspace the forward filled (operands are replayed from it) */
+} fa4b_attn_bwd_args;
+int fa4b_attn_bwd_preprocess(const fa4b_attn_bwd_args* a, void* stream);
+
+/* fa4b_attn_bwd: dQ, dK, dV (bf16, written, not accumulated).  Replaces
+ * backward_nvfp4_score_e4m3_qkv_e5m2_dout_bshd_precleared_dq_out
+ * (tk_fa4/native_gqa_tk_bwd/v509_*bshd.cu:406-444) and the D64 kernel v416.
+ * Runs the preprocess step itself. */
+int fa4b_attn_bwd(const fa4b_attn_bwd_args* a, void* stream);
+
+/* fa4b_attn_check_status: synchronises `stream`, then reports FA4B_TIMEOUT if a
+ * bounded wait inside the last attention kernel on this workspace gave up
+ * (the reference's waits are unbounded, hao_direct_kernel.inc:17-23; this
+ * query has no counterpart there). */
+int fa4b_attn_check_status(const fa4b_attn_dims* d, const void* ws, void* stream);
+
+/* ---- tensor-core self tests ("microgates") -------------------------------
+ * One 128x128xK product per launch through the same tcgen05 instruction
+ * forms, shared-memory descriptors and TMEM layouts the attention kernels
+ * use; out is [128,128] f32.  The reference proves each primitive the same
+ * way (tk_fa4/native_gqa_tk_bwd/e5m2_dout_mixed_mma_microgate_20260831.cuh:213-316).
+ *   kind 0: NVFP4 x NVFP4 block-scaled (a,b packed codes [128,K/2], sfa/sfb pages)
+ *   kind 1: E4M3 x E4M3, both K-major        kind 2: E4M3 x E5M2, both K-major
+ *   kind 3: E4M3 A K-major, B MN-major ([K,128] row-major)
+ *   kind 4: A MN-major ([K,128]), B MN-major  kind 5: A from TMEM (TS form), B MN-major
+ *   kind 6: MXFP4 x MXFP4 block-scaled (E8M0 scale pages)
+ * status_out [4] u32 device: [0] = 0 ok / 1 wait ran out. */
+int fa4b_microgate(int kind, int K, const void* a, const void* b, const void* sfa, const void* sfb,
+                   float* out, uint32_t* status_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA4B_H_ */

@@ -1,0 +1,133 @@
+"""GPU parity of the attention path against the CPU oracle on the same seeded
+inputs: quantised operands bit-exact; O and LSE within rel-L2 1e-2 / abs 1e-3;
+dQ, dK, dV within rel-L2 2e-2."""
+
+import pytest
+import torch
+
+import fa4b_oracle as O
+from fa4b import attention
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _pages(scales):  # [B,H,S,D/16] bytes -> [B,H,S/128,D/64,512]
+    B, H = scales.shape[:2]
+    return torch.stack([torch.stack([O.scales_to_pages(scales[b, h]) for h in range(H)]) for b in range(B)])
+
+
+def _check_operands(ws, fwd):
+    ops = ws.operands()
+    assert torch.equal(ops["q_global"].cpu(), fwd.q_global)
+    assert torch.equal(ops["k_global"].cpu(), fwd.k_global)
+    for name, want in (("q_codes", fwd.q_codes), ("k_codes", fwd.k_codes), ("q_scales", _pages(fwd.q_scales)),
+                       ("k_scales", _pages(fwd.k_scales)), ("v_fp8", fwd.v_fp8.view(torch.uint8))):
+        got = ops[name].cpu().view(torch.uint8)
+        bad = (got != want.view(torch.uint8)).sum().item()
+        assert bad == 0, f"{name}: {bad} bytes differ"
+
+
+def _check_forward(o, lse, fwd):
+    torch.cuda.synchronize()
+    assert O.rel_l2(fwd.lse, lse.cpu()) < 1e-2 and (fwd.lse - lse.cpu()).abs().max() < 1e-3
+    assert O.rel_l2(fwd.o, o.cpu()) < 1e-2, O.rel_l2(fwd.o, o.cpu())
+
+
+FWD_CASES = [
+    # B, Hq, Hkv, S, D, rope
+    (1, 4, 4, 512, 64, False),   # the CPU-runnable reference configuration
+    (1, 4, 1, 256, 128, False),  # one GQA group, D128
+    (2, 8, 2, 384, 128, True),   # RoPE'd, ragged tile count, batch > 1
+    (1, 2, 2, 128, 64, False),   # single tile (diagonal only)
+]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,S,D,rope", FWD_CASES)
+def test_forward_matches_oracle(B, Hq, Hkv, S, D, rope):
+    q, k, v, _ = O.make_attention_inputs(B, Hq, Hkv, S, D, seed=20260825 + S + D, rope=rope)
+    fwd = O.attn_forward(q, k, v)
+    o, lse, ws = attention.attn_forward(q.to(DEV), k.to(DEV), v.to(DEV))
+    ws.check_status()
+    _check_operands(ws, fwd)
+    _check_forward(o, lse, fwd)
+
+
+def test_forward_accepts_bshd_strides_and_custom_scale():
+    q, k, v, _ = O.make_attention_inputs(1, 4, 2, 256, 128, seed=9)
+    fwd = O.attn_forward(q, k, v, softmax_scale=0.05)
+    # [B,S,H,D] storage viewed as [B,H,S,D]
+    qd, kd, vd = (t.permute(0, 2, 1, 3).contiguous().to(DEV).permute(0, 2, 1, 3) for t in (q, k, v))
+    o, lse, ws = attention.attn_forward(qd, kd, vd, softmax_scale=0.05)
+    ws.check_status()
+    _check_forward(o, lse, fwd)
+
+
+def test_forward_is_bitwise_reproducible():
+    q, k, v, _ = O.make_attention_inputs(1, 4, 2, 512, 128, seed=4)
+    a = attention.attn_forward(q.to(DEV), k.to(DEV), v.to(DEV))
+    b = attention.attn_forward(q.to(DEV), k.to(DEV), v.to(DEV))
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_forward_long_sequence_against_chunked_oracle():
+    """S=2048: many kv tiles per query tile (stage ring wraps, maxima move)."""
+    q, k, v, _ = O.make_attention_inputs(1, 4, 1, 2048, 128, seed=17, rope=True)
+    fwd = O.attn_forward(q, k, v, query_chunk=512)
+    o, lse, ws = attention.attn_forward(q.to(DEV), k.to(DEV), v.to(DEV))
+    ws.check_status()
+    _check_forward(o, lse, fwd)
+
+
+def test_backward_preprocess_matches_oracle():
+    q, k, v, do = O.make_attention_inputs(1, 4, 2, 256, 128, seed=21, do_std=0.01)
+    fwd = O.attn_forward(q, k, v)
+    _, _, ws = attention.attn_forward(q.to(DEV), k.to(DEV), v.to(DEV))
+    do5, dstat, lstat = attention.attn_bwd_preprocess(fwd.o.to(DEV), fwd.lse.to(DEV), do.to(DEV), ws)
+    r5, rd, rl = O.attn_bwd_preprocess(fwd.o, do, fwd.lse)
+    assert torch.equal(do5.cpu().view(torch.uint8), r5.view(torch.uint8))
+    assert torch.allclose(lstat.cpu(), rl, rtol=0, atol=1e-5)
+    assert O.rel_l2(rd, dstat.cpu()) < 1e-5
+
+
+BWD_CASES = [
+    (1, 4, 4, 512, 64),    # the CPU-runnable reference configuration
+    (1, 4, 1, 256, 128),   # one GQA group of four query heads
+    (2, 8, 2, 384, 128),   # batch, several kv heads, three key tiles
+    (1, 2, 2, 128, 64),
+]
+
+
+def _run_backward(q, k, v, do, scale=None):
+    fwd = O.attn_forward(q, k, v, softmax_scale=scale)
+    o, lse, ws = attention.attn_forward(q.to(DEV), k.to(DEV), v.to(DEV), softmax_scale=scale)
+    # both sides consume their own forward results, as a training step does
+    want = O.attn_backward(q, k, v, fwd.o, fwd.lse, do, softmax_scale=scale)
+    got = attention.attn_backward(o, lse, do.to(DEV), ws)
+    ws.check_status()
+    return want, got
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,S,D", BWD_CASES)
+def test_backward_matches_oracle(B, Hq, Hkv, S, D):
+    q, k, v, do = O.make_attention_inputs(B, Hq, Hkv, S, D, seed=20260829 + S + D, rope=(D == 128), do_std=0.01)
+    want, got = _run_backward(q, k, v, do)
+    for w, g, name in zip(want, got, ("dq", "dk", "dv")):
+        err = O.rel_l2(w, g.cpu())
+        assert err < 2e-2, (name, err)
+
+
+def test_backward_zero_dout_gives_exact_zero_gradients():
+    # validate_native_tk_d128_backward.py:707-738 of the reference
+    q, k, v, do = O.make_attention_inputs(1, 4, 1, 256, 128, seed=33)
+    o, lse, ws = attention.attn_forward(q.to(DEV), k.to(DEV), v.to(DEV))
+    dq, dk, dv = attention.attn_backward(o, lse, torch.zeros_like(do).to(DEV), ws)
+    ws.check_status()
+    assert not dq.any() and not dk.any() and not dv.any()
+
+
+def test_backward_long_sequence():
+    q, k, v, do = O.make_attention_inputs(1, 4, 1, 1024, 128, seed=41, rope=True, do_std=0.01)
+    want, got = _run_backward(q, k, v, do)
+    for w, g, name in zip(want, got, ("dq", "dk", "dv")):
+        assert O.rel_l2(w, g.cpu()) < 2e-2, name

@@ -1,0 +1,122 @@
+"""GPU parity of the block quantizers against the CPU oracle: codes, scale
+pages and global scales bit-exact (integer/byte work, tolerance zero)."""
+
+import pytest
+import torch
+
+import fa4b
+import fa4b_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _same(a, b, what):
+    a, b = a.cpu(), b.cpu()
+    assert a.shape == b.shape, (what, a.shape, b.shape)
+    bad = (a != b).sum().item()
+    assert bad == 0, f"{what}: {bad} of {a.numel()} bytes differ"
+
+
+@pytest.mark.parametrize("shape,seed", [((128, 128), 1), ((256, 512), 2), ((384, 1024), 3)])
+def test_nvfp4_row_and_transposed_match_oracle(shape, seed):
+    x, _ = O.make_quantizer_inputs(*shape, seed=seed)
+    fp4_row, sc_row, fp4_col, sc_col, sg, am = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=True)
+    ref = O.nvfp4_quantize(x)
+    ref_t = O.nvfp4_quantize_transposed(x)
+    assert float(am) == float(x.float().abs().amax())
+    assert float(sg) == float(ref.global_scale)
+    _same(fp4_row, ref.codes, "row codes")
+    _same(sc_row, ref.pages(), "row scale pages")
+    _same(fp4_col, ref_t.codes, "transposed codes")
+    _same(sc_col, ref_t.pages(), "transposed scale pages")
+    # decode utility agrees with the oracle's decode
+    assert torch.equal(fa4b.dequant_nvfp4(fp4_row, sc_row, sg).cpu(), ref.dequant())
+
+
+def test_nvfp4_edge_cases_zero_tensor_zero_blocks_ties_and_row_only():
+    x = torch.zeros(128, 128, dtype=torch.bfloat16)
+    out = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=False)
+    assert out[2] is None and out[3] is None
+    assert not out[0].any() and not out[1].any() and float(out[4]) == 0.0
+    x, _ = O.make_quantizer_inputs(256, 256, seed=5)
+    x[3, 32:64] = 0
+    x[:, 17] = 0
+    x[9, :16] = (torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0] * 2) * float(x.float().abs().amax()) / 6.0).bfloat16()
+    x[10, :16] = -x[9, :16]
+    fp4_row, sc_row, fp4_col, sc_col, sg, _ = fa4b.tk_quantize_for_gemm(x.to(DEV))
+    ref, ref_t = O.nvfp4_quantize(x), O.nvfp4_quantize_transposed(x)
+    _same(fp4_row, ref.codes, "row codes")
+    _same(sc_row, ref.pages(), "row pages")
+    _same(fp4_col, ref_t.codes, "col codes")
+    _same(sc_col, ref_t.pages(), "col pages")
+
+
+def test_nvfp4_with_supplied_amax_and_strided_input():
+    x, _ = O.make_quantizer_inputs(256, 512, seed=7)
+    big = x.to(DEV)
+    view = big[:, 128:384]  # ld = 512, cols = 256
+    am = torch.tensor([float(x.float().abs().amax())], device=DEV)
+    fp4_row, sc_row, _, _, sg, _ = fa4b.tk_quantize_for_gemm(view, return_transpose=False, amax_in=am)
+    ref = O.nvfp4_quantize(x[:, 128:384].contiguous(), amax=am.cpu())
+    _same(fp4_row, ref.codes, "row codes")
+    _same(sc_row, ref.pages(), "row pages")
+
+
+@pytest.mark.parametrize("mode", ["ceil", "rte_mantissa", "floor"])
+def test_mxfp4_matches_oracle(mode):
+    x, _ = O.make_quantizer_inputs(256, 512, seed=11)
+    x[5, 64:96] = 0
+    x[6, :32] = torch.full((32,), 2.0 ** -100).bfloat16()
+    fp4, sc = fa4b.mxfp4_quantize_for_gemm(x.to(DEV), mode)
+    ref = O.mxfp4_quantize(x, mode)
+    _same(fp4, ref.codes, "codes")
+    _same(sc, ref.pages(), "E8M0 pages")
+    assert torch.equal(fa4b.dequant_mxfp4(fp4, sc).cpu(), ref.dequant())
+
+
+def test_fused_rmsnorm_nvfp4_matches_oracle():
+    x, gamma = O.make_quantizer_inputs(256, 1024, seed=13)
+    fp4_row, sc_row, fp4_col, sc_col, sg, inv_rms, am, y = fa4b.tk_fused_norm_quantize(
+        x.to(DEV), gamma.to(DEV), 1e-6, return_transpose=True, return_normalized=True)
+    _, inv_ref = O.rmsnorm_reference(x, gamma, 1e-6)
+    # FP32 tree sum vs the oracle's FP64 mean: at most 2 ulp on inv_rms
+    ulp = (inv_rms.cpu().view(torch.int32) - inv_ref.view(torch.int32)).abs().max().item()
+    assert ulp <= 2, ulp
+    ref = O.rmsnorm_nvfp4(x, gamma, 1e-6, inv_rms=inv_rms.cpu())
+    _same(y.view(torch.int16), ref.y.view(torch.int16), "normalised bf16")
+    assert float(am) == float(ref.amax) and float(sg) == float(ref.row.global_scale)
+    _same(fp4_row, ref.row.codes, "row codes")
+    _same(sc_row, ref.row.pages(), "row pages")
+    _same(fp4_col, ref.col.codes, "col codes")
+    _same(sc_col, ref.col.pages(), "col pages")
+
+
+def test_full_size_quantizers_by_slabs_and_transpose_property():
+    """16384 x 4096 (the benchmark shape): oracle on sampled 128-row slabs, and the
+    transposed output must equal the row-wise output of the transposed input."""
+    M, K = 16384, 4096
+    x, gamma = O.make_quantizer_inputs(M, K, seed=20260825)
+    xd = x.to(DEV)
+    fp4_row, sc_row, fp4_col, sc_col, sg, am = fa4b.tk_quantize_for_gemm(xd)
+    amax = am.cpu()
+    for r0 in (0, 4096 + 128, M - 128):
+        ref = O.nvfp4_quantize(x[r0:r0 + 128], amax=amax)
+        _same(fp4_row[r0:r0 + 128], ref.codes, f"row codes slab {r0}")
+        _same(sc_row[r0 // 128], ref.pages()[0], f"row pages slab {r0}")
+    t_row, t_sc, _, _, _, _ = fa4b.tk_quantize_for_gemm(xd.t().contiguous(), return_transpose=False)
+    _same(fp4_col, t_row, "transposed codes vs row-wise of x^T")
+    _same(sc_col, t_sc, "transposed pages vs row-wise of x^T")
+    fp4, sc = fa4b.mxfp4_quantize_for_gemm(xd)
+    for r0 in (0, M - 128):
+        ref = O.mxfp4_quantize(x[r0:r0 + 128])
+        _same(fp4[r0:r0 + 128], ref.codes, f"mx codes slab {r0}")
+        _same(sc[r0 // 128], ref.pages()[0], f"mx pages slab {r0}")
+    out = fa4b.tk_fused_norm_quantize(xd, gamma.to(DEV), 1e-6)
+    inv = out[5].cpu()
+    r0 = 8192
+    y = O.rmsnorm_apply(x[r0:r0 + 128], gamma, inv[r0:r0 + 128])
+    ref = O.nvfp4_quantize(y, amax=out[6].cpu())
+    _same(out[0][r0:r0 + 128], ref.codes, "fused row codes slab")
+    _same(out[1][r0 // 128], ref.pages()[0], "fused row pages slab")
+    assert fa4b.amax(xd).item() == float(x.float().abs().amax())
