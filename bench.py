@@ -1,0 +1,337 @@
+#!/usr/bin/env python
+"""Benchmark of the low-precision attention path (and the block quantizers).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one causal attention forward + backward over one batch of synthetic
+input of the Llama-3-8B attention shape (B=2, Hq=32, Hkv=8, S=8192, D=128;
+bf16 N(0,1) Q/K with RoPE theta=5e5, V ~ N(0,1), dO ~ N(0,1e-2)).  With N > 1
+(torchrun, one rank per GPU) every rank runs that shape on its own
+(batch, kv-head) units -- no collective on the data path -- so the global batch
+is 2N ("weak" scaling).  Rank 0 prints one JSON line.
+
+value   : algorithmic TFLOP/s (6 causal matmuls: 2 forward, 4 backward), inputs resident in HBM
+e2e     : same metric through FA4AttentionWrapper + autograd with q, k, v, dO copied
+          from pinned host memory every step and a 16-byte checksum copied back
+roofline: the backward kernel against the FP4/FP8 tensor peak derived from the measured
+          bf16 GEMM rate (x4 for FP4, x2 for FP8; no FP4/FP8 figure is measured on this pool)
+--impl reference times the CPU emulation (oracle/) of the same path on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+for _p in (ROOT / "fp4-fa4_b200", ROOT / "oracle"):
+    if str(_p) not in sys.path:
+        sys.path.insert(0, str(_p))
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    "c2": dict(B=2, Hq=32, Hkv=8, S=8192, D=128),     # the benchmark configuration
+    "small": dict(B=1, Hq=8, Hkv=2, S=8192, D=128),  # same tiles and sequence, 1/8 of the heads: profiler captures only
+}
+WORKLOAD = dict(WORKLOADS["c2"])
+METRIC = "causal_attn_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+
+
+def causal_matmul_flops(B, Hq, S, D):
+    return 2.0 * B * Hq * D * (S * (S + 1) / 2.0)
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=d["hbm_gbs"], bf16=d["bf16_tflops"], bf16_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle samples during the timed region (read-only)."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for r in self.rows if len(r) >= 6 and r[0].isdigit()]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = sorted(int(r[0]) for r in rows)
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows)}
+
+
+def make_inputs(seed, device, pin=False):
+    """Synthetic C2 inputs, generated on the CPU so that every rank/arm sees the same values."""
+    import fa4b_oracle as O
+
+    q, k, v, do = O.make_attention_inputs(WORKLOAD["B"], WORKLOAD["Hq"], WORKLOAD["Hkv"], WORKLOAD["S"], WORKLOAD["D"],
+                                          seed=seed, rope=True, do_std=0.01)
+    host = [t.pin_memory() if pin else t for t in (q, k, v, do)]
+    return host, [t.to(device) for t in host]
+
+
+def cpu_emulation_rate(seconds_budget=20.0, S=4096):
+    """The oracle's forward + backward of one (batch, kv-head) unit (4 query heads) at a reduced
+    sequence length, as algorithmic TFLOP/s on the host cores."""
+    import fa4b_oracle as O
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    D = WORKLOAD["D"]
+    q, k, v, do = O.make_attention_inputs(1, 4, 1, S, D, seed=1, rope=True, do_std=0.01)
+    flops = 6.0 * causal_matmul_flops(1, 4, S, D)
+    reps, t_total = 0, 0.0
+    while reps < 1 or (t_total < seconds_budget and reps < 8):
+        t0 = time.perf_counter()
+        fwd = O.attn_forward(q, k, v)
+        O.attn_backward(q, k, v, fwd.o, fwd.lse, do)
+        t_total += time.perf_counter() - t0
+        reps += 1
+    sec = t_total / reps
+    return dict(value=flops / sec / 1e12, unit=UNIT, cores=torch.get_num_threads(), kind="port",
+                sample=f"oracle fwd+bwd of 1 batch x 1 kv-head group (4 query heads) at S={S}, D={D}; {reps} reps, "
+                       f"{sec:.2f} s each"), sec
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    rates = []
+    for _ in range(max(1, args.warmup and 1)):
+        cpu_emulation_rate(seconds_budget=0.0, S=1024)
+    t_steps = []
+    for _ in range(args.steps):
+        r, sec = cpu_emulation_rate(seconds_budget=0.0, S=4096)
+        rates.append(r)
+        t_steps.append(sec)
+    best = rates[len(rates) // 2]
+    value = sorted(x["value"] for x in rates)[len(rates) // 2]
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * sum(t_steps) / len(t_steps), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 emulation of fp4_e2m1 x fp8_e4m3", "data": "synthetic",
+        "config": {"workload": "C2 Llama-3-8B attention B2 Hq32 Hkv8 S8192 D128 causal fwd+bwd", "timed_sample": best["sample"]},
+        "cpu_baseline": dict(best, value=value),
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def quantizer_rates(device, reps=10):
+    """C4: fused RMSNorm + NVFP4 (row + transposed) and MXFP4 of [16384, 4096] bf16, algorithmic GB/s."""
+    import fa4b
+    import fa4b_oracle as O
+
+    M, K = 16384, 4096
+    x, gamma = O.make_quantizer_inputs(M, K, seed=20260825)
+    x, gamma = x.to(device), gamma.to(device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    out = {}
+    cases = {
+        "rmsnorm_nvfp4_row_col": (lambda: fa4b.tk_fused_norm_quantize(x, gamma, 1e-6), 2 * M * K + 2 * K + 2 * (M * K // 2) + 2 * (M * K // 16) + 4 * M + 4),
+        "nvfp4_row_col": (lambda: fa4b.tk_quantize_for_gemm(x), 2 * M * K + 2 * (M * K // 2) + 2 * (M * K // 16)),
+        "mxfp4": (lambda: fa4b.mxfp4_quantize_for_gemm(x), 2 * M * K + M * K // 2 + M * K // 32),
+    }
+    for name, (fn, nbytes) in cases.items():
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()  # evict the 126 MB L2
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            b.synchronize()
+            ts.append(a.elapsed_time(b))
+        ms = sorted(ts)[len(ts) // 2]
+        out[name] = {"gbs": nbytes / ms / 1e6, "ms": ms, "algorithmic_bytes": nbytes}
+    return out
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+
+    from fa4b import attention, fa4_attention
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    B, Hq, Hkv, S, D = (WORKLOAD[k] for k in ("B", "Hq", "Hkv", "S", "D"))
+    host, (q, k, v, do) = make_inputs(20260825 + rank, device, pin=True)
+    flops_step = 6.0 * causal_matmul_flops(B, Hq, S, D)  # per rank
+    dims = attention.make_dims(q, k, None, "e4m3_fp8")
+    ws = attention.alloc_workspace(dims, device)
+
+    def ev():
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()  # creates the underlying handle
+        return e
+
+    def step(events=None):
+        e = events or [None] * 4
+        o, lse, _ = attention.attn_forward(q, k, v, workspace=ws, events=(e[0], e[1]))
+        return attention.attn_backward(o, lse, do, ws, events=(e[2], e[3]))
+
+    def sync():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ws.check_status()
+    sync()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    pairs = [[ev() for _ in range(4)] for _ in range(args.steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    t0.record()
+    for i in range(args.steps):
+        step(pairs[i])
+    t1.record()
+    sync()
+    ms_total = t0.elapsed_time(t1)
+    clocks = sampler.stop() if rank == 0 else None
+    ws.check_status()
+    fwd_ms = sum(p[0].elapsed_time(p[1]) for p in pairs) / args.steps
+    bwd_ms = sum(p[2].elapsed_time(p[3]) for p in pairs) / args.steps
+
+    extras = not args.no_extras
+    # ---- end to end through the public operator, host buffers, copies inside the timed region
+    wrapper = fa4_attention.FA4AttentionWrapper(fa4_attention.resolve_fa4_config(fa4_attention.FA4()), head_dim=D)
+    dq_, dk_, dv_, ddo = (torch.empty_like(t) for t in (q, k, v, do))
+    result_host = torch.empty(4, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        for dst, src in zip((dq_, dk_, dv_, ddo), host):
+            dst.copy_(src, non_blocking=True)
+        qq, kk, vv = dq_.requires_grad_(True), dk_.requires_grad_(True), dv_.requires_grad_(True)
+        out = wrapper(qq, kk, vv)
+        out.backward(ddo)
+        chk = torch.stack([out.float().sum(), qq.grad.float().sum(), kk.grad.float().sum(), vv.grad.float().sum()])
+        result_host.copy_(chk, non_blocking=True)
+        for t in (qq, kk, vv):
+            t.grad = None
+            t.requires_grad_(False)
+
+    e2e_ms = float("nan")
+    if extras:
+        for _ in range(2):
+            e2e_step()
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record()
+        sync()
+        e2e_ms = e0.elapsed_time(e1)
+
+    times = torch.tensor([ms_total, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms = (float(x) for x in times.cpu())
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = measured_peaks()
+    f1 = causal_matmul_flops(B, Hq, S, D)
+    # backward kernel: 4 algorithmic matmuls; 1 FP4 (score recompute) + 4 FP8 executed
+    p8, p4 = 2.0 * peaks["bf16"], 4.0 * peaks["bf16"]
+    bwd_peak = 4.0 * f1 / (f1 / (p4 * 1e12) + 4.0 * f1 / (p8 * 1e12)) / 1e12
+    bwd_ach = 4.0 * f1 / (bwd_ms * 1e-3) / 1e12
+    fwd_peak = 2.0 * f1 / (f1 / (p4 * 1e12) + f1 / (p8 * 1e12)) / 1e12
+    fwd_ach = 2.0 * f1 / (fwd_ms * 1e-3) / 1e12
+    cpu = cpu_emulation_rate()[0] if extras else None
+    quant = quantizer_rates(device) if extras else {}
+    for qv in quant.values():
+        qv["frac_of_hbm"] = qv["gbs"] / peaks["hbm_gbs"]
+    nbytes_in = sum(t.numel() * t.element_size() for t in host)
+    line = {
+        "metric": METRIC, "value": world * flops_step * args.steps / (ms_total * 1e-3) / 1e12, "unit": UNIT,
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp4_e2m1 (QK^T) x fp8_e4m3/e5m2 (PV, gradients), f32 accumulate", "data": "synthetic",
+        "config": {"workload": ("C2 Llama-3-8B attention B2 Hq32 Hkv8 S8192 D128 causal fwd+bwd per GPU" if args.workload == "c2" else
+                                "PROFILER CASE (not a benchmark result): B1 Hq8 Hkv2 S8192 D128 causal fwd+bwd"),
+                   "global_batch": B * world, "l2": "inputs (448 MiB bf16 + 470 MiB operand cache) exceed the 126 MB L2",
+                   "flops": "6 causal matmuls = 12*B*Hq*D*S(S+1)/2", "includes": "Q/K/V quantisation and dO/statistics publication"},
+        "clocks": clocks,
+        "e2e": {"value": world * flops_step * args.steps / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
+                "h2d_bytes_per_step": nbytes_in, "d2h_bytes_per_step": 16},
+        "gpu_launches": 10 * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "attn_bwd_kernel<128>", "achieved": bwd_ach, "peak": bwd_peak, "unit": UNIT,
+                     "frac": bwd_ach / bwd_peak, "traffic": None, "ms_per_launch": bwd_ms,
+                     "peak_source": f"{peaks['source']} bf16 burst {peaks['bf16']} TF/s x4 (FP4) / x2 (FP8)",
+                     "forward": {"achieved": fwd_ach, "peak": fwd_peak, "frac": fwd_ach / fwd_peak, "ms_per_launch": fwd_ms}},
+        "cpu_baseline": cpu,
+        "quantizers": quant,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=tuple(WORKLOADS), default="c2",
+                    help="'small' is for profiler captures; its line is not a benchmark result")
+    ap.add_argument("--no-extras", action="store_true", help="skip the CPU baseline, quantizer and end-to-end legs")
+    args = ap.parse_args()
+    WORKLOAD.update(WORKLOADS[args.workload])
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU fallback (use --impl reference for the CPU emulation)")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

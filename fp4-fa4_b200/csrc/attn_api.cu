@@ -12,7 +12,7 @@ int fa4b_query(fa4b_info* out) {
   out->build_sm = 100;
   out->tile_q = 128;
   out->tile_kv = 128;
-  out->wait_limit = (int)kWaitLimit;
+  out->wait_limit = (int)(kWaitLimitNs / 1000000);
   fill_kernel_info(out);
   return FA4B_OK;
 }
@@ -40,7 +40,7 @@ extern "C" int fa4b_attn_check_status(const fa4b_attn_dims* d, const void* ws, v
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   FA4B_CUDA(cudaMemcpyAsync(host, static_cast<const uint8_t*>(ws) + l.status, sizeof(host), cudaMemcpyDeviceToHost, st));
   FA4B_CUDA(cudaStreamSynchronize(st));
-  FA4B_REQUIRE(host[0] == 0, FA4B_TIMEOUT, "a device-side wait ran out (site %u)", host[1]);
+  FA4B_REQUIRE(host[0] == 0, FA4B_TIMEOUT, "a device-side wait ran out (site %u, block %u, detail %u)", host[1], host[2], host[3]);
   return FA4B_OK;
 }
 

@@ -106,6 +106,13 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
   const int n_sub = (n_tiles - kt) * sub_per_tile;  // query sub-tiles per head
   const int n_it = G * n_sub;
   const int sub0 = kt * sub_per_tile;
+  {
+    // an earlier CTA of this launch gave up: leave at once, as one (the decision is CTA-uniform)
+    __shared__ uint32_t skip;
+    if (t == 0) skip = *reinterpret_cast<volatile uint32_t*>(p.status);
+    __syncthreads();
+    if (skip != 0u) return;
+  }
 
   if (t == 0) {
     mbar_init(&s.kv_full, 1);
@@ -139,7 +146,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       tma_load_3d(s.v8, &map_v8, 0, kt * 128, bhk, &s.kv_full);
       for (int it = 0; it < n_it; ++it) {
         const int st = it % kBwdStages;
-        if (it >= kBwdStages && !mbar_wait(&s.in_empty[st], ((it / kBwdStages) - 1) & 1, &s.abort_flag, p.status, 110)) break;
+        if (it >= kBwdStages && !mbar_wait(&s.in_empty[st], ((it / kBwdStages) - 1) & 1, &s.abort_flag, p.status, 110, it)) break;
         const int g = it / n_sub, qs = sub0 + it % n_sub;
         const int bh = b * p.Hq + hk * G + g;
         const int q0 = qs * QT;
@@ -169,7 +176,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       // S^T and dP^T of iteration `it` (inputs in stage it % kBwdStages)
       auto issue_scores = [&](int it) -> bool {
         const int st = it % kBwdStages;
-        if (!mbar_wait(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 121)) return false;
+        if (!mbar_wait(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 121, it)) return false;
         tc_fence_after();
         const int qs = sub0 + it % n_sub;
         const uint32_t sf_shift = (QT == 64) ? 2u * (uint32_t)(qs & 1) : 0u;  // which 64 rows of the 128-row scale page
@@ -188,14 +195,14 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       if (ok) ok = issue_scores(0);
       for (int it = 0; ok && it < n_it; ++it) {
         const int st = it % kBwdStages, buf = it & 1;
-        ok = mbar_wait(&s.pt_ready, it & 1, &s.abort_flag, p.status, 122);
+        ok = mbar_wait(&s.pt_ready, it & 1, &s.abort_flag, p.status, 122, it);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < QT / 32; ++k)
           mma_f8_ss(tm + C::colDV, make_tile_desc(smem_u32(s.pt[buf]) + 32 * k, QT), make_tile_desc(smem_u32(s.do5[st]) + 32 * D * k, D),
                     id_dv, (it > 0 || k > 0) ? 1u : 0u);
-        ok = mbar_wait(&s.ds_ready, it & 1, &s.abort_flag, p.status, 123);
+        ok = mbar_wait(&s.ds_ready, it & 1, &s.abort_flag, p.status, 123, it);
         if (!ok) break;
         tc_fence_after();
         if (it + 1 < n_it) {
@@ -207,7 +214,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           mma_f8_ss(tm + C::colDK, make_tile_desc(smem_u32(s.dst[buf]) + 32 * k, QT), make_tile_desc(smem_u32(s.q8[st]) + 32 * D * k, D),
                     id_dk, (it > 0 || k > 0) ? 1u : 0u);
         if (it > 0) {
-          ok = mbar_wait(&s.dq_free, (it - 1) & 1, &s.abort_flag, p.status, 124);
+          ok = mbar_wait(&s.dq_free, (it - 1) & 1, &s.abort_flag, p.status, 124, it);
           if (!ok) break;
           tc_fence_after();
         }
@@ -231,7 +238,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     const uint32_t lane_base = tm + ((uint32_t)(w4 * 32) << 16);
     const int r = w4 * 32 + lane;  // TMEM lane: d (D = 128) or query row (D = 64)
     for (int it = 0; it < n_it; ++it) {
-      if (!mbar_wait(&s.dq_full, it & 1, &s.abort_flag, p.status, 130)) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(&s.dq_full, it & 1, &s.abort_flag, p.status, 130, it))) break;
       tc_fence_after();
       const int g = it / n_sub, qs = sub0 + it % n_sub;
       const int bh = b * p.Hq + hk * G + g;
@@ -240,7 +247,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       for (int c0 = 0; c0 < 64; c0 += 32) {
         uint32_t v[32];
         tmem_ld32(lane_base + C::colDQ + c0, v);
-        tmem_ld_wait();
+        tmem_ld_wait(v);
         if (D == 128) {
           // lane = d, column = query row: one coalesced 128-byte reduction per column
 #pragma unroll
@@ -272,7 +279,10 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       const float c2 = kg * p.q_global[bh];
       const int q_first = qs * QT + half * CW;   // global query index of this thread's first column
       const bool diag = qs * QT < kt * 128 + 128;  // sub-tile overlaps the key tile: mask needed
-      ok = mbar_wait(&s.st_full, it & 1, &s.abort_flag, p.status, 140);
+      // the row statistics arrive through the async proxy: observe their barrier before reading them
+      ok = __all_sync(0xffffffffu, mbar_wait(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 143, it));
+      if (!ok) break;
+      ok = __all_sync(0xffffffffu, mbar_wait(&s.st_full, it & 1, &s.abort_flag, p.status, 140, it));
       if (!ok) break;
       tc_fence_after();
       uint32_t pk[CW / 4];
@@ -280,7 +290,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       for (int c0 = 0; c0 < CW; c0 += 32) {
         uint32_t v[32];
         tmem_ld32(lane_base + C::colSt + half * CW + c0, v);
-        tmem_ld_wait();
+        tmem_ld_wait(v);
         float pr[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -299,14 +309,14 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       tc_fence_before();
       mbar_arrive(&s.pt_ready);
 
-      ok = mbar_wait(&s.dp_full, it & 1, &s.abort_flag, p.status, 141);
+      ok = __all_sync(0xffffffffu, mbar_wait(&s.dp_full, it & 1, &s.abort_flag, p.status, 141, it));
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
       for (int c0 = 0; c0 < CW; c0 += 32) {
         uint32_t v[32];
         tmem_ld32(lane_base + C::colDPt + half * CW + c0, v);
-        tmem_ld_wait();
+        tmem_ld_wait(v);
         uint32_t dk4[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -330,6 +340,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     }
     // ------------------------------------------------------------------ dK, dV of this key tile
     if (ok) ok = mbar_wait(&s.acc_done, 0, &s.abort_flag, p.status, 142);
+    ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
       constexpr float inv = 1.0f / 1024.0f;
@@ -343,7 +354,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         for (int c0 = 0; c0 < D / 2; c0 += 32) {
           uint32_t v[32];
           tmem_ld32(lane_base + col + c0, v);
-          tmem_ld_wait();
+          tmem_ld_wait(v);
           uint32_t w[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -425,8 +436,10 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
     }
   }
   const unsigned grid = (unsigned)(nk * (S / 128));
+  if (a.ev_before) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_before), st));
   attn_bwd_kernel<D><<<grid, kBwdThreads, smem, st>>>(p, m_kc, m_k8, m_v8, m_qc, m_q8, m_do);
   FA4B_CUDA(cudaGetLastError());
+  if (a.ev_after) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_after), st));
   const int64_t n_rows = (int64_t)nq * S;
   const unsigned cgrid = (unsigned)std::min<int64_t>((n_rows * (D / 8) + 255) / 256, 148 * 16);
   dq_convert_kernel<D><<<cgrid, 256, 0, st>>>(p.dq_accum, d.Hq, d.S, n_rows, static_cast<__nv_bfloat16*>(a.dq), a.dq_strides.batch,
@@ -448,7 +461,9 @@ int launch_attn_bwd(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   if (int s = check_out(a.dq, a.dq_strides, "dq")) return s;
   if (int s = check_out(a.dk, a.dk_strides, "dk")) return s;
   if (int s = check_out(a.dv, a.dv_strides, "dv")) return s;
-  if (int s = launch_attn_bwd_preprocess(a, st)) return s;
+  if (!a.preprocessed) {
+    if (int s = launch_attn_bwd_preprocess(a, st)) return s;
+  }
   return a.dims.D == 128 ? bwd_impl<128>(a, st) : bwd_impl<64>(a, st);
 }
 

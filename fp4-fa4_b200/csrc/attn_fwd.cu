@@ -73,6 +73,13 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
   const int b = bh / p.Hq, h = bh % p.Hq;
   const int bhk = b * p.Hkv + h / (p.Hq / p.Hkv);
   const int n_kv = qt + 1;
+  {
+    // an earlier CTA of this launch gave up: leave at once, as one (the decision is CTA-uniform)
+    __shared__ uint32_t skip;
+    if (t == 0) skip = *reinterpret_cast<volatile uint32_t*>(p.status);
+    __syncthreads();
+    if (skip != 0u) return;
+  }
 
   if (t == 0) {
     mbar_init(&s.q_full, 1);
@@ -105,7 +112,7 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       bulk_load(s.q_sf, p.q_sf + ((size_t)bh * n_tiles + qt) * kPages * 512, kPages * 512, &s.q_full);
       for (int j = 0; j < n_kv; ++j) {
         const int st = j % kStages;
-        if (j >= kStages && !mbar_wait(&s.kv_empty[st], ((j / kStages) - 1) & 1, &s.abort_flag, p.status, 10)) break;
+        if (j >= kStages && !mbar_wait(&s.kv_empty[st], ((j / kStages) - 1) & 1, &s.abort_flag, p.status, 10, j)) break;
         mbar_expect_tx(&s.kv_full[st], kKvBytes);
         tma_load_3d(s.k_codes[st], &map_k, 0, j * 128, bhk, &s.kv_full[st]);
         bulk_load(s.k_sf[st], p.k_sf + ((size_t)bhk * n_tiles + j) * kPages * 512, kPages * 512, &s.kv_full[st]);
@@ -125,7 +132,7 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       for (int j = 0; ok && j <= n_kv; ++j) {
         if (j < n_kv) {
           const int st = j % kStages, sb = j & 1;
-          ok = mbar_wait(&s.kv_full[st], (j / kStages) & 1, &s.abort_flag, p.status, 21);
+          ok = mbar_wait(&s.kv_full[st], (j / kStages) & 1, &s.abort_flag, p.status, 21, j);
           if (!ok) break;
           tc_fence_after();
           for (int pg = 0; pg < kPages; ++pg)
@@ -139,7 +146,7 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         }
         if (j > 0) {
           const int jj = j - 1, st = jj % kStages, sb = jj & 1;
-          ok = mbar_wait(&s.p_ready[sb], (jj >> 1) & 1, &s.abort_flag, p.status, 22);
+          ok = mbar_wait(&s.p_ready[sb], (jj >> 1) & 1, &s.abort_flag, p.status, 22, j);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
@@ -163,7 +170,8 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
     // wait has given up (ok == false): a thread that left early would strand its partner.
     for (int j = 0; j < n_kv; ++j) {
       const int sb = j & 1;
-      if (ok) ok = mbar_wait(&s.s_full[sb], (j >> 1) & 1, &s.abort_flag, p.status, 30);
+      if (ok) ok = mbar_wait(&s.s_full[sb], (j >> 1) & 1, &s.abort_flag, p.status, 30, j);
+      ok = __all_sync(0xffffffffu, ok);
       float x[64];
       float mx = -INFINITY;
       if (ok) {
@@ -171,7 +179,8 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         uint32_t r0[32], r1[32];
         tmem_ld32(lane_base + kColS + 128 * sb + 64 * half, r0);
         tmem_ld32(lane_base + kColS + 128 * sb + 64 * half + 32, r1);
-        tmem_ld_wait();
+        tmem_ld_wait(r0);
+        tmem_ld_wait(r1);
         const bool diag = (j == qt);
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -191,26 +200,26 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       mx = fmaxf(mx, s.xchg[sb][half ^ 1][row]);
       if (!ok) continue;
       const float mnew = fmaxf(mhat, ceilf(mx));
-      if (mnew > mhat) {
-        if (j > 0) {
-          // O and the running sum move to the new reference point (a power of two)
-          const float f = ex2_approx(mhat - mnew);
-          lsum *= f;
-          ok = mbar_wait(&s.o_done, (j - 1) & 1, &s.abort_flag, p.status, 31);
-          if (!ok) continue;
-          tc_fence_after();
+      // tcgen05.ld/st are warp-collective: the accumulator rescale is taken by the whole warp
+      // as soon as one of its rows has a new maximum (factor 1 for the rows that keep theirs)
+      if (j > 0 && __any_sync(0xffffffffu, mnew > mhat)) {
+        const float f = ex2_approx(mhat - mnew);  // 2^0 = 1 when unchanged
+        lsum *= f;
+        ok = mbar_wait(&s.o_done, (j - 1) & 1, &s.abort_flag, p.status, 31, j);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) continue;
+        tc_fence_after();
 #pragma unroll
-          for (int c0 = 0; c0 < D / 2; c0 += 32) {
-            uint32_t r[32];
-            tmem_ld32(lane_base + kColO + (D / 2) * half + c0, r);
-            tmem_ld_wait();
+        for (int c0 = 0; c0 < D / 2; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(lane_base + kColO + (D / 2) * half + c0, r);
+          tmem_ld_wait(r);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
-            tmem_st32(lane_base + kColO + (D / 2) * half + c0, r);
-          }
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
+          tmem_st32(lane_base + kColO + (D / 2) * half + c0, r);
         }
-        mhat = mnew;
       }
+      mhat = mnew;
       const float shift = kPLift - mhat;
       uint32_t pa[8], pb[8];
 #pragma unroll
@@ -228,7 +237,8 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       mbar_arrive(&s.p_ready[sb]);
     }
     // ---------------------------------------------------------------- epilogue
-    if (ok) ok = mbar_wait(&s.o_done, (n_kv - 1) & 1, &s.abort_flag, p.status, 32);
+    if (ok) ok = mbar_wait(&s.o_done, (n_kv - 1) & 1, &s.abort_flag, p.status, 32, n_kv);
+    ok = __all_sync(0xffffffffu, ok);
     s.lsum_x[half][row] = lsum;
     named_bar_sync(1, 256);
     if (ok) {
@@ -240,7 +250,7 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       for (int c0 = 0; c0 < D / 2; c0 += 32) {
         uint32_t r[32];
         tmem_ld32(lane_base + kColO + (D / 2) * half + c0, r);
-        tmem_ld_wait();
+        tmem_ld_wait(r);
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -293,8 +303,10 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
     }
   }
   const unsigned grid = (unsigned)(d.B * d.Hq * (d.S / 128));
+  if (a.ev_before) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_before), st));
   attn_fwd_kernel<D><<<grid, kFwdThreads, smem, st>>>(p, mq, mk, mv);
   FA4B_CUDA(cudaGetLastError());
+  if (a.ev_after) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_after), st));
   return FA4B_OK;
 }
 

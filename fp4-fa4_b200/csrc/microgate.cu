@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(128, 1) microgate_kernel(int kind, int K, cons
     for (int c0 = 0; c0 < 128; c0 += 32) {
       uint32_t r[32];
       tmem_ld32(lane_addr + c0, r);
-      tmem_ld_wait();
+      tmem_ld_wait(r);
 #pragma unroll
       for (int j = 0; j < 32; ++j) out[(size_t)t * 128 + c0 + j] = __uint_as_float(r[j]);
     }

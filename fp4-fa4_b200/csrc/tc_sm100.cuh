@@ -8,9 +8,9 @@
 
 namespace fa4b {
 
-// every device-side wait gives up after this many polls, records where, and the
-// kernel tears down (TMEM freed) instead of spinning
-constexpr uint32_t kWaitLimit = 1u << 22;
+// every device-side wait gives up after this long, records where, and the kernel
+// tears down (TMEM freed) instead of spinning
+constexpr uint64_t kWaitLimitNs = 400ull * 1000 * 1000;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -34,20 +34,37 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  `abort_flag` lives in shared memory: once any role has given up,
-// every other wait returns false at once so that all roles reach the teardown.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
-                                          uint32_t where) {
-  for (uint32_t it = 0; it < kWaitLimit; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 63u && *abort_flag) return false;
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait (wall-clock limit kWaitLimitNs).  `abort_flag` lives in shared memory:
+// once any role has given up, every other wait of the CTA returns false at once so
+// that all roles reach the teardown.  status[0] = 1, status[1] = site, status[2] =
+// block, status[3] = caller's detail word.
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
+                                            uint32_t where, uint32_t detail) {
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > kWaitLimitNs) break;
   }
   *abort_flag = 1u;
-  if (status) {
-    atomicExch(status, 1u);
-    atomicExch(status + 1, where);
+  if (status && atomicCAS(status, 0u, 1u) == 0u) {
+    status[1] = where;
+    status[2] = blockIdx.x;
+    status[3] = detail;
   }
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
+                                          uint32_t where, uint32_t detail = 0) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, status, where, detail);
 }
 
 // ---- proxies and fences -----------------------------------------------------------
@@ -106,6 +123,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+#define FA4B_RW8(r, o) "+r"(r[o + 0]), "+r"(r[o + 1]), "+r"(r[o + 2]), "+r"(r[o + 3]), "+r"(r[o + 4]), "+r"(r[o + 5]), "+r"(r[o + 6]), "+r"(r[o + 7])
+// wait for the loads and make the compiler treat the registers as produced here
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : FA4B_RW8(r, 0), FA4B_RW8(r, 8), FA4B_RW8(r, 16), FA4B_RW8(r, 24)::"memory");
+}
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
                "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])

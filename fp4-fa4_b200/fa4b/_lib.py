@@ -60,13 +60,15 @@ class AttnPrepareArgs(C.Structure):
 class AttnFwdArgs(C.Structure):
     _fields_ = [("dims", AttnDims), ("q", C.c_void_p), ("q_strides", Strides), ("k", C.c_void_p), ("k_strides", Strides),
                 ("v", C.c_void_p), ("v_strides", Strides), ("o", C.c_void_p), ("o_strides", Strides),
-                ("lse", C.c_void_p), ("ws", C.c_void_p), ("prepared", C.c_int32)]
+                ("lse", C.c_void_p), ("ws", C.c_void_p), ("prepared", C.c_int32), ("ev_before", C.c_void_p),
+                ("ev_after", C.c_void_p)]
 
 
 class AttnBwdArgs(C.Structure):
     _fields_ = [("dims", AttnDims), ("o", C.c_void_p), ("o_strides", Strides), ("dout", C.c_void_p), ("do_strides", Strides),
                 ("lse", C.c_void_p), ("dq", C.c_void_p), ("dq_strides", Strides), ("dk", C.c_void_p), ("dk_strides", Strides),
-                ("dv", C.c_void_p), ("dv_strides", Strides), ("ws", C.c_void_p)]
+                ("dv", C.c_void_p), ("dv_strides", Strides), ("ws", C.c_void_p), ("preprocessed", C.c_int32),
+                ("ev_before", C.c_void_p), ("ev_after", C.c_void_p)]
 
 
 class Info(C.Structure):

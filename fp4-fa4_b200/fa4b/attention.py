@@ -82,7 +82,12 @@ def alloc_workspace(dims: _lib.AttnDims, device) -> Workspace:
     return Workspace(dims, layout, buf[shift:shift + layout.total])
 
 
-def attn_forward(q, k, v, softmax_scale: float | None = None, pv_format: str = "e4m3_fp8", workspace: Workspace | None = None):
+def _ev(e) -> int:
+    return 0 if e is None else e.cuda_event
+
+
+def attn_forward(q, k, v, softmax_scale: float | None = None, pv_format: str = "e4m3_fp8", workspace: Workspace | None = None,
+                 prepared: bool = False, events=(None, None)):
     """O ``[B,Hq,S,D]`` bf16, LSE ``[B,Hq,S]`` f32 and the workspace holding the quantised operands."""
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _check_bhsd(t, n)
@@ -94,12 +99,18 @@ def attn_forward(q, k, v, softmax_scale: float | None = None, pv_format: str = "
     o = torch.empty(B, Hq, S, D, dtype=torch.bfloat16, device=q.device)
     lse = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
     a = _lib.AttnFwdArgs(dims, ptr(q), _strides(q), ptr(k), _strides(k), ptr(v), _strides(v), ptr(o), _strides(o), ptr(lse),
-                         ptr(ws.buf), 0)
+                         ptr(ws.buf), int(prepared), _ev(events[0]), _ev(events[1]))
     check(lib().fa4b_attn_fwd(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_fwd")
     return o, lse, ws
 
 
-def attn_backward(o, lse, dout, ws: Workspace):
+def attn_prepare(q, k, v, ws: Workspace) -> None:
+    """Publish the quantised operands of q, k, v into ``ws`` (the first half of :func:`attn_forward`)."""
+    a = _lib.AttnPrepareArgs(ws.dims, ptr(q), _strides(q), ptr(k), _strides(k), ptr(v), _strides(v), ptr(ws.buf))
+    check(lib().fa4b_attn_prepare(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_prepare")
+
+
+def attn_backward(o, lse, dout, ws: Workspace, preprocessed: bool = False, events=(None, None)):
     """dQ ``[B,Hq,S,D]``, dK, dV ``[B,Hkv,S,D]`` bf16, replaying the operands the forward cached in ``ws``."""
     for t, n in ((o, "o"), (dout, "dout")):
         _check_bhsd(t, n)
@@ -108,7 +119,7 @@ def attn_backward(o, lse, dout, ws: Workspace):
     dk = torch.empty(d.B, d.Hkv, d.S, d.D, dtype=torch.bfloat16, device=o.device)
     dv = torch.empty_like(dk)
     a = _lib.AttnBwdArgs(d, ptr(o), _strides(o), ptr(dout), _strides(dout), ptr(lse), ptr(dq), _strides(dq), ptr(dk), _strides(dk),
-                         ptr(dv), _strides(dv), ptr(ws.buf))
+                         ptr(dv), _strides(dv), ptr(ws.buf), int(preprocessed), _ev(events[0]), _ev(events[1]))
     check(lib().fa4b_attn_bwd(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_bwd")
     return dq, dk, dv
 
@@ -116,7 +127,7 @@ def attn_backward(o, lse, dout, ws: Workspace):
 def attn_bwd_preprocess(o, lse, dout, ws: Workspace):
     d = ws.dims
     a = _lib.AttnBwdArgs(d, ptr(o), _strides(o), ptr(dout), _strides(dout), ptr(lse), 0, _lib.Strides(), 0, _lib.Strides(), 0,
-                         _lib.Strides(), ptr(ws.buf))
+                         _lib.Strides(), ptr(ws.buf), 0, 0, 0)
     check(lib().fa4b_attn_bwd_preprocess(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_bwd_preprocess")
     ops = ws.operands()
     return ops["do_fp8"], ops["dstat"], ops["lstat"]

@@ -52,7 +52,7 @@ typedef struct fa4b_info {
   int fwd_threads, fwd_smem_bytes, fwd_tmem_columns, fwd_kv_stages;
   int bwd_threads, bwd_smem_bytes, bwd_tmem_columns;
   int tile_q, tile_kv;     /* 128, 128                                        */
-  int wait_limit;          /* iteration cap of every device-side wait         */
+  int wait_limit;          /* wall-clock cap of every device-side wait, ms    */
 } fa4b_info;
 int fa4b_query(fa4b_info* out);
 
@@ -188,6 +188,8 @@ typedef struct fa4b_attn_fwd_args {
   float* lse;
   void* ws;
   int32_t prepared;
+  void* ev_before; /* optional cudaEvent_t recorded just before / after the */
+  void* ev_after;  /* attention kernel itself (per-kernel timing)           */
 } fa4b_attn_fwd_args;
 int fa4b_attn_fwd(const fa4b_attn_fwd_args* a, void* stream);
 
@@ -204,13 +206,17 @@ typedef struct fa4b_attn_bwd_args {
   void* dk; fa4b_strides dk_strides;
   void* dv; fa4b_strides dv_strides;
   void* ws; /* the workspace the forward filled (operands are replayed from it) */
+  int32_t preprocessed; /* non-zero: fa4b_attn_bwd_preprocess already ran on ws */
+  void* ev_before;      /* optional cudaEvent_t around the main backward kernel */
+  void* ev_after;
 } fa4b_attn_bwd_args;
 int fa4b_attn_bwd_preprocess(const fa4b_attn_bwd_args* a, void* stream);
 
 /* fa4b_attn_bwd: dQ, dK, dV (bf16, written, not accumulated).  Replaces
  * backward_nvfp4_score_e4m3_qkv_e5m2_dout_bshd_precleared_dq_out
  * (tk_fa4/native_gqa_tk_bwd/v509_*bshd.cu:406-444) and the D64 kernel v416.
- * Runs the preprocess step itself. */
+ * Runs the preprocess step itself unless `preprocessed` is set.  Uses the
+ * workspace's FP32 dQ accumulator as scratch (zeroed here). */
 int fa4b_attn_bwd(const fa4b_attn_bwd_args* a, void* stream);
 
 /* fa4b_attn_check_status: synchronises `stream`, then reports FA4B_TIMEOUT if a
