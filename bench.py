@@ -103,7 +103,7 @@ def make_inputs(seed, device, pin=False):
     return host, [t.to(device) for t in host]
 
 
-def cpu_emulation_rate(seconds_budget=20.0, S=4096):
+def cpu_emulation_rate(seconds_budget=12.0, S=4096):
     """The oracle's forward + backward of one (batch, kv-head) unit (4 query heads) at a reduced
     sequence length, as algorithmic TFLOP/s on the host cores."""
     import fa4b_oracle as O
@@ -113,7 +113,7 @@ def cpu_emulation_rate(seconds_budget=20.0, S=4096):
     q, k, v, do = O.make_attention_inputs(1, 4, 1, S, D, seed=1, rope=True, do_std=0.01)
     flops = 6.0 * causal_matmul_flops(1, 4, S, D)
     reps, t_total = 0, 0.0
-    while reps < 1 or (t_total < seconds_budget and reps < 8):
+    while reps < 1 or (t_total < seconds_budget and reps < 256):
         t0 = time.perf_counter()
         fwd = O.attn_forward(q, k, v)
         O.attn_backward(q, k, v, fwd.o, fwd.lse, do)
