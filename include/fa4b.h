@@ -193,6 +193,20 @@ typedef struct fa4b_attn_fwd_args {
 } fa4b_attn_fwd_args;
 int fa4b_attn_fwd(const fa4b_attn_fwd_args* a, void* stream);
 
+/* fa4b_attn_fwd_static: fa4b_attn_fwd for hosts that cannot allocate device
+ * memory where attention runs (an execute hook that must not allocate, a
+ * serving loop with a frozen memory budget).  No counterpart in the reference,
+ * whose callers always pre-allocate.  `ws` and `prepared` of the args are
+ * ignored: the operand cache is a fixed array inside the library, held by every
+ * GPU that loads it until the process exits.  Shapes whose cache
+ * (fa4b_attn_workspace_bytes) exceeds FA4B_STATIC_WS_BYTES are rejected with
+ * FA4B_BAD_SHAPE.  Calls no cudaMalloc/cudaFree or any allocating routine.
+ * The first call on a device looks the array's address up (once per device,
+ * with that device current); make that first call before any stream capture.
+ * All calls share the array: calls that overlap on the GPU race. */
+#define FA4B_STATIC_WS_BYTES (8u << 20)
+int fa4b_attn_fwd_static(const fa4b_attn_fwd_args* a, void* stream);
+
 /* fa4b_attn_bwd_preprocess: dO5 = E5M2(4 dO), dstat = -4 sum_d O*dO5,
  * lstat = 8 - LSE*log2e, into `ws`.  Replaces the dO/statistics publisher
  * project_dout_unified_fp4_nvfp4_v509_e5m2
