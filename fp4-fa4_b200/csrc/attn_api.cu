@@ -12,7 +12,7 @@ int fa4b_query(fa4b_info* out) {
   out->build_sm = 100;
   out->tile_q = 128;
   out->tile_kv = 128;
-  out->wait_limit = (int)(kWaitLimitNs / 1000000);
+  out->wait_limit = (int)(kWaitLimitCycles / 2000000);  // ms at 2 GHz
   fill_kernel_info(out);
   return FA4B_OK;
 }

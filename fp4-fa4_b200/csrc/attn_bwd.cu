@@ -20,7 +20,7 @@
 namespace fa4b {
 
 constexpr int kBwdThreads = 448;
-constexpr int kBwdStages = 3;
+constexpr int kBwdStages = 5;
 
 template <int D>
 struct BwdCfg {
@@ -46,10 +46,13 @@ struct BwdSmem {
   alignas(16) uint8_t q_sf[kBwdStages][C::kPages * 512];
   alignas(16) float lstat[kBwdStages][C::QT];
   alignas(16) float dstat[kBwdStages][C::QT];
-  alignas(8) uint64_t kv_full, in_full[kBwdStages], in_empty[kBwdStages], st_full, dp_full, pt_ready, ds_ready, dq_full, dq_free,
-      acc_done;
+  alignas(16) float c2[16];  // per query head of the group: global scales * softmax scale * log2(e)
+  alignas(8) uint64_t kv_full, in_full[kBwdStages], in_empty[kBwdStages], st_full, dp_full, pt_ready[2], ds_ready[2], dq_full, dq_free,
+      acc_done, mma_drained;
   uint32_t tmem_base;
-  volatile uint32_t abort_flag;
+  alignas(8) volatile uint32_t abort_flag;
+  uint32_t pad_;
+  FA4B_PROF_FIELD
 };
 
 struct BwdParams {
@@ -122,20 +125,29 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     }
     mbar_init(&s.st_full, 1);
     mbar_init(&s.dp_full, 1);
-    mbar_init(&s.pt_ready, 256);
-    mbar_init(&s.ds_ready, 256);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.pt_ready[i], 256);
+      mbar_init(&s.ds_ready[i], 256);
+    }
     mbar_init(&s.dq_full, 1);
     mbar_init(&s.dq_free, 128);
     mbar_init(&s.acc_done, 1);
+    mbar_init(&s.mma_drained, 1);
     s.abort_flag = 0;
     fence_barrier_init();
   }
+  waitprof_clear(&s.abort_flag);
   if (warp == 12) tmem_alloc(&s.tmem_base, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = s.tmem_base;
 
+#ifdef FA4B_EXP_NOSYNC
+  if (warp >= 8 && !(warp >= 8 && warp < 12 && 1)) {
+    // timing experiment: producer and issuer (and nothing they would feed) stay idle
+  } else
+#endif
   if (warp == 12) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
@@ -144,9 +156,11 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       bulk_load(s.k_sf, p.k_sf + ((size_t)bhk * n_tiles + kt) * kPages * 512, kPages * 512, &s.kv_full);
       tma_load_3d(s.k8, &map_k8, 0, kt * 128, bhk, &s.kv_full);
       tma_load_3d(s.v8, &map_v8, 0, kt * 128, bhk, &s.kv_full);
+      int issued = 0;
       for (int it = 0; it < n_it; ++it) {
         const int st = it % kBwdStages;
         if (it >= kBwdStages && !mbar_wait(&s.in_empty[st], ((it / kBwdStages) - 1) & 1, &s.abort_flag, p.status, 110, it)) break;
+        issued = it + 1;
         const int g = it / n_sub, qs = sub0 + it % n_sub;
         const int bh = b * p.Hq + hk * G + g;
         const int q0 = qs * QT;
@@ -158,6 +172,10 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         bulk_load(s.lstat[st], p.lstat + (size_t)bh * p.S + q0, QT * 4, &s.in_full[st]);
         bulk_load(s.dstat[st], p.dstat + (size_t)bh * p.S + q0, QT * 4, &s.in_full[st]);
       }
+      // no copy of this CTA may still be in flight when its shared memory is given up
+      mbar_wait_teardown(&s.kv_full, 0);
+      for (int it = issued > kBwdStages ? issued - kBwdStages : 0; it < issued; ++it)
+        mbar_wait_teardown(&s.in_full[it % kBwdStages], (it / kBwdStages) & 1);
     }
   } else if (warp == 13) {
     // ------------------------------------------------------------------ MMA issuer
@@ -167,52 +185,84 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       constexpr uint32_t id_dv = idesc_f8(128, D, 0, 1, 0, 1);    // P8^T (K-major) x dO5 (MN-major)
       constexpr uint32_t id_dk = idesc_f8(128, D, 0, 0, 0, 1);    // dS8^T (K-major) x Q8 (MN-major)
       constexpr uint32_t id_dq = idesc_f8(128, 64, 0, 0, 1, 1);   // both MN-major
-      const uint32_t kc = smem_u32(s.k_codes), k8 = smem_u32(s.k8), v8 = smem_u32(s.v8);
+      // The issuing thread shares its scheduler with busy compute warps, so its instruction count
+      // bounds the issue rate: every descriptor is a precomputed base plus a small constant
+      // (the address field counts 16-byte units).
+      const uint64_t d_kc = make_tile_desc(smem_u32(s.k_codes), D / 2), d_k8 = make_tile_desc(smem_u32(s.k8), D);
+      const uint64_t d_v8 = make_tile_desc(smem_u32(s.v8), D);
+      const uint64_t d_qc0 = make_tile_desc(smem_u32(s.q_codes[0]), D / 2), d_q80 = make_tile_desc(smem_u32(s.q8[0]), D);
+      const uint64_t d_do0 = make_tile_desc(smem_u32(s.do5[0]), D);
+      const uint64_t d_pt0 = make_tile_desc(smem_u32(s.pt[0]), QT), d_ds0 = make_tile_desc(smem_u32(s.dst[0]), QT);
+      const uint64_t d_sfq0 = make_page_desc(smem_u32(s.q_sf[0]));
+      constexpr uint32_t kQc16 = (QT * D / 2) >> 4, kQ816 = (QT * D) >> 4, kSf16 = (kPages * 512) >> 4, kPt16 = (128 * QT) >> 4;
+      constexpr uint32_t kRow32D = (32 * D) >> 4, kRow32Q = (32 * QT) >> 4;
       bool ok = mbar_wait(&s.kv_full, 0, &s.abort_flag, p.status, 120);
       if (ok) {
         tc_fence_after();
+#pragma unroll
         for (int pg = 0; pg < kPages; ++pg) tmem_cp_page(tm + C::colSfa + 4 * pg, make_page_desc(smem_u32(s.k_sf + 512 * pg)));
       }
-      // S^T and dP^T of iteration `it` (inputs in stage it % kBwdStages)
-      auto issue_scores = [&](int it) -> bool {
-        const int st = it % kBwdStages;
+      // S^T of iteration `it` whose inputs sit in stage `st`; the caller has made sure St is free
+      auto issue_s = [&](int it, uint32_t st) -> bool {
         if (!mbar_wait(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 121, it)) return false;
         tc_fence_after();
-        const int qs = sub0 + it % n_sub;
-        const uint32_t sf_shift = (QT == 64) ? 2u * (uint32_t)(qs & 1) : 0u;  // which 64 rows of the 128-row scale page
-        for (int pg = 0; pg < kPages; ++pg) tmem_cp_page(tm + C::colSfb + 4 * pg, make_page_desc(smem_u32(s.q_sf[st] + 512 * pg)));
+        // D = 128: which 64 rows of the 128-row scale page (sub-tiles alternate, sub0 is even)
+        const uint32_t sf_shift = (QT == 64) ? 2u * (uint32_t)((it % n_sub) & 1) : 0u;
+#pragma unroll
+        for (int pg = 0; pg < kPages; ++pg) tmem_cp_page(tm + C::colSfb + 4 * pg, d_sfq0 + st * kSf16 + (pg * 512 >> 4));
+        const uint64_t qc = d_qc0 + st * kQc16;
 #pragma unroll
         for (int k = 0; k < D / 64; ++k)
-          mma_nvfp4_ss(tm + C::colSt, make_tile_desc(kc + 32 * k, D / 2), make_tile_desc(smem_u32(s.q_codes[st]) + 32 * k, D / 2), id_s,
-                       tm + C::colSfa + 4 * k, tm + C::colSfb + 4 * k + sf_shift, k > 0);
+          mma_nvfp4_ss(tm + C::colSt, d_kc + 2 * k, qc + 2 * k, id_s, tm + C::colSfa + 4 * k, tm + C::colSfb + 4 * k + sf_shift, k > 0);
         mma_commit(&s.st_full);
-#pragma unroll
-        for (int k = 0; k < D / 32; ++k)
-          mma_f8_ss(tm + C::colDPt, make_tile_desc(v8 + 32 * k, D), make_tile_desc(smem_u32(s.do5[st]) + 32 * k, D), id_dp, k > 0);
-        mma_commit(&s.dp_full);
         return true;
       };
-      if (ok) ok = issue_scores(0);
+      auto issue_dp = [&](uint32_t st) {
+        const uint64_t dd = d_do0 + st * kQ816;
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k) mma_f8_ss(tm + C::colDPt, d_v8 + 2 * k, dd + 2 * k, id_dp, k > 0);
+        mma_commit(&s.dp_full);
+      };
+      // The compute warps run  P(0); { P(it+1), dS(it) } for it = 0, 1, ...  The issuer follows the same
+      // order so that every MMA is issued the moment its operands exist:
+      //   pt_ready(it+1) -> dV(it+1) and S(it+2)   (St is free once P(it+1) has been read out of it)
+      //   ds_ready(it)   -> dP(it+1), dK(it), dQ(it) (dPt is free once dS(it) has been read out of it)
+      auto issue_dv = [&](int it, uint32_t st) {
+        const uint64_t dd = d_do0 + st * kQ816, pt = d_pt0 + (it & 1) * kPt16;
+        const uint32_t acc = it > 0 ? 1u : 0u;
+#pragma unroll
+        for (int k = 0; k < QT / 32; ++k) mma_f8_ss(tm + C::colDV, pt + 2 * k, dd + kRow32D * k, id_dv, k > 0 ? 1u : acc);
+      };
+      auto next_stage = [](uint32_t st) { return (st + 1 == kBwdStages) ? 0u : st + 1; };
+      uint32_t st = 0, st1 = next_stage(0), st2 = next_stage(st1);  // stages of it, it+1, it+2
+      if (ok) ok = issue_s(0, 0);
+      if (ok) issue_dp(0);
+      if (ok) ok = mbar_wait(&s.pt_ready[0], 0, &s.abort_flag, p.status, 122, 0);
+      if (ok) {
+        tc_fence_after();
+        issue_dv(0, 0);
+        if (1 < n_it) ok = issue_s(1, st1);
+      }
       for (int it = 0; ok && it < n_it; ++it) {
-        const int st = it % kBwdStages, buf = it & 1;
-        ok = mbar_wait(&s.pt_ready, it & 1, &s.abort_flag, p.status, 122, it);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < QT / 32; ++k)
-          mma_f8_ss(tm + C::colDV, make_tile_desc(smem_u32(s.pt[buf]) + 32 * k, QT), make_tile_desc(smem_u32(s.do5[st]) + 32 * D * k, D),
-                    id_dv, (it > 0 || k > 0) ? 1u : 0u);
-        ok = mbar_wait(&s.ds_ready, it & 1, &s.abort_flag, p.status, 123, it);
-        if (!ok) break;
-        tc_fence_after();
+        const uint32_t buf = it & 1;
         if (it + 1 < n_it) {
-          ok = issue_scores(it + 1);
+          ok = mbar_wait(&s.pt_ready[buf ^ 1], ((it + 1) >> 1) & 1, &s.abort_flag, p.status, 122, it + 1);
           if (!ok) break;
+          tc_fence_after();
+          issue_dv(it + 1, st1);
+          if (it + 2 < n_it) {
+            ok = issue_s(it + 2, st2);
+            if (!ok) break;
+          }
         }
+        ok = mbar_wait(&s.ds_ready[buf], (it >> 1) & 1, &s.abort_flag, p.status, 123, it);
+        if (!ok) break;
+        tc_fence_after();
+        if (it + 1 < n_it) issue_dp(st1);
+        const uint32_t acc = it > 0 ? 1u : 0u;
+        const uint64_t q8 = d_q80 + st * kQ816, ds = d_ds0 + buf * kPt16;
 #pragma unroll
-        for (int k = 0; k < QT / 32; ++k)
-          mma_f8_ss(tm + C::colDK, make_tile_desc(smem_u32(s.dst[buf]) + 32 * k, QT), make_tile_desc(smem_u32(s.q8[st]) + 32 * D * k, D),
-                    id_dk, (it > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < QT / 32; ++k) mma_f8_ss(tm + C::colDK, ds + 2 * k, q8 + kRow32D * k, id_dk, k > 0 ? 1u : acc);
         if (it > 0) {
           ok = mbar_wait(&s.dq_free, (it - 1) & 1, &s.abort_flag, p.status, 124, it);
           if (!ok) break;
@@ -221,16 +271,20 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
 #pragma unroll
         for (int k = 0; k < 4; ++k) {  // 128 keys, 32 per step
           if (D == 128)  // dQ^T[d, q] = K8^T . dS8^T
-            mma_f8_ss(tm + C::colDQ, make_tile_desc(k8 + 32 * D * k, D), make_tile_desc(smem_u32(s.dst[buf]) + 32 * QT * k, QT), id_dq,
-                      k > 0);
+            mma_f8_ss(tm + C::colDQ, d_k8 + kRow32D * k, ds + kRow32Q * k, id_dq, k > 0);
           else  // dQ[q, d] = dS8 . K8
-            mma_f8_ss(tm + C::colDQ, make_tile_desc(smem_u32(s.dst[buf]) + 32 * QT * k, QT), make_tile_desc(k8 + 32 * D * k, D), id_dq,
-                      k > 0);
+            mma_f8_ss(tm + C::colDQ, ds + kRow32Q * k, d_k8 + kRow32D * k, id_dq, k > 0);
         }
         mma_commit(&s.dq_full);
         mma_commit(&s.in_empty[st]);
+        st = st1;
+        st1 = st2;
+        st2 = next_stage(st2);
       }
       if (ok) mma_commit(&s.acc_done);
+      // every tensor-core operation of this CTA has finished before TMEM is freed
+      mma_commit(&s.mma_drained);
+      mbar_wait_teardown(&s.mma_drained, 0);
     }
   } else if (warp >= 8) {
     // ------------------------------------------------------------------ dQ drain (warps 8-11)
@@ -248,6 +302,9 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         uint32_t v[32];
         tmem_ld32(lane_base + C::colDQ + c0, v);
         tmem_ld_wait(v);
+#ifdef FA4B_EXP_NODRAIN
+        if (__uint_as_float(v[0]) == 123.456f) base[0] = 1.f;  // timing experiment: keep the load, drop the reductions
+#else
         if (D == 128) {
           // lane = d, column = query row: one coalesced 128-byte reduction per column
 #pragma unroll
@@ -258,6 +315,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
             red_add_v4(base + (size_t)r * D + c0 + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
                        __uint_as_float(v[i + 3]));
         }
+#endif
       }
       tc_fence_before();
       mbar_arrive(&s.dq_free);
@@ -270,48 +328,78 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     const uint32_t lane_base = tm + ((uint32_t)((warp & 3) * 32) << 16);
     const int key = kt * 128 + row;
     const float beta = p.scale / 16.0f;
-    const float kg = p.k_global[bhk] * p.scale * kLog2e;
+    if (t < 16) s.c2[t] = (t < G) ? p.k_global[bhk] * p.scale * kLog2e * p.q_global[b * p.Hq + hk * G + t] : 0.f;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
     bool ok = true;
-    for (int it = 0; ok && it < n_it; ++it) {
+    // P8^T of sub-tile `it`: St -> 2^min(s2 + lstat, 8) -> E4M3 -> shared memory (A operand of dV);
+    // the packed bytes also stay in registers for the dS step
+    // this thread's row in the swizzled [key][q] tiles: byte offset of 16-byte chunk c is
+    // row_base + (c ^ swz) (the swizzle XORs address bits 4-6 with the row bits above bit 7)
+    const uint32_t row_base = row * QT;
+    const uint32_t swz = (QT == 128 ? (row & 7u) : ((row >> 1) & 3u)) << 4;
+    auto do_p = [&](int it, uint32_t (&pk)[CW / 4]) -> bool {
       const int st = it % kBwdStages, buf = it & 1;
       const int g = it / n_sub, qs = sub0 + it % n_sub;
-      const int bh = b * p.Hq + hk * G + g;
-      const float c2 = kg * p.q_global[bh];
-      const int q_first = qs * QT + half * CW;   // global query index of this thread's first column
+      const uint64_t c2c2 = pack2(s.c2[g], s.c2[g]);
+      const int q_first = qs * QT + half * CW;     // global query index of this thread's first column
       const bool diag = qs * QT < kt * 128 + 128;  // sub-tile overlaps the key tile: mask needed
       // the row statistics arrive through the async proxy: observe their barrier before reading them
-      ok = __all_sync(0xffffffffu, mbar_wait(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 143, it));
-      if (!ok) break;
-      ok = __all_sync(0xffffffffu, mbar_wait(&s.st_full, it & 1, &s.abort_flag, p.status, 140, it));
-      if (!ok) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 143, it))) return false;
+      // st_full(it) is committed after dV(it-1), dK(it-3) and dQ(it-3): once it has fired, the P buffer this
+      // step overwrites (last read by dV(it-2)) and the dS buffer the next dS step overwrites (dS(it-1)
+      // replaces dS(it-3)) are no longer read by the tensor core
+      if (!__all_sync(0xffffffffu, mbar_wait(&s.st_full, it & 1, &s.abort_flag, p.status, 140, it))) return false;
       tc_fence_after();
-      uint32_t pk[CW / 4];
+      const float* ls = &s.lstat[st][half * CW];
+      uint8_t* dst_row = &s.pt[buf][row_base];
 #pragma unroll
       for (int c0 = 0; c0 < CW; c0 += 32) {
         uint32_t v[32];
         tmem_ld32(lane_base + C::colSt + half * CW + c0, v);
         tmem_ld_wait(v);
-        float pr[32];
+        // 2^(s2 + lstat) = 256 P; no clamp at 2^8: the exponent can exceed 8 only by the rounding of
+        // LSE, and E4M3 rounds 2^8.0x back to 256.  The masked variant is a separate, warp-uniform
+        // path so that the common one carries no compare/select per element.
+        if (diag) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float x = fminf(fmaf(__uint_as_float(v[i]), c2, s.lstat[st][half * CW + c0 + i]), kPLift);
-          pr[i] = ex2_approx_b(x);
-          if (diag && key > q_first + c0 + i) pr[i] = 0.f;
+          for (int i = 0; i < 8; ++i) {
+            const float4 l4 = *reinterpret_cast<const float4*>(ls + c0 + 4 * i);
+            float x0, x1, x2, x3;
+            unpack2(fma2(pack2u(v[4 * i], v[4 * i + 1]), c2c2, pack2(l4.x, l4.y)), x0, x1);
+            unpack2(fma2(pack2u(v[4 * i + 2], v[4 * i + 3]), c2c2, pack2(l4.z, l4.w)), x2, x3);
+            const int q = q_first + c0 + 4 * i;  // keys after the query get no weight
+            const float p0 = (key > q) ? 0.f : ex2_approx_b(x0), p1 = (key > q + 1) ? 0.f : ex2_approx_b(x1);
+            const float p2 = (key > q + 2) ? 0.f : ex2_approx_b(x2), p3 = (key > q + 3) ? 0.f : ex2_approx_b(x3);
+            pk[c0 / 4 + i] = cvt_e4m3x4(p0, p1, p2, p3);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 l4 = *reinterpret_cast<const float4*>(ls + c0 + 4 * i);
+            float x0, x1, x2, x3;
+            unpack2(fma2(pack2u(v[4 * i], v[4 * i + 1]), c2c2, pack2(l4.x, l4.y)), x0, x1);
+            unpack2(fma2(pack2u(v[4 * i + 2], v[4 * i + 3]), c2c2, pack2(l4.z, l4.w)), x2, x3);
+            pk[c0 / 4 + i] = cvt_e4m3x4(ex2_approx_b(x0), ex2_approx_b(x1), ex2_approx_b(x2), ex2_approx_b(x3));
+          }
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) pk[c0 / 4 + i] = cvt_e4m3x4(pr[4 * i], pr[4 * i + 1], pr[4 * i + 2], pr[4 * i + 3]);
-#pragma unroll
         for (int i = 0; i < 2; ++i)
-          *reinterpret_cast<uint4*>(&s.pt[buf][swizzled_offset(row, half * CW + c0 + 16 * i, QT)]) =
+          *reinterpret_cast<uint4*>(dst_row + ((uint32_t)(half * CW + c0 + 16 * i) ^ swz)) =
               make_uint4(pk[c0 / 4 + 4 * i], pk[c0 / 4 + 4 * i + 1], pk[c0 / 4 + 4 * i + 2], pk[c0 / 4 + 4 * i + 3]);
       }
       fence_async_smem();
       tc_fence_before();
-      mbar_arrive(&s.pt_ready);
-
-      ok = __all_sync(0xffffffffu, mbar_wait(&s.dp_full, it & 1, &s.abort_flag, p.status, 141, it));
-      if (!ok) break;
+      mbar_arrive(&s.pt_ready[buf]);
+      return true;
+    };
+    // dS8^T of sub-tile `it`: (dP16 + dstat) * P8 * scale/16 -> E4M3 -> shared memory
+    const uint64_t bb = pack2(beta, beta);
+    auto do_ds = [&](int it, const uint32_t (&pk)[CW / 4]) -> bool {
+      const int st = it % kBwdStages, buf = it & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&s.dp_full, it & 1, &s.abort_flag, p.status, 141, it))) return false;
       tc_fence_after();
+      const float* dsm = &s.dstat[st][half * CW];
+      uint8_t* dst_row = &s.dst[buf][row_base];
 #pragma unroll
       for (int c0 = 0; c0 < CW; c0 += 32) {
         uint32_t v[32];
@@ -322,21 +410,33 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         for (int i = 0; i < 8; ++i) {
           const uint32_t w = pk[c0 / 4 + i];
           const float2 p01 = e4m3x2_to_f32(w & 0xffffu), p23 = e4m3x2_to_f32(w >> 16);
-          const float* ds_ = &s.dstat[st][half * CW + c0 + 4 * i];
-          const float d0 = (__uint_as_float(v[4 * i]) + ds_[0]) * p01.x * beta;
-          const float d1 = (__uint_as_float(v[4 * i + 1]) + ds_[1]) * p01.y * beta;
-          const float d2 = (__uint_as_float(v[4 * i + 2]) + ds_[2]) * p23.x * beta;
-          const float d3 = (__uint_as_float(v[4 * i + 3]) + ds_[3]) * p23.y * beta;
+          const float4 d4 = *reinterpret_cast<const float4*>(dsm + c0 + 4 * i);
+          float d0, d1, d2, d3;
+          unpack2(mul2(mul2(add2(pack2u(v[4 * i], v[4 * i + 1]), pack2(d4.x, d4.y)), pack2(p01.x, p01.y)), bb), d0, d1);
+          unpack2(mul2(mul2(add2(pack2u(v[4 * i + 2], v[4 * i + 3]), pack2(d4.z, d4.w)), pack2(p23.x, p23.y)), bb), d2, d3);
           dk4[i] = cvt_e4m3x4(d0, d1, d2, d3);
         }
 #pragma unroll
         for (int i = 0; i < 2; ++i)
-          *reinterpret_cast<uint4*>(&s.dst[buf][swizzled_offset(row, half * CW + c0 + 16 * i, QT)]) =
+          *reinterpret_cast<uint4*>(dst_row + ((uint32_t)(half * CW + c0 + 16 * i) ^ swz)) =
               make_uint4(dk4[4 * i], dk4[4 * i + 1], dk4[4 * i + 2], dk4[4 * i + 3]);
       }
       fence_async_smem();
       tc_fence_before();
-      mbar_arrive(&s.ds_ready);
+      mbar_arrive(&s.ds_ready[buf]);
+      return true;
+    };
+    // software pipeline, unrolled by two so that the two register sets keep static names:
+    // P(it+1) is computed before dS(it)
+    uint32_t pk_a[CW / 4], pk_b[CW / 4];
+    ok = do_p(0, pk_a);
+    for (int it = 0; ok && it < n_it; it += 2) {
+      if (it + 1 < n_it) ok = do_p(it + 1, pk_b);
+      if (ok) ok = do_ds(it, pk_a);
+      if (ok && it + 1 < n_it) {
+        if (it + 2 < n_it) ok = do_p(it + 2, pk_a);
+        if (ok) ok = do_ds(it + 1, pk_b);
+      }
     }
     // ------------------------------------------------------------------ dK, dV of this key tile
     if (ok) ok = mbar_wait(&s.acc_done, 0, &s.abort_flag, p.status, 142);
@@ -370,6 +470,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
   }
   tc_fence_before();
   __syncthreads();
+  waitprof_flush(&s.abort_flag);
   if (warp == 12) tmem_dealloc(tm, 512);
 }
 
@@ -474,3 +575,14 @@ void fill_bwd_info(fa4b_info* out) {
 }
 
 }  // namespace fa4b
+
+#ifdef FA4B_WAITPROF
+// development aid (not part of the ABI): copy out and clear the per-site wait statistics of this file's kernels
+extern "C" int fa4b_debug_waitprof_bwd(unsigned long long* host_out) {
+  FA4B_CUDA(cudaDeviceSynchronize());
+  FA4B_CUDA(cudaMemcpyFromSymbol(host_out, fa4b::g_waitprof, sizeof(unsigned long long) * 512));
+  static unsigned long long zeros[512] = {};
+  FA4B_CUDA(cudaMemcpyToSymbol(fa4b::g_waitprof, zeros, sizeof(zeros)));
+  return FA4B_OK;
+}
+#endif

@@ -2,15 +2,19 @@
 // softmax in the log2 domain with an integer running maximum, P as E4M3 in
 // TMEM, O += P . V8 as a TS-form FP8 MMA.
 //
-// One CTA per (batch, query head, 128-row query tile), heaviest tiles first.
-// Roles: warps 0-7 softmax (two threads per query row: warps 0-3 take key
-// columns 0-63 of a tile, warps 4-7 columns 64-127), warp 8 TMA producer,
-// warp 9 MMA issuer.  The score accumulator is double buffered so that
-// Q.K^T of tile j+1 runs under the softmax of tile j.
+// One CTA per (batch, query head, pair of adjacent 128-row query tiles), heaviest
+// pairs first.  K/V arrive in 128-key stages and are consumed as 64-key blocks.
+// Roles: warps 0-3 softmax of the first tile, warps 4-7 softmax of the second
+// (one thread per query row, 64 key columns per block, no cross-thread
+// exchange), warp 8 TMA producer, warp 9 MMA issuer.  The two tiles run the
+// chain QK -> softmax -> PV independently, so the softmax of one overlaps the
+// tensor work and the other tile's softmax.
 //
-// TMEM columns (512 allocated): S[2] at 0 / 128, O at 256, P[2] at 384 / 416,
-// Q scale factors at 448, K scale factors [2] at 456 / 464.
+// TMEM columns (512 allocated): S0 0, S1 64, O0 128, O1 256, P0 384, P1 400,
+// Q scale factors 416 / 424, K scale factors (per stage parity) 432 / 440.
+#include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 #include "attn.cuh"
 
@@ -18,20 +22,22 @@ namespace fa4b {
 
 constexpr int kFwdThreads = 320;
 constexpr int kStages = 4;
-constexpr uint32_t kColS = 0, kColO = 256, kColP = 384, kColSfq = 448, kColSfk = 456;
+// forward probabilities: nominal lift 2^5, reference point allowed to lag by 3 binades (P <= 2^8)
+constexpr float kLift = 5.0f, kHeadroom = 3.0f;
+constexpr uint32_t kColS = 0, kColO = 128, kColP = 384, kColSfq = 416, kColSfk = 432;
 
 template <int D>
 struct FwdSmem {
-  alignas(1024) uint8_t q_codes[128 * D / 2];
+  alignas(1024) uint8_t q_codes[2][128 * D / 2];
   alignas(1024) uint8_t k_codes[kStages][128 * D / 2];
   alignas(1024) uint8_t v[kStages][128 * D];
-  alignas(16) uint8_t q_sf[(D / 64) * 512];
+  alignas(16) uint8_t q_sf[2][(D / 64) * 512];
   alignas(16) uint8_t k_sf[kStages][(D / 64) * 512];
-  alignas(16) float xchg[2][2][128];
-  alignas(16) float lsum_x[2][128];
-  alignas(8) uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[2], p_ready[2], o_done;
+  alignas(8) uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[2], s_free[2], p_ready[2][2], o_done[2], mma_drained;
   uint32_t tmem_base;
-  volatile uint32_t abort_flag;
+  alignas(8) volatile uint32_t abort_flag;
+  uint32_t pad_;
+  FA4B_PROF_FIELD
 };
 
 struct FwdParams {
@@ -45,15 +51,20 @@ struct FwdParams {
   int64_t o_sb, o_sh, o_ss;
   float* lse;
   uint32_t* status;
+  uint32_t* dbg;  // development aid: progress markers in host-mapped memory (NULL in normal use)
 };
+
+#ifdef FA4B_MARKERS
+#define FA4B_MARK(idx, val) do { if (p.dbg) { reinterpret_cast<volatile uint32_t*>(p.dbg)[idx] = (val); } } while (0)
+#else
+#define FA4B_MARK(idx, val)
+#endif
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-
-__device__ __forceinline__ void named_bar_sync(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 
 template <int D>
 __global__ void __launch_bounds__(kFwdThreads, 1)
@@ -65,14 +76,19 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
   constexpr uint32_t kKvBytes = 128 * D / 2 + kPages * 512 + 128 * D;
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
 
-  // work item: heaviest (last) query tiles first; the query heads of a kv group stay adjacent
+  // work item: heaviest (last) query-tile pairs first; the query heads of a kv group stay adjacent
   const int n_tiles = p.S / 128;
+  const int n_pairs = (n_tiles + 1) / 2;
   const int heads = p.B * p.Hq;
-  const int qt = n_tiles - 1 - (int)(blockIdx.x / heads);
+  const int pi = n_pairs - 1 - (int)(blockIdx.x / heads);
   const int bh = blockIdx.x % heads;
   const int b = bh / p.Hq, h = bh % p.Hq;
   const int bhk = b * p.Hkv + h / (p.Hq / p.Hkv);
-  const int n_kv = qt + 1;
+  // 64-key blocks each tile attends to (tile T sees keys < 128 T + 128); the odd tile may not exist
+  const int nb0 = 2 * (2 * pi) + 2;
+  const int nb1 = (2 * pi + 1 < n_tiles) ? 2 * (2 * pi + 1) + 2 : 0;
+  const int nbmax = nb0 > nb1 ? nb0 : nb1;
+  const int n_stages = (nbmax + 1) / 2;
   {
     // an earlier CTA of this launch gave up: leave at once, as one (the decision is CTA-uniform)
     __shared__ uint32_t skip;
@@ -89,167 +105,317 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.s_full[i], 1);
-      mbar_init(&s.p_ready[i], 256);
+      mbar_init(&s.s_free[i], 128);
+      mbar_init(&s.p_ready[i][0], 128);
+      mbar_init(&s.p_ready[i][1], 128);
+      mbar_init(&s.o_done[i], 1);
     }
-    mbar_init(&s.o_done, 1);
+    mbar_init(&s.mma_drained, 1);
     s.abort_flag = 0;
     fence_barrier_init();
   }
+  waitprof_clear(&s.abort_flag);
   if (warp == 8) tmem_alloc(&s.tmem_base, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = s.tmem_base;
 
+#ifdef FA4B_EXP_NOSYNC
+  if (warp >= 8 && !(warp >= 8 && warp < 12 && 0)) {
+    // timing experiment: producer and issuer (and nothing they would feed) stay idle
+  } else
+#endif
   if (warp == 8) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
       tma_prefetch_desc(&map_q);
       tma_prefetch_desc(&map_k);
       tma_prefetch_desc(&map_v);
-      mbar_expect_tx(&s.q_full, 128 * D / 2 + kPages * 512);
-      tma_load_3d(s.q_codes, &map_q, 0, qt * 128, bh, &s.q_full);
-      bulk_load(s.q_sf, p.q_sf + ((size_t)bh * n_tiles + qt) * kPages * 512, kPages * 512, &s.q_full);
-      for (int j = 0; j < n_kv; ++j) {
+      const int nq = nb1 ? 2 : 1;
+      mbar_expect_tx(&s.q_full, nq * (128 * D / 2 + kPages * 512));
+      for (int i = 0; i < nq; ++i) {
+        const int qt = 2 * pi + i;
+        tma_load_3d(s.q_codes[i], &map_q, 0, qt * 128, bh, &s.q_full);
+        bulk_load(s.q_sf[i], p.q_sf + ((size_t)bh * n_tiles + qt) * kPages * 512, kPages * 512, &s.q_full);
+      }
+      int issued = 0;
+      for (int j = 0; j < n_stages; ++j) {
         const int st = j % kStages;
         if (j >= kStages && !mbar_wait(&s.kv_empty[st], ((j / kStages) - 1) & 1, &s.abort_flag, p.status, 10, j)) break;
         mbar_expect_tx(&s.kv_full[st], kKvBytes);
         tma_load_3d(s.k_codes[st], &map_k, 0, j * 128, bhk, &s.kv_full[st]);
         bulk_load(s.k_sf[st], p.k_sf + ((size_t)bhk * n_tiles + j) * kPages * 512, kPages * 512, &s.kv_full[st]);
         tma_load_3d(s.v[st], &map_v, 0, j * 128, bhk, &s.kv_full[st]);
+        issued = j + 1;
+        FA4B_MARK(3, 10 + j);
       }
+      // no copy of this CTA may still be in flight when its shared memory is given up
+      mbar_wait_teardown(&s.q_full, 0);
+      for (int j = issued > kStages ? issued - kStages : 0; j < issued; ++j)
+        mbar_wait_teardown(&s.kv_full[j % kStages], (j / kStages) & 1);
     }
   } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t id_qk = idesc_fp4(128, 128, 0, 0, 0);
+      constexpr uint32_t id_qk = idesc_fp4(128, 64, 0, 0, 0);
       constexpr uint32_t id_pv = idesc_f8(128, D, 0, 0, 0, 1);  // A = P (TMEM), B = V8 [keys, D] MN-major
+      static_assert((kStages & (kStages - 1)) == 0, "stage index is taken with a mask");
+      FA4B_MARK(0, 1);
       bool ok = mbar_wait(&s.q_full, 0, &s.abort_flag, p.status, 20);
+      FA4B_MARK(0, 2);
       if (ok) {
         tc_fence_after();
-        for (int pg = 0; pg < kPages; ++pg) tmem_cp_page(tm + kColSfq + 4 * pg, make_page_desc(smem_u32(s.q_sf + 512 * pg)));
-      }
-      for (int j = 0; ok && j <= n_kv; ++j) {
-        if (j < n_kv) {
-          const int st = j % kStages, sb = j & 1;
-          ok = mbar_wait(&s.kv_full[st], (j / kStages) & 1, &s.abort_flag, p.status, 21, j);
-          if (!ok) break;
-          tc_fence_after();
+        for (int i = 0; i < (nb1 ? 2 : 1); ++i)
           for (int pg = 0; pg < kPages; ++pg)
-            tmem_cp_page(tm + kColSfk + 8 * sb + 4 * pg, make_page_desc(smem_u32(s.k_sf[st] + 512 * pg)));
+            tmem_cp_page(tm + kColSfq + 8 * i + 4 * pg, make_page_desc(smem_u32(s.q_sf[i] + 512 * pg)));
+      }
+      // Q.K^T of 64-key block jb for tile TI; the block's stage has been waited for and its scale pages
+      // copied.  Descriptors are rebuilt from the shared-memory addresses at every issue: a variant
+      // that added constants to precomputed descriptors faulted at D = 64 (cause not established).
+      auto issue_qk = [&](auto ti_c, int jb) {
+        constexpr int TI = decltype(ti_c)::value;
+        FA4B_PROF_SCOPE(&s.abort_flag, 40);
+        const int st = (jb >> 1) & (kStages - 1), hb = jb & 1, sp = (jb >> 1) & 1;
 #pragma unroll
-          for (int k = 0; k < D / 64; ++k)
-            mma_nvfp4_ss(tm + kColS + 128 * sb, make_tile_desc(smem_u32(s.q_codes) + 32 * k, D / 2),
-                         make_tile_desc(smem_u32(s.k_codes[st]) + 32 * k, D / 2), id_qk, tm + kColSfq + 4 * k,
-                         tm + kColSfk + 8 * sb + 4 * k, k > 0);
-          mma_commit(&s.s_full[sb]);
+        for (int k = 0; k < D / 64; ++k)
+          mma_nvfp4_ss(tm + kColS + 64 * TI, make_tile_desc(smem_u32(s.q_codes[TI]) + 32 * k, D / 2),
+                       make_tile_desc(smem_u32(s.k_codes[st]) + hb * 64 * (D / 2) + 32 * k, D / 2), id_qk, tm + kColSfq + 8 * TI + 4 * k,
+                       tm + kColSfk + 8 * sp + 4 * k + 2 * hb, k > 0);
+        {
+          FA4B_PROF_SCOPE(&s.abort_flag, 42);
+          mma_commit(&s.s_full[TI]);
         }
-        if (j > 0) {
-          const int jj = j - 1, st = jj % kStages, sb = jj & 1;
-          ok = mbar_wait(&s.p_ready[sb], (jj >> 1) & 1, &s.abort_flag, p.status, 22, j);
+      };
+      auto open_stage = [&](int jb) -> bool {  // first block of a stage: wait for the data, copy the K scale pages
+        const int sj = jb >> 1, st = sj & (kStages - 1);
+        if (!mbar_wait(&s.kv_full[st], (sj / kStages) & 1, &s.abort_flag, p.status, 21, jb)) return false;
+        tc_fence_after();
+        for (int pg = 0; pg < kPages; ++pg)
+          tmem_cp_page(tm + kColSfk + 8 * (sj & 1) + 4 * pg, make_page_desc(smem_u32(s.k_sf[st] + 512 * pg)));
+        return true;
+      };
+      auto issue_pv = [&](auto ti_c, int j) {
+        constexpr int TI = decltype(ti_c)::value;
+        FA4B_PROF_SCOPE(&s.abort_flag, 41);
+        const int st = (j >> 1) & (kStages - 1), hb = j & 1;
+#pragma unroll
+        for (int k = 0; k < 2; ++k)
+          mma_f8_ts(tm + kColO + 128 * TI, tm + kColP + 16 * TI + 8 * k, make_tile_desc(smem_u32(s.v[st]) + (hb * 64 + 32 * k) * D, D),
+                    id_pv, (j > 0 || k > 0) ? 1u : 0u);
+        {
+          FA4B_PROF_SCOPE(&s.abort_flag, 43);
+          mma_commit(&s.o_done[TI]);
+        }
+      };
+      using T0 = std::integral_constant<int, 0>;
+      using T1 = std::integral_constant<int, 1>;
+      FA4B_MARK(0, 3);
+      if (ok) ok = open_stage(0);
+      FA4B_MARK(0, 4);
+      if (ok) {
+        issue_qk(T0{}, 0);
+        FA4B_MARK(0, 5);
+        if (nb1) issue_qk(T1{}, 0);
+        FA4B_MARK(0, 6);
+      }
+      for (int j = 0; ok && j < nbmax; ++j) {
+        FA4B_PROF_SCOPE(&s.abort_flag, 45);  // whole block step of the issuer
+        const int jn = j + 1;
+        FA4B_MARK(0, 100 + 10 * j);
+        if (jn < nbmax && (jn & 1) == 0) {
+          ok = open_stage(jn);
+          if (!ok) break;
+        }
+        // next block's scores as soon as this block's have been read out of TMEM
+        if (jn < nb0) {
+          ok = mbar_wait(&s.s_free[0], j & 1, &s.abort_flag, p.status, 23, j);
+          if (!ok) break;
+          {
+            FA4B_PROF_SCOPE(&s.abort_flag, 44);
+            tc_fence_after();
+          }
+          issue_qk(T0{}, jn);
+          FA4B_MARK(0, 101 + 10 * j);
+        }
+        if (jn < nb1) {
+          ok = mbar_wait(&s.s_free[1], j & 1, &s.abort_flag, p.status, 23, j);
           if (!ok) break;
           tc_fence_after();
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_f8_ts(tm + kColO, tm + kColP + 32 * sb + 8 * k, make_tile_desc(smem_u32(s.v[st]) + 32 * D * k, D), id_pv,
-                      (jj > 0 || k > 0) ? 1u : 0u);
-          mma_commit(&s.kv_empty[st]);
-          mma_commit(&s.o_done);
+          issue_qk(T1{}, jn);
+          FA4B_MARK(0, 102 + 10 * j);
         }
+        if (j < nb0) {
+          ok = mbar_wait(&s.p_ready[0][j & 1], (j >> 1) & 1, &s.abort_flag, p.status, 22, j);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(T0{}, j);
+          FA4B_MARK(0, 103 + 10 * j);
+        }
+        if (j < nb1) {
+          ok = mbar_wait(&s.p_ready[1][j & 1], (j >> 1) & 1, &s.abort_flag, p.status, 22, j);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(T1{}, j);
+          FA4B_MARK(0, 104 + 10 * j);
+        }
+        if ((j & 1) == 1 || j == nbmax - 1) mma_commit(&s.kv_empty[(j >> 1) & (kStages - 1)]);
       }
+      // every tensor-core operation of this CTA has finished before TMEM is freed
+      mma_commit(&s.mma_drained);
+      FA4B_MARK(0, 900);
+      mbar_wait_teardown(&s.mma_drained, 0);
+      FA4B_MARK(0, 901);
     }
   } else {
-    // ---------------------------------------------------------------- softmax (warps 0-7)
-    const int half = warp >> 2;                 // which 64 key columns of a tile
+    // ---------------------------------------------------------------- softmax (warps 0-3: tile 0, warps 4-7: tile 1)
+    const int ti = warp >> 2;
+    const int nb = ti ? nb1 : nb0;
+    const int qt = 2 * pi + ti;                 // global query tile
     const int row = (warp & 3) * 32 + lane;     // query row inside the tile = TMEM lane
     const uint32_t lane_base = tm + ((uint32_t)((warp & 3) * 32) << 16);
     const float c2 = p.scale_log2 * p.q_global[bh] * p.k_global[bhk];
-    float mhat = -INFINITY, lsum = 0.f;
-    bool ok = true;
-    // Every softmax thread runs every iteration and meets every named barrier, even after a
-    // wait has given up (ok == false): a thread that left early would strand its partner.
-    for (int j = 0; j < n_kv; ++j) {
-      const int sb = j & 1;
-      if (ok) ok = mbar_wait(&s.s_full[sb], (j >> 1) & 1, &s.abort_flag, p.status, 30, j);
-      ok = __all_sync(0xffffffffu, ok);
-      float x[64];
-      float mx = -INFINITY;
-      if (ok) {
-        tc_fence_after();
+    float mhat = -INFINITY;
+    uint64_t lsum2 = pack2(0.f, 0.f);  // running row sum, as two partial sums
+    const uint64_t c2c2 = pack2(c2, c2);
+    bool ok = nb > 0;
+    for (int j = 0; ok && j < nb; ++j) {
+      FA4B_PROF_SCOPE(&s.abort_flag, 55);  // whole block step of a softmax warp
+      if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 1);
+      ok = __all_sync(0xffffffffu, mbar_wait(&s.s_full[ti], j & 1, &s.abort_flag, p.status, 30, j));
+      if (!ok) break;
+      if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 2);
+      tc_fence_after();
+      uint32_t x[64];  // raw scores (FP32 bit patterns) of this row against the block's 64 keys
+      {
+        FA4B_PROF_SCOPE(&s.abort_flag, 50);
         uint32_t r0[32], r1[32];
-        tmem_ld32(lane_base + kColS + 128 * sb + 64 * half, r0);
-        tmem_ld32(lane_base + kColS + 128 * sb + 64 * half + 32, r1);
+        tmem_ld32(lane_base + kColS + 64 * ti, r0);
+        tmem_ld32(lane_base + kColS + 64 * ti + 32, r1);
         tmem_ld_wait(r0);
         tmem_ld_wait(r1);
-        const bool diag = (j == qt);
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          x[i] = __uint_as_float(r0[i]) * c2;
-          x[32 + i] = __uint_as_float(r1[i]) * c2;
+          x[i] = r0[i];
+          x[32 + i] = r1[i];
         }
-        if (diag) {
-#pragma unroll
-          for (int i = 0; i < 64; ++i)
-            if (64 * half + i > row) x[i] = -INFINITY;
-        }
-#pragma unroll
-        for (int i = 0; i < 64; ++i) mx = fmaxf(mx, x[i]);
       }
-      s.xchg[sb][half][row] = mx;
-      named_bar_sync(1, 256);
-      mx = fmaxf(mx, s.xchg[sb][half ^ 1][row]);
-      if (!ok) continue;
-      const float mnew = fmaxf(mhat, ceilf(mx));
+      tc_fence_before();
+      mbar_arrive(&s.s_free[ti]);  // the next block's Q.K^T may overwrite S now
+      if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 3);
+      // keys of this block that lie after the query row (only in the tile's last two blocks)
+      const int lim = qt * 128 + row - 64 * j;  // columns <= lim are visible
+      const bool diag = j >= 2 * qt;            // warp-uniform
+      // c2 >= 0: the maximum of the scaled scores is the scaled maximum of the raw ones
+      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+      if (diag) {
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) {
+          m0 = fmaxf(m0, (i > lim) ? -INFINITY : __uint_as_float(x[i]));
+          m1 = fmaxf(m1, (i + 1 > lim) ? -INFINITY : __uint_as_float(x[i + 1]));
+          m2 = fmaxf(m2, (i + 2 > lim) ? -INFINITY : __uint_as_float(x[i + 2]));
+          m3 = fmaxf(m3, (i + 3 > lim) ? -INFINITY : __uint_as_float(x[i + 3]));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; i += 8) {  // three-input maximum: 32 instructions for 64 values
+          m0 = max3(m0, __uint_as_float(x[i]), __uint_as_float(x[i + 1]));
+          m1 = max3(m1, __uint_as_float(x[i + 2]), __uint_as_float(x[i + 3]));
+          m2 = max3(m2, __uint_as_float(x[i + 4]), __uint_as_float(x[i + 5]));
+          m3 = max3(m3, __uint_as_float(x[i + 6]), __uint_as_float(x[i + 7]));
+        }
+      }
+      float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      mx = (mx == -INFINITY) ? mx : mx * c2;  // a row can be fully masked in the tile's last block
+      // Lazy reference point: probabilities are formed as 2^(s2 - mhat + kLift) and mhat only moves
+      // when the block maximum exceeds it by more than kHeadroom, so that P stays <= 2^(kLift +
+      // kHeadroom) = 256 < 448.  mhat is an integer, so every such P is the probability of the final
+      // reference point times a power of two and rounds to the same E4M3 neighbour.
+      const float cm = ceilf(mx);
+      const bool moved = cm > mhat + kHeadroom;
+      const float mnew = moved ? cm : mhat;
+      // the running sum moves to the new reference point now; the accumulator follows after the
+      // exponentials, once the previous block's P.V has finished
+      const float f = moved ? ex2_approx(mhat - mnew) : 1.0f;
+      if (__any_sync(0xffffffffu, moved)) lsum2 = mul2(lsum2, pack2(f, f));
+      mhat = mnew;
+      if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 5);
+      // P = 2^(x c2 - mhat + kLift): packed FMA for the exponent, MUFU for the power, packed add for the sum
+      const uint64_t shift2 = pack2(kLift - mhat, kLift - mhat);
+      uint32_t pa[8], pb[8];
+      if (diag) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float e0, e1, e2, e3;
+          unpack2(fma2(pack2u(x[4 * i], x[4 * i + 1]), c2c2, shift2), e0, e1);
+          unpack2(fma2(pack2u(x[4 * i + 2], x[4 * i + 3]), c2c2, shift2), e2, e3);
+          // keys after the query get no weight
+          const float p0 = (4 * i > lim) ? 0.f : ex2_approx(e0), p1 = (4 * i + 1 > lim) ? 0.f : ex2_approx(e1);
+          const float p2 = (4 * i + 2 > lim) ? 0.f : ex2_approx(e2), p3 = (4 * i + 3 > lim) ? 0.f : ex2_approx(e3);
+          lsum2 = add2(lsum2, add2(pack2(p0, p1), pack2(p2, p3)));
+          const uint32_t w = cvt_e4m3x4(p0, p1, p2, p3);
+          if (i < 8) pa[i] = w; else pb[i - 8] = w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float e0, e1, e2, e3;
+          unpack2(fma2(pack2u(x[4 * i], x[4 * i + 1]), c2c2, shift2), e0, e1);
+          unpack2(fma2(pack2u(x[4 * i + 2], x[4 * i + 3]), c2c2, shift2), e2, e3);
+          const float p0 = ex2_approx(e0), p1 = ex2_approx(e1), p2 = ex2_approx(e2), p3 = ex2_approx(e3);
+          lsum2 = add2(lsum2, add2(pack2(p0, p1), pack2(p2, p3)));
+          const uint32_t w = cvt_e4m3x4(p0, p1, p2, p3);
+          if (i < 8) pa[i] = w; else pb[i - 8] = w;
+        }
+      }
+      // P and the accumulator of block j-1 must have been consumed before P is overwritten / O rescaled
+      if (j > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&s.o_done[ti], (j - 1) & 1, &s.abort_flag, p.status, 31, j));
+        if (!ok) break;
+        tc_fence_after();
+      }
       // tcgen05.ld/st are warp-collective: the accumulator rescale is taken by the whole warp
       // as soon as one of its rows has a new maximum (factor 1 for the rows that keep theirs)
-      if (j > 0 && __any_sync(0xffffffffu, mnew > mhat)) {
-        const float f = ex2_approx(mhat - mnew);  // 2^0 = 1 when unchanged
-        lsum *= f;
-        ok = mbar_wait(&s.o_done, (j - 1) & 1, &s.abort_flag, p.status, 31, j);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) continue;
-        tc_fence_after();
+      if (j > 0 && __any_sync(0xffffffffu, moved)) {
+        FA4B_PROF_SCOPE(&s.abort_flag, 54);
 #pragma unroll
-        for (int c0 = 0; c0 < D / 2; c0 += 32) {
+        for (int c0 = 0; c0 < D; c0 += 32) {
           uint32_t r[32];
-          tmem_ld32(lane_base + kColO + (D / 2) * half + c0, r);
+          tmem_ld32(lane_base + kColO + 128 * ti + c0, r);
           tmem_ld_wait(r);
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
-          tmem_st32(lane_base + kColO + (D / 2) * half + c0, r);
+          tmem_st32(lane_base + kColO + 128 * ti + c0, r);
+          tmem_st_wait();  // the store reads its registers asynchronously
         }
       }
-      mhat = mnew;
-      const float shift = kPLift - mhat;
-      uint32_t pa[8], pb[8];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float p0 = ex2_approx(x[4 * i] + shift), p1 = ex2_approx(x[4 * i + 1] + shift);
-        const float p2 = ex2_approx(x[4 * i + 2] + shift), p3 = ex2_approx(x[4 * i + 3] + shift);
-        lsum += (p0 + p1) + (p2 + p3);
-        const uint32_t w = cvt_e4m3x4(p0, p1, p2, p3);
-        if (i < 8) pa[i] = w; else pb[i - 8] = w;
+      {
+        FA4B_PROF_SCOPE(&s.abort_flag, 53);
+        tmem_st8(lane_base + kColP + 16 * ti, pa);
+        tmem_st8(lane_base + kColP + 16 * ti + 8, pb);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&s.p_ready[ti][j & 1]);
       }
-      tmem_st8(lane_base + kColP + 32 * sb + 16 * half, pa);
-      tmem_st8(lane_base + kColP + 32 * sb + 16 * half + 8, pb);
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(&s.p_ready[sb]);
+      if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 7);
+    }
+    float lsum;
+    {
+      float lo, hi;
+      unpack2(lsum2, lo, hi);
+      lsum = lo + hi;
     }
     // ---------------------------------------------------------------- epilogue
-    if (ok) ok = mbar_wait(&s.o_done, (n_kv - 1) & 1, &s.abort_flag, p.status, 32, n_kv);
-    ok = __all_sync(0xffffffffu, ok);
-    s.lsum_x[half][row] = lsum;
-    named_bar_sync(1, 256);
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s.o_done[ti], (nb - 1) & 1, &s.abort_flag, p.status, 32, nb));
+    if ((t & 127) == 0) FA4B_MARK(1 + ti, 800);
     if (ok) {
       tc_fence_after();
-      const float l = lsum + s.lsum_x[half ^ 1][row];
-      const float inv = 0.25f / l;
-      __nv_bfloat16* orow = p.o + (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)(qt * 128 + row) * p.o_ss + (D / 2) * half;
+      const float inv = 0.25f / lsum;
+      __nv_bfloat16* orow = p.o + (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)(qt * 128 + row) * p.o_ss;
 #pragma unroll
-      for (int c0 = 0; c0 < D / 2; c0 += 32) {
+      for (int c0 = 0; c0 < D; c0 += 32) {
         uint32_t r[32];
-        tmem_ld32(lane_base + kColO + (D / 2) * half + c0, r);
+        tmem_ld32(lane_base + kColO + 128 * ti + c0, r);
         tmem_ld_wait(r);
         uint32_t w[16];
 #pragma unroll
@@ -261,12 +427,16 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         for (int i = 0; i < 4; ++i)
           *reinterpret_cast<uint4*>(orow + c0 + 8 * i) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
       }
-      if (half == 0) p.lse[(size_t)bh * p.S + qt * 128 + row] = (mhat - kPLift) * kLn2 + logf(l);
+      p.lse[(size_t)bh * p.S + qt * 128 + row] = (mhat - kLift) * kLn2 + logf(lsum);
+      if ((t & 127) == 0) FA4B_MARK(1 + ti, 801);
     }
   }
   tc_fence_before();
   __syncthreads();
+  waitprof_flush(&s.abort_flag);
+  if (t == 0) FA4B_MARK(4, 1);
   if (warp == 8) tmem_dealloc(tm, 512);
+  if (t == 256) FA4B_MARK(4, 2);
 }
 
 template <int D>
@@ -289,7 +459,10 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   p.o_sb = a.o_strides.batch; p.o_sh = a.o_strides.head; p.o_ss = a.o_strides.seq;
   p.lse = a.lse;
   p.status = reinterpret_cast<uint32_t*>(ws + l.status);
-  FA4B_CUDA(cudaMemsetAsync(p.status, 0, 16, st));
+#ifdef FA4B_MARKERS
+  if (const char* e = getenv("FA4B_DEBUG_PTR")) p.dbg = reinterpret_cast<uint32_t*>(strtoull(e, nullptr, 16));
+#endif
+  FA4B_CUDA(cudaMemsetAsync(p.status, 0, 64, st));
   const int smem = (int)sizeof(FwdSmem<D>) + 1024;
   static std::mutex mu;
   static bool configured[64] = {};
@@ -302,7 +475,7 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
       configured[dev] = true;
     }
   }
-  const unsigned grid = (unsigned)(d.B * d.Hq * (d.S / 128));
+  const unsigned grid = (unsigned)(d.B * d.Hq * ((d.S / 128 + 1) / 2));
   if (a.ev_before) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_before), st));
   attn_fwd_kernel<D><<<grid, kFwdThreads, smem, st>>>(p, mq, mk, mv);
   FA4B_CUDA(cudaGetLastError());
@@ -340,3 +513,14 @@ extern "C" int fa4b_attn_fwd(const fa4b_attn_fwd_args* a, void* stream) {
   FA4B_REQUIRE(a != nullptr, FA4B_BAD_ARG, "args is NULL");
   return launch_attn_fwd(*a, static_cast<cudaStream_t>(stream));
 }
+
+#ifdef FA4B_WAITPROF
+// development aid (not part of the ABI): copy out and clear the per-site wait statistics of this file's kernels
+extern "C" int fa4b_debug_waitprof_fwd(unsigned long long* host_out) {
+  FA4B_CUDA(cudaDeviceSynchronize());
+  FA4B_CUDA(cudaMemcpyFromSymbol(host_out, fa4b::g_waitprof, sizeof(unsigned long long) * 512));
+  static unsigned long long zeros[512] = {};
+  FA4B_CUDA(cudaMemcpyToSymbol(fa4b::g_waitprof, zeros, sizeof(zeros)));
+  return FA4B_OK;
+}
+#endif

@@ -54,7 +54,9 @@ struct GateSmem {
   alignas(8) uint64_t bar;
   alignas(8) uint64_t tma_bar;
   uint32_t tmem_base;
-  volatile uint32_t abort_flag;
+  alignas(8) volatile uint32_t abort_flag;
+  uint32_t pad_;
+  FA4B_PROF_FIELD
 };
 
 // kinds: see fa4b_microgate in the public header; kind 7 = kind 1 with TMA loads
@@ -79,6 +81,7 @@ __global__ void __launch_bounds__(128, 1) microgate_kernel(int kind, int K, cons
     s.abort_flag = 0;
     fence_barrier_init();
   }
+  waitprof_clear(&s.abort_flag);
   if (warp == 0) tmem_alloc(&s.tmem_base, 256);
   tc_fence_before();
   __syncthreads();

@@ -8,9 +8,9 @@
 
 namespace fa4b {
 
-// every device-side wait gives up after this long, records where, and the kernel
-// tears down (TMEM freed) instead of spinning
-constexpr uint64_t kWaitLimitNs = 400ull * 1000 * 1000;
+// every device-side wait gives up after this many SM clock cycles (about 0.4 s at 2 GHz),
+// records where, and the kernel tears down (TMEM freed) instead of spinning
+constexpr long long kWaitLimitCycles = 800ll * 1000 * 1000;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -34,24 +34,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait (wall-clock limit kWaitLimitNs).  `abort_flag` lives in shared memory:
-// once any role has given up, every other wait of the CTA returns false at once so
-// that all roles reach the teardown.  status[0] = 1, status[1] = site, status[2] =
-// block, status[3] = caller's detail word.
+// Bounded wait.  `abort_flag` lives in shared memory: once any role has given up, every
+// other wait of the CTA returns false at once so that all roles reach the teardown.
+// status[0] = 1, status[1] = site, status[2] = block, status[3] = caller's detail word.
+// The cycle counter is only consulted after a burst of polls, so a wait that is about to
+// be satisfied never pays for it.
 static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
-                                            uint32_t where, uint32_t detail) {
-  const uint64_t t0 = global_timer_ns();
+                                                   uint32_t where, uint32_t detail) {
+  const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 16; ++i)
+    for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (global_timer_ns() - t0 > kWaitLimitNs) break;
+    if (clock64() - t0 > kWaitLimitCycles) break;
   }
   *abort_flag = 1u;
   if (status && atomicCAS(status, 0u, 1u) == 0u) {
@@ -61,10 +57,84 @@ static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parit
   }
   return false;
 }
+// Teardown wait: lets a role that has given up (or finished) make sure the asynchronous work it
+// started -- bulk copies into its shared memory, tensor-core operations on its TMEM -- has landed
+// before the CTA frees TMEM and exits.  Bounded (about 50 ms); ignores the abort flag.
+static __device__ __noinline__ bool mbar_wait_teardown(uint64_t* bar, uint32_t parity) {
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - t0 > kWaitLimitCycles / 8) return false;
+  }
+}
+
+#ifdef FA4B_WAITPROF
+// Development aid: cycles spent waiting and number of waits per wait site.  The kernels'
+// shared-memory structs carry `unsigned long long prof[128]` directly behind `abort_flag`
+// (8-byte aligned); one lane per warp accumulates there and the CTA flushes to the global
+// table when it ends, so the measurement does not serialise the GPU on a few addresses.
+static __device__ unsigned long long g_waitprof[512];
+__device__ __forceinline__ unsigned long long* waitprof_base(volatile uint32_t* abort_flag) {
+  return reinterpret_cast<unsigned long long*>(const_cast<uint32_t*>(abort_flag) + 2);
+}
+__device__ __forceinline__ void waitprof_flush(volatile uint32_t* abort_flag) {
+  unsigned long long* pr = waitprof_base(abort_flag);
+  for (int i = threadIdx.x; i < 128; i += blockDim.x)
+    if (pr[i]) atomicAdd(&g_waitprof[(i & 63) + (i >= 64 ? 256 : 0)], pr[i]);
+}
+__device__ __forceinline__ void waitprof_clear(volatile uint32_t* abort_flag) {
+  unsigned long long* pr = waitprof_base(abort_flag);
+  for (int i = threadIdx.x; i < 128; i += blockDim.x) pr[i] = 0ull;
+}
+#define FA4B_PROF_FIELD unsigned long long prof[128];
+// duration of a code section (site ids share the table with the wait sites)
+__device__ __forceinline__ long long prof_now() { return clock64(); }
+__device__ __forceinline__ void prof_add(volatile uint32_t* flag, uint32_t site, long long t0) {
+  if ((threadIdx.x & 31) == 0) {
+    unsigned long long* pr = waitprof_base(flag);
+    atomicAdd(&pr[site & 63], (unsigned long long)(prof_now() - t0));
+    atomicAdd(&pr[64 + (site & 63)], 1ull);
+  }
+}
+struct ProfScope {
+  volatile uint32_t* flag;
+  uint32_t site;
+  long long t0;
+  __device__ __forceinline__ ProfScope(volatile uint32_t* f, uint32_t s) : flag(f), site(s) { t0 = prof_now(); }
+  __device__ __forceinline__ ~ProfScope() { prof_add(flag, site, t0); }
+};
+#define FA4B_PROF_SCOPE(flag, site) ::fa4b::ProfScope prof_scope_##site(flag, site)
+#else
+#define FA4B_PROF_SCOPE(flag, site)
+#define FA4B_PROF_FIELD
+__device__ __forceinline__ void waitprof_flush(volatile uint32_t*) {}
+__device__ __forceinline__ void waitprof_clear(volatile uint32_t*) {}
+#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
                                           uint32_t where, uint32_t detail = 0) {
-  if (mbar_try_wait(bar, parity)) return true;
+#ifdef FA4B_EXP_NOSYNC
+  return true;  // timing experiment only: nothing waits for anything
+#endif
+#ifdef FA4B_WAITPROF
+  const long long t0 = clock64();
+  bool r = false;
+#pragma unroll 1
+  for (int i = 0; i < 32 && !r; ++i) r = mbar_try_wait(bar, parity);
+  if (!r) r = mbar_wait_slow(bar, parity, abort_flag, status, where, detail);
+  if ((threadIdx.x & 31) == 0) {
+    unsigned long long* pr = waitprof_base(abort_flag);
+    atomicAdd(&pr[where & 63], (unsigned long long)(clock64() - t0));
+    atomicAdd(&pr[64 + (where & 63)], 1ull);
+  }
+  return r;
+#else
+#pragma unroll 1
+  for (int i = 0; i < 32; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, status, where, detail);
+#endif
 }
 
 // ---- proxies and fences -----------------------------------------------------------

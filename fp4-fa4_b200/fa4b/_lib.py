@@ -7,9 +7,11 @@ caller gets an exception.  Build with ``make -C fp4-fa4_b200/csrc``.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import pathlib
 
-_LIB_PATH = pathlib.Path(__file__).resolve().parents[1] / "lib" / "libfa4b.so"
+# FA4B_LIBRARY points at an alternative build of the same ABI (e.g. an instrumented one)
+_LIB_PATH = pathlib.Path(os.environ.get("FA4B_LIBRARY") or pathlib.Path(__file__).resolve().parents[1] / "lib" / "libfa4b.so")
 
 STATUS_EXC = {1: ValueError, 2: ValueError, 3: NotImplementedError, 4: RuntimeError, 5: TimeoutError, 6: ValueError}
 
