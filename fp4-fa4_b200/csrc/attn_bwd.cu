@@ -13,6 +13,7 @@
 // computed by eight warps, two threads per key row.
 //
 // Warps: 0-7 compute, 8-11 drain dQ, 12 TMA producer, 13 MMA issuer.
+#include <cstdlib>
 #include <mutex>
 
 #include "attn.cuh"
@@ -70,7 +71,23 @@ struct BwdParams {
   __nv_bfloat16* dv;
   int64_t dv_sb, dv_sh, dv_ss;
   uint32_t* status;
+  uint32_t* dbg;  // development aid: event trace buffer (NULL in normal use)
 };
+
+#ifdef FA4B_SELFCHECK
+// development aid: p.dbg points at host-mapped memory, so the words survive a lost context.
+// word [cta*16 + warp] = last progress code of that warp; word [1024 + cta*16 + warp] = failed check
+#define FA4B_HB(code) do { if (p.dbg && lane == 0) reinterpret_cast<volatile uint32_t*>(p.dbg)[blockIdx.x * 16 + warp] = (uint32_t)(code); } while (0)
+#define FA4B_CONV(site, fail_stmt) do { const unsigned am__ = __activemask(); if (am__ != 0xffffffffu) { if (p.dbg) reinterpret_cast<volatile uint32_t*>(p.dbg)[1024 + blockIdx.x * 16 + warp] = ((uint32_t)(site) << 24) | 0x800000u | (am__ & 0x7fffffu); s.abort_flag = 1u; fail_stmt; } } while (0)
+#else
+#define FA4B_HB(code)
+#define FA4B_CONV(site, fail_stmt)
+#endif
+#ifdef FA4B_TRACE
+#define FA4B_TR(role, ev) do { if (p.dbg && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && tr_n < 500) { reinterpret_cast<unsigned long long*>(p.dbg)[(role) * 512 + tr_n++] = ((unsigned long long)(ev) << 40) | ((unsigned long long)clock64() & 0xffffffffffull); } } while (0)
+#else
+#define FA4B_TR(role, ev)
+#endif
 
 __device__ __forceinline__ float ex2_approx_b(float x) {
   float y;
@@ -98,6 +115,8 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
   extern __shared__ uint8_t raw[];
   BwdSmem<D>& s = *reinterpret_cast<BwdSmem<D>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  int tr_n = 0;
+  (void)tr_n;
 
   const int n_tiles = p.S / 128;
   const int heads_kv = p.B * p.Hkv;
@@ -126,11 +145,11 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     mbar_init(&s.st_full, 1);
     mbar_init(&s.dp_full, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&s.pt_ready[i], 256);
-      mbar_init(&s.ds_ready[i], 256);
+      mbar_init(&s.pt_ready[i], 8);  // one arrival per compute warp
+      mbar_init(&s.ds_ready[i], 8);
     }
     mbar_init(&s.dq_full, 1);
-    mbar_init(&s.dq_free, 128);
+    mbar_init(&s.dq_free, 4);
     mbar_init(&s.acc_done, 1);
     mbar_init(&s.mma_drained, 1);
     s.abort_flag = 0;
@@ -161,6 +180,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         const int st = it % kBwdStages;
         if (it >= kBwdStages && !mbar_wait(&s.in_empty[st], ((it / kBwdStages) - 1) & 1, &s.abort_flag, p.status, 110, it)) break;
         issued = it + 1;
+        FA4B_HB(it * 16 + 9);
         const int g = it / n_sub, qs = sub0 + it % n_sub;
         const int bh = b * p.Hq + hk * G + g;
         const int q0 = qs * QT;
@@ -172,14 +192,21 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         bulk_load(s.lstat[st], p.lstat + (size_t)bh * p.S + q0, QT * 4, &s.in_full[st]);
         bulk_load(s.dstat[st], p.dstat + (size_t)bh * p.S + q0, QT * 4, &s.in_full[st]);
       }
-      // no copy of this CTA may still be in flight when its shared memory is given up
+      // no copy of this CTA may still be in flight when its shared memory is given up, and the
+      // tensor core's arrivals on the stage barriers must have landed too (nobody else waits for
+      // the last ones)
       mbar_wait_teardown(&s.kv_full, 0);
-      for (int it = issued > kBwdStages ? issued - kBwdStages : 0; it < issued; ++it)
+      for (int it = issued > kBwdStages ? issued - kBwdStages : 0; it < issued; ++it) {
         mbar_wait_teardown(&s.in_full[it % kBwdStages], (it / kBwdStages) & 1);
+        if (issued == n_it && !s.abort_flag) mbar_wait_teardown(&s.in_empty[it % kBwdStages], (it / kBwdStages) & 1);
+      }
     }
   } else if (warp == 13) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs this loop so that control flow and descriptors stay warp-uniform; one
+    // elected lane (always the same) issues the tensor-core instructions and their commits.
+    {
+      const bool leader = elect_one();
       constexpr uint32_t id_s = idesc_fp4(128, QT, 0, 0, 0);
       constexpr uint32_t id_dp = idesc_f8(128, QT, 0, 1, 0, 0);   // V8 (E4M3, K-major) x dO5 (E5M2, K-major)
       constexpr uint32_t id_dv = idesc_f8(128, D, 0, 1, 0, 1);    // P8^T (K-major) x dO5 (MN-major)
@@ -196,32 +223,32 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       const uint64_t d_sfq0 = make_page_desc(smem_u32(s.q_sf[0]));
       constexpr uint32_t kQc16 = (QT * D / 2) >> 4, kQ816 = (QT * D) >> 4, kSf16 = (kPages * 512) >> 4, kPt16 = (128 * QT) >> 4;
       constexpr uint32_t kRow32D = (32 * D) >> 4, kRow32Q = (32 * QT) >> 4;
-      bool ok = mbar_wait(&s.kv_full, 0, &s.abort_flag, p.status, 120);
+      bool ok = mbar_wait_warp(&s.kv_full, 0, &s.abort_flag, p.status, 120);
       if (ok) {
         tc_fence_after();
 #pragma unroll
-        for (int pg = 0; pg < kPages; ++pg) tmem_cp_page(tm + C::colSfa + 4 * pg, make_page_desc(smem_u32(s.k_sf + 512 * pg)));
+        for (int pg = 0; pg < kPages; ++pg) if (leader) tmem_cp_page(tm + C::colSfa + 4 * pg, make_page_desc(smem_u32(s.k_sf + 512 * pg)));
       }
       // S^T of iteration `it` whose inputs sit in stage `st`; the caller has made sure St is free
       auto issue_s = [&](int it, uint32_t st) -> bool {
-        if (!mbar_wait(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 121, it)) return false;
+        if (!mbar_wait_warp(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 121, it)) return false;
         tc_fence_after();
         // D = 128: which 64 rows of the 128-row scale page (sub-tiles alternate, sub0 is even)
         const uint32_t sf_shift = (QT == 64) ? 2u * (uint32_t)((it % n_sub) & 1) : 0u;
 #pragma unroll
-        for (int pg = 0; pg < kPages; ++pg) tmem_cp_page(tm + C::colSfb + 4 * pg, d_sfq0 + st * kSf16 + (pg * 512 >> 4));
+        for (int pg = 0; pg < kPages; ++pg) if (leader) tmem_cp_page(tm + C::colSfb + 4 * pg, d_sfq0 + st * kSf16 + (pg * 512 >> 4));
         const uint64_t qc = d_qc0 + st * kQc16;
 #pragma unroll
         for (int k = 0; k < D / 64; ++k)
-          mma_nvfp4_ss(tm + C::colSt, d_kc + 2 * k, qc + 2 * k, id_s, tm + C::colSfa + 4 * k, tm + C::colSfb + 4 * k + sf_shift, k > 0);
-        mma_commit(&s.st_full);
+          if (leader) mma_nvfp4_ss(tm + C::colSt, d_kc + 2 * k, qc + 2 * k, id_s, tm + C::colSfa + 4 * k, tm + C::colSfb + 4 * k + sf_shift, k > 0);
+        if (leader) mma_commit(&s.st_full);
         return true;
       };
       auto issue_dp = [&](uint32_t st) {
         const uint64_t dd = d_do0 + st * kQ816;
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k) mma_f8_ss(tm + C::colDPt, d_v8 + 2 * k, dd + 2 * k, id_dp, k > 0);
-        mma_commit(&s.dp_full);
+        for (int k = 0; k < D / 32; ++k) if (leader) mma_f8_ss(tm + C::colDPt, d_v8 + 2 * k, dd + 2 * k, id_dp, k > 0);
+        if (leader) mma_commit(&s.dp_full);
       };
       // The compute warps run  P(0); { P(it+1), dS(it) } for it = 0, 1, ...  The issuer follows the same
       // order so that every MMA is issued the moment its operands exist:
@@ -231,13 +258,13 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         const uint64_t dd = d_do0 + st * kQ816, pt = d_pt0 + (it & 1) * kPt16;
         const uint32_t acc = it > 0 ? 1u : 0u;
 #pragma unroll
-        for (int k = 0; k < QT / 32; ++k) mma_f8_ss(tm + C::colDV, pt + 2 * k, dd + kRow32D * k, id_dv, k > 0 ? 1u : acc);
+        for (int k = 0; k < QT / 32; ++k) if (leader) mma_f8_ss(tm + C::colDV, pt + 2 * k, dd + kRow32D * k, id_dv, k > 0 ? 1u : acc);
       };
       auto next_stage = [](uint32_t st) { return (st + 1 == kBwdStages) ? 0u : st + 1; };
       uint32_t st = 0, st1 = next_stage(0), st2 = next_stage(st1);  // stages of it, it+1, it+2
       if (ok) ok = issue_s(0, 0);
       if (ok) issue_dp(0);
-      if (ok) ok = mbar_wait(&s.pt_ready[0], 0, &s.abort_flag, p.status, 122, 0);
+      if (ok) ok = mbar_wait_warp(&s.pt_ready[0], 0, &s.abort_flag, p.status, 122, 0);
       if (ok) {
         tc_fence_after();
         issue_dv(0, 0);
@@ -245,46 +272,59 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       }
       for (int it = 0; ok && it < n_it; ++it) {
         const uint32_t buf = it & 1;
+        FA4B_HB(it * 16 + 7);
         if (it + 1 < n_it) {
-          ok = mbar_wait(&s.pt_ready[buf ^ 1], ((it + 1) >> 1) & 1, &s.abort_flag, p.status, 122, it + 1);
+          ok = mbar_wait_warp(&s.pt_ready[buf ^ 1], ((it + 1) >> 1) & 1, &s.abort_flag, p.status, 122, it + 1);
           if (!ok) break;
+          FA4B_TR(2, 100);
           tc_fence_after();
           issue_dv(it + 1, st1);
+          FA4B_TR(2, 101);
           if (it + 2 < n_it) {
             ok = issue_s(it + 2, st2);
             if (!ok) break;
+            FA4B_TR(2, 102);
           }
         }
-        ok = mbar_wait(&s.ds_ready[buf], (it >> 1) & 1, &s.abort_flag, p.status, 123, it);
+        ok = mbar_wait_warp(&s.ds_ready[buf], (it >> 1) & 1, &s.abort_flag, p.status, 123, it);
         if (!ok) break;
+        FA4B_TR(2, 110);
         tc_fence_after();
         if (it + 1 < n_it) issue_dp(st1);
+        FA4B_TR(2, 111);
         const uint32_t acc = it > 0 ? 1u : 0u;
         const uint64_t q8 = d_q80 + st * kQ816, ds = d_ds0 + buf * kPt16;
 #pragma unroll
-        for (int k = 0; k < QT / 32; ++k) mma_f8_ss(tm + C::colDK, ds + 2 * k, q8 + kRow32D * k, id_dk, k > 0 ? 1u : acc);
+        for (int k = 0; k < QT / 32; ++k) if (leader) mma_f8_ss(tm + C::colDK, ds + 2 * k, q8 + kRow32D * k, id_dk, k > 0 ? 1u : acc);
+        FA4B_TR(2, 112);
         if (it > 0) {
-          ok = mbar_wait(&s.dq_free, (it - 1) & 1, &s.abort_flag, p.status, 124, it);
+          ok = mbar_wait_warp(&s.dq_free, (it - 1) & 1, &s.abort_flag, p.status, 124, it);
           if (!ok) break;
           tc_fence_after();
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {  // 128 keys, 32 per step
-          if (D == 128)  // dQ^T[d, q] = K8^T . dS8^T
-            mma_f8_ss(tm + C::colDQ, d_k8 + kRow32D * k, ds + kRow32Q * k, id_dq, k > 0);
-          else  // dQ[q, d] = dS8 . K8
-            mma_f8_ss(tm + C::colDQ, ds + kRow32Q * k, d_k8 + kRow32D * k, id_dq, k > 0);
+          if (D == 128) {  // dQ^T[d, q] = K8^T . dS8^T
+            if (leader) mma_f8_ss(tm + C::colDQ, d_k8 + kRow32D * k, ds + kRow32Q * k, id_dq, k > 0);
+          } else {  // dQ[q, d] = dS8 . K8
+            if (leader) mma_f8_ss(tm + C::colDQ, ds + kRow32Q * k, d_k8 + kRow32D * k, id_dq, k > 0);
+          }
         }
-        mma_commit(&s.dq_full);
-        mma_commit(&s.in_empty[st]);
+        if (leader) mma_commit(&s.dq_full);
+        if (leader) mma_commit(&s.in_empty[st]);
+        FA4B_TR(2, 113);
+        FA4B_HB(it * 16 + 8);
         st = st1;
         st1 = st2;
         st2 = next_stage(st2);
       }
-      if (ok) mma_commit(&s.acc_done);
+      if (ok && leader) mma_commit(&s.acc_done);
       // every tensor-core operation of this CTA has finished before TMEM is freed
-      mma_commit(&s.mma_drained);
-      mbar_wait_teardown(&s.mma_drained, 0);
+      if (leader) mma_commit(&s.mma_drained);
+      FA4B_HB(0xE0);
+      if (leader) mbar_wait_teardown(&s.mma_drained, 0);
+      __syncwarp();
+      FA4B_HB(0xE1);
     }
   } else if (warp >= 8) {
     // ------------------------------------------------------------------ dQ drain (warps 8-11)
@@ -292,7 +332,9 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     const uint32_t lane_base = tm + ((uint32_t)(w4 * 32) << 16);
     const int r = w4 * 32 + lane;  // TMEM lane: d (D = 128) or query row (D = 64)
     for (int it = 0; it < n_it; ++it) {
-      if (!__all_sync(0xffffffffu, mbar_wait(&s.dq_full, it & 1, &s.abort_flag, p.status, 130, it))) break;
+      FA4B_HB(it * 16 + 5);
+      if (!mbar_wait_warp(&s.dq_full, it & 1, &s.abort_flag, p.status, 130, it)) break;
+      FA4B_CONV(3, break);
       tc_fence_after();
       const int g = it / n_sub, qs = sub0 + it % n_sub;
       const int bh = b * p.Hq + hk * G + g;
@@ -308,7 +350,16 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         if (D == 128) {
           // lane = d, column = query row: one coalesced 128-byte reduction per column
 #pragma unroll
-          for (int i = 0; i < 32; ++i) atomicAdd(base + (size_t)(c0 + i) * D + r, __uint_as_float(v[i]));
+          for (int i = 0; i < 32; ++i) {
+#ifdef FA4B_SELFCHECK
+            const size_t idx__ = (size_t)(base - p.dq_accum) + (size_t)(c0 + i) * D + r;
+            if (idx__ >= (size_t)p.B * p.Hq * p.S * D) {
+              if (p.dbg) reinterpret_cast<volatile uint32_t*>(p.dbg)[1024 + blockIdx.x * 16 + warp] = (4u << 24) | (uint32_t)(it & 0xffff);
+              continue;
+            }
+#endif
+            atomicAdd(base + (size_t)(c0 + i) * D + r, __uint_as_float(v[i]));
+          }
         } else {
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
@@ -318,7 +369,8 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
 #endif
       }
       tc_fence_before();
-      mbar_arrive(&s.dq_free);
+      mbar_arrive_warp(&s.dq_free);
+      FA4B_HB(it * 16 + 6);
     }
   } else {
     // ------------------------------------------------------------------ compute (warps 0-7)
@@ -344,11 +396,16 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       const int q_first = qs * QT + half * CW;     // global query index of this thread's first column
       const bool diag = qs * QT < kt * 128 + 128;  // sub-tile overlaps the key tile: mask needed
       // the row statistics arrive through the async proxy: observe their barrier before reading them
-      if (!__all_sync(0xffffffffu, mbar_wait(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 143, it))) return false;
+      if ((warp & 3) == 0) FA4B_TR(half, 10);
+      if (!mbar_wait_warp(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 143, it)) return false;
+      if ((warp & 3) == 0) FA4B_TR(half, 11);
       // st_full(it) is committed after dV(it-1), dK(it-3) and dQ(it-3): once it has fired, the P buffer this
       // step overwrites (last read by dV(it-2)) and the dS buffer the next dS step overwrites (dS(it-1)
       // replaces dS(it-3)) are no longer read by the tensor core
-      if (!__all_sync(0xffffffffu, mbar_wait(&s.st_full, it & 1, &s.abort_flag, p.status, 140, it))) return false;
+      if (!mbar_wait_warp(&s.st_full, it & 1, &s.abort_flag, p.status, 140, it)) return false;
+      if ((warp & 3) == 0) FA4B_TR(half, 3);
+      FA4B_HB(it * 16 + 1);
+      FA4B_CONV(1, return false);
       tc_fence_after();
       const float* ls = &s.lstat[st][half * CW];
       uint8_t* dst_row = &s.pt[buf][row_base];
@@ -357,6 +414,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         uint32_t v[32];
         tmem_ld32(lane_base + C::colSt + half * CW + c0, v);
         tmem_ld_wait(v);
+        if ((warp & 3) == 0) FA4B_TR(half, 12);
         // 2^(s2 + lstat) = 256 P; no clamp at 2^8: the exponent can exceed 8 only by the rounding of
         // LSE, and E4M3 rounds 2^8.0x back to 256.  The masked variant is a separate, warp-uniform
         // path so that the common one carries no compare/select per element.
@@ -387,16 +445,24 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           *reinterpret_cast<uint4*>(dst_row + ((uint32_t)(half * CW + c0 + 16 * i) ^ swz)) =
               make_uint4(pk[c0 / 4 + 4 * i], pk[c0 / 4 + 4 * i + 1], pk[c0 / 4 + 4 * i + 2], pk[c0 / 4 + 4 * i + 3]);
       }
+      if ((warp & 3) == 0) FA4B_TR(half, 13);
       fence_async_smem();
+      if ((warp & 3) == 0) FA4B_TR(half, 14);
       tc_fence_before();
-      mbar_arrive(&s.pt_ready[buf]);
+      mbar_arrive_warp(&s.pt_ready[buf]);
+      FA4B_HB(it * 16 + 2);
+      if ((warp & 3) == 0) FA4B_TR(half, 1);
       return true;
     };
     // dS8^T of sub-tile `it`: (dP16 + dstat) * P8 * scale/16 -> E4M3 -> shared memory
     const uint64_t bb = pack2(beta, beta);
     auto do_ds = [&](int it, const uint32_t (&pk)[CW / 4]) -> bool {
       const int st = it % kBwdStages, buf = it & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(&s.dp_full, it & 1, &s.abort_flag, p.status, 141, it))) return false;
+      if ((warp & 3) == 0) FA4B_TR(half, 20);
+      if (!mbar_wait_warp(&s.dp_full, it & 1, &s.abort_flag, p.status, 141, it)) return false;
+      if ((warp & 3) == 0) FA4B_TR(half, 4);
+      FA4B_HB(it * 16 + 3);
+      FA4B_CONV(2, return false);
       tc_fence_after();
       const float* dsm = &s.dstat[st][half * CW];
       uint8_t* dst_row = &s.dst[buf][row_base];
@@ -405,6 +471,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         uint32_t v[32];
         tmem_ld32(lane_base + C::colDPt + half * CW + c0, v);
         tmem_ld_wait(v);
+        if ((warp & 3) == 0) FA4B_TR(half, 22);
         uint32_t dk4[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -421,9 +488,13 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           *reinterpret_cast<uint4*>(dst_row + ((uint32_t)(half * CW + c0 + 16 * i) ^ swz)) =
               make_uint4(dk4[4 * i], dk4[4 * i + 1], dk4[4 * i + 2], dk4[4 * i + 3]);
       }
+      if ((warp & 3) == 0) FA4B_TR(half, 23);
       fence_async_smem();
+      if ((warp & 3) == 0) FA4B_TR(half, 24);
       tc_fence_before();
-      mbar_arrive(&s.ds_ready[buf]);
+      mbar_arrive_warp(&s.ds_ready[buf]);
+      FA4B_HB(it * 16 + 4);
+      if ((warp & 3) == 0) FA4B_TR(half, 2);
       return true;
     };
     // software pipeline, unrolled by two so that the two register sets keep static names:
@@ -439,8 +510,9 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       }
     }
     // ------------------------------------------------------------------ dK, dV of this key tile
-    if (ok) ok = mbar_wait(&s.acc_done, 0, &s.abort_flag, p.status, 142);
-    ok = __all_sync(0xffffffffu, ok);
+    FA4B_HB(0xA0);
+    if (ok) ok = mbar_wait_warp(&s.acc_done, 0, &s.abort_flag, p.status, 142);
+    FA4B_HB(0xA1);
     if (ok) {
       tc_fence_after();
       constexpr float inv = 1.0f / 1024.0f;
@@ -468,10 +540,12 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       }
     }
   }
+  FA4B_HB(0xF0);
   tc_fence_before();
   __syncthreads();
   waitprof_flush(&s.abort_flag);
   if (warp == 12) tmem_dealloc(tm, 512);
+  FA4B_HB(0xF1);
 }
 
 // dQ = bf16(accumulator / 1024) through the caller's strides
@@ -522,6 +596,9 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   p.dk = static_cast<__nv_bfloat16*>(a.dk); p.dk_sb = a.dk_strides.batch; p.dk_sh = a.dk_strides.head; p.dk_ss = a.dk_strides.seq;
   p.dv = static_cast<__nv_bfloat16*>(a.dv); p.dv_sb = a.dv_strides.batch; p.dv_sh = a.dv_strides.head; p.dv_ss = a.dv_strides.seq;
   p.status = reinterpret_cast<uint32_t*>(ws + l.status);
+#if defined(FA4B_TRACE) || defined(FA4B_SELFCHECK)
+  if (const char* e = getenv("FA4B_DEBUG_PTR")) p.dbg = reinterpret_cast<uint32_t*>(strtoull(e, nullptr, 16));
+#endif
   FA4B_CUDA(cudaMemsetAsync(p.status, 0, 16, st));
   FA4B_CUDA(cudaMemsetAsync(p.dq_accum, 0, nq * S * D * sizeof(float), st));
   const int smem = (int)sizeof(BwdSmem<D>) + 1024;

@@ -54,6 +54,11 @@ struct FwdParams {
   uint32_t* dbg;  // development aid: progress markers in host-mapped memory (NULL in normal use)
 };
 
+#ifdef FA4B_TRACE
+#define FA4B_TR(role, ev) do { if (p.dbg && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && tr_n < 500) { reinterpret_cast<unsigned long long*>(p.dbg)[(role) * 512 + tr_n++] = ((unsigned long long)(ev) << 40) | ((unsigned long long)clock64() & 0xffffffffffull); } } while (0)
+#else
+#define FA4B_TR(role, ev)
+#endif
 #ifdef FA4B_MARKERS
 #define FA4B_MARK(idx, val) do { if (p.dbg) { reinterpret_cast<volatile uint32_t*>(p.dbg)[idx] = (val); } } while (0)
 #else
@@ -75,6 +80,8 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
   constexpr int kPages = D / 64;
   constexpr uint32_t kKvBytes = 128 * D / 2 + kPages * 512 + 128 * D;
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  int tr_n = 0;
+  (void)tr_n;
 
   // work item: heaviest (last) query-tile pairs first; the query heads of a kv group stay adjacent
   const int n_tiles = p.S / 128;
@@ -105,9 +112,9 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.s_full[i], 1);
-      mbar_init(&s.s_free[i], 128);
-      mbar_init(&s.p_ready[i][0], 128);
-      mbar_init(&s.p_ready[i][1], 128);
+      mbar_init(&s.s_free[i], 4);   // one arrival per softmax warp
+      mbar_init(&s.p_ready[i][0], 4);
+      mbar_init(&s.p_ready[i][1], 4);
       mbar_init(&s.o_done[i], 1);
     }
     mbar_init(&s.mma_drained, 1);
@@ -150,25 +157,32 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         issued = j + 1;
         FA4B_MARK(3, 10 + j);
       }
-      // no copy of this CTA may still be in flight when its shared memory is given up
+      // no copy of this CTA may still be in flight when its shared memory is given up, and the
+      // tensor core's arrivals on the stage barriers must have landed too (nobody else waits for
+      // the last ones)
       mbar_wait_teardown(&s.q_full, 0);
-      for (int j = issued > kStages ? issued - kStages : 0; j < issued; ++j)
+      for (int j = issued > kStages ? issued - kStages : 0; j < issued; ++j) {
         mbar_wait_teardown(&s.kv_full[j % kStages], (j / kStages) & 1);
+        if (issued == n_stages && !s.abort_flag) mbar_wait_teardown(&s.kv_empty[j % kStages], (j / kStages) & 1);
+      }
     }
   } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The whole warp runs this loop so that control flow and descriptors stay warp-uniform; one
+    // elected lane (always the same) issues the tensor-core instructions and their commits.
+    {
+      const bool leader = elect_one();
       constexpr uint32_t id_qk = idesc_fp4(128, 64, 0, 0, 0);
       constexpr uint32_t id_pv = idesc_f8(128, D, 0, 0, 0, 1);  // A = P (TMEM), B = V8 [keys, D] MN-major
       static_assert((kStages & (kStages - 1)) == 0, "stage index is taken with a mask");
       FA4B_MARK(0, 1);
-      bool ok = mbar_wait(&s.q_full, 0, &s.abort_flag, p.status, 20);
+      bool ok = mbar_wait_warp(&s.q_full, 0, &s.abort_flag, p.status, 20);
       FA4B_MARK(0, 2);
       if (ok) {
         tc_fence_after();
         for (int i = 0; i < (nb1 ? 2 : 1); ++i)
           for (int pg = 0; pg < kPages; ++pg)
-            tmem_cp_page(tm + kColSfq + 8 * i + 4 * pg, make_page_desc(smem_u32(s.q_sf[i] + 512 * pg)));
+            if (leader) tmem_cp_page(tm + kColSfq + 8 * i + 4 * pg, make_page_desc(smem_u32(s.q_sf[i] + 512 * pg)));
       }
       // Q.K^T of 64-key block jb for tile TI; the block's stage has been waited for and its scale pages
       // copied.  Descriptors are rebuilt from the shared-memory addresses at every issue: a variant
@@ -179,20 +193,20 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         const int st = (jb >> 1) & (kStages - 1), hb = jb & 1, sp = (jb >> 1) & 1;
 #pragma unroll
         for (int k = 0; k < D / 64; ++k)
-          mma_nvfp4_ss(tm + kColS + 64 * TI, make_tile_desc(smem_u32(s.q_codes[TI]) + 32 * k, D / 2),
+          if (leader) mma_nvfp4_ss(tm + kColS + 64 * TI, make_tile_desc(smem_u32(s.q_codes[TI]) + 32 * k, D / 2),
                        make_tile_desc(smem_u32(s.k_codes[st]) + hb * 64 * (D / 2) + 32 * k, D / 2), id_qk, tm + kColSfq + 8 * TI + 4 * k,
                        tm + kColSfk + 8 * sp + 4 * k + 2 * hb, k > 0);
         {
           FA4B_PROF_SCOPE(&s.abort_flag, 42);
-          mma_commit(&s.s_full[TI]);
+          if (leader) mma_commit(&s.s_full[TI]);
         }
       };
       auto open_stage = [&](int jb) -> bool {  // first block of a stage: wait for the data, copy the K scale pages
         const int sj = jb >> 1, st = sj & (kStages - 1);
-        if (!mbar_wait(&s.kv_full[st], (sj / kStages) & 1, &s.abort_flag, p.status, 21, jb)) return false;
+        if (!mbar_wait_warp(&s.kv_full[st], (sj / kStages) & 1, &s.abort_flag, p.status, 21, jb)) return false;
         tc_fence_after();
         for (int pg = 0; pg < kPages; ++pg)
-          tmem_cp_page(tm + kColSfk + 8 * (sj & 1) + 4 * pg, make_page_desc(smem_u32(s.k_sf[st] + 512 * pg)));
+          if (leader) tmem_cp_page(tm + kColSfk + 8 * (sj & 1) + 4 * pg, make_page_desc(smem_u32(s.k_sf[st] + 512 * pg)));
         return true;
       };
       auto issue_pv = [&](auto ti_c, int j) {
@@ -201,11 +215,11 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         const int st = (j >> 1) & (kStages - 1), hb = j & 1;
 #pragma unroll
         for (int k = 0; k < 2; ++k)
-          mma_f8_ts(tm + kColO + 128 * TI, tm + kColP + 16 * TI + 8 * k, make_tile_desc(smem_u32(s.v[st]) + (hb * 64 + 32 * k) * D, D),
+          if (leader) mma_f8_ts(tm + kColO + 128 * TI, tm + kColP + 16 * TI + 8 * k, make_tile_desc(smem_u32(s.v[st]) + (hb * 64 + 32 * k) * D, D),
                     id_pv, (j > 0 || k > 0) ? 1u : 0u);
         {
           FA4B_PROF_SCOPE(&s.abort_flag, 43);
-          mma_commit(&s.o_done[TI]);
+          if (leader) mma_commit(&s.o_done[TI]);
         }
       };
       using T0 = std::integral_constant<int, 0>;
@@ -223,48 +237,56 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         FA4B_PROF_SCOPE(&s.abort_flag, 45);  // whole block step of the issuer
         const int jn = j + 1;
         FA4B_MARK(0, 100 + 10 * j);
+        FA4B_TR(2, 140);
         if (jn < nbmax && (jn & 1) == 0) {
           ok = open_stage(jn);
           if (!ok) break;
+          FA4B_TR(2, 141);
         }
         // next block's scores as soon as this block's have been read out of TMEM
         if (jn < nb0) {
-          ok = mbar_wait(&s.s_free[0], j & 1, &s.abort_flag, p.status, 23, j);
+          ok = mbar_wait_warp(&s.s_free[0], j & 1, &s.abort_flag, p.status, 23, j);
           if (!ok) break;
-          {
-            FA4B_PROF_SCOPE(&s.abort_flag, 44);
-            tc_fence_after();
-          }
+          FA4B_TR(2, 100 + 0);
+          tc_fence_after();
           issue_qk(T0{}, jn);
+          FA4B_TR(2, 110 + 0);
           FA4B_MARK(0, 101 + 10 * j);
         }
         if (jn < nb1) {
-          ok = mbar_wait(&s.s_free[1], j & 1, &s.abort_flag, p.status, 23, j);
+          ok = mbar_wait_warp(&s.s_free[1], j & 1, &s.abort_flag, p.status, 23, j);
           if (!ok) break;
+          FA4B_TR(2, 100 + 1);
           tc_fence_after();
           issue_qk(T1{}, jn);
+          FA4B_TR(2, 110 + 1);
           FA4B_MARK(0, 102 + 10 * j);
         }
         if (j < nb0) {
-          ok = mbar_wait(&s.p_ready[0][j & 1], (j >> 1) & 1, &s.abort_flag, p.status, 22, j);
+          ok = mbar_wait_warp(&s.p_ready[0][j & 1], (j >> 1) & 1, &s.abort_flag, p.status, 22, j);
           if (!ok) break;
+          FA4B_TR(2, 120 + 0);
           tc_fence_after();
           issue_pv(T0{}, j);
+          FA4B_TR(2, 130 + 0);
           FA4B_MARK(0, 103 + 10 * j);
         }
         if (j < nb1) {
-          ok = mbar_wait(&s.p_ready[1][j & 1], (j >> 1) & 1, &s.abort_flag, p.status, 22, j);
+          ok = mbar_wait_warp(&s.p_ready[1][j & 1], (j >> 1) & 1, &s.abort_flag, p.status, 22, j);
           if (!ok) break;
+          FA4B_TR(2, 120 + 1);
           tc_fence_after();
           issue_pv(T1{}, j);
+          FA4B_TR(2, 130 + 1);
           FA4B_MARK(0, 104 + 10 * j);
         }
-        if ((j & 1) == 1 || j == nbmax - 1) mma_commit(&s.kv_empty[(j >> 1) & (kStages - 1)]);
+        if (leader && ((j & 1) == 1 || j == nbmax - 1)) mma_commit(&s.kv_empty[(j >> 1) & (kStages - 1)]);
       }
       // every tensor-core operation of this CTA has finished before TMEM is freed
-      mma_commit(&s.mma_drained);
+      if (leader) mma_commit(&s.mma_drained);
       FA4B_MARK(0, 900);
-      mbar_wait_teardown(&s.mma_drained, 0);
+      if (leader) mbar_wait_teardown(&s.mma_drained, 0);
+      __syncwarp();
       FA4B_MARK(0, 901);
     }
   } else {
@@ -282,7 +304,7 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
     for (int j = 0; ok && j < nb; ++j) {
       FA4B_PROF_SCOPE(&s.abort_flag, 55);  // whole block step of a softmax warp
       if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 1);
-      ok = __all_sync(0xffffffffu, mbar_wait(&s.s_full[ti], j & 1, &s.abort_flag, p.status, 30, j));
+      ok = mbar_wait_warp(&s.s_full[ti], j & 1, &s.abort_flag, p.status, 30, j);
       if (!ok) break;
       if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 2);
       tc_fence_after();
@@ -301,7 +323,8 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         }
       }
       tc_fence_before();
-      mbar_arrive(&s.s_free[ti]);  // the next block's Q.K^T may overwrite S now
+      mbar_arrive_warp(&s.s_free[ti]);  // the next block's Q.K^T may overwrite S now
+      if ((warp & 3) == 0) FA4B_TR(ti, 2);
       if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 3);
       // keys of this block that lie after the query row (only in the tile's last two blocks)
       const int lim = qt * 128 + row - 64 * j;  // columns <= lim are visible
@@ -368,14 +391,16 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
           if (i < 8) pa[i] = w; else pb[i - 8] = w;
         }
       }
+      if ((warp & 3) == 0) FA4B_TR(ti, 3);
       // P and the accumulator of block j-1 must have been consumed before P is overwritten / O rescaled
       if (j > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&s.o_done[ti], (j - 1) & 1, &s.abort_flag, p.status, 31, j));
+        ok = mbar_wait_warp(&s.o_done[ti], (j - 1) & 1, &s.abort_flag, p.status, 31, j);
         if (!ok) break;
         tc_fence_after();
       }
       // tcgen05.ld/st are warp-collective: the accumulator rescale is taken by the whole warp
       // as soon as one of its rows has a new maximum (factor 1 for the rows that keep theirs)
+      if ((warp & 3) == 0) FA4B_TR(ti, 4);
       if (j > 0 && __any_sync(0xffffffffu, moved)) {
         FA4B_PROF_SCOPE(&s.abort_flag, 54);
 #pragma unroll
@@ -395,8 +420,9 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         tmem_st8(lane_base + kColP + 16 * ti + 8, pb);
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(&s.p_ready[ti][j & 1]);
+        mbar_arrive_warp(&s.p_ready[ti][j & 1]);
       }
+      if ((warp & 3) == 0) FA4B_TR(ti, 5);
       if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 7);
     }
     float lsum;
@@ -406,7 +432,7 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       lsum = lo + hi;
     }
     // ---------------------------------------------------------------- epilogue
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s.o_done[ti], (nb - 1) & 1, &s.abort_flag, p.status, 32, nb));
+    if (ok) ok = mbar_wait_warp(&s.o_done[ti], (nb - 1) & 1, &s.abort_flag, p.status, 32, nb);
     if ((t & 127) == 0) FA4B_MARK(1 + ti, 800);
     if (ok) {
       tc_fence_after();
@@ -459,7 +485,7 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   p.o_sb = a.o_strides.batch; p.o_sh = a.o_strides.head; p.o_ss = a.o_strides.seq;
   p.lse = a.lse;
   p.status = reinterpret_cast<uint32_t*>(ws + l.status);
-#ifdef FA4B_MARKERS
+#if defined(FA4B_MARKERS) || defined(FA4B_TRACE)
   if (const char* e = getenv("FA4B_DEBUG_PTR")) p.dbg = reinterpret_cast<uint32_t*>(strtoull(e, nullptr, 16));
 #endif
   FA4B_CUDA(cudaMemsetAsync(p.status, 0, 64, st));

@@ -25,13 +25,23 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+// FA4B_WAIT_SPIN (build-time experiment switch): poll with the non-blocking test_wait instead of
+// try_wait, whose failed attempts may park the thread for an implementation-defined time.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
+#ifdef FA4B_WAIT_SPIN
+  asm volatile(
+      "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+#else
   asm volatile(
       "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
+#endif
   return ok != 0;
 }
 // Bounded wait.  `abort_flag` lives in shared memory: once any role has given up, every
@@ -135,6 +145,57 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, status, where, detail);
 #endif
+}
+
+// Whole-warp forms.  Every lane runs the same loop on a warp-wide vote, so the warp is still
+// converged when the wait returns: the warp-collective tcgen05.ld/st that follow fault when lanes
+// arrive separately (a version that put the polling loop under `if (lane == 0)`, and one whose
+// lanes left their own polling loops at different iterations, both left lanes on paths of their
+// own).  All 32 lanes poll: measured inside the running kernels that costs less than one
+// predicated poll plus a broadcast (about 115 against 155 cycles; 16 and 28 on an idle SM).
+__device__ __forceinline__ bool mbar_try_wait_uniform(uint64_t* bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, mbar_try_wait(bar, parity));
+}
+static __device__ __noinline__ bool mbar_wait_warp_slow(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
+                                                        uint32_t where, uint32_t detail) {
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait_uniform(bar, parity)) return true;
+    // lane 0 decides for the warp: 1 = another role gave up, 2 = out of time
+    uint32_t stop = *abort_flag ? 1u : (clock64() - t0 > kWaitLimitCycles ? 2u : 0u);  // branch-free on every lane
+    stop = __shfl_sync(0xffffffffu, stop, 0);
+    if (stop == 1u) return false;
+    if (stop == 2u) break;
+  }
+  if ((threadIdx.x & 31) == 0) {
+    *abort_flag = 1u;
+    if (status && atomicCAS(status, 0u, 1u) == 0u) {
+      status[1] = where;
+      status[2] = blockIdx.x;
+      status[3] = detail;
+    }
+  }
+  __syncwarp();
+  return false;
+}
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
+                                               uint32_t where, uint32_t detail = 0) {
+#ifdef FA4B_EXP_NOSYNC
+  return true;
+#endif
+#pragma unroll 1
+  for (int i = 0; i < 32; ++i)
+    if (mbar_try_wait_uniform(bar, parity)) return true;
+  return mbar_wait_warp_slow(bar, parity, abort_flag, status, where, detail);
+}
+// every lane must have issued its own fences before the call; the barrier counts one arrival per warp
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  asm volatile("{ .reg .pred q; setp.eq.u32 q, %1, 0; @q mbarrier.arrive.shared::cta.b64 _, [%0]; }" ::"r"(smem_u32(bar)),
+               "r"(threadIdx.x & 31u)
+               : "memory");
 }
 
 // ---- proxies and fences -----------------------------------------------------------
@@ -250,6 +311,13 @@ __device__ __host__ constexpr uint32_t idesc_f8(uint32_t M, uint32_t N, uint32_t
 // E2M1 operands (format code 1), both K-major, K = 64 per instruction.
 __device__ __host__ constexpr uint32_t idesc_fp4(uint32_t M, uint32_t N, uint32_t e8m0_scales, uint32_t a_sf_id, uint32_t b_sf_id) {
   return (b_sf_id << 4) | (1u << 7) | (1u << 10) | ((N >> 3) << 17) | (e8m0_scales << 23) | ((M >> 4) << 24) | (a_sf_id << 29);
+}
+
+// one lane of a fully converged warp; the same lane every time
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{ .reg .pred p; elect.sync _|p, 0xffffffff; selp.u32 %0, 1, 0, p; }" : "=r"(pred));
+  return pred != 0;
 }
 
 // ---- MMA issue (one thread) --------------------------------------------------------------
