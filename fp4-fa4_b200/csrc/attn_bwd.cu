@@ -10,9 +10,12 @@
 //   dK  += dS8^T . Q8                   A = dS8^T (smem), B = Q8 MN-major
 //   dQ   = dS8 . K8  (D = 64)  or  dQ^T = K8^T . dS8^T (D = 128), both operands MN-major
 // with P8 = E4M3(2^min(S2 + lstat, 8)) and dS8 = E4M3((dP16 + dstat) * P8 * scale/16)
-// computed by eight warps, two threads per key row.
+// computed by two groups of eight warps (two threads per key row each); group 0 takes the even
+// sub-tiles and group 1 the odd ones, so one group's exponentials overlap the other group's waits.
+// Each group owns one TMEM buffer that first holds S^T and then, once P has been read out of it,
+// dP^T of the same sub-tile.
 //
-// Warps: 0-7 compute, 8-11 drain dQ, 12 TMA producer, 13 MMA issuer.
+// Warps: 0-7 compute group 0, 8-15 compute group 1, 16-19 drain dQ, 20 TMA producer, 21 MMA issuer.
 #include <cstdlib>
 #include <mutex>
 
@@ -20,14 +23,14 @@
 
 namespace fa4b {
 
-constexpr int kBwdThreads = 448;
+constexpr int kBwdThreads = 704;
 constexpr int kBwdStages = 5;
 
 template <int D>
 struct BwdCfg {
   static constexpr int QT = (D == 128) ? 64 : 128;  // query rows per iteration
   static constexpr int kPages = D / 64;
-  static constexpr uint32_t colDK = 0, colDV = D, colSt = 2 * D, colDPt = 2 * D + QT, colDQ = 2 * D + 2 * QT;
+  static constexpr uint32_t colDK = 0, colDV = D, colX = 2 * D, colDQ = 2 * D + 2 * QT;  // colX + g * QT: S^T / dP^T of group g
   static constexpr uint32_t colSfa = colDQ + 64, colSfb = colSfa + 8;
   static_assert(colSfb + 8 <= 512, "TMEM budget");
 };
@@ -48,13 +51,15 @@ struct BwdSmem {
   alignas(16) float lstat[kBwdStages][C::QT];
   alignas(16) float dstat[kBwdStages][C::QT];
   alignas(16) float c2[16];  // per query head of the group: global scales * softmax scale * log2(e)
-  alignas(8) uint64_t kv_full, in_full[kBwdStages], in_empty[kBwdStages], st_full, dp_full, pt_ready[2], ds_ready[2], dq_full, dq_free,
+  alignas(8) uint64_t kv_full, in_full[kBwdStages], in_empty[kBwdStages], st_full[2], dp_full[2], pt_ready[2], ds_ready[2], dq_full, dq_free,
       acc_done, mma_drained;
   uint32_t tmem_base;
   alignas(8) volatile uint32_t abort_flag;
   uint32_t pad_;
   FA4B_PROF_FIELD
 };
+
+static_assert(sizeof(BwdSmem<128>) + 1024 <= 227 * 1024 && sizeof(BwdSmem<64>) + 1024 <= 227 * 1024, "shared memory budget");
 
 struct BwdParams {
   int B, Hq, Hkv, S;
@@ -83,6 +88,16 @@ struct BwdParams {
 #define FA4B_HB(code)
 #define FA4B_CONV(site, fail_stmt)
 #endif
+#ifdef FA4B_ACCT
+// development aid: per-warp cycle accounting by category, flushed once at the end (CTA `FA4B_ACCT_CTA`)
+#define FA4B_ACCT_DECL long long acct[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long acct_t = clock64();
+#define FA4B_ACC(slot) do { const long long now__ = clock64(); acct[slot] += now__ - acct_t; acct_t = now__; } while (0)
+#define FA4B_ACCT_FLUSH(role) do { if (p.dbg && blockIdx.x == 3 && lane == 0) { for (int i__ = 0; i__ < 12; ++i__) reinterpret_cast<unsigned long long*>(p.dbg)[(role) * 16 + i__] = (unsigned long long)acct[i__]; } } while (0)
+#else
+#define FA4B_ACCT_DECL
+#define FA4B_ACC(slot)
+#define FA4B_ACCT_FLUSH(role)
+#endif
 #ifdef FA4B_TRACE
 #define FA4B_TR(role, ev) do { if (p.dbg && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && tr_n < 500) { reinterpret_cast<unsigned long long*>(p.dbg)[(role) * 512 + tr_n++] = ((unsigned long long)(ev) << 40) | ((unsigned long long)clock64() & 0xffffffffffull); } } while (0)
 #else
@@ -90,6 +105,9 @@ struct BwdParams {
 #endif
 
 __device__ __forceinline__ float ex2_approx_b(float x) {
+#ifdef FA4B_EXP_NOEX2
+  return x * 0.001f + 0.5f;  // timing experiment: no MUFU work
+#endif
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
@@ -120,7 +138,10 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
 
   const int n_tiles = p.S / 128;
   const int heads_kv = p.B * p.Hkv;
-  const int kt = blockIdx.x / heads_kv;  // key tile; low tiles (most query tiles) first
+  // key-tile-major order: low key tiles, which see the most query tiles, start first.  (kv-head-major
+  // order, meant to keep the FP32 dQ scratch rows in L2 while their 64 partial sums arrive, was 12 %
+  // slower: the CTAs of one head then reduce into neighbouring rows at the same time.)
+  const int kt = blockIdx.x / heads_kv;
   const int bhk = blockIdx.x % heads_kv;
   const int b = bhk / p.Hkv, hk = bhk % p.Hkv;
   const int G = p.Hq / p.Hkv;
@@ -142,9 +163,9 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       mbar_init(&s.in_full[i], 1);
       mbar_init(&s.in_empty[i], 1);
     }
-    mbar_init(&s.st_full, 1);
-    mbar_init(&s.dp_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 2; ++i) {  // one set per compute group
+      mbar_init(&s.st_full[i], 1);
+      mbar_init(&s.dp_full[i], 1);
       mbar_init(&s.pt_ready[i], 8);  // one arrival per compute warp
       mbar_init(&s.ds_ready[i], 8);
     }
@@ -156,18 +177,19 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     fence_barrier_init();
   }
   waitprof_clear(&s.abort_flag);
-  if (warp == 12) tmem_alloc(&s.tmem_base, 512);
+  if (t < 16) s.c2[t] = (t < G) ? p.k_global[bhk] * p.scale * kLog2e * p.q_global[b * p.Hq + hk * G + t] : 0.f;
+  if (warp == 20) tmem_alloc(&s.tmem_base, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = s.tmem_base;
 
 #ifdef FA4B_EXP_NOSYNC
-  if (warp >= 8 && !(warp >= 8 && warp < 12 && 1)) {
+  if (warp >= 20) {
     // timing experiment: producer and issuer (and nothing they would feed) stay idle
   } else
 #endif
-  if (warp == 12) {
+  if (warp == 20) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
       mbar_expect_tx(&s.kv_full, 128 * D / 2 + kPages * 512 + 2 * 128 * D);
@@ -201,7 +223,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         if (issued == n_it && !s.abort_flag) mbar_wait_teardown(&s.in_empty[it % kBwdStages], (it / kBwdStages) & 1);
       }
     }
-  } else if (warp == 13) {
+  } else if (warp == 21) {
     // ------------------------------------------------------------------ MMA issuer
     // The whole warp runs this loop so that control flow and descriptors stay warp-uniform; one
     // elected lane (always the same) issues the tensor-core instructions and their commits.
@@ -223,101 +245,139 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       const uint64_t d_sfq0 = make_page_desc(smem_u32(s.q_sf[0]));
       constexpr uint32_t kQc16 = (QT * D / 2) >> 4, kQ816 = (QT * D) >> 4, kSf16 = (kPages * 512) >> 4, kPt16 = (128 * QT) >> 4;
       constexpr uint32_t kRow32D = (32 * D) >> 4, kRow32Q = (32 * QT) >> 4;
+      FA4B_ACCT_DECL
       bool ok = mbar_wait_warp(&s.kv_full, 0, &s.abort_flag, p.status, 120);
       if (ok) {
         tc_fence_after();
 #pragma unroll
         for (int pg = 0; pg < kPages; ++pg) if (leader) tmem_cp_page(tm + C::colSfa + 4 * pg, make_page_desc(smem_u32(s.k_sf + 512 * pg)));
       }
-      // S^T of iteration `it` whose inputs sit in stage `st`; the caller has made sure St is free
-      auto issue_s = [&](int it, uint32_t st) -> bool {
+      // S^T of sub-tile `it` (inputs in its stage) into the buffer of the sub-tile's group; the caller
+      // has made sure the buffer is free
+      auto stage_of = [](int it) { return (uint32_t)(it % kBwdStages); };
+      auto issue_s = [&](int it) -> bool {
+        const uint32_t st = stage_of(it), g = it & 1;
         if (!mbar_wait_warp(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 121, it)) return false;
         tc_fence_after();
         // D = 128: which 64 rows of the 128-row scale page (sub-tiles alternate, sub0 is even)
         const uint32_t sf_shift = (QT == 64) ? 2u * (uint32_t)((it % n_sub) & 1) : 0u;
+        if (leader) {
 #pragma unroll
-        for (int pg = 0; pg < kPages; ++pg) if (leader) tmem_cp_page(tm + C::colSfb + 4 * pg, d_sfq0 + st * kSf16 + (pg * 512 >> 4));
-        const uint64_t qc = d_qc0 + st * kQc16;
+          for (int pg = 0; pg < kPages; ++pg) tmem_cp_page(tm + C::colSfb + 4 * pg, d_sfq0 + st * kSf16 + (pg * 512 >> 4));
+          const uint64_t qc = d_qc0 + st * kQc16;
 #pragma unroll
-        for (int k = 0; k < D / 64; ++k)
-          if (leader) mma_nvfp4_ss(tm + C::colSt, d_kc + 2 * k, qc + 2 * k, id_s, tm + C::colSfa + 4 * k, tm + C::colSfb + 4 * k + sf_shift, k > 0);
-        if (leader) mma_commit(&s.st_full);
+          for (int k = 0; k < D / 64; ++k)
+            mma_nvfp4_ss(tm + C::colX + g * QT, d_kc + 2 * k, qc + 2 * k, id_s, tm + C::colSfa + 4 * k, tm + C::colSfb + 4 * k + sf_shift, k > 0);
+          mma_commit(&s.st_full[g]);
+        }
+        __syncwarp();
         return true;
       };
-      auto issue_dp = [&](uint32_t st) {
-        const uint64_t dd = d_do0 + st * kQ816;
-#pragma unroll
-        for (int k = 0; k < D / 32; ++k) if (leader) mma_f8_ss(tm + C::colDPt, d_v8 + 2 * k, dd + 2 * k, id_dp, k > 0);
-        if (leader) mma_commit(&s.dp_full);
-      };
-      // The compute warps run  P(0); { P(it+1), dS(it) } for it = 0, 1, ...  The issuer follows the same
-      // order so that every MMA is issued the moment its operands exist:
-      //   pt_ready(it+1) -> dV(it+1) and S(it+2)   (St is free once P(it+1) has been read out of it)
-      //   ds_ready(it)   -> dP(it+1), dK(it), dQ(it) (dPt is free once dS(it) has been read out of it)
-      auto issue_dv = [&](int it, uint32_t st) {
-        const uint64_t dd = d_do0 + st * kQ816, pt = d_pt0 + (it & 1) * kPt16;
-        const uint32_t acc = it > 0 ? 1u : 0u;
-#pragma unroll
-        for (int k = 0; k < QT / 32; ++k) if (leader) mma_f8_ss(tm + C::colDV, pt + 2 * k, dd + kRow32D * k, id_dv, k > 0 ? 1u : acc);
-      };
-      auto next_stage = [](uint32_t st) { return (st + 1 == kBwdStages) ? 0u : st + 1; };
-      uint32_t st = 0, st1 = next_stage(0), st2 = next_stage(st1);  // stages of it, it+1, it+2
-      if (ok) ok = issue_s(0, 0);
-      if (ok) issue_dp(0);
-      if (ok) ok = mbar_wait_warp(&s.pt_ready[0], 0, &s.abort_flag, p.status, 122, 0);
-      if (ok) {
+      // The two compute groups alternate sub-tiles and each runs  P(it); dS(it).  Per sub-tile the
+      // issuer answers two events, in sub-tile order:
+      //   pt_ready(it) -> dV(it), then dP(it) into the group's buffer (P has been read out of it)
+      //   ds_ready(it) -> S(it+2) into the same buffer (dS has been read out of it), dK(it), dQ(it)
+      // Each kind is answered in sub-tile order (the dQ drain relies on that order); between the two
+      // kinds the issuer takes whichever event is there, so neither group waits behind the other.
+      auto pt_phase = [&](int it) -> bool {
+        const uint32_t st = stage_of(it), g = it & 1;
+        FA4B_TR(2, 100);
         tc_fence_after();
-        issue_dv(0, 0);
-        if (1 < n_it) ok = issue_s(1, st1);
-      }
-      for (int it = 0; ok && it < n_it; ++it) {
-        const uint32_t buf = it & 1;
-        FA4B_HB(it * 16 + 7);
-        if (it + 1 < n_it) {
-          ok = mbar_wait_warp(&s.pt_ready[buf ^ 1], ((it + 1) >> 1) & 1, &s.abort_flag, p.status, 122, it + 1);
-          if (!ok) break;
-          FA4B_TR(2, 100);
-          tc_fence_after();
-          issue_dv(it + 1, st1);
-          FA4B_TR(2, 101);
-          if (it + 2 < n_it) {
-            ok = issue_s(it + 2, st2);
-            if (!ok) break;
-            FA4B_TR(2, 102);
-          }
+        if (leader) {
+          const uint64_t dd = d_do0 + st * kQ816, pt = d_pt0 + g * kPt16;
+          const uint32_t acc = it > 0 ? 1u : 0u;
+#pragma unroll
+          for (int k = 0; k < QT / 32; ++k) mma_f8_ss(tm + C::colDV, pt + 2 * k, dd + kRow32D * k, id_dv, k > 0 ? 1u : acc);
+#pragma unroll
+          for (int k = 0; k < D / 32; ++k) mma_f8_ss(tm + C::colX + g * QT, d_v8 + 2 * k, dd + 2 * k, id_dp, k > 0);
+          mma_commit(&s.dp_full[g]);
         }
-        ok = mbar_wait_warp(&s.ds_ready[buf], (it >> 1) & 1, &s.abort_flag, p.status, 123, it);
-        if (!ok) break;
+        __syncwarp();
+        FA4B_TR(2, 101);
+        return true;
+      };
+      auto ds_phase = [&](int it) -> bool {
+        const uint32_t st = stage_of(it), g = it & 1;
         FA4B_TR(2, 110);
         tc_fence_after();
-        if (it + 1 < n_it) issue_dp(st1);
-        FA4B_TR(2, 111);
+        // the group's next scores first: its threads are about to wait for them
+        FA4B_ACC(3);  // ds: fence
+        if (it + 2 < n_it && !issue_s(it + 2)) return false;
+        FA4B_ACC(4);  // ds: S
         const uint32_t acc = it > 0 ? 1u : 0u;
-        const uint64_t q8 = d_q80 + st * kQ816, ds = d_ds0 + buf * kPt16;
+        const uint64_t q8 = d_q80 + st * kQ816, ds = d_ds0 + g * kPt16;
+        if (leader) {
 #pragma unroll
-        for (int k = 0; k < QT / 32; ++k) if (leader) mma_f8_ss(tm + C::colDK, ds + 2 * k, q8 + kRow32D * k, id_dk, k > 0 ? 1u : acc);
+          for (int k = 0; k < QT / 32; ++k) mma_f8_ss(tm + C::colDK, ds + 2 * k, q8 + kRow32D * k, id_dk, k > 0 ? 1u : acc);
+        }
+        __syncwarp();
+        FA4B_ACC(5);  // ds: dK
         FA4B_TR(2, 112);
         if (it > 0) {
-          ok = mbar_wait_warp(&s.dq_free, (it - 1) & 1, &s.abort_flag, p.status, 124, it);
-          if (!ok) break;
+          if (!mbar_wait_warp(&s.dq_free, (it - 1) & 1, &s.abort_flag, p.status, 124, it)) return false;
           tc_fence_after();
         }
+        FA4B_ACC(6);  // ds: dq_free
+        if (leader) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {  // 128 keys, 32 per step
-          if (D == 128) {  // dQ^T[d, q] = K8^T . dS8^T
-            if (leader) mma_f8_ss(tm + C::colDQ, d_k8 + kRow32D * k, ds + kRow32Q * k, id_dq, k > 0);
-          } else {  // dQ[q, d] = dS8 . K8
-            if (leader) mma_f8_ss(tm + C::colDQ, ds + kRow32Q * k, d_k8 + kRow32D * k, id_dq, k > 0);
+          for (int k = 0; k < 4; ++k) {  // 128 keys, 32 per step
+            if (D == 128) {  // dQ^T[d, q] = K8^T . dS8^T
+              mma_f8_ss(tm + C::colDQ, d_k8 + kRow32D * k, ds + kRow32Q * k, id_dq, k > 0);
+            } else {  // dQ[q, d] = dS8 . K8
+              mma_f8_ss(tm + C::colDQ, ds + kRow32Q * k, d_k8 + kRow32D * k, id_dq, k > 0);
+            }
           }
+          mma_commit(&s.dq_full);
+          mma_commit(&s.in_empty[st]);
         }
-        if (leader) mma_commit(&s.dq_full);
-        if (leader) mma_commit(&s.in_empty[st]);
+        __syncwarp();
         FA4B_TR(2, 113);
         FA4B_HB(it * 16 + 8);
-        st = st1;
-        st1 = st2;
-        st2 = next_stage(st2);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      if (ok && 1 < n_it) ok = issue_s(1);
+      // two in-order streams, served as their events arrive
+      int ip = 0, id = 0;  // next sub-tile of the pt stream / of the ds stream
+      long long t_idle = 0;
+      while (ok && id < n_it) {
+        bool served = false;
+        if (ip < n_it && mbar_test_uniform(&s.pt_ready[ip & 1], (ip >> 1) & 1)) {
+          FA4B_HB(ip * 16 + 7);
+          FA4B_ACC(0);  // idle / polling
+          ok = pt_phase(ip);
+          FA4B_ACC(1);  // pt phase: dV, dP
+          ++ip;
+          served = true;
+        }
+        if (ok && id < ip && mbar_test_uniform(&s.ds_ready[id & 1], (id >> 1) & 1)) {
+          FA4B_ACC(0);
+          ok = ds_phase(id);
+          FA4B_ACC(2);  // ds: dQ + commits
+          ++id;
+          served = true;
+        }
+        if (served) {
+          t_idle = 0;
+        } else {  // bounded like every other wait
+          const long long now = clock64();
+          if (t_idle == 0) t_idle = now;
+          uint32_t stop = s.abort_flag ? 1u : (now - t_idle > kWaitLimitCycles ? 2u : 0u);
+          stop = __shfl_sync(0xffffffffu, stop, 0);
+          if (stop == 2u && leader) {
+            s.abort_flag = 1u;
+            if (atomicCAS(p.status, 0u, 1u) == 0u) {
+              p.status[1] = 125;
+              p.status[2] = blockIdx.x;
+              p.status[3] = (uint32_t)(ip * 65536 + id);
+            }
+          }
+          __syncwarp();
+          if (stop) ok = false;
+        }
       }
+      FA4B_ACC(0);
+      FA4B_ACCT_FLUSH(0);
       if (ok && leader) mma_commit(&s.acc_done);
       // every tensor-core operation of this CTA has finished before TMEM is freed
       if (leader) mma_commit(&s.mma_drained);
@@ -326,63 +386,67 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       __syncwarp();
       FA4B_HB(0xE1);
     }
-  } else if (warp >= 8) {
-    // ------------------------------------------------------------------ dQ drain (warps 8-11)
+  } else if (warp >= 16) {
+    // ------------------------------------------------------------------ dQ drain (warps 16-19)
+    // The partial dQ of a sub-tile leaves TMEM for registers and the accumulator is handed back to the
+    // issuer at once; the FP32 reductions into the scratch accumulator then run beside the next
+    // sub-tile's MMAs.  (Staging the tile in shared memory for one bulk reduction was slower: with
+    // one 32 KB reduction in flight per SM the reductions ran at 2.4-2.7 TB/s, against 3.2 TB/s here.)
     const int w4 = warp & 3;
     const uint32_t lane_base = tm + ((uint32_t)(w4 * 32) << 16);
     const int r = w4 * 32 + lane;  // TMEM lane: d (D = 128) or query row (D = 64)
+    FA4B_ACCT_DECL
     for (int it = 0; it < n_it; ++it) {
       FA4B_HB(it * 16 + 5);
       if (!mbar_wait_warp(&s.dq_full, it & 1, &s.abort_flag, p.status, 130, it)) break;
       FA4B_CONV(3, break);
+      FA4B_ACC(0);  // waiting for dQ
       tc_fence_after();
       const int g = it / n_sub, qs = sub0 + it % n_sub;
       const int bh = b * p.Hq + hk * G + g;
       float* base = p.dq_accum + ((size_t)bh * p.S + (size_t)qs * QT) * D;
-#pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(lane_base + C::colDQ + c0, v);
-        tmem_ld_wait(v);
-#ifdef FA4B_EXP_NODRAIN
-        if (__uint_as_float(v[0]) == 123.456f) base[0] = 1.f;  // timing experiment: keep the load, drop the reductions
-#else
-        if (D == 128) {
-          // lane = d, column = query row: one coalesced 128-byte reduction per column
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-#ifdef FA4B_SELFCHECK
-            const size_t idx__ = (size_t)(base - p.dq_accum) + (size_t)(c0 + i) * D + r;
-            if (idx__ >= (size_t)p.B * p.Hq * p.S * D) {
-              if (p.dbg) reinterpret_cast<volatile uint32_t*>(p.dbg)[1024 + blockIdx.x * 16 + warp] = (4u << 24) | (uint32_t)(it & 0xffff);
-              continue;
-            }
-#endif
-            atomicAdd(base + (size_t)(c0 + i) * D + r, __uint_as_float(v[i]));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            red_add_v4(base + (size_t)r * D + c0 + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
-                       __uint_as_float(v[i + 3]));
-        }
-#endif
-      }
+      uint32_t v0[32], v1[32];
+      tmem_ld32(lane_base + C::colDQ, v0);
+      tmem_ld32(lane_base + C::colDQ + 32, v1);
+      tmem_ld_wait(v0);
+      tmem_ld_wait(v1);
       tc_fence_before();
-      mbar_arrive_warp(&s.dq_free);
+      mbar_arrive_warp(&s.dq_free);  // the next dQ may overwrite the accumulator now
+      FA4B_ACC(1);  // load + arrive
+#ifdef FA4B_EXP_NODRAIN
+      if (__uint_as_float(v0[0]) == 123.456f) base[0] = __uint_as_float(v1[0]);  // timing experiment: keep the load, drop the reductions
+#else
+      if (D == 128) {
+        // lane = d, register i = query row: one coalesced 128-byte reduction per row
+#pragma unroll
+        for (int i = 0; i < 32; ++i) atomicAdd(base + (size_t)i * D + r, __uint_as_float(v0[i]));
+#pragma unroll
+        for (int i = 0; i < 32; ++i) atomicAdd(base + (size_t)(32 + i) * D + r, __uint_as_float(v1[i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          red_add_v4(base + (size_t)r * D + i, __uint_as_float(v0[i]), __uint_as_float(v0[i + 1]), __uint_as_float(v0[i + 2]),
+                     __uint_as_float(v0[i + 3]));
+          red_add_v4(base + (size_t)r * D + 32 + i, __uint_as_float(v1[i]), __uint_as_float(v1[i + 1]), __uint_as_float(v1[i + 2]),
+                     __uint_as_float(v1[i + 3]));
+        }
+      }
+#endif
+      FA4B_ACC(2);  // staging + reduction issue
       FA4B_HB(it * 16 + 6);
     }
+    if (w4 == 0) FA4B_ACCT_FLUSH(1);
   } else {
-    // ------------------------------------------------------------------ compute (warps 0-7)
+    // ------------------------------------------------------------------ compute (warps 0-15)
     constexpr int CW = QT / 2;                   // query columns per thread
-    const int half = warp >> 2;
+    const int grp = warp >> 3;                   // compute group: sub-tiles with it % 2 == grp
+    const int half = (warp >> 2) & 1;
     const int row = (warp & 3) * 32 + lane;      // key row inside the tile = TMEM lane
     const uint32_t lane_base = tm + ((uint32_t)((warp & 3) * 32) << 16);
     const int key = kt * 128 + row;
     const float beta = p.scale / 16.0f;
-    if (t < 16) s.c2[t] = (t < G) ? p.k_global[bhk] * p.scale * kLog2e * p.q_global[b * p.Hq + hk * G + t] : 0.f;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
     bool ok = true;
+    FA4B_ACCT_DECL
     // P8^T of sub-tile `it`: St -> 2^min(s2 + lstat, 8) -> E4M3 -> shared memory (A operand of dV);
     // the packed bytes also stay in registers for the dS step
     // this thread's row in the swizzled [key][q] tiles: byte offset of 16-byte chunk c is
@@ -390,34 +454,40 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     const uint32_t row_base = row * QT;
     const uint32_t swz = (QT == 128 ? (row & 7u) : ((row >> 1) & 3u)) << 4;
     auto do_p = [&](int it, uint32_t (&pk)[CW / 4]) -> bool {
-      const int st = it % kBwdStages, buf = it & 1;
+      const int st = it % kBwdStages;
       const int g = it / n_sub, qs = sub0 + it % n_sub;
       const uint64_t c2c2 = pack2(s.c2[g], s.c2[g]);
       const int q_first = qs * QT + half * CW;     // global query index of this thread's first column
       const bool diag = qs * QT < kt * 128 + 128;  // sub-tile overlaps the key tile: mask needed
       // the row statistics arrive through the async proxy: observe their barrier before reading them
-      if ((warp & 3) == 0) FA4B_TR(half, 10);
+      if ((warp & 7) == 0) FA4B_TR(grp, 10);
+      FA4B_ACC(0);  // loop / prologue
       if (!mbar_wait_warp(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 143, it)) return false;
-      if ((warp & 3) == 0) FA4B_TR(half, 11);
-      // st_full(it) is committed after dV(it-1), dK(it-3) and dQ(it-3): once it has fired, the P buffer this
-      // step overwrites (last read by dV(it-2)) and the dS buffer the next dS step overwrites (dS(it-1)
-      // replaces dS(it-3)) are no longer read by the tensor core
-      if (!mbar_wait_warp(&s.st_full, it & 1, &s.abort_flag, p.status, 140, it)) return false;
-      if ((warp & 3) == 0) FA4B_TR(half, 3);
+      FA4B_ACC(1);  // in_full
+      if ((warp & 7) == 0) FA4B_TR(grp, 11);
+      // st_full(it) is committed after dV(it-2), dK(it-2) and dQ(it-2): once it has fired, the group's P
+      // buffer (last read by dV(it-2)) is no longer read by the tensor core
+      if (!mbar_wait_warp(&s.st_full[grp], (it >> 1) & 1, &s.abort_flag, p.status, 140, it)) return false;
+      FA4B_ACC(2);  // st_full
+      if ((warp & 7) == 0) FA4B_TR(grp, 3);
       FA4B_HB(it * 16 + 1);
       FA4B_CONV(1, return false);
       tc_fence_after();
       const float* ls = &s.lstat[st][half * CW];
-      uint8_t* dst_row = &s.pt[buf][row_base];
+      uint8_t* dst_row = &s.pt[grp][row_base];
 #pragma unroll
       for (int c0 = 0; c0 < CW; c0 += 32) {
         uint32_t v[32];
-        tmem_ld32(lane_base + C::colSt + half * CW + c0, v);
+        tmem_ld32(lane_base + C::colX + grp * QT + half * CW + c0, v);
         tmem_ld_wait(v);
-        if ((warp & 3) == 0) FA4B_TR(half, 12);
+        if ((warp & 7) == 0) FA4B_TR(grp, 12);
         // 2^(s2 + lstat) = 256 P; no clamp at 2^8: the exponent can exceed 8 only by the rounding of
         // LSE, and E4M3 rounds 2^8.0x back to 256.  The masked variant is a separate, warp-uniform
         // path so that the common one carries no compare/select per element.
+#ifdef FA4B_EXP_NOMATH
+        if (v[0] == 0x12345678u) dst_row[0] = 1;  // timing experiment: keep the load, drop math and stores
+        continue;
+#endif
         if (diag) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -445,33 +515,42 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           *reinterpret_cast<uint4*>(dst_row + ((uint32_t)(half * CW + c0 + 16 * i) ^ swz)) =
               make_uint4(pk[c0 / 4 + 4 * i], pk[c0 / 4 + 4 * i + 1], pk[c0 / 4 + 4 * i + 2], pk[c0 / 4 + 4 * i + 3]);
       }
-      if ((warp & 3) == 0) FA4B_TR(half, 13);
+      FA4B_ACC(3);  // P: load + math + stores
+      if ((warp & 7) == 0) FA4B_TR(grp, 13);
       fence_async_smem();
-      if ((warp & 3) == 0) FA4B_TR(half, 14);
+      if ((warp & 7) == 0) FA4B_TR(grp, 14);
       tc_fence_before();
-      mbar_arrive_warp(&s.pt_ready[buf]);
+      mbar_arrive_warp(&s.pt_ready[grp]);
+      FA4B_ACC(4);  // fence + arrive
       FA4B_HB(it * 16 + 2);
-      if ((warp & 3) == 0) FA4B_TR(half, 1);
+      if ((warp & 7) == 0) FA4B_TR(grp, 1);
       return true;
     };
     // dS8^T of sub-tile `it`: (dP16 + dstat) * P8 * scale/16 -> E4M3 -> shared memory
     const uint64_t bb = pack2(beta, beta);
     auto do_ds = [&](int it, const uint32_t (&pk)[CW / 4]) -> bool {
-      const int st = it % kBwdStages, buf = it & 1;
-      if ((warp & 3) == 0) FA4B_TR(half, 20);
-      if (!mbar_wait_warp(&s.dp_full, it & 1, &s.abort_flag, p.status, 141, it)) return false;
-      if ((warp & 3) == 0) FA4B_TR(half, 4);
+      const int st = it % kBwdStages;
+      if ((warp & 7) == 0) FA4B_TR(grp, 20);
+      // dp_full(it) is committed after dK(it-2) and dQ(it-2), the last readers of the group's dS buffer
+      FA4B_ACC(0);
+      if (!mbar_wait_warp(&s.dp_full[grp], (it >> 1) & 1, &s.abort_flag, p.status, 141, it)) return false;
+      FA4B_ACC(5);  // dp_full
+      if ((warp & 7) == 0) FA4B_TR(grp, 4);
       FA4B_HB(it * 16 + 3);
       FA4B_CONV(2, return false);
       tc_fence_after();
       const float* dsm = &s.dstat[st][half * CW];
-      uint8_t* dst_row = &s.dst[buf][row_base];
+      uint8_t* dst_row = &s.dst[grp][row_base];
 #pragma unroll
       for (int c0 = 0; c0 < CW; c0 += 32) {
         uint32_t v[32];
-        tmem_ld32(lane_base + C::colDPt + half * CW + c0, v);
+        tmem_ld32(lane_base + C::colX + grp * QT + half * CW + c0, v);
         tmem_ld_wait(v);
-        if ((warp & 3) == 0) FA4B_TR(half, 22);
+        if ((warp & 7) == 0) FA4B_TR(grp, 22);
+#ifdef FA4B_EXP_NOMATH
+        if (v[0] == 0x12345678u) dst_row[0] = 1;
+        continue;
+#endif
         uint32_t dk4[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -488,55 +567,57 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           *reinterpret_cast<uint4*>(dst_row + ((uint32_t)(half * CW + c0 + 16 * i) ^ swz)) =
               make_uint4(dk4[4 * i], dk4[4 * i + 1], dk4[4 * i + 2], dk4[4 * i + 3]);
       }
-      if ((warp & 3) == 0) FA4B_TR(half, 23);
+      FA4B_ACC(6);  // dS: load + math + stores
+      if ((warp & 7) == 0) FA4B_TR(grp, 23);
       fence_async_smem();
-      if ((warp & 3) == 0) FA4B_TR(half, 24);
+      if ((warp & 7) == 0) FA4B_TR(grp, 24);
       tc_fence_before();
-      mbar_arrive_warp(&s.ds_ready[buf]);
+      mbar_arrive_warp(&s.ds_ready[grp]);
+      FA4B_ACC(7);  // fence + arrive
       FA4B_HB(it * 16 + 4);
-      if ((warp & 3) == 0) FA4B_TR(half, 2);
+      if ((warp & 7) == 0) FA4B_TR(grp, 2);
       return true;
     };
-    // software pipeline, unrolled by two so that the two register sets keep static names:
-    // P(it+1) is computed before dS(it)
-    uint32_t pk_a[CW / 4], pk_b[CW / 4];
-    ok = do_p(0, pk_a);
-    for (int it = 0; ok && it < n_it; it += 2) {
-      if (it + 1 < n_it) ok = do_p(it + 1, pk_b);
-      if (ok) ok = do_ds(it, pk_a);
-      if (ok && it + 1 < n_it) {
-        if (it + 2 < n_it) ok = do_p(it + 2, pk_a);
-        if (ok) ok = do_ds(it + 1, pk_b);
-      }
+    // this group's sub-tiles; the other group works on the ones in between
+    uint32_t pk[CW / 4];
+    for (int it = grp; ok && it < n_it; it += 2) {
+      ok = do_p(it, pk);
+      if (ok) ok = do_ds(it, pk);
     }
+    if ((warp & 7) == 0) FA4B_ACCT_FLUSH(2 + grp);
     // ------------------------------------------------------------------ dK, dV of this key tile
     FA4B_HB(0xA0);
     if (ok) ok = mbar_wait_warp(&s.acc_done, 0, &s.abort_flag, p.status, 142);
     FA4B_HB(0xA1);
     if (ok) {
+      // each of the four warps of a TMEM lane quarter writes a quarter of the columns
       tc_fence_after();
       constexpr float inv = 1.0f / 1024.0f;
-      __nv_bfloat16* dkrow = p.dk + (int64_t)b * p.dk_sb + (int64_t)hk * p.dk_sh + (int64_t)key * p.dk_ss + (D / 2) * half;
-      __nv_bfloat16* dvrow = p.dv + (int64_t)b * p.dv_sb + (int64_t)hk * p.dv_sh + (int64_t)key * p.dv_ss + (D / 2) * half;
+      constexpr int EW = D / 4;
+      const int slice = grp * 2 + half;
+      __nv_bfloat16* dkrow = p.dk + (int64_t)b * p.dk_sb + (int64_t)hk * p.dk_sh + (int64_t)key * p.dk_ss + EW * slice;
+      __nv_bfloat16* dvrow = p.dv + (int64_t)b * p.dv_sb + (int64_t)hk * p.dv_sh + (int64_t)key * p.dv_ss + EW * slice;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         __nv_bfloat16* dst = which ? dvrow : dkrow;
-        const uint32_t col = (which ? C::colDV : C::colDK) + (D / 2) * half;
-#pragma unroll
-        for (int c0 = 0; c0 < D / 2; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(lane_base + col + c0, v);
+        const uint32_t col = (which ? C::colDV : C::colDK) + EW * slice;
+        uint32_t v[EW];
+        if constexpr (EW == 32) {
+          tmem_ld32(lane_base + col, v);
           tmem_ld_wait(v);
-          uint32_t w[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[2 * i]) * inv, __uint_as_float(v[2 * i + 1]) * inv);
-            w[i] = *reinterpret_cast<const uint32_t*>(&h2);
-          }
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            *reinterpret_cast<uint4*>(dst + c0 + 8 * i) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        } else {
+          tmem_ld16(lane_base + col, v);
+          tmem_ld_wait16(v);
         }
+        uint32_t w[EW / 2];
+#pragma unroll
+        for (int i = 0; i < EW / 2; ++i) {
+          const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[2 * i]) * inv, __uint_as_float(v[2 * i + 1]) * inv);
+          w[i] = *reinterpret_cast<const uint32_t*>(&h2);
+        }
+#pragma unroll
+        for (int i = 0; i < EW / 8; ++i)
+          *reinterpret_cast<uint4*>(dst + 8 * i) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
       }
     }
   }
@@ -544,7 +625,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
   tc_fence_before();
   __syncthreads();
   waitprof_flush(&s.abort_flag);
-  if (warp == 12) tmem_dealloc(tm, 512);
+  if (warp == 20) tmem_dealloc(tm, 512);
   FA4B_HB(0xF1);
 }
 
@@ -596,7 +677,7 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   p.dk = static_cast<__nv_bfloat16*>(a.dk); p.dk_sb = a.dk_strides.batch; p.dk_sh = a.dk_strides.head; p.dk_ss = a.dk_strides.seq;
   p.dv = static_cast<__nv_bfloat16*>(a.dv); p.dv_sb = a.dv_strides.batch; p.dv_sh = a.dv_strides.head; p.dv_ss = a.dv_strides.seq;
   p.status = reinterpret_cast<uint32_t*>(ws + l.status);
-#if defined(FA4B_TRACE) || defined(FA4B_SELFCHECK)
+#if defined(FA4B_TRACE) || defined(FA4B_SELFCHECK) || defined(FA4B_ACCT)
   if (const char* e = getenv("FA4B_DEBUG_PTR")) p.dbg = reinterpret_cast<uint32_t*>(strtoull(e, nullptr, 16));
 #endif
   FA4B_CUDA(cudaMemsetAsync(p.status, 0, 16, st));

@@ -156,6 +156,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 __device__ __forceinline__ bool mbar_try_wait_uniform(uint64_t* bar, uint32_t parity) {
   return __all_sync(0xffffffffu, mbar_try_wait(bar, parity));
 }
+// non-blocking form for a warp that serves several barriers: test_wait never parks the thread
+// (a failed try_wait may sleep for microseconds)
+__device__ __forceinline__ bool mbar_test_uniform(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return __all_sync(0xffffffffu, ok != 0u);
+}
 static __device__ __noinline__ bool mbar_wait_warp_slow(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
                                                         uint32_t where, uint32_t detail) {
   const long long t0 = clock64();
@@ -258,6 +269,9 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // wait for the loads and make the compiler treat the registers as produced here
 __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" : FA4B_RW8(r, 0), FA4B_RW8(r, 8), FA4B_RW8(r, 16), FA4B_RW8(r, 24)::"memory");
+}
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : FA4B_RW8(r, 0), FA4B_RW8(r, 8)::"memory");
 }
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
