@@ -6,12 +6,14 @@
 // pairs first.  K/V arrive in 128-key stages and are consumed as 64-key blocks.
 // Roles: warps 0-3 softmax of the first tile, warps 4-7 softmax of the second
 // (one thread per query row, 64 key columns per block, no cross-thread
-// exchange), warp 8 TMA producer, warp 9 MMA issuer.  The two tiles run the
-// chain QK -> softmax -> PV independently, so the softmax of one overlaps the
-// tensor work and the other tile's softmax.
+// exchange), warp 8 TMA producer, warps 9 and 10 MMA issuers of the first and
+// the second tile.  The two tiles run the chain QK -> softmax -> PV
+// independently, each with its own issuer, accumulators and scale-factor
+// columns, so the softmax of one overlaps the tensor work and the other
+// tile's softmax and neither waits behind the other's events.
 //
 // TMEM columns (512 allocated): S0 0, S1 64, O0 128, O1 256, P0 384, P1 400,
-// Q scale factors 416 / 424, K scale factors (per stage parity) 432 / 440.
+// Q scale factors 416 / 424, K scale factors 432 + 16 tile + 8 (stage parity).
 #include <cstdlib>
 #include <mutex>
 #include <type_traits>
@@ -20,7 +22,7 @@
 
 namespace fa4b {
 
-constexpr int kFwdThreads = 320;
+constexpr int kFwdThreads = 352;
 constexpr int kStages = 4;
 // forward probabilities: nominal lift 2^5, reference point allowed to lag by 3 binades (P <= 2^8)
 constexpr float kLift = 5.0f, kHeadroom = 3.0f;
@@ -33,7 +35,7 @@ struct FwdSmem {
   alignas(1024) uint8_t v[kStages][128 * D];
   alignas(16) uint8_t q_sf[2][(D / 64) * 512];
   alignas(16) uint8_t k_sf[kStages][(D / 64) * 512];
-  alignas(8) uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[2], s_free[2], p_ready[2][2], o_done[2], mma_drained;
+  alignas(8) uint64_t q_full, kv_full[kStages], kv_empty[2][kStages], s_full[2], s_free[2], p_ready[2][2], o_done[2], mma_drained;
   uint32_t tmem_base;
   alignas(8) volatile uint32_t abort_flag;
   uint32_t pad_;
@@ -111,7 +113,8 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
     mbar_init(&s.q_full, 1);
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&s.kv_full[i], 1);
-      mbar_init(&s.kv_empty[i], 1);
+      mbar_init(&s.kv_empty[0][i], 1);  // released by each tile's issuer separately
+      mbar_init(&s.kv_empty[1][i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.s_full[i], 1);
@@ -120,7 +123,7 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       mbar_init(&s.p_ready[i][1], 4);
       mbar_init(&s.o_done[i], 1);
     }
-    mbar_init(&s.mma_drained, 1);
+    mbar_init(&s.mma_drained, nb1 ? 2 : 1);
     s.abort_flag = 0;
     fence_barrier_init();
   }
@@ -152,7 +155,9 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       int issued = 0;
       for (int j = 0; j < n_stages; ++j) {
         const int st = j % kStages;
-        if (j >= kStages && !mbar_wait(&s.kv_empty[st], ((j / kStages) - 1) & 1, &s.abort_flag, p.status, 10, j)) break;
+        // both tiles' issuers have released the slot (every stage but the last is used by both tiles)
+        if (j >= kStages && !mbar_wait(&s.kv_empty[0][st], ((j / kStages) - 1) & 1, &s.abort_flag, p.status, 10, j)) break;
+        if (j >= kStages && nb1 && !mbar_wait(&s.kv_empty[1][st], ((j / kStages) - 1) & 1, &s.abort_flag, p.status, 11, j)) break;
         mbar_expect_tx(&s.kv_full[st], kKvBytes);
         tma_load_3d(s.k_codes[st], &map_k, 0, j * 128, bhk, &s.kv_full[st]);
         bulk_load(s.k_sf[st], p.k_sf + ((size_t)bhk * n_tiles + j) * kPages * 512, kPages * 512, &s.kv_full[st]);
@@ -166,131 +171,101 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       mbar_wait_teardown(&s.q_full, 0);
       for (int j = issued > kStages ? issued - kStages : 0; j < issued; ++j) {
         mbar_wait_teardown(&s.kv_full[j % kStages], (j / kStages) & 1);
-        if (issued == n_stages && !s.abort_flag) mbar_wait_teardown(&s.kv_empty[j % kStages], (j / kStages) & 1);
+        if (issued == n_stages && !s.abort_flag) {
+          if (j < (nb0 + 1) / 2) mbar_wait_teardown(&s.kv_empty[0][j % kStages], (j / kStages) & 1);
+          if (nb1) mbar_wait_teardown(&s.kv_empty[1][j % kStages], (j / kStages) & 1);
+        }
       }
     }
-  } else if (warp == 9) {
-    // ---------------------------------------------------------------- MMA issuer
-    // The whole warp runs this loop so that control flow and descriptors stay warp-uniform; one
-    // elected lane (always the same) issues the tensor-core instructions and their commits.
-    {
+  } else if (warp >= 9) {
+    // ---------------------------------------------------------------- MMA issuers (warp 9: tile 0, warp 10: tile 1)
+    // The whole warp runs the loop so that control flow stays warp-uniform; one elected lane (always
+    // the same) issues the tensor-core instructions and their commits.  Everything a tile's chain
+    // writes (S, P, O, its scale-factor columns, its stage-release barriers) belongs to that tile's
+    // issuer alone; the two issuers share only the read-only K/V stages.
+    const int ti = warp - 9;
+    const int nb = ti ? nb1 : nb0;
+    if (nb > 0) {
       const bool leader = elect_one();
       constexpr uint32_t id_qk = idesc_fp4(128, 64, 0, 0, 0);
       constexpr uint32_t id_pv = idesc_f8(128, D, 0, 0, 0, 1);  // A = P (TMEM), B = V8 [keys, D] MN-major
       static_assert((kStages & (kStages - 1)) == 0, "stage index is taken with a mask");
-      FA4B_MARK(0, 1);
+      const uint32_t col_s = tm + kColS + 64 * ti, col_o = tm + kColO + 128 * ti, col_p = tm + kColP + 16 * ti;
+      const uint32_t col_sfq = tm + kColSfq + 8 * ti, col_sfk = tm + kColSfk + 16 * ti;
+      const uint32_t q_addr = smem_u32(s.q_codes[ti]);
       bool ok = mbar_wait_warp(&s.q_full, 0, &s.abort_flag, p.status, 20);
-      FA4B_MARK(0, 2);
       if (ok) {
         tc_fence_after();
-        for (int i = 0; i < (nb1 ? 2 : 1); ++i)
-          for (int pg = 0; pg < kPages; ++pg)
-            if (leader) tmem_cp_page(tm + kColSfq + 8 * i + 4 * pg, make_page_desc(smem_u32(s.q_sf[i] + 512 * pg)));
-      }
-      // Q.K^T of 64-key block jb for tile TI; the block's stage has been waited for and its scale pages
-      // copied.  Descriptors are rebuilt from the shared-memory addresses at every issue: a variant
-      // that added constants to precomputed descriptors faulted at D = 64 (cause not established).
-      auto issue_qk = [&](auto ti_c, int jb) {
-        constexpr int TI = decltype(ti_c)::value;
-        FA4B_PROF_SCOPE(&s.abort_flag, 40);
-        const int st = (jb >> 1) & (kStages - 1), hb = jb & 1, sp = (jb >> 1) & 1;
+        if (leader) {
 #pragma unroll
-        for (int k = 0; k < D / 64; ++k)
-          if (leader) mma_nvfp4_ss(tm + kColS + 64 * TI, make_tile_desc(smem_u32(s.q_codes[TI]) + 32 * k, D / 2),
-                       make_tile_desc(smem_u32(s.k_codes[st]) + hb * 64 * (D / 2) + 32 * k, D / 2), id_qk, tm + kColSfq + 8 * TI + 4 * k,
-                       tm + kColSfk + 8 * sp + 4 * k + 2 * hb, k > 0);
-        {
-          FA4B_PROF_SCOPE(&s.abort_flag, 42);
-          if (leader) mma_commit(&s.s_full[TI]);
+          for (int pg = 0; pg < kPages; ++pg) tmem_cp_page(col_sfq + 4 * pg, make_page_desc(smem_u32(s.q_sf[ti] + 512 * pg)));
         }
+        __syncwarp();
+      }
+      // Q.K^T of 64-key block jb; the block's stage has been waited for and its scale pages copied
+      auto issue_qk = [&](int jb) {
+        const int st = (jb >> 1) & (kStages - 1), hb = jb & 1, sp = (jb >> 1) & 1;
+        if (leader) {
+          const uint32_t k_addr = smem_u32(s.k_codes[st]) + hb * 64 * (D / 2);
+#pragma unroll
+          for (int k = 0; k < D / 64; ++k)
+            mma_nvfp4_ss(col_s, make_tile_desc(q_addr + 32 * k, D / 2), make_tile_desc(k_addr + 32 * k, D / 2), id_qk, col_sfq + 4 * k,
+                         col_sfk + 8 * sp + 4 * k + 2 * hb, k > 0);
+          mma_commit(&s.s_full[ti]);
+        }
+        __syncwarp();
       };
       auto open_stage = [&](int jb) -> bool {  // first block of a stage: wait for the data, copy the K scale pages
         const int sj = jb >> 1, st = sj & (kStages - 1);
         if (!mbar_wait_warp(&s.kv_full[st], (sj / kStages) & 1, &s.abort_flag, p.status, 21, jb)) return false;
         tc_fence_after();
-        for (int pg = 0; pg < kPages; ++pg)
-          if (leader) tmem_cp_page(tm + kColSfk + 8 * (sj & 1) + 4 * pg, make_page_desc(smem_u32(s.k_sf[st] + 512 * pg)));
+        if (leader) {
+#pragma unroll
+          for (int pg = 0; pg < kPages; ++pg) tmem_cp_page(col_sfk + 8 * (sj & 1) + 4 * pg, make_page_desc(smem_u32(s.k_sf[st] + 512 * pg)));
+        }
+        __syncwarp();
         return true;
       };
-      auto issue_pv = [&](auto ti_c, int j) {
-        constexpr int TI = decltype(ti_c)::value;
-        FA4B_PROF_SCOPE(&s.abort_flag, 41);
+      auto issue_pv = [&](int j) {
         const int st = (j >> 1) & (kStages - 1), hb = j & 1;
+        if (leader) {
+          const uint32_t v_addr = smem_u32(s.v[st]) + hb * 64 * D;
 #pragma unroll
-        for (int k = 0; k < 2; ++k)
-          if (leader) mma_f8_ts(tm + kColO + 128 * TI, tm + kColP + 16 * TI + 8 * k, make_tile_desc(smem_u32(s.v[st]) + (hb * 64 + 32 * k) * D, D),
-                    id_pv, (j > 0 || k > 0) ? 1u : 0u);
-        {
-          FA4B_PROF_SCOPE(&s.abort_flag, 43);
-          if (leader) mma_commit(&s.o_done[TI]);
+          for (int k = 0; k < 2; ++k) mma_f8_ts(col_o, col_p + 8 * k, make_tile_desc(v_addr + 32 * k * D, D), id_pv, (j > 0 || k > 0) ? 1u : 0u);
+          mma_commit(&s.o_done[ti]);
+          // the stage's last block for this tile: its K and V are not read again
+          if ((j & 1) == 1 || j == nb - 1) mma_commit(&s.kv_empty[ti][st]);
         }
+        __syncwarp();
       };
-      using T0 = std::integral_constant<int, 0>;
-      using T1 = std::integral_constant<int, 1>;
-      FA4B_MARK(0, 3);
       if (ok) ok = open_stage(0);
-      FA4B_MARK(0, 4);
-      if (ok) {
-        issue_qk(T0{}, 0);
-        FA4B_MARK(0, 5);
-        if (nb1) issue_qk(T1{}, 0);
-        FA4B_MARK(0, 6);
-      }
-      for (int j = 0; ok && j < nbmax; ++j) {
-        FA4B_PROF_SCOPE(&s.abort_flag, 45);  // whole block step of the issuer
+      if (ok) issue_qk(0);
+      for (int j = 0; ok && j < nb; ++j) {
         const int jn = j + 1;
-        FA4B_MARK(0, 100 + 10 * j);
-        FA4B_TR(2, 140);
-        if (jn < nbmax && (jn & 1) == 0) {
-          ok = open_stage(jn);
+        if (jn < nb) {
+          if ((jn & 1) == 0) {
+            ok = open_stage(jn);
+            if (!ok) break;
+          }
+          // next block's scores as soon as this block's have been read out of TMEM
+          ok = mbar_wait_warp(&s.s_free[ti], j & 1, &s.abort_flag, p.status, 23, j);
           if (!ok) break;
-          FA4B_TR(2, 141);
-        }
-        // next block's scores as soon as this block's have been read out of TMEM
-        if (jn < nb0) {
-          ok = mbar_wait_warp(&s.s_free[0], j & 1, &s.abort_flag, p.status, 23, j);
-          if (!ok) break;
-          FA4B_TR(2, 100 + 0);
+          FA4B_TR(2 + ti, 100);
           tc_fence_after();
-          issue_qk(T0{}, jn);
-          FA4B_TR(2, 110 + 0);
-          FA4B_MARK(0, 101 + 10 * j);
+          issue_qk(jn);
+          FA4B_TR(2 + ti, 110);
         }
-        if (jn < nb1) {
-          ok = mbar_wait_warp(&s.s_free[1], j & 1, &s.abort_flag, p.status, 23, j);
-          if (!ok) break;
-          FA4B_TR(2, 100 + 1);
-          tc_fence_after();
-          issue_qk(T1{}, jn);
-          FA4B_TR(2, 110 + 1);
-          FA4B_MARK(0, 102 + 10 * j);
-        }
-        if (j < nb0) {
-          ok = mbar_wait_warp(&s.p_ready[0][j & 1], (j >> 1) & 1, &s.abort_flag, p.status, 22, j);
-          if (!ok) break;
-          FA4B_TR(2, 120 + 0);
-          tc_fence_after();
-          issue_pv(T0{}, j);
-          FA4B_TR(2, 130 + 0);
-          FA4B_MARK(0, 103 + 10 * j);
-        }
-        if (j < nb1) {
-          ok = mbar_wait_warp(&s.p_ready[1][j & 1], (j >> 1) & 1, &s.abort_flag, p.status, 22, j);
-          if (!ok) break;
-          FA4B_TR(2, 120 + 1);
-          tc_fence_after();
-          issue_pv(T1{}, j);
-          FA4B_TR(2, 130 + 1);
-          FA4B_MARK(0, 104 + 10 * j);
-        }
-        if (leader && ((j & 1) == 1 || j == nbmax - 1)) mma_commit(&s.kv_empty[(j >> 1) & (kStages - 1)]);
+        ok = mbar_wait_warp(&s.p_ready[ti][j & 1], (j >> 1) & 1, &s.abort_flag, p.status, 22, j);
+        if (!ok) break;
+        FA4B_TR(2 + ti, 120);
+        tc_fence_after();
+        issue_pv(j);
+        FA4B_TR(2 + ti, 130);
       }
       // every tensor-core operation of this CTA has finished before TMEM is freed
       if (leader) mma_commit(&s.mma_drained);
-      FA4B_MARK(0, 900);
       if (leader) mbar_wait_teardown(&s.mma_drained, 0);
       __syncwarp();
-      FA4B_MARK(0, 901);
     }
   } else {
     // ---------------------------------------------------------------- softmax (warps 0-3: tile 0, warps 4-7: tile 1)

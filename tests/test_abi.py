@@ -27,7 +27,7 @@ def test_query_reports_build_facts():
     assert _lib.lib().fa4b_query(C.byref(info)) == 0
     assert info.abi_version == 1 and info.build_sm == 100
     assert info.tile_q == 128 and info.tile_kv == 128
-    assert info.fwd_tmem_columns == 512 and info.fwd_threads == 320
+    assert info.fwd_tmem_columns == 512 and info.fwd_threads == 352
     assert 0 < info.wait_limit <= 1 << 24
 
 
