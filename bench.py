@@ -298,7 +298,7 @@ def run_ours(args, rank, world, local_rank):
         "clocks": clocks,
         "e2e": {"value": world * flops_step * args.steps / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
                 "h2d_bytes_per_step": nbytes_in, "d2h_bytes_per_step": 16},
-        "gpu_launches": 10 * args.steps,
+        "gpu_launches": 9 * args.steps,  # per step: 2 amax + 2 quantise (Q, K), V to FP8, forward, dO publication, backward, dQ conversion
         "roofline": {"bound": "tensor", "kernel": "attn_bwd_kernel<128>", "achieved": bwd_ach, "peak": bwd_peak, "unit": UNIT,
                      "frac": bwd_ach / bwd_peak, "traffic": None, "ms_per_launch": bwd_ms,
                      "peak_source": f"{peaks['source']} bf16 burst {peaks['bf16']} TF/s x4 (FP4) / x2 (FP8)",
