@@ -146,6 +146,80 @@ __device__ __forceinline__ void quantize_block(const float (&x)[N], float safe, 
   }
 }
 
+// ---- division by a block's step without a divide per element ------------------------------
+// q = RN(x / d) from r = RN(1 / d):  q0 = RN(x r),  e = x - d q0 (exact in one FMA),  q = RN(q0 + e r).
+// That is the correctly rounded quotient whenever r is the correctly rounded reciprocal and d's
+// significand is not all ones (Markstein's theorem); callers send such a d down the division path.
+__device__ __forceinline__ uint64_t div2_exact(uint64_t x2, uint64_t r2, uint64_t neg_d2) {
+  const uint64_t q0 = mul2(x2, r2);
+  return fma2(fma2(q0, neg_d2, x2), r2, q0);
+}
+__device__ __forceinline__ bool significand_all_ones(float d) { return (__float_as_uint(d) & 0x7FFFFFu) == 0x7FFFFFu; }
+// two bf16 in one word -> packed f32 pair (low half first)
+__device__ __forceinline__ uint64_t bf16x2_to_f32x2(uint32_t w) { return pack2u(w << 16, w & 0xFFFF0000u); }
+// |a|, |b| element-wise maximum of packed bf16 pairs
+__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t acc, uint32_t w) {
+  const __nv_bfloat162 m = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&acc), __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w)));
+  return *reinterpret_cast<const uint32_t*>(&m);
+}
+// eight packed f32 pairs -> sixteen E2M1 codes (two words)
+__device__ __forceinline__ void e2m1_pack16(const uint64_t (&q)[8], uint32_t& lo, uint32_t& hi) {
+  uint32_t b[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float a, c;
+    unpack2(q[i], a, c);
+    b[i] = cvt_e2m1x2(a, c);
+  }
+  // byte merges as permutes: three operations per word
+  lo = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+  hi = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
+}
+// NVFP4 scale byte E4M3(clamp(bamax / 6 / g)) from one multiplication by inv6g ~ 1 / (6 g).  The
+// product is within 3 ulp of the twice-rounded quotient; every E4M3 rounding boundary has zero low
+// 19 significand bits, so a product more than 16 ulp away from such a pattern rounds to the same
+// byte, and the rare closer one takes the two divisions.
+__device__ __forceinline__ uint32_t nvfp4_scale_byte(float bamax, float g, float inv6g) {
+  float s = bamax * inv6g;
+  if (((__float_as_uint(s) + 16u) & 0x7FFFFu) <= 32u) s = (bamax / 6.0f) / g;
+  return cvt_e4m3x2(s, 0.f) & 0xffu;
+}
+// per-tensor table over the 127 scale bytes: step d = max(E4M3(byte) g, FLT_MIN) and r = RN(1 / d)
+// (r = 0 marks a step whose significand is all ones: divide).  128 threads fill it.
+struct StepTable {
+  float d[128];
+  float r[128];
+};
+__device__ __forceinline__ void fill_step_table(StepTable& tab, float g, int t) {
+  if (t < 128) {
+    const float dec = (t < 127) ? e4m3_to_f32((uint32_t)t) : 0.f;
+    const float d = fmaxf(dec * g, kFltMin);
+    tab.d[t] = d;
+    tab.r[t] = significand_all_ones(d) ? 0.f : __frcp_rn(d);
+  }
+}
+// sixteen values (eight packed pairs, largest magnitude `bamax`) divided by the step of scale byte
+// `sb`.  A block whose quotients could overflow (a step clamped to FLT_MIN under values of ordinary
+// size) divides: inf - inf in the correction would lose the sign that saturation keeps.
+__device__ __forceinline__ void nvfp4_codes16(const uint64_t (&x)[8], float bamax, const StepTable& tab, uint32_t sb, uint32_t& lo,
+                                              uint32_t& hi) {
+  const float d = tab.d[sb], r = tab.r[sb];
+  uint64_t q[8];
+  if (r != 0.f && bamax * r < 1.0e38f) {
+    const uint64_t r2 = pack2(r, r), nd2 = pack2(-d, -d);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = div2_exact(x[i], r2, nd2);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float a, c;
+      unpack2(x[i], a, c);
+      q[i] = pack2(a / d, c / d);
+    }
+  }
+  e2m1_pack16(q, lo, hi);
+}
+
 // NVFP4 block scale: s = E4M3(clamp(bamax / 6 / g)), returns the byte and safe = max(s*g, FLT_MIN)
 __device__ __forceinline__ uint32_t nvfp4_block_scale(float bamax, float g, float& safe) {
   const float s = (bamax / 6.0f) / g;

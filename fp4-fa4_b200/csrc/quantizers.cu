@@ -146,12 +146,17 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
   __shared__ __align__(16) uint8_t sc_row[2 * 512];
   __shared__ __align__(16) uint8_t sc_col[COL ? 2 * 512 : 16];
   __shared__ __align__(16) uint8_t cb_col[COL ? kTile * 80 : 16];  // [128 columns][64 code bytes + pad]
+  __shared__ StepTable steps;
 
   const int t = threadIdx.x;
-  const int64_t row0 = (int64_t)blockIdx.y * kTile, col0 = (int64_t)blockIdx.x * kTile;
+  // tiles run from the end of the matrix to its start: the statistics pass that precedes this kernel
+  // read the matrix front to back, so its last part is the part still in L2
+  const int64_t row0 = (int64_t)(gridDim.y - 1 - blockIdx.y) * kTile, col0 = (int64_t)(gridDim.x - 1 - blockIdx.x) * kTile;
   const float amax = *p.amax;
   const float g = amax / kNvfp4GlobalDiv;
+  const float inv6g = 1.0f / (6.0f * g);
   if (blockIdx.x == 0 && blockIdx.y == 0 && t == 0) *p.global_scale = g;
+  fill_step_table(steps, g, t);
 
   // ---- stage the tile (and apply the norm) -------------------------------------
 #pragma unroll
@@ -179,55 +184,67 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
   __syncthreads();
 
   const bool all_zero = !(amax > 0.f);
-  // ---- row-wise 1x16 blocks: 1024 per tile, 4 per thread --------------------------
+  // ---- row-wise 1x16 blocks: 512 segments of two blocks, two segments per thread -----------
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int b = t + i * 256;
-    const int r = b >> 3, kb = b & 7;
-    const uint4 lo = *reinterpret_cast<const uint4*>(&tile[r * kPitch + kb * 16]);
-    const uint4 hi = *reinterpret_cast<const uint4*>(&tile[r * kPitch + kb * 16 + 8]);
-    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-    float xv[16];
-    float bamax = 0.f;
+  for (int i = 0; i < 2; ++i) {
+    const int seg = t + i * 256;
+    const int r = seg >> 2, c32 = (seg & 3) * 32;
+    uint32_t w[16];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      xv[2 * k] = bf16_bits_to_f32(w[k] & 0xffffu);
-      xv[2 * k + 1] = bf16_bits_to_f32(w[k] >> 16);
-      bamax = fmaxf(bamax, fmaxf(fabsf(xv[2 * k]), fabsf(xv[2 * k + 1])));
+    for (int j = 0; j < 4; ++j) {
+      const uint4 v = *reinterpret_cast<const uint4*>(&tile[r * kPitch + c32 + 8 * j]);
+      w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
     }
-    uint32_t packed[2] = {0, 0};
-    uint32_t sbyte = 0;
-    if (!all_zero) {
-      float safe;
-      sbyte = nvfp4_block_scale(bamax, g, safe);
-      quantize_block<16>(xv, safe, packed);
-    }
-    *reinterpret_cast<uint2*>(p.codes_row + (row0 + r) * (p.cols / 2) + (col0 + kb * 16) / 2) = make_uint2(packed[0], packed[1]);
-    sc_row[(kb >> 2) * 512 + page_offset(r, kb)] = (uint8_t)sbyte;
-  }
-  // ---- column-wise 16x1 blocks (transposed output) ----------------------------------
-  if (COL) {
+    uint32_t codes[4] = {0, 0, 0, 0};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int b = t + i * 256;
-      const int c = b & 127, rb = b >> 7;  // column c, row block rb (16 rows)
-      float xv[16];
-      float bamax = 0.f;
+    for (int h = 0; h < 2; ++h) {  // the two 16-element blocks of the segment
+      uint32_t m2 = 0;
+      uint64_t x[8];
 #pragma unroll
-      for (int k = 0; k < 16; ++k) {
-        xv[k] = __bfloat162float(tile[(rb * 16 + k) * kPitch + c]);
-        bamax = fmaxf(bamax, fabsf(xv[k]));
+      for (int k = 0; k < 8; ++k) {
+        m2 = absmax_bf16x2(m2, w[8 * h + k]);
+        x[k] = bf16x2_to_f32x2(w[8 * h + k]);
       }
-      uint32_t packed[2] = {0, 0};
+      const float bamax = fmaxf(bf16_bits_to_f32(m2 & 0xffffu), bf16_bits_to_f32(m2 >> 16));
       uint32_t sbyte = 0;
       if (!all_zero) {
-        float safe;
-        sbyte = nvfp4_block_scale(bamax, g, safe);
-        quantize_block<16>(xv, safe, packed);
+        sbyte = nvfp4_scale_byte(bamax, g, inv6g);
+        nvfp4_codes16(x, bamax, steps, sbyte, codes[2 * h], codes[2 * h + 1]);
       }
-      *reinterpret_cast<uint2*>(&cb_col[c * 80 + rb * 8]) = make_uint2(packed[0], packed[1]);
-      // transposed tensor: row = c (within this tile's 128 columns), kblock = rb (within 8)
-      sc_col[(rb >> 2) * 512 + page_offset(c, rb)] = (uint8_t)sbyte;
+      const int kb = (c32 >> 4) + h;
+      sc_row[(kb >> 2) * 512 + page_offset(r, kb)] = (uint8_t)sbyte;
+    }
+    *reinterpret_cast<uint4*>(p.codes_row + (row0 + r) * (p.cols / 2) + (col0 + c32) / 2) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+  }
+  // ---- column-wise 16x1 blocks (transposed output): a thread takes two adjacent columns ------
+  if (COL) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int cp = t & 63, rb = (t >> 6) + 4 * i;  // column pair, block of 16 rows
+      uint32_t w[16];
+      uint32_t m2 = 0;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        w[k] = *reinterpret_cast<const uint32_t*>(&tile[(rb * 16 + k) * kPitch + 2 * cp]);
+        m2 = absmax_bf16x2(m2, w[k]);
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {  // low halves: column 2cp, high halves: column 2cp + 1
+        const int c = 2 * cp + h;
+        const float bamax = bf16_bits_to_f32(h ? (m2 >> 16) : (m2 & 0xffffu));
+        uint64_t x[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          x[k] = h ? pack2u(w[2 * k] & 0xFFFF0000u, w[2 * k + 1] & 0xFFFF0000u) : pack2u(w[2 * k] << 16, w[2 * k + 1] << 16);
+        uint32_t lo = 0, hi = 0, sbyte = 0;
+        if (!all_zero) {
+          sbyte = nvfp4_scale_byte(bamax, g, inv6g);
+          nvfp4_codes16(x, bamax, steps, sbyte, lo, hi);
+        }
+        *reinterpret_cast<uint2*>(&cb_col[c * 80 + rb * 8]) = make_uint2(lo, hi);
+        // transposed tensor: row = c (within this tile's 128 columns), kblock = rb (within 8)
+        sc_col[(rb >> 2) * 512 + page_offset(c, rb)] = (uint8_t)sbyte;
+      }
     }
   }
   __syncthreads();
@@ -272,27 +289,33 @@ __global__ void __launch_bounds__(256) mxfp4_kernel(const __nv_bfloat16* __restr
   const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
   const bool live = idx < rows * kblocks;
   const int64_t row = live ? idx / kblocks : 0, kb = live ? idx % kblocks : 0;
-  float xv[32];
-  float bamax = 0.f;
+  uint32_t w[16];
+  uint32_t m2 = 0;
   const uint4* src = reinterpret_cast<const uint4*>(x + row * ld + kb * 32);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const uint4 v = live ? __ldg(src + j) : make_uint4(0, 0, 0, 0);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      xv[j * 8 + 2 * k] = bf16_bits_to_f32(w[k] & 0xffffu);
-      xv[j * 8 + 2 * k + 1] = bf16_bits_to_f32(w[k] >> 16);
-      bamax = fmaxf(bamax, fmaxf(fabsf(xv[j * 8 + 2 * k]), fabsf(xv[j * 8 + 2 * k + 1])));
-    }
+    w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
   }
+#pragma unroll
+  for (int k = 0; k < 16; ++k) m2 = absmax_bf16x2(m2, w[k]);
+  const float bamax = fmaxf(bf16_bits_to_f32(m2 & 0xffffu), bf16_bits_to_f32(m2 >> 16));
   uint32_t packed[4] = {0, 0, 0, 0};
   uint32_t ebyte = 0;
   if (bamax > 0.f) {
     const int e = max(mx_exponent(bamax, mode), -126);
     ebyte = (uint32_t)min(e + 127, 254);
-    const float d = __uint_as_float((uint32_t)(e + 127) << 23) / 6.0f;
-    quantize_block<32>(xv, fmaxf(d, kFltMin), packed);
+    // step d = RN(2^e / 6) (significand 0x2AAAAB, never all ones); q = RN(x / d) through r = RN(1 / d)
+    const float d = fmaxf(__uint_as_float((uint32_t)(e + 127) << 23) / 6.0f, kFltMin);
+    const float r = __frcp_rn(d);
+    const uint64_t r2 = pack2(r, r), nd2 = pack2(-d, -d);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint64_t q[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) q[k] = div2_exact(bf16x2_to_f32x2(w[8 * h + k]), r2, nd2);
+      e2m1_pack16(q, packed[2 * h], packed[2 * h + 1]);
+    }
   }
   if (live) *reinterpret_cast<uint4*>(codes + row * (cols / 2) + kb * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
   // the four blocks of a 128-column page row are held by four adjacent lanes

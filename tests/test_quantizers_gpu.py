@@ -63,6 +63,45 @@ def test_nvfp4_with_supplied_amax_and_strided_input():
     _same(sc_row, ref.pages(), "row pages")
 
 
+def _wide_range(M, K, seed, lo=-20, hi=20):
+    """rows of very different magnitude: small rows get scale byte 0 (step clamped to FLT_MIN), where x / step
+    overflows and only the sign and saturation survive; mid rows land in the subnormal E4M3 scale range"""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g) * torch.exp2(torch.randint(lo, hi, (M, 1), generator=g).float())
+    return x.bfloat16()
+
+
+@pytest.mark.parametrize("seed,lo,hi", [(31, -20, 20), (32, -40, 0), (33, -4, 12)])
+def test_nvfp4_wide_dynamic_range_matches_oracle(seed, lo, hi):
+    x = _wide_range(512, 512, seed, lo, hi)
+    fp4_row, sc_row, fp4_col, sc_col, sg, _ = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=True)
+    ref, ref_t = O.nvfp4_quantize(x), O.nvfp4_quantize_transposed(x)
+    assert float(sg) == float(ref.global_scale)
+    _same(fp4_row, ref.codes, "row codes")
+    _same(sc_row, ref.pages(), "row scale pages")
+    _same(fp4_col, ref_t.codes, "transposed codes")
+    _same(sc_col, ref_t.pages(), "transposed scale pages")
+
+
+def test_nvfp4_supplied_amax_far_below_the_data_saturates_like_the_oracle():
+    x = _wide_range(256, 256, 34, 0, 10)
+    tiny = torch.tensor([2.0 ** -20], dtype=torch.float32)
+    fp4_row, sc_row, _, _, sg, _ = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=False, amax_in=tiny.to(DEV))
+    ref = O.nvfp4_quantize(x, amax=tiny)
+    assert float(sg) == float(ref.global_scale)
+    _same(fp4_row, ref.codes, "row codes")
+    _same(sc_row, ref.pages(), "row scale pages")
+
+
+def test_mxfp4_wide_dynamic_range_matches_oracle():
+    x = _wide_range(256, 512, 35, -60, 60)
+    for mode in ("ceil", "rte_mantissa", "floor"):
+        fp4, sc = fa4b.mxfp4_quantize_for_gemm(x.to(DEV), mode=mode)
+        ref = O.mxfp4_quantize(x, mode=mode)
+        _same(fp4, ref.codes, f"codes ({mode})")
+        _same(sc, ref.pages(), f"scale pages ({mode})")
+
+
 @pytest.mark.parametrize("mode", ["ceil", "rte_mantissa", "floor"])
 def test_mxfp4_matches_oracle(mode):
     x, _ = O.make_quantizer_inputs(256, 512, seed=11)
