@@ -4,7 +4,7 @@ NVFP4 / MXFP4 block quantizers that feed it.  Host side of the C ABI in
 include/fa4b.h; every operator runs hand-written CUDA and raises if the
 library is missing."""
 
-from . import _lib  # noqa: F401
+from . import _lib, parallel  # noqa: F401
 from .quantizers import (  # noqa: F401
     amax,
     dequant_mxfp4,

@@ -131,3 +131,30 @@ def test_backward_long_sequence():
     want, got = _run_backward(q, k, v, do)
     for w, g, name in zip(want, got, ("dq", "dk", "dv")):
         assert O.rel_l2(w, g.cpu()) < 2e-2, name
+
+
+def test_partition_by_batch_and_kv_head_reproduces_the_unsharded_run():
+    """The multi-GPU split (no collective): every "rank" runs its (batch, kv-head) units as an independent problem
+    on views of the global tensors; O, LSE, dK, dV match the unsharded run bit for bit, dQ up to the order of its
+    FP32 reductions."""
+    from fa4b import parallel
+
+    B, Hq, Hkv, S, D = 2, 8, 2, 384, 128
+    q, k, v, do = (t.to(DEV) for t in O.make_attention_inputs(B, Hq, Hkv, S, D, seed=77, rope=True, do_std=0.01))
+    o, lse, ws = attention.attn_forward(q, k, v)
+    dq, dk, dv = attention.attn_backward(o, lse, do, ws)
+    ws.check_status()
+    world = 3  # uneven on purpose: 4 units over 3 ranks
+    parts = {n: [] for n in ("o", "lse", "dq", "dk", "dv")}
+    for rank in range(world):
+        qs, ks, vs, dos = parallel.shard_attention_inputs(q, k, v, rank, world, do)
+        o_r, lse_r, ws_r = attention.attn_forward(qs, ks, vs)
+        dq_r, dk_r, dv_r = attention.attn_backward(o_r, lse_r, dos, ws_r)
+        ws_r.check_status()
+        for n, t in zip(parts, (o_r, lse_r, dq_r, dk_r, dv_r)):
+            parts[n].append(t)
+    assert torch.equal(parallel.unshard_q_like(parts["o"], B, Hq), o)
+    assert torch.equal(parallel.unshard_q_like(parts["lse"], B, Hq), lse)
+    assert torch.equal(parallel.unshard_kv_like(parts["dk"], B, Hkv), dk)
+    assert torch.equal(parallel.unshard_kv_like(parts["dv"], B, Hkv), dv)
+    assert O.rel_l2(dq.float().cpu(), parallel.unshard_q_like(parts["dq"], B, Hq).float().cpu()) < 1e-3
