@@ -187,6 +187,74 @@ __global__ void __launch_bounds__(128, 1) microgate_kernel(int kind, int K, cons
   if (warp == 0) tmem_dealloc(tm, 256);
 }
 
+// ---- tensor-core peak: every SM issues a long run of MMAs on operands that stay in shared memory ----
+// kind 0: kind::f8f6f4 E4M3 x E4M3, M128 N256 K32;  kind 1: kind::mxf4nvf4 block-scaled E2M1, M128 N256 K64.
+// Operands are pseudo-random bytes (scale bytes 1.0), two 256-column accumulators alternate.
+struct PeakSmem {
+  alignas(1024) uint8_t a[128 * 128];
+  alignas(1024) uint8_t b[256 * 128];
+  alignas(16) uint8_t sf[512];
+  alignas(8) uint64_t done;
+  uint32_t tmem_base;
+  alignas(8) volatile uint32_t abort_flag;
+  uint32_t pad_;
+  FA4B_PROF_FIELD
+};
+__global__ void __launch_bounds__(128, 1) tensor_peak_kernel(int kind, int iters, uint32_t* status) {
+  extern __shared__ uint8_t raw[];
+  PeakSmem& s = *reinterpret_cast<PeakSmem*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  const int t = threadIdx.x, warp = t >> 5;
+  for (int i = t; i < (128 + 256) * 128 / 4; i += 128) {
+    uint32_t h = (uint32_t)i * 2654435761u + blockIdx.x * 40503u;
+    h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+    // keep FP8 bytes finite (clear the top exponent bit of every byte): the timing does not depend on it, the power does not either
+    reinterpret_cast<uint32_t*>(s.a)[i] = h & 0xBFBFBFBFu;
+  }
+  for (int i = t; i < 128; i += 128) reinterpret_cast<uint32_t*>(s.sf)[i] = 0x38383838u;  // E4M3 1.0
+  if (t == 0) {
+    mbar_init(&s.done, 1);
+    s.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) tmem_alloc(&s.tmem_base, 512);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = s.tmem_base;
+  if (warp == 1) {
+    const bool leader = elect_one();
+    if (leader) {
+      if (kind == 0) {
+        constexpr uint32_t id = idesc_f8(128, 256, 0, 0, 0, 0);
+        for (int i = 0; i < iters; ++i) {
+          const uint32_t acc = tm + ((i >> 2) & 1) * 256;
+          const int k = i & 3;
+          mma_f8_ss(acc, make_tile_desc(smem_u32(s.a) + 32 * k, 128), make_tile_desc(smem_u32(s.b) + 32 * k, 128), id, 1);
+        }
+      } else {
+        // FP4 needs only 256 accumulator columns at a time here; the scale factors sit above them
+        constexpr uint32_t id = idesc_fp4(128, 256, 0, 0, 0);
+        const uint32_t sfa = tm + 480, sfb = tm + 488;
+        tmem_cp_page(sfa, make_page_desc(smem_u32(s.sf)));
+        tmem_cp_page(sfb, make_page_desc(smem_u32(s.sf)));
+        tmem_cp_page(sfb + 4, make_page_desc(smem_u32(s.sf)));
+        for (int i = 0; i < iters; ++i) {
+          const int k = i & 3;
+          mma_nvfp4_ss(tm + ((i >> 2) & 1) * 224, make_tile_desc(smem_u32(s.a) + 32 * k, 128), make_tile_desc(smem_u32(s.b) + 32 * k, 128), id, sfa,
+                       sfb, 1);
+        }
+      }
+      mma_commit(&s.done);
+    }
+    __syncwarp();
+    mbar_wait_warp(&s.done, 0, &s.abort_flag, status, 300);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, 512);
+}
+
 }  // namespace fa4b
 
 using namespace fa4b;
@@ -215,6 +283,24 @@ extern "C" int fa4b_microgate(int kind, int K, const void* a, const void* b, con
   FA4B_CUDA(attr_err);
   microgate_kernel<<<1, 128, smem, st>>>(kind, K, static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(b),
                                          static_cast<const uint8_t*>(sfa), static_cast<const uint8_t*>(sfb), out, status_out, ma, mb);
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
+}
+
+extern "C" int fa4b_tensor_peak(int kind, int iters, uint32_t* status_out, void* stream) {
+  FA4B_REQUIRE(kind == 0 || kind == 1, FA4B_UNSUPPORTED, "tensor_peak kind %d", kind);
+  FA4B_REQUIRE(iters > 0 && iters <= (1 << 20) && status_out, FA4B_BAD_ARG, "tensor_peak: iters must be in 1..2^20, status_out non-NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  FA4B_CUDA(cudaMemsetAsync(status_out, 0, 4 * sizeof(uint32_t), st));
+  int dev = 0, sms = 0;
+  FA4B_CUDA(cudaGetDevice(&dev));
+  FA4B_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int smem = sizeof(PeakSmem) + 1024;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(tensor_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
+  FA4B_CUDA(attr_err);
+  tensor_peak_kernel<<<sms, 128, smem, st>>>(kind, iters, status_out);
   FA4B_CUDA(cudaGetLastError());
   return FA4B_OK;
 }

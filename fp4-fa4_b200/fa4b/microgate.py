@@ -22,3 +22,23 @@ def run(kind: str, K: int, a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor |
     if int(status[0]) != 0:
         raise TimeoutError(f"microgate {kind}: device wait ran out at site {int(status[1])}")
     return out
+
+
+def tensor_peak(kind: str, iters: int = 8192, reps: int = 3) -> float:
+    """Measured dense tensor-core rate of the current GPU in TFLOP/s for ``kind`` in {"fp8", "nvfp4"}
+    (all SMs, operands resident in shared memory, CUDA events, best of ``reps``)."""
+    k = {"fp8": 0, "nvfp4": 1}[kind]
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    flops = sms * iters * 2.0 * 128 * 256 * (32 if k == 0 else 64)
+    best = float("inf")
+    for _ in range(reps + 1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        check(lib().fa4b_tensor_peak(C.c_int(k), C.c_int(iters), C.c_void_p(ptr(status)), C.c_void_p(current_stream())), "fa4b_tensor_peak")
+        e1.record()
+        e1.synchronize()
+        if int(status[0]) != 0:
+            raise TimeoutError(f"tensor_peak {kind}: device wait ran out")
+        best = min(best, e0.elapsed_time(e1))
+    return flops / (best * 1e-3) / 1e12

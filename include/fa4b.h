@@ -253,6 +253,14 @@ int fa4b_attn_check_status(const fa4b_attn_dims* d, const void* ws, void* stream
 int fa4b_microgate(int kind, int K, const void* a, const void* b, const void* sfa, const void* sfb,
                    float* out, uint32_t* status_out, void* stream);
 
+/* Tensor-core peak of this GPU for the two MMA kinds the attention kernels use: one CTA per SM issues
+ * `iters` back-to-back MMAs (M128 N256; kind 0: kind::f8f6f4 E4M3, K32; kind 1: kind::mxf4nvf4 block-scaled
+ * E2M1, K64) on operands resident in shared memory.  The caller times the launch; FLOPs = SMs * iters *
+ * 2*128*256*K.  Gives the roofline denominators that the reference reads off data sheets
+ * (results/fp4_fa4_technical_report_v2_20260819/sections/07_profile.tex:183-184 quotes nominal peaks).
+ * status_out [4] u32 device: [0] = 0 ok / 1 wait ran out. */
+int fa4b_tensor_peak(int kind, int iters, uint32_t* status_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -69,3 +69,13 @@ def test_fp8_a_from_tmem(K):
     a, b = _fp8((128, K), 7), _fp8((K, 128), 8)
     got = microgate.run("e4m3_ts_mn", K, a.to(DEV), b.to(DEV))
     assert O.rel_l2(a.float() @ b.float(), got.cpu()) < TOL
+
+
+def test_tensor_peak_reports_a_plausible_rate():
+    """All-SM MMA-only run: FP8 dense should land between the cuBLAS bf16 rate and the nominal 4.5 PF/s,
+    block-scaled FP4 above FP8."""
+    from fa4b import microgate
+    fp8 = microgate.tensor_peak("fp8", iters=4096)
+    fp4 = microgate.tensor_peak("nvfp4", iters=4096)
+    assert 1000.0 < fp8 < 5200.0, fp8
+    assert fp8 < fp4 < 10400.0, (fp8, fp4)
