@@ -52,6 +52,9 @@ inline fa4b_attn_ws_layout make_ws_layout(const fa4b_attn_dims& d) {
   return l;
 }
 
+// MXFP4 P.V route: the V section holds codes [B*Hkv, D, S/2] and then the E8M0 pages [B*Hkv, S/128, 512]
+inline size_t v_mx_pages_offset(const fa4b_attn_dims& d) { return align_up((size_t)d.B * d.Hkv * d.D * d.S / 2, 1024); }
+
 inline float resolve_scale(const fa4b_attn_dims& d) { return d.softmax_scale > 0.f ? d.softmax_scale : 1.0f / sqrtf((float)d.D); }
 
 void fill_kernel_info(fa4b_info* out);

@@ -27,14 +27,18 @@ constexpr int kStages = 4;
 // forward probabilities: nominal lift 2^5, reference point allowed to lag by 3 binades (P <= 2^8)
 constexpr float kLift = 5.0f, kHeadroom = 3.0f;
 constexpr uint32_t kColS = 0, kColO = 128, kColP = 384, kColSfq = 416, kColSfk = 432;
+constexpr uint32_t kColSfp = 464, kColSfv = 472;  // MXFP4 route: P scales (4 per tile), V scales (4 per stage parity, 8 per tile)
 
 template <int D>
 struct FwdSmem {
   alignas(1024) uint8_t q_codes[2][128 * D / 2];
   alignas(1024) uint8_t k_codes[kStages][128 * D / 2];
-  alignas(1024) uint8_t v[kStages][128 * D];
+  alignas(1024) uint8_t v[kStages][128 * D];   // E4M3 [keys][D]; MXFP4 route: codes [D][64 bytes] in the first half
+  alignas(1024) uint8_t p_mx[2][128 * 32];     // MXFP4 route: P codes of one 64-key block per tile, [row][32 bytes]
   alignas(16) uint8_t q_sf[2][(D / 64) * 512];
   alignas(16) uint8_t k_sf[kStages][(D / 64) * 512];
+  alignas(16) uint8_t v_sf[kStages][512];      // MXFP4 route: E8M0 page of the stage's V (row = feature)
+  alignas(16) uint8_t p_sf[2][512];            // MXFP4 route: E8M0 page of the P block (row = query row)
   alignas(8) uint64_t q_full, kv_full[kStages], kv_empty[2][kStages], s_full[2], s_free[2], p_ready[2][2], o_done[2], mma_drained;
   uint32_t tmem_base;
   alignas(8) volatile uint32_t abort_flag;
@@ -44,6 +48,7 @@ struct FwdSmem {
 
 struct FwdParams {
   int B, Hq, Hkv, S;
+  const uint8_t* v_sf;  // MXFP4 route: V scale pages [B*Hkv, S/128, 512]
   float scale_log2;  // softmax_scale * log2(e)
   const uint8_t* q_sf;
   const uint8_t* k_sf;
@@ -76,14 +81,14 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-template <int D>
+template <int D, bool MX>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v) {
   extern __shared__ uint8_t raw[];
   FwdSmem<D>& s = *reinterpret_cast<FwdSmem<D>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   constexpr int kPages = D / 64;
-  constexpr uint32_t kKvBytes = 128 * D / 2 + kPages * 512 + 128 * D;
+  constexpr uint32_t kKvBytes = 128 * D / 2 + kPages * 512 + (MX ? D * 64 + 512 : 128 * D);
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
   int tr_n = 0;
   (void)tr_n;
@@ -161,7 +166,12 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         mbar_expect_tx(&s.kv_full[st], kKvBytes);
         tma_load_3d(s.k_codes[st], &map_k, 0, j * 128, bhk, &s.kv_full[st]);
         bulk_load(s.k_sf[st], p.k_sf + ((size_t)bhk * n_tiles + j) * kPages * 512, kPages * 512, &s.kv_full[st]);
-        tma_load_3d(s.v[st], &map_v, 0, j * 128, bhk, &s.kv_full[st]);
+        if (MX) {
+          tma_load_3d(s.v[st], &map_v, j * 64, 0, bhk, &s.kv_full[st]);  // codes [D][128 keys / 2]
+          bulk_load(s.v_sf[st], p.v_sf + ((size_t)bhk * n_tiles + j) * 512, 512, &s.kv_full[st]);
+        } else {
+          tma_load_3d(s.v[st], &map_v, 0, j * 128, bhk, &s.kv_full[st]);
+        }
         issued = j + 1;
         FA4B_MARK(3, 10 + j);
       }
@@ -192,6 +202,7 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       static_assert((kStages & (kStages - 1)) == 0, "stage index is taken with a mask");
       const uint32_t col_s = tm + kColS + 64 * ti, col_o = tm + kColO + 128 * ti, col_p = tm + kColP + 16 * ti;
       const uint32_t col_sfq = tm + kColSfq + 8 * ti, col_sfk = tm + kColSfk + 16 * ti;
+      const uint32_t col_sfp = tm + kColSfp + 4 * ti, col_sfv = tm + kColSfv + 8 * ti;
       const uint32_t q_addr = smem_u32(s.q_codes[ti]);
       bool ok = mbar_wait_warp(&s.q_full, 0, &s.abort_flag, p.status, 20);
       if (ok) {
@@ -222,6 +233,7 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         if (leader) {
 #pragma unroll
           for (int pg = 0; pg < kPages; ++pg) tmem_cp_page(col_sfk + 8 * (sj & 1) + 4 * pg, make_page_desc(smem_u32(s.k_sf[st] + 512 * pg)));
+          if (MX) tmem_cp_page(col_sfv + 4 * (sj & 1), make_page_desc(smem_u32(s.v_sf[st])));
         }
         __syncwarp();
         return true;
@@ -229,9 +241,17 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       auto issue_pv = [&](int j) {
         const int st = (j >> 1) & (kStages - 1), hb = j & 1;
         if (leader) {
-          const uint32_t v_addr = smem_u32(s.v[st]) + hb * 64 * D;
+          if (MX) {
+            // one block-scaled MMA per 64-key block: A = P codes (shared memory), B = V codes [D][keys], both K-major;
+            // the block's two 32-key scale groups are bytes 0-1 of the P page and bytes 2 hb, 2 hb + 1 of the stage's V page
+            tmem_cp_page(col_sfp, make_page_desc(smem_u32(s.p_sf[ti])));
+            mma_mxfp4_ss(col_o, make_tile_desc(smem_u32(s.p_mx[ti]), 32), make_tile_desc(smem_u32(s.v[st]) + 32 * hb, 64),
+                         idesc_fp4(128, D, 1, 0, 2 * hb), col_sfp, col_sfv + 4 * ((j >> 1) & 1), j > 0 ? 1u : 0u);
+          } else {
+            const uint32_t v_addr = smem_u32(s.v[st]) + hb * 64 * D;
 #pragma unroll
-          for (int k = 0; k < 2; ++k) mma_f8_ts(col_o, col_p + 8 * k, make_tile_desc(v_addr + 32 * k * D, D), id_pv, (j > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < 2; ++k) mma_f8_ts(col_o, col_p + 8 * k, make_tile_desc(v_addr + 32 * k * D, D), id_pv, (j > 0 || k > 0) ? 1u : 0u);
+          }
           mma_commit(&s.o_done[ti]);
           // the stage's last block for this tile: its K and V are not read again
           if ((j & 1) == 1 || j == nb - 1) mma_commit(&s.kv_empty[ti][st]);
@@ -343,7 +363,8 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 5);
       // P = 2^(x c2 - mhat + kLift): packed FMA for the exponent, MUFU for the power, packed add for the sum
       const uint64_t shift2 = pack2(kLift - mhat, kLift - mhat);
-      uint32_t pa[8], pb[8];
+      uint32_t pa[8], pb[8];  // FP8 route: P as E4M3 words; MXFP4 route: pa = the block's 64 E2M1 codes
+      float pf[MX ? 64 : 1];  // MXFP4 route: the un-quantised probabilities, quantised per 32 keys below
       if (diag) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -353,9 +374,13 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
           // keys after the query get no weight
           const float p0 = (4 * i > lim) ? 0.f : ex2_approx(e0), p1 = (4 * i + 1 > lim) ? 0.f : ex2_approx(e1);
           const float p2 = (4 * i + 2 > lim) ? 0.f : ex2_approx(e2), p3 = (4 * i + 3 > lim) ? 0.f : ex2_approx(e3);
-          lsum2 = add2(lsum2, add2(pack2(p0, p1), pack2(p2, p3)));
-          const uint32_t w = cvt_e4m3x4(p0, p1, p2, p3);
-          if (i < 8) pa[i] = w; else pb[i - 8] = w;
+          if constexpr (MX) {
+            pf[4 * i] = p0; pf[4 * i + 1] = p1; pf[4 * i + 2] = p2; pf[4 * i + 3] = p3;
+          } else {
+            lsum2 = add2(lsum2, add2(pack2(p0, p1), pack2(p2, p3)));
+            const uint32_t w = cvt_e4m3x4(p0, p1, p2, p3);
+            if (i < 8) pa[i] = w; else pb[i - 8] = w;
+          }
         }
       } else {
 #pragma unroll
@@ -364,9 +389,58 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
           unpack2(fma2(pack2u(x[4 * i], x[4 * i + 1]), c2c2, shift2), e0, e1);
           unpack2(fma2(pack2u(x[4 * i + 2], x[4 * i + 3]), c2c2, shift2), e2, e3);
           const float p0 = ex2_approx(e0), p1 = ex2_approx(e1), p2 = ex2_approx(e2), p3 = ex2_approx(e3);
-          lsum2 = add2(lsum2, add2(pack2(p0, p1), pack2(p2, p3)));
-          const uint32_t w = cvt_e4m3x4(p0, p1, p2, p3);
-          if (i < 8) pa[i] = w; else pb[i - 8] = w;
+          if constexpr (MX) {
+            pf[4 * i] = p0; pf[4 * i + 1] = p1; pf[4 * i + 2] = p2; pf[4 * i + 3] = p3;
+          } else {
+            lsum2 = add2(lsum2, add2(pack2(p0, p1), pack2(p2, p3)));
+            const uint32_t w = cvt_e4m3x4(p0, p1, p2, p3);
+            if (i < 8) pa[i] = w; else pb[i - 8] = w;
+          }
+        }
+      }
+      uint32_t p_scales = 0;  // MXFP4 route: the block's two E8M0 bytes
+      if constexpr (MX) {
+        // MXFP4 of P in 32-key groups: e = ceil(log2 max), step d = 2^e / 6 = RN(4/3) 2^(e-3) and its correctly rounded
+        // reciprocal RN(1 / RN(4/3)) 2^(3-e) by exponent arithmetic, codes RN(p / d) -> E2M1; the row sum takes the
+        // represented values (the codes decoded, times d), as the reference's MX route does
+        constexpr uint32_t kD0 = 0x3FAAAAABu;  // RN(4/3)
+        const uint32_t r0 = __float_as_uint(__frcp_rn(__uint_as_float(kD0)));
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float b0 = 0.f, b1 = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            b0 = max3(b0, pf[32 * h + i], pf[32 * h + i + 1]);
+            b1 = max3(b1, pf[32 * h + i + 2], pf[32 * h + i + 3]);
+          }
+          const float bmax = fmaxf(b0, b1);
+          uint32_t cw[4] = {0, 0, 0, 0};
+          if (bmax > 0.f) {
+            const uint32_t bits = __float_as_uint(bmax);
+            int e = (int)(bits >> 23) - 127 + ((bits & 0x7FFFFFu) != 0u ? 1 : 0);
+            e = max(e, -100);  // below that every code is zero whatever the step
+            p_scales |= (uint32_t)(e + 127) << (8 * h);
+            const float step = __uint_as_float(kD0 + ((uint32_t)(e - 3) << 23)), r = __uint_as_float(r0 + ((uint32_t)(3 - e) << 23));
+            const uint64_t r2 = pack2(r, r), nd2 = pack2(-step, -step);
+            uint32_t hsum = 0;  // packed f16 pair: sums of the decoded low and high codes (exact: at most 16 x 6)
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              uint32_t word = 0;
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                float a, c;
+                unpack2(div2_exact(pack2(pf[32 * h + 8 * w + 2 * k], pf[32 * h + 8 * w + 2 * k + 1]), r2, nd2), a, c);
+                const uint32_t byte = cvt_e2m1x2(a, c);
+                hsum = hadd2_bits(hsum, e2m1x2_to_f16x2(byte));
+                word |= byte << (8 * k);
+              }
+              cw[w] = word;
+            }
+            const float2 hs = __half22float2(*reinterpret_cast<const __half2*>(&hsum));
+            lsum2 = add2(lsum2, pack2((hs.x + hs.y) * step, 0.f));
+          }
+#pragma unroll
+          for (int w = 0; w < 4; ++w) pa[4 * h + w] = cw[w];
         }
       }
       if ((warp & 3) == 0) FA4B_TR(ti, 3);
@@ -394,9 +468,17 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       }
       {
         FA4B_PROF_SCOPE(&s.abort_flag, 53);
-        tmem_st8(lane_base + kColP + 16 * ti, pa);
-        tmem_st8(lane_base + kColP + 16 * ti + 8, pb);
-        tmem_st_wait();
+        if constexpr (MX) {
+          // this row's 32 bytes of codes in the 32-byte-swizzled tile, its two scale bytes in the page
+          *reinterpret_cast<uint4*>(&s.p_mx[ti][swizzled_offset(row, 0, 32)]) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+          *reinterpret_cast<uint4*>(&s.p_mx[ti][swizzled_offset(row, 16, 32)]) = make_uint4(pa[4], pa[5], pa[6], pa[7]);
+          *reinterpret_cast<uint16_t*>(&s.p_sf[ti][page_offset(row, 0)]) = (uint16_t)p_scales;
+          fence_async_smem();
+        } else {
+          tmem_st8(lane_base + kColP + 16 * ti, pa);
+          tmem_st8(lane_base + kColP + 16 * ti + 8, pb);
+          tmem_st_wait();
+        }
         tc_fence_before();
         mbar_arrive_warp(&s.p_ready[ti][j & 1]);
       }
@@ -414,7 +496,9 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
     if ((t & 127) == 0) FA4B_MARK(1 + ti, 800);
     if (ok) {
       tc_fence_after();
-      const float inv = 0.25f / lsum;
+      // FP8 route: V carries a factor 4.  MXFP4 route: the MMA multiplies code x 2^e on both sides while a value is
+      // code x 2^e / 6, so the accumulator carries a factor 36 (the row sum above is of true values)
+      const float inv = (MX ? 1.0f / 36.0f : 0.25f) / lsum;
       __nv_bfloat16* orow = p.o + (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)(qt * 128 + row) * p.o_ss;
 #pragma unroll
       for (int c0 = 0; c0 < D; c0 += 32) {
@@ -443,7 +527,7 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
   if (t == 256) FA4B_MARK(4, 2);
 }
 
-template <int D>
+template <int D, bool MX>
 static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   const fa4b_attn_dims& d = a.dims;
   const fa4b_attn_ws_layout l = make_ws_layout(d);
@@ -452,11 +536,16 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   const uint64_t S = d.S;
   if (int s = make_tensor_map(&mq, ws + l.q_codes, 1, D / 2, S, (uint64_t)d.B * d.Hq, D / 2, S * (D / 2), D / 2, 128)) return s;
   if (int s = make_tensor_map(&mk, ws + l.k_codes, 1, D / 2, S, (uint64_t)d.B * d.Hkv, D / 2, S * (D / 2), D / 2, 128)) return s;
-  if (int s = make_tensor_map(&mv, ws + l.v_fp8, 1, D, S, (uint64_t)d.B * d.Hkv, D, S * D, D, 128)) return s;
+  if (MX) {  // codes [B*Hkv][D][S/2]: a stage is D rows x 64 bytes (128 keys)
+    if (int s = make_tensor_map(&mv, ws + l.v_fp8, 1, S / 2, D, (uint64_t)d.B * d.Hkv, S / 2, (uint64_t)D * (S / 2), 64, D)) return s;
+  } else {
+    if (int s = make_tensor_map(&mv, ws + l.v_fp8, 1, D, S, (uint64_t)d.B * d.Hkv, D, S * D, D, 128)) return s;
+  }
   FwdParams p{};
   p.B = d.B; p.Hq = d.Hq; p.Hkv = d.Hkv; p.S = d.S;
   p.scale_log2 = resolve_scale(d) * kLog2e;
   p.q_sf = ws + l.q_scales; p.k_sf = ws + l.k_scales;
+  p.v_sf = ws + l.v_fp8 + v_mx_pages_offset(d);
   p.q_global = reinterpret_cast<const float*>(ws + l.q_global);
   p.k_global = reinterpret_cast<const float*>(ws + l.k_global);
   p.o = static_cast<__nv_bfloat16*>(a.o);
@@ -469,19 +558,19 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   FA4B_CUDA(cudaMemsetAsync(p.status, 0, 64, st));
   const int smem = (int)sizeof(FwdSmem<D>) + 1024;
   static std::mutex mu;
-  static bool configured[64] = {};
+  static bool configured[64] = {};  // per instantiation (D, MX)
   int dev = 0;
   FA4B_CUDA(cudaGetDevice(&dev));
   {
     std::lock_guard<std::mutex> lock(mu);
     if (dev < 64 && !configured[dev]) {
-      FA4B_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      FA4B_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<D, MX>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       configured[dev] = true;
     }
   }
   const unsigned grid = (unsigned)(d.B * d.Hq * ((d.S / 128 + 1) / 2));
   if (a.ev_before) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_before), st));
-  attn_fwd_kernel<D><<<grid, kFwdThreads, smem, st>>>(p, mq, mk, mv);
+  attn_fwd_kernel<D, MX><<<grid, kFwdThreads, smem, st>>>(p, mq, mk, mv);
   FA4B_CUDA(cudaGetLastError());
   if (a.ev_after) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_after), st));
   return FA4B_OK;
@@ -489,7 +578,6 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
 
 int launch_attn_fwd(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   if (int s = check_dims(a.dims)) return s;
-  FA4B_REQUIRE(a.dims.pv_format == FA4B_PV_FP8_E4M3, FA4B_UNSUPPORTED, "the MXFP4 P.V route is not built yet");
   FA4B_REQUIRE(a.o && a.lse && a.ws, FA4B_BAD_ARG, "o, lse and ws are required");
   FA4B_REQUIRE((reinterpret_cast<uintptr_t>(a.o) & 15) == 0 && a.o_strides.batch % 8 == 0 && a.o_strides.head % 8 == 0 &&
                    a.o_strides.seq % 8 == 0,
@@ -498,7 +586,8 @@ int launch_attn_fwd(const fa4b_attn_fwd_args& a, cudaStream_t st) {
     fa4b_attn_prepare_args pa{a.dims, a.q, a.q_strides, a.k, a.k_strides, a.v, a.v_strides, a.ws};
     if (int s = launch_attn_prepare(pa, st)) return s;
   }
-  return a.dims.D == 128 ? fwd_impl<128>(a, st) : fwd_impl<64>(a, st);
+  if (a.dims.pv_format == FA4B_PV_MXFP4_E8M0) return a.dims.D == 128 ? fwd_impl<128, true>(a, st) : fwd_impl<64, true>(a, st);
+  return a.dims.D == 128 ? fwd_impl<128, false>(a, st) : fwd_impl<64, false>(a, st);
 }
 
 void fill_kernel_info(fa4b_info* out) {

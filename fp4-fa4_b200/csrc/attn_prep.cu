@@ -119,6 +119,57 @@ __global__ void __launch_bounds__(256) heads_to_fp8_kernel(HeadView x, int S, in
   }
 }
 
+// V as MXFP4 in 1x32 groups along the sequence, stored feature-major: codes [B*Hkv, D, S/2] (two keys
+// per byte) and one 512-byte E8M0 page per 128 keys (row = feature, k-block = 32 keys).  Scale exponent:
+// floor(log2 amax) plus one when amax / 2^floor >= 1.203125 (the reference's V cut-off,
+// projection_quantization_reference.py:695-704); step d = 2^e / 6.  grid (S/128, B*Hkv).
+template <int D>
+__global__ void __launch_bounds__(256) v_to_mx_kernel(HeadView x, int S, uint8_t* __restrict__ codes, uint8_t* __restrict__ pages) {
+  constexpr int kPitch = D + 8;
+  __shared__ __align__(16) __nv_bfloat16 tile[128 * kPitch];
+  __shared__ __align__(16) uint8_t page[512];
+  const int bh = blockIdx.y, kt = blockIdx.x, t = threadIdx.x;
+  constexpr int kVec = D / 8;
+  for (int c = t; c < 128 * kVec; c += 256) {
+    const int r = c / kVec, c8 = (c % kVec) * 8;
+    *reinterpret_cast<uint4*>(&tile[r * kPitch + c8]) = __ldg(reinterpret_cast<const uint4*>(x.row(bh, kt * 128 + r) + c8));
+  }
+  for (int i = t; i < 128; i += 256) reinterpret_cast<uint32_t*>(page)[i] = 0;
+  __syncthreads();
+  for (int item = t; item < D * 4; item += 256) {
+    const int d = item % D, kb = item / D;  // adjacent lanes take adjacent features: conflict-free column reads
+    float v[32];
+    float amax = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      v[k] = __bfloat162float(tile[(kb * 32 + k) * kPitch + d]);
+      amax = fmaxf(amax, fabsf(v[k]));
+    }
+    uint32_t packed[4] = {0, 0, 0, 0};
+    uint32_t ebyte = 0;
+    if (amax > 0.f) {
+      const uint32_t bits = __float_as_uint(fmaxf(amax, kFltMin));
+      int e = (int)(bits >> 23) - 127 + (((bits >> 16) & 0x7fu) >= 26u ? 1 : 0);  // 26/128 = 0.203125
+      e = min(max(e, -126), 127);
+      ebyte = (uint32_t)(e + 127);
+      const float step = fmaxf(__uint_as_float((uint32_t)(e + 127) << 23) / 6.0f, kFltMin);
+      const float r = __frcp_rn(step);
+      const uint64_t r2 = pack2(r, r), nd2 = pack2(-step, -step);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint64_t q[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) q[k] = div2_exact(pack2(v[16 * h + 2 * k], v[16 * h + 2 * k + 1]), r2, nd2);
+        e2m1_pack16(q, packed[2 * h], packed[2 * h + 1]);
+      }
+    }
+    *reinterpret_cast<uint4*>(codes + ((size_t)bh * D + d) * (S / 2) + kt * 64 + kb * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    page[page_offset((uint32_t)d, (uint32_t)kb)] = (uint8_t)ebyte;
+  }
+  __syncthreads();
+  if (t < 32) *reinterpret_cast<uint4*>(pages + ((size_t)bh * (S / 128) + kt) * 512 + t * 16) = *reinterpret_cast<const uint4*>(&page[t * 16]);
+}
+
 __device__ __forceinline__ float e5m2_to_f32(uint32_t byte) { return __half2float(__ushort_as_half((unsigned short)(byte << 8))); }
 
 // dO5 = E5M2(4 dO); dstat = -4 sum_d O * float(dO5); lstat = 8 - LSE * log2e
@@ -185,9 +236,14 @@ static int prepare_impl(const fa4b_attn_prepare_args& a, cudaStream_t st) {
                                                              reinterpret_cast<float*>(ws + l.q_global), ws + l.q_fp8);
   quant_heads_kernel<D><<<dim3(d.S / 128, nk), 256, 0, st>>>(k, d.S, amax_bits + nq, ws + l.k_codes, ws + l.k_scales,
                                                              reinterpret_cast<float*>(ws + l.k_global), ws + l.k_fp8);
-  const int64_t n_chunks = (int64_t)nk * d.S * (D / 16);
-  const unsigned grid = (unsigned)std::min<int64_t>((n_chunks + 255) / 256, 148 * 16);
-  heads_to_fp8_kernel<D><<<grid, 256, 0, st>>>(v, d.S, n_chunks, ws + l.v_fp8);
+  if (d.pv_format == FA4B_PV_MXFP4_E8M0) {
+    // the V section of the cache holds the MXFP4 codes, then (1024-aligned) the scale pages
+    v_to_mx_kernel<D><<<dim3(d.S / 128, nk), 256, 0, st>>>(v, d.S, ws + l.v_fp8, ws + l.v_fp8 + v_mx_pages_offset(d));
+  } else {
+    const int64_t n_chunks = (int64_t)nk * d.S * (D / 16);
+    const unsigned grid = (unsigned)std::min<int64_t>((n_chunks + 255) / 256, 148 * 16);
+    heads_to_fp8_kernel<D><<<grid, 256, 0, st>>>(v, d.S, n_chunks, ws + l.v_fp8);
+  }
   FA4B_CUDA(cudaGetLastError());
   return FA4B_OK;
 }

@@ -1,6 +1,7 @@
 // Shared device/host helpers: status plumbing, number-format conversions.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -76,6 +77,18 @@ __device__ __forceinline__ float e2m1_to_f32(uint32_t code) {
     default: mag = 6.f; break;
   }
   return (code & 8u) ? -mag : mag;
+}
+
+// one byte of two E2M1 codes -> packed f16 pair (low nibble first)
+__device__ __forceinline__ uint32_t e2m1x2_to_f16x2(uint32_t byte) {
+  uint32_t r;
+  asm("{ .reg .b8 t; cvt.u8.u32 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(r) : "r"(byte));
+  return r;
+}
+__device__ __forceinline__ uint32_t hadd2_bits(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
 }
 
 // ---- packed FP32 pairs (sm_100 executes fma/add/mul on two floats per instruction) ----

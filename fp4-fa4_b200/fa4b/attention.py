@@ -47,7 +47,14 @@ class Workspace:
         d = self.dims
         nq, nk, S, D = d.B * d.Hq, d.B * d.Hkv, d.S, d.D
         L = self.layout
-        return {
+        ops = {}
+        if d.pv_format == PV_FORMATS["mxfp4_e8m0_block32"]:
+            # the V section then holds sequence-grouped MXFP4: codes [B,Hkv,D,S/2], then (1024-aligned) E8M0 pages
+            n_codes = nk * D * S // 2
+            pages_at = L.v_fp8 + (n_codes + 1023) // 1024 * 1024
+            ops["v_mx_codes"] = self._view(L.v_fp8, n_codes).view(d.B, d.Hkv, D, S // 2)
+            ops["v_mx_scales"] = self._view(pages_at, nk * (S // 128) * 512).view(d.B, d.Hkv, S // 128, 512)
+        return ops | {
             "q_codes": self._view(L.q_codes, nq * S * D // 2).view(d.B, d.Hq, S, D // 2),
             "q_scales": self._view(L.q_scales, nq * (S // 128) * (D // 64) * 512).view(d.B, d.Hq, S // 128, D // 64, 512),
             "q_global": self._view(L.q_global, nq * 4).view(torch.float32).view(d.B, d.Hq),

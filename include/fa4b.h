@@ -153,7 +153,10 @@ typedef struct fa4b_strides {
 
 size_t fa4b_attn_workspace_bytes(const fa4b_attn_dims* d);
 
-/* Offsets (bytes) of the cached operands inside the workspace. */
+/* Offsets (bytes) of the cached operands inside the workspace.  With pv_format = FA4B_PV_MXFP4_E8M0 the
+ * `v_fp8` section holds V as sequence-grouped MXFP4 instead (the operand of forward_hao_direct_fp4pv,
+ * hao_direct_fp4pv_host.inc:1141-1237): codes [B*Hkv, D, S/2] (two keys per byte, feature-major), then at the
+ * next multiple of 1024 bytes the E8M0 scale pages [B*Hkv, S/128, 512] (row = feature, k-block = 32 keys). */
 typedef struct fa4b_attn_ws_layout {
   size_t q_codes, q_scales, q_global, k_codes, k_scales, k_global;
   size_t v_fp8, q_fp8, k_fp8, do_fp8, dstat, lstat, dq_accum, amax_bits, status, total;
@@ -178,7 +181,8 @@ int fa4b_attn_prepare(const fa4b_attn_prepare_args* a, void* stream);
  * forward_hao_direct_fp8pv / forward_hao_direct_fp4pv
  * (tk_fa4/fp4_fa4_fwd/hao_direct_host.inc:263-275, 511-521;
  * hao_direct_fp4pv_host.inc:1141-1237).  Calls fa4b_attn_prepare first unless
- * `prepared` is non-zero. */
+ * `prepared` is non-zero.  The MXFP4 P.V route quantises P to MXFP4 in 32-key groups (E8M0, ceil) inside the
+ * kernel, takes the row sum over the represented P, and is forward only (fa4b_attn_bwd returns FA4B_UNSUPPORTED). */
 typedef struct fa4b_attn_fwd_args {
   fa4b_attn_dims dims;
   const void* q; fa4b_strides q_strides;

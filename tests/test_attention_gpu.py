@@ -158,3 +158,38 @@ def test_partition_by_batch_and_kv_head_reproduces_the_unsharded_run():
     assert torch.equal(parallel.unshard_kv_like(parts["dk"], B, Hkv), dk)
     assert torch.equal(parallel.unshard_kv_like(parts["dv"], B, Hkv), dv)
     assert O.rel_l2(dq.float().cpu(), parallel.unshard_q_like(parts["dq"], B, Hq).float().cpu()) < 1e-3
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,S,D", [(1, 4, 1, 256, 128), (1, 4, 4, 512, 64), (2, 8, 2, 384, 128)])
+def test_forward_mxfp4_pv_route_matches_oracle(B, Hq, Hkv, S, D):
+    """The diagnostic route: P as MXFP4 in 32-key groups (E8M0, ceil), V as sequence-grouped MXFP4 (cut-off
+    exponent), row sum over the represented P.  V codes and scale pages bit-exact; O and LSE as the FP8 route."""
+    q, k, v, _ = O.make_attention_inputs(B, Hq, Hkv, S, D, seed=20260901 + S + D, rope=(D == 128))
+    fwd = O.attn_forward(q, k, v, pv_format="mxfp4_e8m0_block32")
+    o, lse, ws = attention.attn_forward(q.to(DEV), k.to(DEV), v.to(DEV), pv_format="mxfp4_e8m0_block32")
+    ws.check_status()
+    codes, scales, _ = O.mxfp4_v_sequence(v)
+    ops = ws.operands()
+    assert torch.equal(ops["v_mx_codes"].cpu(), codes)
+    # pages: row = feature, k-block = 32-key group within the 128-key tile
+    want_pages = torch.zeros(B, Hkv, S // 128, 512, dtype=torch.uint8)
+    d_idx = torch.arange(D)
+    for kb in range(4):
+        off = (d_idx % 32) * 16 + ((d_idx % 128) // 32) * 4 + kb
+        want_pages[..., off] = scales.reshape(B, Hkv, D, S // 128, 4)[..., kb].permute(0, 1, 3, 2)
+    assert torch.equal(ops["v_mx_scales"].cpu(), want_pages)
+    torch.cuda.synchronize()
+    assert O.rel_l2(fwd.o, o.cpu()) < 1e-2, O.rel_l2(fwd.o, o.cpu())
+    # LSE: the row sum is over FP4-represented probabilities, so where the 2-ulp ex2.approx lands on the other side of
+    # an E2M1 rounding boundary than the oracle's exp2, one term of one row moves by up to two code steps.  Such rows
+    # are rare (boundary hits at 1e-7 relative distance); all others meet the 1e-3 bound of the FP8 route.
+    err = (fwd.lse - lse.cpu()).abs()
+    assert O.rel_l2(fwd.lse, lse.cpu()) < 1e-2
+    assert (err > 1e-3).float().mean() < 1e-3 and err.max() < 0.5, (float((err > 1e-3).float().mean()), float(err.max()))
+
+
+def test_backward_refuses_the_forward_only_mxfp4_route():
+    q, k, v, do = (t.to(DEV) for t in O.make_attention_inputs(1, 4, 1, 256, 128, seed=3))
+    o, lse, ws = attention.attn_forward(q, k, v, pv_format="mxfp4_e8m0_block32")
+    with pytest.raises(Exception, match="forward only"):
+        attention.attn_backward(o, lse, do, ws)
