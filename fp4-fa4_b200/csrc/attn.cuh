@@ -21,6 +21,7 @@ inline int check_dims(const fa4b_attn_dims& d) {
   FA4B_REQUIRE(d.Hq % d.Hkv == 0, FA4B_BAD_SHAPE, "Hq=%d must be a multiple of Hkv=%d", d.Hq, d.Hkv);
   FA4B_REQUIRE(d.pv_format == FA4B_PV_FP8_E4M3 || d.pv_format == FA4B_PV_MXFP4_E8M0, FA4B_UNSUPPORTED, "unknown pv_format %d",
                d.pv_format);
+  FA4B_REQUIRE(d.mask == FA4B_MASK_CAUSAL || d.mask == FA4B_MASK_NONE, FA4B_UNSUPPORTED, "unknown mask %d", d.mask);
   return FA4B_OK;
 }
 
@@ -64,5 +65,7 @@ int launch_attn_prepare(const fa4b_attn_prepare_args& a, cudaStream_t st);
 int launch_attn_fwd(const fa4b_attn_fwd_args& a, cudaStream_t st);
 int launch_attn_bwd_preprocess(const fa4b_attn_bwd_args& a, cudaStream_t st);
 int launch_attn_bwd(const fa4b_attn_bwd_args& a, cudaStream_t st);
+int launch_attn_merge(float* o_acc, float* lse_acc, const void* o_part, const float* lse_part, int64_t n_rows, int D, void* o_out,
+                      cudaStream_t st);
 
 }  // namespace fa4b

@@ -48,3 +48,8 @@ extern "C" int fa4b_attn_bwd(const fa4b_attn_bwd_args* a, void* stream) {
   FA4B_REQUIRE(a != nullptr, FA4B_BAD_ARG, "args is NULL");
   return launch_attn_bwd(*a, static_cast<cudaStream_t>(stream));
 }
+
+extern "C" int fa4b_attn_merge(float* o_acc, float* lse_acc, const void* o_part, const float* lse_part, int64_t n_rows, int32_t D,
+                               void* o_out, void* stream) {
+  return launch_attn_merge(o_acc, lse_acc, o_part, lse_part, n_rows, D, o_out, static_cast<cudaStream_t>(stream));
+}

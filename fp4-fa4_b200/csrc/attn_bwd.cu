@@ -716,6 +716,7 @@ static int check_out(const void* ptr, const fa4b_strides& s, const char* name) {
 
 int launch_attn_bwd(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   if (int s = check_dims(a.dims)) return s;
+  FA4B_REQUIRE(a.dims.mask == FA4B_MASK_CAUSAL, FA4B_UNSUPPORTED, "the backward is causal only");
   FA4B_REQUIRE(a.dims.pv_format == FA4B_PV_FP8_E4M3, FA4B_UNSUPPORTED, "the MXFP4 P.V route is forward only (a diagnostic route in the reference as well)");
   if (int s = check_out(a.dq, a.dq_strides, "dq")) return s;
   if (int s = check_out(a.dk, a.dk_strides, "dk")) return s;

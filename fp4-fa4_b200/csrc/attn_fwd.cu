@@ -48,6 +48,7 @@ struct FwdSmem {
 
 struct FwdParams {
   int B, Hq, Hkv, S;
+  int causal;  // 0: every key is visible to every query (an off-diagonal block of a sequence-sharded run)
   const uint8_t* v_sf;  // MXFP4 route: V scale pages [B*Hkv, S/128, 512]
   float scale_log2;  // softmax_scale * log2(e)
   const uint8_t* q_sf;
@@ -102,8 +103,8 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
   const int b = bh / p.Hq, h = bh % p.Hq;
   const int bhk = b * p.Hkv + h / (p.Hq / p.Hkv);
   // 64-key blocks each tile attends to (tile T sees keys < 128 T + 128); the odd tile may not exist
-  const int nb0 = 2 * (2 * pi) + 2;
-  const int nb1 = (2 * pi + 1 < n_tiles) ? 2 * (2 * pi + 1) + 2 : 0;
+  const int nb0 = p.causal ? 2 * (2 * pi) + 2 : 2 * n_tiles;
+  const int nb1 = (2 * pi + 1 < n_tiles) ? (p.causal ? 2 * (2 * pi + 1) + 2 : 2 * n_tiles) : 0;
   const int nbmax = nb0 > nb1 ? nb0 : nb1;
   const int n_stages = (nbmax + 1) / 2;
   {
@@ -182,7 +183,7 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       for (int j = issued > kStages ? issued - kStages : 0; j < issued; ++j) {
         mbar_wait_teardown(&s.kv_full[j % kStages], (j / kStages) & 1);
         if (issued == n_stages && !s.abort_flag) {
-          if (j < (nb0 + 1) / 2) mbar_wait_teardown(&s.kv_empty[0][j % kStages], (j / kStages) & 1);
+          if (j < (nb0 + 1) / 2) mbar_wait_teardown(&s.kv_empty[0][j % kStages], (j / kStages) & 1);  // tile 0 may use one stage less
           if (nb1) mbar_wait_teardown(&s.kv_empty[1][j % kStages], (j / kStages) & 1);
         }
       }
@@ -326,7 +327,7 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 3);
       // keys of this block that lie after the query row (only in the tile's last two blocks)
       const int lim = qt * 128 + row - 64 * j;  // columns <= lim are visible
-      const bool diag = j >= 2 * qt;            // warp-uniform
+      const bool diag = p.causal && j >= 2 * qt;  // warp-uniform
       // c2 >= 0: the maximum of the scaled scores is the scaled maximum of the raw ones
       float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
       if (diag) {
@@ -532,22 +533,25 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   const fa4b_attn_dims& d = a.dims;
   const fa4b_attn_ws_layout l = make_ws_layout(d);
   uint8_t* ws = static_cast<uint8_t*>(a.ws);
+  // K and V operands may come from a second cache of the same layout (another sequence shard)
+  uint8_t* kvws = a.kv_ws ? static_cast<uint8_t*>(const_cast<void*>(a.kv_ws)) : ws;
   CUtensorMap mq, mk, mv;
   const uint64_t S = d.S;
   if (int s = make_tensor_map(&mq, ws + l.q_codes, 1, D / 2, S, (uint64_t)d.B * d.Hq, D / 2, S * (D / 2), D / 2, 128)) return s;
-  if (int s = make_tensor_map(&mk, ws + l.k_codes, 1, D / 2, S, (uint64_t)d.B * d.Hkv, D / 2, S * (D / 2), D / 2, 128)) return s;
+  if (int s = make_tensor_map(&mk, kvws + l.k_codes, 1, D / 2, S, (uint64_t)d.B * d.Hkv, D / 2, S * (D / 2), D / 2, 128)) return s;
   if (MX) {  // codes [B*Hkv][D][S/2]: a stage is D rows x 64 bytes (128 keys)
-    if (int s = make_tensor_map(&mv, ws + l.v_fp8, 1, S / 2, D, (uint64_t)d.B * d.Hkv, S / 2, (uint64_t)D * (S / 2), 64, D)) return s;
+    if (int s = make_tensor_map(&mv, kvws + l.v_fp8, 1, S / 2, D, (uint64_t)d.B * d.Hkv, S / 2, (uint64_t)D * (S / 2), 64, D)) return s;
   } else {
-    if (int s = make_tensor_map(&mv, ws + l.v_fp8, 1, D, S, (uint64_t)d.B * d.Hkv, D, S * D, D, 128)) return s;
+    if (int s = make_tensor_map(&mv, kvws + l.v_fp8, 1, D, S, (uint64_t)d.B * d.Hkv, D, S * D, D, 128)) return s;
   }
   FwdParams p{};
   p.B = d.B; p.Hq = d.Hq; p.Hkv = d.Hkv; p.S = d.S;
   p.scale_log2 = resolve_scale(d) * kLog2e;
-  p.q_sf = ws + l.q_scales; p.k_sf = ws + l.k_scales;
-  p.v_sf = ws + l.v_fp8 + v_mx_pages_offset(d);
+  p.causal = d.mask == FA4B_MASK_CAUSAL;
+  p.q_sf = ws + l.q_scales; p.k_sf = kvws + l.k_scales;
+  p.v_sf = kvws + l.v_fp8 + v_mx_pages_offset(d);
   p.q_global = reinterpret_cast<const float*>(ws + l.q_global);
-  p.k_global = reinterpret_cast<const float*>(ws + l.k_global);
+  p.k_global = reinterpret_cast<const float*>(kvws + l.k_global);
   p.o = static_cast<__nv_bfloat16*>(a.o);
   p.o_sb = a.o_strides.batch; p.o_sh = a.o_strides.head; p.o_ss = a.o_strides.seq;
   p.lse = a.lse;
@@ -579,6 +583,8 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
 int launch_attn_fwd(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   if (int s = check_dims(a.dims)) return s;
   FA4B_REQUIRE(a.o && a.lse && a.ws, FA4B_BAD_ARG, "o, lse and ws are required");
+  FA4B_REQUIRE(!a.kv_ws || (a.prepared && (reinterpret_cast<uintptr_t>(a.kv_ws) & 1023) == 0), FA4B_BAD_ARG,
+               "kv_ws needs prepared != 0 and 1024-byte alignment");
   FA4B_REQUIRE((reinterpret_cast<uintptr_t>(a.o) & 15) == 0 && a.o_strides.batch % 8 == 0 && a.o_strides.head % 8 == 0 &&
                    a.o_strides.seq % 8 == 0,
                FA4B_BAD_ALIGN, "o: base must be 16-byte aligned and strides multiples of 8 elements");

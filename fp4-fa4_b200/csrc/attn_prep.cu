@@ -208,6 +208,71 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(HeadView o, HeadVie
   }
 }
 
+// Fold a partial attention result into a running one (rows of D values, D / 8 threads per row):
+// lse' = log(e^lse_acc + e^lse_part), o' = o_acc e^(lse_acc - lse') + o_part e^(lse_part - lse').
+template <int D>
+__global__ void __launch_bounds__(256) merge_kernel(float* __restrict__ o_acc, float* __restrict__ lse_acc,
+                                                    const __nv_bfloat16* __restrict__ o_part, const float* __restrict__ lse_part,
+                                                    int64_t n_rows, __nv_bfloat16* __restrict__ o_out) {
+  constexpr int kLanes = D / 8;
+  const int64_t row = (int64_t)blockIdx.x * (256 / kLanes) + threadIdx.x / kLanes;
+  const int c = threadIdx.x % kLanes;
+  float la = -INFINITY, lp = -INFINITY;
+  if (row < n_rows) {
+    la = lse_acc[row];
+    lp = lse_part[row];
+  }
+  const float m = fmaxf(la, lp);
+  float ln = m, wa = 0.f, wp = 0.f;
+  if (m > -INFINITY) {
+    const float ea = __expf(la - m), ep = __expf(lp - m);
+    ln = m + __logf(ea + ep);
+    wa = ea / (ea + ep);
+    wp = ep / (ea + ep);
+  }
+  __syncwarp();  // every lane of the row has read lse_acc before one of them replaces it
+  if (row < n_rows) {
+    float* oa = o_acc + row * D + c * 8;
+    const float4 a0 = *reinterpret_cast<const float4*>(oa), a1 = *reinterpret_cast<const float4*>(oa + 4);
+    const uint4 pv = __ldg(reinterpret_cast<const uint4*>(o_part + row * D + c * 8));
+    const uint32_t w[4] = {pv.x, pv.y, pv.z, pv.w};
+    float r[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      r[2 * k] = r[2 * k] * wa + bf16_bits_to_f32(w[k] & 0xffffu) * wp;
+      r[2 * k + 1] = r[2 * k + 1] * wa + bf16_bits_to_f32(w[k] >> 16) * wp;
+    }
+    *reinterpret_cast<float4*>(oa) = make_float4(r[0], r[1], r[2], r[3]);
+    *reinterpret_cast<float4*>(oa + 4) = make_float4(r[4], r[5], r[6], r[7]);
+    if (o_out) {
+      uint32_t ow[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(r[2 * k], r[2 * k + 1]);
+        ow[k] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(o_out + row * D + c * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+    if (c == 0) lse_acc[row] = ln;
+  }
+}
+
+int launch_attn_merge(float* o_acc, float* lse_acc, const void* o_part, const float* lse_part, int64_t n_rows, int D, void* o_out,
+                      cudaStream_t st) {
+  FA4B_REQUIRE(o_acc && lse_acc && o_part && lse_part, FA4B_BAD_ARG, "fa4b_attn_merge: NULL pointer");
+  FA4B_REQUIRE(n_rows > 0 && (D == 64 || D == 128), FA4B_BAD_SHAPE, "fa4b_attn_merge: n_rows must be positive and D 64 or 128");
+  FA4B_REQUIRE(((reinterpret_cast<uintptr_t>(o_acc) | reinterpret_cast<uintptr_t>(o_part) | reinterpret_cast<uintptr_t>(o_out)) & 15) == 0,
+               FA4B_BAD_ALIGN, "fa4b_attn_merge: 16-byte alignment");
+  const int rows_per_cta = 256 / (D / 8);
+  const unsigned grid = (unsigned)((n_rows + rows_per_cta - 1) / rows_per_cta);
+  const auto* op = static_cast<const __nv_bfloat16*>(o_part);
+  auto* oo = static_cast<__nv_bfloat16*>(o_out);
+  if (D == 128) merge_kernel<128><<<grid, 256, 0, st>>>(o_acc, lse_acc, op, lse_part, n_rows, oo);
+  else merge_kernel<64><<<grid, 256, 0, st>>>(o_acc, lse_acc, op, lse_part, n_rows, oo);
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
+}
+
 static int check_view(const void* p, const fa4b_strides& s, const char* name) {
   FA4B_REQUIRE(p != nullptr, FA4B_BAD_ARG, "%s is NULL", name);
   FA4B_REQUIRE((reinterpret_cast<uintptr_t>(p) & 15) == 0 && s.batch % 8 == 0 && s.head % 8 == 0 && s.seq % 8 == 0, FA4B_BAD_ALIGN,
@@ -226,12 +291,16 @@ static int prepare_impl(const fa4b_attn_prepare_args& a, cudaStream_t st) {
   uint8_t* ws = static_cast<uint8_t*>(a.ws);
   const int nq = d.B * d.Hq, nk = d.B * d.Hkv;
   int* amax_bits = reinterpret_cast<int*>(ws + l.amax_bits);
-  FA4B_CUDA(cudaMemsetAsync(amax_bits, 0, (size_t)(nq + nk) * 4, st));
-  const int rows_per_cta = 512;
-  const unsigned chunks = (unsigned)((d.S + rows_per_cta - 1) / rows_per_cta);
   const HeadView q = view(a.q, a.q_strides, d.Hq), k = view(a.k, a.k_strides, d.Hkv), v = view(a.v, a.v_strides, d.Hkv);
-  head_amax_kernel<D><<<dim3(chunks, nq), 256, 0, st>>>(q, d.S, rows_per_cta, amax_bits);
-  head_amax_kernel<D><<<dim3(chunks, nk), 256, 0, st>>>(k, d.S, rows_per_cta, amax_bits + nq);
+  if (a.phase != FA4B_PREPARE_QUANTIZE) {
+    FA4B_CUDA(cudaMemsetAsync(amax_bits, 0, (size_t)(nq + nk) * 4, st));
+    const int rows_per_cta = 512;
+    const unsigned chunks = (unsigned)((d.S + rows_per_cta - 1) / rows_per_cta);
+    head_amax_kernel<D><<<dim3(chunks, nq), 256, 0, st>>>(q, d.S, rows_per_cta, amax_bits);
+    head_amax_kernel<D><<<dim3(chunks, nk), 256, 0, st>>>(k, d.S, rows_per_cta, amax_bits + nq);
+    FA4B_CUDA(cudaGetLastError());
+    if (a.phase == FA4B_PREPARE_AMAX) return FA4B_OK;
+  }
   quant_heads_kernel<D><<<dim3(d.S / 128, nq), 256, 0, st>>>(q, d.S, amax_bits, ws + l.q_codes, ws + l.q_scales,
                                                              reinterpret_cast<float*>(ws + l.q_global), ws + l.q_fp8);
   quant_heads_kernel<D><<<dim3(d.S / 128, nk), 256, 0, st>>>(k, d.S, amax_bits + nq, ws + l.k_codes, ws + l.k_scales,
@@ -253,6 +322,7 @@ int launch_attn_prepare(const fa4b_attn_prepare_args& a, cudaStream_t st) {
   if (int s = check_view(a.q, a.q_strides, "q")) return s;
   if (int s = check_view(a.k, a.k_strides, "k")) return s;
   if (int s = check_view(a.v, a.v_strides, "v")) return s;
+  FA4B_REQUIRE(a.phase >= FA4B_PREPARE_ALL && a.phase <= FA4B_PREPARE_QUANTIZE, FA4B_BAD_ARG, "unknown prepare phase %d", a.phase);
   FA4B_REQUIRE(a.ws != nullptr && (reinterpret_cast<uintptr_t>(a.ws) & 1023) == 0, FA4B_BAD_ALIGN,
                "workspace must be non-NULL and 1024-byte aligned");
   return a.dims.D == 128 ? prepare_impl<128>(a, st) : prepare_impl<64>(a, st);

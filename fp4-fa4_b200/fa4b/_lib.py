@@ -41,7 +41,7 @@ class QuantMxfp4Args(C.Structure):
 
 class AttnDims(C.Structure):
     _fields_ = [("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("S", C.c_int32), ("D", C.c_int32),
-                ("softmax_scale", C.c_float), ("pv_format", C.c_int32)]
+                ("softmax_scale", C.c_float), ("pv_format", C.c_int32), ("mask", C.c_int32)]
 
 
 class Strides(C.Structure):
@@ -56,14 +56,14 @@ class WsLayout(C.Structure):
 
 class AttnPrepareArgs(C.Structure):
     _fields_ = [("dims", AttnDims), ("q", C.c_void_p), ("q_strides", Strides), ("k", C.c_void_p), ("k_strides", Strides),
-                ("v", C.c_void_p), ("v_strides", Strides), ("ws", C.c_void_p)]
+                ("v", C.c_void_p), ("v_strides", Strides), ("ws", C.c_void_p), ("phase", C.c_int32)]
 
 
 class AttnFwdArgs(C.Structure):
     _fields_ = [("dims", AttnDims), ("q", C.c_void_p), ("q_strides", Strides), ("k", C.c_void_p), ("k_strides", Strides),
                 ("v", C.c_void_p), ("v_strides", Strides), ("o", C.c_void_p), ("o_strides", Strides),
                 ("lse", C.c_void_p), ("ws", C.c_void_p), ("prepared", C.c_int32), ("ev_before", C.c_void_p),
-                ("ev_after", C.c_void_p)]
+                ("ev_after", C.c_void_p), ("kv_ws", C.c_void_p)]
 
 
 class AttnBwdArgs(C.Structure):
@@ -83,7 +83,7 @@ EXPORTS = (
     "fa4b_status_string", "fa4b_last_error", "fa4b_query", "fa4b_amax", "fa4b_quant_nvfp4",
     "fa4b_rmsnorm_quant_nvfp4", "fa4b_quant_mxfp4", "fa4b_dequant_nvfp4", "fa4b_dequant_mxfp4",
     "fa4b_attn_workspace_bytes", "fa4b_attn_ws_layout_query", "fa4b_attn_prepare", "fa4b_attn_fwd",
-    "fa4b_attn_fwd_static", "fa4b_attn_bwd_preprocess", "fa4b_attn_bwd", "fa4b_attn_check_status", "fa4b_microgate", "fa4b_tensor_peak",
+    "fa4b_attn_fwd_static", "fa4b_attn_bwd_preprocess", "fa4b_attn_bwd", "fa4b_attn_check_status", "fa4b_attn_merge", "fa4b_microgate", "fa4b_tensor_peak",
 )
 
 _lib = None

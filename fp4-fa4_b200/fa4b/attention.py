@@ -69,16 +69,27 @@ class Workspace:
             "lstat": self._view(L.lstat, nq * S * 4).view(torch.float32).view(d.B, d.Hq, S),
         }
 
+    def amax(self) -> torch.Tensor:
+        """The per-(batch, head) amax words of q (B*Hq) then k (B*Hkv), f32, as a view."""
+        d = self.dims
+        return self._view(self.layout.amax_bits, (d.B * d.Hq + d.B * d.Hkv) * 4).view(torch.float32)
+
+    def kv_bytes(self) -> torch.Tensor:
+        """The K and V operands (codes, scale pages, global scales, V) as one contiguous byte range: what a
+        sequence-sharded run sends to the next rank."""
+        return self._view(self.layout.k_codes, self.layout.q_fp8 - self.layout.k_codes)
+
     def check_status(self) -> None:
         check(lib().fa4b_attn_check_status(C.byref(self.dims), C.c_void_p(ptr(self.buf)), C.c_void_p(current_stream())),
               "fa4b_attn_check_status")
 
 
-def make_dims(q: torch.Tensor, k: torch.Tensor, softmax_scale: float | None, pv_format: str) -> _lib.AttnDims:
+def make_dims(q: torch.Tensor, k: torch.Tensor, softmax_scale: float | None, pv_format: str, causal: bool = True) -> _lib.AttnDims:
     if pv_format not in PV_FORMATS:
         raise ValueError(f"unknown pv_format {pv_format!r}; expected one of {sorted(PV_FORMATS)}")
     B, Hq, S, D = q.shape
-    return _lib.AttnDims(B, Hq, k.shape[1], S, D, float(softmax_scale) if softmax_scale else 0.0, PV_FORMATS[pv_format])
+    return _lib.AttnDims(B, Hq, k.shape[1], S, D, float(softmax_scale) if softmax_scale else 0.0, PV_FORMATS[pv_format],
+                         0 if causal else 1)
 
 
 def alloc_workspace(dims: _lib.AttnDims, device) -> Workspace:
@@ -111,10 +122,43 @@ def attn_forward(q, k, v, softmax_scale: float | None = None, pv_format: str = "
     return o, lse, ws
 
 
-def attn_prepare(q, k, v, ws: Workspace) -> None:
-    """Publish the quantised operands of q, k, v into ``ws`` (the first half of :func:`attn_forward`)."""
-    a = _lib.AttnPrepareArgs(ws.dims, ptr(q), _strides(q), ptr(k), _strides(k), ptr(v), _strides(v), ptr(ws.buf))
+PREPARE_PHASES = {"all": 0, "amax": 1, "quantize": 2}
+
+
+def attn_prepare(q, k, v, ws: Workspace, phase: str = "all") -> None:
+    """Publish the quantised operands of q, k, v into ``ws`` (the first half of :func:`attn_forward`).
+    ``phase="amax"`` only fills the per-(batch, head) amax words (``ws.amax()``), ``phase="quantize"`` publishes
+    with the words found there: a sequence-sharded caller maximises them over shards and ranks in between."""
+    a = _lib.AttnPrepareArgs(ws.dims, ptr(q), _strides(q), ptr(k), _strides(k), ptr(v), _strides(v), ptr(ws.buf), PREPARE_PHASES[phase])
     check(lib().fa4b_attn_prepare(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_prepare")
+
+
+def attn_forward_prepared(ws: Workspace, kv_ws: Workspace | None = None, causal: bool = True):
+    """Forward on operands already published: queries from ``ws``, keys and values from ``kv_ws`` (default ``ws``).
+    ``causal=False`` lets every query see every key (an off-diagonal block of a sequence-sharded run)."""
+    d = ws.dims
+    dims = _lib.AttnDims(d.B, d.Hq, d.Hkv, d.S, d.D, d.softmax_scale, d.pv_format, 0 if causal else 1)
+    dev = ws.buf.device
+    o = torch.empty(d.B, d.Hq, d.S, d.D, dtype=torch.bfloat16, device=dev)
+    lse = torch.empty(d.B, d.Hq, d.S, dtype=torch.float32, device=dev)
+    z = _lib.Strides()
+    a = _lib.AttnFwdArgs(dims, 0, z, 0, z, 0, z, ptr(o), _strides(o), ptr(lse), ptr(ws.buf), 1, 0, 0,
+                         ptr(kv_ws.buf) if kv_ws is not None else 0)
+    check(lib().fa4b_attn_fwd(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_fwd")
+    return o, lse
+
+
+def attn_merge(o_acc: torch.Tensor, lse_acc: torch.Tensor, o_part: torch.Tensor, lse_part: torch.Tensor, out: torch.Tensor | None = None):
+    """Fold the partial result ``(o_part bf16, lse_part)`` into the running ``(o_acc f32, lse_acc)`` in place; with
+    ``out`` (bf16) also write the merged rows there."""
+    D = o_acc.shape[-1]
+    n_rows = o_acc.numel() // D
+    for t in (o_acc, lse_acc, o_part, lse_part) + ((out,) if out is not None else ()):
+        if not t.is_contiguous():
+            raise ValueError("attn_merge needs contiguous tensors")
+    check(lib().fa4b_attn_merge(C.c_void_p(ptr(o_acc)), C.c_void_p(ptr(lse_acc)), C.c_void_p(ptr(o_part)), C.c_void_p(ptr(lse_part)),
+                                C.c_int64(n_rows), C.c_int32(D), C.c_void_p(ptr(out) if out is not None else 0),
+                                C.c_void_p(current_stream())), "fa4b_attn_merge")
 
 
 def attn_backward(o, lse, dout, ws: Workspace, preprocessed: bool = False, events=(None, None)):

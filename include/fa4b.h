@@ -38,7 +38,9 @@ const char* fa4b_last_error(void);
 
 /* ---- formats and modes ------------------------------------------------- */
 enum { FA4B_PV_FP8_E4M3 = 0, FA4B_PV_MXFP4_E8M0 = 1 };  /* fa4.exact_pv_format */
+enum { FA4B_MASK_CAUSAL = 0, FA4B_MASK_NONE = 1 };
 enum { FA4B_MX_CEIL = 0, FA4B_MX_RTE_MANTISSA = 1, FA4B_MX_FLOOR = 2 };
+enum { FA4B_PREPARE_ALL = 0, FA4B_PREPARE_AMAX = 1, FA4B_PREPARE_QUANTIZE = 2 };
 enum { FA4B_LAYOUT_BHSD = 0, FA4B_LAYOUT_BSHD = 1 };
 
 /* ---- fa4b_query --------------------------------------------------------
@@ -145,6 +147,8 @@ typedef struct fa4b_attn_dims {
   int32_t B, Hq, Hkv, S, D;
   float softmax_scale; /* <= 0: 1/sqrt(D) */
   int32_t pv_format;   /* FA4B_PV_* */
+  int32_t mask;        /* FA4B_MASK_*; forward only.  FA4B_MASK_NONE serves the off-diagonal blocks of a
+                          sequence-sharded (context-parallel) run, where every key precedes every query */
 } fa4b_attn_dims;
 
 typedef struct fa4b_strides {
@@ -174,6 +178,11 @@ typedef struct fa4b_attn_prepare_args {
   const void* k; fa4b_strides k_strides;
   const void* v; fa4b_strides v_strides;
   void* ws;
+  int32_t phase; /* 0: everything.  FA4B_PREPARE_AMAX: only the per-(batch, head) amax words of q and k
+                    (fa4b_attn_ws_layout.amax_bits: B*Hq then B*Hkv f32).  FA4B_PREPARE_QUANTIZE: publish with
+                    the amax words already in `ws` -- a caller that shards the sequence across GPUs takes the
+                    maximum of the words over its shards and ranks between the two phases, so that every
+                    shard is quantised with the scale of the whole sequence */
 } fa4b_attn_prepare_args;
 int fa4b_attn_prepare(const fa4b_attn_prepare_args* a, void* stream);
 
@@ -194,8 +203,20 @@ typedef struct fa4b_attn_fwd_args {
   int32_t prepared;
   void* ev_before; /* optional cudaEvent_t recorded just before / after the */
   void* ev_after;  /* attention kernel itself (per-kernel timing)           */
+  const void* kv_ws; /* optional: a second operand cache of the same dims whose K and V sections (k_codes up to
+                        q_fp8 of the layout, one contiguous range) are used instead of `ws`'s; with prepared != 0
+                        this is how a block of queries meets the keys of another sequence shard */
 } fa4b_attn_fwd_args;
 int fa4b_attn_fwd(const fa4b_attn_fwd_args* a, void* stream);
+
+/* fa4b_attn_merge: fold one partial result into a running one, row by row (n_rows = B*Hq*S rows of D values):
+ * lse' = log(exp(lse_acc) + exp(lse_part)), o_acc' = o_acc exp(lse_acc - lse') + o_part exp(lse_part - lse').
+ * o_acc f32 [n_rows, D] and lse_acc f32 [n_rows] are updated in place (start from o_acc = 0, lse_acc = -inf);
+ * o_part is the bf16 [n_rows, D] output of fa4b_attn_fwd on one key shard, lse_part its LSE.  With o_out != NULL
+ * the merged rows are also written as bf16 (the last fold).  The reference has no counterpart (it runs
+ * data-parallel replicas only, torchtitan/experiments/fa4/exact_lowp_attention.py:4123-4136). */
+int fa4b_attn_merge(float* o_acc, float* lse_acc, const void* o_part, const float* lse_part, int64_t n_rows, int32_t D,
+                    void* o_out, void* stream);
 
 /* fa4b_attn_fwd_static: fa4b_attn_fwd for hosts that cannot allocate device
  * memory where attention runs (an execute hook that must not allocate, a

@@ -1,0 +1,119 @@
+"""The context-parallel ring schedule on two and three CPU ranks over gloo, with the oracle standing in for the
+kernels: zig-zag sharding, whole-sequence amax, the block calls causality leaves, and the log-sum-exp merge must
+reproduce the single-device oracle (bf16 rounding of the partial results is the only difference)."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import fa4b_oracle as O
+from fa4b import context_parallel as cp
+
+
+class OracleEngine:
+    """CPU stand-in with the interface of context_parallel.KernelEngine."""
+
+    def __init__(self, scale, pv_format="e4m3_fp8"):
+        self.scale, self.pv = scale, pv_format
+
+    def amax(self, q, k, v):
+        st = {"q": q, "k": k, "v": v}
+        am = torch.cat([q.float().abs().amax(dim=(2, 3)).reshape(-1), k.float().abs().amax(dim=(2, 3)).reshape(-1)])
+        return st, am
+
+    def publish(self, q, k, v, st, amax):
+        B, Hq, Hkv = q.shape[0], q.shape[1], k.shape[1]
+        qd = O.quantize_qk_heads(q, amax[:B * Hq].reshape(B, Hq))[3]
+        kd = O.quantize_qk_heads(k, amax[B * Hq:].reshape(B, Hkv))[3]
+        vd = O.fp8_operand(v).float() if self.pv == "e4m3_fp8" else O.mxfp4_v_sequence(v)[2]
+        return {"qd": qd, "kv": torch.cat([kd.reshape(-1), vd.reshape(-1)]).contiguous(), "kshape": tuple(kd.shape)}
+
+    def kv_payload(self, ws):
+        return ws["kv"]
+
+    def empty_like_chunk(self, ws):
+        return {"qd": None, "kv": torch.empty_like(ws["kv"]), "kshape": ws["kshape"]}
+
+    def block(self, ws_q, ws_kv, causal):
+        n = ws_kv["kv"].numel() // 2
+        kd, vd = ws_kv["kv"][:n].reshape(ws_kv["kshape"]), ws_kv["kv"][n:].reshape(ws_kv["kshape"])
+        return O.attn_forward_operands(ws_q["qd"], kd, vd, self.scale, self.pv, causal=causal)
+
+    def new_acc(self, ws):
+        qd = ws["qd"]
+        return [torch.zeros_like(qd), torch.full(qd.shape[:3], float("-inf"))]
+
+    def merge(self, acc, part):
+        o_p, l_p = part[0].float(), part[1]
+        m = torch.maximum(acc[1], l_p)
+        ea, ep = torch.exp(acc[1] - m), torch.exp(l_p - m)
+        acc[0] = acc[0] * (ea / (ea + ep))[..., None] + o_p * (ep / (ea + ep))[..., None]
+        acc[1] = m + torch.log(ea + ep)
+
+    def finish(self, acc):
+        return acc[0].bfloat16(), acc[1]
+
+
+def test_schedule_covers_every_causal_block_once():
+    for world in (1, 2, 3, 8):
+        seen = set()
+        for rank in range(world):
+            chunks = cp.zigzag_chunks(rank, world)
+            per_step = []
+            for src in range(world):
+                calls = cp.block_schedule(rank, src, world)
+                per_step.append(len(calls))
+                for qi, ki, causal in calls:
+                    qc, kc = chunks[qi], cp.zigzag_chunks(src, world)[ki]
+                    assert (kc == qc) == causal and kc <= qc
+                    assert (qc, kc) not in seen
+                    seen.add((qc, kc))
+            assert all(n in (2, 3) for n in per_step)  # balanced: two block calls per hop, three on the home shard
+        n = 2 * world
+        assert seen == {(a, b) for a in range(n) for b in range(a + 1)}
+    x = torch.arange(2 * 3 * 12 * 2).reshape(2, 3, 12, 2)
+    assert torch.equal(cp.unshard_sequence([cp.shard_sequence(x, r, 3) for r in range(3)]), x)
+
+
+def _worker(rank, world, port, pv, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(2)
+        B, Hq, Hkv, D = 1, 2, 1, 64
+        S = 128 * 2 * world
+        q, k, v, _ = O.make_attention_inputs(B, Hq, Hkv, S, D, seed=9, rope=False)
+        ql, kl, vl = (cp.shard_sequence(t, rank, world) for t in (q, k, v))
+        o, lse = cp.ring_attention_forward(ql, kl, vl, OracleEngine(D ** -0.5, pv))
+        parts_o = [torch.empty_like(o) for _ in range(world)]
+        parts_l = [torch.empty_like(lse) for _ in range(world)]
+        dist.all_gather(parts_o, o.contiguous())  # checking only
+        dist.all_gather(parts_l, lse.contiguous())
+        if rank == 0:
+            full = O.attn_forward(q, k, v, pv_format=pv)
+            got_o, got_l = cp.unshard_sequence(parts_o), cp.unshard_sequence(parts_l, dim=2)
+            out.put((O.rel_l2(full.o, got_o), float((full.lse - got_l).abs().max())))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,pv", [(2, "e4m3_fp8"), (3, "e4m3_fp8"), (2, "mxfp4_e8m0_block32")])
+def test_ring_reproduces_the_single_device_oracle(world, pv):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, pv, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    o_err, lse_err = out.get(timeout=300)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert o_err < 4e-3, o_err      # partial results are rounded to bf16 before the merge
+    assert lse_err < 1e-4, lse_err
