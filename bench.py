@@ -39,6 +39,8 @@ import torch  # noqa: E402
 WORKLOADS = {
     "c2": dict(B=2, Hq=32, Hkv=8, S=8192, D=128),     # the benchmark configuration
     "small": dict(B=1, Hq=8, Hkv=2, S=8192, D=128),  # same tiles and sequence, 1/8 of the heads: profiler captures only
+    "c3": dict(B=16, Hq=32, Hkv=8, S=4096, D=64),    # the D = 64 configuration (same FLOPs as c2)
+    "c5": dict(B=1, Hq=32, Hkv=8, S=131072, D=128),  # long context: forward only, MXFP4 P.V, sequence sharded over the ranks
 }
 WORKLOAD = dict(WORKLOADS["c2"])
 METRIC = "causal_attn_fwd_bwd_tflops"
@@ -295,15 +297,16 @@ def run_ours(args, rank, world, local_rank):
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp4_e2m1 (QK^T) x fp8_e4m3/e5m2 (PV, gradients), f32 accumulate", "data": "synthetic",
-        "config": {"workload": ("C2 Llama-3-8B attention B2 Hq32 Hkv8 S8192 D128 causal fwd+bwd per GPU" if args.workload == "c2" else
-                                "PROFILER CASE (not a benchmark result): B1 Hq8 Hkv2 S8192 D128 causal fwd+bwd"),
+        "config": {"workload": {"c2": "C2 Llama-3-8B attention B2 Hq32 Hkv8 S8192 D128 causal fwd+bwd per GPU",
+                                "c3": "C3 B16 Hq32 Hkv8 S4096 D64 causal fwd+bwd per GPU (not the headline configuration)",
+                                "small": "PROFILER CASE (not a benchmark result): B1 Hq8 Hkv2 S8192 D128 causal fwd+bwd"}[args.workload],
                    "global_batch": B * world, "l2": "inputs (448 MiB bf16 + 470 MiB operand cache) exceed the 126 MB L2",
                    "flops": "6 causal matmuls = 12*B*Hq*D*S(S+1)/2", "includes": "Q/K/V quantisation and dO/statistics publication"},
         "clocks": clocks,
         "e2e": {"value": world * flops_step * args.steps / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
                 "h2d_bytes_per_step": nbytes_in, "d2h_bytes_per_step": 16},
         "gpu_launches": 9 * args.steps,  # per step: 2 amax + 2 quantise (Q, K), V to FP8, forward, dO publication, backward, dQ conversion
-        "roofline": {"bound": "tensor", "kernel": "attn_bwd_kernel<128>", "achieved": bwd_ach, "peak": bwd_peak, "unit": UNIT,
+        "roofline": {"bound": "tensor", "kernel": f"attn_bwd_kernel<{D}>", "achieved": bwd_ach, "peak": bwd_peak, "unit": UNIT,
                      "frac": bwd_ach / bwd_peak, "traffic": None, "ms_per_launch": bwd_ms,
                      "peak_source": (f"measured here: tcgen05 MMA-only run on all SMs, FP8 {tp8:.0f} TF/s, NVFP4 {tp4:.0f} TF/s, combined over the "
                                      f"kernel's FP4/FP8 mix ({peaks['source']} cuBLAS bf16 burst {peaks['bf16']} TF/s x2 / x4 would give "
@@ -314,6 +317,64 @@ def run_ours(args, rank, world, local_rank):
         "quantizers": quant,
     }
     print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_c5(args, rank, world, local_rank):
+    """Long-context forward (C5): the whole job is ONE sequence of 131072 tokens, sharded zig-zag over the ranks
+    ("strong" scaling); quantised K/V shards travel round an NCCL ring.  Heavy-tailed (Student-t, 3 degrees of
+    freedom) q and k, MXFP4 P.V route.  value = forward TFLOP/s of the whole job, max over ranks."""
+    import torch.distributed as dist
+
+    from fa4b import context_parallel as cp
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    B, Hq, Hkv, S, D = (WORKLOAD[k] for k in ("B", "Hq", "Hkv", "S", "D"))
+    g = torch.Generator(device=device).manual_seed(20260825 + rank)
+    Sl = S // world
+
+    def student_t(*shape):
+        z = torch.randn(*shape, device=device, generator=g)
+        chi = sum(torch.randn(*shape[:-1], 1, device=device, generator=g) ** 2 for _ in range(3)) / 3.0
+        return (z / chi.sqrt()).bfloat16()
+
+    q, k = student_t(B, Hq, Sl, D), student_t(B, Hkv, Sl, D)
+    v = torch.randn(B, Hkv, Sl, D, device=device, generator=g).bfloat16()
+    engine = cp.KernelEngine(pv_format="mxfp4_e8m0_block32")
+    sampler = ClockSampler(local_rank)
+    for _ in range(max(args.warmup, 3)):
+        cp.ring_attention_forward(q, k, v, engine)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        o, lse = cp.ring_attention_forward(q, k, v, engine)
+    t1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    if world > 1:
+        dist.barrier()
+    times = torch.tensor([t0.elapsed_time(t1)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms = float(times.item())
+    if rank == 0:
+        flops = 2.0 * causal_matmul_flops(B, Hq, S, D)
+        print(json.dumps({
+            "metric": "causal_attn_fwd_tflops_long_context", "value": flops * args.steps / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp4_e2m1 (QK^T) x mxfp4 (P.V), f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"C5 B1 Hq32 Hkv8 S131072 D128 causal forward, MXFP4 P.V, context parallel over {world} rank(s)",
+                       "exchange": "NCCL ring of quantised K/V shards (17.3 MB per chunk per hop), one all_reduce(MAX) of 40 amax words",
+                       "l2": "operands exceed L2", "includes": "amax, quantisation, ring, merges"},
+            "clocks": clocks, "gpu_launches": None}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -337,6 +398,9 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU fallback (use --impl reference for the CPU emulation)")
+    if args.workload == "c5":
+        run_c5(args, rank, world, local_rank)
+        return
     run_ours(args, rank, world, local_rank)
 
 
