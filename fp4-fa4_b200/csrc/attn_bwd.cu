@@ -141,8 +141,18 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
   // key-tile-major order: low key tiles, which see the most query tiles, start first.  (kv-head-major
   // order, meant to keep the FP32 dQ scratch rows in L2 while their 64 partial sums arrive, was 12 %
   // slower: the CTAs of one head then reduce into neighbouring rows at the same time.)
+#ifdef FA4B_BWD_GROUP
+  // experiment: kv heads in groups of FA4B_BWD_GROUP, key-tile-major inside a group (dQ scratch of a group fits in L2)
+  constexpr int GB = FA4B_BWD_GROUP;
+  const int per_group = n_tiles * GB;
+  const int grp = blockIdx.x / per_group, rr = blockIdx.x % per_group;
+  const int gsz = min(GB, heads_kv - grp * GB);
+  const int kt = rr / gsz;
+  const int bhk = grp * GB + rr % gsz;
+#else
   const int kt = blockIdx.x / heads_kv;
   const int bhk = blockIdx.x % heads_kv;
+#endif
   const int b = bhk / p.Hkv, hk = bhk % p.Hkv;
   const int G = p.Hq / p.Hkv;
   const int sub_per_tile = 128 / QT;
