@@ -140,19 +140,10 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
   const int heads_kv = p.B * p.Hkv;
   // key-tile-major order: low key tiles, which see the most query tiles, start first.  (kv-head-major
   // order, meant to keep the FP32 dQ scratch rows in L2 while their 64 partial sums arrive, was 12 %
-  // slower: the CTAs of one head then reduce into neighbouring rows at the same time.)
-#ifdef FA4B_BWD_GROUP
-  // experiment: kv heads in groups of FA4B_BWD_GROUP, key-tile-major inside a group (dQ scratch of a group fits in L2)
-  constexpr int GB = FA4B_BWD_GROUP;
-  const int per_group = n_tiles * GB;
-  const int grp = blockIdx.x / per_group, rr = blockIdx.x % per_group;
-  const int gsz = min(GB, heads_kv - grp * GB);
-  const int kt = rr / gsz;
-  const int bhk = grp * GB + rr % gsz;
-#else
+  // slower, and so were groups of 2, 4 or 8 kv heads, key-tile-major inside a group (2-6 %): a head's heavy
+  // low key tiles then start late, and the reductions are not what bounds the kernel.)
   const int kt = blockIdx.x / heads_kv;
   const int bhk = blockIdx.x % heads_kv;
-#endif
   const int b = bhk / p.Hkv, hk = bhk % p.Hkv;
   const int G = p.Hq / p.Hkv;
   const int sub_per_tile = 128 / QT;
@@ -347,7 +338,9 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       };
       if (ok) ok = issue_s(0);
       if (ok && 1 < n_it) ok = issue_s(1);
-      // two in-order streams, served as their events arrive
+      // two in-order streams, served as their events arrive.  (Answering the ds event in three separately
+      // scheduled steps -- S, dK, dQ -- with pt events taken in between was measured 3 % slower: the two compute
+      // groups then fall back into step with each other.)
       int ip = 0, id = 0;  // next sub-tile of the pt stream / of the ds stream
       long long t_idle = 0;
       while (ok && id < n_it) {
