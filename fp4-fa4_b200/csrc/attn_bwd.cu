@@ -50,6 +50,7 @@ struct BwdSmem {
   alignas(16) uint8_t q_sf[kBwdStages][C::kPages * 512];
   alignas(16) float lstat[kBwdStages][C::QT];
   alignas(16) float dstat[kBwdStages][C::QT];
+  alignas(16) float dq_patch[D == 64 ? 4 : 1][D == 64 ? 32 * 33 : 1];  // D = 64: per drain warp, 32 x 32 transposition patch
   alignas(16) float c2[16];  // per query head of the group: global scales * softmax scale * log2(e)
   alignas(8) uint64_t kv_full, in_full[kBwdStages], in_empty[kBwdStages], st_full[2], dp_full[2], pt_ready[2], ds_ready[2], dq_full, dq_free,
       acc_done, mma_drained;
@@ -117,9 +118,6 @@ __device__ __forceinline__ float2 e4m3x2_to_f32(uint32_t two_bytes) {
   const uint16_t in = (uint16_t)two_bytes;
   asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(in));
   return __half22float2(*reinterpret_cast<const __half2*>(&h2));
-}
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 template <int D>
@@ -426,12 +424,19 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
 #pragma unroll
         for (int i = 0; i < 32; ++i) atomicAdd(base + (size_t)(32 + i) * D + r, __uint_as_float(v1[i]));
       } else {
+        // lane = query row, register i = feature: transpose 32 x 32 blocks through this warp's shared-memory patch
+        // so that every reduction instruction covers 128 contiguous bytes of one row (vector reductions of 16 bytes
+        // per lane, one row per lane, ran at half the rate of these in a stand-alone test)
+        float* patch = s.dq_patch[w4];
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          red_add_v4(base + (size_t)r * D + i, __uint_as_float(v0[i]), __uint_as_float(v0[i + 1]), __uint_as_float(v0[i + 2]),
-                     __uint_as_float(v0[i + 3]));
-          red_add_v4(base + (size_t)r * D + 32 + i, __uint_as_float(v1[i]), __uint_as_float(v1[i + 1]), __uint_as_float(v1[i + 2]),
-                     __uint_as_float(v1[i + 3]));
+        for (int hh = 0; hh < 2; ++hh) {
+          const uint32_t(&v)[32] = hh ? v1 : v0;
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) patch[lane * 33 + i] = __uint_as_float(v[i]);
+          __syncwarp();
+#pragma unroll
+          for (int rr = 0; rr < 32; ++rr) atomicAdd(base + (size_t)(w4 * 32 + rr) * D + 32 * hh + lane, patch[rr * 33 + lane]);
         }
       }
 #endif

@@ -53,11 +53,15 @@ __global__ void __launch_bounds__(256) quant_heads_kernel(HeadView x, int S, con
                                                           float* __restrict__ gscale, uint8_t* __restrict__ fp8) {
   constexpr int kKb = D / 16, kPages = D / 64;
   __shared__ __align__(16) uint8_t sc[kPages * 512];
+  __shared__ StepTable steps;
   const int bh = blockIdx.y, tile = blockIdx.x, t = threadIdx.x;
   const float amax = __int_as_float(amax_bits[bh]);
   const float g = amax / kNvfp4GlobalDiv;
+  const float inv6g = 1.0f / (6.0f * g);
   if (tile == 0 && t == 0) gscale[bh] = g;
   const bool all_zero = !(amax > 0.f);
+  fill_step_table(steps, g, t);
+  __syncthreads();
 #pragma unroll
   for (int i = 0; i < (128 * kKb) / 256; ++i) {
     const int b = t + i * 256;
@@ -66,31 +70,34 @@ __global__ void __launch_bounds__(256) quant_heads_kernel(HeadView x, int S, con
     const uint4* src = reinterpret_cast<const uint4*>(x.row(bh, s) + kb * 16);
     const uint4 lo = __ldg(src), hi = __ldg(src + 1);
     const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-    float xv[16];
-    float bamax = 0.f;
+    uint64_t xp[8];
+    uint32_t m2 = 0;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-      xv[2 * k] = bf16_bits_to_f32(w[k] & 0xffffu);
-      xv[2 * k + 1] = bf16_bits_to_f32(w[k] >> 16);
-      bamax = fmaxf(bamax, fmaxf(fabsf(xv[2 * k]), fabsf(xv[2 * k + 1])));
+      m2 = absmax_bf16x2(m2, w[k]);
+      xp[k] = bf16x2_to_f32x2(w[k]);
     }
+    const float bamax = fmaxf(bf16_bits_to_f32(m2 & 0xffffu), bf16_bits_to_f32(m2 >> 16));
     uint32_t packed[2] = {0, 0};
     uint32_t sbyte = 0;
     if (!all_zero) {
-      float safe;
-      sbyte = nvfp4_block_scale(bamax, g, safe);
-      quantize_block<16>(xv, safe, packed);
+      sbyte = nvfp4_scale_byte(bamax, g, inv6g);
+      nvfp4_codes16(xp, bamax, steps, sbyte, packed[0], packed[1]);
     }
     const size_t row_index = (size_t)bh * S + s;
     *reinterpret_cast<uint2*>(codes + row_index * (D / 2) + kb * 8) = make_uint2(packed[0], packed[1]);
     sc[(kb >> 2) * 512 + page_offset(r, kb)] = (uint8_t)sbyte;
     if (fp8) {
-      uint4 o;
-      o.x = cvt_e4m3x4(4.f * xv[0], 4.f * xv[1], 4.f * xv[2], 4.f * xv[3]);
-      o.y = cvt_e4m3x4(4.f * xv[4], 4.f * xv[5], 4.f * xv[6], 4.f * xv[7]);
-      o.z = cvt_e4m3x4(4.f * xv[8], 4.f * xv[9], 4.f * xv[10], 4.f * xv[11]);
-      o.w = cvt_e4m3x4(4.f * xv[12], 4.f * xv[13], 4.f * xv[14], 4.f * xv[15]);
-      *reinterpret_cast<uint4*>(fp8 + row_index * D + kb * 16) = o;
+      uint32_t o[4];
+      const uint64_t four = pack2(4.f, 4.f);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float a0, a1, b0, b1;
+        unpack2(mul2(xp[2 * k], four), a0, a1);
+        unpack2(mul2(xp[2 * k + 1], four), b0, b1);
+        o[k] = cvt_e4m3x4(a0, a1, b0, b1);
+      }
+      *reinterpret_cast<uint4*>(fp8 + row_index * D + kb * 16) = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
   __syncthreads();

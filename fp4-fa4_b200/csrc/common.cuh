@@ -129,36 +129,6 @@ __device__ __host__ __forceinline__ uint32_t page_offset(uint32_t row, uint32_t 
   return (row & 31u) * 16u + ((row & 127u) >> 5) * 4u + (kblock & 3u);
 }
 
-// ---- one quantisation block ----------------------------------------------------
-// Codes of n (16 or 32) values divided by `safe`, equal to E2M1_rne(x / safe) with
-// an IEEE division.  The fast path multiplies by the reciprocal; that product is
-// within 3 ulp of the rounded quotient, and every E2M1 rounding threshold has
-// zero low 21 mantissa bits, so a product at least 8 ulp away from such a
-// pattern rounds to the same code.  Blocks with a closer product redo the
-// division exactly.
-template <int N>
-__device__ __forceinline__ void quantize_block(const float (&x)[N], float safe, uint32_t (&packed)[N / 8]) {
-  const float r = 1.0f / safe;
-  float q[N];
-  bool danger = false;
-#pragma unroll
-  for (int i = 0; i < N; ++i) {
-    q[i] = x[i] * r;
-    danger |= ((__float_as_uint(q[i]) + 8u) & 0x1FFFFFu) <= 16u;
-  }
-  if (danger) {
-#pragma unroll
-    for (int i = 0; i < N; ++i) q[i] = x[i] / safe;
-  }
-#pragma unroll
-  for (int w = 0; w < N / 8; ++w) {
-    uint32_t v = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) v |= cvt_e2m1x2(q[w * 8 + 2 * j], q[w * 8 + 2 * j + 1]) << (8 * j);
-    packed[w] = v;
-  }
-}
-
 // ---- division by a block's step without a divide per element ------------------------------
 // q = RN(x / d) from r = RN(1 / d):  q0 = RN(x r),  e = x - d q0 (exact in one FMA),  q = RN(q0 + e r).
 // That is the correctly rounded quotient whenever r is the correctly rounded reciprocal and d's
@@ -231,14 +201,6 @@ __device__ __forceinline__ void nvfp4_codes16(const uint64_t (&x)[8], float bama
     }
   }
   e2m1_pack16(q, lo, hi);
-}
-
-// NVFP4 block scale: s = E4M3(clamp(bamax / 6 / g)), returns the byte and safe = max(s*g, FLT_MIN)
-__device__ __forceinline__ uint32_t nvfp4_block_scale(float bamax, float g, float& safe) {
-  const float s = (bamax / 6.0f) / g;
-  const uint32_t byte = cvt_e4m3x2(s, 0.f) & 0xffu;
-  safe = fmaxf(e4m3_to_f32(byte) * g, kFltMin);
-  return byte;
 }
 
 }  // namespace fa4b
