@@ -121,6 +121,108 @@ __global__ void __launch_bounds__(256) rmsnorm_stats_kernel(const __nv_bfloat16*
   }
 }
 
+// ------------------------------------------------------------------ RMSNorm backward
+// One CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; a thread owns VEC chunks of 8 columns, keeps gamma
+// and its column sums of dy * (x * inv_rms) in registers, and leaves the sums as one FP32 row of `partials`.
+constexpr int kRmsBwdParts = 296;  // two CTAs per SM's worth of partial rows
+template <int VEC>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld, const __nv_bfloat16* __restrict__ gamma,
+                                                          const float* __restrict__ inv_rms, const __nv_bfloat16* __restrict__ dy, int64_t ld_dy,
+                                                          int64_t rows, int cols, __nv_bfloat16* __restrict__ dx, float* __restrict__ partials) {
+  const int n_vec = cols / 8;
+  float gv[VEC][8], acc[VEC][8];
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) {
+    const int i = threadIdx.x + j * 256;
+    uint4 g4 = make_uint4(0, 0, 0, 0);
+    if (i < n_vec) g4 = __ldg(reinterpret_cast<const uint4*>(gamma) + i);
+    const uint32_t w[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      gv[j][2 * k] = bf16_bits_to_f32(w[k] & 0xffffu);
+      gv[j][2 * k + 1] = bf16_bits_to_f32(w[k] >> 16);
+      acc[j][2 * k] = acc[j][2 * k + 1] = 0.f;
+    }
+  }
+  __shared__ float red[8];
+  __shared__ float s_proj;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    float xv[VEC][8], dv[VEC][8];
+    float local = 0.f;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const int i = threadIdx.x + j * 256;
+      uint4 x4 = make_uint4(0, 0, 0, 0), d4 = make_uint4(0, 0, 0, 0);
+      if (i < n_vec) {
+        x4 = __ldg(reinterpret_cast<const uint4*>(x + row * ld) + i);
+        d4 = __ldg(reinterpret_cast<const uint4*>(dy + row * ld_dy) + i);
+      }
+      const uint32_t xw[4] = {x4.x, x4.y, x4.z, x4.w}, dw[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        xv[j][2 * k] = bf16_bits_to_f32(xw[k] & 0xffffu);
+        xv[j][2 * k + 1] = bf16_bits_to_f32(xw[k] >> 16);
+        dv[j][2 * k] = bf16_bits_to_f32(dw[k] & 0xffffu);
+        dv[j][2 * k + 1] = bf16_bits_to_f32(dw[k] >> 16);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) local = fmaf(dv[j][e] * gv[j][e], xv[j][e], local);
+    }
+    local = warp_sum(local);
+    __syncthreads();  // the previous row's s_proj has been read by everyone
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = local;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float tsum = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) tsum += red[k];
+      s_proj = tsum / (float)cols;
+    }
+    __syncthreads();
+    const float inv = __ldg(inv_rms + row);
+    const float corr = inv * inv * s_proj;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const int i = threadIdx.x + j * 256;
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float a = inv * (dv[j][2 * k] * gv[j][2 * k] - xv[j][2 * k] * corr);
+        const float b = inv * (dv[j][2 * k + 1] * gv[j][2 * k + 1] - xv[j][2 * k + 1] * corr);
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        o[k] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      if (i < n_vec) *reinterpret_cast<uint4*>(dx + row * (int64_t)cols + (int64_t)i * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[j][e] = fmaf(dv[j][e], xv[j][e] * inv, acc[j][e]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) {
+    const int i = threadIdx.x + j * 256;
+    if (i < n_vec) {
+      float* dst = partials + (int64_t)blockIdx.x * cols + (int64_t)i * 8;
+      *reinterpret_cast<float4*>(dst) = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
+    }
+  }
+}
+__global__ void __launch_bounds__(256) rmsnorm_bwd_reduce_kernel(const float* __restrict__ partials, int n_parts, int cols,
+                                                                 __nv_bfloat16* __restrict__ dgamma) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= cols) return;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  int p = 0;
+  for (; p + 4 <= n_parts; p += 4) {
+    a0 += partials[(int64_t)p * cols + c];
+    a1 += partials[(int64_t)(p + 1) * cols + c];
+    a2 += partials[(int64_t)(p + 2) * cols + c];
+    a3 += partials[(int64_t)(p + 3) * cols + c];
+  }
+  for (; p < n_parts; ++p) a0 += partials[(int64_t)p * cols + c];
+  dgamma[c] = __float2bfloat16_rn((a0 + a1) + (a2 + a3));
+}
+
 // ------------------------------------------------------------------ NVFP4 tile kernel
 constexpr int kTile = 128;
 constexpr int kPitch = kTile + 8;  // bf16 elements; 272-byte rows keep 16-byte alignment
@@ -446,6 +548,35 @@ int fa4b_rmsnorm_quant_nvfp4(const fa4b_rmsnorm_quant_nvfp4_args* a, void* strea
   p.codes_row = a->codes_row; p.scales_row = a->scales_row;
   p.codes_col = a->codes_col; p.scales_col = a->scales_col;
   return launch_nvfp4(p, true, st);
+}
+
+size_t fa4b_rmsnorm_bwd_workspace_bytes(int64_t cols) { return cols > 0 ? (size_t)kRmsBwdParts * (size_t)cols * sizeof(float) : 0; }
+
+int fa4b_rmsnorm_bwd(const fa4b_rmsnorm_bwd_args* a, void* stream) {
+  FA4B_REQUIRE(a != nullptr, FA4B_BAD_ARG, "args is NULL");
+  FA4B_REQUIRE(a->x && a->gamma && a->inv_rms && a->dy && a->dx && a->dgamma && a->partials, FA4B_BAD_ARG, "fa4b_rmsnorm_bwd: NULL pointer");
+  FA4B_REQUIRE(a->rows > 0 && a->cols > 0 && a->cols % 8 == 0 && a->cols <= 8 * 256 * 4, FA4B_BAD_SHAPE,
+               "rows=%lld cols=%lld: cols must be a multiple of 8 up to 8192", (long long)a->rows, (long long)a->cols);
+  FA4B_REQUIRE(a->ld >= a->cols && a->ld_dy >= a->cols && a->ld % 8 == 0 && a->ld_dy % 8 == 0, FA4B_BAD_ALIGN,
+               "row strides must be >= cols and multiples of 8 elements");
+  FA4B_REQUIRE(((reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->dy) | reinterpret_cast<uintptr_t>(a->gamma) |
+                 reinterpret_cast<uintptr_t>(a->dx) | reinterpret_cast<uintptr_t>(a->partials)) & 15) == 0,
+               FA4B_BAD_ALIGN, "fa4b_rmsnorm_bwd: 16-byte alignment");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const auto* x = static_cast<const __nv_bfloat16*>(a->x);
+  const auto* gm = static_cast<const __nv_bfloat16*>(a->gamma);
+  const auto* dy = static_cast<const __nv_bfloat16*>(a->dy);
+  auto* dx = static_cast<__nv_bfloat16*>(a->dx);
+  const int cols = (int)a->cols;
+  const int n_parts = (int)std::min<int64_t>(a->rows, kRmsBwdParts);
+  const int vec = (int)((a->cols / 8 + 255) / 256);
+  if (vec <= 1) rmsnorm_bwd_kernel<1><<<n_parts, 256, 0, st>>>(x, a->ld, gm, a->inv_rms, dy, a->ld_dy, a->rows, cols, dx, a->partials);
+  else if (vec <= 2) rmsnorm_bwd_kernel<2><<<n_parts, 256, 0, st>>>(x, a->ld, gm, a->inv_rms, dy, a->ld_dy, a->rows, cols, dx, a->partials);
+  else rmsnorm_bwd_kernel<4><<<n_parts, 256, 0, st>>>(x, a->ld, gm, a->inv_rms, dy, a->ld_dy, a->rows, cols, dx, a->partials);
+  FA4B_CUDA(cudaGetLastError());
+  rmsnorm_bwd_reduce_kernel<<<(cols + 255) / 256, 256, 0, st>>>(a->partials, n_parts, cols, static_cast<__nv_bfloat16*>(a->dgamma));
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
 }
 
 int fa4b_quant_mxfp4(const fa4b_quant_mxfp4_args* a, void* stream) {

@@ -34,6 +34,12 @@ class RmsnormQuantArgs(C.Structure):
                 ("codes_col", C.c_void_p), ("scales_col", C.c_void_p)]
 
 
+class RmsnormBwdArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("gamma", C.c_void_p), ("inv_rms", C.c_void_p), ("dy", C.c_void_p), ("rows", C.c_int64),
+                ("cols", C.c_int64), ("ld", C.c_int64), ("ld_dy", C.c_int64), ("dx", C.c_void_p), ("dgamma", C.c_void_p),
+                ("partials", C.c_void_p)]
+
+
 class QuantMxfp4Args(C.Structure):
     _fields_ = [("x", C.c_void_p), ("rows", C.c_int64), ("cols", C.c_int64), ("ld", C.c_int64),
                 ("mode", C.c_int), ("codes", C.c_void_p), ("scales", C.c_void_p)]
@@ -83,7 +89,7 @@ EXPORTS = (
     "fa4b_status_string", "fa4b_last_error", "fa4b_query", "fa4b_amax", "fa4b_quant_nvfp4",
     "fa4b_rmsnorm_quant_nvfp4", "fa4b_quant_mxfp4", "fa4b_dequant_nvfp4", "fa4b_dequant_mxfp4",
     "fa4b_attn_workspace_bytes", "fa4b_attn_ws_layout_query", "fa4b_attn_prepare", "fa4b_attn_fwd",
-    "fa4b_attn_fwd_static", "fa4b_attn_bwd_preprocess", "fa4b_attn_bwd", "fa4b_attn_check_status", "fa4b_attn_merge", "fa4b_microgate", "fa4b_tensor_peak",
+    "fa4b_attn_fwd_static", "fa4b_attn_bwd_preprocess", "fa4b_attn_bwd", "fa4b_attn_check_status", "fa4b_attn_merge", "fa4b_rmsnorm_bwd", "fa4b_rmsnorm_bwd_workspace_bytes", "fa4b_microgate", "fa4b_tensor_peak",
 )
 
 _lib = None
@@ -99,6 +105,8 @@ def lib() -> C.CDLL:
         handle.fa4b_status_string.restype = C.c_char_p
         handle.fa4b_last_error.restype = C.c_char_p
         handle.fa4b_attn_workspace_bytes.restype = C.c_size_t
+        handle.fa4b_rmsnorm_bwd_workspace_bytes.restype = C.c_size_t
+        handle.fa4b_rmsnorm_bwd_workspace_bytes.argtypes = [C.c_int64]
         for name in EXPORTS:
             getattr(handle, name)  # AttributeError if the ABI is incomplete
         _lib = handle

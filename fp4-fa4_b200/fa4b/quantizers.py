@@ -84,6 +84,30 @@ def tk_fused_norm_quantize(input: torch.Tensor, gamma: torch.Tensor, eps: float 
     return out + (y,) if return_normalized else out
 
 
+def rmsnorm_backward_bf16(tensor: torch.Tensor, gamma: torch.Tensor, inv_rms: torch.Tensor, gradient: torch.Tensor):
+    """Backward of the fused RMSNorm: ``(dx [M,K] bf16, dgamma [K] bf16)`` from the input, gamma, the saved
+    ``inv_rms [M]`` f32 and the gradient of the normalised output (same name and argument order as the
+    reference's ``rmsnorm_backward_bf16``, ``tk_fa4/interface.py:1144-1150``)."""
+    _require_matrix(tensor, "tensor")
+    _require_matrix(gradient, "gradient")
+    if gradient.shape != tensor.shape:
+        raise ValueError(f"gradient {tuple(gradient.shape)} does not match tensor {tuple(tensor.shape)}")
+    rows, cols = tensor.shape
+    if gamma.dtype != torch.bfloat16 or gamma.shape != (cols,) or not gamma.is_cuda or not gamma.is_contiguous():
+        raise ValueError("gamma must be a contiguous CUDA bfloat16 vector of length K")
+    if inv_rms.dtype != torch.float32 or inv_rms.shape != (rows,) or not inv_rms.is_cuda or not inv_rms.is_contiguous():
+        raise ValueError("inv_rms must be a contiguous CUDA float32 vector of length M")
+    nbytes = lib().fa4b_rmsnorm_bwd_workspace_bytes(cols)
+    dev = tensor.device
+    partials = torch.empty(max(nbytes // 4, 1), dtype=torch.float32, device=dev)
+    dx = torch.empty(rows, cols, dtype=torch.bfloat16, device=dev)
+    dgamma = torch.empty(cols, dtype=torch.bfloat16, device=dev)
+    a = _lib.RmsnormBwdArgs(ptr(tensor), ptr(gamma), ptr(inv_rms), ptr(gradient), rows, cols, tensor.stride(0), gradient.stride(0),
+                            ptr(dx), ptr(dgamma), ptr(partials))
+    check(lib().fa4b_rmsnorm_bwd(C.byref(a), C.c_void_p(current_stream())), "fa4b_rmsnorm_bwd")
+    return dx, dgamma
+
+
 def mxfp4_quantize_for_gemm(input: torch.Tensor, mode: int | str = "ceil"):
     """MXFP4 (1x32, E8M0) of ``input [M,K]``: ``(fp4 [M,K/2], scales [M/128,K/128,512])``."""
     _require_matrix(input, "input")

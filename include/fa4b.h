@@ -111,6 +111,27 @@ typedef struct fa4b_rmsnorm_quant_nvfp4_args {
 } fa4b_rmsnorm_quant_nvfp4_args;
 int fa4b_rmsnorm_quant_nvfp4(const fa4b_rmsnorm_quant_nvfp4_args* a, void* stream);
 
+/* ---- fa4b_rmsnorm_bwd ---------------------------------------------------
+ * Backward of y = (x * inv_rms[row]) * gamma[col] given dy:
+ *   proj[row] = mean_col(dy * gamma * x);  dx = bf16(inv_rms * (dy * gamma - x * inv_rms^2 * proj));
+ *   dgamma[col] = bf16(sum_row dy * (x * inv_rms)), accumulated in FP32.
+ * Replaces rmsnorm_backward_bf16 (tk_fa4/interface.py:1144-1150; kernel
+ * tk_fa4/lowp_fa4_bwd/rmsnorm_nvfp4_quantize.cuh:321-462), for any cols % 8 == 0 up to 8192 instead of
+ * the reference's fixed 2048.  `partials` is caller-owned FP32 scratch of
+ * fa4b_rmsnorm_bwd_workspace_bytes(cols) bytes (per-CTA column sums before the final reduction). */
+typedef struct fa4b_rmsnorm_bwd_args {
+  const void* x;      /* [rows, cols] bf16, row stride ld */
+  const void* gamma;  /* [cols] bf16 */
+  const float* inv_rms; /* [rows] */
+  const void* dy;     /* [rows, cols] bf16, row stride ld_dy */
+  int64_t rows, cols, ld, ld_dy;
+  void* dx;           /* [rows, cols] bf16, dense */
+  void* dgamma;       /* [cols] bf16 */
+  float* partials;
+} fa4b_rmsnorm_bwd_args;
+size_t fa4b_rmsnorm_bwd_workspace_bytes(int64_t cols);
+int fa4b_rmsnorm_bwd(const fa4b_rmsnorm_bwd_args* a, void* stream);
+
 /* ---- fa4b_quant_mxfp4 ---------------------------------------------------
  * Row-wise 1x32 MXFP4 with E8M0 scales.  Replaces mxfp4_quantize_for_gemm
  * (TK_quantisation/mxfp4_v3/tk_quantize.cu:2052-2054).

@@ -159,3 +159,21 @@ def test_full_size_quantizers_by_slabs_and_transpose_property():
     _same(out[0][r0:r0 + 128], ref.codes, "fused row codes slab")
     _same(out[1][r0 // 128], ref.pages()[0], "fused row pages slab")
     assert fa4b.amax(xd).item() == float(x.float().abs().amax())
+
+
+@pytest.mark.parametrize("M,K", [(256, 1024), (384, 2048), (128, 4096)])
+def test_rmsnorm_backward_matches_fp32_reference(M, K):
+    """dx and dgamma of the fused RMSNorm (FP32 arithmetic, bf16 results): agreement to bf16 rounding with the
+    CPU restatement; the forward's inv_rms is the saved statistic."""
+    x, gamma = O.make_quantizer_inputs(M, K, seed=40 + M)
+    g = torch.Generator().manual_seed(M + K)
+    dy = (torch.randn(M, K, generator=g) * 0.1).bfloat16()
+    out = fa4b.tk_fused_norm_quantize(x.to(DEV), gamma.to(DEV), 1e-6, return_transpose=False)
+    inv_rms = out[5]
+    want_dx, want_dg = O.rmsnorm_backward_reference(x, gamma, inv_rms.cpu(), dy)
+    dx, dgamma = fa4b.rmsnorm_backward_bf16(x.to(DEV), gamma.to(DEV), inv_rms, dy.to(DEV))
+    assert O.rel_l2(want_dx, dx.cpu()) < 3e-3      # one bf16 rounding each side: 2^-9 / sqrt(3) per element at most
+    assert (want_dx.float() - dx.cpu().float()).abs().max() <= 2.0 ** -7 * want_dx.float().abs().max()
+    assert O.rel_l2(want_dg, dgamma.cpu()) < 3e-3
+    with pytest.raises(Exception):
+        fa4b.rmsnorm_backward_bf16(x.to(DEV), gamma.to(DEV)[:-8], inv_rms, dy.to(DEV))
