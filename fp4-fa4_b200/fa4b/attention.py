@@ -105,13 +105,14 @@ def _ev(e) -> int:
 
 
 def attn_forward(q, k, v, softmax_scale: float | None = None, pv_format: str = "e4m3_fp8", workspace: Workspace | None = None,
-                 prepared: bool = False, events=(None, None)):
-    """O ``[B,Hq,S,D]`` bf16, LSE ``[B,Hq,S]`` f32 and the workspace holding the quantised operands."""
+                 prepared: bool = False, events=(None, None), causal: bool = True):
+    """O ``[B,Hq,S,D]`` bf16, LSE ``[B,Hq,S]`` f32 and the workspace holding the quantised operands.
+    ``causal=False`` (forward only) lets every query see every key."""
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _check_bhsd(t, n)
     if k.shape != v.shape or q.shape[0] != k.shape[0] or q.shape[2:] != k.shape[2:]:
         raise ValueError(f"inconsistent shapes q{tuple(q.shape)} k{tuple(k.shape)} v{tuple(v.shape)}")
-    dims = make_dims(q, k, softmax_scale, pv_format)
+    dims = make_dims(q, k, softmax_scale, pv_format, causal)
     ws = workspace or alloc_workspace(dims, q.device)
     B, Hq, S, D = q.shape
     o = torch.empty(B, Hq, S, D, dtype=torch.bfloat16, device=q.device)

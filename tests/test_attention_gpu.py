@@ -193,3 +193,21 @@ def test_backward_refuses_the_forward_only_mxfp4_route():
     o, lse, ws = attention.attn_forward(q, k, v, pv_format="mxfp4_e8m0_block32")
     with pytest.raises(Exception, match="forward only"):
         attention.attn_backward(o, lse, do, ws)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,S,D,pv", [(1, 4, 1, 384, 128, "e4m3_fp8"), (1, 4, 2, 256, 64, "e4m3_fp8"),
+                                             (1, 4, 1, 256, 128, "mxfp4_e8m0_block32")])
+def test_forward_without_mask_matches_oracle(B, Hq, Hkv, S, D, pv):
+    """FA4B_MASK_NONE: every query sees every key (the off-diagonal blocks of a sequence-sharded run, and the
+    reference's non-causal inference shape)."""
+    q, k, v, do = O.make_attention_inputs(B, Hq, Hkv, S, D, seed=606 + S, rope=(D == 128))
+    fwd = O.attn_forward(q, k, v, pv_format=pv, causal=False)
+    o, lse, ws = attention.attn_forward(q.to(DEV), k.to(DEV), v.to(DEV), pv_format=pv, causal=False)
+    ws.check_status()
+    torch.cuda.synchronize()
+    assert O.rel_l2(fwd.o, o.cpu()) < 1e-2, O.rel_l2(fwd.o, o.cpu())
+    assert O.rel_l2(fwd.lse, lse.cpu()) < 1e-2
+    if pv == "e4m3_fp8":
+        assert (fwd.lse - lse.cpu()).abs().max() < 1e-3
+    with pytest.raises(Exception, match="causal only"):
+        attention.attn_backward(o, lse, do.to(DEV), ws)
