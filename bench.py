@@ -42,6 +42,7 @@ WORKLOADS = {
     "small": dict(B=1, Hq=8, Hkv=2, S=8192, D=128),  # same tiles and sequence, 1/8 of the heads: profiler captures only
     "c3": dict(B=16, Hq=32, Hkv=8, S=4096, D=64),    # the D = 64 configuration (same FLOPs as c2)
     "c5": dict(B=1, Hq=32, Hkv=8, S=131072, D=128),  # long context: forward only, MXFP4 P.V, sequence sharded over the ranks
+    "noncausal": dict(B=1, Hq=32, Hkv=32, S=32768, D=128),  # the reference's historical inference shape: unmasked forward only
 }
 WORKLOAD = dict(WORKLOADS["c2"])
 METRIC = "causal_attn_fwd_bwd_tflops"
@@ -233,8 +234,13 @@ def run_ours(args, rank, world, local_rank):
     ms_total = t0.elapsed_time(t1)
     clocks = sampler.stop() if rank == 0 else None
     ws.check_status()
-    fwd_ms = sum(p[0].elapsed_time(p[1]) for p in pairs) / args.steps
-    bwd_ms = sum(p[2].elapsed_time(p[3]) for p in pairs) / args.steps
+    fwd_all = sorted(p[0].elapsed_time(p[1]) for p in pairs)
+    bwd_all = sorted(p[2].elapsed_time(p[3]) for p in pairs)
+    fwd_ms, bwd_ms = sum(fwd_all) / args.steps, sum(bwd_all) / args.steps
+
+    def pct(v):  # p10 / median / p90 of the per-step kernel times
+        n = len(v)
+        return {"p10": v[int(0.1 * (n - 1))], "p50": v[n // 2], "p90": v[int(round(0.9 * (n - 1)))]}
 
     extras = not args.no_extras
     # ---- end to end through the public operator, host buffers, copies inside the timed region
@@ -337,7 +343,9 @@ def run_ours(args, rank, world, local_rank):
                                      f"kernel's FP4/FP8 mix ({peaks['source']} cuBLAS bf16 burst {peaks['bf16']} TF/s x2 / x4 would give "
                                      f"{2 * peaks['bf16']:.0f} / {4 * peaks['bf16']:.0f})"),
                      "tensor_peaks": {"fp8_tflops": tp8, "nvfp4_tflops": tp4},
-                     "forward": {"achieved": fwd_ach, "peak": fwd_peak, "frac": fwd_ach / fwd_peak, "ms_per_launch": fwd_ms}},
+                     "ms_per_launch_percentiles": pct(bwd_all),
+                     "forward": {"achieved": fwd_ach, "peak": fwd_peak, "frac": fwd_ach / fwd_peak, "ms_per_launch": fwd_ms,
+                                 "ms_per_launch_percentiles": pct(fwd_all)}},
         "cpu_baseline": cpu,
         "quantizers": quant,
     }
@@ -404,6 +412,39 @@ def run_c5(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_noncausal(args, rank, world, local_rank):
+    """Unmasked forward at the reference's non-causal inference shape (B1, S32768, H32, D128), both P.V formats,
+    operands published beforehand as in the reference's measurement; FLOPs = 4*B*H*S^2*D."""
+    from fa4b import attention
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    B, Hq, Hkv, S, D = (WORKLOAD[k] for k in ("B", "Hq", "Hkv", "S", "D"))
+    g = torch.Generator(device=device).manual_seed(20260825)
+    q, k, v = (torch.randn(B, h, S, D, device=device, generator=g).bfloat16() for h in (Hq, Hkv, Hkv))
+    out = {}
+    for pv in ("e4m3_fp8", "mxfp4_e8m0_block32"):
+        dims = attention.make_dims(q, k, None, pv, causal=False)
+        ws = attention.alloc_workspace(dims, device)
+        attention.attn_prepare(q, k, v, ws)
+        for _ in range(max(args.warmup, 3)):
+            attention.attn_forward_prepared(ws, causal=False)
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            attention.attn_forward_prepared(ws, causal=False)
+        t1.record()
+        torch.cuda.synchronize()
+        ws.check_status()
+        ms = t0.elapsed_time(t1) / args.steps
+        out[pv] = {"ms": ms, "tflops": 4.0 * B * Hq * S * S * D / (ms * 1e-3) / 1e12}
+    print(json.dumps({"metric": "noncausal_attn_fwd_tflops", "value": out["e4m3_fp8"]["tflops"], "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "ms_per_step": out["e4m3_fp8"]["ms"], "higher_is_better": True, "data": "synthetic",
+                      "config": {"workload": "unmasked forward B1 H32 S32768 D128, operands published beforehand (not the headline configuration)"},
+                      "by_pv_format": out}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -425,6 +466,10 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU fallback (use --impl reference for the CPU emulation)")
     if args.workload == "c5":
         run_c5(args, rank, world, local_rank)
+        return
+    if args.workload == "noncausal":
+        if rank == 0:
+            run_noncausal(args, rank, world, local_rank)
         return
     run_ours(args, rank, world, local_rank)
 
