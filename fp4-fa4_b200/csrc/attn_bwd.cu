@@ -57,7 +57,6 @@ struct BwdSmem {
   uint32_t tmem_base;
   alignas(8) volatile uint32_t abort_flag;
   uint32_t pad_;
-  FA4B_PROF_FIELD
 };
 
 static_assert(sizeof(BwdSmem<128>) + 1024 <= 227 * 1024 && sizeof(BwdSmem<64>) + 1024 <= 227 * 1024, "shared memory budget");
@@ -80,15 +79,6 @@ struct BwdParams {
   uint32_t* dbg;  // development aid: event trace buffer (NULL in normal use)
 };
 
-#ifdef FA4B_SELFCHECK
-// development aid: p.dbg points at host-mapped memory, so the words survive a lost context.
-// word [cta*16 + warp] = last progress code of that warp; word [1024 + cta*16 + warp] = failed check
-#define FA4B_HB(code) do { if (p.dbg && lane == 0) reinterpret_cast<volatile uint32_t*>(p.dbg)[blockIdx.x * 16 + warp] = (uint32_t)(code); } while (0)
-#define FA4B_CONV(site, fail_stmt) do { const unsigned am__ = __activemask(); if (am__ != 0xffffffffu) { if (p.dbg) reinterpret_cast<volatile uint32_t*>(p.dbg)[1024 + blockIdx.x * 16 + warp] = ((uint32_t)(site) << 24) | 0x800000u | (am__ & 0x7fffffu); s.abort_flag = 1u; fail_stmt; } } while (0)
-#else
-#define FA4B_HB(code)
-#define FA4B_CONV(site, fail_stmt)
-#endif
 #ifdef FA4B_ACCT
 // development aid: per-warp cycle accounting by category, flushed once at the end (CTA `FA4B_ACCT_CTA`)
 #define FA4B_ACCT_DECL long long acct[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long acct_t = clock64();
@@ -106,9 +96,6 @@ struct BwdParams {
 #endif
 
 __device__ __forceinline__ float ex2_approx_b(float x) {
-#ifdef FA4B_EXP_NOEX2
-  return x * 0.001f + 0.5f;  // timing experiment: no MUFU work
-#endif
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
@@ -175,7 +162,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     s.abort_flag = 0;
     fence_barrier_init();
   }
-  waitprof_clear(&s.abort_flag);
   if (t < 16) s.c2[t] = (t < G) ? p.k_global[bhk] * p.scale * kLog2e * p.q_global[b * p.Hq + hk * G + t] : 0.f;
   if (warp == 20) tmem_alloc(&s.tmem_base, 512);
   tc_fence_before();
@@ -183,11 +169,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
   tc_fence_after();
   const uint32_t tm = s.tmem_base;
 
-#ifdef FA4B_EXP_NOSYNC
-  if (warp >= 20) {
-    // timing experiment: producer and issuer (and nothing they would feed) stay idle
-  } else
-#endif
   if (warp == 20) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
@@ -201,7 +182,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         const int st = it % kBwdStages;
         if (it >= kBwdStages && !mbar_wait(&s.in_empty[st], ((it / kBwdStages) - 1) & 1, &s.abort_flag, p.status, 110, it)) break;
         issued = it + 1;
-        FA4B_HB(it * 16 + 9);
         const int g = it / n_sub, qs = sub0 + it % n_sub;
         const int bh = b * p.Hq + hk * G + g;
         const int q0 = qs * QT;
@@ -331,7 +311,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         }
         __syncwarp();
         FA4B_TR(2, 113);
-        FA4B_HB(it * 16 + 8);
         return true;
       };
       if (ok) ok = issue_s(0);
@@ -344,7 +323,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       while (ok && id < n_it) {
         bool served = false;
         if (ip < n_it && mbar_test_uniform(&s.pt_ready[ip & 1], (ip >> 1) & 1)) {
-          FA4B_HB(ip * 16 + 7);
           FA4B_ACC(0);  // idle / polling
           ok = pt_phase(ip);
           FA4B_ACC(1);  // pt phase: dV, dP
@@ -382,10 +360,8 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       if (ok && leader) mma_commit(&s.acc_done);
       // every tensor-core operation of this CTA has finished before TMEM is freed
       if (leader) mma_commit(&s.mma_drained);
-      FA4B_HB(0xE0);
       if (leader) mbar_wait_teardown(&s.mma_drained, 0);
       __syncwarp();
-      FA4B_HB(0xE1);
     }
   } else if (warp >= 16) {
     // ------------------------------------------------------------------ dQ drain (warps 16-19)
@@ -398,9 +374,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     const int r = w4 * 32 + lane;  // TMEM lane: d (D = 128) or query row (D = 64)
     FA4B_ACCT_DECL
     for (int it = 0; it < n_it; ++it) {
-      FA4B_HB(it * 16 + 5);
       if (!mbar_wait_warp(&s.dq_full, it & 1, &s.abort_flag, p.status, 130, it)) break;
-      FA4B_CONV(3, break);
       FA4B_ACC(0);  // waiting for dQ
       tc_fence_after();
       const int g = it / n_sub, qs = sub0 + it % n_sub;
@@ -414,9 +388,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       tc_fence_before();
       mbar_arrive_warp(&s.dq_free);  // the next dQ may overwrite the accumulator now
       FA4B_ACC(1);  // load + arrive
-#ifdef FA4B_EXP_NODRAIN
-      if (__uint_as_float(v0[0]) == 123.456f) base[0] = __uint_as_float(v1[0]);  // timing experiment: keep the load, drop the reductions
-#else
       if (D == 128) {
         // lane = d, register i = query row: one coalesced 128-byte reduction per row
 #pragma unroll
@@ -439,9 +410,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           for (int rr = 0; rr < 32; ++rr) atomicAdd(base + (size_t)(w4 * 32 + rr) * D + 32 * hh + lane, patch[rr * 33 + lane]);
         }
       }
-#endif
       FA4B_ACC(2);  // staging + reduction issue
-      FA4B_HB(it * 16 + 6);
     }
     if (w4 == 0) FA4B_ACCT_FLUSH(1);
   } else {
@@ -478,8 +447,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       if (!mbar_wait_warp(&s.st_full[grp], (it >> 1) & 1, &s.abort_flag, p.status, 140, it)) return false;
       FA4B_ACC(2);  // st_full
       if ((warp & 7) == 0) FA4B_TR(grp, 3);
-      FA4B_HB(it * 16 + 1);
-      FA4B_CONV(1, return false);
       tc_fence_after();
       const float* ls = &s.lstat[st][half * CW];
       uint8_t* dst_row = &s.pt[grp][row_base];
@@ -492,10 +459,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         // 2^(s2 + lstat) = 256 P; no clamp at 2^8: the exponent can exceed 8 only by the rounding of
         // LSE, and E4M3 rounds 2^8.0x back to 256.  The masked variant is a separate, warp-uniform
         // path so that the common one carries no compare/select per element.
-#ifdef FA4B_EXP_NOMATH
-        if (v[0] == 0x12345678u) dst_row[0] = 1;  // timing experiment: keep the load, drop math and stores
-        continue;
-#endif
         if (diag) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -530,7 +493,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       tc_fence_before();
       mbar_arrive_warp(&s.pt_ready[grp]);
       FA4B_ACC(4);  // fence + arrive
-      FA4B_HB(it * 16 + 2);
       if ((warp & 7) == 0) FA4B_TR(grp, 1);
       return true;
     };
@@ -544,8 +506,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       if (!mbar_wait_warp(&s.dp_full[grp], (it >> 1) & 1, &s.abort_flag, p.status, 141, it)) return false;
       FA4B_ACC(5);  // dp_full
       if ((warp & 7) == 0) FA4B_TR(grp, 4);
-      FA4B_HB(it * 16 + 3);
-      FA4B_CONV(2, return false);
       tc_fence_after();
       const float* dsm = &s.dstat[st][half * CW];
       uint8_t* dst_row = &s.dst[grp][row_base];
@@ -555,10 +515,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         tmem_ld32(lane_base + C::colX + grp * QT + half * CW + c0, v);
         tmem_ld_wait(v);
         if ((warp & 7) == 0) FA4B_TR(grp, 22);
-#ifdef FA4B_EXP_NOMATH
-        if (v[0] == 0x12345678u) dst_row[0] = 1;
-        continue;
-#endif
         uint32_t dk4[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -582,7 +538,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       tc_fence_before();
       mbar_arrive_warp(&s.ds_ready[grp]);
       FA4B_ACC(7);  // fence + arrive
-      FA4B_HB(it * 16 + 4);
       if ((warp & 7) == 0) FA4B_TR(grp, 2);
       return true;
     };
@@ -594,9 +549,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     }
     if ((warp & 7) == 0) FA4B_ACCT_FLUSH(2 + grp);
     // ------------------------------------------------------------------ dK, dV of this key tile
-    FA4B_HB(0xA0);
     if (ok) ok = mbar_wait_warp(&s.acc_done, 0, &s.abort_flag, p.status, 142);
-    FA4B_HB(0xA1);
     if (ok) {
       // each of the four warps of a TMEM lane quarter writes a quarter of the columns
       tc_fence_after();
@@ -629,12 +582,9 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       }
     }
   }
-  FA4B_HB(0xF0);
   tc_fence_before();
   __syncthreads();
-  waitprof_flush(&s.abort_flag);
   if (warp == 20) tmem_dealloc(tm, 512);
-  FA4B_HB(0xF1);
 }
 
 // dQ = bf16(accumulator / 1024) through the caller's strides
@@ -685,7 +635,7 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   p.dk = static_cast<__nv_bfloat16*>(a.dk); p.dk_sb = a.dk_strides.batch; p.dk_sh = a.dk_strides.head; p.dk_ss = a.dk_strides.seq;
   p.dv = static_cast<__nv_bfloat16*>(a.dv); p.dv_sb = a.dv_strides.batch; p.dv_sh = a.dv_strides.head; p.dv_ss = a.dv_strides.seq;
   p.status = reinterpret_cast<uint32_t*>(ws + l.status);
-#if defined(FA4B_TRACE) || defined(FA4B_SELFCHECK) || defined(FA4B_ACCT)
+#if defined(FA4B_TRACE) || defined(FA4B_ACCT)
   if (const char* e = getenv("FA4B_DEBUG_PTR")) p.dbg = reinterpret_cast<uint32_t*>(strtoull(e, nullptr, 16));
 #endif
   FA4B_CUDA(cudaMemsetAsync(p.status, 0, 16, st));
@@ -743,13 +693,3 @@ void fill_bwd_info(fa4b_info* out) {
 
 }  // namespace fa4b
 
-#ifdef FA4B_WAITPROF
-// development aid (not part of the ABI): copy out and clear the per-site wait statistics of this file's kernels
-extern "C" int fa4b_debug_waitprof_bwd(unsigned long long* host_out) {
-  FA4B_CUDA(cudaDeviceSynchronize());
-  FA4B_CUDA(cudaMemcpyFromSymbol(host_out, fa4b::g_waitprof, sizeof(unsigned long long) * 512));
-  static unsigned long long zeros[512] = {};
-  FA4B_CUDA(cudaMemcpyToSymbol(fa4b::g_waitprof, zeros, sizeof(zeros)));
-  return FA4B_OK;
-}
-#endif

@@ -43,7 +43,6 @@ struct FwdSmem {
   uint32_t tmem_base;
   alignas(8) volatile uint32_t abort_flag;
   uint32_t pad_;
-  FA4B_PROF_FIELD
 };
 
 struct FwdParams {
@@ -59,7 +58,7 @@ struct FwdParams {
   int64_t o_sb, o_sh, o_ss;
   float* lse;
   uint32_t* status;
-  uint32_t* dbg;  // development aid: progress markers in host-mapped memory (NULL in normal use)
+  uint32_t* dbg;  // development aid (FA4B_TRACE builds): event trace buffer, NULL in normal use
 };
 
 #ifdef FA4B_TRACE
@@ -67,16 +66,8 @@ struct FwdParams {
 #else
 #define FA4B_TR(role, ev)
 #endif
-#ifdef FA4B_MARKERS
-#define FA4B_MARK(idx, val) do { if (p.dbg) { reinterpret_cast<volatile uint32_t*>(p.dbg)[idx] = (val); } } while (0)
-#else
-#define FA4B_MARK(idx, val)
-#endif
 
 __device__ __forceinline__ float ex2_approx(float x) {
-#ifdef FA4B_EXP_NOEX2
-  return x * 0.001f + 0.5f;  // timing experiment: no MUFU work
-#endif
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
@@ -133,18 +124,12 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
     s.abort_flag = 0;
     fence_barrier_init();
   }
-  waitprof_clear(&s.abort_flag);
   if (warp == 8) tmem_alloc(&s.tmem_base, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = s.tmem_base;
 
-#ifdef FA4B_EXP_NOSYNC
-  if (warp >= 8 && !(warp >= 8 && warp < 12 && 0)) {
-    // timing experiment: producer and issuer (and nothing they would feed) stay idle
-  } else
-#endif
   if (warp == 8) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
@@ -174,7 +159,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
           tma_load_3d(s.v[st], &map_v, 0, j * 128, bhk, &s.kv_full[st]);
         }
         issued = j + 1;
-        FA4B_MARK(3, 10 + j);
       }
       // no copy of this CTA may still be in flight when its shared memory is given up, and the
       // tensor core's arrivals on the stage barriers must have landed too (nobody else waits for
@@ -301,15 +285,11 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
     const uint64_t c2c2 = pack2(c2, c2);
     bool ok = nb > 0;
     for (int j = 0; ok && j < nb; ++j) {
-      FA4B_PROF_SCOPE(&s.abort_flag, 55);  // whole block step of a softmax warp
-      if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 1);
       ok = mbar_wait_warp(&s.s_full[ti], j & 1, &s.abort_flag, p.status, 30, j);
       if (!ok) break;
-      if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 2);
       tc_fence_after();
       uint32_t x[64];  // raw scores (FP32 bit patterns) of this row against the block's 64 keys
       {
-        FA4B_PROF_SCOPE(&s.abort_flag, 50);
         uint32_t r0[32], r1[32];
         tmem_ld32(lane_base + kColS + 64 * ti, r0);
         tmem_ld32(lane_base + kColS + 64 * ti + 32, r1);
@@ -324,7 +304,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       tc_fence_before();
       mbar_arrive_warp(&s.s_free[ti]);  // the next block's Q.K^T may overwrite S now
       if ((warp & 3) == 0) FA4B_TR(ti, 2);
-      if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 3);
       // keys of this block that lie after the query row (only in the tile's last two blocks)
       const int lim = qt * 128 + row - 64 * j;  // columns <= lim are visible
       const bool diag = p.causal && j >= 2 * qt;  // warp-uniform
@@ -361,7 +340,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       const float f = moved ? ex2_approx(mhat - mnew) : 1.0f;
       if (__any_sync(0xffffffffu, moved)) lsum2 = mul2(lsum2, pack2(f, f));
       mhat = mnew;
-      if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 5);
       // P = 2^(x c2 - mhat + kLift): packed FMA for the exponent, MUFU for the power, packed add for the sum
       const uint64_t shift2 = pack2(kLift - mhat, kLift - mhat);
       uint32_t pa[8], pb[8];  // FP8 route: P as E4M3 words; MXFP4 route: pa = the block's 64 E2M1 codes
@@ -455,7 +433,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       // as soon as one of its rows has a new maximum (factor 1 for the rows that keep theirs)
       if ((warp & 3) == 0) FA4B_TR(ti, 4);
       if (j > 0 && __any_sync(0xffffffffu, moved)) {
-        FA4B_PROF_SCOPE(&s.abort_flag, 54);
 #pragma unroll
         for (int c0 = 0; c0 < D; c0 += 32) {
           uint32_t r[32];
@@ -468,7 +445,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         }
       }
       {
-        FA4B_PROF_SCOPE(&s.abort_flag, 53);
         if constexpr (MX) {
           // this row's 32 bytes of codes in the 32-byte-swizzled tile, its two scale bytes in the page
           *reinterpret_cast<uint4*>(&s.p_mx[ti][swizzled_offset(row, 0, 32)]) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
@@ -484,7 +460,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         mbar_arrive_warp(&s.p_ready[ti][j & 1]);
       }
       if ((warp & 3) == 0) FA4B_TR(ti, 5);
-      if ((t & 127) == 0) FA4B_MARK(1 + ti, 10 * j + 7);
     }
     float lsum;
     {
@@ -494,7 +469,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
     }
     // ---------------------------------------------------------------- epilogue
     if (ok) ok = mbar_wait_warp(&s.o_done[ti], (nb - 1) & 1, &s.abort_flag, p.status, 32, nb);
-    if ((t & 127) == 0) FA4B_MARK(1 + ti, 800);
     if (ok) {
       tc_fence_after();
       // FP8 route: V carries a factor 4.  MXFP4 route: the MMA multiplies code x 2^e on both sides while a value is
@@ -517,15 +491,11 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
           *reinterpret_cast<uint4*>(orow + c0 + 8 * i) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
       }
       p.lse[(size_t)bh * p.S + qt * 128 + row] = (mhat - kLift) * kLn2 + logf(lsum);
-      if ((t & 127) == 0) FA4B_MARK(1 + ti, 801);
     }
   }
   tc_fence_before();
   __syncthreads();
-  waitprof_flush(&s.abort_flag);
-  if (t == 0) FA4B_MARK(4, 1);
   if (warp == 8) tmem_dealloc(tm, 512);
-  if (t == 256) FA4B_MARK(4, 2);
 }
 
 template <int D, bool MX>
@@ -556,7 +526,7 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   p.o_sb = a.o_strides.batch; p.o_sh = a.o_strides.head; p.o_ss = a.o_strides.seq;
   p.lse = a.lse;
   p.status = reinterpret_cast<uint32_t*>(ws + l.status);
-#if defined(FA4B_MARKERS) || defined(FA4B_TRACE)
+#if defined(FA4B_TRACE)
   if (const char* e = getenv("FA4B_DEBUG_PTR")) p.dbg = reinterpret_cast<uint32_t*>(strtoull(e, nullptr, 16));
 #endif
   FA4B_CUDA(cudaMemsetAsync(p.status, 0, 64, st));
@@ -613,13 +583,3 @@ extern "C" int fa4b_attn_fwd(const fa4b_attn_fwd_args* a, void* stream) {
   return launch_attn_fwd(*a, static_cast<cudaStream_t>(stream));
 }
 
-#ifdef FA4B_WAITPROF
-// development aid (not part of the ABI): copy out and clear the per-site wait statistics of this file's kernels
-extern "C" int fa4b_debug_waitprof_fwd(unsigned long long* host_out) {
-  FA4B_CUDA(cudaDeviceSynchronize());
-  FA4B_CUDA(cudaMemcpyFromSymbol(host_out, fa4b::g_waitprof, sizeof(unsigned long long) * 512));
-  static unsigned long long zeros[512] = {};
-  FA4B_CUDA(cudaMemcpyToSymbol(fa4b::g_waitprof, zeros, sizeof(zeros)));
-  return FA4B_OK;
-}
-#endif

@@ -56,7 +56,6 @@ struct GateSmem {
   uint32_t tmem_base;
   alignas(8) volatile uint32_t abort_flag;
   uint32_t pad_;
-  FA4B_PROF_FIELD
 };
 
 // kinds: see fa4b_microgate in the public header; kind 7 = kind 1 with TMA loads
@@ -81,7 +80,6 @@ __global__ void __launch_bounds__(128, 1) microgate_kernel(int kind, int K, cons
     s.abort_flag = 0;
     fence_barrier_init();
   }
-  waitprof_clear(&s.abort_flag);
   if (warp == 0) tmem_alloc(&s.tmem_base, 256);
   tc_fence_before();
   __syncthreads();
@@ -198,7 +196,6 @@ struct PeakSmem {
   uint32_t tmem_base;
   alignas(8) volatile uint32_t abort_flag;
   uint32_t pad_;
-  FA4B_PROF_FIELD
 };
 __global__ void __launch_bounds__(128, 1) tensor_peak_kernel(int kind, int iters, uint32_t* status) {
   extern __shared__ uint8_t raw[];

@@ -25,23 +25,13 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// FA4B_WAIT_SPIN (build-time experiment switch): poll with the non-blocking test_wait instead of
-// try_wait, whose failed attempts may park the thread for an implementation-defined time.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
-#ifdef FA4B_WAIT_SPIN
-  asm volatile(
-      "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-#else
   asm volatile(
       "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
-#endif
   return ok != 0;
 }
 // Bounded wait.  `abort_flag` lives in shared memory: once any role has given up, every
@@ -80,71 +70,12 @@ static __device__ __noinline__ bool mbar_wait_teardown(uint64_t* bar, uint32_t p
   }
 }
 
-#ifdef FA4B_WAITPROF
-// Development aid: cycles spent waiting and number of waits per wait site.  The kernels'
-// shared-memory structs carry `unsigned long long prof[128]` directly behind `abort_flag`
-// (8-byte aligned); one lane per warp accumulates there and the CTA flushes to the global
-// table when it ends, so the measurement does not serialise the GPU on a few addresses.
-static __device__ unsigned long long g_waitprof[512];
-__device__ __forceinline__ unsigned long long* waitprof_base(volatile uint32_t* abort_flag) {
-  return reinterpret_cast<unsigned long long*>(const_cast<uint32_t*>(abort_flag) + 2);
-}
-__device__ __forceinline__ void waitprof_flush(volatile uint32_t* abort_flag) {
-  unsigned long long* pr = waitprof_base(abort_flag);
-  for (int i = threadIdx.x; i < 128; i += blockDim.x)
-    if (pr[i]) atomicAdd(&g_waitprof[(i & 63) + (i >= 64 ? 256 : 0)], pr[i]);
-}
-__device__ __forceinline__ void waitprof_clear(volatile uint32_t* abort_flag) {
-  unsigned long long* pr = waitprof_base(abort_flag);
-  for (int i = threadIdx.x; i < 128; i += blockDim.x) pr[i] = 0ull;
-}
-#define FA4B_PROF_FIELD unsigned long long prof[128];
-// duration of a code section (site ids share the table with the wait sites)
-__device__ __forceinline__ long long prof_now() { return clock64(); }
-__device__ __forceinline__ void prof_add(volatile uint32_t* flag, uint32_t site, long long t0) {
-  if ((threadIdx.x & 31) == 0) {
-    unsigned long long* pr = waitprof_base(flag);
-    atomicAdd(&pr[site & 63], (unsigned long long)(prof_now() - t0));
-    atomicAdd(&pr[64 + (site & 63)], 1ull);
-  }
-}
-struct ProfScope {
-  volatile uint32_t* flag;
-  uint32_t site;
-  long long t0;
-  __device__ __forceinline__ ProfScope(volatile uint32_t* f, uint32_t s) : flag(f), site(s) { t0 = prof_now(); }
-  __device__ __forceinline__ ~ProfScope() { prof_add(flag, site, t0); }
-};
-#define FA4B_PROF_SCOPE(flag, site) ::fa4b::ProfScope prof_scope_##site(flag, site)
-#else
-#define FA4B_PROF_SCOPE(flag, site)
-#define FA4B_PROF_FIELD
-__device__ __forceinline__ void waitprof_flush(volatile uint32_t*) {}
-__device__ __forceinline__ void waitprof_clear(volatile uint32_t*) {}
-#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
                                           uint32_t where, uint32_t detail = 0) {
-#ifdef FA4B_EXP_NOSYNC
-  return true;  // timing experiment only: nothing waits for anything
-#endif
-#ifdef FA4B_WAITPROF
-  const long long t0 = clock64();
-  bool r = false;
-#pragma unroll 1
-  for (int i = 0; i < 32 && !r; ++i) r = mbar_try_wait(bar, parity);
-  if (!r) r = mbar_wait_slow(bar, parity, abort_flag, status, where, detail);
-  if ((threadIdx.x & 31) == 0) {
-    unsigned long long* pr = waitprof_base(abort_flag);
-    atomicAdd(&pr[where & 63], (unsigned long long)(clock64() - t0));
-    atomicAdd(&pr[64 + (where & 63)], 1ull);
-  }
-  return r;
-#else
 #pragma unroll 1
   for (int i = 0; i < 32; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, status, where, detail);
-#endif
 }
 
 // Whole-warp forms.  Every lane runs the same loop on a warp-wide vote, so the warp is still
@@ -193,9 +124,6 @@ static __device__ __noinline__ bool mbar_wait_warp_slow(uint64_t* bar, uint32_t 
 }
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
                                                uint32_t where, uint32_t detail = 0) {
-#ifdef FA4B_EXP_NOSYNC
-  return true;
-#endif
 #pragma unroll 1
   for (int i = 0; i < 32; ++i)
     if (mbar_try_wait_uniform(bar, parity)) return true;
