@@ -211,3 +211,45 @@ def test_forward_without_mask_matches_oracle(B, Hq, Hkv, S, D, pv):
         assert (fwd.lse - lse.cpu()).abs().max() < 1e-3
     with pytest.raises(Exception, match="causal only"):
         attention.attn_backward(o, lse, do.to(DEV), ws)
+
+
+def test_full_size_properties_at_the_benchmark_shape():
+    """C2 (B2, Hq32, Hkv8, S8192, D128) is too large for the CPU oracle as a whole, so the full size is checked
+    through (a) a property: permuting the kv groups permutes O and LSE bit for bit (every statistic is local to a
+    (batch, head) slice); (b) a slab: by (a) one (batch, kv head) unit of the full run equals that unit run alone, so
+    the oracle of one unit (4 query heads, S = 8192) checks O, LSE, dQ, dK, dV of its rows in the full run;
+    (c) dK and dV reproduce bit for bit from run to run and zero dO gives exactly zero gradients."""
+    B, Hq, Hkv, S, D = 2, 32, 8, 8192, 128
+    q, k, v, do = O.make_attention_inputs(1, 4 * Hkv, Hkv, S, D, seed=20260825, rope=True, do_std=0.01)
+    # batch 1 is batch 0 with the kv groups in reverse order: the permutation property and the slab in one run
+    G = Hq // Hkv
+    perm_kv = torch.arange(Hkv - 1, -1, -1)
+    perm_q = (perm_kv[:, None] * G + torch.arange(G)[None, :]).reshape(-1)
+    qd = torch.cat([q, q[:, perm_q]]).to(DEV)
+    kd = torch.cat([k, k[:, perm_kv]]).to(DEV)
+    vd = torch.cat([v, v[:, perm_kv]]).to(DEV)
+    dod = torch.cat([do, do[:, perm_q]]).to(DEV)
+    o, lse, ws = attention.attn_forward(qd, kd, vd)
+    ws.check_status()
+    dq, dk, dv = attention.attn_backward(o, lse, dod, ws)
+    ws.check_status()
+    # (a)
+    pq, pk = perm_q.to(DEV), perm_kv.to(DEV)
+    assert torch.equal(o[1], o[0][pq]) and torch.equal(lse[1], lse[0][pq])
+    assert torch.equal(dk[1], dk[0][pk]) and torch.equal(dv[1], dv[0][pk])
+    # (b) kv head 5 of batch 0 against the oracle of that unit alone
+    hk = 5
+    hq = slice(hk * G, (hk + 1) * G)
+    qu, ku, vu, dou = q[:, hq], k[:, hk:hk + 1], v[:, hk:hk + 1], do[:, hq]
+    fwd = O.attn_forward(qu, ku, vu, query_chunk=512)
+    want = O.attn_backward(qu, ku, vu, fwd.o, fwd.lse, dou, query_chunk=512)
+    assert O.rel_l2(fwd.o, o[0:1, hq].cpu()) < 1e-2 and (fwd.lse - lse[0:1, hq].cpu()).abs().max() < 1e-3
+    for w, g_, name in zip(want, (dq[0:1, hq], dk[0:1, hk:hk + 1], dv[0:1, hk:hk + 1]), ("dq", "dk", "dv")):
+        assert O.rel_l2(w, g_.cpu()) < 2e-2, (name, O.rel_l2(w, g_.cpu()))
+    # (c)
+    dq2, dk2, dv2 = attention.attn_backward(o, lse, dod, ws)
+    ws.check_status()
+    assert torch.equal(dk2, dk) and torch.equal(dv2, dv) and O.rel_l2(dq.float().cpu(), dq2.float().cpu()) < 1e-3
+    dq0, dk0, dv0 = attention.attn_backward(o, lse, torch.zeros_like(dod), ws)
+    ws.check_status()
+    assert not dq0.any() and not dk0.any() and not dv0.any()
