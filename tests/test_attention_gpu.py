@@ -253,3 +253,27 @@ def test_full_size_properties_at_the_benchmark_shape():
     dq0, dk0, dv0 = attention.attn_backward(o, lse, torch.zeros_like(dod), ws)
     ws.check_status()
     assert not dq0.any() and not dk0.any() and not dv0.any()
+
+
+def test_forward_and_backward_replay_from_a_cuda_graph():
+    """The entry points only enqueue work on the caller's stream (memsets, kernels; tensor maps travel by value),
+    so after one warm-up call a forward + backward pair can be captured once and replayed."""
+    B, Hq, Hkv, S, D = 1, 8, 2, 1024, 128
+    q, k, v, do = (t.to(DEV) for t in O.make_attention_inputs(B, Hq, Hkv, S, D, seed=91, rope=True, do_std=0.01))
+    o_ref, lse_ref, ws = attention.attn_forward(q, k, v)
+    grads_ref = attention.attn_backward(o_ref, lse_ref, do, ws)
+    ws.check_status()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        o, lse, ws_g = attention.attn_forward(q, k, v)
+        dq, dk, dv = attention.attn_backward(o, lse, do, ws_g)
+    for _ in range(2):
+        o.zero_()
+        dk.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(o, o_ref) and torch.equal(lse, lse_ref)
+        assert torch.equal(dk, grads_ref[1]) and torch.equal(dv, grads_ref[2])
+        assert O.rel_l2(grads_ref[0].float().cpu(), dq.float().cpu()) < 1e-3
+    ws_g.check_status()
