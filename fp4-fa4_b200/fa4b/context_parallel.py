@@ -12,8 +12,7 @@ point is an integer, the FP8 / FP4 rounding of the probabilities does not depend
 sees, so the partial results are the exact pieces of the single-device computation.
 
 The reference has no such path (data-parallel replicas only,
-``torchtitan/experiments/fa4/exact_lowp_attention.py:4123-4136``); the schedule follows what its survey of
-long-context configurations asks for.  The compute steps go through an ``engine`` so that the schedule can
+``torchtitan/experiments/fa4/exact_lowp_attention.py:4123-4136``).  The compute steps go through an ``engine`` so that the schedule can
 be exercised on CPU ranks (gloo) with the oracle standing in for the kernels.
 """
 

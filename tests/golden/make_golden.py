@@ -13,6 +13,7 @@ reference.  BF16 / FP8 tensors are stored as raw integer bit patterns.
 from __future__ import annotations
 
 import pathlib
+import os
 import sys
 
 import numpy as np
@@ -89,4 +90,4 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FA4_REFERENCE_ROOT", "reference"))
