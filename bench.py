@@ -153,6 +153,47 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def other_configurations(device):
+    """The other configurations of the path on this GPU, for the record beside the headline (rank 0, one GPU each):
+    C3 (D = 64, B16, S4096) forward + backward and C5's forward (S = 131072, MXFP4 P.V) as one rank's three block calls."""
+    from fa4b import attention
+    from fa4b import context_parallel as cp
+
+    out = {}
+    g = torch.Generator(device=device).manual_seed(7)
+    B, Hq, Hkv, S, D = (WORKLOADS["c3"][k] for k in ("B", "Hq", "Hkv", "S", "D"))
+    q, k, v = (torch.randn(B, h, S, D, device=device, generator=g).bfloat16() for h in (Hq, Hkv, Hkv))
+    do = (torch.randn(B, Hq, S, D, device=device, generator=g) * 0.01).bfloat16()
+    ws = attention.alloc_workspace(attention.make_dims(q, k, None, "e4m3_fp8"), device)
+
+    def c3_step():
+        o, lse, _ = attention.attn_forward(q, k, v, workspace=ws)
+        attention.attn_backward(o, lse, do, ws)
+
+    def timed(fn, warm, reps):
+        for _ in range(warm):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        b.synchronize()
+        return a.elapsed_time(b) / reps
+
+    ms = timed(c3_step, 3, 5)
+    ws.check_status()
+    out["c3_B16_Hq32_Hkv8_S4096_D64_fwd_bwd"] = {"ms_per_step": ms, "tflops": 6.0 * causal_matmul_flops(B, Hq, S, D) / (ms * 1e-3) / 1e12}
+    del q, k, v, do, ws
+    B, Hq, Hkv, S, D = (WORKLOADS["c5"][k] for k in ("B", "Hq", "Hkv", "S", "D"))
+    q, k, v = (torch.randn(B, h, S, D, device=device, generator=g).bfloat16() for h in (Hq, Hkv, Hkv))
+    engine = cp.KernelEngine(pv_format="mxfp4_e8m0_block32")
+    ms = timed(lambda: cp.ring_attention_forward(q, k, v, engine), 2, 3)
+    out["c5_B1_Hq32_Hkv8_S131072_D128_fwd_mxfp4_pv_one_rank"] = {"ms_per_step": ms, "tflops": 2.0 * causal_matmul_flops(B, Hq, S, D) / (ms * 1e-3) / 1e12}
+    return out
+
+
 def quantizer_rates(device, reps=10):
     """C4: fused RMSNorm + NVFP4 (row + transposed) and MXFP4 of [16384, 4096] bf16, algorithmic GB/s."""
     import fa4b
@@ -317,6 +358,7 @@ def run_ours(args, rank, world, local_rank):
     fwd_ach = 2.0 * f1 / (fwd_ms * 1e-3) / 1e12
     cpu = cpu_emulation_rate()[0] if extras else None
     quant = quantizer_rates(device) if extras else {}
+    others = other_configurations(device) if (extras and args.workload == "c2") else {}
     for qv in quant.values():
         qv["frac_of_hbm"] = qv["gbs"] / peaks["hbm_gbs"]
     nbytes_in = sum(t.numel() * t.element_size() for t in host)
@@ -348,6 +390,7 @@ def run_ours(args, rank, world, local_rank):
                                  "ms_per_launch_percentiles": pct(fwd_all)}},
         "cpu_baseline": cpu,
         "quantizers": quant,
+        "other_configurations": others,
     }
     print(json.dumps(line), flush=True)
     if world > 1:
