@@ -100,6 +100,16 @@ __device__ __forceinline__ float ex2_approx_b(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// The drain warps' reductions go through the same load/store queue as every other warp of their scheduler;
+// 64 of them back to back fill it and the barrier polls, shared-memory accesses and MMA issues of the compute
+// and issuer warps wait behind them (poll latency 115-150 cycles against 16-35 on an idle SM).  The drain has
+// time to spare, so it stops for about 90 cycles after every eighth reduction: measured 2.61 -> 2.35 ms at the
+// benchmark shape (pauses after every 2nd, 4th or 16th, or of 60 / 140 / 250 cycles, or by __nanosleep: slower).
+__device__ __forceinline__ void drain_pause() {
+  const long long t0 = clock64();
+  while (clock64() - t0 < 90) {
+  }
+}
 __device__ __forceinline__ float2 e4m3x2_to_f32(uint32_t two_bytes) {
   uint32_t h2;
   const uint16_t in = (uint16_t)two_bytes;
@@ -391,9 +401,15 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       if (D == 128) {
         // lane = d, register i = query row: one coalesced 128-byte reduction per row
 #pragma unroll
-        for (int i = 0; i < 32; ++i) atomicAdd(base + (size_t)i * D + r, __uint_as_float(v0[i]));
+        for (int i = 0; i < 32; ++i) {
+          atomicAdd(base + (size_t)i * D + r, __uint_as_float(v0[i]));
+          if ((i & 7) == 7) drain_pause();
+        }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) atomicAdd(base + (size_t)(32 + i) * D + r, __uint_as_float(v1[i]));
+        for (int i = 0; i < 32; ++i) {
+          atomicAdd(base + (size_t)(32 + i) * D + r, __uint_as_float(v1[i]));
+          if ((i & 7) == 7) drain_pause();
+        }
       } else {
         // lane = query row, register i = feature: transpose 32 x 32 blocks through this warp's shared-memory patch
         // so that every reduction instruction covers 128 contiguous bytes of one row (vector reductions of 16 bytes
@@ -407,7 +423,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           for (int i = 0; i < 32; ++i) patch[lane * 33 + i] = __uint_as_float(v[i]);
           __syncwarp();
 #pragma unroll
-          for (int rr = 0; rr < 32; ++rr) atomicAdd(base + (size_t)(w4 * 32 + rr) * D + 32 * hh + lane, patch[rr * 33 + lane]);
+          for (int rr = 0; rr < 32; ++rr) atomicAdd(base + (size_t)(w4 * 32 + rr) * D + 32 * hh + lane, patch[rr * 33 + lane]);  // no pauses: at D = 64 the drain has no time to spare (pausing cost 23 %)
         }
       }
       FA4B_ACC(2);  // staging + reduction issue
