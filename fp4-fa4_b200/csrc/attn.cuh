@@ -41,8 +41,8 @@ inline fa4b_attn_ws_layout make_ws_layout(const fa4b_attn_dims& d) {
   l.k_scales = take(nk * (S / 128) * (D / 64) * 512);
   l.k_global = take(nk * 4);
   l.v_fp8 = take(nk * S * D);
+  l.k_fp8 = take(nk * S * D);  // k_codes .. k_fp8 are one contiguous range: what a sequence-sharded run sends on
   l.q_fp8 = take(nq * S * D);
-  l.k_fp8 = take(nk * S * D);
   l.do_fp8 = take(nq * S * D);
   l.dstat = take(nq * S * 4);
   l.lstat = take(nq * S * 4);
@@ -65,6 +65,7 @@ int launch_attn_prepare(const fa4b_attn_prepare_args& a, cudaStream_t st);
 int launch_attn_fwd(const fa4b_attn_fwd_args& a, cudaStream_t st);
 int launch_attn_bwd_preprocess(const fa4b_attn_bwd_args& a, cudaStream_t st);
 int launch_attn_bwd(const fa4b_attn_bwd_args& a, cudaStream_t st);
+int launch_attn_accumulate(float* acc, const void* part, int64_t n, void* out, cudaStream_t st);
 int launch_attn_merge(float* o_acc, float* lse_acc, const void* o_part, const float* lse_part, int64_t n_rows, int D, void* o_out,
                       cudaStream_t st);
 

@@ -53,3 +53,7 @@ extern "C" int fa4b_attn_merge(float* o_acc, float* lse_acc, const void* o_part,
                                void* o_out, void* stream) {
   return launch_attn_merge(o_acc, lse_acc, o_part, lse_part, n_rows, D, o_out, static_cast<cudaStream_t>(stream));
 }
+
+extern "C" int fa4b_attn_accumulate(float* acc, const void* part, int64_t n, void* out, void* stream) {
+  return launch_attn_accumulate(acc, part, n, out, static_cast<cudaStream_t>(stream));
+}

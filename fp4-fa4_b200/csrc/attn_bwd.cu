@@ -63,6 +63,7 @@ static_assert(sizeof(BwdSmem<128>) + 1024 <= 227 * 1024 && sizeof(BwdSmem<64>) +
 
 struct BwdParams {
   int B, Hq, Hkv, S;
+  int causal;  // 0: every key of the tile is visible to every query (a key shard that precedes the query shard)
   float scale;
   const uint8_t* q_sf;
   const uint8_t* k_sf;
@@ -142,9 +143,9 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
   const int b = bhk / p.Hkv, hk = bhk % p.Hkv;
   const int G = p.Hq / p.Hkv;
   const int sub_per_tile = 128 / QT;
-  const int n_sub = (n_tiles - kt) * sub_per_tile;  // query sub-tiles per head
+  const int n_sub = (p.causal ? n_tiles - kt : n_tiles) * sub_per_tile;  // query sub-tiles per head
   const int n_it = G * n_sub;
-  const int sub0 = kt * sub_per_tile;
+  const int sub0 = p.causal ? kt * sub_per_tile : 0;
   {
     // an earlier CTA of this launch gave up: leave at once, as one (the decision is CTA-uniform)
     __shared__ uint32_t skip;
@@ -451,7 +452,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       const int g = it / n_sub, qs = sub0 + it % n_sub;
       const uint64_t c2c2 = pack2(s.c2[g], s.c2[g]);
       const int q_first = qs * QT + half * CW;     // global query index of this thread's first column
-      const bool diag = qs * QT < kt * 128 + 128;  // sub-tile overlaps the key tile: mask needed
+      const bool diag = p.causal && qs * QT < kt * 128 + 128;  // sub-tile overlaps the key tile: mask needed
       // the row statistics arrive through the async proxy: observe their barrier before reading them
       if ((warp & 7) == 0) FA4B_TR(grp, 10);
       FA4B_ACC(0);  // loop / prologue
@@ -631,20 +632,22 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   const fa4b_attn_dims& d = a.dims;
   const fa4b_attn_ws_layout l = make_ws_layout(d);
   uint8_t* ws = static_cast<uint8_t*>(a.ws);
+  uint8_t* kvws = a.kv_ws ? static_cast<uint8_t*>(const_cast<void*>(a.kv_ws)) : ws;  // K and V operands may be another shard's
   const uint64_t S = d.S, nq = (uint64_t)d.B * d.Hq, nk = (uint64_t)d.B * d.Hkv;
   CUtensorMap m_kc, m_k8, m_v8, m_qc, m_q8, m_do;
-  if (int s = make_tensor_map(&m_kc, ws + l.k_codes, 1, D / 2, S, nk, D / 2, S * (D / 2), D / 2, 128)) return s;
-  if (int s = make_tensor_map(&m_k8, ws + l.k_fp8, 1, D, S, nk, D, S * D, D, 128)) return s;
-  if (int s = make_tensor_map(&m_v8, ws + l.v_fp8, 1, D, S, nk, D, S * D, D, 128)) return s;
+  if (int s = make_tensor_map(&m_kc, kvws + l.k_codes, 1, D / 2, S, nk, D / 2, S * (D / 2), D / 2, 128)) return s;
+  if (int s = make_tensor_map(&m_k8, kvws + l.k_fp8, 1, D, S, nk, D, S * D, D, 128)) return s;
+  if (int s = make_tensor_map(&m_v8, kvws + l.v_fp8, 1, D, S, nk, D, S * D, D, 128)) return s;
   if (int s = make_tensor_map(&m_qc, ws + l.q_codes, 1, D / 2, S, nq, D / 2, S * (D / 2), D / 2, C::QT)) return s;
   if (int s = make_tensor_map(&m_q8, ws + l.q_fp8, 1, D, S, nq, D, S * D, D, C::QT)) return s;
   if (int s = make_tensor_map(&m_do, ws + l.do_fp8, 1, D, S, nq, D, S * D, D, C::QT)) return s;
   BwdParams p{};
   p.B = d.B; p.Hq = d.Hq; p.Hkv = d.Hkv; p.S = d.S;
   p.scale = resolve_scale(d);
-  p.q_sf = ws + l.q_scales; p.k_sf = ws + l.k_scales;
+  p.causal = d.mask == FA4B_MASK_CAUSAL;
+  p.q_sf = ws + l.q_scales; p.k_sf = kvws + l.k_scales;
   p.q_global = reinterpret_cast<const float*>(ws + l.q_global);
-  p.k_global = reinterpret_cast<const float*>(ws + l.k_global);
+  p.k_global = reinterpret_cast<const float*>(kvws + l.k_global);
   p.lstat = reinterpret_cast<const float*>(ws + l.lstat);
   p.dstat = reinterpret_cast<const float*>(ws + l.dstat);
   p.dq_accum = reinterpret_cast<float*>(ws + l.dq_accum);
@@ -655,7 +658,7 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   if (const char* e = getenv("FA4B_DEBUG_PTR")) p.dbg = reinterpret_cast<uint32_t*>(strtoull(e, nullptr, 16));
 #endif
   FA4B_CUDA(cudaMemsetAsync(p.status, 0, 16, st));
-  FA4B_CUDA(cudaMemsetAsync(p.dq_accum, 0, nq * S * D * sizeof(float), st));
+  if (!(a.flags & FA4B_BWD_KEEP_DQ_ACCUM)) FA4B_CUDA(cudaMemsetAsync(p.dq_accum, 0, nq * S * D * sizeof(float), st));
   const int smem = (int)sizeof(BwdSmem<D>) + 1024;
   static std::mutex mu;
   static bool configured[64] = {};
@@ -673,6 +676,7 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   attn_bwd_kernel<D><<<grid, kBwdThreads, smem, st>>>(p, m_kc, m_k8, m_v8, m_qc, m_q8, m_do);
   FA4B_CUDA(cudaGetLastError());
   if (a.ev_after) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_after), st));
+  if (a.flags & FA4B_BWD_SKIP_DQ_OUT) return FA4B_OK;
   const int64_t n_rows = (int64_t)nq * S;
   const unsigned cgrid = (unsigned)std::min<int64_t>((n_rows * (D / 8) + 255) / 256, 148 * 16);
   dq_convert_kernel<D><<<cgrid, 256, 0, st>>>(p.dq_accum, d.Hq, d.S, n_rows, static_cast<__nv_bfloat16*>(a.dq), a.dq_strides.batch,
@@ -690,9 +694,10 @@ static int check_out(const void* ptr, const fa4b_strides& s, const char* name) {
 
 int launch_attn_bwd(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   if (int s = check_dims(a.dims)) return s;
-  FA4B_REQUIRE(a.dims.mask == FA4B_MASK_CAUSAL, FA4B_UNSUPPORTED, "the backward is causal only");
+  FA4B_REQUIRE(!a.kv_ws || (reinterpret_cast<uintptr_t>(a.kv_ws) & 1023) == 0, FA4B_BAD_ALIGN, "kv_ws must be 1024-byte aligned");
   FA4B_REQUIRE(a.dims.pv_format == FA4B_PV_FP8_E4M3, FA4B_UNSUPPORTED, "the MXFP4 P.V route is forward only (a diagnostic route in the reference as well)");
-  if (int s = check_out(a.dq, a.dq_strides, "dq")) return s;
+  if (!(a.flags & FA4B_BWD_SKIP_DQ_OUT))
+    if (int s = check_out(a.dq, a.dq_strides, "dq")) return s;
   if (int s = check_out(a.dk, a.dk_strides, "dk")) return s;
   if (int s = check_out(a.dv, a.dv_strides, "dv")) return s;
   if (!a.preprocessed) {

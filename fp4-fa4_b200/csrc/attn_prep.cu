@@ -264,6 +264,37 @@ __global__ void __launch_bounds__(256) merge_kernel(float* __restrict__ o_acc, f
   }
 }
 
+__global__ void __launch_bounds__(256) accumulate_kernel(float* __restrict__ acc, const __nv_bfloat16* __restrict__ part, int64_t n_vec,
+                                                         __nv_bfloat16* __restrict__ out) {
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * 256) {
+    const uint4 pv = __ldg(reinterpret_cast<const uint4*>(part) + i);
+    float4 a0 = reinterpret_cast<float4*>(acc)[2 * i], a1 = reinterpret_cast<float4*>(acc)[2 * i + 1];
+    a0.x += bf16_bits_to_f32(pv.x & 0xffffu); a0.y += bf16_bits_to_f32(pv.x >> 16);
+    a0.z += bf16_bits_to_f32(pv.y & 0xffffu); a0.w += bf16_bits_to_f32(pv.y >> 16);
+    a1.x += bf16_bits_to_f32(pv.z & 0xffffu); a1.y += bf16_bits_to_f32(pv.z >> 16);
+    a1.z += bf16_bits_to_f32(pv.w & 0xffffu); a1.w += bf16_bits_to_f32(pv.w >> 16);
+    reinterpret_cast<float4*>(acc)[2 * i] = a0;
+    reinterpret_cast<float4*>(acc)[2 * i + 1] = a1;
+    if (out) {
+      const __nv_bfloat162 h0 = __floats2bfloat162_rn(a0.x, a0.y), h1 = __floats2bfloat162_rn(a0.z, a0.w);
+      const __nv_bfloat162 h2 = __floats2bfloat162_rn(a1.x, a1.y), h3 = __floats2bfloat162_rn(a1.z, a1.w);
+      reinterpret_cast<uint4*>(out)[i] = make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
+                                                    *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
+    }
+  }
+}
+
+int launch_attn_accumulate(float* acc, const void* part, int64_t n, void* out, cudaStream_t st) {
+  FA4B_REQUIRE(acc && part && n > 0 && n % 8 == 0, FA4B_BAD_ARG, "fa4b_attn_accumulate: NULL pointer or n not a positive multiple of 8");
+  FA4B_REQUIRE(((reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(part) | reinterpret_cast<uintptr_t>(out)) & 15) == 0, FA4B_BAD_ALIGN,
+               "fa4b_attn_accumulate: 16-byte alignment");
+  const int64_t n_vec = n / 8;
+  const unsigned grid = (unsigned)std::min<int64_t>((n_vec + 255) / 256, 148 * 16);
+  accumulate_kernel<<<grid, 256, 0, st>>>(acc, static_cast<const __nv_bfloat16*>(part), n_vec, static_cast<__nv_bfloat16*>(out));
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
+}
+
 int launch_attn_merge(float* o_acc, float* lse_acc, const void* o_part, const float* lse_part, int64_t n_rows, int D, void* o_out,
                       cudaStream_t st) {
   FA4B_REQUIRE(o_acc && lse_acc && o_part && lse_part, FA4B_BAD_ARG, "fa4b_attn_merge: NULL pointer");

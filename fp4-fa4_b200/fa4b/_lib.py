@@ -76,7 +76,7 @@ class AttnBwdArgs(C.Structure):
     _fields_ = [("dims", AttnDims), ("o", C.c_void_p), ("o_strides", Strides), ("dout", C.c_void_p), ("do_strides", Strides),
                 ("lse", C.c_void_p), ("dq", C.c_void_p), ("dq_strides", Strides), ("dk", C.c_void_p), ("dk_strides", Strides),
                 ("dv", C.c_void_p), ("dv_strides", Strides), ("ws", C.c_void_p), ("preprocessed", C.c_int32),
-                ("ev_before", C.c_void_p), ("ev_after", C.c_void_p)]
+                ("ev_before", C.c_void_p), ("ev_after", C.c_void_p), ("kv_ws", C.c_void_p), ("flags", C.c_int32)]
 
 
 class Info(C.Structure):
@@ -89,7 +89,7 @@ EXPORTS = (
     "fa4b_status_string", "fa4b_last_error", "fa4b_query", "fa4b_amax", "fa4b_quant_nvfp4",
     "fa4b_rmsnorm_quant_nvfp4", "fa4b_quant_mxfp4", "fa4b_dequant_nvfp4", "fa4b_dequant_mxfp4",
     "fa4b_attn_workspace_bytes", "fa4b_attn_ws_layout_query", "fa4b_attn_prepare", "fa4b_attn_fwd",
-    "fa4b_attn_fwd_static", "fa4b_attn_bwd_preprocess", "fa4b_attn_bwd", "fa4b_attn_check_status", "fa4b_attn_merge", "fa4b_rmsnorm_bwd", "fa4b_rmsnorm_bwd_workspace_bytes", "fa4b_microgate", "fa4b_tensor_peak",
+    "fa4b_attn_fwd_static", "fa4b_attn_bwd_preprocess", "fa4b_attn_bwd", "fa4b_attn_check_status", "fa4b_attn_merge", "fa4b_attn_accumulate", "fa4b_rmsnorm_bwd", "fa4b_rmsnorm_bwd_workspace_bytes", "fa4b_microgate", "fa4b_tensor_peak",
 )
 
 _lib = None

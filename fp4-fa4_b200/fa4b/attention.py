@@ -176,6 +176,39 @@ def attn_backward(o, lse, dout, ws: Workspace, preprocessed: bool = False, event
     return dq, dk, dv
 
 
+BWD_KEEP_DQ_ACCUM, BWD_SKIP_DQ_OUT = 1, 2
+
+
+def attn_backward_prepared(ws: Workspace, kv_ws: Workspace | None = None, causal: bool = True, keep_dq_accum: bool = False,
+                           write_dq: bool = True):
+    """Backward block call on published operands and statistics: queries, dO and the row statistics from ``ws``
+    (:func:`attn_bwd_preprocess` has run on it with the LSE and O of the whole sequence), keys and values from
+    ``kv_ws`` (default ``ws``).  Returns ``(dq | None, dk, dv)``: dK and dV of this block alone (bf16); the query
+    gradient accumulates in ``ws``'s FP32 scratch across calls with ``keep_dq_accum`` and is only converted into
+    ``dq`` when ``write_dq``."""
+    d = ws.dims
+    dims = _lib.AttnDims(d.B, d.Hq, d.Hkv, d.S, d.D, d.softmax_scale, d.pv_format, 0 if causal else 1)
+    dev = ws.buf.device
+    dq = torch.empty(d.B, d.Hq, d.S, d.D, dtype=torch.bfloat16, device=dev) if write_dq else None
+    dk = torch.empty(d.B, d.Hkv, d.S, d.D, dtype=torch.bfloat16, device=dev)
+    dv = torch.empty_like(dk)
+    z = _lib.Strides()
+    flags = (BWD_KEEP_DQ_ACCUM if keep_dq_accum else 0) | (0 if write_dq else BWD_SKIP_DQ_OUT)
+    a = _lib.AttnBwdArgs(dims, 0, z, 0, z, 0, ptr(dq) if write_dq else 0, _strides(dq) if write_dq else z, ptr(dk), _strides(dk),
+                         ptr(dv), _strides(dv), ptr(ws.buf), 1, 0, 0, ptr(kv_ws.buf) if kv_ws is not None else 0, flags)
+    check(lib().fa4b_attn_bwd(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_bwd")
+    return dq, dk, dv
+
+
+def attn_accumulate(acc: torch.Tensor, part: torch.Tensor, out: torch.Tensor | None = None) -> None:
+    """``acc (f32) += part (bf16)`` in place; with ``out`` (bf16) also write the sums there."""
+    for t in (acc, part) + ((out,) if out is not None else ()):
+        if not t.is_contiguous():
+            raise ValueError("attn_accumulate needs contiguous tensors")
+    check(lib().fa4b_attn_accumulate(C.c_void_p(ptr(acc)), C.c_void_p(ptr(part)), C.c_int64(acc.numel()),
+                                     C.c_void_p(ptr(out) if out is not None else 0), C.c_void_p(current_stream())), "fa4b_attn_accumulate")
+
+
 def attn_bwd_preprocess(o, lse, dout, ws: Workspace):
     d = ws.dims
     a = _lib.AttnBwdArgs(d, ptr(o), _strides(o), ptr(dout), _strides(dout), ptr(lse), 0, _lib.Strides(), 0, _lib.Strides(), 0,

@@ -7,7 +7,8 @@ data path: an ``all_reduce(MAX)`` of ``B*(Hq+Hkv)`` floats) and then publish the
 equals the single-device one up to the rounding of the merge.  The K/V operands then travel round the ring
 (``N-1`` hops of one contiguous byte range per chunk) while every rank runs, per visiting shard, the block
 calls causality leaves: a chunk against an earlier chunk is unmasked, against itself causal, against a later
-one skipped.  Partial results are folded with their log-sum-exp.  Because the kernels' softmax reference
+one skipped.  Partial results are folded with their log-sum-exp.  The backward sends the operands round once more
+together with FP32 dK / dV sums of their chunk.  Because the kernels' softmax reference
 point is an integer, the FP8 / FP4 rounding of the probabilities does not depend on which keys a block call
 sees, so the partial results are the exact pieces of the single-device computation.
 
@@ -97,10 +98,28 @@ class KernelEngine:
     def finish(self, acc):
         return acc[0].to(torch.bfloat16), acc[1]
 
+    # ---- backward pieces
+    def preprocess(self, ws, o, lse, dout):
+        self.A.attn_bwd_preprocess(o, lse, dout, ws)
 
-def ring_attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, engine, group=None):
+    def bwd_block(self, ws_q, ws_kv, causal, keep_dq, write_dq):
+        return self.A.attn_backward_prepared(ws_q, ws_kv, causal=causal, keep_dq_accum=keep_dq, write_dq=write_dq)
+
+    def new_kv_acc(self, ws):
+        d, dev = ws.dims, ws.buf.device
+        return [torch.zeros(d.B, d.Hkv, d.S, d.D, dtype=torch.float32, device=dev) for _ in range(2)]
+
+    def accumulate(self, acc, part):
+        self.A.attn_accumulate(acc, part)
+
+    def finish_kv(self, acc):
+        return acc.to(torch.bfloat16)
+
+
+def ring_attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, engine, group=None, return_state: bool = False):
     """Causal attention of the whole sequence given this rank's zig-zag shard ``q [B,Hq,S/N,D]``, ``k, v
-    [B,Hkv,S/N,D]`` (:func:`shard_sequence` order).  Returns this rank's rows of O (bf16) and LSE (f32)."""
+    [B,Hkv,S/N,D]`` (:func:`shard_sequence` order).  Returns this rank's rows of O (bf16) and LSE (f32), and with
+    ``return_state`` the published operand caches of the two local chunks for :func:`ring_attention_backward`."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     halves = [tuple(t.chunk(2, dim=2)[i].contiguous() for t in (q, k, v)) for i in range(2)]
@@ -131,4 +150,56 @@ def ring_attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, en
         if step + 1 < world:
             visiting = nxt
     outs = [engine.finish(a) for a in accs]
-    return torch.cat([outs[0][0], outs[1][0]], dim=2), torch.cat([outs[0][1], outs[1][1]], dim=2)
+    o, lse = torch.cat([outs[0][0], outs[1][0]], dim=2), torch.cat([outs[0][1], outs[1][1]], dim=2)
+    return (o, lse, local) if return_state else (o, lse)
+
+
+def ring_attention_backward(o: torch.Tensor, lse: torch.Tensor, dout: torch.Tensor, state, engine, group=None):
+    """Gradients of :func:`ring_attention_forward` for this rank's shard: ``dq [B,Hq,S/N,D]``, ``dk, dv
+    [B,Hkv,S/N,D]`` (bf16).  ``state`` is the forward's (the two local operand caches); ``o``, ``lse`` are the
+    forward's results for the local rows, i.e. of the whole sequence, so every block call recomputes its piece of
+    the true probabilities.  The K/V operands go round the ring once more, now together with FP32 dK / dV sums of
+    their chunk that every rank adds its block calls to; one last hop takes the sums home.  dQ accumulates in the
+    local cache's FP32 scratch across the block calls of a query chunk."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    local = state
+    for i in range(2):
+        engine.preprocess(local[i], *(t.chunk(2, dim=2)[i].contiguous() for t in (o, lse, dout)))
+    # every block call of this rank, in ring order, to know the first and the last one of each query chunk
+    calls = [(step, qi, ki, causal) for step in range(world) for qi, ki, causal in block_schedule(rank, (rank - step) % world, world)]
+    first = {qi: min(i for i, c in enumerate(calls) if c[1] == qi) for qi in (0, 1)}
+    last = {qi: max(i for i, c in enumerate(calls) if c[1] == qi) for qi in (0, 1)}
+    dq = [None, None]
+    visiting = local
+    sums = [engine.new_kv_acc(local[i]) for i in range(2)]  # [chunk][dk, dv], travelling with the chunk
+    spare = [[engine.empty_like_chunk(local[i]) for i in range(2)] for _ in range(2)] if world > 1 else None
+    spare_sums = [[engine.new_kv_acc(local[i]) for i in range(2)] for _ in range(2)] if world > 1 else None
+    idx = 0
+    for step in range(world):
+        while idx < len(calls) and calls[idx][0] == step:
+            _, qi, ki, causal = calls[idx]
+            got = engine.bwd_block(local[qi], visiting[ki], causal, keep_dq=(idx != first[qi]), write_dq=(idx == last[qi]))
+            if idx == last[qi]:
+                dq[qi] = got[0]
+            engine.accumulate(sums[ki][0], got[1])
+            engine.accumulate(sums[ki][1], got[2])
+            idx += 1
+        if world > 1:
+            nxt, nxt_sums = spare[step % 2], spare_sums[step % 2]
+            ops = []
+            for i in range(2):
+                if step + 1 < world:  # the operands are not needed after the last step, the sums go home
+                    ops.append(dist.P2POp(dist.isend, engine.kv_payload(visiting[i]), (rank + 1) % world, group))
+                    ops.append(dist.P2POp(dist.irecv, engine.kv_payload(nxt[i]), (rank - 1) % world, group))
+                for j in range(2):
+                    ops.append(dist.P2POp(dist.isend, sums[i][j], (rank + 1) % world, group))
+                    ops.append(dist.P2POp(dist.irecv, nxt_sums[i][j], (rank - 1) % world, group))
+            for r in dist.batch_isend_irecv(ops):
+                r.wait()
+            if step + 1 < world:
+                visiting = nxt
+            sums = nxt_sums
+    dk = torch.cat([engine.finish_kv(sums[0][0]), engine.finish_kv(sums[1][0])], dim=2)
+    dv = torch.cat([engine.finish_kv(sums[0][1]), engine.finish_kv(sums[1][1])], dim=2)
+    return torch.cat(dq, dim=2), dk, dv

@@ -40,6 +40,8 @@ const char* fa4b_last_error(void);
 enum { FA4B_PV_FP8_E4M3 = 0, FA4B_PV_MXFP4_E8M0 = 1 };  /* fa4.exact_pv_format */
 enum { FA4B_MASK_CAUSAL = 0, FA4B_MASK_NONE = 1 };
 enum { FA4B_MX_CEIL = 0, FA4B_MX_RTE_MANTISSA = 1, FA4B_MX_FLOOR = 2 };
+/* fa4b_attn_bwd flags: a sequence-sharded run folds several key shards into one query shard's dQ */
+enum { FA4B_BWD_KEEP_DQ_ACCUM = 1 /* do not zero the accumulator first */, FA4B_BWD_SKIP_DQ_OUT = 2 /* do not convert it into dq */ };
 enum { FA4B_PREPARE_ALL = 0, FA4B_PREPARE_AMAX = 1, FA4B_PREPARE_QUANTIZE = 2 };
 enum { FA4B_LAYOUT_BHSD = 0, FA4B_LAYOUT_BSHD = 1 };
 
@@ -269,6 +271,9 @@ typedef struct fa4b_attn_bwd_args {
   int32_t preprocessed; /* non-zero: fa4b_attn_bwd_preprocess already ran on ws */
   void* ev_before;      /* optional cudaEvent_t around the main backward kernel */
   void* ev_after;
+  const void* kv_ws;    /* optional: a second operand cache of the same dims whose K and V sections are used instead
+                           of `ws`'s (the keys of another sequence shard); the queries, dO and statistics stay `ws`'s */
+  int32_t flags;        /* FA4B_BWD_*: how this call treats the FP32 dQ accumulator of `ws` */
 } fa4b_attn_bwd_args;
 int fa4b_attn_bwd_preprocess(const fa4b_attn_bwd_args* a, void* stream);
 
@@ -276,8 +281,14 @@ int fa4b_attn_bwd_preprocess(const fa4b_attn_bwd_args* a, void* stream);
  * backward_nvfp4_score_e4m3_qkv_e5m2_dout_bshd_precleared_dq_out
  * (tk_fa4/native_gqa_tk_bwd/v509_*bshd.cu:406-444) and the D64 kernel v416.
  * Runs the preprocess step itself unless `preprocessed` is set.  Uses the
- * workspace's FP32 dQ accumulator as scratch (zeroed here). */
+ * workspace's FP32 dQ accumulator as scratch (zeroed here unless FA4B_BWD_KEEP_DQ_ACCUM).  With
+ * dims.mask = FA4B_MASK_NONE every key is visible to every query (a key shard that precedes the query shard);
+ * the statistics must then come from the LSE and O of the whole sequence. */
 int fa4b_attn_bwd(const fa4b_attn_bwd_args* a, void* stream);
+
+/* fa4b_attn_accumulate: acc[i] += part[i] (FP32 += bf16) over n values, n % 8 == 0; with out != NULL the sums are
+ * also written as bf16.  Folds the dK / dV of one block call into a running FP32 sum (no reference counterpart). */
+int fa4b_attn_accumulate(float* acc, const void* part, int64_t n, void* out, void* stream);
 
 /* fa4b_attn_check_status: synchronises `stream`, then reports FA4B_TIMEOUT if a
  * bounded wait inside the last attention kernel on this workspace gave up

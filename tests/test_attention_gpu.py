@@ -209,8 +209,18 @@ def test_forward_without_mask_matches_oracle(B, Hq, Hkv, S, D, pv):
     assert O.rel_l2(fwd.lse, lse.cpu()) < 1e-2
     if pv == "e4m3_fp8":
         assert (fwd.lse - lse.cpu()).abs().max() < 1e-3
-    with pytest.raises(Exception, match="causal only"):
-        attention.attn_backward(o, lse, do.to(DEV), ws)
+    if pv != "e4m3_fp8":
+        with pytest.raises(Exception, match="forward only"):
+            attention.attn_backward(o, lse, do.to(DEV), ws)
+        return
+    # the unmasked backward (the workspace remembers the mask of its forward)
+    dq, dk, dv = attention.attn_backward(o, lse, do.to(DEV), ws)
+    ws.check_status()
+    do5, dstat, lstat = O.attn_bwd_preprocess(fwd.o, do, fwd.lse)
+    want = O.attn_backward_operands(O.quantize_qk_heads(q)[3], O.fp8_operand(q).float(), O.quantize_qk_heads(k)[3], O.fp8_operand(k).float(),
+                                    O.fp8_operand(v).float(), do5.float(), dstat, lstat, D ** -0.5, causal=False)
+    for w, g_, name in zip(want, (dq, dk, dv), ("dq", "dk", "dv")):
+        assert O.rel_l2(w / 1024, g_.float().cpu()) < 2e-2, (name, O.rel_l2(w / 1024, g_.float().cpu()))
 
 
 def test_full_size_properties_at_the_benchmark_shape():
@@ -277,3 +287,61 @@ def test_forward_and_backward_replay_from_a_cuda_graph():
         assert torch.equal(dk, grads_ref[1]) and torch.equal(dv, grads_ref[2])
         assert O.rel_l2(grads_ref[0].float().cpu(), dq.float().cpu()) < 1e-3
     ws_g.check_status()
+
+
+def test_backward_block_calls_against_oracle_and_the_single_kernel():
+    """The pieces a sequence-sharded backward is made of: an unmasked block call with the keys of another operand
+    cache (against the oracle's operand-level arithmetic), and a causal run split into block calls over two
+    sequence halves that accumulate dQ in the workspace and dK/dV through fa4b_attn_accumulate (against the single
+    kernel over the whole sequence)."""
+    B, Hq, Hkv, S, D = 1, 4, 1, 512, 128
+    q, k, v, do = O.make_attention_inputs(B, Hq, Hkv, S, D, seed=515, rope=True, do_std=0.01)
+    qd_, kd_, vd_, dod = (t.to(DEV) for t in (q, k, v, do))
+    o, lse, ws = attention.attn_forward(qd_, kd_, vd_)
+    dq_ref, dk_ref, dv_ref = attention.attn_backward(o, lse, dod, ws)
+    ws.check_status()
+    # the two halves as their own operand caches, quantised with the amax of the whole sequence
+    h = S // 2
+    halves = []
+    for i in range(2):
+        sl = slice(i * h, (i + 1) * h)
+        qs, ks, vs = (t[:, :, sl].contiguous() for t in (qd_, kd_, vd_))
+        w = attention.alloc_workspace(attention.make_dims(qs, ks, None, "e4m3_fp8"), DEV)
+        attention.attn_prepare(qs, ks, vs, w, phase="amax")
+        halves.append((w, qs, ks, vs))
+    amax = torch.maximum(halves[0][0].amax(), halves[1][0].amax()).clone()
+    assert torch.equal(amax, ws.amax())
+    for i, (w, qs, ks, vs) in enumerate(halves):
+        w.amax().copy_(amax)
+        attention.attn_prepare(qs, ks, vs, w, phase="quantize")
+        sl = slice(i * h, (i + 1) * h)
+        attention.attn_bwd_preprocess(o[:, :, sl].contiguous(), lse[:, :, sl].contiguous(), dod[:, :, sl].contiguous(), w)
+    w0, w1 = halves[0][0], halves[1][0]
+    # unmasked block (queries of the late half, keys of the early half) against the oracle
+    _, dk_blk, dv_blk = attention.attn_backward_prepared(w1, w0, causal=False, write_dq=False)
+    w1.check_status()
+    fwd = O.attn_forward(q, k, v)
+    do5, dstat, lstat = O.attn_bwd_preprocess(fwd.o, do, fwd.lse)
+    am_q, am_k = q.float().abs().amax(dim=(2, 3)), k.float().abs().amax(dim=(2, 3))
+    qdq = O.quantize_qk_heads(q[:, :, h:], am_q)[3]
+    kdq = O.quantize_qk_heads(k[:, :, :h], am_k)[3]
+    want = O.attn_backward_operands(qdq, O.fp8_operand(q[:, :, h:]).float(), kdq, O.fp8_operand(k[:, :, :h]).float(),
+                                    O.fp8_operand(v[:, :, :h]).float(), do5[:, :, h:].float(), dstat[:, :, h:], lstat[:, :, h:],
+                                    D ** -0.5, causal=False)
+    assert O.rel_l2(want[1] / 1024, dk_blk.float().cpu()) < 2e-2 and O.rel_l2(want[2] / 1024, dv_blk.float().cpu()) < 2e-2
+    # the whole causal run as three block calls
+    dk_acc = torch.zeros(B, Hkv, S, D, dtype=torch.float32, device=DEV)
+    dv_acc = torch.zeros_like(dk_acc)
+    dq0, dk00, dv00 = attention.attn_backward_prepared(w0, w0, causal=True)                      # early x early
+    _, dk10, dv10 = attention.attn_backward_prepared(w1, w0, causal=False, write_dq=False)        # late x early
+    dq1, dk11, dv11 = attention.attn_backward_prepared(w1, w1, causal=True, keep_dq_accum=True)   # late x late
+    w0.check_status()
+    w1.check_status()
+    for acc, parts in ((dk_acc, (dk00, dk10, dk11)), (dv_acc, (dv00, dv10, dv11))):
+        lo, hi = acc[:, :, :h].contiguous(), acc[:, :, h:].contiguous()
+        attention.attn_accumulate(lo, parts[0])
+        attention.attn_accumulate(lo, parts[1])
+        attention.attn_accumulate(hi, parts[2])
+        acc[:, :, :h], acc[:, :, h:] = lo, hi
+    assert O.rel_l2(dq_ref.float().cpu(), torch.cat([dq0, dq1], dim=2).float().cpu()) < 2e-3
+    assert O.rel_l2(dk_ref.float().cpu(), dk_acc.cpu()) < 4e-3 and O.rel_l2(dv_ref.float().cpu(), dv_acc.cpu()) < 4e-3
