@@ -23,7 +23,7 @@
 
 namespace fa4b {
 
-constexpr int kBwdThreads = 704;
+constexpr int kBwdThreads = 768;
 constexpr int kBwdStages = 5;
 
 template <int D>
@@ -103,12 +103,14 @@ __device__ __forceinline__ float ex2_approx_b(float x) {
 }
 // The drain warps' reductions go through the same load/store queue as every other warp of their scheduler;
 // 64 of them back to back fill it and the barrier polls, shared-memory accesses and MMA issues of the compute
-// and issuer warps wait behind them (poll latency 115-150 cycles against 16-35 on an idle SM).  The drain has
-// time to spare, so it stops for about 90 cycles after every eighth reduction: measured 2.61 -> 2.35 ms at the
-// benchmark shape (pauses after every 2nd, 4th or 16th, or of 60 / 140 / 250 cycles, or by __nanosleep: slower).
+// and issuer warps wait behind them (poll latency 115-150 cycles against 16-35 on an idle SM).  So the drain
+// stops for about 60 cycles after every eighth reduction.  With one issuer warp the pauses were worth 10 %
+// (2.61 -> 2.35 ms at the benchmark shape, best at 90 cycles); with one issuer warp per stream they are worth
+// 2 % (2.24 -> 2.19 ms) and the drain itself is the longest loop of the CTA (poll, load, 64 reductions per
+// sub-tile), so longer or more frequent pauses cost time: 120 cycles 2.45 ms, after every 4th 2.64 ms.
 __device__ __forceinline__ void drain_pause() {
   const long long t0 = clock64();
-  while (clock64() - t0 < 90) {
+  while (clock64() - t0 < 60) {
   }
 }
 __device__ __forceinline__ float2 e4m3x2_to_f32(uint32_t two_bytes) {
@@ -158,7 +160,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     mbar_init(&s.kv_full, 1);
     for (int i = 0; i < kBwdStages; ++i) {
       mbar_init(&s.in_full[i], 1);
-      mbar_init(&s.in_empty[i], 1);
+      mbar_init(&s.in_empty[i], 2);  // the S/dK stream and the dQ stream each release a stage
     }
     for (int i = 0; i < 2; ++i) {  // one set per compute group
       mbar_init(&s.st_full[i], 1);
@@ -168,8 +170,8 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     }
     mbar_init(&s.dq_full, 1);
     mbar_init(&s.dq_free, 4);
-    mbar_init(&s.acc_done, 1);
-    mbar_init(&s.mma_drained, 1);
+    mbar_init(&s.acc_done, 3);     // one commit per issuer warp
+    mbar_init(&s.mma_drained, 3);
     s.abort_flag = 0;
     fence_barrier_init();
   }
@@ -213,11 +215,17 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         if (issued == n_it && !s.abort_flag) mbar_wait_teardown(&s.in_empty[it % kBwdStages], (it / kBwdStages) & 1);
       }
     }
-  } else if (warp == 21) {
-    // ------------------------------------------------------------------ MMA issuer
-    // The whole warp runs this loop so that control flow and descriptors stay warp-uniform; one
-    // elected lane (always the same) issues the tensor-core instructions and their commits.
+  } else if (warp >= 21) {
+    // ------------------------------------------------------------------ MMA issuers (warps 21-23)
+    // Three warps, one per in-order stream of tensor-core work, so that no stream's wait holds up another's
+    // issue: warp 21 answers pt_ready (dV, dP); warp 22 answers ds_ready with S of the group's next sub-tile
+    // and dK; warp 23 answers ds_ready with dQ once the drain has handed the dQ accumulator back.  A whole
+    // warp runs each loop so that control flow and descriptors stay warp-uniform; one elected lane (always
+    // the same) issues the tensor-core instructions and their commits.  A commit covers only the issuing
+    // thread's operations, so every reuse of a buffer that another stream reads is ordered through a barrier
+    // that the reader's own stream commits, or through the compute warps' observation of one.
     {
+      const int stream = warp - 21;  // 0: dV, dP   1: S, dK   2: dQ
       const bool leader = elect_one();
       constexpr uint32_t id_s = idesc_fp4(128, QT, 0, 0, 0);
       constexpr uint32_t id_dp = idesc_f8(128, QT, 0, 1, 0, 0);   // V8 (E4M3, K-major) x dO5 (E5M2, K-major)
@@ -240,20 +248,30 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       if (ok) {
         tc_fence_after();
 #pragma unroll
-        for (int pg = 0; pg < kPages; ++pg) if (leader) tmem_cp_page(tm + C::colSfa + 4 * pg, make_page_desc(smem_u32(s.k_sf + 512 * pg)));
+        for (int pg = 0; pg < kPages; ++pg)
+          if (leader && stream == 1) tmem_cp_page(tm + C::colSfa + 4 * pg, make_page_desc(smem_u32(s.k_sf + 512 * pg)));
       }
       // S^T of sub-tile `it` (inputs in its stage) into the buffer of the sub-tile's group; the caller
       // has made sure the buffer is free
       auto stage_of = [](int it) { return (uint32_t)(it % kBwdStages); };
-      auto issue_s = [&](int it) -> bool {
-        const uint32_t st = stage_of(it), g = it & 1;
+      // in two parts: the scale factors go to TMEM as soon as the stage has landed (in order behind the
+      // previous S on this thread), the MMAs follow when the buffer is free
+      auto prep_s = [&](int it) -> bool {
+        const uint32_t st = stage_of(it);
         if (!mbar_wait_warp(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 121, it)) return false;
         tc_fence_after();
-        // D = 128: which 64 rows of the 128-row scale page (sub-tiles alternate, sub0 is even)
-        const uint32_t sf_shift = (QT == 64) ? 2u * (uint32_t)((it % n_sub) & 1) : 0u;
         if (leader) {
 #pragma unroll
           for (int pg = 0; pg < kPages; ++pg) tmem_cp_page(tm + C::colSfb + 4 * pg, d_sfq0 + st * kSf16 + (pg * 512 >> 4));
+        }
+        __syncwarp();
+        return true;
+      };
+      auto fire_s = [&](int it) {
+        const uint32_t st = stage_of(it), g = it & 1;
+        // D = 128: which 64 rows of the 128-row scale page (sub-tiles alternate, sub0 is even)
+        const uint32_t sf_shift = (QT == 64) ? 2u * (uint32_t)((it % n_sub) & 1) : 0u;
+        if (leader) {
           const uint64_t qc = d_qc0 + st * kQc16;
 #pragma unroll
           for (int k = 0; k < D / 64; ++k)
@@ -261,16 +279,17 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           mma_commit(&s.st_full[g]);
         }
         __syncwarp();
-        return true;
       };
-      // The two compute groups alternate sub-tiles and each runs  P(it); dS(it).  Per sub-tile the
-      // issuer answers two events, in sub-tile order:
+      // The two compute groups alternate sub-tiles and each runs  P(it); dS(it).  Per sub-tile:
       //   pt_ready(it) -> dV(it), then dP(it) into the group's buffer (P has been read out of it)
-      //   ds_ready(it) -> S(it+2) into the same buffer (dS has been read out of it), dK(it), dQ(it)
-      // Each kind is answered in sub-tile order (the dQ drain relies on that order); between the two
-      // kinds the issuer takes whichever event is there, so neither group waits behind the other.
+      //   ds_ready(it) -> S(it+2) into the same buffer (dS has been read out of it), dK(it); dQ(it)
+      // Each stream runs in sub-tile order (the dQ drain relies on that order).
       auto pt_phase = [&](int it) -> bool {
         const uint32_t st = stage_of(it), g = it & 1;
+        // dO of the stage arrives through the async proxy: this thread observes its barrier itself
+        if (!mbar_wait_warp(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 126, it)) return false;
+        if (!mbar_wait_warp(&s.pt_ready[g], (it >> 1) & 1, &s.abort_flag, p.status, 122, it)) return false;
+        FA4B_ACC(0);  // waiting for P
         FA4B_TR(2, 100);
         tc_fence_after();
         if (leader) {
@@ -283,31 +302,41 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           mma_commit(&s.dp_full[g]);
         }
         __syncwarp();
+        FA4B_ACC(1);  // dV, dP
         FA4B_TR(2, 101);
         return true;
       };
       auto ds_phase = [&](int it) -> bool {
         const uint32_t st = stage_of(it), g = it & 1;
+        if (!mbar_wait_warp(&s.ds_ready[g], (it >> 1) & 1, &s.abort_flag, p.status, 123, it)) return false;
+        FA4B_ACC(0);  // waiting for dS
         FA4B_TR(2, 110);
         tc_fence_after();
         // the group's next scores first: its threads are about to wait for them
-        FA4B_ACC(3);  // ds: fence
-        if (it + 2 < n_it && !issue_s(it + 2)) return false;
-        FA4B_ACC(4);  // ds: S
+        if (it + 2 < n_it) fire_s(it + 2);
+        FA4B_ACC(4);  // S
         const uint32_t acc = it > 0 ? 1u : 0u;
         const uint64_t q8 = d_q80 + st * kQ816, ds = d_ds0 + g * kPt16;
         if (leader) {
 #pragma unroll
           for (int k = 0; k < QT / 32; ++k) mma_f8_ss(tm + C::colDK, ds + 2 * k, q8 + kRow32D * k, id_dk, k > 0 ? 1u : acc);
+          mma_commit(&s.in_empty[st]);  // one of two arrivals: S and dK have read the stage
         }
         __syncwarp();
-        FA4B_ACC(5);  // ds: dK
+        FA4B_ACC(5);  // dK
         FA4B_TR(2, 112);
-        if (it > 0) {
-          if (!mbar_wait_warp(&s.dq_free, (it - 1) & 1, &s.abort_flag, p.status, 124, it)) return false;
-          tc_fence_after();
-        }
-        FA4B_ACC(6);  // ds: dq_free
+        if (it + 3 < n_it && !prep_s(it + 3)) return false;
+        FA4B_ACC(3);  // scale factors of the next S
+        return true;
+      };
+      auto dq_phase = [&](int it) -> bool {
+        const uint32_t st = stage_of(it), g = it & 1;
+        if (!mbar_wait_warp(&s.ds_ready[g], (it >> 1) & 1, &s.abort_flag, p.status, 127, it)) return false;
+        FA4B_ACC(0);  // waiting for dS
+        if (it > 0 && !mbar_wait_warp(&s.dq_free, (it - 1) & 1, &s.abort_flag, p.status, 124, it)) return false;
+        FA4B_ACC(6);  // waiting for the accumulator
+        tc_fence_after();
+        const uint64_t ds = d_ds0 + g * kPt16;
         if (leader) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) {  // 128 keys, 32 per step
@@ -318,56 +347,27 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
             }
           }
           mma_commit(&s.dq_full);
-          mma_commit(&s.in_empty[st]);
+          mma_commit(&s.in_empty[st]);  // the other arrival: the last reader of the group's dS buffer
         }
         __syncwarp();
+        FA4B_ACC(2);  // dQ + commits
         FA4B_TR(2, 113);
         return true;
       };
-      if (ok) ok = issue_s(0);
-      if (ok && 1 < n_it) ok = issue_s(1);
-      // two in-order streams, served as their events arrive.  (Answering the ds event in three separately
-      // scheduled steps -- S, dK, dQ -- with pt events taken in between was measured 3 % slower: the two compute
-      // groups then fall back into step with each other.)
-      int ip = 0, id = 0;  // next sub-tile of the pt stream / of the ds stream
-      long long t_idle = 0;
-      while (ok && id < n_it) {
-        bool served = false;
-        if (ip < n_it && mbar_test_uniform(&s.pt_ready[ip & 1], (ip >> 1) & 1)) {
-          FA4B_ACC(0);  // idle / polling
-          ok = pt_phase(ip);
-          FA4B_ACC(1);  // pt phase: dV, dP
-          ++ip;
-          served = true;
+      // (One warp serving all streams as their events arrived left each compute group waiting behind the
+      // other's phase and the next S behind the wait for the dQ accumulator.)
+      if (stream == 0) {
+        for (int it = 0; ok && it < n_it; ++it) ok = pt_phase(it);
+      } else if (stream == 1) {
+        for (int it = 0; ok && it < 3 && it < n_it; ++it) {
+          ok = prep_s(it);
+          if (ok && it < 2) fire_s(it);
         }
-        if (ok && id < ip && mbar_test_uniform(&s.ds_ready[id & 1], (id >> 1) & 1)) {
-          FA4B_ACC(0);
-          ok = ds_phase(id);
-          FA4B_ACC(2);  // ds: dQ + commits
-          ++id;
-          served = true;
-        }
-        if (served) {
-          t_idle = 0;
-        } else {  // bounded like every other wait
-          const long long now = clock64();
-          if (t_idle == 0) t_idle = now;
-          uint32_t stop = s.abort_flag ? 1u : (now - t_idle > kWaitLimitCycles ? 2u : 0u);
-          stop = __shfl_sync(0xffffffffu, stop, 0);
-          if (stop == 2u && leader) {
-            s.abort_flag = 1u;
-            if (atomicCAS(p.status, 0u, 1u) == 0u) {
-              p.status[1] = 125;
-              p.status[2] = blockIdx.x;
-              p.status[3] = (uint32_t)(ip * 65536 + id);
-            }
-          }
-          __syncwarp();
-          if (stop) ok = false;
-        }
+        for (int it = 0; ok && it < n_it; ++it) ok = ds_phase(it);
+      } else {
+        for (int it = 0; ok && it < n_it; ++it) ok = dq_phase(it);
       }
-      FA4B_ACC(0);
-      FA4B_ACCT_FLUSH(0);
+      FA4B_ACCT_FLUSH(stream == 0 ? 0 : 3 + stream);
       if (ok && leader) mma_commit(&s.acc_done);
       // every tensor-core operation of this CTA has finished before TMEM is freed
       if (leader) mma_commit(&s.mma_drained);
@@ -459,8 +459,8 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       if (!mbar_wait_warp(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 143, it)) return false;
       FA4B_ACC(1);  // in_full
       if ((warp & 7) == 0) FA4B_TR(grp, 11);
-      // st_full(it) is committed after dV(it-2), dK(it-2) and dQ(it-2): once it has fired, the group's P
-      // buffer (last read by dV(it-2)) is no longer read by the tensor core
+      // the group's P buffer was last read by dV(it-2); dp_full(it-2), which this warp observed in the dS
+      // step of that sub-tile, was committed by the same thread after dV(it-2)
       if (!mbar_wait_warp(&s.st_full[grp], (it >> 1) & 1, &s.abort_flag, p.status, 140, it)) return false;
       FA4B_ACC(2);  // st_full
       if ((warp & 7) == 0) FA4B_TR(grp, 3);
@@ -518,8 +518,11 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     auto do_ds = [&](int it, const uint32_t (&pk)[CW / 4]) -> bool {
       const int st = it % kBwdStages;
       if ((warp & 7) == 0) FA4B_TR(grp, 20);
-      // dp_full(it) is committed after dK(it-2) and dQ(it-2), the last readers of the group's dS buffer
+      // dK(it-2) and dQ(it-2), the last readers of the group's dS buffer, belong to the other issuer's stream:
+      // the release of their input stage is committed after them
       FA4B_ACC(0);
+      if (it >= 2 && !mbar_wait_warp(&s.in_empty[(it - 2) % kBwdStages], ((it - 2) / kBwdStages) & 1, &s.abort_flag, p.status, 144, it))
+        return false;
       if (!mbar_wait_warp(&s.dp_full[grp], (it >> 1) & 1, &s.abort_flag, p.status, 141, it)) return false;
       FA4B_ACC(5);  // dp_full
       if ((warp & 7) == 0) FA4B_TR(grp, 4);
