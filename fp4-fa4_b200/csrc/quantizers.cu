@@ -242,13 +242,17 @@ struct Nvfp4Params {
   uint8_t* scales_col;
 };
 
-template <bool NORM, bool COL>
+// W2D: one scale per 16 x 16 tile (learned projection weights): every 1 x 16 group of the tile, in either
+// orientation, carries the scale of the tile's amax, so the transposed output is the byte-for-byte transpose of
+// the row-wise one.
+template <bool NORM, bool COL, bool W2D = false>
 __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
   __shared__ __align__(16) __nv_bfloat16 tile[kTile * kPitch];
   __shared__ __align__(16) uint8_t sc_row[2 * 512];
   __shared__ __align__(16) uint8_t sc_col[COL ? 2 * 512 : 16];
   __shared__ __align__(16) uint8_t cb_col[COL ? kTile * 80 : 16];  // [128 columns][64 code bytes + pad]
   __shared__ StepTable steps;
+  __shared__ float tile_amax[W2D ? 64 : 1];
 
   const int t = threadIdx.x;
   // tiles run from the end of the matrix to its start: the statistics pass that precedes this kernel
@@ -284,6 +288,22 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
     *reinterpret_cast<uint4*>(&tile[r * kPitch + c8]) = v;
   }
   __syncthreads();
+  if (W2D) {  // four threads per 16 x 16 tile, four rows each
+    const int id = t >> 2, r0 = (id >> 3) * 16 + (t & 3) * 4, c0 = (id & 7) * 16;
+    uint32_t m2 = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint4 a = *reinterpret_cast<const uint4*>(&tile[(r0 + k) * kPitch + c0]);
+      const uint4 b = *reinterpret_cast<const uint4*>(&tile[(r0 + k) * kPitch + c0 + 8]);
+      m2 = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(m2, a.x), a.y), a.z), a.w);
+      m2 = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(m2, b.x), b.y), b.z), b.w);
+    }
+    float m = fmaxf(bf16_bits_to_f32(m2 & 0xffffu), bf16_bits_to_f32(m2 >> 16));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    if ((t & 3) == 0) tile_amax[id] = m;
+    __syncthreads();
+  }
 
   const bool all_zero = !(amax > 0.f);
   // ---- row-wise 1x16 blocks: 512 segments of two blocks, two segments per thread -----------
@@ -307,13 +327,13 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
         m2 = absmax_bf16x2(m2, w[8 * h + k]);
         x[k] = bf16x2_to_f32x2(w[8 * h + k]);
       }
-      const float bamax = fmaxf(bf16_bits_to_f32(m2 & 0xffffu), bf16_bits_to_f32(m2 >> 16));
+      const int kb = (c32 >> 4) + h;
+      const float bamax = W2D ? tile_amax[(r >> 4) * 8 + kb] : fmaxf(bf16_bits_to_f32(m2 & 0xffffu), bf16_bits_to_f32(m2 >> 16));
       uint32_t sbyte = 0;
       if (!all_zero) {
         sbyte = nvfp4_scale_byte(bamax, g, inv6g);
         nvfp4_codes16(x, bamax, steps, sbyte, codes[2 * h], codes[2 * h + 1]);
       }
-      const int kb = (c32 >> 4) + h;
       sc_row[(kb >> 2) * 512 + page_offset(r, kb)] = (uint8_t)sbyte;
     }
     *reinterpret_cast<uint4*>(p.codes_row + (row0 + r) * (p.cols / 2) + (col0 + c32) / 2) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
@@ -333,7 +353,7 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {  // low halves: column 2cp, high halves: column 2cp + 1
         const int c = 2 * cp + h;
-        const float bamax = bf16_bits_to_f32(h ? (m2 >> 16) : (m2 & 0xffffu));
+        const float bamax = W2D ? tile_amax[rb * 8 + (c >> 4)] : bf16_bits_to_f32(h ? (m2 >> 16) : (m2 & 0xffffu));
         uint64_t x[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k)
@@ -489,10 +509,13 @@ int fa4b_amax(const void* x, int64_t n, float* amax, void* stream) {
   return FA4B_OK;
 }
 
-static int launch_nvfp4(const Nvfp4Params& p, bool norm, cudaStream_t st) {
+static int launch_nvfp4(const Nvfp4Params& p, bool norm, cudaStream_t st, bool weight_tiles = false) {
   dim3 grid((unsigned)(p.cols / 128), (unsigned)(p.rows / 128));
   const bool col = p.codes_col != nullptr;
-  if (norm) {
+  if (weight_tiles) {
+    if (col) nvfp4_tile_kernel<false, true, true><<<grid, 256, 0, st>>>(p);
+    else nvfp4_tile_kernel<false, false, true><<<grid, 256, 0, st>>>(p);
+  } else if (norm) {
     if (col) nvfp4_tile_kernel<true, true><<<grid, 256, 0, st>>>(p);
     else nvfp4_tile_kernel<true, false><<<grid, 256, 0, st>>>(p);
   } else {
@@ -503,7 +526,7 @@ static int launch_nvfp4(const Nvfp4Params& p, bool norm, cudaStream_t st) {
   return FA4B_OK;
 }
 
-int fa4b_quant_nvfp4(const fa4b_quant_nvfp4_args* a, void* stream) {
+static int quant_nvfp4_impl(const fa4b_quant_nvfp4_args* a, void* stream, bool weight_tiles) {
   FA4B_REQUIRE(a != nullptr, FA4B_BAD_ARG, "args is NULL");
   if (int s = check_matrix(a->x, a->rows, a->cols, a->ld)) return s;
   FA4B_REQUIRE(a->amax && a->global_scale && a->codes_row && a->scales_row, FA4B_BAD_ARG, "fa4b_quant_nvfp4: an output pointer is NULL");
@@ -519,8 +542,12 @@ int fa4b_quant_nvfp4(const fa4b_quant_nvfp4_args* a, void* stream) {
   p.amax = a->amax; p.global_scale = a->global_scale;
   p.codes_row = a->codes_row; p.scales_row = a->scales_row;
   p.codes_col = a->codes_col; p.scales_col = a->scales_col;
-  return launch_nvfp4(p, false, st);
+  return launch_nvfp4(p, false, st, weight_tiles);
 }
+
+int fa4b_quant_nvfp4(const fa4b_quant_nvfp4_args* a, void* stream) { return quant_nvfp4_impl(a, stream, false); }
+
+int fa4b_quant_nvfp4_weight(const fa4b_quant_nvfp4_args* a, void* stream) { return quant_nvfp4_impl(a, stream, true); }
 
 int fa4b_rmsnorm_quant_nvfp4(const fa4b_rmsnorm_quant_nvfp4_args* a, void* stream) {
   FA4B_REQUIRE(a != nullptr, FA4B_BAD_ARG, "args is NULL");

@@ -10,12 +10,14 @@ from .quantizers import (  # noqa: F401
     dequant_mxfp4,
     dequant_nvfp4,
     mxfp4_quantize_for_gemm,
+    prepare_nvfp4_projection_weight,
+    prepare_nvfp4_projection_weight_dual,
     rmsnorm_backward_bf16,
     tk_fused_norm_quantize,
     tk_quantize_for_gemm,
 )
 
 __all__ = [
-    "amax", "dequant_mxfp4", "dequant_nvfp4", "mxfp4_quantize_for_gemm", "rmsnorm_backward_bf16", "tk_fused_norm_quantize",
+    "amax", "dequant_mxfp4", "dequant_nvfp4", "mxfp4_quantize_for_gemm", "prepare_nvfp4_projection_weight", "prepare_nvfp4_projection_weight_dual", "rmsnorm_backward_bf16", "tk_fused_norm_quantize",
     "tk_quantize_for_gemm",
 ]

@@ -61,6 +61,34 @@ def tk_quantize_for_gemm(input: torch.Tensor, return_transpose: bool = True, ama
     return fp4_row, sc_row, fp4_col, sc_col, sg, am
 
 
+def prepare_nvfp4_projection_weight(tensor: torch.Tensor):
+    """Learned projection weight ``[N,K]`` with 16x16 NVFP4 scaling: ``(payload [N,K/2], scales
+    [N/128,K/64,512], global [1])`` (b300_prepare_nvfp4_projection_weight, tk_fa4/interface.py:1221-1244)."""
+    fwd, _ = _prepare_weight(tensor, dual=False)
+    return fwd
+
+
+def prepare_nvfp4_projection_weight_dual(tensor: torch.Tensor):
+    """The weight and its exact physical transpose, quantised once: ``(forward, transpose)``, each a
+    ``(payload, scales, global)`` triple; both share one global decode scale tensor
+    (b300_prepare_nvfp4_projection_weight_dual, tk_fa4/interface.py:1247-1313)."""
+    return _prepare_weight(tensor, dual=True)
+
+
+def _prepare_weight(tensor: torch.Tensor, dual: bool):
+    _require_matrix(tensor, "tensor")
+    if not tensor.is_contiguous():
+        raise ValueError("tensor must be contiguous")
+    rows, cols = tensor.shape
+    fp4_row, sc_row, fp4_col, sc_col = _alloc_outputs(rows, cols, dual, tensor.device)
+    am = torch.empty(1, dtype=torch.float32, device=tensor.device)
+    sg = torch.empty(1, dtype=torch.float32, device=tensor.device)
+    a = _lib.QuantNvfp4Args(ptr(tensor), rows, cols, tensor.stride(0), ptr(am), 0, ptr(sg),
+                            ptr(fp4_row), ptr(sc_row), ptr(fp4_col), ptr(sc_col))
+    check(lib().fa4b_quant_nvfp4_weight(C.byref(a), C.c_void_p(current_stream())), "fa4b_quant_nvfp4_weight")
+    return (fp4_row, sc_row, sg), ((fp4_col, sc_col, sg) if dual else None)
+
+
 def tk_fused_norm_quantize(input: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6, with_silu: bool = False,
                            return_transpose: bool = True, return_normalized: bool = False):
     """Fused RMSNorm + NVFP4: returns ``(fp4_row, sc_row, fp4_col, sc_col, sg,

@@ -91,6 +91,41 @@ typedef struct fa4b_quant_nvfp4_args {
 } fa4b_quant_nvfp4_args;
 int fa4b_quant_nvfp4(const fa4b_quant_nvfp4_args* a, void* stream);
 
+/* ---- fa4b_quant_nvfp4_weight --------------------------------------------
+ * The same outputs for a learned projection weight: one scale per 16 x 16
+ * tile (the E4M3 byte of the tile's amax), stored once per 1 x 16 group of
+ * the tile in either orientation, so that the transposed operand is the
+ * byte-for-byte transpose of the row-wise one and both share global_scale.
+ * Replaces quantize_nvfp4_projection_weight and
+ * quantize_nvfp4_projection_weight_dual (tk_fa4/interface.py:1221-1313);
+ * arithmetic of fake_quantize_nvfp4(block_shape=(16, 16)), layout of
+ * transpose_prepared_nvfp4_weight_reference
+ * (projection_quantization_reference.py:473-590, 200-290). */
+int fa4b_quant_nvfp4_weight(const fa4b_quant_nvfp4_args* a, void* stream);
+
+/* ---- fa4b_project_nvfp4 --------------------------------------------------
+ * y[M, N] bf16 = A[M, K] . W[N, K]^T for two prepared NVFP4 operands (the
+ * outputs of fa4b_quant_nvfp4 / fa4b_rmsnorm_quant_nvfp4 for the activation,
+ * fa4b_quant_nvfp4_weight for the weight): block-scaled FP4 tensor-core MMAs,
+ * FP32 accumulation, the product of the two global scales applied once at
+ * the end.  Replaces project_nvfp4_generic behind b300_project_nvfp4
+ * (tk_fa4/interface.py:1619-1640).  M % 128 == 0, N % 256 == 0, K % 256 == 0.
+ *   status [4] u32 (device): zeroed by the call; status[0] != 0 afterwards
+ *   means a device-side wait gave up (status[1] = site). */
+typedef struct fa4b_project_nvfp4_args {
+  const uint8_t* a_codes;   /* [M, K/2] */
+  const uint8_t* a_scales;  /* [M/128, K/64, 512] */
+  const float* a_global;    /* [1] */
+  const uint8_t* w_codes;   /* [N, K/2] */
+  const uint8_t* w_scales;  /* [N/128, K/64, 512] */
+  const float* w_global;    /* [1] */
+  int64_t M, N, K;
+  void* y;                  /* bf16 [M, ldy] */
+  int64_t ldy;
+  uint32_t* status;
+} fa4b_project_nvfp4_args;
+int fa4b_project_nvfp4(const fa4b_project_nvfp4_args* a, void* stream);
+
 /* ---- fa4b_rmsnorm_quant_nvfp4 -------------------------------------------
  * y = bf16((x * inv_rms[row]) * gamma[col]), inv_rms = 1/sqrt(mean x^2 + eps);
  * then fa4b_quant_nvfp4 of y with amax over the bf16 y.  Replaces

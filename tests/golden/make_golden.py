@@ -53,6 +53,7 @@ def main(ref_root: str) -> None:
         rne = R.fake_quantize_nvfp4(x, block_shape=(1, 16))
         rne_t = R.fake_quantize_nvfp4(x.t().contiguous(), block_shape=(1, 16))
         mx = {m: R.fake_quantize_mxfp4(x, block_shape=(1, 32), scale_mode=m) for m in ("ceil", "rte")}
+        w2d = R.fake_quantize_nvfp4(x, block_shape=(16, 16))
     finally:
         R._quantize_e2m1 = saved
     fx["nvfp4_values"] = bits16(rne.values)
@@ -60,6 +61,27 @@ def main(ref_root: str) -> None:
     fx["nvfp4_global_decode"] = np.float32(rne.diagnostics["global_decode"])
     fx["nvfp4_t_values"] = bits16(rne_t.values)
     fx["nvfp4_t_block_scales"] = rne_t.block_scales.reshape(256, 8).numpy()
+    # learned-weight recipe: one scale per 16x16 tile; and the reference's byte-level transposition of a
+    # prepared operand (built here from the represented values and scales the reference itself returned)
+    fx["nvfp4_w2d_values"] = bits16(w2d.values)
+    fx["nvfp4_w2d_block_scales"] = w2d.block_scales.reshape(8, 16).numpy()
+    gd = torch.tensor(w2d.diagnostics["global_decode"], dtype=torch.float32)
+    sc = w2d.block_scales.reshape(8, 16).to(torch.float8_e4m3fn)  # exact: the values are E4M3 numbers
+    dec = sc.float().repeat_interleave(16, 0).repeat_interleave(16, 1) * gd
+    mag = (w2d.values.float().abs() / dec.clamp_min(1e-30))
+    lv = torch.tensor(R.E2M1_LEVELS)
+    code = (mag[..., None] - lv).abs().argmin(-1).to(torch.uint8) | (torch.signbit(w2d.values).to(torch.uint8) << 3)
+    payload = (code[:, 0::2] | (code[:, 1::2] << 4)).contiguous()
+    rows, cols = x.shape
+    rr = torch.arange(rows)[:, None]
+    gg = torch.arange(cols // 16)[None, :]
+    pages = torch.zeros(rows // 128, cols // 64, 512, dtype=torch.uint8)
+    pages[rr // 128, gg // 4, (rr % 32) * 16 + ((rr % 128) // 32) * 4 + gg % 4] = sc.view(torch.uint8).repeat_interleave(16, 0)
+    tp, ts, _ = R.transpose_prepared_nvfp4_weight_reference((payload, pages, gd.reshape(1)))
+    fx["nvfp4_w2d_payload"] = payload.numpy()
+    fx["nvfp4_w2d_pages"] = pages.numpy()
+    fx["nvfp4_w2d_t_payload"] = tp.numpy()
+    fx["nvfp4_w2d_t_pages"] = ts.numpy()
     for m, r in mx.items():
         fx[f"mxfp4_{m}_values"] = bits16(r.values)
         fx[f"mxfp4_{m}_block_scales"] = r.block_scales.reshape(128, 8).numpy()

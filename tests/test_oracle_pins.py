@@ -48,6 +48,24 @@ def test_nvfp4_transposed_matches_reference_fixture(golden_dir):
     assert torch.equal(q.scales.view(torch.float8_e4m3fn).float(), torch.from_numpy(fx["nvfp4_t_block_scales"]))
 
 
+def test_nvfp4_weight_tiles_match_reference_fixture(golden_dir):
+    # fake_quantize_nvfp4(block_shape=(16, 16)) and transpose_prepared_nvfp4_weight_reference, run by the generator
+    fx = np.load(golden_dir / "quantizers.npz")
+    x = _bf16(fx["x"])
+    fwd, tr = O.nvfp4_quantize_weight(x)
+    assert torch.equal(fwd.dequant().bfloat16().view(torch.int16), torch.from_numpy(fx["nvfp4_w2d_values"]))
+    tile_scales = fwd.scales.view(torch.float8_e4m3fn).float()[0::16]
+    assert torch.equal(tile_scales, torch.from_numpy(fx["nvfp4_w2d_block_scales"]))
+    assert torch.equal(fwd.codes, torch.from_numpy(fx["nvfp4_w2d_payload"]))
+    assert torch.equal(fwd.pages(), torch.from_numpy(fx["nvfp4_w2d_pages"]))
+    # the operand of the transposed weight is the reference's byte-level transposition of the first
+    assert torch.equal(tr.codes, torch.from_numpy(fx["nvfp4_w2d_t_payload"]))
+    assert torch.equal(tr.pages(), torch.from_numpy(fx["nvfp4_w2d_t_pages"]))
+    assert torch.equal(tr.dequant(), fwd.dequant().t())
+    # a tile never has a larger error than the 1x16 recipe allows for its amax: codes stay within +-6
+    assert float(fwd.dequant().abs().max()) <= float(x.float().abs().max()) * 1.07
+
+
 def test_mxfp4_matches_reference_fixture(golden_dir):
     fx = np.load(golden_dir / "quantizers.npz")
     x = _bf16(fx["x"])

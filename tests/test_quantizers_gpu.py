@@ -63,6 +63,38 @@ def test_nvfp4_with_supplied_amax_and_strided_input():
     _same(sc_row, ref.pages(), "row pages")
 
 
+@pytest.mark.parametrize("shape,seed", [((128, 128), 4), ((256, 384), 5), ((512, 1024), 6)])
+def test_nvfp4_weight_tiles_and_dual_transpose_match_oracle(shape, seed):
+    w, _ = O.make_quantizer_inputs(*shape, seed=seed)
+    w[16:32, 32:48] = 0.0  # an all-zero tile
+    fwd, tr = fa4b.prepare_nvfp4_projection_weight_dual(w.to(DEV))
+    ref, ref_t = O.nvfp4_quantize_weight(w)
+    assert fwd[2].data_ptr() == tr[2].data_ptr() and float(fwd[2]) == float(ref.global_scale)
+    _same(fwd[0], ref.codes, "weight codes")
+    _same(fwd[1], ref.pages(), "weight scale pages")
+    _same(tr[0], ref_t.codes, "transposed weight codes")
+    _same(tr[1], ref_t.pages(), "transposed weight scale pages")
+    single = fa4b.prepare_nvfp4_projection_weight(w.to(DEV))
+    _same(single[0], ref.codes, "weight codes (single)")
+    _same(single[1], ref.pages(), "weight scale pages (single)")
+
+
+def test_nvfp4_weight_dual_is_a_transpose_at_projection_size():
+    # 4096 x 4096 (a Llama-3-8B projection): the two operands decode to transposes of each other, and every
+    # 16 x 16 tile carries one scale
+    g = torch.Generator(device=DEV).manual_seed(11)
+    w = (torch.randn(4096, 4096, device=DEV, generator=g) * 0.02).bfloat16()
+    fwd, tr = fa4b.prepare_nvfp4_projection_weight_dual(w)
+    a = fa4b.dequant_nvfp4(*fwd)
+    b = fa4b.dequant_nvfp4(*tr)
+    assert torch.equal(a, b.t())
+    assert O.rel_l2(w.float().cpu(), a.cpu()) < 0.12
+    ref, _ = O.nvfp4_quantize_weight(w[:256].cpu())  # a slab against the oracle (same tensor-wide amax needed)
+    slab = O.nvfp4_quantize_weight(w.cpu())[0]
+    _same(fwd[0], slab.codes, "codes at 4096 x 4096")
+    _same(fwd[1], slab.pages(), "scale pages at 4096 x 4096")
+
+
 def _wide_range(M, K, seed, lo=-20, hi=20):
     """rows of very different magnitude: small rows get scale byte 0 (step clamped to FLT_MIN), where x / step
     overflows and only the sign and saturation survive; mid rows land in the subnormal E4M3 scale range"""
