@@ -225,6 +225,28 @@ def quantizer_rates(device, reps=10):
             ts.append(a.elapsed_time(b))
         ms = sorted(ts)[len(ts) // 2]
         out[name] = {"gbs": nbytes / ms / 1e6, "ms": ms, "algorithmic_bytes": nbytes}
+    # Llama-3-8B QKV projection [16384, 4096] x [6144, 4096]^T on prepared NVFP4 operands (tensor-bound: TFLOP/s)
+    N = 6144
+    w = (torch.randn(N, K, device=device) * 0.02).bfloat16()
+    fr, sr, _, _, sg, _ = fa4b.tk_quantize_for_gemm(x, return_transpose=False)
+    wq = fa4b.prepare_nvfp4_projection_weight(w)
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+    st = torch.zeros(4, dtype=torch.int32, device=device)
+    for _ in range(3):
+        fa4b.project_nvfp4((fr, sr, sg), wq, out=y, status=st)
+    ts = []
+    for _ in range(reps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fa4b.project_nvfp4((fr, sr, sg), wq, out=y, status=st)
+        b.record()
+        b.synchronize()
+        ts.append(a.elapsed_time(b))
+    if int(st[0]) != 0:
+        raise RuntimeError(f"project_nvfp4: device-side wait gave up: {st.tolist()}")
+    ms = sorted(ts)[len(ts) // 2]
+    out["project_nvfp4_qkv_16384x6144x4096"] = {"tflops": 2.0 * M * N * K / ms / 1e9, "ms": ms}
     return out
 
 
@@ -362,7 +384,10 @@ def run_ours(args, rank, world, local_rank):
     quant = quantizer_rates(device) if extras else {}
     others = other_configurations(device) if (extras and args.workload == "c2") else {}
     for qv in quant.values():
-        qv["frac_of_hbm"] = qv["gbs"] / peaks["hbm_gbs"]
+        if "gbs" in qv:
+            qv["frac_of_hbm"] = qv["gbs"] / peaks["hbm_gbs"]
+        else:
+            qv["frac_of_nvfp4_peak"] = qv["tflops"] / p4
     nbytes_in = sum(t.numel() * t.element_size() for t in host)
     line = {
         "metric": METRIC, "value": world * flops_step * args.steps / (ms_total * 1e-3) / 1e12, "unit": UNIT,

@@ -2,37 +2,45 @@
 // 512-byte pages, one FP32 global scale each), BF16 out.  Replaces project_nvfp4_generic behind
 // b300_project_nvfp4 (tk_fa4/interface.py:1619-1640).
 //
-// One persistent CTA per SM walks 128 x 256 output tiles.  Per K step of 256 values a stage holds the A codes
-// (128 rows x 128 bytes), the W codes (256 rows x 128 bytes) and their scale pages (4 + 8); a producer warp
-// fills the stages by TMA, an issuer warp copies the scale pages to TMEM and issues four block-scaled
+// One persistent CTA per SM walks 128 x 256 output tiles.  Per K step of 128 values a stage holds the A codes
+// (128 rows x 64 bytes), the W codes (256 rows x 64 bytes) and their scale pages (2 + 4); a producer warp
+// fills the seven stages by TMA, an issuer warp copies the scale pages to TMEM and issues two block-scaled
 // tcgen05 MMAs (M128 N256 K64) per stage into a 256-column FP32 accumulator, and four epilogue warps read the
-// accumulator out of TMEM, apply the two global scales and store BF16.  The accumulator is handed back to the
-// issuer as soon as it is in registers, so the next tile's MMAs run beside the stores.
+// accumulator out of TMEM (eight warps, 128 columns in flight each), apply the two global scales, stage BF16 rows in
+// shared memory and hand them to TMA stores.  The accumulator goes back to the issuer as soon as it is in
+// registers, so the next tile's MMAs run beside the stores.
 #include <algorithm>
 #include <mutex>
 
 #include <cuda_bf16.h>
 
 #include "common.cuh"
-#include "fa4b.h"
 #include "tc_sm100.cuh"
 
 namespace fa4b {
 
-constexpr int kProjStages = 4;
-constexpr int kProjThreads = 192;  // warp 0 producer, warp 1 issuer, warps 2-5 epilogue
-constexpr int kProjTileM = 128, kProjTileN = 256, kProjStepK = 256;
+#ifndef FA4B_PROJ_STEPK
+#define FA4B_PROJ_STEPK 256
+#endif
+constexpr int kProjThreads = 320;  // warp 0 producer, warp 1 issuer, warps 2-9 epilogue
+constexpr int kProjTileM = 128, kProjTileN = 256, kProjStepK = FA4B_PROJ_STEPK;
+constexpr int kProjStages = kProjStepK == 256 ? 4 : 8;
+constexpr int kRowBytes = kProjStepK / 2;   // code bytes per row and stage: 128 (128-byte swizzle) or 64
+constexpr int kStepMmas = kProjStepK / 64;  // K64 MMAs, and scale pages per 128 rows, per stage
 
 struct ProjStage {
-  alignas(1024) uint8_t a[kProjTileM * 128];
-  alignas(1024) uint8_t w[kProjTileN * 128];
-  alignas(16) uint8_t a_sf[4 * 512];
-  alignas(16) uint8_t w_sf[2][4 * 512];
+  alignas(1024) uint8_t a[kProjTileM * kRowBytes];
+  alignas(1024) uint8_t w[kProjTileN * kRowBytes];
+  alignas(16) uint8_t a_sf[kStepMmas * 512];
+  alignas(16) uint8_t w_sf[2][kStepMmas * 512];
 };
-constexpr uint32_t kProjStageBytes = kProjTileM * 128 + kProjTileN * 128 + 4 * 512 + 8 * 512;
+constexpr uint32_t kProjStageBytes = (kProjTileM + kProjTileN) * kRowBytes + 3 * kStepMmas * 512;
 
 struct ProjSmem {
   ProjStage stage[kProjStages];
+  // per epilogue warp: one box of 8 rows x 64 bf16 (128-byte rows, 128-byte swizzle), the source of a TMA store;
+  // four stages leave no room for more
+  alignas(1024) uint8_t out[8][8 * 128];
   alignas(8) uint64_t full[kProjStages];
   uint64_t empty[kProjStages];
   uint64_t acc_full, acc_free, mma_drained;
@@ -51,14 +59,25 @@ struct ProjParams {
   uint32_t* status;
 };
 
-// TMEM columns: accumulator 0-255; scale factors of a stage: A 16 columns, W 32 columns, two slots
-constexpr uint32_t kColSf = 256, kSfSlot = 48;
+// TMEM columns: accumulator 0-255; scale factors of a stage: A 8 columns, W 16 columns, two slots
+constexpr uint32_t kColSf = 256, kSfSlot = 12 * kStepMmas;
 
 __global__ void __launch_bounds__(kProjThreads, 1)
-project_nvfp4_kernel(const ProjParams p, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w) {
-  extern __shared__ uint8_t raw[];
-  ProjSmem& s = *reinterpret_cast<ProjSmem*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+project_nvfp4_kernel(const ProjParams p, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                     const __grid_constant__ CUtensorMap map_y) {
+  // the dynamic shared memory of a kernel without static shared memory starts on a 1024-byte boundary of the
+  // CTA's window; four stages leave no room to round the pointer up, so the kernel checks and refuses otherwise
+  extern __shared__ __align__(1024) uint8_t raw[];
+  ProjSmem& s = *reinterpret_cast<ProjSmem*>(raw);
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  if ((smem_u32(raw) & 1023u) != 0u) {  // CTA-uniform
+    if (t == 0 && atomicCAS(p.status, 0u, 1u) == 0u) {
+      p.status[1] = 400;
+      p.status[2] = blockIdx.x;
+      p.status[3] = smem_u32(raw);
+    }
+    return;
+  }
   const int tiles_n = p.N / kProjTileN, n_tiles = (p.M / kProjTileM) * tiles_n, n_k = p.K / kProjStepK;
   const int64_t pages_k = p.K / 64;
 
@@ -68,7 +87,7 @@ project_nvfp4_kernel(const ProjParams p, const __grid_constant__ CUtensorMap map
       mbar_init(&s.empty[i], 1);
     }
     mbar_init(&s.acc_full, 1);
-    mbar_init(&s.acc_free, 4);
+    mbar_init(&s.acc_free, 8);
     mbar_init(&s.mma_drained, 1);
     s.abort_flag = 0;
     fence_barrier_init();
@@ -97,11 +116,11 @@ project_nvfp4_kernel(const ProjParams p, const __grid_constant__ CUtensorMap map
           issued = it + 1;
           ProjStage& g = s.stage[st];
           mbar_expect_tx(&s.full[st], kProjStageBytes);
-          tma_load_2d(g.a, &map_a, kb * 128, tm_i * kProjTileM, &s.full[st]);
-          tma_load_2d(g.w, &map_w, kb * 128, tn_i * kProjTileN, &s.full[st]);
-          bulk_load(g.a_sf, p.a_sf + ((int64_t)tm_i * pages_k + kb * 4) * 512, 4 * 512, &s.full[st]);
-          bulk_load(g.w_sf[0], p.w_sf + ((int64_t)(2 * tn_i) * pages_k + kb * 4) * 512, 4 * 512, &s.full[st]);
-          bulk_load(g.w_sf[1], p.w_sf + ((int64_t)(2 * tn_i + 1) * pages_k + kb * 4) * 512, 4 * 512, &s.full[st]);
+          tma_load_2d(g.a, &map_a, kb * kRowBytes, tm_i * kProjTileM, &s.full[st]);
+          tma_load_2d(g.w, &map_w, kb * kRowBytes, tn_i * kProjTileN, &s.full[st]);
+          bulk_load(g.a_sf, p.a_sf + ((int64_t)tm_i * pages_k + kb * kStepMmas) * 512, kStepMmas * 512, &s.full[st]);
+          bulk_load(g.w_sf[0], p.w_sf + ((int64_t)(2 * tn_i) * pages_k + kb * kStepMmas) * 512, kStepMmas * 512, &s.full[st]);
+          bulk_load(g.w_sf[1], p.w_sf + ((int64_t)(2 * tn_i + 1) * pages_k + kb * kStepMmas) * 512, kStepMmas * 512, &s.full[st]);
         }
       }
       // no copy of this CTA may still be in flight when its shared memory is given up
@@ -135,15 +154,15 @@ project_nvfp4_kernel(const ProjParams p, const __grid_constant__ CUtensorMap map
           ProjStage& g = s.stage[st];
           const uint32_t sf = tm + kColSf + (it & 1) * kSfSlot;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
+          for (int k = 0; k < kStepMmas; ++k) {
             tmem_cp_page(sf + 4 * k, make_page_desc(smem_u32(g.a_sf + 512 * k)));
-            tmem_cp_page(sf + 16 + 8 * k, make_page_desc(smem_u32(g.w_sf[0] + 512 * k)));
-            tmem_cp_page(sf + 16 + 8 * k + 4, make_page_desc(smem_u32(g.w_sf[1] + 512 * k)));
+            tmem_cp_page(sf + 4 * kStepMmas + 8 * k, make_page_desc(smem_u32(g.w_sf[0] + 512 * k)));
+            tmem_cp_page(sf + 4 * kStepMmas + 8 * k + 4, make_page_desc(smem_u32(g.w_sf[1] + 512 * k)));
           }
-          const uint64_t da = make_tile_desc(smem_u32(g.a), 128), dw = make_tile_desc(smem_u32(g.w), 128);
+          const uint64_t da = make_tile_desc(smem_u32(g.a), kRowBytes), dw = make_tile_desc(smem_u32(g.w), kRowBytes);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_nvfp4_ss(tm, da + 2 * k, dw + 2 * k, idesc, sf + 4 * k, sf + 16 + 8 * k, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kStepMmas; ++k)
+            mma_nvfp4_ss(tm, da + 2 * k, dw + 2 * k, idesc, sf + 4 * k, sf + 4 * kStepMmas + 8 * k, (kb > 0 || k > 0) ? 1u : 0u);
           mma_commit(&s.empty[st]);
           if (kb == n_k - 1) mma_commit(&s.acc_full);
         }
@@ -157,35 +176,63 @@ project_nvfp4_kernel(const ProjParams p, const __grid_constant__ CUtensorMap map
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2-5)
-    const int quarter = warp & 3;  // the TMEM lanes this warp may read
-    const uint32_t lane_base = tm + ((uint32_t)(quarter * 32) << 16);
+    // ------------------------------------------------------------------ epilogue (warps 2-9)
+    // two warps per TMEM lane quarter, 128 accumulator columns each: all four loads of a warp are in flight at
+    // once and the accumulator goes back to the issuer as soon as they have landed
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const uint32_t lane_base = tm + ((uint32_t)(quarter * 32) << 16) + half * 128;
     const float gscale = __ldg(p.a_global) * __ldg(p.w_global);
+    uint8_t* const box = s.out[warp - 2];
+    const uint32_t swz = (uint32_t)(lane & 7);
     int n_done = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++n_done) {
       const int tm_i = tile / tiles_n, tn_i = tile % tiles_n;
       if (!mbar_wait_warp(&s.acc_full, n_done & 1, &s.abort_flag, p.status, 430, tile)) break;
       tc_fence_after();
-      __nv_bfloat16* yrow = p.y + (int64_t)(tm_i * kProjTileM + quarter * 32 + lane) * p.ldy + (int64_t)tn_i * kProjTileN;
-#pragma unroll 1
-      for (int c = 0; c < kProjTileN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(lane_base + c * 32, v);
-        tmem_ld_wait(v);
-        if (c == kProjTileN / 32 - 1) {  // the accumulator is in registers: the next tile may overwrite it
-          tc_fence_before();
-          mbar_arrive_warp(&s.acc_free);
-        }
-        uint32_t w[16];
+      uint32_t v[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(lane_base + c * 32, v[c]);
+      tmem_ld_wait(v[0]);
+      tmem_ld_wait(v[1]);
+      tmem_ld_wait(v[2]);
+      tmem_ld_wait(v[3]);
+      tc_fence_before();
+      mbar_arrive_warp(&s.acc_free);
+      const int col = tn_i * kProjTileN + half * 128, row = tm_i * kProjTileM + quarter * 32;
+      // BF16 in place: word 16 * c + i of `o` = columns 32 * c + 2 * i, + 1 of this lane's row
+      uint32_t o[64];
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[2 * i]) * gscale, __uint_as_float(v[2 * i + 1]) * gscale);
-          w[i] = *reinterpret_cast<const uint32_t*>(&h2);
+          const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[c][2 * i]) * gscale, __uint_as_float(v[c][2 * i + 1]) * gscale);
+          o[16 * c + i] = *reinterpret_cast<const uint32_t*>(&h2);
         }
+      // eight stores of 8 rows x 64 columns: the lanes of the row group write their 128 bytes, lane 0 stores the box
 #pragma unroll
-        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(yrow + c * 32 + 8 * i) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+      for (int b2 = 0; b2 < 2; ++b2) {
+#pragma unroll 1
+        for (int rg = 0; rg < 4; ++rg) {
+          if (lane == 0) tma_store_wait_read();  // the box is free once the store that read it last has done so
+          __syncwarp();
+          if ((lane >> 3) == rg) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+              *reinterpret_cast<uint4*>(box + (lane & 7) * 128 + (((uint32_t)ch ^ swz) << 4)) =
+                  make_uint4(o[32 * b2 + 4 * ch], o[32 * b2 + 4 * ch + 1], o[32 * b2 + 4 * ch + 2], o[32 * b2 + 4 * ch + 3]);
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&map_y, box, col + 64 * b2, row + 8 * rg);
+            tma_store_commit();
+          }
+        }
       }
     }
+    // shared memory stays valid until the stores have read it
+    if (lane == 0) tma_store_wait_read();
+    __syncwarp();
   }
   tc_fence_before();
   __syncthreads();
@@ -201,7 +248,7 @@ int fa4b_project_nvfp4(const fa4b_project_nvfp4_args* a, void* stream) {
   FA4B_REQUIRE(a->a_codes && a->a_scales && a->a_global && a->w_codes && a->w_scales && a->w_global && a->y && a->status, FA4B_BAD_ARG,
                "fa4b_project_nvfp4: NULL pointer");
   FA4B_REQUIRE(a->M > 0 && a->N > 0 && a->K > 0 && a->M % kProjTileM == 0 && a->N % kProjTileN == 0 && a->K % kProjStepK == 0, FA4B_BAD_SHAPE,
-               "M=%lld N=%lld K=%lld: M must be a multiple of 128, N and K of 256", (long long)a->M, (long long)a->N, (long long)a->K);
+               "M=%lld N=%lld K=%lld: M must be a multiple of 128, N of 256 and K of %d", (long long)a->M, (long long)a->N, (long long)a->K, kProjStepK);
   FA4B_REQUIRE(a->M < (1ll << 31) && a->N < (1ll << 31) && a->K < (1ll << 31), FA4B_BAD_SHAPE, "dimensions must fit 31 bits");
   FA4B_REQUIRE(a->ldy >= a->N && a->ldy % 8 == 0 && (reinterpret_cast<uintptr_t>(a->y) & 15) == 0, FA4B_BAD_ALIGN,
                "y must be 16-byte aligned with a row stride >= N that is a multiple of 8 elements");
@@ -210,12 +257,14 @@ int fa4b_project_nvfp4(const fa4b_project_nvfp4_args* a, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   FA4B_CUDA(cudaMemsetAsync(a->status, 0, 4 * sizeof(uint32_t), st));
   CUtensorMap ma{}, mw{};
-  if (int s = make_tensor_map(&ma, a->a_codes, 1, (uint64_t)a->K / 2, (uint64_t)a->M, 0, (uint64_t)a->K / 2, 0, 128, kProjTileM)) return s;
-  if (int s = make_tensor_map(&mw, a->w_codes, 1, (uint64_t)a->K / 2, (uint64_t)a->N, 0, (uint64_t)a->K / 2, 0, 128, kProjTileN)) return s;
+  CUtensorMap my{};
+  if (int s = make_tensor_map(&ma, a->a_codes, 1, (uint64_t)a->K / 2, (uint64_t)a->M, 0, (uint64_t)a->K / 2, 0, kRowBytes, kProjTileM)) return s;
+  if (int s = make_tensor_map(&mw, a->w_codes, 1, (uint64_t)a->K / 2, (uint64_t)a->N, 0, (uint64_t)a->K / 2, 0, kRowBytes, kProjTileN)) return s;
+  if (int s = make_tensor_map(&my, a->y, 2, (uint64_t)a->N, (uint64_t)a->M, 0, (uint64_t)a->ldy * 2, 0, 64, 8)) return s;
   int dev = 0, sms = 0;
   FA4B_CUDA(cudaGetDevice(&dev));
   FA4B_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const int smem = sizeof(ProjSmem) + 1024;
+  const int smem = sizeof(ProjSmem);
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(project_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
@@ -227,7 +276,7 @@ int fa4b_project_nvfp4(const fa4b_project_nvfp4_args* a, void* stream) {
   p.M = (int)a->M; p.N = (int)a->N; p.K = (int)a->K;
   p.status = a->status;
   const int n_tiles = (p.M / kProjTileM) * (p.N / kProjTileN);
-  project_nvfp4_kernel<<<std::min(n_tiles, sms), kProjThreads, smem, st>>>(p, ma, mw);
+  project_nvfp4_kernel<<<std::min(n_tiles, sms), kProjThreads, smem, st>>>(p, ma, mw, my);
   FA4B_CUDA(cudaGetLastError());
   return FA4B_OK;
 }

@@ -27,6 +27,13 @@ class QuantNvfp4Args(C.Structure):
                 ("codes_col", C.c_void_p), ("scales_col", C.c_void_p)]
 
 
+class ProjectNvfp4Args(C.Structure):
+    _fields_ = [("a_codes", C.c_void_p), ("a_scales", C.c_void_p), ("a_global", C.c_void_p),
+                ("w_codes", C.c_void_p), ("w_scales", C.c_void_p), ("w_global", C.c_void_p),
+                ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64), ("y", C.c_void_p), ("ldy", C.c_int64),
+                ("status", C.c_void_p)]
+
+
 class RmsnormQuantArgs(C.Structure):
     _fields_ = [("x", C.c_void_p), ("gamma", C.c_void_p), ("rows", C.c_int64), ("cols", C.c_int64), ("ld", C.c_int64),
                 ("eps", C.c_float), ("inv_rms", C.c_void_p), ("y_out", C.c_void_p), ("amax", C.c_void_p),
@@ -86,7 +93,7 @@ class Info(C.Structure):
 
 
 EXPORTS = (
-    "fa4b_status_string", "fa4b_last_error", "fa4b_query", "fa4b_amax", "fa4b_quant_nvfp4", "fa4b_quant_nvfp4_weight",
+    "fa4b_status_string", "fa4b_last_error", "fa4b_query", "fa4b_amax", "fa4b_quant_nvfp4", "fa4b_quant_nvfp4_weight", "fa4b_project_nvfp4",
     "fa4b_rmsnorm_quant_nvfp4", "fa4b_quant_mxfp4", "fa4b_dequant_nvfp4", "fa4b_dequant_mxfp4",
     "fa4b_attn_workspace_bytes", "fa4b_attn_ws_layout_query", "fa4b_attn_prepare", "fa4b_attn_fwd",
     "fa4b_attn_fwd_static", "fa4b_attn_bwd_preprocess", "fa4b_attn_bwd", "fa4b_attn_check_status", "fa4b_attn_merge", "fa4b_attn_accumulate", "fa4b_rmsnorm_bwd", "fa4b_rmsnorm_bwd_workspace_bytes", "fa4b_microgate", "fa4b_tensor_peak",

@@ -89,6 +89,41 @@ def _prepare_weight(tensor: torch.Tensor, dual: bool):
     return (fp4_row, sc_row, sg), ((fp4_col, sc_col, sg) if dual else None)
 
 
+def project_nvfp4(input_operand, weight_operand, out: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+    """``[M,K] x [N,K]^T -> bf16 [M,N]`` for two prepared NVFP4 operands ``(payload, scale pages, global)``
+    (b300_project_nvfp4, tk_fa4/interface.py:1619-1640).  ``status`` (u32 [4], device) receives the kernel's
+    wait status; when it is not supplied the call synchronises and raises if a device-side wait gave up."""
+    if len(input_operand) != 3 or len(weight_operand) != 3:
+        raise ValueError("NVFP4 operands must contain packed data, block scales, and one global scale")
+    a, a_sc, a_g = input_operand
+    w, w_sc, w_g = weight_operand
+    for name, t in (("payload", a), ("scales", a_sc), ("weight payload", w), ("weight scales", w_sc)):
+        if not t.is_cuda or t.element_size() != 1 or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous byte-sized CUDA tensor")
+    M, K = a.shape[0], a.shape[1] * 2
+    N = w.shape[0]
+    if w.shape[1] * 2 != K:
+        raise ValueError(f"inner dimensions differ: activation K={K}, weight K={w.shape[1] * 2}")
+    if tuple(a_sc.shape) != (M // 128, K // 64, 512) or tuple(w_sc.shape) != (N // 128, K // 64, 512):
+        raise ValueError("scale pages have an invalid shape")
+    if a_g.numel() != 1 or w_g.numel() != 1 or a_g.dtype != torch.float32 or w_g.dtype != torch.float32:
+        raise ValueError("global scales must be one float32 each")
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    elif out.dtype != torch.bfloat16 or tuple(out.shape) != (M, N) or out.stride(1) != 1:
+        raise ValueError("out must be bfloat16 [M, N] with a contiguous last dimension")
+    own = status is None
+    if own:
+        status = torch.empty(4, dtype=torch.int32, device=a.device)
+    args = _lib.ProjectNvfp4Args(ptr(a), ptr(a_sc), ptr(a_g), ptr(w), ptr(w_sc), ptr(w_g), M, N, K, ptr(out), out.stride(0), ptr(status))
+    check(lib().fa4b_project_nvfp4(C.byref(args), C.c_void_p(current_stream())), "fa4b_project_nvfp4")
+    if own:
+        st = status.cpu().tolist()
+        if st[0] != 0:
+            raise RuntimeError(f"fa4b_project_nvfp4: a device-side wait gave up (site {st[1]}, block {st[2]}, detail {st[3]})")
+    return out
+
+
 def tk_fused_norm_quantize(input: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6, with_silu: bool = False,
                            return_transpose: bool = True, return_normalized: bool = False):
     """Fused RMSNorm + NVFP4: returns ``(fp4_row, sc_row, fp4_col, sc_col, sg,

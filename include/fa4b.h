@@ -109,7 +109,7 @@ int fa4b_quant_nvfp4_weight(const fa4b_quant_nvfp4_args* a, void* stream);
  * fa4b_quant_nvfp4_weight for the weight): block-scaled FP4 tensor-core MMAs,
  * FP32 accumulation, the product of the two global scales applied once at
  * the end.  Replaces project_nvfp4_generic behind b300_project_nvfp4
- * (tk_fa4/interface.py:1619-1640).  M % 128 == 0, N % 256 == 0, K % 256 == 0.
+ * (tk_fa4/interface.py:1619-1640).  M % 128 == 0, N % 256 == 0, K % 128 == 0.
  *   status [4] u32 (device): zeroed by the call; status[0] != 0 afterwards
  *   means a device-side wait gave up (status[1] = site). */
 typedef struct fa4b_project_nvfp4_args {

@@ -95,6 +95,46 @@ def test_nvfp4_weight_dual_is_a_transpose_at_projection_size():
     _same(fwd[1], slab.pages(), "scale pages at 4096 x 4096")
 
 
+@pytest.mark.parametrize("M,N,K,seed", [(128, 256, 256, 1), (256, 512, 1024, 2), (384, 768, 4096, 3)])
+def test_project_nvfp4_matches_oracle_on_represented_operands(M, N, K, seed):
+    x, _ = O.make_quantizer_inputs(M, K, seed=seed)
+    w, _ = O.make_quantizer_inputs(N, K, seed=seed + 100)
+    w = (w * 0.05).bfloat16()
+    fp4, sc, _, _, sg, _ = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=False)
+    weight = fa4b.prepare_nvfp4_projection_weight(w.to(DEV))
+    y = fa4b.project_nvfp4((fp4, sc, sg), weight)
+    assert y.shape == (M, N) and y.dtype == torch.bfloat16
+    ref = O.project_nvfp4_reference(O.nvfp4_quantize(x), O.nvfp4_quantize_weight(w)[0])
+    # FP32 sums on the tensor core against float64 sums: the same bf16 value except where the exact result sits
+    # within an FP32 rounding of a bf16 boundary (tolerance: rel-L2 1e-4, no element off by more than one bf16 step)
+    assert O.rel_l2(ref.float(), y.float().cpu()) < 1e-4
+    step = torch.maximum(ref.float().abs(), torch.tensor(1e-3)) * 2.0 ** -7
+    assert bool(((ref.float() - y.float().cpu()).abs() <= step).all())
+
+
+def test_project_nvfp4_with_the_transposed_weight_gives_the_input_gradient_product():
+    # dX = dY . W uses the [K, N] operand of the dual publication: same represented weight, transposed
+    g = torch.Generator().manual_seed(9)
+    w = (torch.randn(512, 256, generator=g) * 0.05).bfloat16()   # [N, K]
+    dy = torch.randn(128, 512, generator=g).bfloat16()           # [M, N]
+    fwd, tr = fa4b.prepare_nvfp4_projection_weight_dual(w.to(DEV))
+    fp4, sc, _, _, sg, _ = fa4b.tk_quantize_for_gemm(dy.to(DEV), return_transpose=False)
+    dx = fa4b.project_nvfp4((fp4, sc, sg), tr)                   # [M, K]
+    ref = (O.nvfp4_quantize(dy).dequant().double() @ O.nvfp4_quantize_weight(w)[0].dequant().double()).to(torch.bfloat16)
+    assert O.rel_l2(ref.float(), dx.float().cpu()) < 1e-4
+
+
+def test_project_nvfp4_rejects_bad_shapes():
+    a = (torch.zeros(128, 128, dtype=torch.uint8, device=DEV), torch.zeros(1, 4, 512, dtype=torch.uint8, device=DEV),
+         torch.ones(1, device=DEV))
+    w = (torch.zeros(128, 128, dtype=torch.uint8, device=DEV), torch.zeros(1, 4, 512, dtype=torch.uint8, device=DEV),
+         torch.ones(1, device=DEV))
+    with pytest.raises(ValueError):  # N = 128 is not a multiple of 256
+        fa4b.project_nvfp4(a, w)
+    with pytest.raises(ValueError):
+        fa4b.project_nvfp4(a, (w[0][:, :64], w[1], w[2]))
+
+
 def _wide_range(M, K, seed, lo=-20, hi=20):
     """rows of very different magnitude: small rows get scale byte 0 (step clamped to FLT_MIN), where x / step
     overflows and only the sign and saturation survive; mid rows land in the subnormal E4M3 scale range"""
