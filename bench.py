@@ -43,6 +43,9 @@ WORKLOADS = {
     "c3": dict(B=16, Hq=32, Hkv=8, S=4096, D=64),    # the D = 64 configuration (same FLOPs as c2)
     "c5": dict(B=1, Hq=32, Hkv=8, S=131072, D=128),  # long context: forward only, MXFP4 P.V, sequence sharded over the ranks
     "noncausal": dict(B=1, Hq=32, Hkv=32, S=32768, D=128),  # the reference's historical inference shape: unmasked forward only
+    # NVFP4 projection GEMMs (rows = tokens): the Llama-3-8B QKV projection, and a quarter of its rows for profiler captures
+    "project": dict(M=16384, N=6144, K=4096),
+    "project_small": dict(M=4096, N=6144, K=4096),
 }
 WORKLOAD = dict(WORKLOADS["c2"])
 METRIC = "causal_attn_fwd_bwd_tflops"
@@ -515,6 +518,48 @@ def run_noncausal(args, rank, world, local_rank):
                       "by_pv_format": out}), flush=True)
 
 
+def run_project(args, rank, world, local_rank):
+    """y = x . w^T on prepared NVFP4 operands (activation 1x16 blocks, weight 16x16 tiles), the kernel alone."""
+    import fa4b
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    M, N, K = (WORKLOAD[k] for k in ("M", "N", "K"))
+    g = torch.Generator(device=device).manual_seed(20260825)
+    x = torch.randn(M, K, device=device, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=device, generator=g) * 0.02).bfloat16()
+    fr, sr, _, _, sg, _ = fa4b.tk_quantize_for_gemm(x, return_transpose=False)
+    wq = fa4b.prepare_nvfp4_projection_weight(w)
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+    st = torch.zeros(4, dtype=torch.int32, device=device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    for _ in range(max(args.warmup, 1)):
+        fa4b.project_nvfp4((fr, sr, sg), wq, out=y, status=st)
+    ts = []
+    for _ in range(args.steps):
+        flush.zero_()  # evict the 126 MB L2
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fa4b.project_nvfp4((fr, sr, sg), wq, out=y, status=st)
+        b.record()
+        b.synchronize()
+        ts.append(a.elapsed_time(b))
+    if int(st[0]) != 0:
+        raise RuntimeError(f"project_nvfp4: device-side wait gave up: {st.tolist()}")
+    ms = sorted(ts)[len(ts) // 2]
+    from fa4b import microgate
+
+    p4 = microgate.tensor_peak("nvfp4") if not args.no_extras else None
+    print(json.dumps({"metric": "nvfp4_projection_tflops", "value": 2.0 * M * N * K / ms / 1e9, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True, "data": "synthetic",
+                      "config": {"workload": f"NVFP4 projection [{M}, {K}] x [{N}, {K}]^T -> bf16, operands prepared beforehand (not the headline configuration)",
+                                 "l2": "flushed between timed launches"},
+                      "roofline": None if p4 is None else {"bound": "tensor", "achieved": 2.0 * M * N * K / ms / 1e9, "peak": p4, "unit": UNIT,
+                                                           "frac": 2.0 * M * N * K / ms / 1e9 / p4,
+                                                           "peak_source": "measured here: tcgen05 NVFP4 MMA-only run on all SMs"},
+                      "gpu_launches": args.steps}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -540,6 +585,10 @@ def main():
     if args.workload == "noncausal":
         if rank == 0:
             run_noncausal(args, rank, world, local_rank)
+        return
+    if args.workload.startswith("project"):
+        if rank == 0:
+            run_project(args, rank, world, local_rank)
         return
     run_ours(args, rank, world, local_rank)
 
