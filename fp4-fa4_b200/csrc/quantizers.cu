@@ -637,3 +637,58 @@ int fa4b_dequant_mxfp4(const uint8_t* codes, const uint8_t* pages, int64_t rows,
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------ pair-native RoPE
+// x[b, s, h, 2i], x[b, s, h, 2i+1] rotate by the angle whose cosine and sine are cos[s, i], sin[s, i] (bf16), in
+// packed BF16 arithmetic: out = fma(perp, sin, mul(pair, cos)) with perp = (-y, x), one rounding each -- the
+// arithmetic of apply_rope_pair (tk_fa4/lowp_fa4_bwd/projection_fp4_epilogue.cuh:447-479).  The inverse
+// rotation (gradients) negates the sine.  Eight elements per thread, in place.
+namespace fa4b {
+__global__ void __launch_bounds__(256) rope_pair_kernel(__nv_bfloat16* __restrict__ x, int64_t sb, int64_t ss, int64_t sh, int S, int H, int D,
+                                                        int64_t n_chunks, const __nv_bfloat16* __restrict__ cs, const __nv_bfloat16* __restrict__ sn,
+                                                        int inverse) {
+  const int per_row = D / 8;
+  for (int64_t c = (int64_t)blockIdx.x * 256 + threadIdx.x; c < n_chunks; c += (int64_t)gridDim.x * 256) {
+    const int d8 = (int)(c % per_row);
+    const int64_t row = c / per_row;
+    const int h = (int)(row % H);
+    const int64_t bs = row / H;
+    const int s = (int)(bs % S);
+    const int64_t b = bs / S;
+    uint4* px = reinterpret_cast<uint4*>(x + b * sb + (int64_t)s * ss + (int64_t)h * sh + d8 * 8);
+    const uint2 cv = __ldg(reinterpret_cast<const uint2*>(cs + (int64_t)s * (D / 2) + d8 * 4));
+    const uint2 sv = __ldg(reinterpret_cast<const uint2*>(sn + (int64_t)s * (D / 2) + d8 * 4));
+    uint4 v = *px;
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    const uint32_t cw[2] = {cv.x, cv.y}, sw[2] = {sv.x, sv.y};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t c16 = (cw[k >> 1] >> (16 * (k & 1))) & 0xffffu;
+      uint32_t s16 = (sw[k >> 1] >> (16 * (k & 1))) & 0xffffu;
+      if (inverse) s16 ^= 0x8000u;
+      const uint32_t cc = c16 * 0x00010001u, s2 = s16 * 0x00010001u;
+      const uint32_t perp = ((w[k] << 16) | (w[k] >> 16)) ^ 0x00008000u;  // (x, y) -> (-y, x)
+      const __nv_bfloat162 r = __hfma2(*reinterpret_cast<const __nv_bfloat162*>(&perp), *reinterpret_cast<const __nv_bfloat162*>(&s2),
+                                       __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]), *reinterpret_cast<const __nv_bfloat162*>(&cc)));
+      w[k] = *reinterpret_cast<const uint32_t*>(&r);
+    }
+    *px = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+}  // namespace fa4b
+
+int fa4b_rope_pair(const fa4b_rope_pair_args* a, void* stream) {
+  FA4B_REQUIRE(a != nullptr && a->x && a->rope_cos && a->rope_sin, FA4B_BAD_ARG, "fa4b_rope_pair: NULL pointer");
+  FA4B_REQUIRE(a->B > 0 && a->S > 0 && a->H > 0 && a->D > 0 && a->D % 8 == 0, FA4B_BAD_SHAPE, "B, S, H must be positive and D a positive multiple of 8");
+  FA4B_REQUIRE(a->stride_b % 8 == 0 && a->stride_s % 8 == 0 && a->stride_h % 8 == 0 && (reinterpret_cast<uintptr_t>(a->x) & 15) == 0, FA4B_BAD_ALIGN,
+               "x must be 16-byte aligned with strides that are multiples of 8 elements");
+  FA4B_REQUIRE(((reinterpret_cast<uintptr_t>(a->rope_cos) | reinterpret_cast<uintptr_t>(a->rope_sin)) & 7) == 0, FA4B_BAD_ALIGN,
+               "rope tables must be 8-byte aligned");
+  const int64_t n_chunks = a->B * a->S * a->H * (a->D / 8);
+  const unsigned grid = (unsigned)std::min<int64_t>((n_chunks + 255) / 256, 148 * 16);
+  fa4b::rope_pair_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(a->x), a->stride_b, a->stride_s, a->stride_h, (int)a->S, (int)a->H, (int)a->D, n_chunks,
+      static_cast<const __nv_bfloat16*>(a->rope_cos), static_cast<const __nv_bfloat16*>(a->rope_sin), a->inverse);
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
+}

@@ -126,6 +126,25 @@ typedef struct fa4b_project_nvfp4_args {
 } fa4b_project_nvfp4_args;
 int fa4b_project_nvfp4(const fa4b_project_nvfp4_args* a, void* stream);
 
+/* ---- fa4b_rope_pair -------------------------------------------------------
+ * In-place rotary embedding of x[B, S, H, D] bf16 (element strides given; the
+ * last dimension contiguous) in the pair-native order: (x[2i], x[2i+1]) turns
+ * by the angle of (rope_cos[s, i], rope_sin[s, i]), tables bf16 [S, D/2].
+ * Packed BF16 arithmetic, out = fma(perp, sin, mul(pair, cos)): the numbers of
+ * rope_pair_qk_inplace behind b300_rope_pair_qk_ (tk_fa4/interface.py:6584-6599;
+ * apply_rope_pair, projection_fp4_epilogue.cuh:447-479).  inverse != 0 turns
+ * the other way (the gradient's rotation, b300_inverse_rope_interleaved_qkv_grad_,
+ * tk_fa4/interface.py:6564). */
+typedef struct fa4b_rope_pair_args {
+  void* x;
+  int64_t B, S, H, D;
+  int64_t stride_b, stride_s, stride_h;
+  const void* rope_cos;
+  const void* rope_sin;
+  int inverse;
+} fa4b_rope_pair_args;
+int fa4b_rope_pair(const fa4b_rope_pair_args* a, void* stream);
+
 /* ---- fa4b_rmsnorm_quant_nvfp4 -------------------------------------------
  * y = bf16((x * inv_rms[row]) * gamma[col]), inv_rms = 1/sqrt(mean x^2 + eps);
  * then fa4b_quant_nvfp4 of y with amax over the bf16 y.  Replaces
