@@ -105,9 +105,10 @@ def _ev(e) -> int:
 
 
 def attn_forward(q, k, v, softmax_scale: float | None = None, pv_format: str = "e4m3_fp8", workspace: Workspace | None = None,
-                 prepared: bool = False, events=(None, None), causal: bool = True):
+                 prepared: bool = False, events=(None, None), causal: bool = True, out: torch.Tensor | None = None):
     """O ``[B,Hq,S,D]`` bf16, LSE ``[B,Hq,S]`` f32 and the workspace holding the quantised operands.
-    ``causal=False`` (forward only) lets every query see every key."""
+    ``causal=False`` (forward only) lets every query see every key.  ``out`` receives O when given: a
+    ``[B,Hq,S,D]``-shaped bf16 view with any strides (e.g. a permuted ``[B,S,Hq,D]`` buffer)."""
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _check_bhsd(t, n)
     if k.shape != v.shape or q.shape[0] != k.shape[0] or q.shape[2:] != k.shape[2:]:
@@ -115,7 +116,13 @@ def attn_forward(q, k, v, softmax_scale: float | None = None, pv_format: str = "
     dims = make_dims(q, k, softmax_scale, pv_format, causal)
     ws = workspace or alloc_workspace(dims, q.device)
     B, Hq, S, D = q.shape
-    o = torch.empty(B, Hq, S, D, dtype=torch.bfloat16, device=q.device)
+    if out is None:
+        o = torch.empty(B, Hq, S, D, dtype=torch.bfloat16, device=q.device)
+    else:
+        _check_bhsd(out, "out")
+        if tuple(out.shape) != (B, Hq, S, D):
+            raise ValueError(f"out must be shaped {(B, Hq, S, D)}, got {tuple(out.shape)}")
+        o = out
     lse = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
     a = _lib.AttnFwdArgs(dims, ptr(q), _strides(q), ptr(k), _strides(k), ptr(v), _strides(v), ptr(o), _strides(o), ptr(lse),
                          ptr(ws.buf), int(prepared), _ev(events[0]), _ev(events[1]))

@@ -124,6 +124,21 @@ def project_nvfp4(input_operand, weight_operand, out: torch.Tensor | None = None
     return out
 
 
+def rope_pair_(x: torch.Tensor, rope_cos: torch.Tensor, rope_sin: torch.Tensor, inverse: bool = False) -> torch.Tensor:
+    """In-place pair-native rotary embedding of ``x [B,S,H,D]`` bf16 (any strides with a contiguous last dimension)
+    with bf16 tables ``[S, D/2]``; ``inverse=True`` turns the other way (gradients).  One tensor of
+    ``b300_rope_pair_qk_`` / ``b300_inverse_rope_interleaved_qkv_grad_`` (tk_fa4/interface.py:6584, 6564)."""
+    if x.ndim != 4 or x.dtype != torch.bfloat16 or not x.is_cuda or x.stride(3) != 1:
+        raise ValueError("x must be a CUDA bfloat16 [B,S,H,D] tensor with a contiguous last dimension")
+    B, S, H, D = x.shape
+    for name, t in (("rope_cos", rope_cos), ("rope_sin", rope_sin)):
+        if t.dtype != torch.bfloat16 or tuple(t.shape) != (S, D // 2) or not t.is_contiguous() or t.device != x.device:
+            raise ValueError(f"{name} must be a contiguous bfloat16 [S, D/2] tensor on the device of x")
+    a = _lib.RopePairArgs(ptr(x), B, S, H, D, x.stride(0), x.stride(1), x.stride(2), ptr(rope_cos), ptr(rope_sin), int(inverse))
+    check(lib().fa4b_rope_pair(C.byref(a), C.c_void_p(current_stream())), "fa4b_rope_pair")
+    return x
+
+
 def tk_fused_norm_quantize(input: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6, with_silu: bool = False,
                            return_transpose: bool = True, return_normalized: bool = False):
     """Fused RMSNorm + NVFP4: returns ``(fp4_row, sc_row, fp4_col, sc_col, sg,

@@ -1,0 +1,77 @@
+"""Module-level forward (hidden states in, hidden states out) against the oracle's composition of the same steps."""
+
+import pytest
+import torch
+
+import fa4b
+import fa4b_oracle as O
+from fa4b.lowp_module import LowpFA4AttentionBlock, pair_interleave_qk_rows
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _block_inputs(B, S, hidden, Hq, Hkv, D, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(B, S, hidden, generator=g).bfloat16()
+    mk = lambda r, c: (torch.randn(r, c, generator=g) / c ** 0.5).bfloat16()
+    wq, wk, wv, wo = mk(Hq * D, hidden), mk(Hkv * D, hidden), mk(Hkv * D, hidden), mk(hidden, Hq * D)
+    cos, sin = O.rope_tables(S, D)
+    return x, wq, wk, wv, wo, cos, sin
+
+
+def test_module_forward_matches_oracle_composition():
+    B, S, hidden, Hq, Hkv, D = 1, 256, 512, 4, 2, 128
+    x, wq, wk, wv, wo, cos, sin = _block_inputs(B, S, hidden, Hq, Hkv, D, seed=21)
+    blk = LowpFA4AttentionBlock(wq.to(DEV), wk.to(DEV), wv.to(DEV), wo.to(DEV), Hq, Hkv, D)
+    y, mid = blk.forward(x.to(DEV), cos.to(DEV), sin.to(DEV), return_intermediates=True)
+    ref_y, ref_qkv, ref_o = O.lowp_attention_block_reference(x, wq, wk, wv, wo, cos, sin, Hq, Hkv, D)
+    assert y.shape == (B, S, hidden) and y.dtype == torch.bfloat16
+    # projections: FP32 sums on the tensor core against float64 sums (rel-L2 1e-4); a bf16 value that lands on
+    # the other side of a rounding boundary can move an FP4 code downstream, hence the wider bounds after it
+    v_cols = slice((Hq + Hkv) * D, (Hq + 2 * Hkv) * D)  # the q and k columns of the buffer have been rotated in place
+    assert O.rel_l2(ref_qkv[:, v_cols].float(), mid["qkv"][:, v_cols].float().cpu()) < 1e-4
+    assert O.rel_l2(ref_o.float(), mid["o"].float().cpu()) < 1e-2
+    assert O.rel_l2(ref_y.float(), y.float().cpu()) < 2e-2
+
+
+def test_module_forward_tracks_a_bf16_attention_block():
+    # against plain bf16 / fp32 math the low-precision block stays within the error of its formats
+    B, S, hidden, Hq, Hkv, D = 2, 256, 1024, 8, 2, 128
+    x, wq, wk, wv, wo, cos, sin = _block_inputs(B, S, hidden, Hq, Hkv, D, seed=22)
+    blk = LowpFA4AttentionBlock(wq.to(DEV), wk.to(DEV), wv.to(DEV), wo.to(DEV), Hq, Hkv, D)
+    y = blk(x.to(DEV), cos.to(DEV), sin.to(DEV))
+    rows = x.float().reshape(B * S, hidden)
+    q = (rows @ wq.float().t()).bfloat16().reshape(B, S, Hq, D)
+    k = (rows @ wk.float().t()).bfloat16().reshape(B, S, Hkv, D)
+    v = (rows @ wv.float().t()).bfloat16().reshape(B, S, Hkv, D)
+    q, k = O.rope_pair_reference(q, cos, sin), O.rope_pair_reference(k, cos, sin)
+    o, _ = O.attn_reference_fp32(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3))
+    ref = (o.permute(0, 2, 1, 3).reshape(B * S, Hq * D).float() @ wo.float().t()).reshape(B, S, hidden)
+    # two NVFP4 x NVFP4 projections and an FP4 score matmul on Gaussian data: the CPU oracle of the same block sits
+    # at 0.29 from this reference
+    assert O.rel_l2(ref, y.float().cpu()) < 0.4
+
+
+def test_pair_interleave_keeps_scores():
+    Hq, D, hidden = 2, 8, 16
+    g = torch.Generator().manual_seed(5)
+    w = torch.randn(Hq * D, hidden, generator=g)
+    wi = pair_interleave_qk_rows(w, Hq, D)
+    assert torch.equal(wi[0], w[0]) and torch.equal(wi[1], w[D // 2]) and torch.equal(wi[2], w[1])
+    a, b = torch.randn(3, hidden, generator=g), torch.randn(3, hidden, generator=g)
+    s0 = (a @ w.t()).reshape(3, Hq, D) @ (b @ w.t()).reshape(3, Hq, D).transpose(1, 2)
+    s1 = (a @ wi.t()).reshape(3, Hq, D) @ (b @ wi.t()).reshape(3, Hq, D).transpose(1, 2)
+    assert torch.allclose(s0, s1, atol=1e-4)
+
+
+def test_module_rejects_masks_and_bad_shapes():
+    B, S, hidden, Hq, Hkv, D = 1, 128, 512, 4, 2, 128
+    x, wq, wk, wv, wo, cos, sin = _block_inputs(B, S, hidden, Hq, Hkv, D, seed=23)
+    blk = LowpFA4AttentionBlock(wq.to(DEV), wk.to(DEV), wv.to(DEV), wo.to(DEV), Hq, Hkv, D)
+    with pytest.raises(ValueError):
+        blk.forward(x.to(DEV), cos.to(DEV), sin.to(DEV), attention_masks=object())
+    with pytest.raises(ValueError):
+        blk.forward(x.to(DEV)[:, :100], cos.to(DEV), sin.to(DEV))
+    with pytest.raises(ValueError):
+        LowpFA4AttentionBlock(wq.to(DEV), wk.to(DEV), wv.to(DEV), wo.to(DEV), Hq, 3, D)

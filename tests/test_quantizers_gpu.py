@@ -135,6 +135,37 @@ def test_project_nvfp4_rejects_bad_shapes():
         fa4b.project_nvfp4(a, (w[0][:, :64], w[1], w[2]))
 
 
+@pytest.mark.parametrize("inverse", [False, True])
+def test_rope_pair_matches_packed_bf16_oracle_bit_for_bit(inverse):
+    g = torch.Generator().manual_seed(3)
+    B, S, H, D = 2, 96, 5, 128
+    big = torch.randn(B, S, H + 2, D + 64, generator=g).bfloat16()
+    x = big[:, :, 1:H + 1, 32:32 + D]  # a strided view, as the q columns of a fused QKV projection are
+    cos, sin = O.rope_tables(S, D)
+    ref = O.rope_pair_reference(x, cos, sin, inverse=inverse)
+    dev = big.to(DEV)
+    xd = dev[:, :, 1:H + 1, 32:32 + D]
+    fa4b.rope_pair_(xd, cos.to(DEV), sin.to(DEV), inverse=inverse)
+    _same(xd.contiguous().view(torch.int16), ref.contiguous().view(torch.int16), "rotated values")
+    # nothing outside the view moved
+    keep = torch.ones_like(big, dtype=torch.bool)
+    keep[:, :, 1:H + 1, 32:32 + D] = False
+    assert torch.equal(dev.cpu()[keep], big[keep])
+
+
+def test_rope_pair_inverse_undoes_the_rotation_within_bf16_rounding():
+    g = torch.Generator(device=DEV).manual_seed(4)
+    x = torch.randn(1, 4096, 8, 128, device=DEV, generator=g).bfloat16()
+    cos, sin = (t.to(DEV) for t in O.rope_tables(4096, 128))
+    y = fa4b.rope_pair_(x.clone(), cos, sin)
+    z = fa4b.rope_pair_(y.clone(), cos, sin, inverse=True)
+    assert O.rel_l2(x.float().cpu(), z.float().cpu()) < 1e-2   # two roundings to bf16 each way
+    # the rotation keeps each pair's length (to bf16 rounding)
+    n0 = x.float().reshape(-1, 2).norm(dim=1)
+    n1 = y.float().reshape(-1, 2).norm(dim=1)
+    assert float(((n0 - n1).abs() / n0.clamp_min(1e-3)).max()) < 2e-2
+
+
 def _wide_range(M, K, seed, lo=-20, hi=20):
     """rows of very different magnitude: small rows get scale byte 0 (step clamped to FLT_MIN), where x / step
     overflows and only the sign and saturation survive; mid rows land in the subnormal E4M3 scale range"""
