@@ -46,6 +46,8 @@ WORKLOADS = {
     # NVFP4 projection GEMMs (rows = tokens): the Llama-3-8B QKV projection, and a quarter of its rows for profiler captures
     "project": dict(M=16384, N=6144, K=4096),
     "project_small": dict(M=4096, N=6144, K=4096),
+    # module-level forward of one Llama-3-8B attention block (hidden 4096): projections + rotation + attention core
+    "module": dict(B=2, Hq=32, Hkv=8, S=8192, D=128, hidden=4096),
 }
 WORKLOAD = dict(WORKLOADS["c2"])
 METRIC = "causal_attn_fwd_bwd_tflops"
@@ -560,6 +562,46 @@ def run_project(args, rank, world, local_rank):
                       "gpu_launches": args.steps}), flush=True)
 
 
+def run_module(args, rank, world, local_rank):
+    """Forward of the attention block from hidden states to hidden states, per-step and per-stage times."""
+    import fa4b
+    from fa4b import attention
+    from fa4b.lowp_module import LowpFA4AttentionBlock
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    B, Hq, Hkv, S, D, hidden = (WORKLOAD[k] for k in ("B", "Hq", "Hkv", "S", "D", "hidden"))
+    g = torch.Generator(device=device).manual_seed(20260825)
+    mk = lambda r, c: (torch.randn(r, c, device=device, generator=g) / c ** 0.5).bfloat16()
+    blk = LowpFA4AttentionBlock(mk(Hq * D, hidden), mk(Hkv * D, hidden), mk(Hkv * D, hidden), mk(hidden, Hq * D), Hq, Hkv, D)
+    x = torch.randn(B, S, hidden, device=device, generator=g).bfloat16()
+    inv = 1.0 / (500000.0 ** (torch.arange(0, D, 2, device=device, dtype=torch.float64) / D))
+    ang = torch.arange(S, device=device, dtype=torch.float64)[:, None] * inv[None, :]
+    cos, sin = ang.cos().bfloat16(), ang.sin().bfloat16()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    for _ in range(max(args.warmup, 3)):
+        blk(x, cos, sin)
+    ts = []
+    for _ in range(args.steps):
+        flush.zero_()  # evict the 126 MB L2
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        y, mid = blk.forward(x, cos, sin, return_intermediates=True)
+        b.record()
+        b.synchronize()
+        mid["workspace"].check_status()
+        ts.append(a.elapsed_time(b))
+    ms = sorted(ts)[len(ts) // 2]
+    M = B * S
+    flops = 2.0 * M * hidden * (Hq + 2 * Hkv) * D + 2.0 * M * hidden * Hq * D + 2.0 * causal_matmul_flops(B, Hq, S, D)
+    print(json.dumps({"metric": "attention_block_fwd_tflops", "value": flops / ms / 1e9, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "data": "synthetic",
+                      "config": {"workload": f"attention block forward B{B} S{S} hidden {hidden} Hq{Hq} Hkv{Hkv} D{D}: NVFP4 QKV projection, "
+                                             "pair-native RoPE, NVFP4/FP8 causal attention, NVFP4 output projection (not the headline configuration)",
+                                 "flops": "2*M*hidden*(Hq+2Hkv)*D + 2*M*hidden*Hq*D + 2 causal matmuls", "l2": "flushed between timed steps"},
+                      "gpu_launches": 13 * args.steps}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -585,6 +627,10 @@ def main():
     if args.workload == "noncausal":
         if rank == 0:
             run_noncausal(args, rank, world, local_rank)
+        return
+    if args.workload == "module":
+        if rank == 0:
+            run_module(args, rank, world, local_rank)
         return
     if args.workload.startswith("project"):
         if rank == 0:

@@ -172,3 +172,40 @@ def test_forward_rounding_is_invariant_to_the_running_maximum():
     keep = torch.exp2(s2 - mhat + 8.0) >= 2.0 ** -6  # normal range of the final grid
     keep &= torch.exp2(s2 - (mhat - 3.0) + 8.0) <= 448.0
     assert torch.equal(final[keep], early[keep])
+
+
+def test_rope_pair_reference_is_one_rounding_per_step_and_close_to_the_complex_rotation():
+    # apply_rope_pair (projection_fp4_epilogue.cuh:447-479): t = bf16(pair * cos); out = bf16(fma(perp, sin, t))
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(1, 64, 3, 32, generator=g).bfloat16()
+    cos, sin = O.rope_tables(64, 32)
+    y = O.rope_pair_reference(x, cos, sin)
+    xc = torch.view_as_complex(x.float().reshape(1, 64, 3, 16, 2))
+    want = torch.view_as_real(xc * torch.complex(cos.float(), sin.float())[None, :, None, :]).flatten(3)
+    assert O.rel_l2(want, y.float()) < 5e-3                       # bf16 tables and two bf16 roundings
+    assert torch.equal(y[:, 0], x[:, 0])                         # position 0: cos = 1, sin = 0
+    z = O.rope_pair_reference(y, cos, sin, inverse=True)
+    assert O.rel_l2(x.float(), z.float()) < 1e-2
+    # hand-checked pair: (x, y) = (1.5, -2), cos = 0.5, sin = 0.25 -> t = (0.75, -1); out = (0.75 + 0.5, -1 + 0.375)
+    one = torch.tensor([1.5, -2.0]).bfloat16().reshape(1, 1, 1, 2)
+    out = O.rope_pair_reference(one, torch.tensor([[0.5]]).bfloat16(), torch.tensor([[0.25]]).bfloat16())
+    assert out.flatten().tolist() == [1.25, -0.625]
+
+
+def test_float64_to_bf16_rounds_once():
+    # 1 + 2^-8 is a bf16 tie (rounds to even: 1.0); a float64 just above it must round up although the detour through
+    # float32 alone would first land on the tie
+    v = torch.tensor([1.0 + 2.0 ** -8, 1.0 + 2.0 ** -8 + 2.0 ** -40, 1.0 + 2.0 ** -8 - 2.0 ** -40, 1.0 + 3 * 2.0 ** -8], dtype=torch.float64)
+    got = O._round_f64_to_bf16(v).double().tolist()
+    assert got == [1.0, 1.0 + 2.0 ** -7, 1.0, 1.0 + 2.0 ** -6]
+
+
+def test_project_reference_and_block_composition_shapes():
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(128, 64, generator=g).bfloat16()
+    w = (torch.randn(32, 64, generator=g) * 0.1).bfloat16()
+    a, (wf, wt) = O.nvfp4_quantize(x), O.nvfp4_quantize_weight(w)
+    y = O.project_nvfp4_reference(a, wf)
+    assert y.shape == (128, 32) and y.dtype == torch.bfloat16
+    assert O.rel_l2((a.dequant() @ wf.dequant().t()), y.float()) < 4e-3
+    assert torch.equal(wt.dequant(), wf.dequant().t())
