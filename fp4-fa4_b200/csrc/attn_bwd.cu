@@ -379,7 +379,9 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     // The partial dQ of a sub-tile leaves TMEM for registers and the accumulator is handed back to the
     // issuer at once; the FP32 reductions into the scratch accumulator then run beside the next
     // sub-tile's MMAs.  (Staging the tile in shared memory for one bulk reduction was slower: with
-    // one 32 KB reduction in flight per SM the reductions ran at 2.4-2.7 TB/s, against 3.2 TB/s here.)
+    // one 32 KB reduction in flight per SM the reductions ran at 2.4-2.7 TB/s, against 3.2 TB/s here.
+    // Software-pipelining this loop -- the next sub-tile's poll and first TMEM load between the two halves'
+    // reductions -- was slower too: 2.39 against 2.20 ms at the benchmark shape.)
     const int w4 = warp & 3;
     const uint32_t lane_base = tm + ((uint32_t)(w4 * 32) << 16);
     const int r = w4 * 32 + lane;  // TMEM lane: d (D = 128) or query row (D = 64)
