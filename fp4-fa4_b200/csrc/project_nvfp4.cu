@@ -2,13 +2,19 @@
 // 512-byte pages, one FP32 global scale each), BF16 out.  Replaces project_nvfp4_generic behind
 // b300_project_nvfp4 (tk_fa4/interface.py:1619-1640).
 //
-// One persistent CTA per SM walks 128 x 256 output tiles.  Per K step of 128 values a stage holds the A codes
-// (128 rows x 64 bytes), the W codes (256 rows x 64 bytes) and their scale pages (2 + 4); a producer warp
-// fills the seven stages by TMA, an issuer warp copies the scale pages to TMEM and issues two block-scaled
-// tcgen05 MMAs (M128 N256 K64) per stage into a 256-column FP32 accumulator, and four epilogue warps read the
-// accumulator out of TMEM (eight warps, 128 columns in flight each), apply the two global scales, stage BF16 rows in
-// shared memory and hand them to TMA stores.  The accumulator goes back to the issuer as soon as it is in
-// registers, so the next tile's MMAs run beside the stores.
+// One persistent CTA per SM walks 128 x 256 output tiles.  Per K step of 256 values a stage holds the A codes
+// (128 rows x 128 bytes), the W codes (256 rows x 128 bytes) and their scale pages (4 + 8).  Roles: a producer
+// warp fills the four stages by TMA; an issuer warp copies each stage's scale pages to TMEM (tcgen05.cp) and
+// issues four block-scaled tcgen05 MMAs (M128 N256 K64) per stage into a 256-column FP32 accumulator; eight
+// epilogue warps read the accumulator out of TMEM (128 columns in flight each), hand it back to the issuer,
+// apply the two global scales and store BF16 rows through small swizzled boxes and TMA stores, beside the next
+// tile's MMAs.
+//
+// Measured at [16384, 4096] x [6144, 4096]^T (launches back to back): 0.194 ms.  Variants that were slower:
+// K steps of 128 values in eight stages (0.29 ms: the issuer's per-stage work no longer fits under two MMAs);
+// three stages with larger store boxes (0.203 ms); four epilogue warps storing straight from registers, 16 bytes
+// per row and instruction (0.252 ms); the scale-page copies on a warp of their own (0.201 ms).  With parts
+// switched off: no scale-page copies -9 %, no accumulator read-out -17 %.
 #include <algorithm>
 #include <mutex>
 
