@@ -592,13 +592,31 @@ def run_module(args, rank, world, local_rank):
         mid["workspace"].check_status()
         ts.append(a.elapsed_time(b))
     ms = sorted(ts)[len(ts) // 2]
+    # forward + backward (input and weight gradients of both projections, attention backward, inverse rotation)
+    dy = (torch.randn(B, S, hidden, device=device, generator=g) * 0.05).bfloat16()
+    tb = []
+    for i in range(args.steps + 1):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        y, mid = blk.forward(x, cos, sin, return_intermediates=True)
+        blk.backward(dy, mid, cos, sin)
+        b.record()
+        b.synchronize()
+        mid["workspace"].check_status()
+        if i:
+            tb.append(a.elapsed_time(b))
+    ms_fb = sorted(tb)[len(tb) // 2]
     M = B * S
     flops = 2.0 * M * hidden * (Hq + 2 * Hkv) * D + 2.0 * M * hidden * Hq * D + 2.0 * causal_matmul_flops(B, Hq, S, D)
+    flops_fb = 3.0 * (2.0 * M * hidden * (Hq + 2 * Hkv) * D + 2.0 * M * hidden * Hq * D) + 6.0 * causal_matmul_flops(B, Hq, S, D)
     print(json.dumps({"metric": "attention_block_fwd_tflops", "value": flops / ms / 1e9, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
                       "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "data": "synthetic",
                       "config": {"workload": f"attention block forward B{B} S{S} hidden {hidden} Hq{Hq} Hkv{Hkv} D{D}: NVFP4 QKV projection, "
                                              "pair-native RoPE, NVFP4/FP8 causal attention, NVFP4 output projection (not the headline configuration)",
                                  "flops": "2*M*hidden*(Hq+2Hkv)*D + 2*M*hidden*Hq*D + 2 causal matmuls", "l2": "flushed between timed steps"},
+                      "forward_backward": {"ms_per_step": ms_fb, "tflops": flops_fb / ms_fb / 1e9,
+                                           "flops": "3x the projection matmuls + 6 causal matmuls"},
                       "gpu_launches": 13 * args.steps}), flush=True)
 
 

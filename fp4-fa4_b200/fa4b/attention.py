@@ -169,14 +169,23 @@ def attn_merge(o_acc: torch.Tensor, lse_acc: torch.Tensor, o_part: torch.Tensor,
                                 C.c_void_p(current_stream())), "fa4b_attn_merge")
 
 
-def attn_backward(o, lse, dout, ws: Workspace, preprocessed: bool = False, events=(None, None)):
-    """dQ ``[B,Hq,S,D]``, dK, dV ``[B,Hkv,S,D]`` bf16, replaying the operands the forward cached in ``ws``."""
+def attn_backward(o, lse, dout, ws: Workspace, preprocessed: bool = False, events=(None, None), out=None):
+    """dQ ``[B,Hq,S,D]``, dK, dV ``[B,Hkv,S,D]`` bf16, replaying the operands the forward cached in ``ws``.
+    ``out=(dq, dk, dv)`` supplies the destinations: bf16 views of those shapes with any strides (e.g. the column
+    ranges of one ``[B*S, (Hq + 2 Hkv) D]`` buffer)."""
     for t, n in ((o, "o"), (dout, "dout")):
         _check_bhsd(t, n)
     d = ws.dims
-    dq = torch.empty(d.B, d.Hq, d.S, d.D, dtype=torch.bfloat16, device=o.device)
-    dk = torch.empty(d.B, d.Hkv, d.S, d.D, dtype=torch.bfloat16, device=o.device)
-    dv = torch.empty_like(dk)
+    if out is None:
+        dq = torch.empty(d.B, d.Hq, d.S, d.D, dtype=torch.bfloat16, device=o.device)
+        dk = torch.empty(d.B, d.Hkv, d.S, d.D, dtype=torch.bfloat16, device=o.device)
+        dv = torch.empty_like(dk)
+    else:
+        dq, dk, dv = out
+        for t, n, h in ((dq, "dq", d.Hq), (dk, "dk", d.Hkv), (dv, "dv", d.Hkv)):
+            _check_bhsd(t, n)
+            if tuple(t.shape) != (d.B, h, d.S, d.D):
+                raise ValueError(f"{n} must be shaped {(d.B, h, d.S, d.D)}, got {tuple(t.shape)}")
     a = _lib.AttnBwdArgs(d, ptr(o), _strides(o), ptr(dout), _strides(dout), ptr(lse), ptr(dq), _strides(dq), ptr(dk), _strides(dk),
                          ptr(dv), _strides(dv), ptr(ws.buf), int(preprocessed), _ev(events[0]), _ev(events[1]))
     check(lib().fa4b_attn_bwd(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_bwd")

@@ -80,7 +80,92 @@ class LowpFA4AttentionBlock:
         o_codes, o_pages, _, _, o_g, _ = tk_quantize_for_gemm(o_rows, return_transpose=False)
         y = project_nvfp4((o_codes, o_pages, o_g), self.w_o).view(B, S, self.hidden)
         if return_intermediates:
-            return y, {"qkv": qkv, "o": o_rows, "lse": lse, "workspace": ws}
+            return y, {"qkv": qkv, "o": o_rows, "lse": lse, "workspace": ws, "x_rows": rows}
         return y
 
     __call__ = forward
+
+    def backward(self, dy: torch.Tensor, saved: dict, rope_cos: torch.Tensor, rope_sin: torch.Tensor):
+        """Gradients of :meth:`forward` from ``dy [B,S,hidden]`` and the intermediates the forward returned:
+        ``(dx [B,S,hidden], dwq, dwk, dwv, dwo)``, all bf16.  Every GEMM is the NVFP4 projection kernel: the input
+        gradients multiply the row-quantised upstream gradient with the transposed weight operand of the dual
+        publication, the weight gradients multiply the two column-quantised (token-major blocks) activations --
+        the operand formats of b300_mha_bwd_adaptive_lowp_hierarchical_nvfp4_qkv_projection_dgrad
+        (tk_fa4/interface.py:6313-6441); the query and key gradients turn back through the inverse rotation."""
+        Hq, Hkv, D = self.n_heads, self.n_kv_heads, self.head_dim
+        B, S, _ = dy.shape
+        M = B * S
+        if M % 256:
+            raise ValueError("B*S must be a multiple of 256 (the weight-gradient GEMMs contract over the tokens)")
+        dy_rows = dy.reshape(M, self.hidden)
+        if not dy_rows.is_contiguous():
+            dy_rows = dy_rows.contiguous()
+        o_rows, qkv, lse, ws, x_rows = saved["o"], saved["qkv"], saved["lse"], saved["workspace"], saved["x_rows"]
+        # output projection: dO = dY . Wo, dWo = dY^T . O
+        dy_r, dy_rp, dy_c, dy_cp, dy_g, _ = tk_quantize_for_gemm(dy_rows, return_transpose=True)
+        do_rows = project_nvfp4((dy_r, dy_rp, dy_g), self.w_o_t)                               # [M, Hq D]
+        _, _, o_c, o_cp, o_g, _ = tk_quantize_for_gemm(o_rows, return_transpose=True)
+        dwo = project_nvfp4((dy_c, dy_cp, dy_g), (o_c, o_cp, o_g))                             # [hidden, Hq D]
+        # attention core, gradients written into the columns of one [M, (Hq + 2 Hkv) D] buffer
+        dqkv = torch.empty(M, (Hq + 2 * Hkv) * D, dtype=torch.bfloat16, device=dy.device)
+        dq = dqkv[:, :Hq * D].view(B, S, Hq, D)
+        dk = dqkv[:, Hq * D:(Hq + Hkv) * D].view(B, S, Hkv, D)
+        dv = dqkv[:, (Hq + Hkv) * D:].view(B, S, Hkv, D)
+        attention.attn_backward(o_rows.view(B, S, Hq, D).permute(0, 2, 1, 3), lse, do_rows.view(B, S, Hq, D).permute(0, 2, 1, 3), ws,
+                                out=(dq.permute(0, 2, 1, 3), dk.permute(0, 2, 1, 3), dv.permute(0, 2, 1, 3)))
+        rope_pair_(dq, rope_cos, rope_sin, inverse=True)
+        rope_pair_(dk, rope_cos, rope_sin, inverse=True)
+        # QKV projection: dX = dQKV . Wqkv, dWqkv = dQKV^T . X
+        g_r, g_rp, g_c, g_cp, g_g, _ = tk_quantize_for_gemm(dqkv, return_transpose=True)
+        dx = project_nvfp4((g_r, g_rp, g_g), self.w_qkv_t).view(B, S, self.hidden)
+        _, _, x_c, x_cp, x_g, _ = tk_quantize_for_gemm(x_rows, return_transpose=True)
+        dwqkv = project_nvfp4((g_c, g_cp, g_g), (x_c, x_cp, x_g))                              # [(Hq + 2 Hkv) D, hidden]
+        return dx, dwqkv[:Hq * D], dwqkv[Hq * D:(Hq + Hkv) * D], dwqkv[(Hq + Hkv) * D:], dwo
+
+
+class _BlockFunction(torch.autograd.Function):
+    """Autograd binding of :class:`LowpFA4AttentionBlock` (the role of _LowpAttentionFunction,
+    tk_fa4/lowp_fa4_bwd/benchmark_llama12b_e2e.py:5841-6546); backward runs on the stream of the forward."""
+
+    @staticmethod
+    def forward(ctx, x, wq, wk, wv, wo, block, rope_cos, rope_sin):
+        y, saved = block.forward(x, rope_cos, rope_sin, return_intermediates=True)
+        ctx.block, ctx.saved, ctx.tables = block, saved, (rope_cos, rope_sin)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        dx, dwq, dwk, dwv, dwo = ctx.block.backward(dy, ctx.saved, *ctx.tables)
+        ctx.saved = None
+        return dx, dwq, dwk, dwv, dwo, None, None, None
+
+
+class LowpFA4Attention(torch.nn.Module):
+    """Trainable module: ``forward(x, (rope_cos, rope_sin), attention_masks=None) -> [B,S,hidden]``.  The parameters
+    keep the names of TorchTitan's Llama ``Attention`` (``wq``, ``wk``, ``wv``, ``wo`` as ``nn.Linear`` without
+    bias), so a checkpoint of the original module loads unchanged; ``wq`` / ``wk`` rows are expected in the
+    pair-native rotary order.  The quantised weight operands are rebuilt whenever a parameter has changed
+    (optimizer step, ``load_state_dict``), as the reference requires of a cached preparation."""
+
+    def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, device="cuda"):
+        super().__init__()
+        self.n_heads, self.n_kv_heads, self.head_dim = n_heads, n_kv_heads, head_dim
+        mk = lambda o, i: torch.nn.Linear(i, o, bias=False, device=device, dtype=torch.bfloat16)
+        self.wq, self.wk, self.wv = mk(n_heads * head_dim, hidden), mk(n_kv_heads * head_dim, hidden), mk(n_kv_heads * head_dim, hidden)
+        self.wo = mk(hidden, n_heads * head_dim)
+        self._block, self._versions = None, None
+
+    def _prepared(self) -> LowpFA4AttentionBlock:
+        ws = (self.wq.weight, self.wk.weight, self.wv.weight, self.wo.weight)
+        versions = tuple((w.data_ptr(), w._version) for w in ws)
+        if self._block is None or versions != self._versions:
+            with torch.no_grad():
+                self._block = LowpFA4AttentionBlock(*(w.detach() for w in ws), self.n_heads, self.n_kv_heads, self.head_dim)
+            self._versions = versions
+        return self._block
+
+    def forward(self, x: torch.Tensor, freqs, attention_masks=None) -> torch.Tensor:
+        if attention_masks is not None:
+            raise ValueError("causal attention_masks=None only")
+        rope_cos, rope_sin = freqs
+        return _BlockFunction.apply(x, self.wq.weight, self.wk.weight, self.wv.weight, self.wo.weight, self._prepared(), rope_cos, rope_sin)

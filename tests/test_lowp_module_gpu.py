@@ -5,7 +5,7 @@ import torch
 
 import fa4b
 import fa4b_oracle as O
-from fa4b.lowp_module import LowpFA4AttentionBlock, pair_interleave_qk_rows
+from fa4b.lowp_module import LowpFA4Attention, LowpFA4AttentionBlock, pair_interleave_qk_rows
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -51,6 +51,75 @@ def test_module_forward_tracks_a_bf16_attention_block():
     # two NVFP4 x NVFP4 projections and an FP4 score matmul on Gaussian data: the CPU oracle of the same block sits
     # at 0.29 from this reference
     assert O.rel_l2(ref, y.float().cpu()) < 0.4
+
+
+def test_module_backward_matches_oracle_composition():
+    B, S, hidden, Hq, Hkv, D = 1, 256, 512, 4, 2, 128
+    x, wq, wk, wv, wo, cos, sin = _block_inputs(B, S, hidden, Hq, Hkv, D, seed=31)
+    dy = (torch.randn(B, S, hidden, generator=torch.Generator().manual_seed(32)) * 0.05).bfloat16()
+    blk = LowpFA4AttentionBlock(wq.to(DEV), wk.to(DEV), wv.to(DEV), wo.to(DEV), Hq, Hkv, D)
+    y, saved = blk.forward(x.to(DEV), cos.to(DEV), sin.to(DEV), return_intermediates=True)
+    got = blk.backward(dy.to(DEV), saved, cos.to(DEV), sin.to(DEV))
+    want = O.lowp_attention_block_backward_reference(dy, x, wq, wk, wv, wo, cos, sin, Hq, Hkv, D)
+    # Five chained low-precision GEMMs and the attention backward: a bf16 value on the other side of a rounding
+    # boundary in one stage moves FP4 / FP8 codes in the next, so the bound is wider than a single kernel's
+    # (tolerance: rel-L2 5e-2 per gradient; the single kernels are tested at 1e-4 / 2e-2 on their own)
+    for name, g, w in zip(("dx", "dwq", "dwk", "dwv", "dwo"), got, want):
+        assert g.shape == w.shape, name
+        assert O.rel_l2(w.float(), g.float().cpu()) < 5e-2, name
+
+
+def test_module_gradients_point_along_fp32_gradients():
+    # cosine similarity against autograd through the same block in FP32 math
+    B, S, hidden, Hq, Hkv, D = 1, 256, 512, 4, 2, 128
+    x, wq, wk, wv, wo, cos, sin = _block_inputs(B, S, hidden, Hq, Hkv, D, seed=33)
+    dy = (torch.randn(B, S, hidden, generator=torch.Generator().manual_seed(34)) * 0.05).bfloat16()
+    blk = LowpFA4AttentionBlock(wq.to(DEV), wk.to(DEV), wv.to(DEV), wo.to(DEV), Hq, Hkv, D)
+    y, saved = blk.forward(x.to(DEV), cos.to(DEV), sin.to(DEV), return_intermediates=True)
+    got = blk.backward(dy.to(DEV), saved, cos.to(DEV), sin.to(DEV))
+    xf, ws = x.float().requires_grad_(), [w.float().requires_grad_() for w in (wq, wk, wv, wo)]
+    rows = xf.reshape(B * S, hidden)
+    fc = torch.complex(cos.float(), sin.float())[None, :, None, :]
+    rot = lambda t: torch.view_as_real(torch.view_as_complex(t.reshape(*t.shape[:-1], -1, 2)) * fc).flatten(3)
+    q = rot((rows @ ws[0].t()).reshape(B, S, Hq, D)).permute(0, 2, 1, 3)
+    k = rot((rows @ ws[1].t()).reshape(B, S, Hkv, D)).permute(0, 2, 1, 3).repeat_interleave(Hq // Hkv, dim=1)
+    v = (rows @ ws[2].t()).reshape(B, S, Hkv, D).permute(0, 2, 1, 3).repeat_interleave(Hq // Hkv, dim=1)
+    sc = (q @ k.transpose(-1, -2)) * D ** -0.5
+    sc = sc.masked_fill(torch.ones(S, S, dtype=torch.bool).triu(1), float("-inf"))
+    o = (torch.softmax(sc, -1) @ v).permute(0, 2, 1, 3).reshape(B * S, Hq * D)
+    (o @ ws[3].t()).reshape(B, S, hidden).backward(dy.float())
+    for name, g, w in zip(("dx", "dwq", "dwk", "dwv", "dwo"), got, (xf.grad, ws[0].grad, ws[1].grad, ws[2].grad, ws[3].grad)):
+        cosine = torch.nn.functional.cosine_similarity(g.float().cpu().flatten(), w.flatten(), dim=0)
+        assert float(cosine) > 0.85, (name, float(cosine))
+
+
+def test_trainable_module_routes_autograd_through_the_block_and_requantises_after_an_update():
+    B, S, hidden, Hq, Hkv, D = 1, 256, 512, 4, 2, 128
+    x, wq, wk, wv, wo, cos, sin = _block_inputs(B, S, hidden, Hq, Hkv, D, seed=41)
+    mod = LowpFA4Attention(hidden, Hq, Hkv, D, device=DEV)
+    with torch.no_grad():
+        for lin, w in ((mod.wq, wq), (mod.wk, wk), (mod.wv, wv), (mod.wo, wo)):
+            lin.weight.copy_(w.to(DEV))
+    xd = x.to(DEV).requires_grad_()
+    freqs = (cos.to(DEV), sin.to(DEV))
+    y = mod(xd, freqs)
+    dy = (torch.randn(B, S, hidden, generator=torch.Generator().manual_seed(42)) * 0.05).bfloat16().to(DEV)
+    y.backward(dy)
+    blk = LowpFA4AttentionBlock(wq.to(DEV), wk.to(DEV), wv.to(DEV), wo.to(DEV), Hq, Hkv, D)
+    y2, saved = blk.forward(x.to(DEV), *freqs, return_intermediates=True)
+    want = blk.backward(dy, saved, *freqs)
+    assert torch.equal(y, y2)
+    for g, w in zip((xd.grad, mod.wq.weight.grad, mod.wk.weight.grad, mod.wv.weight.grad, mod.wo.weight.grad), want):
+        assert torch.equal(g, w)
+    # an in-place update of a weight invalidates the cached quantised operands
+    first = mod._block
+    with torch.no_grad():
+        mod.wo.weight.mul_(0.5)
+    y3 = mod(x.to(DEV), freqs)
+    assert mod._block is not first
+    assert O.rel_l2(0.5 * y.float().cpu(), y3.float().cpu()) < 2e-2
+    with pytest.raises(ValueError):
+        mod(x.to(DEV), freqs, attention_masks=object())
 
 
 def test_pair_interleave_keeps_scores():
