@@ -147,13 +147,45 @@ class LowpFA4Attention(torch.nn.Module):
     pair-native rotary order.  The quantised weight operands are rebuilt whenever a parameter has changed
     (optimizer step, ``load_state_dict``), as the reference requires of a cached preparation."""
 
-    def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, device="cuda"):
+    def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, device="cuda", linears=None):
         super().__init__()
         self.n_heads, self.n_kv_heads, self.head_dim = n_heads, n_kv_heads, head_dim
-        mk = lambda o, i: torch.nn.Linear(i, o, bias=False, device=device, dtype=torch.bfloat16)
-        self.wq, self.wk, self.wv = mk(n_heads * head_dim, hidden), mk(n_kv_heads * head_dim, hidden), mk(n_kv_heads * head_dim, hidden)
-        self.wo = mk(hidden, n_heads * head_dim)
+        self.n_rep = n_heads // n_kv_heads
+        self.use_flex_attn = False
+        if linears is None:
+            mk = lambda o, i: torch.nn.Linear(i, o, bias=False, device=device, dtype=torch.bfloat16)
+            linears = (mk(n_heads * head_dim, hidden), mk(n_kv_heads * head_dim, hidden), mk(n_kv_heads * head_dim, hidden),
+                       mk(hidden, n_heads * head_dim))
+        self.wq, self.wk, self.wv, self.wo = linears
         self._block, self._versions = None, None
+        self._tables = None
+
+    @classmethod
+    def from_attention(cls, original: torch.nn.Module) -> "LowpFA4Attention":
+        """Take over the projections of a TorchTitan Llama ``Attention`` (same ``nn.Linear`` objects, so the
+        state-dict keys and the optimizer's parameters stay what they were), as ``ExactLowpFA4Attention(original, ...)``
+        does (exact_lowp_attention.py:3792-3830).  TorchTitan rotates adjacent pairs, the order used here."""
+        for name in ("wq", "wk", "wv", "wo", "n_heads", "n_kv_heads", "head_dim"):
+            if not hasattr(original, name):
+                raise TypeError(f"{type(original).__name__} has no attribute {name!r}: not a Llama-style attention module")
+        for lin in (original.wq, original.wk, original.wv, original.wo):
+            if not isinstance(lin, torch.nn.Linear) or lin.bias is not None:
+                raise TypeError("the projections must be bias-free nn.Linear modules")
+            if lin.weight.dtype != torch.bfloat16:
+                raise TypeError(f"the low-precision block runs on bfloat16 weights, got {lin.weight.dtype}")
+        return cls(original.wq.in_features, int(original.n_heads), int(original.n_kv_heads), int(original.head_dim),
+                   linears=(original.wq, original.wk, original.wv, original.wo))
+
+    def _rope_tables(self, freqs):
+        """(cos, sin) bf16 [S, D/2] from a pair of tables or from TorchTitan's complex ``freqs_cis [S, D/2]``."""
+        if isinstance(freqs, (tuple, list)):
+            return freqs
+        if not torch.is_complex(freqs) or freqs.ndim != 2:
+            raise TypeError("freqs must be (cos, sin) tables or a complex [S, D/2] tensor")
+        key = (freqs.data_ptr(), tuple(freqs.shape), freqs._version)
+        if self._tables is None or self._tables[0] != key:
+            self._tables = (key, freqs.real.to(torch.bfloat16).contiguous(), freqs.imag.to(torch.bfloat16).contiguous())
+        return self._tables[1], self._tables[2]
 
     def _prepared(self) -> LowpFA4AttentionBlock:
         ws = (self.wq.weight, self.wk.weight, self.wv.weight, self.wo.weight)
@@ -167,5 +199,23 @@ class LowpFA4Attention(torch.nn.Module):
     def forward(self, x: torch.Tensor, freqs, attention_masks=None) -> torch.Tensor:
         if attention_masks is not None:
             raise ValueError("causal attention_masks=None only")
-        rope_cos, rope_sin = freqs
+        rope_cos, rope_sin = self._rope_tables(freqs)
+        S = x.shape[1]
+        if rope_cos.shape[0] != S:  # TorchTitan hands over the table of the longest sequence
+            rope_cos, rope_sin = rope_cos[:S].contiguous(), rope_sin[:S].contiguous()
         return _BlockFunction.apply(x, self.wq.weight, self.wk.weight, self.wv.weight, self.wo.weight, self._prepared(), rope_cos, rope_sin)
+
+
+def replace_attention_modules(model: torch.nn.Module) -> int:
+    """Swap every Llama-style attention module of ``model`` (attributes ``wq, wk, wv, wo, n_heads, n_kv_heads,
+    head_dim``) for a :class:`LowpFA4Attention` that shares its projections; returns how many were replaced.  The
+    module-level counterpart of ``patch_attention_modules`` (which only replaces the inner attention op)."""
+    replaced = 0
+    for parent in list(model.modules()):
+        for name, child in list(parent.named_children()):
+            if isinstance(child, LowpFA4Attention):
+                continue
+            if all(hasattr(child, a) for a in ("wq", "wk", "wv", "wo", "n_heads", "n_kv_heads", "head_dim")):
+                setattr(parent, name, LowpFA4Attention.from_attention(child))
+                replaced += 1
+    return replaced
