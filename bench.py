@@ -46,6 +46,8 @@ WORKLOADS = {
     # NVFP4 projection GEMMs (rows = tokens): the Llama-3-8B QKV projection, and a quarter of its rows for profiler captures
     "project": dict(M=16384, N=6144, K=4096),
     "project_small": dict(M=4096, N=6144, K=4096),
+    # the block quantizers alone at the C4 shape [16384, 4096] (also a leg of the default run)
+    "quant": dict(M=16384, K=4096),
     # module-level forward of one Llama-3-8B attention block (hidden 4096): projections + rotation + attention core
     "module": dict(B=2, Hq=32, Hkv=8, S=8192, D=128, hidden=4096),
 }
@@ -649,6 +651,14 @@ def main():
     if args.workload == "module":
         if rank == 0:
             run_module(args, rank, world, local_rank)
+        return
+    if args.workload == "quant":
+        if rank == 0:
+            torch.cuda.set_device(local_rank)
+            rates = quantizer_rates(torch.device("cuda", local_rank), reps=max(args.steps, 1))
+            print(json.dumps({"metric": "block_quantizer_rates", "unit": "GB/s (algorithmic bytes) or TFLOP/s", "n_gpus": 1, "data": "synthetic",
+                              "config": {"workload": "C4 [16384, 4096] bf16 (not the headline configuration)", "l2": "flushed between timed launches"},
+                              "quantizers": rates}), flush=True)
         return
     if args.workload.startswith("project"):
         if rank == 0:
