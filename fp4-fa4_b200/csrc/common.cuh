@@ -145,6 +145,13 @@ __device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t acc, uint32_t w) {
   const __nv_bfloat162 m = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&acc), __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w)));
   return *reinterpret_cast<const uint32_t*>(&m);
 }
+// max(m, |a|, |b|) in one three-input maximum (the absolute values fold into its operands)
+__device__ __forceinline__ float absmax3(float m, uint64_t pair) {
+  float a, b, r;
+  unpack2(pair, a, b);
+  asm("{ .reg .f32 aa, bb; abs.f32 aa, %2; abs.f32 bb, %3; max.f32 %0, %1, aa, bb; }" : "=f"(r) : "f"(m), "f"(a), "f"(b));
+  return r;
+}
 // eight packed f32 pairs -> sixteen E2M1 codes (two words)
 __device__ __forceinline__ void e2m1_pack16(const uint64_t (&q)[8], uint32_t& lo, uint32_t& hi) {
   uint32_t b[8];

@@ -320,15 +320,15 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
     uint32_t codes[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int h = 0; h < 2; ++h) {  // the two 16-element blocks of the segment
-      uint32_t m2 = 0;
+      float m = 0.f;
       uint64_t x[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        m2 = absmax_bf16x2(m2, w[8 * h + k]);
         x[k] = bf16x2_to_f32x2(w[8 * h + k]);
+        if (!W2D) m = absmax3(m, x[k]);  // on the unpacked values: one three-input maximum per pair
       }
       const int kb = (c32 >> 4) + h;
-      const float bamax = W2D ? tile_amax[(r >> 4) * 8 + kb] : fmaxf(bf16_bits_to_f32(m2 & 0xffffu), bf16_bits_to_f32(m2 >> 16));
+      const float bamax = W2D ? tile_amax[(r >> 4) * 8 + kb] : m;
       uint32_t sbyte = 0;
       if (!all_zero) {
         sbyte = nvfp4_scale_byte(bamax, g, inv6g);
@@ -344,20 +344,19 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
     for (int i = 0; i < 2; ++i) {
       const int cp = t & 63, rb = (t >> 6) + 4 * i;  // column pair, block of 16 rows
       uint32_t w[16];
-      uint32_t m2 = 0;
 #pragma unroll
-      for (int k = 0; k < 16; ++k) {
-        w[k] = *reinterpret_cast<const uint32_t*>(&tile[(rb * 16 + k) * kPitch + 2 * cp]);
-        m2 = absmax_bf16x2(m2, w[k]);
-      }
+      for (int k = 0; k < 16; ++k) w[k] = *reinterpret_cast<const uint32_t*>(&tile[(rb * 16 + k) * kPitch + 2 * cp]);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {  // low halves: column 2cp, high halves: column 2cp + 1
         const int c = 2 * cp + h;
-        const float bamax = W2D ? tile_amax[rb * 8 + (c >> 4)] : bf16_bits_to_f32(h ? (m2 >> 16) : (m2 & 0xffffu));
         uint64_t x[8];
+        float m = 0.f;
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
+        for (int k = 0; k < 8; ++k) {
           x[k] = h ? pack2u(w[2 * k] & 0xFFFF0000u, w[2 * k + 1] & 0xFFFF0000u) : pack2u(w[2 * k] << 16, w[2 * k + 1] << 16);
+          if (!W2D) m = absmax3(m, x[k]);
+        }
+        const float bamax = W2D ? tile_amax[rb * 8 + (c >> 4)] : m;
         uint32_t lo = 0, hi = 0, sbyte = 0;
         if (!all_zero) {
           sbyte = nvfp4_scale_byte(bamax, g, inv6g);
