@@ -22,6 +22,8 @@ inline int check_dims(const fa4b_attn_dims& d) {
   FA4B_REQUIRE(d.pv_format == FA4B_PV_FP8_E4M3 || d.pv_format == FA4B_PV_MXFP4_E8M0, FA4B_UNSUPPORTED, "unknown pv_format %d",
                d.pv_format);
   FA4B_REQUIRE(d.mask == FA4B_MASK_CAUSAL || d.mask == FA4B_MASK_NONE, FA4B_UNSUPPORTED, "unknown mask %d", d.mask);
+  FA4B_REQUIRE(d.global_scale_mode == FA4B_GLOBAL_AMAX_PER_BH || d.global_scale_mode == FA4B_GLOBAL_ONE, FA4B_UNSUPPORTED,
+               "unknown global_scale_mode %d", d.global_scale_mode);
   return FA4B_OK;
 }
 

@@ -322,6 +322,12 @@ static HeadView view(const void* p, const fa4b_strides& s, int H) {
   return HeadView{static_cast<const __nv_bfloat16*>(p), s.batch, s.head, s.seq, H};
 }
 
+// the amax words of a tensor whose global decode scale is to be exactly one: amax / 2688 = 1
+__global__ void fill_unit_amax_kernel(int* __restrict__ amax_bits, int n) {
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i < n) amax_bits[i] = __float_as_int(kNvfp4GlobalDiv);
+}
+
 template <int D>
 static int prepare_impl(const fa4b_attn_prepare_args& a, cudaStream_t st) {
   const fa4b_attn_dims& d = a.dims;
@@ -330,7 +336,11 @@ static int prepare_impl(const fa4b_attn_prepare_args& a, cudaStream_t st) {
   const int nq = d.B * d.Hq, nk = d.B * d.Hkv;
   int* amax_bits = reinterpret_cast<int*>(ws + l.amax_bits);
   const HeadView q = view(a.q, a.q_strides, d.Hq), k = view(a.k, a.k_strides, d.Hkv), v = view(a.v, a.v_strides, d.Hkv);
-  if (a.phase != FA4B_PREPARE_QUANTIZE) {
+  if (a.phase != FA4B_PREPARE_QUANTIZE && d.global_scale_mode == FA4B_GLOBAL_ONE) {
+    fill_unit_amax_kernel<<<(nq + nk + 255) / 256, 256, 0, st>>>(amax_bits, nq + nk);
+    FA4B_CUDA(cudaGetLastError());
+    if (a.phase == FA4B_PREPARE_AMAX) return FA4B_OK;
+  } else if (a.phase != FA4B_PREPARE_QUANTIZE) {
     FA4B_CUDA(cudaMemsetAsync(amax_bits, 0, (size_t)(nq + nk) * 4, st));
     const int rows_per_cta = 512;
     const unsigned chunks = (unsigned)((d.S + rows_per_cta - 1) / rows_per_cta);

@@ -60,7 +60,7 @@ class QuantMxfp4Args(C.Structure):
 
 class AttnDims(C.Structure):
     _fields_ = [("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("S", C.c_int32), ("D", C.c_int32),
-                ("softmax_scale", C.c_float), ("pv_format", C.c_int32), ("mask", C.c_int32)]
+                ("softmax_scale", C.c_float), ("pv_format", C.c_int32), ("mask", C.c_int32), ("global_scale_mode", C.c_int32)]
 
 
 class Strides(C.Structure):

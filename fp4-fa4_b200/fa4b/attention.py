@@ -84,12 +84,18 @@ class Workspace:
               "fa4b_attn_check_status")
 
 
-def make_dims(q: torch.Tensor, k: torch.Tensor, softmax_scale: float | None, pv_format: str, causal: bool = True) -> _lib.AttnDims:
+GLOBAL_SCALE_MODES = {"amax_per_bh": 0, "one": 1}
+
+
+def make_dims(q: torch.Tensor, k: torch.Tensor, softmax_scale: float | None, pv_format: str, causal: bool = True,
+              global_scale: str = "amax_per_bh") -> _lib.AttnDims:
     if pv_format not in PV_FORMATS:
         raise ValueError(f"unknown pv_format {pv_format!r}; expected one of {sorted(PV_FORMATS)}")
+    if global_scale not in GLOBAL_SCALE_MODES:
+        raise ValueError(f"unknown global_scale {global_scale!r}; expected one of {sorted(GLOBAL_SCALE_MODES)}")
     B, Hq, S, D = q.shape
     return _lib.AttnDims(B, Hq, k.shape[1], S, D, float(softmax_scale) if softmax_scale else 0.0, PV_FORMATS[pv_format],
-                         0 if causal else 1)
+                         0 if causal else 1, GLOBAL_SCALE_MODES[global_scale])
 
 
 def alloc_workspace(dims: _lib.AttnDims, device) -> Workspace:
@@ -105,15 +111,18 @@ def _ev(e) -> int:
 
 
 def attn_forward(q, k, v, softmax_scale: float | None = None, pv_format: str = "e4m3_fp8", workspace: Workspace | None = None,
-                 prepared: bool = False, events=(None, None), causal: bool = True, out: torch.Tensor | None = None):
+                 prepared: bool = False, events=(None, None), causal: bool = True, out: torch.Tensor | None = None,
+                 global_scale: str = "amax_per_bh"):
     """O ``[B,Hq,S,D]`` bf16, LSE ``[B,Hq,S]`` f32 and the workspace holding the quantised operands.
     ``causal=False`` (forward only) lets every query see every key.  ``out`` receives O when given: a
-    ``[B,Hq,S,D]``-shaped bf16 view with any strides (e.g. a permuted ``[B,S,Hq,D]`` buffer)."""
+    ``[B,Hq,S,D]``-shaped bf16 view with any strides (e.g. a permuted ``[B,S,Hq,D]`` buffer).
+    ``global_scale="one"`` quantises Q and K with a unit global decode scale (block scale ``E4M3(block amax / 6)``,
+    no statistics pass), as the reference's attention route does."""
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _check_bhsd(t, n)
     if k.shape != v.shape or q.shape[0] != k.shape[0] or q.shape[2:] != k.shape[2:]:
         raise ValueError(f"inconsistent shapes q{tuple(q.shape)} k{tuple(k.shape)} v{tuple(v.shape)}")
-    dims = make_dims(q, k, softmax_scale, pv_format, causal)
+    dims = make_dims(q, k, softmax_scale, pv_format, causal, global_scale)
     ws = workspace or alloc_workspace(dims, q.device)
     B, Hq, S, D = q.shape
     if out is None:
@@ -145,7 +154,7 @@ def attn_forward_prepared(ws: Workspace, kv_ws: Workspace | None = None, causal:
     """Forward on operands already published: queries from ``ws``, keys and values from ``kv_ws`` (default ``ws``).
     ``causal=False`` lets every query see every key (an off-diagonal block of a sequence-sharded run)."""
     d = ws.dims
-    dims = _lib.AttnDims(d.B, d.Hq, d.Hkv, d.S, d.D, d.softmax_scale, d.pv_format, 0 if causal else 1)
+    dims = _lib.AttnDims(d.B, d.Hq, d.Hkv, d.S, d.D, d.softmax_scale, d.pv_format, 0 if causal else 1, d.global_scale_mode)
     dev = ws.buf.device
     o = torch.empty(d.B, d.Hq, d.S, d.D, dtype=torch.bfloat16, device=dev)
     lse = torch.empty(d.B, d.Hq, d.S, dtype=torch.float32, device=dev)
@@ -203,7 +212,7 @@ def attn_backward_prepared(ws: Workspace, kv_ws: Workspace | None = None, causal
     gradient accumulates in ``ws``'s FP32 scratch across calls with ``keep_dq_accum`` and is only converted into
     ``dq`` when ``write_dq``."""
     d = ws.dims
-    dims = _lib.AttnDims(d.B, d.Hq, d.Hkv, d.S, d.D, d.softmax_scale, d.pv_format, 0 if causal else 1)
+    dims = _lib.AttnDims(d.B, d.Hq, d.Hkv, d.S, d.D, d.softmax_scale, d.pv_format, 0 if causal else 1, d.global_scale_mode)
     dev = ws.buf.device
     dq = torch.empty(d.B, d.Hq, d.S, d.D, dtype=torch.bfloat16, device=dev) if write_dq else None
     dk = torch.empty(d.B, d.Hkv, d.S, d.D, dtype=torch.bfloat16, device=dev)

@@ -39,6 +39,10 @@ const char* fa4b_last_error(void);
 /* ---- formats and modes ------------------------------------------------- */
 enum { FA4B_PV_FP8_E4M3 = 0, FA4B_PV_MXFP4_E8M0 = 1 };  /* fa4.exact_pv_format */
 enum { FA4B_MASK_CAUSAL = 0, FA4B_MASK_NONE = 1 };
+/* global (per batch and head) decode scale of the NVFP4 Q / K operands: amax / 2688 (the recipe of
+ * fake_quantize_nvfp4, a statistics pass over Q and K first), or 1 (the reference's attention route,
+ * projection_fp4_epilogue.cuh:1922,1942: block scale E4M3(block amax / 6), no statistics pass) */
+enum { FA4B_GLOBAL_AMAX_PER_BH = 0, FA4B_GLOBAL_ONE = 1 };
 enum { FA4B_MX_CEIL = 0, FA4B_MX_RTE_MANTISSA = 1, FA4B_MX_FLOOR = 2 };
 /* fa4b_attn_bwd flags: a sequence-sharded run folds several key shards into one query shard's dQ */
 enum { FA4B_BWD_KEEP_DQ_ACCUM = 1 /* do not zero the accumulator first */, FA4B_BWD_SKIP_DQ_OUT = 2 /* do not convert it into dq */ };
@@ -226,6 +230,7 @@ typedef struct fa4b_attn_dims {
   int32_t pv_format;   /* FA4B_PV_* */
   int32_t mask;        /* FA4B_MASK_*; forward only.  FA4B_MASK_NONE serves the off-diagonal blocks of a
                           sequence-sharded (context-parallel) run, where every key precedes every query */
+  int32_t global_scale_mode; /* FA4B_GLOBAL_*; read by fa4b_attn_prepare (and fa4b_attn_fwd when it prepares) */
 } fa4b_attn_dims;
 
 typedef struct fa4b_strides {

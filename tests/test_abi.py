@@ -67,6 +67,7 @@ def test_attention_dims_are_validated_on_the_host():
                 _lib.AttnDims(2, 32, 5, 8192, 128, 0.0, 0)):
         assert h.fa4b_attn_ws_layout_query(C.byref(bad), C.byref(layout)) == 1
     assert h.fa4b_attn_ws_layout_query(C.byref(_lib.AttnDims(2, 32, 8, 8192, 128, 0.0, 7)), C.byref(layout)) == 3
+    assert h.fa4b_attn_ws_layout_query(C.byref(_lib.AttnDims(2, 32, 8, 8192, 128, 0.0, 0, 0, 5)), C.byref(layout)) == 3  # global_scale_mode
     assert h.fa4b_attn_workspace_bytes(C.byref(_lib.AttnDims(2, 32, 8, 8100, 128, 0.0, 0))) == 0
 
 

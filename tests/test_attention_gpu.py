@@ -53,6 +53,24 @@ def test_forward_matches_oracle(B, Hq, Hkv, S, D, rope):
     _check_forward(o, lse, fwd)
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,S,D", [(1, 4, 1, 256, 128), (1, 4, 4, 256, 64)])
+def test_unit_global_scale_route_matches_oracle_forward_and_backward(B, Hq, Hkv, S, D):
+    # the reference's attention route: global decode scale 1, block scale E4M3(block amax / 6), no statistics pass
+    q, k, v, do = O.make_attention_inputs(B, Hq, Hkv, S, D, seed=77 + D)
+    q[0, 0, 5, :16] *= 3000.0  # a block whose amax / 6 is beyond E4M3: the scale byte saturates, the codes clip
+    fwd = O.attn_forward(q, k, v, global_scale="one")
+    assert float(fwd.q_global.min()) == 1.0 == float(fwd.k_global.max())
+    o, lse, ws = attention.attn_forward(q.to(DEV), k.to(DEV), v.to(DEV), global_scale="one")
+    ws.check_status()
+    _check_operands(ws, fwd)
+    _check_forward(o, lse, fwd)
+    dq, dk, dv = attention.attn_backward(o, lse, do.to(DEV), ws)
+    ws.check_status()
+    rq, rk, rv = O.attn_backward(q, k, v, fwd.o, fwd.lse, do, global_scale="one")
+    for name, got, want in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
+        assert O.rel_l2(want.float(), got.float().cpu()) < 2e-2, name
+
+
 def test_forward_accepts_bshd_strides_and_custom_scale():
     q, k, v, _ = O.make_attention_inputs(1, 4, 2, 256, 128, seed=9)
     fwd = O.attn_forward(q, k, v, softmax_scale=0.05)
