@@ -214,6 +214,8 @@ def quantizer_rates(device, reps=10):
     cases = {
         "rmsnorm_nvfp4_row_col": (lambda: fa4b.tk_fused_norm_quantize(x, gamma, 1e-6), 2 * M * K + 2 * K + 2 * (M * K // 2) + 2 * (M * K // 16) + 4 * M + 4),
         "nvfp4_row_col": (lambda: fa4b.tk_quantize_for_gemm(x), 2 * M * K + 2 * (M * K // 2) + 2 * (M * K // 16)),
+        # the TK quantiser's own default recipe (one multiplication per element instead of an exact division)
+        "nvfp4_row_col_encode_centric": (lambda: fa4b.tk_quantize_for_gemm(x, encode_centric=True), 2 * M * K + 2 * (M * K // 2) + 2 * (M * K // 16)),
         "mxfp4": (lambda: fa4b.mxfp4_quantize_for_gemm(x), 2 * M * K + M * K // 2 + M * K // 32),
         # learned-weight recipe (one scale per 16 x 16 tile), both orientations, on the same matrix
         "nvfp4_weight_dual": (lambda: fa4b.prepare_nvfp4_projection_weight_dual(x), 2 * M * K + 2 * (M * K // 2) + 2 * (M * K // 16)),

@@ -210,4 +210,19 @@ __device__ __forceinline__ void nvfp4_codes16(const uint64_t (&x)[8], float bama
   e2m1_pack16(q, lo, hi);
 }
 
+// Encode-centric recipe of the TK quantiser (TK_quantisation/nvfp4_v6/core.cuh:47-60, 86-101;
+// fused_amax_quantize.cuh:235-256): the block's multiplier M = E4M3(6 / (bamax * S_enc)) is what is rounded, the
+// stored scale is E4M3(1 / M), and every element is one multiplication by M * S_enc before the E2M1 rounding.
+__device__ __forceinline__ void nvfp4_codes16_encode(const uint64_t (&x)[8], float bamax, float s_enc, uint32_t& sb, uint32_t& lo, uint32_t& hi) {
+  const uint32_t mbyte = bamax <= 1.0e-9f ? 0x7eu : (cvt_e4m3x2(fminf(6.0f / (bamax * s_enc), 3.4028235e38f), 0.f) & 0xffu);
+  const float m = e4m3_to_f32(mbyte);
+  const float coeff = m * s_enc;
+  sb = cvt_e4m3x2(1.0f / m, 0.f) & 0xffu;
+  const uint64_t c2 = pack2(coeff, coeff);
+  uint64_t q[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) q[i] = mul2(x[i], c2);
+  e2m1_pack16(q, lo, hi);
+}
+
 }  // namespace fa4b

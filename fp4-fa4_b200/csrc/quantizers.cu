@@ -240,6 +240,7 @@ struct Nvfp4Params {
   uint8_t* scales_row;
   uint8_t* codes_col;
   uint8_t* scales_col;
+  int recipe;  // FA4B_RECIPE_*
 };
 
 // W2D: one scale per 16 x 16 tile (learned projection weights): every 1 x 16 group of the tile, in either
@@ -261,6 +262,10 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
   const float amax = *p.amax;
   const float g = amax / kNvfp4GlobalDiv;
   const float inv6g = 1.0f / (6.0f * g);
+  // encode-centric recipe: S_enc = 2688 / amax, 1 for an all-zero tensor (core.cuh:103-113)
+  const bool enc = !W2D && p.recipe == FA4B_RECIPE_ENCODE_CENTRIC;
+  float s_enc = fminf(kNvfp4GlobalDiv / amax, 3.4028235e38f);
+  if (amax == 0.f || s_enc == 0.f) s_enc = 1.0f;
   if (blockIdx.x == 0 && blockIdx.y == 0 && t == 0) *p.global_scale = g;
   fill_step_table(steps, g, t);
 
@@ -330,7 +335,9 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
       const int kb = (c32 >> 4) + h;
       const float bamax = W2D ? tile_amax[(r >> 4) * 8 + kb] : m;
       uint32_t sbyte = 0;
-      if (!all_zero) {
+      if (enc) {
+        nvfp4_codes16_encode(x, bamax, s_enc, sbyte, codes[2 * h], codes[2 * h + 1]);
+      } else if (!all_zero) {
         sbyte = nvfp4_scale_byte(bamax, g, inv6g);
         nvfp4_codes16(x, bamax, steps, sbyte, codes[2 * h], codes[2 * h + 1]);
       }
@@ -358,7 +365,9 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
         }
         const float bamax = W2D ? tile_amax[rb * 8 + (c >> 4)] : m;
         uint32_t lo = 0, hi = 0, sbyte = 0;
-        if (!all_zero) {
+        if (enc) {
+          nvfp4_codes16_encode(x, bamax, s_enc, sbyte, lo, hi);
+        } else if (!all_zero) {
           sbyte = nvfp4_scale_byte(bamax, g, inv6g);
           nvfp4_codes16(x, bamax, steps, sbyte, lo, hi);
         }
@@ -541,6 +550,9 @@ static int quant_nvfp4_impl(const fa4b_quant_nvfp4_args* a, void* stream, bool w
   p.amax = a->amax; p.global_scale = a->global_scale;
   p.codes_row = a->codes_row; p.scales_row = a->scales_row;
   p.codes_col = a->codes_col; p.scales_col = a->scales_col;
+  FA4B_REQUIRE(a->recipe == FA4B_RECIPE_DECODE_CENTRIC || (a->recipe == FA4B_RECIPE_ENCODE_CENTRIC && !weight_tiles), FA4B_UNSUPPORTED,
+               "recipe %d (the 16 x 16 weight recipe is decode-centric only)", a->recipe);
+  p.recipe = a->recipe;
   return launch_nvfp4(p, false, st, weight_tiles);
 }
 
@@ -573,6 +585,8 @@ int fa4b_rmsnorm_quant_nvfp4(const fa4b_rmsnorm_quant_nvfp4_args* a, void* strea
   p.amax = a->amax; p.global_scale = a->global_scale;
   p.codes_row = a->codes_row; p.scales_row = a->scales_row;
   p.codes_col = a->codes_col; p.scales_col = a->scales_col;
+  FA4B_REQUIRE(a->recipe == FA4B_RECIPE_DECODE_CENTRIC || a->recipe == FA4B_RECIPE_ENCODE_CENTRIC, FA4B_UNSUPPORTED, "recipe %d", a->recipe);
+  p.recipe = a->recipe;
   return launch_nvfp4(p, true, st);
 }
 

@@ -24,7 +24,7 @@ class QuantNvfp4Args(C.Structure):
     _fields_ = [("x", C.c_void_p), ("rows", C.c_int64), ("cols", C.c_int64), ("ld", C.c_int64),
                 ("amax", C.c_void_p), ("amax_is_input", C.c_int), ("global_scale", C.c_void_p),
                 ("codes_row", C.c_void_p), ("scales_row", C.c_void_p),
-                ("codes_col", C.c_void_p), ("scales_col", C.c_void_p)]
+                ("codes_col", C.c_void_p), ("scales_col", C.c_void_p), ("recipe", C.c_int)]
 
 
 class ProjectNvfp4Args(C.Structure):
@@ -44,7 +44,7 @@ class RmsnormQuantArgs(C.Structure):
     _fields_ = [("x", C.c_void_p), ("gamma", C.c_void_p), ("rows", C.c_int64), ("cols", C.c_int64), ("ld", C.c_int64),
                 ("eps", C.c_float), ("inv_rms", C.c_void_p), ("y_out", C.c_void_p), ("amax", C.c_void_p),
                 ("global_scale", C.c_void_p), ("codes_row", C.c_void_p), ("scales_row", C.c_void_p),
-                ("codes_col", C.c_void_p), ("scales_col", C.c_void_p)]
+                ("codes_col", C.c_void_p), ("scales_col", C.c_void_p), ("recipe", C.c_int)]
 
 
 class RmsnormBwdArgs(C.Structure):

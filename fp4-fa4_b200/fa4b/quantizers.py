@@ -46,17 +46,20 @@ def _alloc_outputs(rows, cols, transpose, dev, block=16):
     return fp4_row, sc_row, fp4_col, sc_col
 
 
-def tk_quantize_for_gemm(input: torch.Tensor, return_transpose: bool = True, amax_in: torch.Tensor | None = None):
+def tk_quantize_for_gemm(input: torch.Tensor, return_transpose: bool = True, amax_in: torch.Tensor | None = None,
+                         encode_centric: bool = False):
     """NVFP4 of ``input [M,K]``: returns ``(fp4_row [M,K/2], sc_row [M/128,K/64,512],
     fp4_col [K,M/2] | None, sc_col [K/128,M/64,512] | None, sg [1], amax [1])``.
-    ``sg = amax/2688``; scale bytes are E4M3."""
+    ``sg = amax/2688``; scale bytes are E4M3.  ``encode_centric=True`` selects the TK quantiser's own default recipe
+    (the rounded quantity is the block multiplier, the stored scale its reciprocal); the default here is the
+    decode-centric arithmetic of the reference's Python oracle."""
     _require_matrix(input, "input")
     rows, cols = input.shape
     fp4_row, sc_row, fp4_col, sc_col = _alloc_outputs(rows, cols, return_transpose, input.device)
     am = torch.empty(1, dtype=torch.float32, device=input.device) if amax_in is None else amax_in
     sg = torch.empty(1, dtype=torch.float32, device=input.device)
     a = _lib.QuantNvfp4Args(ptr(input), rows, cols, input.stride(0), ptr(am), int(amax_in is not None), ptr(sg),
-                            ptr(fp4_row), ptr(sc_row), ptr(fp4_col), ptr(sc_col))
+                            ptr(fp4_row), ptr(sc_row), ptr(fp4_col), ptr(sc_col), int(bool(encode_centric)))
     check(lib().fa4b_quant_nvfp4(C.byref(a), C.c_void_p(current_stream())), "fa4b_quant_nvfp4")
     return fp4_row, sc_row, fp4_col, sc_col, sg, am
 
@@ -140,7 +143,7 @@ def rope_pair_(x: torch.Tensor, rope_cos: torch.Tensor, rope_sin: torch.Tensor, 
 
 
 def tk_fused_norm_quantize(input: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6, with_silu: bool = False,
-                           return_transpose: bool = True, return_normalized: bool = False):
+                           return_transpose: bool = True, return_normalized: bool = False, encode_centric: bool = False):
     """Fused RMSNorm + NVFP4: returns ``(fp4_row, sc_row, fp4_col, sc_col, sg,
     inv_rms [M], amax [1])`` (plus the bf16 normalised tensor when asked)."""
     _require_matrix(input, "input")
@@ -156,7 +159,7 @@ def tk_fused_norm_quantize(input: torch.Tensor, gamma: torch.Tensor, eps: float 
     sg = torch.empty(1, dtype=torch.float32, device=dev)
     y = torch.empty(rows, cols, dtype=torch.bfloat16, device=dev) if return_normalized else None
     a = _lib.RmsnormQuantArgs(ptr(input), ptr(gamma.contiguous()), rows, cols, input.stride(0), float(eps), ptr(inv_rms), ptr(y),
-                              ptr(am), ptr(sg), ptr(fp4_row), ptr(sc_row), ptr(fp4_col), ptr(sc_col))
+                              ptr(am), ptr(sg), ptr(fp4_row), ptr(sc_row), ptr(fp4_col), ptr(sc_col), int(bool(encode_centric)))
     check(lib().fa4b_rmsnorm_quant_nvfp4(C.byref(a), C.c_void_p(current_stream())), "fa4b_rmsnorm_quant_nvfp4")
     out = (fp4_row, sc_row, fp4_col, sc_col, sg, inv_rms, am)
     return out + (y,) if return_normalized else out

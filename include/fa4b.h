@@ -44,6 +44,11 @@ enum { FA4B_MASK_CAUSAL = 0, FA4B_MASK_NONE = 1 };
  * projection_fp4_epilogue.cuh:1922,1942: block scale E4M3(block amax / 6), no statistics pass) */
 enum { FA4B_GLOBAL_AMAX_PER_BH = 0, FA4B_GLOBAL_ONE = 1 };
 enum { FA4B_MX_CEIL = 0, FA4B_MX_RTE_MANTISSA = 1, FA4B_MX_FLOOR = 2 };
+/* NVFP4 block-scale recipe: decode-centric (the stored scale E4M3(bamax / 6 / g) is what is rounded; the
+ * arithmetic of fake_quantize_nvfp4) or encode-centric (the multiplier E4M3(6 / (bamax * 2688 / amax)) is
+ * rounded and the stored scale is E4M3 of its reciprocal: the default of tk_quantize_for_gemm,
+ * TK_quantisation/nvfp4_v6/fused_amax_quantize.cuh:235-256) */
+enum { FA4B_RECIPE_DECODE_CENTRIC = 0, FA4B_RECIPE_ENCODE_CENTRIC = 1 };
 /* fa4b_attn_bwd flags: a sequence-sharded run folds several key shards into one query shard's dQ */
 enum { FA4B_BWD_KEEP_DQ_ACCUM = 1 /* do not zero the accumulator first */, FA4B_BWD_SKIP_DQ_OUT = 2 /* do not convert it into dq */ };
 enum { FA4B_PREPARE_ALL = 0, FA4B_PREPARE_AMAX = 1, FA4B_PREPARE_QUANTIZE = 2 };
@@ -92,6 +97,7 @@ typedef struct fa4b_quant_nvfp4_args {
   uint8_t* scales_row;
   uint8_t* codes_col;  /* NULL = no transposed output */
   uint8_t* scales_col;
+  int recipe;          /* FA4B_RECIPE_* */
 } fa4b_quant_nvfp4_args;
 int fa4b_quant_nvfp4(const fa4b_quant_nvfp4_args* a, void* stream);
 
@@ -168,6 +174,7 @@ typedef struct fa4b_rmsnorm_quant_nvfp4_args {
   uint8_t* scales_row;
   uint8_t* codes_col;
   uint8_t* scales_col;
+  int recipe;          /* FA4B_RECIPE_* */
 } fa4b_rmsnorm_quant_nvfp4_args;
 int fa4b_rmsnorm_quant_nvfp4(const fa4b_rmsnorm_quant_nvfp4_args* a, void* stream);
 

@@ -166,6 +166,30 @@ def test_rope_pair_inverse_undoes_the_rotation_within_bf16_rounding():
     assert float(((n0 - n1).abs() / n0.clamp_min(1e-3)).max()) < 2e-2
 
 
+@pytest.mark.parametrize("shape,seed", [((128, 128), 11), ((256, 512), 12)])
+def test_nvfp4_encode_centric_recipe_matches_its_restatement(shape, seed):
+    # the TK quantiser's default recipe; its oracle is restated from the CUDA source only (parity unpinned)
+    x, gamma = O.make_quantizer_inputs(*shape, seed=seed)
+    x[3, 16:32] = 0.0            # an all-zero block: multiplier 448, stored scale E4M3(1/448)
+    x[7, :16] *= 1.0e-4          # a tiny block: the multiplier saturates at 448
+    fp4_row, sc_row, fp4_col, sc_col, sg, am = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=True, encode_centric=True)
+    ref, ref_t = O.nvfp4_quantize_encode_centric(x), O.nvfp4_quantize_encode_centric(x.t().contiguous())
+    assert float(sg) == float(ref.global_scale)
+    _same(fp4_row, ref.codes, "row codes")
+    _same(sc_row, ref.pages(), "row scale pages")
+    _same(fp4_col, ref_t.codes, "transposed codes")
+    _same(sc_col, ref_t.pages(), "transposed scale pages")
+    # fused with the RMSNorm
+    out = fa4b.tk_fused_norm_quantize(x.to(DEV), gamma.to(DEV), 1e-6, return_transpose=False, return_normalized=True, encode_centric=True)
+    y = out[-1].cpu()
+    ref_y = O.nvfp4_quantize_encode_centric(y)
+    _same(out[0], ref_y.codes, "fused row codes")
+    _same(out[1], ref_y.pages(), "fused row scale pages")
+    # a zero tensor keeps the recipe's E4M3(1/448) scale bytes and zero codes
+    z = fa4b.tk_quantize_for_gemm(torch.zeros(128, 128, dtype=torch.bfloat16, device=DEV), return_transpose=False, encode_centric=True)
+    assert int(z[0].max()) == 0 and z[1].unique().tolist() == [1] and float(z[4]) == 0.0
+
+
 def _wide_range(M, K, seed, lo=-20, hi=20):
     """rows of very different magnitude: small rows get scale byte 0 (step clamped to FLT_MIN), where x / step
     overflows and only the sign and saturation survive; mid rows land in the subnormal E4M3 scale range"""
