@@ -577,7 +577,9 @@ def run_module(args, rank, world, local_rank):
     B, Hq, Hkv, S, D, hidden = (WORKLOAD[k] for k in ("B", "Hq", "Hkv", "S", "D", "hidden"))
     g = torch.Generator(device=device).manual_seed(20260825)
     mk = lambda r, c: (torch.randn(r, c, device=device, generator=g) / c ** 0.5).bfloat16()
-    blk = LowpFA4AttentionBlock(mk(Hq * D, hidden), mk(Hkv * D, hidden), mk(Hkv * D, hidden), mk(hidden, Hq * D), Hq, Hkv, D)
+    # the QKV projection publishes the attention operands from its epilogue (no BF16 Q/K/V round trip)
+    blk = LowpFA4AttentionBlock(mk(Hq * D, hidden), mk(Hkv * D, hidden), mk(Hkv * D, hidden), mk(hidden, Hq * D), Hq, Hkv, D,
+                                fused_publish=not args.no_fused)
     x = torch.randn(B, S, hidden, device=device, generator=g).bfloat16()
     inv = 1.0 / (500000.0 ** (torch.arange(0, D, 2, device=device, dtype=torch.float64) / D))
     ang = torch.arange(S, device=device, dtype=torch.float64)[:, None] * inv[None, :]
@@ -621,7 +623,7 @@ def run_module(args, rank, world, local_rank):
                                  "flops": "2*M*hidden*(Hq+2Hkv)*D + 2*M*hidden*Hq*D + 2 causal matmuls", "l2": "flushed between timed steps"},
                       "forward_backward": {"ms_per_step": ms_fb, "tflops": flops_fb / ms_fb / 1e9,
                                            "flops": "3x the projection matmuls + 6 causal matmuls"},
-                      "gpu_launches": 13 * args.steps}), flush=True)
+                      "fused_publication": not args.no_fused, "gpu_launches": (10 if not args.no_fused else 13) * args.steps}), flush=True)
 
 
 def main():
@@ -633,6 +635,7 @@ def main():
     ap.add_argument("--workload", choices=tuple(WORKLOADS), default="c2",
                     help="'small' is for profiler captures; its line is not a benchmark result")
     ap.add_argument("--no-extras", action="store_true", help="skip the CPU baseline, quantizer and end-to-end legs")
+    ap.add_argument("--no-fused", action="store_true", help="module workload: separate projection, rotation and publication passes")
     args = ap.parse_args()
     WORKLOAD.update(WORKLOADS[args.workload])
     rank = int(os.environ.get("RANK", "0"))

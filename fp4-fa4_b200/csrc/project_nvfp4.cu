@@ -20,6 +20,7 @@
 
 #include <cuda_bf16.h>
 
+#include "attn.cuh"
 #include "common.cuh"
 #include "tc_sm100.cuh"
 
@@ -52,6 +53,7 @@ struct ProjSmem {
   uint64_t acc_full, acc_free, mma_drained;
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
+  StepTable steps;  // PUBLISH: steps of the 127 scale bytes at a unit global scale
 };
 
 struct ProjParams {
@@ -63,11 +65,19 @@ struct ProjParams {
   int64_t ldy;
   int M, N, K;
   uint32_t* status;
+  // publication mode (PUBLISH): the output columns are Hq query heads, Hkv key heads, Hkv value heads of 128 features;
+  // instead of BF16 rows the epilogue writes the attention operands of every head into the attention workspace
+  const __nv_bfloat16* rope_cos;  // [S, 64]
+  const __nv_bfloat16* rope_sin;
+  int S, Hq, Hkv;
+  uint8_t *q_codes, *q_pages, *q_fp8, *k_codes, *k_pages, *k_fp8, *v_fp8;
+  float *q_global, *k_global;
 };
 
 // TMEM columns: accumulator 0-255; scale factors of a stage: A 8 columns, W 16 columns, two slots
 constexpr uint32_t kColSf = 256, kSfSlot = 12 * kStepMmas;
 
+template <bool PUBLISH>
 __global__ void __launch_bounds__(kProjThreads, 1)
 project_nvfp4_kernel(const ProjParams p, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                      const __grid_constant__ CUtensorMap map_y) {
@@ -97,6 +107,14 @@ project_nvfp4_kernel(const ProjParams p, const __grid_constant__ CUtensorMap map
     mbar_init(&s.mma_drained, 1);
     s.abort_flag = 0;
     fence_barrier_init();
+  }
+  if (PUBLISH) {
+    fill_step_table(s.steps, 1.0f, t);
+    if (blockIdx.x == 0) {  // unit global decode scales of every (batch, head)
+      const int B = p.M / p.S;
+      for (int i = t; i < B * p.Hq; i += kProjThreads) p.q_global[i] = 1.0f;
+      for (int i = t; i < B * p.Hkv; i += kProjThreads) p.k_global[i] = 1.0f;
+    }
   }
   if (warp == 0) tmem_alloc(&s.tmem_base, 512);
   tc_fence_before();
@@ -204,6 +222,80 @@ project_nvfp4_kernel(const ProjParams p, const __grid_constant__ CUtensorMap map
       tmem_ld_wait(v[3]);
       tc_fence_before();
       mbar_arrive_warp(&s.acc_free);
+      if constexpr (PUBLISH) {
+        // This warp holds 32 tokens x the 128 features of one head.  Per 32 features: round to BF16 (the projection's
+        // output), rotate Q and K in packed BF16 (the arithmetic of rope_pair_kernel), then publish what the attention
+        // kernels read: E4M3(4x) rows, and for Q and K the NVFP4 codes and scale bytes at a unit global scale
+        // (fused in the reference's projection epilogue, projection_fp4_epilogue.cuh:1453-1579, 873-983).
+        const int hh = tn_i * 2 + half;
+        const int m = tm_i * kProjTileM + quarter * 32 + lane;
+        const int bi = m / p.S, si = m % p.S;
+        const bool is_v = hh >= p.Hq + p.Hkv;
+        const bool is_q = hh < p.Hq;
+        const int bh = is_q ? bi * p.Hq + hh : (is_v ? bi * p.Hkv + hh - p.Hq - p.Hkv : bi * p.Hkv + hh - p.Hq);
+        const size_t row_index = (size_t)bh * p.S + si;
+        uint8_t* fp8 = (is_q ? p.q_fp8 : is_v ? p.v_fp8 : p.k_fp8) + row_index * 128;
+        uint8_t* codes = (is_q ? p.q_codes : p.k_codes) + row_index * 64;
+        uint8_t* pages = (is_q ? p.q_pages : p.k_pages) + ((size_t)bh * (p.S / 128) + si / 128) * 2 * 512 + lane * 16 + quarter * 4;
+        const uint4* ct = reinterpret_cast<const uint4*>(p.rope_cos + (size_t)si * 64);
+        const uint4* st4 = reinterpret_cast<const uint4*>(p.rope_sin + (size_t)si * 64);
+        uint32_t sc4 = 0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[c][2 * i]) * gscale, __uint_as_float(v[c][2 * i + 1]) * gscale);
+            w[i] = *reinterpret_cast<const uint32_t*>(&h2);
+          }
+          if (!is_v) {
+            const uint4 c0 = __ldg(ct + 2 * c), c1 = __ldg(ct + 2 * c + 1), s0 = __ldg(st4 + 2 * c), s1 = __ldg(st4 + 2 * c + 1);
+            const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w}, sw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const uint32_t cc = ((cw[i >> 1] >> (16 * (i & 1))) & 0xffffu) * 0x00010001u;
+              const uint32_t s2 = ((sw[i >> 1] >> (16 * (i & 1))) & 0xffffu) * 0x00010001u;
+              const uint32_t perp = ((w[i] << 16) | (w[i] >> 16)) ^ 0x00008000u;  // (x, y) -> (-y, x)
+              const __nv_bfloat162 r = __hfma2(*reinterpret_cast<const __nv_bfloat162*>(&perp), *reinterpret_cast<const __nv_bfloat162*>(&s2),
+                                               __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]), *reinterpret_cast<const __nv_bfloat162*>(&cc)));
+              w[i] = *reinterpret_cast<const uint32_t*>(&r);
+            }
+          }
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk) {  // 16 features
+            uint64_t xp[8];
+            float bamax = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              xp[k] = bf16x2_to_f32x2(w[8 * blk + k]);
+              bamax = absmax3(bamax, xp[k]);
+            }
+            uint32_t o8[4];
+            const uint64_t four = pack2(4.f, 4.f);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              float a0, a1, b0, b1;
+              unpack2(mul2(xp[2 * k], four), a0, a1);
+              unpack2(mul2(xp[2 * k + 1], four), b0, b1);
+              o8[k] = cvt_e4m3x4(a0, a1, b0, b1);
+            }
+            *reinterpret_cast<uint4*>(fp8 + c * 32 + blk * 16) = make_uint4(o8[0], o8[1], o8[2], o8[3]);
+            if (!is_v) {
+              const int kb = 2 * c + blk;
+              const uint32_t sbyte = nvfp4_scale_byte(bamax, 1.0f, 1.0f / 6.0f);
+              uint32_t lo, hi;
+              nvfp4_codes16(xp, bamax, s.steps, sbyte, lo, hi);
+              *reinterpret_cast<uint2*>(codes + kb * 8) = make_uint2(lo, hi);
+              sc4 |= sbyte << (8 * (kb & 3));
+              if ((kb & 3) == 3) {  // the four scale bytes of this row in one page
+                *reinterpret_cast<uint32_t*>(pages + (kb >> 2) * 512) = sc4;
+                sc4 = 0;
+              }
+            }
+          }
+        }
+        continue;
+      }
       const int col = tn_i * kProjTileN + half * 128, row = tm_i * kProjTileM + quarter * 32;
       // BF16 in place: word 16 * c + i of `o` = columns 32 * c + 2 * i, + 1 of this lane's row
       uint32_t o[64];
@@ -249,40 +341,73 @@ project_nvfp4_kernel(const ProjParams p, const __grid_constant__ CUtensorMap map
 
 using namespace fa4b;
 
-int fa4b_project_nvfp4(const fa4b_project_nvfp4_args* a, void* stream) {
+static int project_check(const fa4b_project_nvfp4_args* a, bool need_y) {
   FA4B_REQUIRE(a != nullptr, FA4B_BAD_ARG, "args is NULL");
-  FA4B_REQUIRE(a->a_codes && a->a_scales && a->a_global && a->w_codes && a->w_scales && a->w_global && a->y && a->status, FA4B_BAD_ARG,
+  FA4B_REQUIRE(a->a_codes && a->a_scales && a->a_global && a->w_codes && a->w_scales && a->w_global && (a->y || !need_y) && a->status, FA4B_BAD_ARG,
                "fa4b_project_nvfp4: NULL pointer");
   FA4B_REQUIRE(a->M > 0 && a->N > 0 && a->K > 0 && a->M % kProjTileM == 0 && a->N % kProjTileN == 0 && a->K % kProjStepK == 0, FA4B_BAD_SHAPE,
                "M=%lld N=%lld K=%lld: M must be a multiple of 128, N of 256 and K of %d", (long long)a->M, (long long)a->N, (long long)a->K, kProjStepK);
   FA4B_REQUIRE(a->M < (1ll << 31) && a->N < (1ll << 31) && a->K < (1ll << 31), FA4B_BAD_SHAPE, "dimensions must fit 31 bits");
-  FA4B_REQUIRE(a->ldy >= a->N && a->ldy % 8 == 0 && (reinterpret_cast<uintptr_t>(a->y) & 15) == 0, FA4B_BAD_ALIGN,
-               "y must be 16-byte aligned with a row stride >= N that is a multiple of 8 elements");
   FA4B_REQUIRE(((reinterpret_cast<uintptr_t>(a->a_codes) | reinterpret_cast<uintptr_t>(a->w_codes) | reinterpret_cast<uintptr_t>(a->a_scales) |
                  reinterpret_cast<uintptr_t>(a->w_scales)) & 15) == 0, FA4B_BAD_ALIGN, "operands must be 16-byte aligned");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return FA4B_OK;
+}
+
+template <bool PUBLISH>
+static int project_launch(const fa4b_project_nvfp4_args* a, ProjParams p, const CUtensorMap& my, cudaStream_t st) {
   FA4B_CUDA(cudaMemsetAsync(a->status, 0, 4 * sizeof(uint32_t), st));
   CUtensorMap ma{}, mw{};
-  CUtensorMap my{};
   if (int s = make_tensor_map(&ma, a->a_codes, 1, (uint64_t)a->K / 2, (uint64_t)a->M, 0, (uint64_t)a->K / 2, 0, kRowBytes, kProjTileM)) return s;
   if (int s = make_tensor_map(&mw, a->w_codes, 1, (uint64_t)a->K / 2, (uint64_t)a->N, 0, (uint64_t)a->K / 2, 0, kRowBytes, kProjTileN)) return s;
-  if (int s = make_tensor_map(&my, a->y, 2, (uint64_t)a->N, (uint64_t)a->M, 0, (uint64_t)a->ldy * 2, 0, 64, 8)) return s;
   int dev = 0, sms = 0;
   FA4B_CUDA(cudaGetDevice(&dev));
   FA4B_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int smem = sizeof(ProjSmem);
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(project_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
+  std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(project_nvfp4_kernel<PUBLISH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
   FA4B_CUDA(attr_err);
-  ProjParams p{};
   p.a_sf = a->a_scales; p.w_sf = a->w_scales;
   p.a_global = a->a_global; p.w_global = a->w_global;
-  p.y = static_cast<__nv_bfloat16*>(a->y); p.ldy = a->ldy;
   p.M = (int)a->M; p.N = (int)a->N; p.K = (int)a->K;
   p.status = a->status;
   const int n_tiles = (p.M / kProjTileM) * (p.N / kProjTileN);
-  project_nvfp4_kernel<<<std::min(n_tiles, sms), kProjThreads, smem, st>>>(p, ma, mw, my);
+  project_nvfp4_kernel<PUBLISH><<<std::min(n_tiles, sms), kProjThreads, smem, st>>>(p, ma, mw, my);
   FA4B_CUDA(cudaGetLastError());
   return FA4B_OK;
+}
+
+int fa4b_project_nvfp4(const fa4b_project_nvfp4_args* a, void* stream) {
+  if (int s = project_check(a, true)) return s;
+  FA4B_REQUIRE(a->ldy >= a->N && a->ldy % 8 == 0 && (reinterpret_cast<uintptr_t>(a->y) & 15) == 0, FA4B_BAD_ALIGN,
+               "y must be 16-byte aligned with a row stride >= N that is a multiple of 8 elements");
+  CUtensorMap my{};
+  if (int s = make_tensor_map(&my, a->y, 2, (uint64_t)a->N, (uint64_t)a->M, 0, (uint64_t)a->ldy * 2, 0, 64, 8)) return s;
+  ProjParams p{};
+  p.y = static_cast<__nv_bfloat16*>(a->y); p.ldy = a->ldy;
+  return project_launch<false>(a, p, my, static_cast<cudaStream_t>(stream));
+}
+
+int fa4b_project_qkv_publish(const fa4b_project_nvfp4_args* a, const fa4b_attn_dims* d, const void* rope_cos, const void* rope_sin, void* ws,
+                             void* stream) {
+  if (int s = project_check(a, false)) return s;
+  FA4B_REQUIRE(d && rope_cos && rope_sin && ws, FA4B_BAD_ARG, "fa4b_project_qkv_publish: NULL pointer");
+  if (int s = check_dims(*d)) return s;
+  FA4B_REQUIRE(d->D == 128 && d->pv_format == FA4B_PV_FP8_E4M3 && d->global_scale_mode == FA4B_GLOBAL_ONE, FA4B_UNSUPPORTED,
+               "the fused publication serves head dim 128, FP8 P.V and the unit global scale");
+  FA4B_REQUIRE(a->M == (int64_t)d->B * d->S && a->N == (int64_t)(d->Hq + 2 * d->Hkv) * 128, FA4B_BAD_SHAPE,
+               "M=%lld N=%lld do not match B*S=%lld and (Hq + 2 Hkv) * 128 = %lld", (long long)a->M, (long long)a->N, (long long)d->B * d->S,
+               (long long)(d->Hq + 2 * d->Hkv) * 128);
+  FA4B_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 1023) == 0 && ((reinterpret_cast<uintptr_t>(rope_cos) | reinterpret_cast<uintptr_t>(rope_sin)) & 15) == 0,
+               FA4B_BAD_ALIGN, "workspace must be 1024-byte aligned, rope tables 16-byte aligned");
+  const fa4b_attn_ws_layout l = make_ws_layout(*d);
+  uint8_t* w8 = static_cast<uint8_t*>(ws);
+  ProjParams p{};
+  p.rope_cos = static_cast<const __nv_bfloat16*>(rope_cos); p.rope_sin = static_cast<const __nv_bfloat16*>(rope_sin);
+  p.S = d->S; p.Hq = d->Hq; p.Hkv = d->Hkv;
+  p.q_codes = w8 + l.q_codes; p.q_pages = w8 + l.q_scales; p.q_fp8 = w8 + l.q_fp8; p.q_global = reinterpret_cast<float*>(w8 + l.q_global);
+  p.k_codes = w8 + l.k_codes; p.k_pages = w8 + l.k_scales; p.k_fp8 = w8 + l.k_fp8; p.k_global = reinterpret_cast<float*>(w8 + l.k_global);
+  p.v_fp8 = w8 + l.v_fp8;
+  CUtensorMap my{};  // unused in this mode
+  return project_launch<true>(a, p, my, static_cast<cudaStream_t>(stream));
 }

@@ -12,6 +12,7 @@ from .quantizers import (  # noqa: F401
     mxfp4_quantize_for_gemm,
     prepare_nvfp4_projection_weight,
     project_nvfp4,
+    project_qkv_publish,
     rope_pair_,
     prepare_nvfp4_projection_weight_dual,
     rmsnorm_backward_bf16,
@@ -20,6 +21,6 @@ from .quantizers import (  # noqa: F401
 )
 
 __all__ = [
-    "amax", "dequant_mxfp4", "dequant_nvfp4", "mxfp4_quantize_for_gemm", "prepare_nvfp4_projection_weight", "project_nvfp4", "rope_pair_", "prepare_nvfp4_projection_weight_dual", "rmsnorm_backward_bf16", "tk_fused_norm_quantize",
+    "amax", "dequant_mxfp4", "dequant_nvfp4", "mxfp4_quantize_for_gemm", "prepare_nvfp4_projection_weight", "project_nvfp4", "project_qkv_publish", "rope_pair_", "prepare_nvfp4_projection_weight_dual", "rmsnorm_backward_bf16", "tk_fused_norm_quantize",
     "tk_quantize_for_gemm",
 ]

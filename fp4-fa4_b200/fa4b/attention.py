@@ -150,13 +150,20 @@ def attn_prepare(q, k, v, ws: Workspace, phase: str = "all") -> None:
     check(lib().fa4b_attn_prepare(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_prepare")
 
 
-def attn_forward_prepared(ws: Workspace, kv_ws: Workspace | None = None, causal: bool = True):
+def attn_forward_prepared(ws: Workspace, kv_ws: Workspace | None = None, causal: bool = True, out: torch.Tensor | None = None):
     """Forward on operands already published: queries from ``ws``, keys and values from ``kv_ws`` (default ``ws``).
-    ``causal=False`` lets every query see every key (an off-diagonal block of a sequence-sharded run)."""
+    ``causal=False`` lets every query see every key (an off-diagonal block of a sequence-sharded run); ``out`` as in
+    :func:`attn_forward`."""
     d = ws.dims
     dims = _lib.AttnDims(d.B, d.Hq, d.Hkv, d.S, d.D, d.softmax_scale, d.pv_format, 0 if causal else 1, d.global_scale_mode)
     dev = ws.buf.device
-    o = torch.empty(d.B, d.Hq, d.S, d.D, dtype=torch.bfloat16, device=dev)
+    if out is None:
+        o = torch.empty(d.B, d.Hq, d.S, d.D, dtype=torch.bfloat16, device=dev)
+    else:
+        _check_bhsd(out, "out")
+        if tuple(out.shape) != (d.B, d.Hq, d.S, d.D):
+            raise ValueError(f"out must be shaped {(d.B, d.Hq, d.S, d.D)}, got {tuple(out.shape)}")
+        o = out
     lse = torch.empty(d.B, d.Hq, d.S, dtype=torch.float32, device=dev)
     z = _lib.Strides()
     a = _lib.AttnFwdArgs(dims, 0, z, 0, z, 0, z, ptr(o), _strides(o), ptr(lse), ptr(ws.buf), 1, 0, 0,

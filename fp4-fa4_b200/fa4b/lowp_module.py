@@ -14,7 +14,8 @@ from __future__ import annotations
 import torch
 
 from . import attention
-from .quantizers import prepare_nvfp4_projection_weight_dual, project_nvfp4, rope_pair_, tk_quantize_for_gemm
+from . import _lib
+from .quantizers import prepare_nvfp4_projection_weight_dual, project_nvfp4, project_qkv_publish, rope_pair_, tk_quantize_for_gemm
 
 
 def pair_interleave_qk_rows(weight: torch.Tensor, n_heads: int, head_dim: int) -> torch.Tensor:
@@ -33,8 +34,17 @@ class LowpFA4AttentionBlock:
     rows of ``wq`` / ``wk`` are expected in the pair-native rotary order (see :func:`pair_interleave_qk_rows`)."""
 
     def __init__(self, wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, wo: torch.Tensor, n_heads: int, n_kv_heads: int,
-                 head_dim: int):
+                 head_dim: int, fused_publish: bool = False, global_scale: str | None = None):
+        """``fused_publish`` runs the QKV projection with rotation, quantisation and publication of the attention
+        operands in its epilogue (head_dim 128; implies the unit global scale of the reference's attention route);
+        ``global_scale`` ("amax_per_bh" or "one") chooses the Q/K recipe of the unfused path."""
         hidden = wq.shape[1]
+        if fused_publish and head_dim != 128:
+            raise ValueError("the fused publication serves head_dim 128")
+        if fused_publish and global_scale not in (None, "one"):
+            raise ValueError("the fused publication quantises Q and K at the unit global scale")
+        self.fused_publish = bool(fused_publish)
+        self.global_scale = "one" if fused_publish else (global_scale or "amax_per_bh")
         if head_dim not in (64, 128):
             raise ValueError(f"head_dim {head_dim}: the attention core supports 64 and 128")
         if n_heads % n_kv_heads:
@@ -68,15 +78,27 @@ class LowpFA4AttentionBlock:
         if not rows.is_contiguous():
             rows = rows.contiguous()
         a_codes, a_pages, _, _, a_g, _ = tk_quantize_for_gemm(rows, return_transpose=False)
+        o_rows = torch.empty(B * S, Hq * D, dtype=torch.bfloat16, device=x.device)
+        o_view = o_rows.view(B, S, Hq, D).permute(0, 2, 1, 3)
+        if self.fused_publish:
+            dims = _lib.AttnDims(B, Hq, Hkv, S, D, float(softmax_scale) if softmax_scale else 0.0, attention.PV_FORMATS["e4m3_fp8"], 0,
+                                 attention.GLOBAL_SCALE_MODES["one"])
+            ws = attention.alloc_workspace(dims, x.device)
+            project_qkv_publish((a_codes, a_pages, a_g), self.w_qkv, rope_cos, rope_sin, ws)
+            _, lse = attention.attn_forward_prepared(ws, out=o_view)
+            qkv = None
+            return self._finish(o_rows, lse, ws, qkv, rows, B, S, return_intermediates)
         qkv = project_nvfp4((a_codes, a_pages, a_g), self.w_qkv)                 # [B*S, (Hq + 2 Hkv) D]
         q = qkv[:, :Hq * D].view(B, S, Hq, D)
         k = qkv[:, Hq * D:(Hq + Hkv) * D].view(B, S, Hkv, D)
         v = qkv[:, (Hq + Hkv) * D:].view(B, S, Hkv, D)
         rope_pair_(q, rope_cos, rope_sin)
         rope_pair_(k, rope_cos, rope_sin)
-        o_rows = torch.empty(B * S, Hq * D, dtype=torch.bfloat16, device=x.device)
-        o, lse, ws = attention.attn_forward(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), softmax_scale,
-                                            out=o_rows.view(B, S, Hq, D).permute(0, 2, 1, 3))
+        _, lse, ws = attention.attn_forward(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), softmax_scale,
+                                            out=o_view, global_scale=self.global_scale)
+        return self._finish(o_rows, lse, ws, qkv, rows, B, S, return_intermediates)
+
+    def _finish(self, o_rows, lse, ws, qkv, rows, B, S, return_intermediates):
         o_codes, o_pages, _, _, o_g, _ = tk_quantize_for_gemm(o_rows, return_transpose=False)
         y = project_nvfp4((o_codes, o_pages, o_g), self.w_o).view(B, S, self.hidden)
         if return_intermediates:
@@ -147,8 +169,9 @@ class LowpFA4Attention(torch.nn.Module):
     pair-native rotary order.  The quantised weight operands are rebuilt whenever a parameter has changed
     (optimizer step, ``load_state_dict``), as the reference requires of a cached preparation."""
 
-    def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, device="cuda", linears=None):
+    def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, device="cuda", linears=None, fused_publish: bool = False):
         super().__init__()
+        self.fused_publish = bool(fused_publish)
         self.n_heads, self.n_kv_heads, self.head_dim = n_heads, n_kv_heads, head_dim
         self.n_rep = n_heads // n_kv_heads
         self.use_flex_attn = False
@@ -192,7 +215,8 @@ class LowpFA4Attention(torch.nn.Module):
         versions = tuple((w.data_ptr(), w._version) for w in ws)
         if self._block is None or versions != self._versions:
             with torch.no_grad():
-                self._block = LowpFA4AttentionBlock(*(w.detach() for w in ws), self.n_heads, self.n_kv_heads, self.head_dim)
+                self._block = LowpFA4AttentionBlock(*(w.detach() for w in ws), self.n_heads, self.n_kv_heads, self.head_dim,
+                                                    fused_publish=self.fused_publish)
             self._versions = versions
         return self._block
 

@@ -127,6 +127,33 @@ def project_nvfp4(input_operand, weight_operand, out: torch.Tensor | None = None
     return out
 
 
+def project_qkv_publish(input_operand, weight_operand, rope_cos: torch.Tensor, rope_sin: torch.Tensor, workspace,
+                        status: torch.Tensor | None = None) -> None:
+    """QKV projection with the attention operands published from its epilogue: after the call ``workspace`` (an
+    ``attention.Workspace`` whose dims have ``D = 128``, FP8 P.V and ``global_scale="one"``) holds what
+    ``project_nvfp4`` + ``rope_pair_`` on Q and K + ``attention.attn_prepare`` would have put there, and the forward
+    runs with ``attention.attn_forward_prepared``.  Weight rows: Hq query heads, Hkv key heads, Hkv value heads."""
+    a, a_sc, a_g = input_operand
+    w, w_sc, w_g = weight_operand
+    M, K, N = a.shape[0], a.shape[1] * 2, w.shape[0]
+    if w.shape[1] * 2 != K:
+        raise ValueError(f"inner dimensions differ: activation K={K}, weight K={w.shape[1] * 2}")
+    d = workspace.dims
+    for name, t in (("rope_cos", rope_cos), ("rope_sin", rope_sin)):
+        if t.dtype != torch.bfloat16 or tuple(t.shape) != (d.S, 64) or not t.is_contiguous() or not t.is_cuda:
+            raise ValueError(f"{name} must be a contiguous CUDA bfloat16 [S, 64] tensor")
+    own = status is None
+    if own:
+        status = torch.empty(4, dtype=torch.int32, device=a.device)
+    args = _lib.ProjectNvfp4Args(ptr(a), ptr(a_sc), ptr(a_g), ptr(w), ptr(w_sc), ptr(w_g), M, N, K, 0, 0, ptr(status))
+    check(lib().fa4b_project_qkv_publish(C.byref(args), C.byref(d), C.c_void_p(ptr(rope_cos)), C.c_void_p(ptr(rope_sin)),
+                                         C.c_void_p(ptr(workspace.buf)), C.c_void_p(current_stream())), "fa4b_project_qkv_publish")
+    if own:
+        st = status.cpu().tolist()
+        if st[0] != 0:
+            raise RuntimeError(f"fa4b_project_qkv_publish: a device-side wait gave up (site {st[1]}, block {st[2]}, detail {st[3]})")
+
+
 def rope_pair_(x: torch.Tensor, rope_cos: torch.Tensor, rope_sin: torch.Tensor, inverse: bool = False) -> torch.Tensor:
     """In-place pair-native rotary embedding of ``x [B,S,H,D]`` bf16 (any strides with a contiguous last dimension)
     with bf16 tables ``[S, D/2]``; ``inverse=True`` turns the other way (gradients).  One tensor of

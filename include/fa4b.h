@@ -136,6 +136,21 @@ typedef struct fa4b_project_nvfp4_args {
 } fa4b_project_nvfp4_args;
 int fa4b_project_nvfp4(const fa4b_project_nvfp4_args* a, void* stream);
 
+/* ---- fa4b_project_qkv_publish --------------------------------------------
+ * The QKV projection of an attention block with the publication of the
+ * attention operands fused into its epilogue: y = x . Wqkv^T is never written;
+ * per head of 128 features the epilogue rounds to bf16, rotates Q and K
+ * (pair-native, tables bf16 [S, 64]) and writes into the attention workspace
+ * `ws` (layout of fa4b_attn_ws_layout_query for `d`) the NVFP4 codes and scale
+ * pages of Q and K at a unit global scale, and E4M3(4x) of Q, K and V --
+ * what fa4b_project_nvfp4 + fa4b_rope_pair + fa4b_attn_prepare produce in
+ * three passes.  The columns of Wqkv are Hq query heads, Hkv key heads, Hkv
+ * value heads; rows of x are tokens (batch-major).  a->y is ignored.
+ * Requires d->D == 128, FA4B_PV_FP8_E4M3, FA4B_GLOBAL_ONE.  Replaces the
+ * epilogue of b300_project_qkv_gqa_d128_unified_lowp_nvfp4
+ * (tk_fa4/interface.py:5238; projection_fp4_epilogue.cuh:1453-1579, 873-983).
+ * Declared after fa4b_attn_dims below. */
+
 /* ---- fa4b_rope_pair -------------------------------------------------------
  * In-place rotary embedding of x[B, S, H, D] bf16 (element strides given; the
  * last dimension contiguous) in the pair-native order: (x[2i], x[2i+1]) turns
@@ -245,6 +260,8 @@ typedef struct fa4b_strides {
 } fa4b_strides;
 
 size_t fa4b_attn_workspace_bytes(const fa4b_attn_dims* d);
+int fa4b_project_qkv_publish(const fa4b_project_nvfp4_args* a, const fa4b_attn_dims* d, const void* rope_cos, const void* rope_sin, void* ws,
+                             void* stream);
 
 /* Offsets (bytes) of the cached operands inside the workspace.  With pv_format = FA4B_PV_MXFP4_E8M0 the
  * `v_fp8` section holds V as sequence-grouped MXFP4 instead (the operand of forward_hao_direct_fp4pv,

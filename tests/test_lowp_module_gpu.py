@@ -122,6 +122,59 @@ def test_trainable_module_routes_autograd_through_the_block_and_requantises_afte
         mod(x.to(DEV), freqs, attention_masks=object())
 
 
+def test_fused_qkv_publication_writes_the_same_operands_as_the_three_passes():
+    from fa4b import attention
+
+    B, S, hidden, Hq, Hkv, D = 2, 256, 512, 4, 2, 128
+    x, wq, wk, wv, wo, cos, sin = _block_inputs(B, S, hidden, Hq, Hkv, D, seed=61)
+    cos, sin = cos.to(DEV), sin.to(DEV)
+    rows = x.to(DEV).reshape(B * S, hidden)
+    a_codes, a_pages, _, _, a_g, _ = fa4b.tk_quantize_for_gemm(rows, return_transpose=False)
+    weight = fa4b.prepare_nvfp4_projection_weight(torch.cat((wq, wk, wv), 0).contiguous().to(DEV))
+    # three passes: projection, rotation, publication at a unit global scale
+    qkv = fa4b.project_nvfp4((a_codes, a_pages, a_g), weight)
+    q = qkv[:, :Hq * D].view(B, S, Hq, D)
+    k = qkv[:, Hq * D:(Hq + Hkv) * D].view(B, S, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(B, S, Hkv, D)
+    fa4b.rope_pair_(q, cos, sin)
+    fa4b.rope_pair_(k, cos, sin)
+    qh, kh, vh = (t.permute(0, 2, 1, 3) for t in (q, k, v))
+    o_ref, lse_ref, ws_ref = attention.attn_forward(qh, kh, vh, global_scale="one")
+    # one pass
+    ws = attention.alloc_workspace(attention.make_dims(qh, kh, None, "e4m3_fp8", global_scale="one"), DEV)
+    ws.buf.zero_()
+    fa4b.project_qkv_publish((a_codes, a_pages, a_g), weight, cos, sin, ws)
+    got, want = ws.operands(), ws_ref.operands()
+    for name in ("q_codes", "q_scales", "q_global", "k_codes", "k_scales", "k_global", "v_fp8", "q_fp8", "k_fp8"):
+        if name in want:
+            assert torch.equal(got[name].view(torch.uint8), want[name].view(torch.uint8)), name
+    o, lse = attention.attn_forward_prepared(ws)
+    assert torch.equal(o, o_ref) and torch.equal(lse, lse_ref)
+
+
+def test_module_with_fused_publication_matches_the_unfused_module_and_the_oracle():
+    B, S, hidden, Hq, Hkv, D = 1, 256, 512, 4, 2, 128
+    x, wq, wk, wv, wo, cos, sin = _block_inputs(B, S, hidden, Hq, Hkv, D, seed=71)
+    dy = (torch.randn(B, S, hidden, generator=torch.Generator().manual_seed(72)) * 0.05).bfloat16()
+    w = [t.to(DEV) for t in (wq, wk, wv, wo)]
+    fused = LowpFA4AttentionBlock(*w, Hq, Hkv, D, fused_publish=True)
+    plain = LowpFA4AttentionBlock(*w, Hq, Hkv, D, global_scale="one")
+    yf, sf = fused.forward(x.to(DEV), cos.to(DEV), sin.to(DEV), return_intermediates=True)
+    yp, sp = plain.forward(x.to(DEV), cos.to(DEV), sin.to(DEV), return_intermediates=True)
+    assert torch.equal(yf, yp) and torch.equal(sf["lse"], sp["lse"]) and sf["qkv"] is None
+    gf = fused.backward(dy.to(DEV), sf, cos.to(DEV), sin.to(DEV))
+    gp = plain.backward(dy.to(DEV), sp, cos.to(DEV), sin.to(DEV))
+    for a, b in zip(gf, gp):
+        assert torch.equal(a, b)
+    ref_y, _, _ = O.lowp_attention_block_reference(x, wq, wk, wv, wo, cos, sin, Hq, Hkv, D, global_scale="one")
+    assert O.rel_l2(ref_y.float(), yf.float().cpu()) < 2e-2
+    want = O.lowp_attention_block_backward_reference(dy, x, wq, wk, wv, wo, cos, sin, Hq, Hkv, D, global_scale="one")
+    for name, g, r in zip(("dx", "dwq", "dwk", "dwv", "dwo"), gf, want):
+        assert O.rel_l2(r.float(), g.float().cpu()) < 5e-2, name
+    with pytest.raises(ValueError):
+        LowpFA4AttentionBlock(*w, Hq, Hkv, D, fused_publish=True, global_scale="amax_per_bh")
+
+
 class _TitanAttention(torch.nn.Module):
     """TorchTitan's Llama attention in a few lines: complex-pair rotation, repeated KV, causal softmax attention."""
 
