@@ -259,6 +259,24 @@ def quantizer_rates(device, reps=10):
     return out
 
 
+def init_nccl(device):
+    """Process group for the ranks torchrun started.  NCCL may print its version banner on standard output when the
+    first communicator is built; standard output carries the one JSON line, so the banner goes to standard error."""
+    import torch.distributed as dist
+
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        dist.init_process_group("nccl", device_id=device)
+        dist.barrier()
+        torch.cuda.synchronize()
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
 
@@ -267,7 +285,7 @@ def run_ours(args, rank, world, local_rank):
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        init_nccl(device)
     B, Hq, Hkv, S, D = (WORKLOAD[k] for k in ("B", "Hq", "Hkv", "S", "D"))
     host, (q, k, v, do) = make_inputs(20260825 + rank, device, pin=True)
     flops_step = 6.0 * causal_matmul_flops(B, Hq, S, D)  # per rank
@@ -391,7 +409,9 @@ def run_ours(args, rank, world, local_rank):
     fwd_ach = 2.0 * f1 / (fwd_ms * 1e-3) / 1e12
     cpu = cpu_emulation_rate()[0] if extras else None
     quant = quantizer_rates(device) if extras else {}
-    others = other_configurations(device) if (extras and args.workload == "c2") else {}
+    # one-GPU side measurements: with more ranks the other ranks have already left, and the long-context route would
+    # address them through the default process group
+    others = other_configurations(device) if (extras and args.workload == "c2" and world == 1) else {}
     for qv in quant.values():
         if "gbs" in qv:
             qv["frac_of_hbm"] = qv["gbs"] / peaks["hbm_gbs"]
@@ -444,7 +464,7 @@ def run_c5(args, rank, world, local_rank):
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        init_nccl(device)
     B, Hq, Hkv, S, D = (WORKLOAD[k] for k in ("B", "Hq", "Hkv", "S", "D"))
     g = torch.Generator(device=device).manual_seed(20260825 + rank)
     Sl = S // world
