@@ -77,7 +77,9 @@ class LowpFA4AttentionBlock:
         rows = x.reshape(B * S, self.hidden)
         if not rows.is_contiguous():
             rows = rows.contiguous()
-        a_codes, a_pages, _, _, a_g, _ = tk_quantize_for_gemm(rows, return_transpose=False)
+        # with a backward to follow, the token-major (column) operand of the weight-gradient GEMM comes from the same pass
+        a_codes, a_pages, x_c, x_cp, a_g, _ = tk_quantize_for_gemm(rows, return_transpose=return_intermediates)
+        x_cols = (x_c, x_cp, a_g) if return_intermediates else None
         o_rows = torch.empty(B * S, Hq * D, dtype=torch.bfloat16, device=x.device)
         o_view = o_rows.view(B, S, Hq, D).permute(0, 2, 1, 3)
         if self.fused_publish:
@@ -87,7 +89,7 @@ class LowpFA4AttentionBlock:
             project_qkv_publish((a_codes, a_pages, a_g), self.w_qkv, rope_cos, rope_sin, ws)
             _, lse = attention.attn_forward_prepared(ws, out=o_view)
             qkv = None
-            return self._finish(o_rows, lse, ws, qkv, rows, B, S, return_intermediates)
+            return self._finish(o_rows, lse, ws, qkv, rows, x_cols, B, S, return_intermediates)
         qkv = project_nvfp4((a_codes, a_pages, a_g), self.w_qkv)                 # [B*S, (Hq + 2 Hkv) D]
         q = qkv[:, :Hq * D].view(B, S, Hq, D)
         k = qkv[:, Hq * D:(Hq + Hkv) * D].view(B, S, Hkv, D)
@@ -96,13 +98,13 @@ class LowpFA4AttentionBlock:
         rope_pair_(k, rope_cos, rope_sin)
         _, lse, ws = attention.attn_forward(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), softmax_scale,
                                             out=o_view, global_scale=self.global_scale)
-        return self._finish(o_rows, lse, ws, qkv, rows, B, S, return_intermediates)
+        return self._finish(o_rows, lse, ws, qkv, rows, x_cols, B, S, return_intermediates)
 
-    def _finish(self, o_rows, lse, ws, qkv, rows, B, S, return_intermediates):
-        o_codes, o_pages, _, _, o_g, _ = tk_quantize_for_gemm(o_rows, return_transpose=False)
+    def _finish(self, o_rows, lse, ws, qkv, rows, x_cols, B, S, return_intermediates):
+        o_codes, o_pages, o_c, o_cp, o_g, _ = tk_quantize_for_gemm(o_rows, return_transpose=return_intermediates)
         y = project_nvfp4((o_codes, o_pages, o_g), self.w_o).view(B, S, self.hidden)
         if return_intermediates:
-            return y, {"qkv": qkv, "o": o_rows, "lse": lse, "workspace": ws, "x_rows": rows}
+            return y, {"qkv": qkv, "o": o_rows, "lse": lse, "workspace": ws, "x_rows": rows, "x_cols": x_cols, "o_cols": (o_c, o_cp, o_g)}
         return y
 
     __call__ = forward
@@ -122,12 +124,11 @@ class LowpFA4AttentionBlock:
         dy_rows = dy.reshape(M, self.hidden)
         if not dy_rows.is_contiguous():
             dy_rows = dy_rows.contiguous()
-        o_rows, qkv, lse, ws, x_rows = saved["o"], saved["qkv"], saved["lse"], saved["workspace"], saved["x_rows"]
+        o_rows, lse, ws = saved["o"], saved["lse"], saved["workspace"]
         # output projection: dO = dY . Wo, dWo = dY^T . O
         dy_r, dy_rp, dy_c, dy_cp, dy_g, _ = tk_quantize_for_gemm(dy_rows, return_transpose=True)
         do_rows = project_nvfp4((dy_r, dy_rp, dy_g), self.w_o_t)                               # [M, Hq D]
-        _, _, o_c, o_cp, o_g, _ = tk_quantize_for_gemm(o_rows, return_transpose=True)
-        dwo = project_nvfp4((dy_c, dy_cp, dy_g), (o_c, o_cp, o_g))                             # [hidden, Hq D]
+        dwo = project_nvfp4((dy_c, dy_cp, dy_g), saved["o_cols"])                              # [hidden, Hq D]
         # attention core, gradients written into the columns of one [M, (Hq + 2 Hkv) D] buffer
         dqkv = torch.empty(M, (Hq + 2 * Hkv) * D, dtype=torch.bfloat16, device=dy.device)
         dq = dqkv[:, :Hq * D].view(B, S, Hq, D)
@@ -140,8 +141,7 @@ class LowpFA4AttentionBlock:
         # QKV projection: dX = dQKV . Wqkv, dWqkv = dQKV^T . X
         g_r, g_rp, g_c, g_cp, g_g, _ = tk_quantize_for_gemm(dqkv, return_transpose=True)
         dx = project_nvfp4((g_r, g_rp, g_g), self.w_qkv_t).view(B, S, self.hidden)
-        _, _, x_c, x_cp, x_g, _ = tk_quantize_for_gemm(x_rows, return_transpose=True)
-        dwqkv = project_nvfp4((g_c, g_cp, g_g), (x_c, x_cp, x_g))                              # [(Hq + 2 Hkv) D, hidden]
+        dwqkv = project_nvfp4((g_c, g_cp, g_g), saved["x_cols"])                               # [(Hq + 2 Hkv) D, hidden]
         return dx, dwqkv[:Hq * D], dwqkv[Hq * D:(Hq + Hkv) * D], dwqkv[(Hq + Hkv) * D:], dwo
 
 
