@@ -72,12 +72,19 @@ struct ProjParams {
   int S, Hq, Hkv;
   uint8_t *q_codes, *q_pages, *q_fp8, *k_codes, *k_pages, *k_fp8, *v_fp8;
   float *q_global, *k_global;
+  // dO publication mode: the output columns are the Hq heads of dO; O rows [M, Hq * 128] bf16 and LSE [B, Hq, S] in
+  const __nv_bfloat16* o_rows;
+  const float* lse;
+  uint8_t* do_fp8;
+  float *dstat, *lstat;
 };
 
 // TMEM columns: accumulator 0-255; scale factors of a stage: A 8 columns, W 16 columns, two slots
 constexpr uint32_t kColSf = 256, kSfSlot = 12 * kStepMmas;
 
-template <bool PUBLISH>
+// MODE 0: BF16 rows out; 1: QKV projection publishing the attention operands; 2: output projection's input-gradient
+// GEMM publishing dO and the row statistics of the attention backward
+template <int MODE>
 __global__ void __launch_bounds__(kProjThreads, 1)
 project_nvfp4_kernel(const ProjParams p, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                      const __grid_constant__ CUtensorMap map_y) {
@@ -108,6 +115,7 @@ project_nvfp4_kernel(const ProjParams p, const __grid_constant__ CUtensorMap map
     s.abort_flag = 0;
     fence_barrier_init();
   }
+  constexpr bool PUBLISH = MODE == 1;
   if (PUBLISH) {
     fill_step_table(s.steps, 1.0f, t);
     if (blockIdx.x == 0) {  // unit global decode scales of every (batch, head)
@@ -296,6 +304,58 @@ project_nvfp4_kernel(const ProjParams p, const __grid_constant__ CUtensorMap map
         }
         continue;
       }
+      if constexpr (MODE == 2) {
+        // This warp holds dO of 32 tokens x one head.  Round to BF16 (the GEMM's output), then what
+        // bwd_preprocess_kernel makes of it: E5M2(4 dO), dstat = -4 sum_d O float(dO5) with that kernel's
+        // association order (sixteen partial sums of eight features, then a balanced tree), lstat = 8 - LSE log2e
+        // (fused in the reference's output-projection dgrad epilogue, projection_fp4_epilogue.cuh:4049-4127).
+        const int hh = tn_i * 2 + half;
+        const int m = tm_i * kProjTileM + quarter * 32 + lane;
+        const int bi = m / p.S, si = m % p.S;
+        const size_t row_index = ((size_t)bi * p.Hq + hh) * p.S + si;
+        const uint4* orow = reinterpret_cast<const uint4*>(p.o_rows + (size_t)m * p.Hq * 128 + hh * 128);
+        uint8_t* dst = p.do_fp8 + row_index * 128;
+        float part[16];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int g8 = 0; g8 < 4; ++g8) {  // eight features
+            uint32_t dw[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[c][8 * g8 + 2 * i]) * gscale,
+                                                               __uint_as_float(v[c][8 * g8 + 2 * i + 1]) * gscale);
+              dw[i] = *reinterpret_cast<const uint32_t*>(&h2);
+            }
+            const uint4 ov = __ldg(orow + 4 * c + g8);
+            const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
+            uint32_t packed[2];
+            float acc = 0.f;
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+              packed[k] = cvt_e5m2x4(4.f * bf16_bits_to_f32(dw[2 * k] & 0xffffu), 4.f * bf16_bits_to_f32(dw[2 * k] >> 16),
+                                     4.f * bf16_bits_to_f32(dw[2 * k + 1] & 0xffffu), 4.f * bf16_bits_to_f32(dw[2 * k + 1] >> 16));
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const uint32_t ob = ow[2 * k + (e >> 1)];
+                const float of = bf16_bits_to_f32((e & 1) ? (ob >> 16) : (ob & 0xffffu));
+                acc = fmaf(of, __half2float(__ushort_as_half((unsigned short)(((packed[k] >> (8 * e)) & 0xffu) << 8))), acc);
+              }
+            }
+            *reinterpret_cast<uint2*>(dst + (4 * c + g8) * 8) = make_uint2(packed[0], packed[1]);
+            part[4 * c + g8] = acc;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) part[i] += part[i + 8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) part[i] += part[i + 4];
+        part[0] += part[2];
+        part[1] += part[3];
+        p.dstat[row_index] = -4.0f * (part[0] + part[1]);
+        p.lstat[row_index] = kPLift - __ldg(p.lse + row_index) * kLog2e;
+        continue;
+      }
       const int col = tn_i * kProjTileN + half * 128, row = tm_i * kProjTileM + quarter * 32;
       // BF16 in place: word 16 * c + i of `o` = columns 32 * c + 2 * i, + 1 of this lane's row
       uint32_t o[64];
@@ -353,7 +413,7 @@ static int project_check(const fa4b_project_nvfp4_args* a, bool need_y) {
   return FA4B_OK;
 }
 
-template <bool PUBLISH>
+template <int MODE>
 static int project_launch(const fa4b_project_nvfp4_args* a, ProjParams p, const CUtensorMap& my, cudaStream_t st) {
   FA4B_CUDA(cudaMemsetAsync(a->status, 0, 4 * sizeof(uint32_t), st));
   CUtensorMap ma{}, mw{};
@@ -365,14 +425,14 @@ static int project_launch(const fa4b_project_nvfp4_args* a, ProjParams p, const 
   const int smem = sizeof(ProjSmem);
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(project_nvfp4_kernel<PUBLISH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
+  std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(project_nvfp4_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
   FA4B_CUDA(attr_err);
   p.a_sf = a->a_scales; p.w_sf = a->w_scales;
   p.a_global = a->a_global; p.w_global = a->w_global;
   p.M = (int)a->M; p.N = (int)a->N; p.K = (int)a->K;
   p.status = a->status;
   const int n_tiles = (p.M / kProjTileM) * (p.N / kProjTileN);
-  project_nvfp4_kernel<PUBLISH><<<std::min(n_tiles, sms), kProjThreads, smem, st>>>(p, ma, mw, my);
+  project_nvfp4_kernel<MODE><<<std::min(n_tiles, sms), kProjThreads, smem, st>>>(p, ma, mw, my);
   FA4B_CUDA(cudaGetLastError());
   return FA4B_OK;
 }
@@ -385,7 +445,7 @@ int fa4b_project_nvfp4(const fa4b_project_nvfp4_args* a, void* stream) {
   if (int s = make_tensor_map(&my, a->y, 2, (uint64_t)a->N, (uint64_t)a->M, 0, (uint64_t)a->ldy * 2, 0, 64, 8)) return s;
   ProjParams p{};
   p.y = static_cast<__nv_bfloat16*>(a->y); p.ldy = a->ldy;
-  return project_launch<false>(a, p, my, static_cast<cudaStream_t>(stream));
+  return project_launch<0>(a, p, my, static_cast<cudaStream_t>(stream));
 }
 
 int fa4b_project_qkv_publish(const fa4b_project_nvfp4_args* a, const fa4b_attn_dims* d, const void* rope_cos, const void* rope_sin, void* ws,
@@ -409,5 +469,26 @@ int fa4b_project_qkv_publish(const fa4b_project_nvfp4_args* a, const fa4b_attn_d
   p.k_codes = w8 + l.k_codes; p.k_pages = w8 + l.k_scales; p.k_fp8 = w8 + l.k_fp8; p.k_global = reinterpret_cast<float*>(w8 + l.k_global);
   p.v_fp8 = w8 + l.v_fp8;
   CUtensorMap my{};  // unused in this mode
-  return project_launch<true>(a, p, my, static_cast<cudaStream_t>(stream));
+  return project_launch<1>(a, p, my, static_cast<cudaStream_t>(stream));
+}
+
+int fa4b_project_dout_publish(const fa4b_project_nvfp4_args* a, const fa4b_attn_dims* d, const void* o_rows, const float* lse, void* ws,
+                              void* stream) {
+  if (int s = project_check(a, false)) return s;
+  FA4B_REQUIRE(d && o_rows && lse && ws, FA4B_BAD_ARG, "fa4b_project_dout_publish: NULL pointer");
+  if (int s = check_dims(*d)) return s;
+  FA4B_REQUIRE(d->D == 128 && d->pv_format == FA4B_PV_FP8_E4M3, FA4B_UNSUPPORTED, "the fused dO publication serves head dim 128 and FP8 P.V");
+  FA4B_REQUIRE(a->M == (int64_t)d->B * d->S && a->N == (int64_t)d->Hq * 128, FA4B_BAD_SHAPE,
+               "M=%lld N=%lld do not match B*S=%lld and Hq * 128 = %lld", (long long)a->M, (long long)a->N, (long long)d->B * d->S,
+               (long long)d->Hq * 128);
+  FA4B_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 1023) == 0 && (reinterpret_cast<uintptr_t>(o_rows) & 15) == 0, FA4B_BAD_ALIGN,
+               "workspace must be 1024-byte aligned, the O rows 16-byte aligned");
+  const fa4b_attn_ws_layout l = make_ws_layout(*d);
+  uint8_t* w8 = static_cast<uint8_t*>(ws);
+  ProjParams p{};
+  p.S = d->S; p.Hq = d->Hq; p.Hkv = d->Hkv;
+  p.o_rows = static_cast<const __nv_bfloat16*>(o_rows); p.lse = lse;
+  p.do_fp8 = w8 + l.do_fp8; p.dstat = reinterpret_cast<float*>(w8 + l.dstat); p.lstat = reinterpret_cast<float*>(w8 + l.lstat);
+  CUtensorMap my{};  // unused in this mode
+  return project_launch<2>(a, p, my, static_cast<cudaStream_t>(stream));
 }

@@ -13,6 +13,7 @@ from .quantizers import (  # noqa: F401
     prepare_nvfp4_projection_weight,
     project_nvfp4,
     project_qkv_publish,
+    project_dout_publish,
     rope_pair_,
     prepare_nvfp4_projection_weight_dual,
     rmsnorm_backward_bf16,
@@ -21,6 +22,6 @@ from .quantizers import (  # noqa: F401
 )
 
 __all__ = [
-    "amax", "dequant_mxfp4", "dequant_nvfp4", "mxfp4_quantize_for_gemm", "prepare_nvfp4_projection_weight", "project_nvfp4", "project_qkv_publish", "rope_pair_", "prepare_nvfp4_projection_weight_dual", "rmsnorm_backward_bf16", "tk_fused_norm_quantize",
+    "amax", "dequant_mxfp4", "dequant_nvfp4", "mxfp4_quantize_for_gemm", "prepare_nvfp4_projection_weight", "project_nvfp4", "project_qkv_publish", "project_dout_publish", "rope_pair_", "prepare_nvfp4_projection_weight_dual", "rmsnorm_backward_bf16", "tk_fused_norm_quantize",
     "tk_quantize_for_gemm",
 ]

@@ -212,18 +212,27 @@ BWD_KEEP_DQ_ACCUM, BWD_SKIP_DQ_OUT = 1, 2
 
 
 def attn_backward_prepared(ws: Workspace, kv_ws: Workspace | None = None, causal: bool = True, keep_dq_accum: bool = False,
-                           write_dq: bool = True):
+                           write_dq: bool = True, out=None):
     """Backward block call on published operands and statistics: queries, dO and the row statistics from ``ws``
     (:func:`attn_bwd_preprocess` has run on it with the LSE and O of the whole sequence), keys and values from
     ``kv_ws`` (default ``ws``).  Returns ``(dq | None, dk, dv)``: dK and dV of this block alone (bf16); the query
     gradient accumulates in ``ws``'s FP32 scratch across calls with ``keep_dq_accum`` and is only converted into
-    ``dq`` when ``write_dq``."""
+    ``dq`` when ``write_dq``.  ``out=(dq, dk, dv)`` supplies strided destinations as in :func:`attn_backward`."""
     d = ws.dims
     dims = _lib.AttnDims(d.B, d.Hq, d.Hkv, d.S, d.D, d.softmax_scale, d.pv_format, 0 if causal else 1, d.global_scale_mode)
     dev = ws.buf.device
-    dq = torch.empty(d.B, d.Hq, d.S, d.D, dtype=torch.bfloat16, device=dev) if write_dq else None
-    dk = torch.empty(d.B, d.Hkv, d.S, d.D, dtype=torch.bfloat16, device=dev)
-    dv = torch.empty_like(dk)
+    if out is None:
+        dq = torch.empty(d.B, d.Hq, d.S, d.D, dtype=torch.bfloat16, device=dev) if write_dq else None
+        dk = torch.empty(d.B, d.Hkv, d.S, d.D, dtype=torch.bfloat16, device=dev)
+        dv = torch.empty_like(dk)
+    else:
+        dq, dk, dv = out
+        for t, n, h in ((dq, "dq", d.Hq), (dk, "dk", d.Hkv), (dv, "dv", d.Hkv)):
+            if t is None and n == "dq" and not write_dq:
+                continue
+            _check_bhsd(t, n)
+            if tuple(t.shape) != (d.B, h, d.S, d.D):
+                raise ValueError(f"{n} must be shaped {(d.B, h, d.S, d.D)}, got {tuple(t.shape)}")
     z = _lib.Strides()
     flags = (BWD_KEEP_DQ_ACCUM if keep_dq_accum else 0) | (0 if write_dq else BWD_SKIP_DQ_OUT)
     a = _lib.AttnBwdArgs(dims, 0, z, 0, z, 0, ptr(dq) if write_dq else 0, _strides(dq) if write_dq else z, ptr(dk), _strides(dk),

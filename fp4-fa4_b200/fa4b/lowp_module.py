@@ -15,7 +15,8 @@ import torch
 
 from . import attention
 from . import _lib
-from .quantizers import prepare_nvfp4_projection_weight_dual, project_nvfp4, project_qkv_publish, rope_pair_, tk_quantize_for_gemm
+from .quantizers import (prepare_nvfp4_projection_weight_dual, project_dout_publish, project_nvfp4, project_qkv_publish, rope_pair_,
+                         tk_quantize_for_gemm)
 
 
 def pair_interleave_qk_rows(weight: torch.Tensor, n_heads: int, head_dim: int) -> torch.Tensor:
@@ -127,15 +128,23 @@ class LowpFA4AttentionBlock:
         o_rows, lse, ws = saved["o"], saved["lse"], saved["workspace"]
         # output projection: dO = dY . Wo, dWo = dY^T . O
         dy_r, dy_rp, dy_c, dy_cp, dy_g, _ = tk_quantize_for_gemm(dy_rows, return_transpose=True)
-        do_rows = project_nvfp4((dy_r, dy_rp, dy_g), self.w_o_t)                               # [M, Hq D]
+        fused = self.fused_publish
+        if fused:  # dO goes straight into the workspace as E5M2 with its row statistics
+            project_dout_publish((dy_r, dy_rp, dy_g), self.w_o_t, o_rows, lse, ws)
+        else:
+            do_rows = project_nvfp4((dy_r, dy_rp, dy_g), self.w_o_t)                           # [M, Hq D]
         dwo = project_nvfp4((dy_c, dy_cp, dy_g), saved["o_cols"])                              # [hidden, Hq D]
         # attention core, gradients written into the columns of one [M, (Hq + 2 Hkv) D] buffer
         dqkv = torch.empty(M, (Hq + 2 * Hkv) * D, dtype=torch.bfloat16, device=dy.device)
         dq = dqkv[:, :Hq * D].view(B, S, Hq, D)
         dk = dqkv[:, Hq * D:(Hq + Hkv) * D].view(B, S, Hkv, D)
         dv = dqkv[:, (Hq + Hkv) * D:].view(B, S, Hkv, D)
-        attention.attn_backward(o_rows.view(B, S, Hq, D).permute(0, 2, 1, 3), lse, do_rows.view(B, S, Hq, D).permute(0, 2, 1, 3), ws,
-                                out=(dq.permute(0, 2, 1, 3), dk.permute(0, 2, 1, 3), dv.permute(0, 2, 1, 3)))
+        grads = (dq.permute(0, 2, 1, 3), dk.permute(0, 2, 1, 3), dv.permute(0, 2, 1, 3))
+        if fused:
+            attention.attn_backward_prepared(ws, out=grads)
+        else:
+            attention.attn_backward(o_rows.view(B, S, Hq, D).permute(0, 2, 1, 3), lse, do_rows.view(B, S, Hq, D).permute(0, 2, 1, 3), ws,
+                                    out=grads)
         rope_pair_(dq, rope_cos, rope_sin, inverse=True)
         rope_pair_(dk, rope_cos, rope_sin, inverse=True)
         # QKV projection: dX = dQKV . Wqkv, dWqkv = dQKV^T . X

@@ -154,6 +154,35 @@ def project_qkv_publish(input_operand, weight_operand, rope_cos: torch.Tensor, r
             raise RuntimeError(f"fa4b_project_qkv_publish: a device-side wait gave up (site {st[1]}, block {st[2]}, detail {st[3]})")
 
 
+def project_dout_publish(grad_operand, weight_t_operand, o_rows: torch.Tensor, lse: torch.Tensor, workspace,
+                         status: torch.Tensor | None = None) -> None:
+    """Input-gradient GEMM of the output projection (``dO = dY . Wo``, the weight operand being the transposed one of
+    the dual publication) with the attention backward's publication in its epilogue: ``workspace`` receives E5M2(4 dO)
+    and the row statistics that ``attention.attn_bwd_preprocess`` would compute from a BF16 dO, which is never
+    written; the backward then runs with ``attention.attn_backward_prepared``.  ``o_rows`` bf16 ``[B*S, Hq*128]``
+    (the forward's output), ``lse`` f32 ``[B, Hq, S]``."""
+    a, a_sc, a_g = grad_operand
+    w, w_sc, w_g = weight_t_operand
+    M, K, N = a.shape[0], a.shape[1] * 2, w.shape[0]
+    if w.shape[1] * 2 != K:
+        raise ValueError(f"inner dimensions differ: gradient K={K}, weight K={w.shape[1] * 2}")
+    d = workspace.dims
+    if o_rows.dtype != torch.bfloat16 or tuple(o_rows.shape) != (M, N) or not o_rows.is_contiguous() or not o_rows.is_cuda:
+        raise ValueError(f"o_rows must be a contiguous CUDA bfloat16 {(M, N)} tensor")
+    if lse.dtype != torch.float32 or tuple(lse.shape) != (d.B, d.Hq, d.S) or not lse.is_contiguous():
+        raise ValueError(f"lse must be a contiguous float32 {(d.B, d.Hq, d.S)} tensor")
+    own = status is None
+    if own:
+        status = torch.empty(4, dtype=torch.int32, device=a.device)
+    args = _lib.ProjectNvfp4Args(ptr(a), ptr(a_sc), ptr(a_g), ptr(w), ptr(w_sc), ptr(w_g), M, N, K, 0, 0, ptr(status))
+    check(lib().fa4b_project_dout_publish(C.byref(args), C.byref(d), C.c_void_p(ptr(o_rows)), C.c_void_p(ptr(lse)),
+                                          C.c_void_p(ptr(workspace.buf)), C.c_void_p(current_stream())), "fa4b_project_dout_publish")
+    if own:
+        st = status.cpu().tolist()
+        if st[0] != 0:
+            raise RuntimeError(f"fa4b_project_dout_publish: a device-side wait gave up (site {st[1]}, block {st[2]}, detail {st[3]})")
+
+
 def rope_pair_(x: torch.Tensor, rope_cos: torch.Tensor, rope_sin: torch.Tensor, inverse: bool = False) -> torch.Tensor:
     """In-place pair-native rotary embedding of ``x [B,S,H,D]`` bf16 (any strides with a contiguous last dimension)
     with bf16 tables ``[S, D/2]``; ``inverse=True`` turns the other way (gradients).  One tensor of

@@ -262,6 +262,13 @@ typedef struct fa4b_strides {
 size_t fa4b_attn_workspace_bytes(const fa4b_attn_dims* d);
 int fa4b_project_qkv_publish(const fa4b_project_nvfp4_args* a, const fa4b_attn_dims* d, const void* rope_cos, const void* rope_sin, void* ws,
                              void* stream);
+/* The output projection's input-gradient GEMM dO = dY . Wo with the backward's publication fused into its epilogue:
+ * dO is never written as bf16; per head the epilogue writes E5M2(4 dO), dstat and lstat into `ws` -- what
+ * fa4b_project_nvfp4 + fa4b_attn_bwd_preprocess produce in two passes (fa4b_attn_bwd then runs with
+ * preprocessed = 1).  o_rows: the forward's output, bf16 [B*S, Hq*128]; lse f32 [B, Hq, S].  Replaces the epilogue of
+ * b300_project_dout_unified_lowp_nvfp4_v509_e5m2 (tk_fa4/interface.py:5824-5942; projection_fp4_epilogue.cuh:4049-4127). */
+int fa4b_project_dout_publish(const fa4b_project_nvfp4_args* a, const fa4b_attn_dims* d, const void* o_rows, const float* lse, void* ws,
+                              void* stream);
 
 /* Offsets (bytes) of the cached operands inside the workspace.  With pv_format = FA4B_PV_MXFP4_E8M0 the
  * `v_fp8` section holds V as sequence-grouped MXFP4 instead (the operand of forward_hao_direct_fp4pv,

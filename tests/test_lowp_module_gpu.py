@@ -152,6 +152,29 @@ def test_fused_qkv_publication_writes_the_same_operands_as_the_three_passes():
     assert torch.equal(o, o_ref) and torch.equal(lse, lse_ref)
 
 
+def test_fused_dout_publication_writes_the_same_statistics_as_the_two_passes():
+    from fa4b import attention
+
+    B, S, hidden, Hq, Hkv, D = 2, 256, 512, 4, 2, 128
+    x, wq, wk, wv, wo, cos, sin = _block_inputs(B, S, hidden, Hq, Hkv, D, seed=81)
+    blk = LowpFA4AttentionBlock(wq.to(DEV), wk.to(DEV), wv.to(DEV), wo.to(DEV), Hq, Hkv, D)
+    y, saved = blk.forward(x.to(DEV), cos.to(DEV), sin.to(DEV), return_intermediates=True)
+    dy = (torch.randn(B * S, hidden, generator=torch.Generator().manual_seed(82)) * 0.05).bfloat16().to(DEV)
+    g_r, g_p, _, _, g_g, _ = fa4b.tk_quantize_for_gemm(dy, return_transpose=False)
+    o_rows, lse, ws = saved["o"], saved["lse"], saved["workspace"]
+    # two passes
+    do_rows = fa4b.project_nvfp4((g_r, g_p, g_g), blk.w_o_t)
+    attention.attn_bwd_preprocess(o_rows.view(B, S, Hq, D).permute(0, 2, 1, 3), lse, do_rows.view(B, S, Hq, D).permute(0, 2, 1, 3), ws)
+    want = {k: v.clone() for k, v in ws.operands().items() if k in ("do_fp8", "dstat", "lstat")}
+    for k in want:
+        ws.operands()[k].view(torch.uint8).zero_()
+    # one pass
+    fa4b.project_dout_publish((g_r, g_p, g_g), blk.w_o_t, o_rows, lse, ws)
+    got = ws.operands()
+    for k in want:
+        assert torch.equal(got[k].view(torch.uint8), want[k].view(torch.uint8)), k
+
+
 def test_module_with_fused_publication_matches_the_unfused_module_and_the_oracle():
     B, S, hidden, Hq, Hkv, D = 1, 256, 512, 4, 2, 128
     x, wq, wk, wv, wo, cos, sin = _block_inputs(B, S, hidden, Hq, Hkv, D, seed=71)
