@@ -50,6 +50,7 @@ WORKLOADS = {
     "quant": dict(M=16384, K=4096),
     # module-level forward of one Llama-3-8B attention block (hidden 4096): projections + rotation + attention core
     "module": dict(B=2, Hq=32, Hkv=8, S=8192, D=128, hidden=4096),
+    "module_small": dict(B=1, Hq=16, Hkv=4, S=4096, D=128, hidden=2048),  # profiler captures only
 }
 WORKLOAD = dict(WORKLOADS["c2"])
 METRIC = "causal_attn_fwd_bwd_tflops"
@@ -672,7 +673,7 @@ def main():
         if rank == 0:
             run_noncausal(args, rank, world, local_rank)
         return
-    if args.workload == "module":
+    if args.workload.startswith("module"):
         if rank == 0:
             run_module(args, rank, world, local_rank)
         return
