@@ -95,7 +95,8 @@ def test_nvfp4_weight_dual_is_a_transpose_at_projection_size():
     _same(fwd[1], slab.pages(), "scale pages at 4096 x 4096")
 
 
-@pytest.mark.parametrize("M,N,K,seed", [(128, 256, 256, 1), (256, 512, 1024, 2), (384, 768, 4096, 3)])
+@pytest.mark.parametrize("M,N,K,seed", [(128, 256, 256, 1), (256, 512, 1024, 2), (384, 768, 4096, 3), (384, 1280, 768, 4),
+                                        (1152, 768, 1792, 5), (128, 4096, 256, 6)])
 def test_project_nvfp4_matches_oracle_on_represented_operands(M, N, K, seed):
     x, _ = O.make_quantizer_inputs(M, K, seed=seed)
     w, _ = O.make_quantizer_inputs(N, K, seed=seed + 100)
