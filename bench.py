@@ -437,7 +437,7 @@ def run_ours(args, rank, world, local_rank):
                      "frac": bwd_ach / bwd_peak,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
                      # profiles/attn_kernels_dram_traffic_bench_c2.md (not measured live)
-                     "traffic": 2924492288 if args.workload == "c2" else None, "ms_per_launch": bwd_ms,
+                     "traffic": 3030788608 if args.workload == "c2" else None, "ms_per_launch": bwd_ms,
                      "peak_source": (f"measured here: tcgen05 MMA-only run on all SMs, FP8 {tp8:.0f} TF/s, NVFP4 {tp4:.0f} TF/s, combined over the "
                                      f"kernel's FP4/FP8 mix ({peaks['source']} cuBLAS bf16 burst {peaks['bf16']} TF/s x2 / x4 would give "
                                      f"{2 * peaks['bf16']:.0f} / {4 * peaks['bf16']:.0f})"),
