@@ -17,6 +17,12 @@ e2e     : same metric through FA4AttentionWrapper + autograd with q, k, v, dO co
 roofline: the backward kernel against the FP4/FP8 tensor peaks measured in the same run by an
           MMA-only kernel of the library (all SMs, operands resident in shared memory)
 --impl reference times the CPU emulation (oracle/) of the same path on the host cores.
+
+--workload picks other measurements, each printing one JSON line of its own and none of them the headline:
+c3 (D = 64), c5 (S = 131072 forward through the context-parallel ring, strong scaling over the ranks), noncausal,
+quant (block quantizers), project / project_small (NVFP4 projection GEMM), module / module_small (attention block
+from hidden states to hidden states, forward and forward + backward; --no-fused for separate passes), small (profiler
+case of the headline kernels).
 """
 
 from __future__ import annotations
