@@ -6,23 +6,26 @@
 A step is one causal attention forward + backward over one batch of synthetic
 input of the Llama-3-8B attention shape (B=2, Hq=32, Hkv=8, S=8192, D=128;
 bf16 N(0,1) Q/K with RoPE theta=5e5, V ~ N(0,1), dO ~ N(0,1e-2)).  With N > 1
-(torchrun, one rank per GPU) every rank runs that shape on its own
-(batch, kv-head) units -- no collective on the data path -- so the global batch
-is 2N ("weak" scaling).  Rank 0 prints one JSON line.
+(torchrun, one rank per GPU) that ONE problem is partitioned by (batch, kv head):
+16 units, 16 / N per rank, no collective on the data path ("strong" scaling;
+value = the problem's FLOPs over the slowest rank's time).  Rank 0 prints one JSON line.
 
 value   : algorithmic TFLOP/s (6 causal matmuls: 2 forward, 4 backward), inputs resident in HBM
-e2e     : same metric through FA4AttentionWrapper + autograd with q, k, v, dO copied
-          from pinned host memory every step (the next step's upload overlaps this step's
-          kernels on a second stream) and a 16-byte checksum copied back
+e2e     : same metric through FA4AttentionWrapper + autograd with q, k, v, dO copied from pinned host
+          memory every step and O, dQ, dK, dV copied back to pinned host memory every step (uploads of
+          the next step and downloads of the previous one overlap the kernels on two more streams);
+          the returned tensors are compared with the resident-input run's
 roofline: the backward kernel against the FP4/FP8 tensor peaks measured in the same run by an
           MMA-only kernel of the library (all SMs, operands resident in shared memory)
+With N > 1 the line also carries `weak_scaling` (every rank the whole shape) and `long_context_c5`
+(S = 131072 sharded over the ranks through the context-parallel NCCL ring).
 --impl reference times the CPU emulation (oracle/) of the same path on the host cores.
 
 --workload picks other measurements, each printing one JSON line of its own and none of them the headline:
 c3 (D = 64), c5 (S = 131072 forward through the context-parallel ring, strong scaling over the ranks), noncausal,
 quant (block quantizers), project / project_small (NVFP4 projection GEMM), module / module_small (attention block
 from hidden states to hidden states, forward and forward + backward; --no-fused for separate passes), small (profiler
-case of the headline kernels).
+case of the headline kernels: one eighth of the benchmark configuration, what one of eight GPUs holds of it).
 """
 
 from __future__ import annotations
@@ -158,7 +161,7 @@ def run_reference(args, rank, world):
     value = sorted(x["value"] for x in rates)[len(rates) // 2]
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": 1e3 * sum(t_steps) / len(t_steps), "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": 1e3 * sum(t_steps) / len(t_steps), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32 emulation of fp4_e2m1 x fp8_e4m3", "data": "synthetic",
         "config": {"workload": "C2 Llama-3-8B attention B2 Hq32 Hkv8 S8192 D128 causal fwd+bwd", "timed_sample": best["sample"]},
         "cpu_baseline": dict(best, value=value),
@@ -219,8 +222,8 @@ def quantizer_rates(device, reps=10):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     out = {}
     cases = {
-        "rmsnorm_nvfp4_row_col": (lambda: fa4b.tk_fused_norm_quantize(x, gamma, 1e-6), 2 * M * K + 2 * K + 2 * (M * K // 2) + 2 * (M * K // 16) + 4 * M + 4),
-        "nvfp4_row_col": (lambda: fa4b.tk_quantize_for_gemm(x), 2 * M * K + 2 * (M * K // 2) + 2 * (M * K // 16)),
+        "rmsnorm_nvfp4_row_col": (lambda: fa4b.tk_fused_norm_quantize(x, gamma, 1e-6, encode_centric=False), 2 * M * K + 2 * K + 2 * (M * K // 2) + 2 * (M * K // 16) + 4 * M + 4),
+        "nvfp4_row_col": (lambda: fa4b.tk_quantize_for_gemm(x, encode_centric=False), 2 * M * K + 2 * (M * K // 2) + 2 * (M * K // 16)),
         # the TK quantiser's own default recipe (one multiplication per element instead of an exact division)
         "nvfp4_row_col_encode_centric": (lambda: fa4b.tk_quantize_for_gemm(x, encode_centric=True), 2 * M * K + 2 * (M * K // 2) + 2 * (M * K // 16)),
         "mxfp4": (lambda: fa4b.mxfp4_quantize_for_gemm(x), 2 * M * K + M * K // 2 + M * K // 32),
@@ -244,7 +247,7 @@ def quantizer_rates(device, reps=10):
     # Llama-3-8B QKV projection [16384, 4096] x [6144, 4096]^T on prepared NVFP4 operands (tensor-bound: TFLOP/s)
     N = 6144
     w = (torch.randn(N, K, device=device) * 0.02).bfloat16()
-    fr, sr, _, _, sg, _ = fa4b.tk_quantize_for_gemm(x, return_transpose=False)
+    fr, sr, _, _, sg, _ = fa4b.tk_quantize_for_gemm(x, return_transpose=False, encode_centric=False)
     wq = fa4b.prepare_nvfp4_projection_weight(w)
     y = torch.empty(M, N, dtype=torch.bfloat16, device=device)
     st = torch.zeros(4, dtype=torch.int32, device=device)
@@ -284,18 +287,44 @@ def init_nccl(device):
         os.close(saved)
 
 
+def dram_traffic_from_profile(kernel: str, workload: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of `kernel` at `workload`, as recorded by the last ncu
+    capture whose summary is committed under profiles/ (a line `dram_bytes_per_launch <kernel> <workload> <bytes>`);
+    (None, None) when no such record exists.  Never measured inside a benchmark run: ncu replays the kernel."""
+    import re
+
+    for path in sorted((ROOT / "profiles").glob("*.md")):
+        m = re.search(rf"^dram_bytes_per_launch\s+{re.escape(kernel)}\s+{re.escape(workload)}\s+(\d+)\s*$", path.read_text(), re.M)
+        if m:
+            return int(m.group(1)), f"profiles/{path.name}"
+    return None, None
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
 
-    from fa4b import attention, fa4_attention
+    from fa4b import attention, fa4_attention, parallel
 
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         init_nccl(device)
     B, Hq, Hkv, S, D = (WORKLOAD[k] for k in ("B", "Hq", "Hkv", "S", "D"))
-    host, (q, k, v, do) = make_inputs(20260825 + rank, device, pin=True)
-    flops_step = 6.0 * causal_matmul_flops(B, Hq, S, D)  # per rank
+    G = Hq // Hkv
+    # ONE problem of the configured shape for the whole job, partitioned by (batch, kv head): every rank generates the
+    # same global tensors from the same seed and keeps its own units; no collective on the data path
+    host_global, _ = make_inputs(20260825, "cpu", pin=False)
+    n_units = B * Hkv
+    if world > n_units:
+        raise SystemExit(f"{world} ranks for {n_units} (batch, kv-head) units")
+    mine = parallel.shard_attention_inputs(host_global[0], host_global[1], host_global[2], rank, world, host_global[3])
+    host = [t.contiguous().pin_memory() for t in (mine[0], mine[1], mine[2], mine[3])]  # q [U,G,S,D], k, v [U,1,S,D], dO
+    del host_global, mine
+    q, k, v, do = (t.to(device) for t in host)
+    U = q.shape[0]
+    flops_job = 6.0 * causal_matmul_flops(B, Hq, S, D)       # the whole job
+    flops_rank = 6.0 * causal_matmul_flops(U, G, S, D)
     dims = attention.make_dims(q, k, None, "e4m3_fp8")
     ws = attention.alloc_workspace(dims, device)
 
@@ -304,60 +333,72 @@ def run_ours(args, rank, world, local_rank):
         e.record()  # creates the underlying handle
         return e
 
-    def step(events=None):
-        e = events or [None] * 4
-        o, lse, _ = attention.attn_forward(q, k, v, workspace=ws, events=(e[0], e[1]))
-        return attention.attn_backward(o, lse, do, ws, events=(e[2], e[3]))
-
     def sync():
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
             torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    ws.check_status()
-    sync()
+    def timed_steps(step_fn, n_warm, n_steps, sampler=None):
+        for _ in range(n_warm):
+            step_fn(None)
+        sync()
+        if sampler is not None:
+            sampler.start()
+        pairs = [[ev() for _ in range(4)] for _ in range(n_steps)]
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sync()
+        t0.record()
+        for i in range(n_steps):
+            step_fn(pairs[i])
+        t1.record()
+        sync()
+        return t0.elapsed_time(t1), pairs
+
+    result = {}
+
+    def step(events=None):
+        e = events or [None] * 4
+        o, lse, _ = attention.attn_forward(q, k, v, workspace=ws, events=(e[0], e[1]))
+        result["o"] = o
+        result["grads"] = attention.attn_backward(o, lse, do, ws, events=(e[2], e[3]))
+
     sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    pairs = [[ev() for _ in range(4)] for _ in range(args.steps)]
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync()
-    t0.record()
-    for i in range(args.steps):
-        step(pairs[i])
-    t1.record()
-    sync()
-    ms_total = t0.elapsed_time(t1)
+    ms_total, pairs = timed_steps(step, max(args.warmup, 3), args.steps, sampler if rank == 0 else None)
     clocks = sampler.stop() if rank == 0 else None
     ws.check_status()
     fwd_all = sorted(p[0].elapsed_time(p[1]) for p in pairs)
     bwd_all = sorted(p[2].elapsed_time(p[3]) for p in pairs)
     fwd_ms, bwd_ms = sum(fwd_all) / args.steps, sum(bwd_all) / args.steps
+    resident = [result["o"].float().cpu()] + [t.float().cpu() for t in result["grads"]]
+    plan = attention.backward_plan(dims)
+    n_launches = 5 + 1 + 1 + 1 + 1 + (2 if plan.split_rows else 0)
 
     def pct(v):  # p10 / median / p90 of the per-step kernel times
         n = len(v)
         return {"p10": v[int(0.1 * (n - 1))], "p50": v[n // 2], "p90": v[int(round(0.9 * (n - 1)))]}
 
     extras = not args.no_extras
-    # ---- end to end through the public operator, host buffers, copies inside the timed region
+    # ---- end to end through the public operator: host buffers, copies both ways inside the timed region
     wrapper = fa4_attention.FA4AttentionWrapper(fa4_attention.resolve_fa4_config(fa4_attention.FA4()), head_dim=D)
     # Two sets of device buffers: the copy stream uploads step i + 1's inputs from pinned host memory while step i
-    # computes (the prefetch a training loop does); every step's inputs still cross PCIe inside the timed region.
+    # computes (the prefetch a training loop does), and step i's results (O, dQ, dK, dV) go back to pinned host memory
+    # on a third stream while step i + 1 computes; every step's inputs and results cross PCIe inside the timed region.
     bufs = [tuple(torch.empty_like(t) for t in (q, k, v, do)) for _ in range(2)]
-    result_host = torch.empty(4, dtype=torch.float32).pin_memory()
-    copy_stream = torch.cuda.Stream(device=device)
+    out_host = [tuple(torch.empty(t.shape, dtype=torch.bfloat16).pin_memory() for t in (q, q, k, v)) for _ in range(2)]
+    up_stream, down_stream = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
     ready = [torch.cuda.Event() for _ in range(2)]
     free = [torch.cuda.Event() for _ in range(2)]
+    computed = [torch.cuda.Event() for _ in range(2)]
+    drained = [torch.cuda.Event() for _ in range(2)]
+    keep = [None, None]  # results stay referenced until their download has been issued
 
     def upload(i):
-        with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(free[i % 2])  # the step that last used this set has finished with it
+        with torch.cuda.stream(up_stream):
+            up_stream.wait_event(free[i % 2])  # the step that last used this set has finished with it
             for dst, src in zip(bufs[i % 2], host):
                 dst.copy_(src, non_blocking=True)
-            ready[i % 2].record(copy_stream)
+            ready[i % 2].record(up_stream)
 
     def e2e_step(i, last):
         if not last:
@@ -368,42 +409,77 @@ def run_ours(args, rank, world, local_rank):
         qq, kk, vv = dq_.requires_grad_(True), dk_.requires_grad_(True), dv_.requires_grad_(True)
         out = wrapper(qq, kk, vv)
         out.backward(ddo)
-        chk = torch.stack([t.sum(dtype=torch.float32) for t in (out, qq.grad, kk.grad, vv.grad)])
-        result_host.copy_(chk, non_blocking=True)
+        res = (out.detach(), qq.grad, kk.grad, vv.grad)
+        computed[i % 2].record(main)
         free[i % 2].record(main)
+        keep[i % 2] = res
+        with torch.cuda.stream(down_stream):
+            down_stream.wait_event(computed[i % 2])
+            for dst, src in zip(out_host[i % 2], res):
+                dst.copy_(src, non_blocking=True)
+                src.record_stream(down_stream)
+            drained[i % 2].record(down_stream)
         for t in (qq, kk, vv):
             t.grad = None
             t.requires_grad_(False)
 
-    e2e_ms = float("nan")
+    e2e_ms, e2e_check = float("nan"), None
     if extras:
-        for ev_ in free:
-            ev_.record()
-        upload(0)
-        for i in range(2):
-            e2e_step(i, last=(i == 1))
+        def e2e_run(n_steps, e0=None):
+            for ev_ in free:
+                ev_.record()
+            if e0 is not None:
+                up_stream.wait_event(e0)  # the first upload starts inside the timed region
+            upload(0)
+            for i in range(n_steps):
+                e2e_step(i, last=(i == n_steps - 1))
+            torch.cuda.current_stream(device).wait_stream(down_stream)  # the last results have landed on the host
+
+        e2e_run(2)
         sync()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        copy_stream.wait_event(e0)  # the first upload starts inside the timed region
-        upload(0)
-        for i in range(args.steps):
-            e2e_step(i, last=(i == args.steps - 1))
+        e2e_run(args.steps, e0)
         e1.record()
         sync()
         e2e_ms = e0.elapsed_time(e1)
+        # what came back over PCIe against the resident-input run of the same problem (dQ sums in another order)
+        got = [t.float() for t in out_host[(args.steps - 1) % 2]]
+        import fa4b_oracle as O
+        diffs = {n: O.rel_l2(a, b) for n, a, b in zip(("o", "dq", "dk", "dv"), resident, got)}
+        e2e_check = {"rel_l2_vs_resident_run": diffs, "ok": bool(diffs["o"] == 0.0 and max(diffs.values()) < 1e-3)}
+        if not e2e_check["ok"]:
+            raise SystemExit(f"end-to-end results differ from the resident-input run: {diffs}")
+        del bufs, keep
 
-    times = torch.tensor([ms_total, e2e_ms], dtype=torch.float64, device=device)
+    # ---- secondary: every rank runs the whole configured shape on its own ("weak" scaling, global batch B * world)
+    weak_ms = None
+    if world > 1 and extras:
+        host_w, (qw, kw, vw, dow) = make_inputs(20260825 + rank, device, pin=False)
+        ws_w = attention.alloc_workspace(attention.make_dims(qw, kw, None, "e4m3_fp8"), device)
+
+        def step_w(events=None):
+            o, lse, _ = attention.attn_forward(qw, kw, vw, workspace=ws_w)
+            attention.attn_backward(o, lse, dow, ws_w)
+
+        weak_ms, _ = timed_steps(step_w, 3, args.steps)
+        ws_w.check_status()
+        del host_w, qw, kw, vw, dow, ws_w
+
+    # ---- long-context configuration (C5) on the same ranks: the only part of the path with a collective
+    c5 = run_c5_leg(device, rank, world) if (world > 1 and extras and args.workload == "c2") else None
+
+    times = torch.tensor([ms_total, e2e_ms, weak_ms if weak_ms is not None else 0.0], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms = (float(x) for x in times.cpu())
+    ms_total, e2e_ms, weak_ms_max = (float(x) for x in times.cpu())
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
     peaks = measured_peaks()
-    f1 = causal_matmul_flops(B, Hq, S, D)
+    f1 = causal_matmul_flops(U, G, S, D)  # this rank's share: what its kernels were timed on
     # backward kernel: 4 algorithmic matmuls; 1 FP4 (score recompute) + 4 FP8 executed
     # tensor denominators: measured on this GPU by the library's own MMA-only run (all SMs, operands in shared
     # memory); the cuBLAS bf16 figure x2 / x4 is kept beside them for comparison
@@ -414,10 +490,9 @@ def run_ours(args, rank, world, local_rank):
     bwd_ach = 4.0 * f1 / (bwd_ms * 1e-3) / 1e12
     fwd_peak = 2.0 * f1 / (f1 / (p4 * 1e12) + f1 / (p8 * 1e12)) / 1e12
     fwd_ach = 2.0 * f1 / (fwd_ms * 1e-3) / 1e12
-    cpu = cpu_emulation_rate()[0] if extras else None
-    quant = quantizer_rates(device) if extras else {}
-    # one-GPU side measurements: with more ranks the other ranks have already left, and the long-context route would
-    # address them through the default process group
+    cpu = cpu_emulation_rate()[0] if (extras and world == 1) else None
+    quant = quantizer_rates(device) if (extras and world == 1) else {}
+    # one-GPU side measurements (C3, one rank's C5 block calls)
     others = other_configurations(device) if (extras and args.workload == "c2" and world == 1) else {}
     for qv in quant.values():
         if "gbs" in qv:
@@ -425,39 +500,115 @@ def run_ours(args, rank, world, local_rank):
         else:
             qv["frac_of_nvfp4_peak"] = qv["tflops"] / p4
     nbytes_in = sum(t.numel() * t.element_size() for t in host)
+    nbytes_out = sum(t.numel() * t.element_size() for t in out_host[0])
+    traffic, traffic_source = dram_traffic_from_profile(f"attn_bwd_kernel<{D}>", args.workload) if world == 1 else (None, None)
+    names = {"c2": "C2 Llama-3-8B attention B2 Hq32 Hkv8 S8192 D128 causal fwd+bwd",
+             "c3": "C3 B16 Hq32 Hkv8 S4096 D64 causal fwd+bwd (not the headline configuration)",
+             "small": "PROFILER CASE (not a benchmark result): B1 Hq8 Hkv2 S8192 D128 causal fwd+bwd"}
     line = {
-        "metric": METRIC, "value": world * flops_step * args.steps / (ms_total * 1e-3) / 1e12, "unit": UNIT,
+        "metric": METRIC, "value": flops_job * args.steps / (ms_total * 1e-3) / 1e12, "unit": UNIT,
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "fp4_e2m1 (QK^T) x fp8_e4m3/e5m2 (PV, gradients), f32 accumulate", "data": "synthetic",
-        "config": {"workload": {"c2": "C2 Llama-3-8B attention B2 Hq32 Hkv8 S8192 D128 causal fwd+bwd per GPU",
-                                "c3": "C3 B16 Hq32 Hkv8 S4096 D64 causal fwd+bwd per GPU (not the headline configuration)",
-                                "small": "PROFILER CASE (not a benchmark result): B1 Hq8 Hkv2 S8192 D128 causal fwd+bwd"}[args.workload],
-                   "global_batch": B * world, "l2": "inputs (448 MiB bf16 + 470 MiB operand cache) exceed the 126 MB L2",
+        "config": {"workload": names[args.workload] + (f", ONE problem partitioned by (batch, kv head) over {world} GPUs: {U} of {n_units} units per GPU, no collective" if world > 1 else ""),
+                   "global_batch": B, "units_per_gpu": U,
+                   "l2": "inputs and operand cache of a rank exceed the 126 MB L2" if U * G * S * D * 2 > (126 << 20) else "a rank's inputs fit in L2: timed back to back, other tensors in between",
                    "flops": "6 causal matmuls = 12*B*Hq*D*S(S+1)/2", "includes": "Q/K/V quantisation and dO/statistics publication"},
         "clocks": clocks,
-        "e2e": {"value": world * flops_step * args.steps / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
-                "h2d_bytes_per_step": nbytes_in, "d2h_bytes_per_step": 16},
-        "gpu_launches": 9 * args.steps,  # per step: 2 amax + 2 quantise (Q, K), V to FP8, forward, dO publication, backward, dQ conversion
+        "e2e": {"value": flops_job * args.steps / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
+                "h2d_bytes_per_step": nbytes_in, "d2h_bytes_per_step": nbytes_out,
+                "returns": "O, dQ, dK, dV to pinned host memory every step (third stream, overlapped with the next step)",
+                "check": e2e_check},
+        "gpu_launches": n_launches * args.steps,  # per step: 2 amax + 2 quantise (Q, K), V to FP8, forward, dO publication, backward, dQ (+ dK, dV) conversion
         "roofline": {"bound": "tensor", "kernel": f"attn_bwd_kernel<{D}>", "achieved": bwd_ach, "peak": bwd_peak, "unit": UNIT,
                      "frac": bwd_ach / bwd_peak,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
-                     # profiles/attn_kernels_dram_traffic_bench_c2.md (not measured live)
-                     "traffic": 3030788608 if args.workload == "c2" else None, "ms_per_launch": bwd_ms,
+                     "traffic": traffic, "traffic_source": traffic_source, "ms_per_launch": bwd_ms,
+                     "work_list": {"chunk_query_tiles": plan.chunk, "ctas": plan.grid, "split_key_rows_per_head": plan.split_rows},
                      "peak_source": (f"measured here: tcgen05 MMA-only run on all SMs, FP8 {tp8:.0f} TF/s, NVFP4 {tp4:.0f} TF/s, combined over the "
                                      f"kernel's FP4/FP8 mix ({peaks['source']} cuBLAS bf16 burst {peaks['bf16']} TF/s x2 / x4 would give "
                                      f"{2 * peaks['bf16']:.0f} / {4 * peaks['bf16']:.0f})"),
                      "tensor_peaks": {"fp8_tflops": tp8, "nvfp4_tflops": tp4},
                      "ms_per_launch_percentiles": pct(bwd_all),
                      "forward": {"achieved": fwd_ach, "peak": fwd_peak, "frac": fwd_ach / fwd_peak, "ms_per_launch": fwd_ms,
-                                 "ms_per_launch_percentiles": pct(fwd_all)}},
+                                 "ms_per_launch_percentiles": pct(fwd_all)},
+                     "whole_step": {"achieved": flops_rank / (ms_total / args.steps * 1e-3) / 1e12,
+                                    "peak": 6.0 * f1 / (2.0 * f1 / (p4 * 1e12) + 5.0 * f1 / (p8 * 1e12)) / 1e12}},
         "cpu_baseline": cpu,
         "quantizers": quant,
         "other_configurations": others,
     }
+    line["roofline"]["whole_step"]["frac"] = line["roofline"]["whole_step"]["achieved"] / line["roofline"]["whole_step"]["peak"]
+    if world > 1 and extras:
+        line["weak_scaling"] = {"value": world * 6.0 * causal_matmul_flops(B, Hq, S, D) * args.steps / (weak_ms_max * 1e-3) / 1e12, "unit": UNIT,
+                                "ms_per_step": weak_ms_max / args.steps, "global_batch": B * world,
+                                "note": "every rank runs the whole configured shape on inputs of its own"}
+    if c5 is not None:
+        line["long_context_c5"] = c5
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def c5_inputs(device, rank, Sl, B, Hq, Hkv, D):
+    g = torch.Generator(device=device).manual_seed(20260825 + rank)
+
+    def student_t(*shape):
+        z = torch.randn(*shape, device=device, generator=g)
+        chi = sum(torch.randn(*shape[:-1], 1, device=device, generator=g) ** 2 for _ in range(3)) / 3.0
+        return (z / chi.sqrt()).bfloat16()
+
+    q, k = student_t(B, Hq, Sl, D), student_t(B, Hkv, Sl, D)
+    v = torch.randn(B, Hkv, Sl, D, device=device, generator=g).bfloat16()
+    return q, k, v, g
+
+
+def run_c5_leg(device, rank, world):
+    """The long-context configuration as an extra of the default line when the job has several ranks: ONE sequence of
+    131072 tokens sharded zig-zag over the ranks, quantised K/V shards round an NCCL ring.  Forward on the MXFP4 P.V
+    route (the configuration's route; forward only, as the reference's diagnostic route is), and forward + backward
+    on the FP8 P.V route, for which the backward exists.  Times are the slowest rank's."""
+    import torch.distributed as dist
+
+    from fa4b import context_parallel as cp
+
+    B, Hq, Hkv, S, D = (WORKLOADS["c5"][k] for k in ("B", "Hq", "Hkv", "S", "D"))
+    Sl = S // world
+    q, k, v, g = c5_inputs(device, rank, Sl, B, Hq, Hkv, D)
+    out = {"n_gpus": world, "scaling": "strong", "unit": UNIT,
+           "workload": f"C5 B1 Hq32 Hkv8 S131072 D128 causal, one sequence over {world} ranks (zig-zag), Student-t(3) Q and K",
+           "exchange": "NCCL ring (NVLS off) of quantised K/V chunks: 17.3 MB per chunk and hop forward; one all_reduce(MAX) of 40 amax words"}
+
+    def timed(fn, warm, reps):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(reps):
+            fn()
+        t1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([t0.elapsed_time(t1) / reps], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    f1 = causal_matmul_flops(B, Hq, S, D)
+    engine = cp.KernelEngine(pv_format="mxfp4_e8m0_block32")
+    ms = timed(lambda: cp.ring_attention_forward(q, k, v, engine), 2, 3)
+    out["forward_mxfp4_pv"] = {"ms_per_step": ms, "value": 2.0 * f1 / (ms * 1e-3) / 1e12}
+    del engine
+    engine8 = cp.KernelEngine()
+    do = (torch.randn(B, Hq, Sl, D, device=device, generator=g) * 0.01).bfloat16()
+
+    def fwd_bwd():
+        o, lse, state = cp.ring_attention_forward(q, k, v, engine8, return_state=True)
+        cp.ring_attention_backward(o, lse, do, state, engine8)
+
+    ms = timed(fwd_bwd, 1, 2)
+    out["forward_backward_fp8_pv"] = {"ms_per_step": ms, "value": 6.0 * f1 / (ms * 1e-3) / 1e12}
+    return out
 
 
 def run_c5(args, rank, world, local_rank):
@@ -471,18 +622,11 @@ def run_c5(args, rank, world, local_rank):
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         init_nccl(device)
     B, Hq, Hkv, S, D = (WORKLOAD[k] for k in ("B", "Hq", "Hkv", "S", "D"))
-    g = torch.Generator(device=device).manual_seed(20260825 + rank)
     Sl = S // world
-
-    def student_t(*shape):
-        z = torch.randn(*shape, device=device, generator=g)
-        chi = sum(torch.randn(*shape[:-1], 1, device=device, generator=g) ** 2 for _ in range(3)) / 3.0
-        return (z / chi.sqrt()).bfloat16()
-
-    q, k = student_t(B, Hq, Sl, D), student_t(B, Hkv, Sl, D)
-    v = torch.randn(B, Hkv, Sl, D, device=device, generator=g).bfloat16()
+    q, k, v, _ = c5_inputs(device, rank, Sl, B, Hq, Hkv, D)
     engine = cp.KernelEngine(pv_format="mxfp4_e8m0_block32")
     sampler = ClockSampler(local_rank)
     for _ in range(max(args.warmup, 3)):
@@ -561,7 +705,7 @@ def run_project(args, rank, world, local_rank):
     g = torch.Generator(device=device).manual_seed(20260825)
     x = torch.randn(M, K, device=device, generator=g).bfloat16()
     w = (torch.randn(N, K, device=device, generator=g) * 0.02).bfloat16()
-    fr, sr, _, _, sg, _ = fa4b.tk_quantize_for_gemm(x, return_transpose=False)
+    fr, sr, _, _, sg, _ = fa4b.tk_quantize_for_gemm(x, return_transpose=False, encode_centric=False)
     wq = fa4b.prepare_nvfp4_projection_weight(w)
     y = torch.empty(M, N, dtype=torch.bfloat16, device=device)
     st = torch.zeros(4, dtype=torch.int32, device=device)

@@ -2,6 +2,8 @@
 // operand cache (workspace), kernel launchers.
 #pragma once
 #include "common.cuh"
+#include <algorithm>
+
 #include "tc_sm100.cuh"
 
 namespace fa4b {
@@ -27,6 +29,10 @@ inline int check_dims(const fa4b_attn_dims& d) {
   return FA4B_OK;
 }
 
+// The operand cache in two sections.  Saved: what the forward publishes and the backward replays (Q/K codes, scale
+// pages and global scales, the E4M3 operands, the amax and status words) -- the bytes a training step keeps from
+// forward to backward.  Transient: what only lives inside one backward call (E5M2 dO, the row statistics, the FP32
+// accumulators); it may be a second buffer shared by every layer (fa4b_attn_bwd_args.scratch).
 inline fa4b_attn_ws_layout make_ws_layout(const fa4b_attn_dims& d) {
   fa4b_attn_ws_layout l{};
   const size_t nq = (size_t)d.B * d.Hq, nk = (size_t)d.B * d.Hkv, S = d.S, D = d.D;
@@ -45,20 +51,79 @@ inline fa4b_attn_ws_layout make_ws_layout(const fa4b_attn_dims& d) {
   l.v_fp8 = take(nk * S * D);
   l.k_fp8 = take(nk * S * D);  // k_codes .. k_fp8 are one contiguous range: what a sequence-sharded run sends on
   l.q_fp8 = take(nq * S * D);
+  l.amax_bits = take((nq + nk) * 4);
+  l.status = take(64);
+  l.saved_total = off;
   l.do_fp8 = take(nq * S * D);
   l.dstat = take(nq * S * 4);
   l.lstat = take(nq * S * 4);
   l.dq_accum = take(nq * S * D * 4);
-  l.amax_bits = take((nq + nk) * 4);
-  l.status = take(64);
+  l.dkv_accum = take(2 * nk * S * D * 4);  // dK sums, then dV sums
   l.total = off;
   return l;
+}
+
+// ---- work list of the backward ------------------------------------------------------------------------------
+// Per (batch, kv head): the key tiles in order, each one's L query tiles (L = n - kt under the causal mask, n
+// otherwise) cut into ceil(L / chunk) parts of nearly equal length.
+struct BwdItem {
+  int kt, qt_lo, qt_hi, parts;
+};
+// sum over L = 1..m of ceil(L / chunk)
+__host__ __device__ inline int bwd_items_upto(int m, int chunk) {
+  const int a = m / chunk, r = m % chunk;
+  return chunk * a * (a + 1) / 2 + r * (a + 1);
+}
+__host__ __device__ inline int bwd_items_per_head(int n_tiles, int chunk, bool causal) {
+  return causal ? bwd_items_upto(n_tiles, chunk) : n_tiles * ((n_tiles + chunk - 1) / chunk);
+}
+__host__ __device__ inline BwdItem bwd_item_of(int idx, int n_tiles, int chunk, bool causal) {
+  BwdItem it;
+  int L, part, first;
+  if (causal) {
+    const int total = bwd_items_upto(n_tiles, chunk);
+    int lo = 0, hi = n_tiles - 1;  // largest kt whose first item is at or before idx
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (total - bwd_items_upto(n_tiles - mid, chunk) <= idx) lo = mid; else hi = mid - 1;
+    }
+    it.kt = lo;
+    part = idx - (total - bwd_items_upto(n_tiles - lo, chunk));
+    L = n_tiles - lo;
+    first = lo;
+  } else {
+    const int per_tile = (n_tiles + chunk - 1) / chunk;
+    it.kt = idx / per_tile;
+    part = idx % per_tile;
+    L = n_tiles;
+    first = 0;
+  }
+  it.parts = (L + chunk - 1) / chunk;
+  it.qt_lo = first + (int)((long long)L * part / it.parts);
+  it.qt_hi = first + (int)((long long)L * (part + 1) / it.parts);
+  return it;
+}
+// Query tiles per work item: small enough that a launch has about eight items per SM (so that neither the last
+// head's heavy key tiles nor a launch of few heads leaves SMs idle), at least two (a shorter item is mostly set-up).
+inline int bwd_chunk(const fa4b_attn_dims& d, int n_sm) {
+  const long long n = d.S / 128;
+  const long long units = (long long)d.B * d.Hkv * (d.mask == FA4B_MASK_CAUSAL ? n * (n + 1) / 2 : n * n);
+  const long long want = (units + 8ll * n_sm - 1) / (8ll * n_sm);
+  return (int)std::min<long long>(std::max<long long>(want, 2), n);
+}
+
+// base to which the layout's transient offsets apply: the caller's separate scratch buffer, or the workspace itself
+inline uint8_t* transient_base(const fa4b_attn_bwd_args& a, const fa4b_attn_ws_layout& l) {
+  return a.scratch ? static_cast<uint8_t*>(a.scratch) - l.saved_total : static_cast<uint8_t*>(a.ws);
 }
 
 // MXFP4 P.V route: the V section holds codes [B*Hkv, D, S/2] and then the E8M0 pages [B*Hkv, S/128, 512]
 inline size_t v_mx_pages_offset(const fa4b_attn_dims& d) { return align_up((size_t)d.B * d.Hkv * d.D * d.S / 2, 1024); }
 
 inline float resolve_scale(const fa4b_attn_dims& d) { return d.softmax_scale > 0.f ? d.softmax_scale : 1.0f / sqrtf((float)d.D); }
+
+// device address of the library's built-in operand cache (fa4b_attn_fwd_static) on the current device
+int static_ws_pointer(void** out);
 
 void fill_kernel_info(fa4b_info* out);
 void fill_bwd_info(fa4b_info* out);

@@ -33,9 +33,15 @@ int fa4b_attn_ws_layout_query(const fa4b_attn_dims* d, fa4b_attn_ws_layout* out)
 }  // extern "C"
 
 extern "C" int fa4b_attn_check_status(const fa4b_attn_dims* d, const void* ws, void* stream) {
-  FA4B_REQUIRE(d && ws, FA4B_BAD_ARG, "NULL argument");
+  FA4B_REQUIRE(d != nullptr, FA4B_BAD_ARG, "NULL argument");
   if (int s = check_dims(*d)) return s;
   const fa4b_attn_ws_layout l = make_ws_layout(*d);
+  if (ws == nullptr) {  // the built-in cache of fa4b_attn_fwd_static on the current device
+    FA4B_REQUIRE(l.saved_total <= FA4B_STATIC_WS_BYTES, FA4B_BAD_SHAPE, "ws is NULL and this shape does not fit the built-in operand cache");
+    void* p = nullptr;
+    if (int s = static_ws_pointer(&p)) return s;
+    ws = p;
+  }
   uint32_t host[4] = {0, 0, 0, 0};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   FA4B_CUDA(cudaMemcpyAsync(host, static_cast<const uint8_t*>(ws) + l.status, sizeof(host), cudaMemcpyDeviceToHost, st));

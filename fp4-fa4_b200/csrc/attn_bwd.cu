@@ -77,24 +77,13 @@ struct BwdParams {
   __nv_bfloat16* dv;
   int64_t dv_sb, dv_sh, dv_ss;
   uint32_t* status;
-  uint32_t* dbg;  // development aid: event trace buffer (NULL in normal use)
+  // work list: every key tile's query range is cut into parts of at most `chunk` query tiles
+  int chunk;           // query tiles per work item
+  int items_per_head;  // work items of one (batch, kv head)
+  float* dk_accum;     // [B*Hkv, S, D] f32 each: sums of the parts of key tiles that were cut (zeroed before launch)
+  float* dv_accum;
 };
 
-#ifdef FA4B_ACCT
-// development aid: per-warp cycle accounting by category, flushed once at the end (CTA `FA4B_ACCT_CTA`)
-#define FA4B_ACCT_DECL long long acct[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long acct_t = clock64();
-#define FA4B_ACC(slot) do { const long long now__ = clock64(); acct[slot] += now__ - acct_t; acct_t = now__; } while (0)
-#define FA4B_ACCT_FLUSH(role) do { if (p.dbg && blockIdx.x == 3 && lane == 0) { for (int i__ = 0; i__ < 12; ++i__) reinterpret_cast<unsigned long long*>(p.dbg)[(role) * 16 + i__] = (unsigned long long)acct[i__]; } } while (0)
-#else
-#define FA4B_ACCT_DECL
-#define FA4B_ACC(slot)
-#define FA4B_ACCT_FLUSH(role)
-#endif
-#ifdef FA4B_TRACE
-#define FA4B_TR(role, ev) do { if (p.dbg && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && tr_n < 500) { reinterpret_cast<unsigned long long*>(p.dbg)[(role) * 512 + tr_n++] = ((unsigned long long)(ev) << 40) | ((unsigned long long)clock64() & 0xffffffffffull); } } while (0)
-#else
-#define FA4B_TR(role, ev)
-#endif
 
 __device__ __forceinline__ float ex2_approx_b(float x) {
   float y;
@@ -112,6 +101,10 @@ __device__ __forceinline__ void drain_pause() {
   const long long t0 = clock64();
   while (clock64() - t0 < 60) {
   }
+}
+// four adjacent FP32 sums in one reduction (16-byte aligned)
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 __device__ __forceinline__ float2 e4m3x2_to_f32(uint32_t two_bytes) {
   uint32_t h2;
@@ -131,23 +124,23 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
   extern __shared__ uint8_t raw[];
   BwdSmem<D>& s = *reinterpret_cast<BwdSmem<D>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
-  int tr_n = 0;
-  (void)tr_n;
 
   const int n_tiles = p.S / 128;
-  const int heads_kv = p.B * p.Hkv;
-  // key-tile-major order: low key tiles, which see the most query tiles, start first.  (kv-head-major
-  // order, meant to keep the FP32 dQ scratch rows in L2 while their 64 partial sums arrive, was 12 %
-  // slower, and so were groups of 2, 4 or 8 kv heads, key-tile-major inside a group (2-6 %): a head's heavy
-  // low key tiles then start late, and the reductions are not what bounds the kernel.)
-  const int kt = blockIdx.x / heads_kv;
-  const int bhk = blockIdx.x % heads_kv;
+  // Work item = (batch and kv head, key tile, part of the tile's query range).  kv-head-major order: the CTAs
+  // in flight then add into the FP32 dQ rows of two or three kv heads (17 MB each at S = 8192, D = 128), which
+  // stay in L2 until their last partial sum has arrived.  Inside a head the key tiles run from the one that
+  // sees the most query tiles down, and a tile's range is cut into parts of at most `chunk` query tiles so that
+  // no CTA is long against the whole launch: the last head's heavy tiles no longer leave a tail, and a launch
+  // of few (batch, kv head) units still fills the GPU.
+  const BwdItem item = bwd_item_of((int)blockIdx.x % p.items_per_head, n_tiles, p.chunk, p.causal != 0);
+  const int kt = item.kt;
+  const int bhk = blockIdx.x / p.items_per_head;
   const int b = bhk / p.Hkv, hk = bhk % p.Hkv;
   const int G = p.Hq / p.Hkv;
   const int sub_per_tile = 128 / QT;
-  const int n_sub = (p.causal ? n_tiles - kt : n_tiles) * sub_per_tile;  // query sub-tiles per head
+  const int n_sub = (item.qt_hi - item.qt_lo) * sub_per_tile;  // query sub-tiles per head
   const int n_it = G * n_sub;
-  const int sub0 = p.causal ? kt * sub_per_tile : 0;
+  const int sub0 = item.qt_lo * sub_per_tile;
   {
     // an earlier CTA of this launch gave up: leave at once, as one (the decision is CTA-uniform)
     __shared__ uint32_t skip;
@@ -243,7 +236,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       const uint64_t d_sfq0 = make_page_desc(smem_u32(s.q_sf[0]));
       constexpr uint32_t kQc16 = (QT * D / 2) >> 4, kQ816 = (QT * D) >> 4, kSf16 = (kPages * 512) >> 4, kPt16 = (128 * QT) >> 4;
       constexpr uint32_t kRow32D = (32 * D) >> 4, kRow32Q = (32 * QT) >> 4;
-      FA4B_ACCT_DECL
       bool ok = mbar_wait_warp(&s.kv_full, 0, &s.abort_flag, p.status, 120);
       if (ok) {
         tc_fence_after();
@@ -289,8 +281,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         // dO of the stage arrives through the async proxy: this thread observes its barrier itself
         if (!mbar_wait_warp(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 126, it)) return false;
         if (!mbar_wait_warp(&s.pt_ready[g], (it >> 1) & 1, &s.abort_flag, p.status, 122, it)) return false;
-        FA4B_ACC(0);  // waiting for P
-        FA4B_TR(2, 100);
         tc_fence_after();
         if (leader) {
           const uint64_t dd = d_do0 + st * kQ816, pt = d_pt0 + g * kPt16;
@@ -302,19 +292,14 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           mma_commit(&s.dp_full[g]);
         }
         __syncwarp();
-        FA4B_ACC(1);  // dV, dP
-        FA4B_TR(2, 101);
         return true;
       };
       auto ds_phase = [&](int it) -> bool {
         const uint32_t st = stage_of(it), g = it & 1;
         if (!mbar_wait_warp(&s.ds_ready[g], (it >> 1) & 1, &s.abort_flag, p.status, 123, it)) return false;
-        FA4B_ACC(0);  // waiting for dS
-        FA4B_TR(2, 110);
         tc_fence_after();
         // the group's next scores first: its threads are about to wait for them
         if (it + 2 < n_it) fire_s(it + 2);
-        FA4B_ACC(4);  // S
         const uint32_t acc = it > 0 ? 1u : 0u;
         const uint64_t q8 = d_q80 + st * kQ816, ds = d_ds0 + g * kPt16;
         if (leader) {
@@ -323,18 +308,13 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           mma_commit(&s.in_empty[st]);  // one of two arrivals: S and dK have read the stage
         }
         __syncwarp();
-        FA4B_ACC(5);  // dK
-        FA4B_TR(2, 112);
         if (it + 3 < n_it && !prep_s(it + 3)) return false;
-        FA4B_ACC(3);  // scale factors of the next S
         return true;
       };
       auto dq_phase = [&](int it) -> bool {
         const uint32_t st = stage_of(it), g = it & 1;
         if (!mbar_wait_warp(&s.ds_ready[g], (it >> 1) & 1, &s.abort_flag, p.status, 127, it)) return false;
-        FA4B_ACC(0);  // waiting for dS
         if (it > 0 && !mbar_wait_warp(&s.dq_free, (it - 1) & 1, &s.abort_flag, p.status, 124, it)) return false;
-        FA4B_ACC(6);  // waiting for the accumulator
         tc_fence_after();
         const uint64_t ds = d_ds0 + g * kPt16;
         if (leader) {
@@ -350,8 +330,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           mma_commit(&s.in_empty[st]);  // the other arrival: the last reader of the group's dS buffer
         }
         __syncwarp();
-        FA4B_ACC(2);  // dQ + commits
-        FA4B_TR(2, 113);
         return true;
       };
       // (One warp serving all streams as their events arrived left each compute group waiting behind the
@@ -367,7 +345,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       } else {
         for (int it = 0; ok && it < n_it; ++it) ok = dq_phase(it);
       }
-      FA4B_ACCT_FLUSH(stream == 0 ? 0 : 3 + stream);
       if (ok && leader) mma_commit(&s.acc_done);
       // every tensor-core operation of this CTA has finished before TMEM is freed
       if (leader) mma_commit(&s.mma_drained);
@@ -385,10 +362,8 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     const int w4 = warp & 3;
     const uint32_t lane_base = tm + ((uint32_t)(w4 * 32) << 16);
     const int r = w4 * 32 + lane;  // TMEM lane: d (D = 128) or query row (D = 64)
-    FA4B_ACCT_DECL
     for (int it = 0; it < n_it; ++it) {
       if (!mbar_wait_warp(&s.dq_full, it & 1, &s.abort_flag, p.status, 130, it)) break;
-      FA4B_ACC(0);  // waiting for dQ
       tc_fence_after();
       const int g = it / n_sub, qs = sub0 + it % n_sub;
       const int bh = b * p.Hq + hk * G + g;
@@ -400,7 +375,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       tmem_ld_wait(v1);
       tc_fence_before();
       mbar_arrive_warp(&s.dq_free);  // the next dQ may overwrite the accumulator now
-      FA4B_ACC(1);  // load + arrive
       if (D == 128) {
         // lane = d, register i = query row: one coalesced 128-byte reduction per row
 #pragma unroll
@@ -429,9 +403,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           for (int rr = 0; rr < 32; ++rr) atomicAdd(base + (size_t)(w4 * 32 + rr) * D + 32 * hh + lane, patch[rr * 33 + lane]);  // no pauses: at D = 64 the drain has no time to spare (pausing cost 23 %)
         }
       }
-      FA4B_ACC(2);  // staging + reduction issue
     }
-    if (w4 == 0) FA4B_ACCT_FLUSH(1);
   } else {
     // ------------------------------------------------------------------ compute (warps 0-15)
     constexpr int CW = QT / 2;                   // query columns per thread
@@ -442,7 +414,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     const int key = kt * 128 + row;
     const float beta = p.scale / 16.0f;
     bool ok = true;
-    FA4B_ACCT_DECL
     // P8^T of sub-tile `it`: St -> 2^min(s2 + lstat, 8) -> E4M3 -> shared memory (A operand of dV);
     // the packed bytes also stay in registers for the dS step
     // this thread's row in the swizzled [key][q] tiles: byte offset of 16-byte chunk c is
@@ -456,16 +427,9 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       const int q_first = qs * QT + half * CW;     // global query index of this thread's first column
       const bool diag = p.causal && qs * QT < kt * 128 + 128;  // sub-tile overlaps the key tile: mask needed
       // the row statistics arrive through the async proxy: observe their barrier before reading them
-      if ((warp & 7) == 0) FA4B_TR(grp, 10);
-      FA4B_ACC(0);  // loop / prologue
       if (!mbar_wait_warp(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 143, it)) return false;
-      FA4B_ACC(1);  // in_full
-      if ((warp & 7) == 0) FA4B_TR(grp, 11);
-      // the group's P buffer was last read by dV(it-2); dp_full(it-2), which this warp observed in the dS
       // step of that sub-tile, was committed by the same thread after dV(it-2)
       if (!mbar_wait_warp(&s.st_full[grp], (it >> 1) & 1, &s.abort_flag, p.status, 140, it)) return false;
-      FA4B_ACC(2);  // st_full
-      if ((warp & 7) == 0) FA4B_TR(grp, 3);
       tc_fence_after();
       const float* ls = &s.lstat[st][half * CW];
       uint8_t* dst_row = &s.pt[grp][row_base];
@@ -474,8 +438,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         uint32_t v[32];
         tmem_ld32(lane_base + C::colX + grp * QT + half * CW + c0, v);
         tmem_ld_wait(v);
-        if ((warp & 7) == 0) FA4B_TR(grp, 12);
-        // 2^(s2 + lstat) = 256 P; no clamp at 2^8: the exponent can exceed 8 only by the rounding of
         // LSE, and E4M3 rounds 2^8.0x back to 256.  The masked variant is a separate, warp-uniform
         // path so that the common one carries no compare/select per element.
         if (diag) {
@@ -505,29 +467,19 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           *reinterpret_cast<uint4*>(dst_row + ((uint32_t)(half * CW + c0 + 16 * i) ^ swz)) =
               make_uint4(pk[c0 / 4 + 4 * i], pk[c0 / 4 + 4 * i + 1], pk[c0 / 4 + 4 * i + 2], pk[c0 / 4 + 4 * i + 3]);
       }
-      FA4B_ACC(3);  // P: load + math + stores
-      if ((warp & 7) == 0) FA4B_TR(grp, 13);
       fence_async_smem();
-      if ((warp & 7) == 0) FA4B_TR(grp, 14);
       tc_fence_before();
       mbar_arrive_warp(&s.pt_ready[grp]);
-      FA4B_ACC(4);  // fence + arrive
-      if ((warp & 7) == 0) FA4B_TR(grp, 1);
       return true;
     };
     // dS8^T of sub-tile `it`: (dP16 + dstat) * P8 * scale/16 -> E4M3 -> shared memory
     const uint64_t bb = pack2(beta, beta);
     auto do_ds = [&](int it, const uint32_t (&pk)[CW / 4]) -> bool {
       const int st = it % kBwdStages;
-      if ((warp & 7) == 0) FA4B_TR(grp, 20);
-      // dK(it-2) and dQ(it-2), the last readers of the group's dS buffer, belong to the other issuer's stream:
       // the release of their input stage is committed after them
-      FA4B_ACC(0);
       if (it >= 2 && !mbar_wait_warp(&s.in_empty[(it - 2) % kBwdStages], ((it - 2) / kBwdStages) & 1, &s.abort_flag, p.status, 144, it))
         return false;
       if (!mbar_wait_warp(&s.dp_full[grp], (it >> 1) & 1, &s.abort_flag, p.status, 141, it)) return false;
-      FA4B_ACC(5);  // dp_full
-      if ((warp & 7) == 0) FA4B_TR(grp, 4);
       tc_fence_after();
       const float* dsm = &s.dstat[st][half * CW];
       uint8_t* dst_row = &s.dst[grp][row_base];
@@ -536,7 +488,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         uint32_t v[32];
         tmem_ld32(lane_base + C::colX + grp * QT + half * CW + c0, v);
         tmem_ld_wait(v);
-        if ((warp & 7) == 0) FA4B_TR(grp, 22);
         uint32_t dk4[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -553,14 +504,9 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           *reinterpret_cast<uint4*>(dst_row + ((uint32_t)(half * CW + c0 + 16 * i) ^ swz)) =
               make_uint4(dk4[4 * i], dk4[4 * i + 1], dk4[4 * i + 2], dk4[4 * i + 3]);
       }
-      FA4B_ACC(6);  // dS: load + math + stores
-      if ((warp & 7) == 0) FA4B_TR(grp, 23);
       fence_async_smem();
-      if ((warp & 7) == 0) FA4B_TR(grp, 24);
       tc_fence_before();
       mbar_arrive_warp(&s.ds_ready[grp]);
-      FA4B_ACC(7);  // fence + arrive
-      if ((warp & 7) == 0) FA4B_TR(grp, 2);
       return true;
     };
     // this group's sub-tiles; the other group works on the ones in between
@@ -569,7 +515,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       ok = do_p(it, pk);
       if (ok) ok = do_ds(it, pk);
     }
-    if ((warp & 7) == 0) FA4B_ACCT_FLUSH(2 + grp);
     // ------------------------------------------------------------------ dK, dV of this key tile
     if (ok) ok = mbar_wait_warp(&s.acc_done, 0, &s.abort_flag, p.status, 142);
     if (ok) {
@@ -580,6 +525,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       const int slice = grp * 2 + half;
       __nv_bfloat16* dkrow = p.dk + (int64_t)b * p.dk_sb + (int64_t)hk * p.dk_sh + (int64_t)key * p.dk_ss + EW * slice;
       __nv_bfloat16* dvrow = p.dv + (int64_t)b * p.dv_sb + (int64_t)hk * p.dv_sh + (int64_t)key * p.dv_ss + EW * slice;
+      const size_t acc_at = ((size_t)bhk * p.S + key) * D + EW * slice;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         __nv_bfloat16* dst = which ? dvrow : dkrow;
@@ -591,6 +537,15 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         } else {
           tmem_ld16(lane_base + col, v);
           tmem_ld_wait16(v);
+        }
+        if (item.parts > 1) {
+          // one of several parts of this key tile: the FP32 sums are rounded by a second kernel
+          float* acc = (which ? p.dv_accum : p.dk_accum) + acc_at;
+#pragma unroll
+          for (int i = 0; i < EW / 4; ++i)
+            red_add_v4(acc + 4 * i, __uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]),
+                       __uint_as_float(v[4 * i + 3]));
+          continue;
         }
         uint32_t w[EW / 2];
 #pragma unroll
@@ -609,16 +564,17 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
   if (warp == 20) tmem_dealloc(tm, 512);
 }
 
-// dQ = bf16(accumulator / 1024) through the caller's strides
+// out = bf16(accumulator / 1024) through the caller's strides, for the first `rows_per_head` rows of every head
 template <int D>
-__global__ void __launch_bounds__(256) dq_convert_kernel(const float* __restrict__ acc, int Hq, int S, int64_t n_rows, __nv_bfloat16* dq,
-                                                         int64_t sb, int64_t sh, int64_t ss) {
+__global__ void __launch_bounds__(256) accum_convert_kernel(const float* __restrict__ acc, int H, int S, int rows_per_head, int64_t n_rows,
+                                                            __nv_bfloat16* out, int64_t sb, int64_t sh, int64_t ss) {
   constexpr int kPerRow = D / 8;
   for (int64_t c = (int64_t)blockIdx.x * 256 + threadIdx.x; c < n_rows * kPerRow; c += (int64_t)gridDim.x * 256) {
-    const int64_t row = c / kPerRow;
+    const int64_t r = c / kPerRow;
     const int cb = (int)(c % kPerRow) * 8;
-    const int bh = (int)(row / S), sidx = (int)(row % S);
-    const float4 a = *reinterpret_cast<const float4*>(acc + row * D + cb), bq = *reinterpret_cast<const float4*>(acc + row * D + cb + 4);
+    const int bh = (int)(r / rows_per_head), sidx = (int)(r % rows_per_head);
+    const float* src = acc + ((int64_t)bh * S + sidx) * D + cb;
+    const float4 a = *reinterpret_cast<const float4*>(src), bq = *reinterpret_cast<const float4*>(src + 4);
     constexpr float inv = 1.0f / 1024.0f;
     const __nv_bfloat162 h0 = __floats2bfloat162_rn(a.x * inv, a.y * inv), h1 = __floats2bfloat162_rn(a.z * inv, a.w * inv);
     const __nv_bfloat162 h2 = __floats2bfloat162_rn(bq.x * inv, bq.y * inv), h3 = __floats2bfloat162_rn(bq.z * inv, bq.w * inv);
@@ -627,8 +583,18 @@ __global__ void __launch_bounds__(256) dq_convert_kernel(const float* __restrict
     o.y = *reinterpret_cast<const uint32_t*>(&h1);
     o.z = *reinterpret_cast<const uint32_t*>(&h2);
     o.w = *reinterpret_cast<const uint32_t*>(&h3);
-    *reinterpret_cast<uint4*>(dq + (int64_t)(bh / Hq) * sb + (int64_t)(bh % Hq) * sh + (int64_t)sidx * ss + cb) = o;
+    *reinterpret_cast<uint4*>(out + (int64_t)(bh / H) * sb + (int64_t)(bh % H) * sh + (int64_t)sidx * ss + cb) = o;
   }
+}
+
+template <int D>
+static int convert_rows(const float* acc, int H, int S, int rows_per_head, int64_t n_heads, void* out, const fa4b_strides& st, cudaStream_t stream) {
+  const int64_t n_rows = n_heads * rows_per_head;
+  if (n_rows == 0) return FA4B_OK;
+  const unsigned grid = (unsigned)std::min<int64_t>((n_rows * (D / 8) + 255) / 256, (int64_t)std::max(sm_count(), 1) * 16);
+  accum_convert_kernel<D><<<grid, 256, 0, stream>>>(acc, H, S, rows_per_head, n_rows, static_cast<__nv_bfloat16*>(out), st.batch, st.head, st.seq);
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
 }
 
 template <int D>
@@ -637,6 +603,7 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   const fa4b_attn_dims& d = a.dims;
   const fa4b_attn_ws_layout l = make_ws_layout(d);
   uint8_t* ws = static_cast<uint8_t*>(a.ws);
+  uint8_t* tws = transient_base(a, l);  // dO5, row statistics, FP32 accumulators
   uint8_t* kvws = a.kv_ws ? static_cast<uint8_t*>(const_cast<void*>(a.kv_ws)) : ws;  // K and V operands may be another shard's
   const uint64_t S = d.S, nq = (uint64_t)d.B * d.Hq, nk = (uint64_t)d.B * d.Hkv;
   CUtensorMap m_kc, m_k8, m_v8, m_qc, m_q8, m_do;
@@ -645,7 +612,9 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   if (int s = make_tensor_map(&m_v8, kvws + l.v_fp8, 1, D, S, nk, D, S * D, D, 128)) return s;
   if (int s = make_tensor_map(&m_qc, ws + l.q_codes, 1, D / 2, S, nq, D / 2, S * (D / 2), D / 2, C::QT)) return s;
   if (int s = make_tensor_map(&m_q8, ws + l.q_fp8, 1, D, S, nq, D, S * D, D, C::QT)) return s;
-  if (int s = make_tensor_map(&m_do, ws + l.do_fp8, 1, D, S, nq, D, S * D, D, C::QT)) return s;
+  if (int s = make_tensor_map(&m_do, tws + l.do_fp8, 1, D, S, nq, D, S * D, D, C::QT)) return s;
+  const int n_sm = sm_count();
+  FA4B_REQUIRE(n_sm > 0, FA4B_CUDA_ERROR, "could not read the multiprocessor count of the current device");
   BwdParams p{};
   p.B = d.B; p.Hq = d.Hq; p.Hkv = d.Hkv; p.S = d.S;
   p.scale = resolve_scale(d);
@@ -653,17 +622,24 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   p.q_sf = ws + l.q_scales; p.k_sf = kvws + l.k_scales;
   p.q_global = reinterpret_cast<const float*>(ws + l.q_global);
   p.k_global = reinterpret_cast<const float*>(kvws + l.k_global);
-  p.lstat = reinterpret_cast<const float*>(ws + l.lstat);
-  p.dstat = reinterpret_cast<const float*>(ws + l.dstat);
-  p.dq_accum = reinterpret_cast<float*>(ws + l.dq_accum);
+  p.lstat = reinterpret_cast<const float*>(tws + l.lstat);
+  p.dstat = reinterpret_cast<const float*>(tws + l.dstat);
+  p.dq_accum = reinterpret_cast<float*>(tws + l.dq_accum);
+  p.dk_accum = reinterpret_cast<float*>(tws + l.dkv_accum);
+  p.dv_accum = p.dk_accum + nk * S * D;
   p.dk = static_cast<__nv_bfloat16*>(a.dk); p.dk_sb = a.dk_strides.batch; p.dk_sh = a.dk_strides.head; p.dk_ss = a.dk_strides.seq;
   p.dv = static_cast<__nv_bfloat16*>(a.dv); p.dv_sb = a.dv_strides.batch; p.dv_sh = a.dv_strides.head; p.dv_ss = a.dv_strides.seq;
   p.status = reinterpret_cast<uint32_t*>(ws + l.status);
-#if defined(FA4B_TRACE) || defined(FA4B_ACCT)
-  if (const char* e = getenv("FA4B_DEBUG_PTR")) p.dbg = reinterpret_cast<uint32_t*>(strtoull(e, nullptr, 16));
-#endif
+  const int n_tiles = d.S / 128;
+  p.chunk = bwd_chunk(d, n_sm);
+  p.items_per_head = bwd_items_per_head(n_tiles, p.chunk, p.causal != 0);
+  // rows of every kv head whose key tiles are cut into parts (the tiles that see more than `chunk` query tiles):
+  // their dK and dV arrive as FP32 sums
+  const int split_rows = n_tiles > p.chunk ? (p.causal ? (n_tiles - p.chunk) * 128 : d.S) : 0;
   FA4B_CUDA(cudaMemsetAsync(p.status, 0, 16, st));
   if (!(a.flags & FA4B_BWD_KEEP_DQ_ACCUM)) FA4B_CUDA(cudaMemsetAsync(p.dq_accum, 0, nq * S * D * sizeof(float), st));
+  if (split_rows)
+    FA4B_CUDA(cudaMemset2DAsync(p.dk_accum, S * D * sizeof(float), 0, (size_t)split_rows * D * sizeof(float), 2 * nk, st));
   const int smem = (int)sizeof(BwdSmem<D>) + 1024;
   static std::mutex mu;
   static bool configured[64] = {};
@@ -671,23 +647,22 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   FA4B_CUDA(cudaGetDevice(&dev));
   {
     std::lock_guard<std::mutex> lock(mu);
-    if (dev < 64 && !configured[dev]) {
+    if (dev >= 64 || !configured[dev]) {
       FA4B_CUDA(cudaFuncSetAttribute(attn_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      configured[dev] = true;
+      if (dev < 64) configured[dev] = true;
     }
   }
-  const unsigned grid = (unsigned)(nk * (S / 128));
+  const unsigned grid = (unsigned)(nk * (uint64_t)p.items_per_head);
   if (a.ev_before) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_before), st));
   attn_bwd_kernel<D><<<grid, kBwdThreads, smem, st>>>(p, m_kc, m_k8, m_v8, m_qc, m_q8, m_do);
   FA4B_CUDA(cudaGetLastError());
   if (a.ev_after) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_after), st));
+  if (split_rows) {
+    if (int s = convert_rows<D>(p.dk_accum, d.Hkv, d.S, split_rows, (int64_t)nk, a.dk, a.dk_strides, st)) return s;
+    if (int s = convert_rows<D>(p.dv_accum, d.Hkv, d.S, split_rows, (int64_t)nk, a.dv, a.dv_strides, st)) return s;
+  }
   if (a.flags & FA4B_BWD_SKIP_DQ_OUT) return FA4B_OK;
-  const int64_t n_rows = (int64_t)nq * S;
-  const unsigned cgrid = (unsigned)std::min<int64_t>((n_rows * (D / 8) + 255) / 256, 148 * 16);
-  dq_convert_kernel<D><<<cgrid, 256, 0, st>>>(p.dq_accum, d.Hq, d.S, n_rows, static_cast<__nv_bfloat16*>(a.dq), a.dq_strides.batch,
-                                              a.dq_strides.head, a.dq_strides.seq);
-  FA4B_CUDA(cudaGetLastError());
-  return FA4B_OK;
+  return convert_rows<D>(p.dq_accum, d.Hq, d.S, d.S, (int64_t)nq, a.dq, a.dq_strides, st);
 }
 
 static int check_out(const void* ptr, const fa4b_strides& s, const char* name) {
@@ -699,6 +674,9 @@ static int check_out(const void* ptr, const fa4b_strides& s, const char* name) {
 
 int launch_attn_bwd(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   if (int s = check_dims(a.dims)) return s;
+  FA4B_REQUIRE(a.ws != nullptr && (reinterpret_cast<uintptr_t>(a.ws) & 1023) == 0, FA4B_BAD_ALIGN,
+               "workspace must be non-NULL and 1024-byte aligned");
+  FA4B_REQUIRE((reinterpret_cast<uintptr_t>(a.scratch) & 1023) == 0, FA4B_BAD_ALIGN, "scratch must be 1024-byte aligned");
   FA4B_REQUIRE(!a.kv_ws || (reinterpret_cast<uintptr_t>(a.kv_ws) & 1023) == 0, FA4B_BAD_ALIGN, "kv_ws must be 1024-byte aligned");
   FA4B_REQUIRE(a.dims.pv_format == FA4B_PV_FP8_E4M3, FA4B_UNSUPPORTED, "the MXFP4 P.V route is forward only (a diagnostic route in the reference as well)");
   if (!(a.flags & FA4B_BWD_SKIP_DQ_OUT))
@@ -719,3 +697,32 @@ void fill_bwd_info(fa4b_info* out) {
 
 }  // namespace fa4b
 
+using namespace fa4b;
+
+extern "C" int fa4b_attn_bwd_plan(const fa4b_attn_dims* d, int32_t n_sm, fa4b_bwd_plan* out) {
+  FA4B_REQUIRE(d && out, FA4B_BAD_ARG, "NULL argument");
+  if (int s = check_dims(*d)) return s;
+  if (n_sm <= 0) n_sm = sm_count();
+  FA4B_REQUIRE(n_sm > 0, FA4B_CUDA_ERROR, "could not read the multiprocessor count of the current device");
+  const int n = d->S / 128;
+  const bool causal = d->mask == FA4B_MASK_CAUSAL;
+  out->chunk = bwd_chunk(*d, n_sm);
+  out->items_per_head = bwd_items_per_head(n, out->chunk, causal);
+  out->grid = (int64_t)d->B * d->Hkv * out->items_per_head;
+  out->split_rows = n > out->chunk ? (causal ? (n - out->chunk) * 128 : d->S) : 0;
+  return FA4B_OK;
+}
+
+extern "C" int fa4b_attn_bwd_plan_item(const fa4b_attn_dims* d, int32_t n_sm, int64_t index, int32_t out[5]) {
+  fa4b_bwd_plan plan;
+  if (int s = fa4b_attn_bwd_plan(d, n_sm, &plan)) return s;
+  FA4B_REQUIRE(out != nullptr && index >= 0 && index < plan.grid, FA4B_BAD_ARG, "item index outside the launch's %lld work items",
+               (long long)plan.grid);
+  const BwdItem it = bwd_item_of((int)(index % plan.items_per_head), d->S / 128, plan.chunk, d->mask == FA4B_MASK_CAUSAL);
+  out[0] = (int32_t)(index / plan.items_per_head);
+  out[1] = it.kt;
+  out[2] = it.qt_lo;
+  out[3] = it.qt_hi;
+  out[4] = it.parts;
+  return FA4B_OK;
+}

@@ -58,19 +58,26 @@ struct FwdParams {
   int64_t o_sb, o_sh, o_ss;
   float* lse;
   uint32_t* status;
-  uint32_t* dbg;  // development aid (FA4B_TRACE builds): event trace buffer, NULL in normal use
 };
 
-#ifdef FA4B_TRACE
-#define FA4B_TR(role, ev) do { if (p.dbg && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && tr_n < 500) { reinterpret_cast<unsigned long long*>(p.dbg)[(role) * 512 + tr_n++] = ((unsigned long long)(ev) << 40) | ((unsigned long long)clock64() & 0xffffffffffull); } } while (0)
-#else
-#define FA4B_TR(role, ev)
-#endif
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// 2^e of two adjacent key columns: the exponential unit for most pairs, the FMA-pipe polynomial for the pairs
+// ex2_pair_on_fma names (`pair` is a compile-time constant wherever this is called)
+__device__ __forceinline__ void ex2_pair(uint64_t e2, int pair, float& lo, float& hi) {
+  if (ex2_pair_on_fma(pair)) {
+    unpack2(ex2_poly2(e2), lo, hi);
+  } else {
+    float a, b;
+    unpack2(e2, a, b);
+    lo = ex2_approx(a);
+    hi = ex2_approx(b);
+  }
 }
 
 template <int D, bool MX>
@@ -82,8 +89,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
   constexpr int kPages = D / 64;
   constexpr uint32_t kKvBytes = 128 * D / 2 + kPages * 512 + (MX ? D * 64 + 512 : 128 * D);
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
-  int tr_n = 0;
-  (void)tr_n;
 
   // work item: heaviest (last) query-tile pairs first; the query heads of a kv group stay adjacent
   const int n_tiles = p.S / 128;
@@ -256,17 +261,13 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
           // next block's scores as soon as this block's have been read out of TMEM
           ok = mbar_wait_warp(&s.s_free[ti], j & 1, &s.abort_flag, p.status, 23, j);
           if (!ok) break;
-          FA4B_TR(2 + ti, 100);
           tc_fence_after();
           issue_qk(jn);
-          FA4B_TR(2 + ti, 110);
         }
         ok = mbar_wait_warp(&s.p_ready[ti][j & 1], (j >> 1) & 1, &s.abort_flag, p.status, 22, j);
         if (!ok) break;
-        FA4B_TR(2 + ti, 120);
         tc_fence_after();
         issue_pv(j);
-        FA4B_TR(2 + ti, 130);
       }
       // every tensor-core operation of this CTA has finished before TMEM is freed
       if (leader) mma_commit(&s.mma_drained);
@@ -305,8 +306,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       }
       tc_fence_before();
       mbar_arrive_warp(&s.s_free[ti]);  // the next block's Q.K^T may overwrite S now
-      if ((warp & 3) == 0) FA4B_TR(ti, 2);
-      // keys of this block that lie after the query row (only in the tile's last two blocks)
       const int lim = qt * 128 + row - 64 * j;  // columns <= lim are visible
       const bool diag = p.causal && j >= 2 * qt;  // warp-uniform
       // c2 >= 0: the maximum of the scaled scores is the scaled maximum of the raw ones
@@ -356,19 +355,22 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
           if (!ok) break;
         }
       }
-      // P = 2^(x c2 - mhat + kLift): packed FMA for the exponent, MUFU for the power, packed add for the sum
+      // P = 2^(x c2 - mhat + kLift): packed FMA for the exponent, the exponential unit or (6 of 16 columns) the FMA-pipe
+      // polynomial for the power, packed add for the sum
       const uint64_t shift2 = pack2(kLift - mhat, kLift - mhat);
       uint32_t pa[8], pb[8];  // FP8 route: P as E4M3 words; MXFP4 route: pa = the block's 64 E2M1 codes
       float pf[MX ? 64 : 1];  // MXFP4 route: the un-quantised probabilities, quantised per 32 keys below
       if (diag) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float e0, e1, e2, e3;
-          unpack2(fma2(pack2u(x[4 * i], x[4 * i + 1]), c2c2, shift2), e0, e1);
-          unpack2(fma2(pack2u(x[4 * i + 2], x[4 * i + 3]), c2c2, shift2), e2, e3);
+          float p0, p1, p2, p3;
+          ex2_pair(fma2(pack2u(x[4 * i], x[4 * i + 1]), c2c2, shift2), 2 * i, p0, p1);
+          ex2_pair(fma2(pack2u(x[4 * i + 2], x[4 * i + 3]), c2c2, shift2), 2 * i + 1, p2, p3);
           // keys after the query get no weight
-          const float p0 = (4 * i > lim) ? 0.f : ex2_approx(e0), p1 = (4 * i + 1 > lim) ? 0.f : ex2_approx(e1);
-          const float p2 = (4 * i + 2 > lim) ? 0.f : ex2_approx(e2), p3 = (4 * i + 3 > lim) ? 0.f : ex2_approx(e3);
+          p0 = (4 * i > lim) ? 0.f : p0;
+          p1 = (4 * i + 1 > lim) ? 0.f : p1;
+          p2 = (4 * i + 2 > lim) ? 0.f : p2;
+          p3 = (4 * i + 3 > lim) ? 0.f : p3;
           if constexpr (MX) {
             pf[4 * i] = p0; pf[4 * i + 1] = p1; pf[4 * i + 2] = p2; pf[4 * i + 3] = p3;
           } else {
@@ -380,10 +382,9 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       } else {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float e0, e1, e2, e3;
-          unpack2(fma2(pack2u(x[4 * i], x[4 * i + 1]), c2c2, shift2), e0, e1);
-          unpack2(fma2(pack2u(x[4 * i + 2], x[4 * i + 3]), c2c2, shift2), e2, e3);
-          const float p0 = ex2_approx(e0), p1 = ex2_approx(e1), p2 = ex2_approx(e2), p3 = ex2_approx(e3);
+          float p0, p1, p2, p3;
+          ex2_pair(fma2(pack2u(x[4 * i], x[4 * i + 1]), c2c2, shift2), 2 * i, p0, p1);
+          ex2_pair(fma2(pack2u(x[4 * i + 2], x[4 * i + 3]), c2c2, shift2), 2 * i + 1, p2, p3);
           if constexpr (MX) {
             pf[4 * i] = p0; pf[4 * i + 1] = p1; pf[4 * i + 2] = p2; pf[4 * i + 3] = p3;
           } else {
@@ -439,8 +440,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
           for (int w = 0; w < 4; ++w) pa[4 * h + w] = cw[w];
         }
       }
-      if ((warp & 3) == 0) FA4B_TR(ti, 3);
-      // P and the accumulator of block j-1 must have been consumed before P is overwritten / O rescaled
       if (j > 0) {
         ok = mbar_wait_warp(&s.o_done[ti], (j - 1) & 1, &s.abort_flag, p.status, 31, j);
         if (!ok) break;
@@ -448,7 +447,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       }
       // tcgen05.ld/st are warp-collective: the accumulator rescale is taken by the whole warp
       // as soon as one of its rows has a new maximum (factor 1 for the rows that keep theirs)
-      if ((warp & 3) == 0) FA4B_TR(ti, 4);
       if (j > 0 && __any_sync(0xffffffffu, moved)) {
 #pragma unroll
         for (int c0 = 0; c0 < D; c0 += 32) {
@@ -476,7 +474,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         tc_fence_before();
         mbar_arrive_warp(&s.p_ready[ti][j & 1]);
       }
-      if ((warp & 3) == 0) FA4B_TR(ti, 5);
     }
     float lsum;
     {
@@ -543,9 +540,6 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   p.o_sb = a.o_strides.batch; p.o_sh = a.o_strides.head; p.o_ss = a.o_strides.seq;
   p.lse = a.lse;
   p.status = reinterpret_cast<uint32_t*>(ws + l.status);
-#if defined(FA4B_TRACE)
-  if (const char* e = getenv("FA4B_DEBUG_PTR")) p.dbg = reinterpret_cast<uint32_t*>(strtoull(e, nullptr, 16));
-#endif
   FA4B_CUDA(cudaMemsetAsync(p.status, 0, 64, st));
   const int smem = (int)sizeof(FwdSmem<D>) + 1024;
   static std::mutex mu;
@@ -569,7 +563,9 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
 
 int launch_attn_fwd(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   if (int s = check_dims(a.dims)) return s;
-  FA4B_REQUIRE(a.o && a.lse && a.ws, FA4B_BAD_ARG, "o, lse and ws are required");
+  FA4B_REQUIRE(a.o && a.lse, FA4B_BAD_ARG, "o and lse are required");
+  FA4B_REQUIRE(a.ws != nullptr && (reinterpret_cast<uintptr_t>(a.ws) & 1023) == 0, FA4B_BAD_ALIGN,
+               "workspace must be non-NULL and 1024-byte aligned");
   FA4B_REQUIRE(!a.kv_ws || (a.prepared && (reinterpret_cast<uintptr_t>(a.kv_ws) & 1023) == 0), FA4B_BAD_ARG,
                "kv_ws needs prepared != 0 and 1024-byte alignment");
   FA4B_REQUIRE((reinterpret_cast<uintptr_t>(a.o) & 15) == 0 && a.o_strides.batch % 8 == 0 && a.o_strides.head % 8 == 0 &&

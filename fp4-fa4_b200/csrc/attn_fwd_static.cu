@@ -23,7 +23,7 @@ static __device__ __align__(256) unsigned char g_static_ws[kStaticWsBytes + 1024
 
 // Device address of the array for the current device.  In host code `g_static_ws` is only
 // a handle for the runtime: the address a kernel may use comes from cudaGetSymbolAddress.
-static int static_ws_pointer(void** out) {
+int static_ws_pointer(void** out) {
   static std::mutex mu;
   static void* cached[64] = {};
   int dev = 0;
@@ -47,7 +47,8 @@ using namespace fa4b;
 extern "C" int fa4b_attn_fwd_static(const fa4b_attn_fwd_args* a, void* stream) {
   FA4B_REQUIRE(a != nullptr, FA4B_BAD_ARG, "args is NULL");
   if (int s = check_dims(a->dims)) return s;
-  const size_t need = make_ws_layout(a->dims).total;
+  // the forward touches the saved section of the layout only (operands, amax and status words)
+  const size_t need = make_ws_layout(a->dims).saved_total;
   FA4B_REQUIRE(need <= kStaticWsBytes, FA4B_BAD_SHAPE,
                "this shape needs an operand cache of %zu bytes; the built-in scratch holds %zu (FA4B_STATIC_WS_BYTES): "
                "use fa4b_attn_fwd with a caller-allocated workspace",

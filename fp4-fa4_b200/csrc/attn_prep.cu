@@ -289,7 +289,7 @@ int launch_attn_accumulate(float* acc, const void* part, int64_t n, void* out, c
   FA4B_REQUIRE(((reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(part) | reinterpret_cast<uintptr_t>(out)) & 15) == 0, FA4B_BAD_ALIGN,
                "fa4b_attn_accumulate: 16-byte alignment");
   const int64_t n_vec = n / 8;
-  const unsigned grid = (unsigned)std::min<int64_t>((n_vec + 255) / 256, 148 * 16);
+  const unsigned grid = (unsigned)std::min<int64_t>((n_vec + 255) / 256, (int64_t)std::max(sm_count(), 1) * 16);
   accumulate_kernel<<<grid, 256, 0, st>>>(acc, static_cast<const __nv_bfloat16*>(part), n_vec, static_cast<__nv_bfloat16*>(out));
   FA4B_CUDA(cudaGetLastError());
   return FA4B_OK;
@@ -358,7 +358,7 @@ static int prepare_impl(const fa4b_attn_prepare_args& a, cudaStream_t st) {
     v_to_mx_kernel<D><<<dim3(d.S / 128, nk), 256, 0, st>>>(v, d.S, ws + l.v_fp8, ws + l.v_fp8 + v_mx_pages_offset(d));
   } else {
     const int64_t n_chunks = (int64_t)nk * d.S * (D / 16);
-    const unsigned grid = (unsigned)std::min<int64_t>((n_chunks + 255) / 256, 148 * 16);
+    const unsigned grid = (unsigned)std::min<int64_t>((n_chunks + 255) / 256, (int64_t)std::max(sm_count(), 1) * 16);
     heads_to_fp8_kernel<D><<<grid, 256, 0, st>>>(v, d.S, n_chunks, ws + l.v_fp8);
   }
   FA4B_CUDA(cudaGetLastError());
@@ -380,7 +380,7 @@ template <int D>
 static int preprocess_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   const fa4b_attn_dims& d = a.dims;
   const fa4b_attn_ws_layout l = make_ws_layout(d);
-  uint8_t* ws = static_cast<uint8_t*>(a.ws);
+  uint8_t* ws = transient_base(a, l);
   const int64_t n_rows = (int64_t)d.B * d.Hq * d.S;
   constexpr int kRowsPerCta = 256 / (D / 8);
   bwd_preprocess_kernel<D><<<(unsigned)((n_rows + kRowsPerCta - 1) / kRowsPerCta), 256, 0, st>>>(
@@ -397,6 +397,7 @@ int launch_attn_bwd_preprocess(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   FA4B_REQUIRE(a.lse != nullptr, FA4B_BAD_ARG, "lse is NULL");
   FA4B_REQUIRE(a.ws != nullptr && (reinterpret_cast<uintptr_t>(a.ws) & 1023) == 0, FA4B_BAD_ALIGN,
                "workspace must be non-NULL and 1024-byte aligned");
+  FA4B_REQUIRE((reinterpret_cast<uintptr_t>(a.scratch) & 1023) == 0, FA4B_BAD_ALIGN, "scratch must be 1024-byte aligned");
   return a.dims.D == 128 ? preprocess_impl<128>(a, st) : preprocess_impl<64>(a, st);
 }
 

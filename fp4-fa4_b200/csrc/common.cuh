@@ -11,6 +11,7 @@
 namespace fa4b {
 
 void set_error(const char* fmt, ...);
+int sm_count();  // multiprocessors of the current device, cached per device; 0 when the query fails
 
 #define FA4B_REQUIRE(cond, status, ...)        \
   do {                                         \
@@ -123,6 +124,33 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
+
+// 2^x of a packed pair on the FMA pipe instead of the exponential unit (which delivers 16 results per clock and
+// SM and bounds the forward's softmax): n = floor(x) from a round-down add of 1.5 * 2^23 (the low significand bits of
+// the sum are n), f = x - n in [0, 1) exactly, 2^f by a degree-3 polynomial (relative minimax fit on [0, 1], error
+// <= 7.5e-5 -- an E4M3 probability keeps 3 significand bits), and n added into the exponent field.  x is clamped
+// at -125 so that the exponent field stays positive.  The idea of the reference's exponential emulation
+// (tk_fa4/fp4_fa4_fwd/stage2_ex2_alu_helpers.cuh:7-50); coefficients fitted for this build.
+constexpr float kEx2C0 = 0.9999251961708069f, kEx2C1 = 0.6958335638046265f, kEx2C2 = 0.22606715559959412f, kEx2C3 = 0.07802452147006989f;
+__device__ __forceinline__ uint64_t ex2_poly2(uint64_t x2) {
+  float a, b;
+  unpack2(x2, a, b);
+  x2 = pack2(fmaxf(a, -125.0f), fmaxf(b, -125.0f));
+  uint64_t t;
+  asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(t) : "l"(x2), "l"(pack2(12582912.0f, 12582912.0f)));
+  const uint64_t n = add2(t, pack2(-12582912.0f, -12582912.0f));   // exact
+  const uint64_t f = fma2(n, pack2(-1.0f, -1.0f), x2);            // exact
+  uint64_t p = fma2(f, pack2(kEx2C3, kEx2C3), pack2(kEx2C2, kEx2C2));
+  p = fma2(f, p, pack2(kEx2C1, kEx2C1));
+  p = fma2(f, p, pack2(kEx2C0, kEx2C0));
+  uint32_t t0, t1, p0, p1;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(t0), "=r"(t1) : "l"(t));
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(p0), "=r"(p1) : "l"(p));
+  return pack2u(p0 + (t0 << 23), p1 + (t1 << 23));
+}
+// which of a row's key columns take the polynomial: 6 of every 16 (pairs 1, 4 and 6 of each eight pairs), the share the
+// reference moves off the exponential unit (hao_direct_config.inc:47-50); the oracle applies the same rule to the same keys
+__device__ __host__ constexpr bool ex2_pair_on_fma(int pair) { return (pair & 7) == 1 || (pair & 7) == 4 || (pair & 7) == 6; }
 
 // byte offset of the scale of (row, kblock) inside its 512-byte page
 __device__ __host__ __forceinline__ uint32_t page_offset(uint32_t row, uint32_t kblock) {

@@ -274,10 +274,8 @@ extern "C" int fa4b_microgate(int kind, int K, const void* a, const void* b, con
     if (int s = make_tensor_map(&mb, b, 1, K, 128, 0, K, 0, K, 128)) return s;
   }
   const int smem = sizeof(GateSmem) + 1024;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(microgate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
-  FA4B_CUDA(attr_err);
+  // the attribute belongs to the current device's context: set on every call (cheap) so that a second GPU of the process gets it too
+  FA4B_CUDA(cudaFuncSetAttribute(microgate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   microgate_kernel<<<1, 128, smem, st>>>(kind, K, static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(b),
                                          static_cast<const uint8_t*>(sfa), static_cast<const uint8_t*>(sfb), out, status_out, ma, mb);
   FA4B_CUDA(cudaGetLastError());
@@ -293,11 +291,54 @@ extern "C" int fa4b_tensor_peak(int kind, int iters, uint32_t* status_out, void*
   FA4B_CUDA(cudaGetDevice(&dev));
   FA4B_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int smem = sizeof(PeakSmem) + 1024;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(tensor_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
-  FA4B_CUDA(attr_err);
+  // the attribute belongs to the current device's context: set on every call (cheap) so that a second GPU of the process gets it too
+  FA4B_CUDA(cudaFuncSetAttribute(tensor_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   tensor_peak_kernel<<<sms, 128, smem, st>>>(kind, iters, status_out);
   FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
+}
+
+// ---- wait self-test ------------------------------------------------------------------------------------------
+// The give-up path of the bounded waits, exercised without a fault: two warps wait, with a short cycle budget, on
+// barriers that are initialised and never armed -- nothing asynchronous is in flight, nothing is allocated in TMEM.
+// Warp 0 uses the one-thread form, warp 1 the whole-warp form and (once warp 0 has raised the CTA's abort flag, or
+// on its own budget) returns as well; both record where they gave up in `status` exactly as the attention kernels do.
+__global__ void __launch_bounds__(64, 1) wait_selftest_kernel(long long limit, uint32_t* status, uint32_t* seen) {
+  __shared__ alignas(8) uint64_t bar[2];
+  __shared__ volatile uint32_t abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  bool ok;
+  if (warp == 0) {
+    ok = lane == 0 ? mbar_wait(&bar[0], 0, &abort_flag, status, 900, 7, limit) : false;
+    if (lane == 0) seen[0] = ok ? 1u : 0u;
+  } else {
+    ok = mbar_wait_warp(&bar[1], 0, &abort_flag, status, 901, 8, 4 * limit);
+    if (lane == 0) seen[1] = ok ? 1u : 0u;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) seen[2] = abort_flag;
+}
+
+extern "C" int fa4b_wait_selftest(int64_t limit_cycles, uint32_t* status_out, void* stream) {
+  FA4B_REQUIRE(status_out != nullptr, FA4B_BAD_ARG, "wait_selftest: status_out is NULL");
+  FA4B_REQUIRE(limit_cycles > 0 && limit_cycles <= (int64_t)100 * 1000 * 1000, FA4B_BAD_ARG,
+               "wait_selftest: the cycle budget must be in 1..1e8 (this entry point is a short self-test)");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  FA4B_CUDA(cudaMemsetAsync(status_out, 0, 8 * sizeof(uint32_t), st));
+  wait_selftest_kernel<<<1, 64, 0, st>>>((long long)limit_cycles, status_out, status_out + 4);
+  FA4B_CUDA(cudaGetLastError());
+  uint32_t host[8] = {};
+  FA4B_CUDA(cudaMemcpyAsync(host, status_out, sizeof(host), cudaMemcpyDeviceToHost, st));
+  FA4B_CUDA(cudaStreamSynchronize(st));
+  // the barriers are never armed: a wait that reports success, or a missing give-up record, is the failure here
+  FA4B_REQUIRE(host[4] == 0 && host[5] == 0 && host[6] == 1, FA4B_CUDA_ERROR, "wait_selftest: a wait on an unarmed barrier did not give up");
+  FA4B_REQUIRE(host[0] == 0, FA4B_TIMEOUT, "a device-side wait ran out (site %u, block %u, detail %u)", host[1], host[2], host[3]);
   return FA4B_OK;
 }

@@ -423,10 +423,8 @@ static int project_launch(const fa4b_project_nvfp4_args* a, ProjParams p, const 
   FA4B_CUDA(cudaGetDevice(&dev));
   FA4B_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int smem = sizeof(ProjSmem);
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(project_nvfp4_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
-  FA4B_CUDA(attr_err);
+  // the attribute belongs to the current device's context: set on every call (cheap) so that a second GPU of the process gets it too
+  FA4B_CUDA(cudaFuncSetAttribute(project_nvfp4_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   p.a_sf = a->a_scales; p.w_sf = a->w_scales;
   p.a_global = a->a_global; p.w_global = a->w_global;
   p.M = (int)a->M; p.N = (int)a->N; p.K = (int)a->K;

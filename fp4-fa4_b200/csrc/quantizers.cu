@@ -4,6 +4,7 @@
 // 128x128 tile per CTA staged in shared memory so that the transposed
 // quantisation reads the input once.
 #include <cstdarg>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -17,6 +18,20 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 const char* last_error() { return g_error; }
+
+// multiprocessors of the current device (148 on a B200); 0 when the query fails
+int sm_count() {
+  static std::mutex mu;
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  if (dev >= 0 && dev < 64) cached[dev] = n;
+  return n;
+}
 
 // ------------------------------------------------------------------ amax
 __device__ __forceinline__ float warp_max(float v) {
@@ -124,7 +139,7 @@ __global__ void __launch_bounds__(256) rmsnorm_stats_kernel(const __nv_bfloat16*
 // ------------------------------------------------------------------ RMSNorm backward
 // One CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; a thread owns VEC chunks of 8 columns, keeps gamma
 // and its column sums of dy * (x * inv_rms) in registers, and leaves the sums as one FP32 row of `partials`.
-constexpr int kRmsBwdParts = 296;  // two CTAs per SM's worth of partial rows
+constexpr int kRmsBwdParts = 512;  // upper bound of the partial rows (sizes the workspace, whatever the device); a launch uses two CTAs per SM
 template <int VEC>
 __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld, const __nv_bfloat16* __restrict__ gamma,
                                                           const float* __restrict__ inv_rms, const __nv_bfloat16* __restrict__ dy, int64_t ld_dy,
@@ -511,7 +526,7 @@ int fa4b_amax(const void* x, int64_t n, float* amax, void* stream) {
   FA4B_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), st));
   const int64_t n_vec = n / 8;
   const int n_tail = (int)(n % 8);
-  const int grid = (int)std::min<int64_t>(148 * 8, std::max<int64_t>(1, (n_vec + 255) / 256));
+  const int grid = (int)std::min<int64_t>((int64_t)std::max(sm_count(), 1) * 8, std::max<int64_t>(1, (n_vec + 255) / 256));
   amax_kernel<<<grid, 256, 0, st>>>(static_cast<const uint4*>(x), n_vec, static_cast<const __nv_bfloat16*>(x) + n_vec * 8, n_tail, amax);
   FA4B_CUDA(cudaGetLastError());
   return FA4B_OK;
@@ -608,7 +623,7 @@ int fa4b_rmsnorm_bwd(const fa4b_rmsnorm_bwd_args* a, void* stream) {
   const auto* dy = static_cast<const __nv_bfloat16*>(a->dy);
   auto* dx = static_cast<__nv_bfloat16*>(a->dx);
   const int cols = (int)a->cols;
-  const int n_parts = (int)std::min<int64_t>(a->rows, kRmsBwdParts);
+  const int n_parts = (int)std::min<int64_t>(a->rows, std::min(kRmsBwdParts, 2 * std::max(sm_count(), 1)));
   const int vec = (int)((a->cols / 8 + 255) / 256);
   if (vec <= 1) rmsnorm_bwd_kernel<1><<<n_parts, 256, 0, st>>>(x, a->ld, gm, a->inv_rms, dy, a->ld_dy, a->rows, cols, dx, a->partials);
   else if (vec <= 2) rmsnorm_bwd_kernel<2><<<n_parts, 256, 0, st>>>(x, a->ld, gm, a->inv_rms, dy, a->ld_dy, a->rows, cols, dx, a->partials);
@@ -698,7 +713,7 @@ int fa4b_rope_pair(const fa4b_rope_pair_args* a, void* stream) {
   FA4B_REQUIRE(((reinterpret_cast<uintptr_t>(a->rope_cos) | reinterpret_cast<uintptr_t>(a->rope_sin)) & 7) == 0, FA4B_BAD_ALIGN,
                "rope tables must be 8-byte aligned");
   const int64_t n_chunks = a->B * a->S * a->H * (a->D / 8);
-  const unsigned grid = (unsigned)std::min<int64_t>((n_chunks + 255) / 256, 148 * 16);
+  const unsigned grid = (unsigned)std::min<int64_t>((n_chunks + 255) / 256, (int64_t)std::max(sm_count(), 1) * 16);
   fa4b::rope_pair_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(a->x), a->stride_b, a->stride_s, a->stride_h, (int)a->S, (int)a->H, (int)a->D, n_chunks,
       static_cast<const __nv_bfloat16*>(a->rope_cos), static_cast<const __nv_bfloat16*>(a->rope_sin), a->inverse);

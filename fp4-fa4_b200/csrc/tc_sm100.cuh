@@ -40,14 +40,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // The cycle counter is only consulted after a burst of polls, so a wait that is about to
 // be satisfied never pays for it.
 static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
-                                                   uint32_t where, uint32_t detail) {
+                                                   uint32_t where, uint32_t detail, long long limit) {
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitLimitCycles) break;
+    if (clock64() - t0 > limit) break;
   }
   *abort_flag = 1u;
   if (status && atomicCAS(status, 0u, 1u) == 0u) {
@@ -70,12 +70,13 @@ static __device__ __noinline__ bool mbar_wait_teardown(uint64_t* bar, uint32_t p
   }
 }
 
+// `limit`: the cycle budget of this wait (the kernels use the default; the wait self-test passes a short one)
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
-                                          uint32_t where, uint32_t detail = 0) {
+                                          uint32_t where, uint32_t detail = 0, long long limit = kWaitLimitCycles) {
 #pragma unroll 1
   for (int i = 0; i < 32; ++i)
     if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, abort_flag, status, where, detail);
+  return mbar_wait_slow(bar, parity, abort_flag, status, where, detail, limit);
 }
 
 // Whole-warp forms.  Every lane runs the same loop on a warp-wide vote, so the warp is still
@@ -99,14 +100,14 @@ __device__ __forceinline__ bool mbar_test_uniform(uint64_t* bar, uint32_t parity
   return __all_sync(0xffffffffu, ok != 0u);
 }
 static __device__ __noinline__ bool mbar_wait_warp_slow(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
-                                                        uint32_t where, uint32_t detail) {
+                                                        uint32_t where, uint32_t detail, long long limit) {
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait_uniform(bar, parity)) return true;
     // lane 0 decides for the warp: 1 = another role gave up, 2 = out of time
-    uint32_t stop = *abort_flag ? 1u : (clock64() - t0 > kWaitLimitCycles ? 2u : 0u);  // branch-free on every lane
+    uint32_t stop = *abort_flag ? 1u : (clock64() - t0 > limit ? 2u : 0u);  // branch-free on every lane
     stop = __shfl_sync(0xffffffffu, stop, 0);
     if (stop == 1u) return false;
     if (stop == 2u) break;
@@ -123,11 +124,11 @@ static __device__ __noinline__ bool mbar_wait_warp_slow(uint64_t* bar, uint32_t 
   return false;
 }
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
-                                               uint32_t where, uint32_t detail = 0) {
+                                               uint32_t where, uint32_t detail = 0, long long limit = kWaitLimitCycles) {
 #pragma unroll 1
   for (int i = 0; i < 32; ++i)
     if (mbar_try_wait_uniform(bar, parity)) return true;
-  return mbar_wait_warp_slow(bar, parity, abort_flag, status, where, detail);
+  return mbar_wait_warp_slow(bar, parity, abort_flag, status, where, detail, limit);
 }
 // every lane must have issued its own fences before the call; the barrier counts one arrival per warp
 __device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {

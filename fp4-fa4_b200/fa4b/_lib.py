@@ -7,11 +7,9 @@ caller gets an exception.  Build with ``make -C fp4-fa4_b200/csrc``.
 from __future__ import annotations
 
 import ctypes as C
-import os
 import pathlib
 
-# FA4B_LIBRARY points at an alternative build of the same ABI (e.g. an instrumented one)
-_LIB_PATH = pathlib.Path(os.environ.get("FA4B_LIBRARY") or pathlib.Path(__file__).resolve().parents[1] / "lib" / "libfa4b.so")
+_LIB_PATH = pathlib.Path(__file__).resolve().parents[1] / "lib" / "libfa4b.so"
 
 STATUS_EXC = {1: ValueError, 2: ValueError, 3: NotImplementedError, 4: RuntimeError, 5: TimeoutError, 6: ValueError}
 
@@ -69,8 +67,8 @@ class Strides(C.Structure):
 
 class WsLayout(C.Structure):
     _fields_ = [(n, C.c_size_t) for n in (
-        "q_codes", "q_scales", "q_global", "k_codes", "k_scales", "k_global", "v_fp8", "q_fp8", "k_fp8",
-        "do_fp8", "dstat", "lstat", "dq_accum", "amax_bits", "status", "total")]
+        "q_codes", "q_scales", "q_global", "k_codes", "k_scales", "k_global", "v_fp8", "k_fp8", "q_fp8",
+        "amax_bits", "status", "saved_total", "do_fp8", "dstat", "lstat", "dq_accum", "dkv_accum", "total")]
 
 
 class AttnPrepareArgs(C.Structure):
@@ -89,7 +87,12 @@ class AttnBwdArgs(C.Structure):
     _fields_ = [("dims", AttnDims), ("o", C.c_void_p), ("o_strides", Strides), ("dout", C.c_void_p), ("do_strides", Strides),
                 ("lse", C.c_void_p), ("dq", C.c_void_p), ("dq_strides", Strides), ("dk", C.c_void_p), ("dk_strides", Strides),
                 ("dv", C.c_void_p), ("dv_strides", Strides), ("ws", C.c_void_p), ("preprocessed", C.c_int32),
-                ("ev_before", C.c_void_p), ("ev_after", C.c_void_p), ("kv_ws", C.c_void_p), ("flags", C.c_int32)]
+                ("ev_before", C.c_void_p), ("ev_after", C.c_void_p), ("kv_ws", C.c_void_p), ("flags", C.c_int32),
+                ("scratch", C.c_void_p)]
+
+
+class BwdPlan(C.Structure):
+    _fields_ = [("chunk", C.c_int32), ("items_per_head", C.c_int32), ("split_rows", C.c_int32), ("grid", C.c_int64)]
 
 
 class Info(C.Structure):
@@ -102,7 +105,7 @@ EXPORTS = (
     "fa4b_status_string", "fa4b_last_error", "fa4b_query", "fa4b_amax", "fa4b_quant_nvfp4", "fa4b_quant_nvfp4_weight", "fa4b_project_nvfp4", "fa4b_project_qkv_publish", "fa4b_project_dout_publish", "fa4b_rope_pair",
     "fa4b_rmsnorm_quant_nvfp4", "fa4b_quant_mxfp4", "fa4b_dequant_nvfp4", "fa4b_dequant_mxfp4",
     "fa4b_attn_workspace_bytes", "fa4b_attn_ws_layout_query", "fa4b_attn_prepare", "fa4b_attn_fwd",
-    "fa4b_attn_fwd_static", "fa4b_attn_bwd_preprocess", "fa4b_attn_bwd", "fa4b_attn_check_status", "fa4b_attn_merge", "fa4b_attn_accumulate", "fa4b_rmsnorm_bwd", "fa4b_rmsnorm_bwd_workspace_bytes", "fa4b_microgate", "fa4b_tensor_peak",
+    "fa4b_attn_fwd_static", "fa4b_attn_bwd_preprocess", "fa4b_attn_bwd", "fa4b_attn_bwd_plan", "fa4b_attn_bwd_plan_item", "fa4b_attn_check_status", "fa4b_attn_merge", "fa4b_attn_accumulate", "fa4b_rmsnorm_bwd", "fa4b_rmsnorm_bwd_workspace_bytes", "fa4b_microgate", "fa4b_tensor_peak", "fa4b_wait_selftest",
 )
 
 _lib = None

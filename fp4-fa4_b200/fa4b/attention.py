@@ -34,14 +34,34 @@ def _check_bhsd(t: torch.Tensor, name: str) -> None:
 
 @dataclass
 class Workspace:
-    """Operand cache of one attention call (see fa4b_attn_ws_layout)."""
+    """Operand cache of one attention call (see fa4b_attn_ws_layout).
+
+    ``buf`` holds the saved section (what the forward publishes and the backward replays) and, unless ``scratch``
+    is given, the transient section behind it (E5M2 dO, row statistics, FP32 accumulators of one backward call).
+    ``scratch`` is that transient section as a buffer of its own, which many workspaces may share."""
 
     dims: _lib.AttnDims
     layout: _lib.WsLayout
     buf: torch.Tensor
+    scratch: torch.Tensor | None = None
 
     def _view(self, off: int, nbytes: int) -> torch.Tensor:
+        if off >= self.layout.saved_total and self.scratch is not None:
+            off -= self.layout.saved_total
+            return self.scratch[off:off + nbytes]
+        if off + nbytes > self.buf.numel():
+            raise RuntimeError("this workspace holds the saved section only; the transient section needs a scratch buffer")
         return self.buf[off:off + nbytes]
+
+    def saved(self) -> torch.Tensor:
+        """The bytes a training step keeps from forward to backward (a view)."""
+        return self.buf[:self.layout.saved_total]
+
+    def with_scratch(self, scratch: torch.Tensor) -> "Workspace":
+        need = self.layout.total - self.layout.saved_total
+        if scratch.numel() < need or scratch.data_ptr() % 1024:
+            raise ValueError(f"scratch must hold {need} bytes and be 1024-byte aligned")
+        return Workspace(self.dims, self.layout, self.buf, scratch[:need])
 
     def operands(self):
         d = self.dims
@@ -98,12 +118,56 @@ def make_dims(q: torch.Tensor, k: torch.Tensor, softmax_scale: float | None, pv_
                          0 if causal else 1, GLOBAL_SCALE_MODES[global_scale])
 
 
-def alloc_workspace(dims: _lib.AttnDims, device) -> Workspace:
+def ws_layout(dims: _lib.AttnDims) -> _lib.WsLayout:
     layout = _lib.WsLayout()
     check(lib().fa4b_attn_ws_layout_query(C.byref(dims), C.byref(layout)), "fa4b_attn_ws_layout_query")
-    buf = torch.empty(layout.total + 1024, dtype=torch.uint8, device=device)
+    return layout
+
+
+def _aligned_bytes(n: int, device) -> torch.Tensor:
+    buf = torch.empty(n + 1024, dtype=torch.uint8, device=device)
     shift = (-buf.data_ptr()) % 1024
-    return Workspace(dims, layout, buf[shift:shift + layout.total])
+    return buf[shift:shift + n]
+
+
+def alloc_workspace(dims: _lib.AttnDims, device, saved_only: bool = False) -> Workspace:
+    """A workspace for ``dims``.  ``saved_only``: just the section the backward replays (Q/K codes, scale pages, E4M3
+    operands); the backward then needs a scratch buffer (:func:`alloc_scratch`, :meth:`Workspace.with_scratch`)."""
+    layout = ws_layout(dims)
+    return Workspace(dims, layout, _aligned_bytes(layout.saved_total if saved_only else layout.total, device))
+
+
+def alloc_scratch(dims: _lib.AttnDims, device) -> torch.Tensor:
+    """The transient section of a backward call for ``dims`` as a buffer of its own."""
+    layout = ws_layout(dims)
+    return _aligned_bytes(layout.total - layout.saved_total, device)
+
+
+_scratch_cache: dict = {}
+
+
+def shared_scratch(dims: _lib.AttnDims, device) -> torch.Tensor:
+    """One grow-only transient buffer per device, shared by every layer's backward (backward calls on one device are
+    serial on the stream they share)."""
+    layout = ws_layout(dims)
+    need = layout.total - layout.saved_total
+    key = torch.device(device)
+    if key.index is None:
+        key = torch.device("cuda", torch.cuda.current_device())
+    have = _scratch_cache.get(key)
+    if have is None or have.numel() < need:
+        have = _aligned_bytes(need, key)
+        _scratch_cache[key] = have
+    return have[:need]
+
+
+def backward_plan(dims: _lib.AttnDims, n_sm: int = 0) -> _lib.BwdPlan:
+    """The work list :func:`attn_backward` launches for ``dims`` (host-only query; ``n_sm = 0``: the current device):
+    ``chunk`` query tiles per work item, ``items_per_head``, ``grid`` and ``split_rows`` -- the leading key rows of
+    every kv head whose dK / dV are summed in FP32 over several CTAs."""
+    plan = _lib.BwdPlan()
+    check(lib().fa4b_attn_bwd_plan(C.byref(dims), C.c_int32(n_sm), C.byref(plan)), "fa4b_attn_bwd_plan")
+    return plan
 
 
 def _ev(e) -> int:
@@ -203,7 +267,7 @@ def attn_backward(o, lse, dout, ws: Workspace, preprocessed: bool = False, event
             if tuple(t.shape) != (d.B, h, d.S, d.D):
                 raise ValueError(f"{n} must be shaped {(d.B, h, d.S, d.D)}, got {tuple(t.shape)}")
     a = _lib.AttnBwdArgs(d, ptr(o), _strides(o), ptr(dout), _strides(dout), ptr(lse), ptr(dq), _strides(dq), ptr(dk), _strides(dk),
-                         ptr(dv), _strides(dv), ptr(ws.buf), int(preprocessed), _ev(events[0]), _ev(events[1]))
+                         ptr(dv), _strides(dv), ptr(ws.buf), int(preprocessed), _ev(events[0]), _ev(events[1]), 0, 0, ptr(ws.scratch))
     check(lib().fa4b_attn_bwd(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_bwd")
     return dq, dk, dv
 
@@ -236,7 +300,7 @@ def attn_backward_prepared(ws: Workspace, kv_ws: Workspace | None = None, causal
     z = _lib.Strides()
     flags = (BWD_KEEP_DQ_ACCUM if keep_dq_accum else 0) | (0 if write_dq else BWD_SKIP_DQ_OUT)
     a = _lib.AttnBwdArgs(dims, 0, z, 0, z, 0, ptr(dq) if write_dq else 0, _strides(dq) if write_dq else z, ptr(dk), _strides(dk),
-                         ptr(dv), _strides(dv), ptr(ws.buf), 1, 0, 0, ptr(kv_ws.buf) if kv_ws is not None else 0, flags)
+                         ptr(dv), _strides(dv), ptr(ws.buf), 1, 0, 0, ptr(kv_ws.buf) if kv_ws is not None else 0, flags, ptr(ws.scratch))
     check(lib().fa4b_attn_bwd(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_bwd")
     return dq, dk, dv
 
@@ -253,7 +317,7 @@ def attn_accumulate(acc: torch.Tensor, part: torch.Tensor, out: torch.Tensor | N
 def attn_bwd_preprocess(o, lse, dout, ws: Workspace):
     d = ws.dims
     a = _lib.AttnBwdArgs(d, ptr(o), _strides(o), ptr(dout), _strides(dout), ptr(lse), 0, _lib.Strides(), 0, _lib.Strides(), 0,
-                         _lib.Strides(), ptr(ws.buf), 0, 0, 0)
+                         _lib.Strides(), ptr(ws.buf), 0, 0, 0, 0, 0, ptr(ws.scratch))
     check(lib().fa4b_attn_bwd_preprocess(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_bwd_preprocess")
     ops = ws.operands()
     return ops["do_fp8"], ops["dstat"], ops["lstat"]

@@ -77,14 +77,21 @@ _PV_CODE = attention.PV_FORMATS
 @torch.library.custom_op("fa4b::attn_fwd", mutates_args=())
 def _attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, pv_code: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     pv = _EXACT_FP8_PV if pv_code == 0 else _EXACT_MXFP4_PV
-    o, lse, ws = attention.attn_forward(q, k, v, softmax_scale=scale if scale > 0 else None, pv_format=pv)
+    # only the saved section of the operand cache is allocated here and kept for the backward: the quantised
+    # operands, as the reference saves them (release/routes.json:443-447); the backward's dO / statistics /
+    # FP32 accumulators live in one scratch buffer per device that every layer shares
+    dims = attention.make_dims(q, k, scale if scale > 0 else None, pv)
+    ws = attention.alloc_workspace(dims, q.device, saved_only=True)
+    o, lse, ws = attention.attn_forward(q, k, v, softmax_scale=scale if scale > 0 else None, pv_format=pv, workspace=ws)
     return o, lse, ws.buf
 
 
 @_attn_fwd_op.register_fake
 def _(q, k, v, scale, pv_code):
     B, Hq, S, D = q.shape
-    return (q.new_empty(B, Hq, S, D), q.new_empty(B, Hq, S, dtype=torch.float32), q.new_empty(0, dtype=torch.uint8))
+    dims = attention._lib.AttnDims(B, Hq, k.shape[1], S, D, scale if scale > 0 else 0.0, pv_code)
+    saved = attention.ws_layout(dims).saved_total  # host-only query: the real op returns exactly these bytes
+    return (q.new_empty(B, Hq, S, D), q.new_empty(B, Hq, S, dtype=torch.float32), q.new_empty(saved, dtype=torch.uint8))
 
 
 @torch.library.custom_op("fa4b::attn_bwd", mutates_args=("ws",))
@@ -92,11 +99,12 @@ def _attn_bwd_op(o: torch.Tensor, lse: torch.Tensor, dout: torch.Tensor, ws: tor
                  pv_code: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     B, Hq, S, D = o.shape
     dims = attention._lib.AttnDims(B, Hq, Hkv, S, D, scale if scale > 0 else 0.0, pv_code)
-    layout = attention._lib.WsLayout()
-    attention.check(attention.lib().fa4b_attn_ws_layout_query(attention.C.byref(dims), attention.C.byref(layout)), "ws layout")
-    if ws.numel() != layout.total or ws.data_ptr() % 1024:
+    layout = attention.ws_layout(dims)
+    if ws.numel() != layout.saved_total or ws.data_ptr() % 1024:
         raise RuntimeError("the saved operand cache does not match this call's shape")
-    return attention.attn_backward(o, lse, dout, attention.Workspace(dims, layout, ws))
+    work = attention.Workspace(dims, layout, ws).with_scratch(attention.shared_scratch(dims, o.device))
+    grads = attention.attn_backward(o, lse, dout, work)
+    return grads
 
 
 @_attn_bwd_op.register_fake

@@ -5,8 +5,11 @@ Mirrors the forward of ``ExactLowpFA4Attention.forward(x, freqs_cis, None)``
 NVFP4 projection route (tk_fa4/interface.py:5238, b300_project_qkv_gqa_d128_unified_lowp_nvfp4): the activation
 rows are quantised to NVFP4 (1x16 blocks), the stacked Q/K/V weight and the output weight to NVFP4 with one scale
 per 16x16 tile, both projections run as block-scaled FP4 GEMMs, Q and K rotate in the pair-native order in packed
-BF16, and the attention core is the NVFP4 Q.K^T / FP8 P.V kernel.  The reference fuses rotation, quantisation and
-publication into the projection epilogues; here they are separate launches on the same stream.
+BF16, and the attention core is the NVFP4 Q.K^T / FP8 P.V kernel.  With ``fused_publish=True`` rotation, Q/K/V
+quantisation and publication run in the QKV projection's epilogue and the dO / statistics publication in the output
+projection's input-gradient epilogue, as in the reference; otherwise they are separate launches on the same stream.
+The projections write their wait status into one status tensor of the block and never synchronise the host;
+``check_status()`` reads it (and a workspace's) on demand.
 """
 
 from __future__ import annotations
@@ -62,6 +65,23 @@ class LowpFA4AttentionBlock:
         # quantised once; a cached result is valid only until the next optimizer update of the weight
         self.w_qkv, self.w_qkv_t = prepare_nvfp4_projection_weight_dual(torch.cat((wq, wk, wv), dim=0).contiguous())
         self.w_o, self.w_o_t = prepare_nvfp4_projection_weight_dual(wo.contiguous())
+        self._status = None  # [6, 4] u32 on the block's device: one slot per projection GEMM of a step
+
+    def _slot(self, device, i: int) -> torch.Tensor:
+        if self._status is None or self._status.device != torch.device(device):
+            self._status = torch.zeros(6, 4, dtype=torch.int32, device=device)
+        return self._status[i]
+
+    def check_status(self, workspace=None) -> None:
+        """One host synchronisation: raises if a device-side wait of any projection since the last check (or of the
+        attention kernels that last used ``workspace``) gave up."""
+        if self._status is not None:
+            st = self._status.cpu()
+            bad = [(i, st[i].tolist()) for i in range(st.shape[0]) if int(st[i, 0]) != 0]
+            if bad:
+                raise TimeoutError(f"projection GEMM wait status (slot, [flag, site, block, detail]): {bad}")
+        if workspace is not None:
+            workspace.check_status()
 
     def forward(self, x: torch.Tensor, rope_cos: torch.Tensor, rope_sin: torch.Tensor, attention_masks=None,
                 softmax_scale: float | None = None, return_intermediates: bool = False):
@@ -79,7 +99,7 @@ class LowpFA4AttentionBlock:
         if not rows.is_contiguous():
             rows = rows.contiguous()
         # with a backward to follow, the token-major (column) operand of the weight-gradient GEMM comes from the same pass
-        a_codes, a_pages, x_c, x_cp, a_g, _ = tk_quantize_for_gemm(rows, return_transpose=return_intermediates)
+        a_codes, a_pages, x_c, x_cp, a_g, _ = tk_quantize_for_gemm(rows, return_transpose=return_intermediates, encode_centric=False)
         x_cols = (x_c, x_cp, a_g) if return_intermediates else None
         o_rows = torch.empty(B * S, Hq * D, dtype=torch.bfloat16, device=x.device)
         o_view = o_rows.view(B, S, Hq, D).permute(0, 2, 1, 3)
@@ -87,11 +107,11 @@ class LowpFA4AttentionBlock:
             dims = _lib.AttnDims(B, Hq, Hkv, S, D, float(softmax_scale) if softmax_scale else 0.0, attention.PV_FORMATS["e4m3_fp8"], 0,
                                  attention.GLOBAL_SCALE_MODES["one"])
             ws = attention.alloc_workspace(dims, x.device)
-            project_qkv_publish((a_codes, a_pages, a_g), self.w_qkv, rope_cos, rope_sin, ws)
+            project_qkv_publish((a_codes, a_pages, a_g), self.w_qkv, rope_cos, rope_sin, ws, status=self._slot(x.device, 0))
             _, lse = attention.attn_forward_prepared(ws, out=o_view)
             qkv = None
             return self._finish(o_rows, lse, ws, qkv, rows, x_cols, B, S, return_intermediates)
-        qkv = project_nvfp4((a_codes, a_pages, a_g), self.w_qkv)                 # [B*S, (Hq + 2 Hkv) D]
+        qkv = project_nvfp4((a_codes, a_pages, a_g), self.w_qkv, status=self._slot(x.device, 0))                 # [B*S, (Hq + 2 Hkv) D]
         q = qkv[:, :Hq * D].view(B, S, Hq, D)
         k = qkv[:, Hq * D:(Hq + Hkv) * D].view(B, S, Hkv, D)
         v = qkv[:, (Hq + Hkv) * D:].view(B, S, Hkv, D)
@@ -102,8 +122,8 @@ class LowpFA4AttentionBlock:
         return self._finish(o_rows, lse, ws, qkv, rows, x_cols, B, S, return_intermediates)
 
     def _finish(self, o_rows, lse, ws, qkv, rows, x_cols, B, S, return_intermediates):
-        o_codes, o_pages, o_c, o_cp, o_g, _ = tk_quantize_for_gemm(o_rows, return_transpose=return_intermediates)
-        y = project_nvfp4((o_codes, o_pages, o_g), self.w_o).view(B, S, self.hidden)
+        o_codes, o_pages, o_c, o_cp, o_g, _ = tk_quantize_for_gemm(o_rows, return_transpose=return_intermediates, encode_centric=False)
+        y = project_nvfp4((o_codes, o_pages, o_g), self.w_o, status=self._slot(o_rows.device, 1)).view(B, S, self.hidden)
         if return_intermediates:
             return y, {"qkv": qkv, "o": o_rows, "lse": lse, "workspace": ws, "x_rows": rows, "x_cols": x_cols, "o_cols": (o_c, o_cp, o_g)}
         return y
@@ -127,13 +147,13 @@ class LowpFA4AttentionBlock:
             dy_rows = dy_rows.contiguous()
         o_rows, lse, ws = saved["o"], saved["lse"], saved["workspace"]
         # output projection: dO = dY . Wo, dWo = dY^T . O
-        dy_r, dy_rp, dy_c, dy_cp, dy_g, _ = tk_quantize_for_gemm(dy_rows, return_transpose=True)
+        dy_r, dy_rp, dy_c, dy_cp, dy_g, _ = tk_quantize_for_gemm(dy_rows, return_transpose=True, encode_centric=False)
         fused = self.fused_publish
         if fused:  # dO goes straight into the workspace as E5M2 with its row statistics
-            project_dout_publish((dy_r, dy_rp, dy_g), self.w_o_t, o_rows, lse, ws)
+            project_dout_publish((dy_r, dy_rp, dy_g), self.w_o_t, o_rows, lse, ws, status=self._slot(dy.device, 2))
         else:
-            do_rows = project_nvfp4((dy_r, dy_rp, dy_g), self.w_o_t)                           # [M, Hq D]
-        dwo = project_nvfp4((dy_c, dy_cp, dy_g), saved["o_cols"])                              # [hidden, Hq D]
+            do_rows = project_nvfp4((dy_r, dy_rp, dy_g), self.w_o_t, status=self._slot(dy.device, 2))                           # [M, Hq D]
+        dwo = project_nvfp4((dy_c, dy_cp, dy_g), saved["o_cols"], status=self._slot(dy.device, 3))                              # [hidden, Hq D]
         # attention core, gradients written into the columns of one [M, (Hq + 2 Hkv) D] buffer
         dqkv = torch.empty(M, (Hq + 2 * Hkv) * D, dtype=torch.bfloat16, device=dy.device)
         dq = dqkv[:, :Hq * D].view(B, S, Hq, D)
@@ -148,9 +168,9 @@ class LowpFA4AttentionBlock:
         rope_pair_(dq, rope_cos, rope_sin, inverse=True)
         rope_pair_(dk, rope_cos, rope_sin, inverse=True)
         # QKV projection: dX = dQKV . Wqkv, dWqkv = dQKV^T . X
-        g_r, g_rp, g_c, g_cp, g_g, _ = tk_quantize_for_gemm(dqkv, return_transpose=True)
-        dx = project_nvfp4((g_r, g_rp, g_g), self.w_qkv_t).view(B, S, self.hidden)
-        dwqkv = project_nvfp4((g_c, g_cp, g_g), saved["x_cols"])                               # [(Hq + 2 Hkv) D, hidden]
+        g_r, g_rp, g_c, g_cp, g_g, _ = tk_quantize_for_gemm(dqkv, return_transpose=True, encode_centric=False)
+        dx = project_nvfp4((g_r, g_rp, g_g), self.w_qkv_t, status=self._slot(dy.device, 4)).view(B, S, self.hidden)
+        dwqkv = project_nvfp4((g_c, g_cp, g_g), saved["x_cols"], status=self._slot(dy.device, 5))                               # [(Hq + 2 Hkv) D, hidden]
         return dx, dwqkv[:Hq * D], dwqkv[Hq * D:(Hq + Hkv) * D], dwqkv[(Hq + Hkv) * D:], dwo
 
 

@@ -42,3 +42,14 @@ def tensor_peak(kind: str, iters: int = 8192, reps: int = 3) -> float:
             raise TimeoutError(f"tensor_peak {kind}: device wait ran out")
         best = min(best, e0.elapsed_time(e1))
     return flops / (best * 1e-3) / 1e12
+
+
+def wait_selftest(limit_cycles: int = 1_000_000) -> torch.Tensor:
+    """Make a bounded device-side wait run out on purpose (an unarmed barrier, nothing in flight) and return the
+    8 status words; raises unless the library reports exactly FA4B_TIMEOUT."""
+    status = torch.zeros(8, dtype=torch.int32, device="cuda")
+    rc = lib().fa4b_wait_selftest(C.c_int64(limit_cycles), C.c_void_p(ptr(status)), C.c_void_p(current_stream()))
+    if rc != 5:
+        check(rc, "fa4b_wait_selftest")
+        raise RuntimeError("fa4b_wait_selftest returned FA4B_OK: the wait did not run out")
+    return status

@@ -46,13 +46,16 @@ def _alloc_outputs(rows, cols, transpose, dev, block=16):
     return fp4_row, sc_row, fp4_col, sc_col
 
 
-def tk_quantize_for_gemm(input: torch.Tensor, return_transpose: bool = True, amax_in: torch.Tensor | None = None,
-                         encode_centric: bool = False):
+def tk_quantize_for_gemm(input: torch.Tensor, return_transpose: bool = True, encode_centric: bool = True, *,
+                         amax_in: torch.Tensor | None = None):
     """NVFP4 of ``input [M,K]``: returns ``(fp4_row [M,K/2], sc_row [M/128,K/64,512],
     fp4_col [K,M/2] | None, sc_col [K/128,M/64,512] | None, sg [1], amax [1])``.
-    ``sg = amax/2688``; scale bytes are E4M3.  ``encode_centric=True`` selects the TK quantiser's own default recipe
-    (the rounded quantity is the block multiplier, the stored scale its reciprocal); the default here is the
-    decode-centric arithmetic of the reference's Python oracle."""
+    ``sg = amax/2688``; scale bytes are E4M3.  Positional arguments and defaults are the reference binding's
+    (``tk_quantize_for_gemm(input, return_transpose, encode_centric=true)``,
+    TK_quantisation/nvfp4_v6/tk_quantize.cu:3170-3172): ``encode_centric=True`` rounds the block multiplier and
+    stores the E4M3 of its reciprocal; ``False`` is the decode-centric arithmetic of the reference's Python oracle
+    (``fake_quantize_nvfp4``), which the attention block's projections use.  ``amax_in`` (keyword only, not in the
+    reference) supplies the tensor amax instead of a statistics pass."""
     _require_matrix(input, "input")
     rows, cols = input.shape
     fp4_row, sc_row, fp4_col, sc_col = _alloc_outputs(rows, cols, return_transpose, input.device)
@@ -198,8 +201,8 @@ def rope_pair_(x: torch.Tensor, rope_cos: torch.Tensor, rope_sin: torch.Tensor, 
     return x
 
 
-def tk_fused_norm_quantize(input: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6, with_silu: bool = False,
-                           return_transpose: bool = True, return_normalized: bool = False, encode_centric: bool = False):
+def tk_fused_norm_quantize(input: torch.Tensor, gamma: torch.Tensor, epsilon: float = 1e-6, with_silu: bool = False,
+                           return_transpose: bool = True, *, return_normalized: bool = False, encode_centric: bool = True):
     """Fused RMSNorm + NVFP4: returns ``(fp4_row, sc_row, fp4_col, sc_col, sg,
     inv_rms [M], amax [1])`` (plus the bf16 normalised tensor when asked)."""
     _require_matrix(input, "input")
@@ -214,7 +217,7 @@ def tk_fused_norm_quantize(input: torch.Tensor, gamma: torch.Tensor, eps: float 
     am = torch.empty(1, dtype=torch.float32, device=dev)
     sg = torch.empty(1, dtype=torch.float32, device=dev)
     y = torch.empty(rows, cols, dtype=torch.bfloat16, device=dev) if return_normalized else None
-    a = _lib.RmsnormQuantArgs(ptr(input), ptr(gamma.contiguous()), rows, cols, input.stride(0), float(eps), ptr(inv_rms), ptr(y),
+    a = _lib.RmsnormQuantArgs(ptr(input), ptr(gamma.contiguous()), rows, cols, input.stride(0), float(epsilon), ptr(inv_rms), ptr(y),
                               ptr(am), ptr(sg), ptr(fp4_row), ptr(sc_row), ptr(fp4_col), ptr(sc_col), int(bool(encode_centric)))
     check(lib().fa4b_rmsnorm_quant_nvfp4(C.byref(a), C.c_void_p(current_stream())), "fa4b_rmsnorm_quant_nvfp4")
     out = (fp4_row, sc_row, fp4_col, sc_col, sg, inv_rms, am)

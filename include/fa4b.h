@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define FA4B_ABI_VERSION 1
+#define FA4B_ABI_VERSION 2
 
 typedef enum fa4b_status {
   FA4B_OK = 0,
@@ -275,8 +275,15 @@ int fa4b_project_dout_publish(const fa4b_project_nvfp4_args* a, const fa4b_attn_
  * hao_direct_fp4pv_host.inc:1141-1237): codes [B*Hkv, D, S/2] (two keys per byte, feature-major), then at the
  * next multiple of 1024 bytes the E8M0 scale pages [B*Hkv, S/128, 512] (row = feature, k-block = 32 keys). */
 typedef struct fa4b_attn_ws_layout {
+  /* saved section [0, saved_total): published by the forward, replayed by the backward -- the only bytes a
+   * training step has to keep between the two (the reference keeps the same operands, release/routes.json:443-447) */
   size_t q_codes, q_scales, q_global, k_codes, k_scales, k_global;
-  size_t v_fp8, q_fp8, k_fp8, do_fp8, dstat, lstat, dq_accum, amax_bits, status, total;
+  size_t v_fp8, k_fp8, q_fp8, amax_bits, status, saved_total;
+  /* transient section [saved_total, total): lives inside one backward call -- E5M2 dO, dstat, lstat, the FP32 dQ
+   * accumulator and the FP32 dK / dV accumulators of key tiles whose query range is split over several CTAs.
+   * Either the tail of `ws`, or a separate buffer of total - saved_total bytes passed as
+   * fa4b_attn_bwd_args.scratch and shared by every layer */
+  size_t do_fp8, dstat, lstat, dq_accum, dkv_accum, total;
 } fa4b_attn_ws_layout;
 int fa4b_attn_ws_layout_query(const fa4b_attn_dims* d, fa4b_attn_ws_layout* out);
 
@@ -336,9 +343,11 @@ int fa4b_attn_merge(float* o_acc, float* lse_acc, const void* o_part, const floa
  * serving loop with a frozen memory budget).  No counterpart in the reference,
  * whose callers always pre-allocate.  `ws` and `prepared` of the args are
  * ignored: the operand cache is a fixed array inside the library, held by every
- * GPU that loads it until the process exits.  Shapes whose cache
- * (fa4b_attn_workspace_bytes) exceeds FA4B_STATIC_WS_BYTES are rejected with
+ * GPU that loads it until the process exits.  Shapes whose forward operands
+ * (fa4b_attn_ws_layout.saved_total) exceed FA4B_STATIC_WS_BYTES are rejected with
  * FA4B_BAD_SHAPE.  Calls no cudaMalloc/cudaFree or any allocating routine.
+ * fa4b_attn_check_status(dims, NULL, stream) reports a device-side wait that ran
+ * out during the last such call on the current device.
  * The first call on a device looks the array's address up (once per device,
  * with that device current); make that first call before any stream capture.
  * All calls share the array: calls that overlap on the GPU race. */
@@ -363,7 +372,10 @@ typedef struct fa4b_attn_bwd_args {
   void* ev_after;
   const void* kv_ws;    /* optional: a second operand cache of the same dims whose K and V sections are used instead
                            of `ws`'s (the keys of another sequence shard); the queries, dO and statistics stay `ws`'s */
-  int32_t flags;        /* FA4B_BWD_*: how this call treats the FP32 dQ accumulator of `ws` */
+  int32_t flags;        /* FA4B_BWD_*: how this call treats the FP32 dQ accumulator */
+  void* scratch;        /* optional, 1024-byte aligned: the transient section of the layout (total - saved_total
+                           bytes) as a buffer of its own; `ws` then only needs its first saved_total bytes.  NULL:
+                           the transient section is the tail of `ws` */
 } fa4b_attn_bwd_args;
 int fa4b_attn_bwd_preprocess(const fa4b_attn_bwd_args* a, void* stream);
 
@@ -371,10 +383,26 @@ int fa4b_attn_bwd_preprocess(const fa4b_attn_bwd_args* a, void* stream);
  * backward_nvfp4_score_e4m3_qkv_e5m2_dout_bshd_precleared_dq_out
  * (tk_fa4/native_gqa_tk_bwd/v509_*bshd.cu:406-444) and the D64 kernel v416.
  * Runs the preprocess step itself unless `preprocessed` is set.  Uses the
- * workspace's FP32 dQ accumulator as scratch (zeroed here unless FA4B_BWD_KEEP_DQ_ACCUM).  With
+ * transient section's FP32 accumulators as scratch (dQ zeroed here unless FA4B_BWD_KEEP_DQ_ACCUM).  One CTA per
+ * (batch, kv head, key tile, part of the tile's query range), kv-head-major; a key tile that sees more query
+ * tiles than the launch's chunk length is cut into parts whose dK / dV meet as FP32 sums.  With
  * dims.mask = FA4B_MASK_NONE every key is visible to every query (a key shard that precedes the query shard);
  * the statistics must then come from the LSE and O of the whole sequence. */
 int fa4b_attn_bwd(const fa4b_attn_bwd_args* a, void* stream);
+
+/* fa4b_attn_bwd_plan / _plan_item: host only.  The work list fa4b_attn_bwd launches for `d` on a device of n_sm
+ * multiprocessors (n_sm <= 0: the current device): one CTA per item, items_per_head consecutive items per
+ * (batch, kv head), inside a head the key tiles in order and each tile's query range in `parts` nearly equal
+ * pieces of at most `chunk` query tiles.  split_rows: leading key rows of every kv head whose dK / dV pass through
+ * the FP32 accumulators.  Stands in for the grid half of native_tk_d128_backward_metadata()
+ * (tk_fa4/native_gqa_tk_bwd/v509_*bshd.cu:446-522; grid at v509_*bshd.cuh:1561-1565).
+ * _plan_item writes {batch * Hkv + kv head, key tile, first query tile, end query tile, parts} of item `index`. */
+typedef struct fa4b_bwd_plan {
+  int32_t chunk, items_per_head, split_rows;
+  int64_t grid;
+} fa4b_bwd_plan;
+int fa4b_attn_bwd_plan(const fa4b_attn_dims* d, int32_t n_sm, fa4b_bwd_plan* out);
+int fa4b_attn_bwd_plan_item(const fa4b_attn_dims* d, int32_t n_sm, int64_t index, int32_t out[5]);
 
 /* fa4b_attn_accumulate: acc[i] += part[i] (FP32 += bf16) over n values, n % 8 == 0; with out != NULL the sums are
  * also written as bf16.  Folds the dK / dV of one block call into a running FP32 sum (no reference counterpart). */
@@ -383,7 +411,8 @@ int fa4b_attn_accumulate(float* acc, const void* part, int64_t n, void* out, voi
 /* fa4b_attn_check_status: synchronises `stream`, then reports FA4B_TIMEOUT if a
  * bounded wait inside the last attention kernel on this workspace gave up
  * (the reference's waits are unbounded, hao_direct_kernel.inc:17-23; this
- * query has no counterpart there). */
+ * query has no counterpart there).  ws == NULL: the built-in operand cache of
+ * fa4b_attn_fwd_static on the current device. */
 int fa4b_attn_check_status(const fa4b_attn_dims* d, const void* ws, void* stream);
 
 /* ---- tensor-core self tests ("microgates") -------------------------------
@@ -407,6 +436,14 @@ int fa4b_microgate(int kind, int K, const void* a, const void* b, const void* sf
  * (results/fp4_fa4_technical_report_v2_20260819/sections/07_profile.tex:183-184 quotes nominal peaks).
  * status_out [4] u32 device: [0] = 0 ok / 1 wait ran out. */
 int fa4b_tensor_peak(int kind, int iters, uint32_t* status_out, void* stream);
+
+/* fa4b_wait_selftest: the give-up path of the kernels' bounded waits, run on purpose and harmlessly: one small
+ * kernel waits, with a budget of limit_cycles SM clocks (1..1e8), on barriers that nothing arms -- no copy or
+ * tensor-core operation in flight -- records the site as the attention kernels do and returns.  The expected
+ * result is FA4B_TIMEOUT with the site in fa4b_last_error(); the context stays usable.  status_out [8] u32 device:
+ * [0..3] the give-up record, [4..6] what the two waits saw.  (The reference's waits are unbounded,
+ * hao_direct_kernel.inc:17-23, and have no such test.) */
+int fa4b_wait_selftest(int64_t limit_cycles, uint32_t* status_out, void* stream);
 
 #ifdef __cplusplus
 }

@@ -28,6 +28,18 @@ def _check_operands(ws, fwd):
         assert bad == 0, f"{name}: {bad} bytes differ"
 
 
+def _assert_dkv_reproduce(dims, a, b, name):
+    """dK / dV of two runs of the same problem: bit for bit where a key tile's query range is handled by one CTA or
+    two (a + b = b + a), within FP32 summation order where three or more partial sums meet."""
+    plan = attention.backward_plan(dims)
+    n = dims.S // 128
+    causal = dims.mask == 0
+    many = max(0, (n - 2 * plan.chunk) * 128) if causal else (dims.S if n > 2 * plan.chunk else 0)
+    assert torch.equal(a[:, :, many:], b[:, :, many:]), name
+    if many:
+        assert O.rel_l2(a[:, :, :many].float().cpu(), b[:, :, :many].float().cpu()) < 1e-4, name
+
+
 def _check_forward(o, lse, fwd):
     torch.cuda.synchronize()
     assert O.rel_l2(fwd.lse, lse.cpu()) < 1e-2 and (fwd.lse - lse.cpu()).abs().max() < 1e-3
@@ -173,8 +185,8 @@ def test_partition_by_batch_and_kv_head_reproduces_the_unsharded_run():
             parts[n].append(t)
     assert torch.equal(parallel.unshard_q_like(parts["o"], B, Hq), o)
     assert torch.equal(parallel.unshard_q_like(parts["lse"], B, Hq), lse)
-    assert torch.equal(parallel.unshard_kv_like(parts["dk"], B, Hkv), dk)
-    assert torch.equal(parallel.unshard_kv_like(parts["dv"], B, Hkv), dv)
+    _assert_dkv_reproduce(ws.dims, parallel.unshard_kv_like(parts["dk"], B, Hkv), dk, "dk")
+    _assert_dkv_reproduce(ws.dims, parallel.unshard_kv_like(parts["dv"], B, Hkv), dv, "dv")
     assert O.rel_l2(dq.float().cpu(), parallel.unshard_q_like(parts["dq"], B, Hq).float().cpu()) < 1e-3
 
 
@@ -203,7 +215,7 @@ def test_forward_mxfp4_pv_route_matches_oracle(B, Hq, Hkv, S, D):
     # are rare (boundary hits at 1e-7 relative distance); all others meet the 1e-3 bound of the FP8 route.
     err = (fwd.lse - lse.cpu()).abs()
     assert O.rel_l2(fwd.lse, lse.cpu()) < 1e-2
-    assert (err > 1e-3).float().mean() < 1e-3 and err.max() < 0.5, (float((err > 1e-3).float().mean()), float(err.max()))
+    assert (err > 1e-3).float().mean() < 1e-4 and err.max() < 5e-3, (float((err > 1e-3).float().mean()), float(err.max()))
 
 
 def test_backward_refuses_the_forward_only_mxfp4_route():
@@ -246,7 +258,8 @@ def test_full_size_properties_at_the_benchmark_shape():
     through (a) a property: permuting the kv groups permutes O and LSE bit for bit (every statistic is local to a
     (batch, head) slice); (b) a slab: by (a) one (batch, kv head) unit of the full run equals that unit run alone, so
     the oracle of one unit (4 query heads, S = 8192) checks O, LSE, dQ, dK, dV of its rows in the full run;
-    (c) dK and dV reproduce bit for bit from run to run and zero dO gives exactly zero gradients."""
+    (c) dK and dV reproduce from run to run (bit for bit where at most two partial sums meet) and zero dO gives
+    exactly zero gradients."""
     B, Hq, Hkv, S, D = 2, 32, 8, 8192, 128
     q, k, v, do = O.make_attention_inputs(1, 4 * Hkv, Hkv, S, D, seed=20260825, rope=True, do_std=0.01)
     # batch 1 is batch 0 with the kv groups in reverse order: the permutation property and the slab in one run
@@ -264,7 +277,8 @@ def test_full_size_properties_at_the_benchmark_shape():
     # (a)
     pq, pk = perm_q.to(DEV), perm_kv.to(DEV)
     assert torch.equal(o[1], o[0][pq]) and torch.equal(lse[1], lse[0][pq])
-    assert torch.equal(dk[1], dk[0][pk]) and torch.equal(dv[1], dv[0][pk])
+    _assert_dkv_reproduce(ws.dims, dk[1:2], dk[0:1][:, pk], "dk")
+    _assert_dkv_reproduce(ws.dims, dv[1:2], dv[0:1][:, pk], "dv")
     # (b) kv head 5 of batch 0 against the oracle of that unit alone
     hk = 5
     hq = slice(hk * G, (hk + 1) * G)
@@ -277,7 +291,9 @@ def test_full_size_properties_at_the_benchmark_shape():
     # (c)
     dq2, dk2, dv2 = attention.attn_backward(o, lse, dod, ws)
     ws.check_status()
-    assert torch.equal(dk2, dk) and torch.equal(dv2, dv) and O.rel_l2(dq.float().cpu(), dq2.float().cpu()) < 1e-3
+    _assert_dkv_reproduce(ws.dims, dk2, dk, "dk")
+    _assert_dkv_reproduce(ws.dims, dv2, dv, "dv")
+    assert O.rel_l2(dq.float().cpu(), dq2.float().cpu()) < 1e-3
     dq0, dk0, dv0 = attention.attn_backward(o, lse, torch.zeros_like(dod), ws)
     ws.check_status()
     assert not dq0.any() and not dk0.any() and not dv0.any()
@@ -302,7 +318,8 @@ def test_forward_and_backward_replay_from_a_cuda_graph():
         graph.replay()
         torch.cuda.synchronize()
         assert torch.equal(o, o_ref) and torch.equal(lse, lse_ref)
-        assert torch.equal(dk, grads_ref[1]) and torch.equal(dv, grads_ref[2])
+        _assert_dkv_reproduce(ws.dims, dk, grads_ref[1], "dk")
+        _assert_dkv_reproduce(ws.dims, dv, grads_ref[2], "dv")
         assert O.rel_l2(grads_ref[0].float().cpu(), dq.float().cpu()) < 1e-3
     ws_g.check_status()
 

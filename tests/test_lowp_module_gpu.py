@@ -60,6 +60,7 @@ def test_module_backward_matches_oracle_composition():
     blk = LowpFA4AttentionBlock(wq.to(DEV), wk.to(DEV), wv.to(DEV), wo.to(DEV), Hq, Hkv, D)
     y, saved = blk.forward(x.to(DEV), cos.to(DEV), sin.to(DEV), return_intermediates=True)
     got = blk.backward(dy.to(DEV), saved, cos.to(DEV), sin.to(DEV))
+    blk.check_status(saved["workspace"])  # the one host synchronisation of the step: six projection slots + attention
     want = O.lowp_attention_block_backward_reference(dy, x, wq, wk, wv, wo, cos, sin, Hq, Hkv, D)
     # Five chained low-precision GEMMs and the attention backward: a bf16 value on the other side of a rounding
     # boundary in one stage moves FP4 / FP8 codes in the next, so the bound is wider than a single kernel's
@@ -129,7 +130,7 @@ def test_fused_qkv_publication_writes_the_same_operands_as_the_three_passes():
     x, wq, wk, wv, wo, cos, sin = _block_inputs(B, S, hidden, Hq, Hkv, D, seed=61)
     cos, sin = cos.to(DEV), sin.to(DEV)
     rows = x.to(DEV).reshape(B * S, hidden)
-    a_codes, a_pages, _, _, a_g, _ = fa4b.tk_quantize_for_gemm(rows, return_transpose=False)
+    a_codes, a_pages, _, _, a_g, _ = fa4b.tk_quantize_for_gemm(rows, return_transpose=False, encode_centric=False)
     weight = fa4b.prepare_nvfp4_projection_weight(torch.cat((wq, wk, wv), 0).contiguous().to(DEV))
     # three passes: projection, rotation, publication at a unit global scale
     qkv = fa4b.project_nvfp4((a_codes, a_pages, a_g), weight)
@@ -160,7 +161,7 @@ def test_fused_dout_publication_writes_the_same_statistics_as_the_two_passes():
     blk = LowpFA4AttentionBlock(wq.to(DEV), wk.to(DEV), wv.to(DEV), wo.to(DEV), Hq, Hkv, D)
     y, saved = blk.forward(x.to(DEV), cos.to(DEV), sin.to(DEV), return_intermediates=True)
     dy = (torch.randn(B * S, hidden, generator=torch.Generator().manual_seed(82)) * 0.05).bfloat16().to(DEV)
-    g_r, g_p, _, _, g_g, _ = fa4b.tk_quantize_for_gemm(dy, return_transpose=False)
+    g_r, g_p, _, _, g_g, _ = fa4b.tk_quantize_for_gemm(dy, return_transpose=False, encode_centric=False)
     o_rows, lse, ws = saved["o"], saved["lse"], saved["workspace"]
     # two passes
     do_rows = fa4b.project_nvfp4((g_r, g_p, g_g), blk.w_o_t)

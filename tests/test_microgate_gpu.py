@@ -79,3 +79,18 @@ def test_tensor_peak_reports_a_plausible_rate():
     fp4 = microgate.tensor_peak("nvfp4", iters=4096)
     assert 1000.0 < fp8 < 5200.0, fp8
     assert fp8 < fp4 < 10400.0, (fp8, fp4)
+
+
+def test_a_wait_that_runs_out_reports_timeout_and_leaves_the_context_usable():
+    """The give-up path of the kernels' bounded waits (abort flag, status record, orderly return), made to run out on
+    an unarmed barrier with a budget of a million cycles and nothing asynchronous in flight; then a normal launch."""
+    from fa4b import _lib
+
+    status = microgate.wait_selftest(1_000_000)
+    assert status[0].item() == 1 and status[1].item() in (900, 901) and status[4:7].tolist() == [0, 0, 1]
+    assert "site 90" in _lib.lib().fa4b_last_error().decode()
+    with pytest.raises(TimeoutError):
+        _lib.check(5, "fa4b_wait_selftest")
+    a, b = _fp8((128, 64), 1), _fp8((128, 64), 2)
+    got = microgate.run("e4m3_kk", 64, a.to(DEV), b.to(DEV))
+    assert O.rel_l2(a.float() @ b.float().t(), got.cpu()) < TOL

@@ -209,3 +209,68 @@ def test_project_reference_and_block_composition_shapes():
     assert y.shape == (128, 32) and y.dtype == torch.bfloat16
     assert O.rel_l2((a.dequant() @ wf.dequant().t()), y.float()) < 4e-3
     assert torch.equal(wt.dequant(), wf.dequant().t())
+
+
+def test_encode_centric_recipe_against_blocks_worked_by_hand():
+    """Known answers for the TK quantiser's default recipe, worked from core.cuh:47-60, 103-113 and
+    fused_amax_quantize.cuh:235-256 of the reference without this repo's restatement:
+    S_enc = 2688 / amax; M = E4M3(6 / (bamax S_enc)) (448 when bamax <= 1e-9); coeff = M S_enc;
+    stored scale = E4M3(1 / M); code = E2M1_rne(x coeff).  The tensor's amax is 2688, so S_enc = 1.
+    E4M3 bytes: 1 = 0x38, 2 = 0x40, 0.5 = 0x30, 1.25 = 0x3A, 0.8125 = 0x35, 448 = 0x7E, 2^-9 = 0x01.
+    E2M1 codes: 0, .5, 1, 1.5, 2, 3, 4, 6 = 0..7 (ties to the even code)."""
+    x = torch.zeros(2, 64)
+    # block (0,0): bamax 6 -> M = 1, scale 1; elements exercise every tie of the payload grid
+    x[0, :16] = torch.tensor([6, -3, 1.5, 0.75, 0.25, 1.25, 1.75, 2.5, 3.5, 5, -0.75, -5, 0, 0.5, 2, 4])
+    want00 = [7, 8 + 5, 3, 2, 0, 2, 4, 4, 6, 6, 8 + 2, 8 + 6, 0, 1, 4, 6]
+    # block (0,1): holds the tensor maximum 2688 -> M = 6/2688 = 0.00223 -> sub-normal E4M3 2^-9; the stored scale
+    # 1/M = 512 saturates at 448; 2688 * 2^-9 = 5.25 -> 6; 1024 * 2^-9 = 2 -> 2; 512 * 2^-9 = 1
+    x[0, 16:32] = torch.tensor([2688, 1024, 512, -2688] + [0] * 12)
+    want01 = [7, 4, 2, 15] + [0] * 12
+    # block (0,2): all zero -> M = 448, stored scale E4M3(1/448) = 2^-9 (not zero), codes zero
+    # block (0,3): bamax 2^-10 -> M = 6144 saturates at 448; 2^-10 * 448 = 0.4375 -> 0.5; 2^-12 * 448 = 0.109 -> 0
+    x[0, 48:64] = torch.tensor([2.0 ** -10, -(2.0 ** -10), 2.0 ** -12] + [0] * 13)
+    want03 = [1, 9, 0] + [0] * 13
+    # block (1,0): bamax 3 -> M = 2, scale 0.5; 0.375 * 2 = 0.75 (tie -> 1), 0.125 * 2 = 0.25 (tie -> 0), 3 * 2 = 6
+    x[1, :16] = torch.tensor([3, 0.375, 0.125, -0.375] + [0] * 12)
+    want10 = [7, 2, 0, 10] + [0] * 12
+    # block (1,1): bamax 5 -> M = 1.2 -> E4M3 1.25; stored scale E4M3(0.8) = 0.8125; 5 * 1.25 = 6.25 -> 6;
+    # 4 * 1.25 = 5 (tie between 4 and 6 -> 4); 1 * 1.25 = 1.25 (tie -> 1); 2 * 1.25 = 2.5 (tie -> 2)
+    x[1, 16:32] = torch.tensor([5, 4, 1, 2, -4] + [0] * 11)
+    want11 = [7, 6, 2, 4, 14] + [0] * 11
+    q = O.nvfp4_quantize_encode_centric(x.bfloat16())
+    codes = O.unpack_nibbles(q.codes)
+    assert float(q.global_scale) == 1.0
+    assert codes[0, :16].tolist() == want00 and codes[0, 16:32].tolist() == want01 and codes[0, 48:64].tolist() == want03
+    assert codes[1, :16].tolist() == want10 and codes[1, 16:32].tolist() == want11
+    assert not codes[0, 32:48].any() and not codes[1, 32:].any()
+    assert q.scales[0].tolist() == [0x38, 0x7E, 0x01, 0x01]
+    assert q.scales[1].tolist() == [0x30, 0x35, 0x01, 0x01]
+    # an all-zero tensor: S_enc = 1, every block as the zero block above
+    z = O.nvfp4_quantize_encode_centric(torch.zeros(1, 32).bfloat16())
+    assert z.scales.tolist() == [[0x01, 0x01]] and not z.codes.any() and float(z.global_scale) == 0.0
+
+
+def test_forward_emulation_passes_the_reference_forward_gate():
+    """validate_causal_gqa_fp8pv_batch.py:268-324, 705-706 of the reference: O against exact attention on the decoded
+    operands, cosine >= 0.999 and rel-L2 <= 0.03 -- the check that pins the one free choice of the forward emulation
+    (integer reference point, 2^8 lift, exponential split) to what the reference accepts of its own kernel."""
+    for (B, Hq, Hkv, S, D, rope) in ((1, 4, 1, 256, 128, True), (1, 4, 4, 512, 64, False)):
+        q, k, v, _ = O.make_attention_inputs(B, Hq, Hkv, S, D, seed=20260825, rope=rope)
+        for gs in ("amax_per_bh", "one"):
+            fwd = O.attn_forward(q, k, v, global_scale=gs)
+            cosine, rel = O.represented_forward_gate(fwd.o, fwd)
+            assert cosine >= 0.999 and rel <= 0.03, (S, D, gs, cosine, rel)
+
+
+def test_exponential_split_tracks_exp2_and_keeps_powers_of_two_scaling():
+    x = torch.linspace(-40.0, 8.0, 20001)
+    p, r = O.exp2_polynomial(x).double(), torch.exp2(x.double())
+    assert ((p - r) / r).abs().max() < 8e-5
+    # an integer shift of the exponent is an exact power-of-two factor: what makes the rounding of a probability
+    # independent of the (integer) reference point a streaming kernel holds
+    xe = torch.arange(-40 * 256, 5 * 256 + 1).float() / 256.0  # x + 3 is exact on this grid
+    assert torch.equal(O.exp2_polynomial(xe + 3.0), O.exp2_polynomial(xe) * 8.0)
+    e = torch.tensor([[0.0, 1.0, 2.5, 3.5, float("-inf"), 5.0] + [0.0] * 10])
+    out = O.exp2_split(e)
+    assert out[0, 4] == 0.0 and out[0, 0] == 1.0 and out[0, 1] == 2.0        # keys 0, 1: exponential unit
+    assert out[0, 2] == O.exp2_polynomial(torch.tensor(2.5)) != 2.0 ** 2.5   # keys 2, 3 (pair 1): polynomial

@@ -21,7 +21,7 @@ def _same(a, b, what):
 @pytest.mark.parametrize("shape,seed", [((128, 128), 1), ((256, 512), 2), ((384, 1024), 3)])
 def test_nvfp4_row_and_transposed_match_oracle(shape, seed):
     x, _ = O.make_quantizer_inputs(*shape, seed=seed)
-    fp4_row, sc_row, fp4_col, sc_col, sg, am = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=True)
+    fp4_row, sc_row, fp4_col, sc_col, sg, am = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=True, encode_centric=False)
     ref = O.nvfp4_quantize(x)
     ref_t = O.nvfp4_quantize_transposed(x)
     assert float(am) == float(x.float().abs().amax())
@@ -36,7 +36,7 @@ def test_nvfp4_row_and_transposed_match_oracle(shape, seed):
 
 def test_nvfp4_edge_cases_zero_tensor_zero_blocks_ties_and_row_only():
     x = torch.zeros(128, 128, dtype=torch.bfloat16)
-    out = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=False)
+    out = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=False, encode_centric=False)
     assert out[2] is None and out[3] is None
     assert not out[0].any() and not out[1].any() and float(out[4]) == 0.0
     x, _ = O.make_quantizer_inputs(256, 256, seed=5)
@@ -44,7 +44,7 @@ def test_nvfp4_edge_cases_zero_tensor_zero_blocks_ties_and_row_only():
     x[:, 17] = 0
     x[9, :16] = (torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0] * 2) * float(x.float().abs().amax()) / 6.0).bfloat16()
     x[10, :16] = -x[9, :16]
-    fp4_row, sc_row, fp4_col, sc_col, sg, _ = fa4b.tk_quantize_for_gemm(x.to(DEV))
+    fp4_row, sc_row, fp4_col, sc_col, sg, _ = fa4b.tk_quantize_for_gemm(x.to(DEV), encode_centric=False)
     ref, ref_t = O.nvfp4_quantize(x), O.nvfp4_quantize_transposed(x)
     _same(fp4_row, ref.codes, "row codes")
     _same(sc_row, ref.pages(), "row pages")
@@ -57,7 +57,7 @@ def test_nvfp4_with_supplied_amax_and_strided_input():
     big = x.to(DEV)
     view = big[:, 128:384]  # ld = 512, cols = 256
     am = torch.tensor([float(x.float().abs().amax())], device=DEV)
-    fp4_row, sc_row, _, _, sg, _ = fa4b.tk_quantize_for_gemm(view, return_transpose=False, amax_in=am)
+    fp4_row, sc_row, _, _, sg, _ = fa4b.tk_quantize_for_gemm(view, return_transpose=False, amax_in=am, encode_centric=False)
     ref = O.nvfp4_quantize(x[:, 128:384].contiguous(), amax=am.cpu())
     _same(fp4_row, ref.codes, "row codes")
     _same(sc_row, ref.pages(), "row pages")
@@ -101,7 +101,7 @@ def test_project_nvfp4_matches_oracle_on_represented_operands(M, N, K, seed):
     x, _ = O.make_quantizer_inputs(M, K, seed=seed)
     w, _ = O.make_quantizer_inputs(N, K, seed=seed + 100)
     w = (w * 0.05).bfloat16()
-    fp4, sc, _, _, sg, _ = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=False)
+    fp4, sc, _, _, sg, _ = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=False, encode_centric=False)
     weight = fa4b.prepare_nvfp4_projection_weight(w.to(DEV))
     y = fa4b.project_nvfp4((fp4, sc, sg), weight)
     assert y.shape == (M, N) and y.dtype == torch.bfloat16
@@ -119,7 +119,7 @@ def test_project_nvfp4_with_the_transposed_weight_gives_the_input_gradient_produ
     w = (torch.randn(512, 256, generator=g) * 0.05).bfloat16()   # [N, K]
     dy = torch.randn(128, 512, generator=g).bfloat16()           # [M, N]
     fwd, tr = fa4b.prepare_nvfp4_projection_weight_dual(w.to(DEV))
-    fp4, sc, _, _, sg, _ = fa4b.tk_quantize_for_gemm(dy.to(DEV), return_transpose=False)
+    fp4, sc, _, _, sg, _ = fa4b.tk_quantize_for_gemm(dy.to(DEV), return_transpose=False, encode_centric=False)
     dx = fa4b.project_nvfp4((fp4, sc, sg), tr)                   # [M, K]
     ref = (O.nvfp4_quantize(dy).dequant().double() @ O.nvfp4_quantize_weight(w)[0].dequant().double()).to(torch.bfloat16)
     assert O.rel_l2(ref.float(), dx.float().cpu()) < 1e-4
@@ -202,7 +202,7 @@ def _wide_range(M, K, seed, lo=-20, hi=20):
 @pytest.mark.parametrize("seed,lo,hi", [(31, -20, 20), (32, -40, 0), (33, -4, 12)])
 def test_nvfp4_wide_dynamic_range_matches_oracle(seed, lo, hi):
     x = _wide_range(512, 512, seed, lo, hi)
-    fp4_row, sc_row, fp4_col, sc_col, sg, _ = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=True)
+    fp4_row, sc_row, fp4_col, sc_col, sg, _ = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=True, encode_centric=False)
     ref, ref_t = O.nvfp4_quantize(x), O.nvfp4_quantize_transposed(x)
     assert float(sg) == float(ref.global_scale)
     _same(fp4_row, ref.codes, "row codes")
@@ -214,7 +214,7 @@ def test_nvfp4_wide_dynamic_range_matches_oracle(seed, lo, hi):
 def test_nvfp4_supplied_amax_far_below_the_data_saturates_like_the_oracle():
     x = _wide_range(256, 256, 34, 0, 10)
     tiny = torch.tensor([2.0 ** -20], dtype=torch.float32)
-    fp4_row, sc_row, _, _, sg, _ = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=False, amax_in=tiny.to(DEV))
+    fp4_row, sc_row, _, _, sg, _ = fa4b.tk_quantize_for_gemm(x.to(DEV), return_transpose=False, amax_in=tiny.to(DEV), encode_centric=False)
     ref = O.nvfp4_quantize(x, amax=tiny)
     assert float(sg) == float(ref.global_scale)
     _same(fp4_row, ref.codes, "row codes")
@@ -245,7 +245,7 @@ def test_mxfp4_matches_oracle(mode):
 def test_fused_rmsnorm_nvfp4_matches_oracle():
     x, gamma = O.make_quantizer_inputs(256, 1024, seed=13)
     fp4_row, sc_row, fp4_col, sc_col, sg, inv_rms, am, y = fa4b.tk_fused_norm_quantize(
-        x.to(DEV), gamma.to(DEV), 1e-6, return_transpose=True, return_normalized=True)
+        x.to(DEV), gamma.to(DEV), 1e-6, return_transpose=True, return_normalized=True, encode_centric=False)
     _, inv_ref = O.rmsnorm_reference(x, gamma, 1e-6)
     # FP32 tree sum vs the oracle's FP64 mean: at most 2 ulp on inv_rms
     ulp = (inv_rms.cpu().view(torch.int32) - inv_ref.view(torch.int32)).abs().max().item()
@@ -265,13 +265,13 @@ def test_full_size_quantizers_by_slabs_and_transpose_property():
     M, K = 16384, 4096
     x, gamma = O.make_quantizer_inputs(M, K, seed=20260825)
     xd = x.to(DEV)
-    fp4_row, sc_row, fp4_col, sc_col, sg, am = fa4b.tk_quantize_for_gemm(xd)
+    fp4_row, sc_row, fp4_col, sc_col, sg, am = fa4b.tk_quantize_for_gemm(xd, encode_centric=False)
     amax = am.cpu()
     for r0 in (0, 4096 + 128, M - 128):
         ref = O.nvfp4_quantize(x[r0:r0 + 128], amax=amax)
         _same(fp4_row[r0:r0 + 128], ref.codes, f"row codes slab {r0}")
         _same(sc_row[r0 // 128], ref.pages()[0], f"row pages slab {r0}")
-    t_row, t_sc, _, _, _, _ = fa4b.tk_quantize_for_gemm(xd.t().contiguous(), return_transpose=False)
+    t_row, t_sc, _, _, _, _ = fa4b.tk_quantize_for_gemm(xd.t().contiguous(), return_transpose=False, encode_centric=False)
     _same(fp4_col, t_row, "transposed codes vs row-wise of x^T")
     _same(sc_col, t_sc, "transposed pages vs row-wise of x^T")
     fp4, sc = fa4b.mxfp4_quantize_for_gemm(xd)
@@ -279,7 +279,7 @@ def test_full_size_quantizers_by_slabs_and_transpose_property():
         ref = O.mxfp4_quantize(x[r0:r0 + 128])
         _same(fp4[r0:r0 + 128], ref.codes, f"mx codes slab {r0}")
         _same(sc[r0 // 128], ref.pages()[0], f"mx pages slab {r0}")
-    out = fa4b.tk_fused_norm_quantize(xd, gamma.to(DEV), 1e-6)
+    out = fa4b.tk_fused_norm_quantize(xd, gamma.to(DEV), 1e-6, encode_centric=False)
     inv = out[5].cpu()
     r0 = 8192
     y = O.rmsnorm_apply(x[r0:r0 + 128], gamma, inv[r0:r0 + 128])
@@ -296,7 +296,7 @@ def test_rmsnorm_backward_matches_fp32_reference(M, K):
     x, gamma = O.make_quantizer_inputs(M, K, seed=40 + M)
     g = torch.Generator().manual_seed(M + K)
     dy = (torch.randn(M, K, generator=g) * 0.1).bfloat16()
-    out = fa4b.tk_fused_norm_quantize(x.to(DEV), gamma.to(DEV), 1e-6, return_transpose=False)
+    out = fa4b.tk_fused_norm_quantize(x.to(DEV), gamma.to(DEV), 1e-6, return_transpose=False, encode_centric=False)
     inv_rms = out[5]
     want_dx, want_dg = O.rmsnorm_backward_reference(x, gamma, inv_rms.cpu(), dy)
     dx, dgamma = fa4b.rmsnorm_backward_bf16(x.to(DEV), gamma.to(DEV), inv_rms, dy.to(DEV))
