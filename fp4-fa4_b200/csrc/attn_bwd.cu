@@ -122,25 +122,30 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
   constexpr int QT = C::QT;
   constexpr int kPages = C::kPages;
   extern __shared__ uint8_t raw[];
-  BwdSmem<D>& s = *reinterpret_cast<BwdSmem<D>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  // aligned by offsetting the shared array itself, so that accesses stay shared-space loads and stores
+  BwdSmem<D>& s = *reinterpret_cast<BwdSmem<D>*>(raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u));
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
 
   const int n_tiles = p.S / 128;
-  // Work item = (batch and kv head, key tile, part of the tile's query range).  kv-head-major order: the CTAs
-  // in flight then add into the FP32 dQ rows of two or three kv heads (17 MB each at S = 8192, D = 128), which
-  // stay in L2 until their last partial sum has arrived.  Inside a head the key tiles run from the one that
-  // sees the most query tiles down, and a tile's range is cut into parts of at most `chunk` query tiles so that
-  // no CTA is long against the whole launch: the last head's heavy tiles no longer leave a tail, and a launch
-  // of few (batch, kv head) units still fills the GPU.
-  const BwdItem item = bwd_item_of((int)blockIdx.x % p.items_per_head, n_tiles, p.chunk, p.causal != 0);
+  // Work item = (key tile, part of the tile's query range, batch and kv head), key-tile-major: the key tiles that
+  // see the most query tiles start first, all heads of a tile side by side.  When the launch has few (batch, kv
+  // head) units a tile's query range is cut into parts of at most `chunk` query tiles, so that the work still
+  // spreads over every SM (kv-head-major order, which keeps a head's FP32 dQ rows in L2 while their partial sums
+  // arrive, measured 8 % slower at B2 Hkv8 S8192 and the same on a launch of two units: the reductions do not
+  // bound the kernel).
+  const int heads_kv = p.B * p.Hkv;
+  const BwdItem item = bwd_item_of((int)blockIdx.x / heads_kv, n_tiles, p.chunk, p.causal != 0);
   const int kt = item.kt;
-  const int bhk = blockIdx.x / p.items_per_head;
+  const int bhk = blockIdx.x % heads_kv;
   const int b = bhk / p.Hkv, hk = bhk % p.Hkv;
   const int G = p.Hq / p.Hkv;
   const int sub_per_tile = 128 / QT;
   const int n_sub = (item.qt_hi - item.qt_lo) * sub_per_tile;  // query sub-tiles per head
   const int n_it = G * n_sub;
   const int sub0 = item.qt_lo * sub_per_tile;
+  // it -> (it / n_sub, it % n_sub) without a division per use: exact for it * n_sub < 2^32
+  const uint32_t n_sub_inv = 0xFFFFFFFFu / (uint32_t)n_sub + 1u;
+  auto head_of = [&](int it) { return n_sub == 1 ? it : (int)__umulhi((uint32_t)it, n_sub_inv); };
   {
     // an earlier CTA of this launch gave up: leave at once, as one (the decision is CTA-uniform)
     __shared__ uint32_t skip;
@@ -188,7 +193,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         const int st = it % kBwdStages;
         if (it >= kBwdStages && !mbar_wait(&s.in_empty[st], ((it / kBwdStages) - 1) & 1, &s.abort_flag, p.status, 110, it)) break;
         issued = it + 1;
-        const int g = it / n_sub, qs = sub0 + it % n_sub;
+        const int g = head_of(it), qs = sub0 + it - g * n_sub;
         const int bh = b * p.Hq + hk * G + g;
         const int q0 = qs * QT;
         mbar_expect_tx(&s.in_full[st], QT * D / 2 + kPages * 512 + 2 * QT * D + 2 * QT * 4);
@@ -262,7 +267,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       auto fire_s = [&](int it) {
         const uint32_t st = stage_of(it), g = it & 1;
         // D = 128: which 64 rows of the 128-row scale page (sub-tiles alternate, sub0 is even)
-        const uint32_t sf_shift = (QT == 64) ? 2u * (uint32_t)((it % n_sub) & 1) : 0u;
+        const uint32_t sf_shift = (QT == 64) ? 2u * (uint32_t)(it & 1) : 0u;  // n_sub is even at QT = 64
         if (leader) {
           const uint64_t qc = d_qc0 + st * kQc16;
 #pragma unroll
@@ -365,7 +370,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     for (int it = 0; it < n_it; ++it) {
       if (!mbar_wait_warp(&s.dq_full, it & 1, &s.abort_flag, p.status, 130, it)) break;
       tc_fence_after();
-      const int g = it / n_sub, qs = sub0 + it % n_sub;
+      const int g = head_of(it), qs = sub0 + it - g * n_sub;
       const int bh = b * p.Hq + hk * G + g;
       float* base = p.dq_accum + ((size_t)bh * p.S + (size_t)qs * QT) * D;
       uint32_t v0[32], v1[32];
@@ -422,7 +427,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     const uint32_t swz = (QT == 128 ? (row & 7u) : ((row >> 1) & 3u)) << 4;
     auto do_p = [&](int it, uint32_t (&pk)[CW / 4]) -> bool {
       const int st = it % kBwdStages;
-      const int g = it / n_sub, qs = sub0 + it % n_sub;
+      const int g = head_of(it), qs = sub0 + it - g * n_sub;
       const uint64_t c2c2 = pack2(s.c2[g], s.c2[g]);
       const int q_first = qs * QT + half * CW;     // global query index of this thread's first column
       const bool diag = p.causal && qs * QT < kt * 128 + 128;  // sub-tile overlaps the key tile: mask needed
@@ -718,8 +723,9 @@ extern "C" int fa4b_attn_bwd_plan_item(const fa4b_attn_dims* d, int32_t n_sm, in
   if (int s = fa4b_attn_bwd_plan(d, n_sm, &plan)) return s;
   FA4B_REQUIRE(out != nullptr && index >= 0 && index < plan.grid, FA4B_BAD_ARG, "item index outside the launch's %lld work items",
                (long long)plan.grid);
-  const BwdItem it = bwd_item_of((int)(index % plan.items_per_head), d->S / 128, plan.chunk, d->mask == FA4B_MASK_CAUSAL);
-  out[0] = (int32_t)(index / plan.items_per_head);
+  const int64_t heads = (int64_t)d->B * d->Hkv;
+  const BwdItem it = bwd_item_of((int)(index / heads), d->S / 128, plan.chunk, d->mask == FA4B_MASK_CAUSAL);
+  out[0] = (int32_t)(index % heads);
   out[1] = it.kt;
   out[2] = it.qt_lo;
   out[3] = it.qt_hi;

@@ -85,7 +85,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v) {
   extern __shared__ uint8_t raw[];
-  FwdSmem<D>& s = *reinterpret_cast<FwdSmem<D>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  // aligned by offsetting the shared array itself, so that accesses stay shared-space loads and stores
+  FwdSmem<D>& s = *reinterpret_cast<FwdSmem<D>*>(raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u));
   constexpr int kPages = D / 64;
   constexpr uint32_t kKvBytes = 128 * D / 2 + kPages * 512 + (MX ? D * 64 + 512 : 128 * D);
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;

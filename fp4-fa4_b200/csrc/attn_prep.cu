@@ -20,10 +20,13 @@ struct HeadView {
   }
 };
 
-// grid (row chunks, B*H): amax over the [S, D] slice of one head
+// grid (row chunks, B*Hq + B*Hkv): amax over the [S, D] slice of one head of Q (first n_first slices) or K
 template <int D>
-__global__ void __launch_bounds__(256) head_amax_kernel(HeadView x, int S, int rows_per_cta, int* __restrict__ amax_bits) {
-  const int bh = blockIdx.y;
+__global__ void __launch_bounds__(256) head_amax_kernel(HeadView xq, HeadView xk, int n_first, int S, int rows_per_cta,
+                                                        int* __restrict__ amax_bits) {
+  const bool second = (int)blockIdx.y >= n_first;
+  const HeadView& x = second ? xk : xq;
+  const int bh = second ? blockIdx.y - n_first : blockIdx.y;
   constexpr int kVec = D / 8;             // 16-byte chunks per row
   constexpr int kRowsPerPass = 256 / kVec;
   const int r0 = blockIdx.x * rows_per_cta;
@@ -42,23 +45,61 @@ __global__ void __launch_bounds__(256) head_amax_kernel(HeadView x, int S, int r
   if (threadIdx.x == 0) {
 #pragma unroll
     for (int k = 1; k < 8; ++k) m = fmaxf(m, wm[k]);
-    atomicMax(amax_bits + bh, __float_as_int(m));
+    atomicMax(amax_bits + blockIdx.y, __float_as_int(m));
   }
 }
 
-// grid (S/128, B*H): NVFP4 codes, scale pages, global scale and (optionally) E4M3(4x) of one 128-row tile
+// One tensor's share of the publication launch
+struct PublishSide {
+  HeadView x;
+  int* amax_bits;   // [heads] f32 bits
+  uint8_t* codes;   // NVFP4 codes [heads, S, D/2]; NULL for V
+  uint8_t* pages;   // scale pages [heads, S/128, D/64, 512]
+  float* gscale;    // [heads]
+  uint8_t* fp8;     // E4M3(4x) [heads, S, D]
+};
+
+// grid (S/128, B*Hq + 2 B*Hkv): one 128-row tile of one head of Q, K or V per CTA.  Q and K: NVFP4 codes, scale pages,
+// global scale and E4M3(4x); V (`with_v`): E4M3(4x) only.  `unit_global`: the global decode scale is exactly one
+// (amax word 2688, written here) and no statistics pass has run.
 template <int D>
-__global__ void __launch_bounds__(256) quant_heads_kernel(HeadView x, int S, const int* __restrict__ amax_bits,
-                                                          uint8_t* __restrict__ codes, uint8_t* __restrict__ pages,
-                                                          float* __restrict__ gscale, uint8_t* __restrict__ fp8) {
+__global__ void __launch_bounds__(256) publish_heads_kernel(PublishSide sq, PublishSide sk, PublishSide sv, int nq, int nk, int S,
+                                                            int unit_global) {
   constexpr int kKb = D / 16, kPages = D / 64;
   __shared__ __align__(16) uint8_t sc[kPages * 512];
   __shared__ StepTable steps;
-  const int bh = blockIdx.y, tile = blockIdx.x, t = threadIdx.x;
-  const float amax = __int_as_float(amax_bits[bh]);
+  const int which = (int)blockIdx.y < nq ? 0 : ((int)blockIdx.y < nq + nk ? 1 : 2);
+  const PublishSide& side = which == 0 ? sq : (which == 1 ? sk : sv);
+  const HeadView& x = side.x;
+  const int bh = which == 0 ? blockIdx.y : (which == 1 ? blockIdx.y - nq : blockIdx.y - nq - nk);
+  const int tile = blockIdx.x, t = threadIdx.x;
+  uint8_t* __restrict__ fp8 = side.fp8;
+  if (which == 2) {  // V: E4M3(4v) of the tile's 128 rows
+    constexpr int kPerRow = D / 16;
+    for (int c = t; c < 128 * kPerRow; c += 256) {
+      const int r = c / kPerRow, kb = c % kPerRow;
+      const int s = tile * 128 + r;
+      const uint4* src = reinterpret_cast<const uint4*>(x.row(bh, s) + kb * 16);
+      const uint4 lo = __ldg(src), hi = __ldg(src + 1);
+      const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        o[k] = cvt_e4m3x4(4.f * bf16_bits_to_f32(w[2 * k] & 0xffffu), 4.f * bf16_bits_to_f32(w[2 * k] >> 16),
+                          4.f * bf16_bits_to_f32(w[2 * k + 1] & 0xffffu), 4.f * bf16_bits_to_f32(w[2 * k + 1] >> 16));
+      *reinterpret_cast<uint4*>(fp8 + ((size_t)bh * S + s) * D + kb * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    return;
+  }
+  uint8_t* __restrict__ codes = side.codes;
+  uint8_t* __restrict__ pages = side.pages;
+  const float amax = unit_global ? kNvfp4GlobalDiv : __int_as_float(side.amax_bits[bh]);
   const float g = amax / kNvfp4GlobalDiv;
   const float inv6g = 1.0f / (6.0f * g);
-  if (tile == 0 && t == 0) gscale[bh] = g;
+  if (tile == 0 && t == 0) {
+    side.gscale[bh] = g;
+    if (unit_global) side.amax_bits[bh] = __float_as_int(kNvfp4GlobalDiv);
+  }
   const bool all_zero = !(amax > 0.f);
   fill_step_table(steps, g, t);
   __syncthreads();
@@ -104,25 +145,6 @@ __global__ void __launch_bounds__(256) quant_heads_kernel(HeadView x, int S, con
   if (t < kPages * 32) {
     uint8_t* dst = pages + (((size_t)bh * (S / 128) + tile) * kPages) * 512 + t * 16;
     *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&sc[t * 16]);
-  }
-}
-
-// E4M3(4x) of [B,H,S,D] through strides into a dense [B*H, S, D]
-template <int D>
-__global__ void __launch_bounds__(256) heads_to_fp8_kernel(HeadView x, int S, int64_t n_chunks, uint8_t* __restrict__ out) {
-  constexpr int kPerRow = D / 16;
-  for (int64_t c = (int64_t)blockIdx.x * 256 + threadIdx.x; c < n_chunks; c += (int64_t)gridDim.x * 256) {
-    const int64_t row = c / kPerRow;
-    const int kb = (int)(c % kPerRow);
-    const uint4* src = reinterpret_cast<const uint4*>(x.row((int)(row / S), (int)(row % S)) + kb * 16);
-    const uint4 lo = __ldg(src), hi = __ldg(src + 1);
-    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-    uint32_t o[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k)
-      o[k] = cvt_e4m3x4(4.f * bf16_bits_to_f32(w[2 * k] & 0xffffu), 4.f * bf16_bits_to_f32(w[2 * k] >> 16),
-                        4.f * bf16_bits_to_f32(w[2 * k + 1] & 0xffffu), 4.f * bf16_bits_to_f32(w[2 * k + 1] >> 16));
-    *reinterpret_cast<uint4*>(out + row * D + kb * 16) = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
@@ -311,6 +333,12 @@ int launch_attn_merge(float* o_acc, float* lse_acc, const void* o_part, const fl
   return FA4B_OK;
 }
 
+// the amax words of tensors whose global decode scale is to be exactly one: amax / 2688 = 1
+__global__ void publish_unit_amax_kernel(int* __restrict__ amax_bits, int n) {
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i < n) amax_bits[i] = __float_as_int(kNvfp4GlobalDiv);
+}
+
 static int check_view(const void* p, const fa4b_strides& s, const char* name) {
   FA4B_REQUIRE(p != nullptr, FA4B_BAD_ARG, "%s is NULL", name);
   FA4B_REQUIRE((reinterpret_cast<uintptr_t>(p) & 15) == 0 && s.batch % 8 == 0 && s.head % 8 == 0 && s.seq % 8 == 0, FA4B_BAD_ALIGN,
@@ -322,12 +350,6 @@ static HeadView view(const void* p, const fa4b_strides& s, int H) {
   return HeadView{static_cast<const __nv_bfloat16*>(p), s.batch, s.head, s.seq, H};
 }
 
-// the amax words of a tensor whose global decode scale is to be exactly one: amax / 2688 = 1
-__global__ void fill_unit_amax_kernel(int* __restrict__ amax_bits, int n) {
-  const int i = blockIdx.x * 256 + threadIdx.x;
-  if (i < n) amax_bits[i] = __float_as_int(kNvfp4GlobalDiv);
-}
-
 template <int D>
 static int prepare_impl(const fa4b_attn_prepare_args& a, cudaStream_t st) {
   const fa4b_attn_dims& d = a.dims;
@@ -336,32 +358,36 @@ static int prepare_impl(const fa4b_attn_prepare_args& a, cudaStream_t st) {
   const int nq = d.B * d.Hq, nk = d.B * d.Hkv;
   int* amax_bits = reinterpret_cast<int*>(ws + l.amax_bits);
   const HeadView q = view(a.q, a.q_strides, d.Hq), k = view(a.k, a.k_strides, d.Hkv), v = view(a.v, a.v_strides, d.Hkv);
-  if (a.phase != FA4B_PREPARE_QUANTIZE && d.global_scale_mode == FA4B_GLOBAL_ONE) {
-    fill_unit_amax_kernel<<<(nq + nk + 255) / 256, 256, 0, st>>>(amax_bits, nq + nk);
-    FA4B_CUDA(cudaGetLastError());
-    if (a.phase == FA4B_PREPARE_AMAX) return FA4B_OK;
-  } else if (a.phase != FA4B_PREPARE_QUANTIZE) {
+  const bool unit = d.global_scale_mode == FA4B_GLOBAL_ONE;
+  const bool mx = d.pv_format == FA4B_PV_MXFP4_E8M0;
+  PublishSide sq{q, amax_bits, ws + l.q_codes, ws + l.q_scales, reinterpret_cast<float*>(ws + l.q_global), ws + l.q_fp8};
+  PublishSide sk{k, amax_bits + nq, ws + l.k_codes, ws + l.k_scales, reinterpret_cast<float*>(ws + l.k_global), ws + l.k_fp8};
+  PublishSide sv{v, nullptr, nullptr, nullptr, nullptr, ws + l.v_fp8};
+  if (a.phase != FA4B_PREPARE_QUANTIZE && !unit) {
+    // one statistics launch over the heads of Q and K
     FA4B_CUDA(cudaMemsetAsync(amax_bits, 0, (size_t)(nq + nk) * 4, st));
     const int rows_per_cta = 512;
     const unsigned chunks = (unsigned)((d.S + rows_per_cta - 1) / rows_per_cta);
-    head_amax_kernel<D><<<dim3(chunks, nq), 256, 0, st>>>(q, d.S, rows_per_cta, amax_bits);
-    head_amax_kernel<D><<<dim3(chunks, nk), 256, 0, st>>>(k, d.S, rows_per_cta, amax_bits + nq);
+    head_amax_kernel<D><<<dim3(chunks, nq + nk), 256, 0, st>>>(q, k, nq, d.S, rows_per_cta, amax_bits);
     FA4B_CUDA(cudaGetLastError());
-    if (a.phase == FA4B_PREPARE_AMAX) return FA4B_OK;
   }
-  quant_heads_kernel<D><<<dim3(d.S / 128, nq), 256, 0, st>>>(q, d.S, amax_bits, ws + l.q_codes, ws + l.q_scales,
-                                                             reinterpret_cast<float*>(ws + l.q_global), ws + l.q_fp8);
-  quant_heads_kernel<D><<<dim3(d.S / 128, nk), 256, 0, st>>>(k, d.S, amax_bits + nq, ws + l.k_codes, ws + l.k_scales,
-                                                             reinterpret_cast<float*>(ws + l.k_global), ws + l.k_fp8);
-  if (d.pv_format == FA4B_PV_MXFP4_E8M0) {
+  if (a.phase == FA4B_PREPARE_AMAX) {
+    if (unit) {  // the words a caller may read between the phases: 2688 = a unit global scale
+      publish_unit_amax_kernel<<<(nq + nk + 255) / 256, 256, 0, st>>>(amax_bits, nq + nk);
+      FA4B_CUDA(cudaGetLastError());
+    }
+    return FA4B_OK;
+  }
+  // one publication launch: Q and K codes, pages, global scales and E4M3 copies, and E4M3 V.  With a unit global
+  // scale and phase ALL this is the only launch in front of the forward kernel.
+  const bool unit_here = unit && a.phase == FA4B_PREPARE_ALL;
+  publish_heads_kernel<D><<<dim3(d.S / 128, nq + nk + (mx ? 0 : nk)), 256, 0, st>>>(sq, sk, sv, nq, nk, d.S, unit_here ? 1 : 0);
+  FA4B_CUDA(cudaGetLastError());
+  if (mx) {
     // the V section of the cache holds the MXFP4 codes, then (1024-aligned) the scale pages
     v_to_mx_kernel<D><<<dim3(d.S / 128, nk), 256, 0, st>>>(v, d.S, ws + l.v_fp8, ws + l.v_fp8 + v_mx_pages_offset(d));
-  } else {
-    const int64_t n_chunks = (int64_t)nk * d.S * (D / 16);
-    const unsigned grid = (unsigned)std::min<int64_t>((n_chunks + 255) / 256, (int64_t)std::max(sm_count(), 1) * 16);
-    heads_to_fp8_kernel<D><<<grid, 256, 0, st>>>(v, d.S, n_chunks, ws + l.v_fp8);
+    FA4B_CUDA(cudaGetLastError());
   }
-  FA4B_CUDA(cudaGetLastError());
   return FA4B_OK;
 }
 

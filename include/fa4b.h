@@ -384,19 +384,22 @@ int fa4b_attn_bwd_preprocess(const fa4b_attn_bwd_args* a, void* stream);
  * (tk_fa4/native_gqa_tk_bwd/v509_*bshd.cu:406-444) and the D64 kernel v416.
  * Runs the preprocess step itself unless `preprocessed` is set.  Uses the
  * transient section's FP32 accumulators as scratch (dQ zeroed here unless FA4B_BWD_KEEP_DQ_ACCUM).  One CTA per
- * (batch, kv head, key tile, part of the tile's query range), kv-head-major; a key tile that sees more query
- * tiles than the launch's chunk length is cut into parts whose dK / dV meet as FP32 sums.  With
+ * (key tile, part of the tile's query range, batch and kv head), key-tile-major; in a launch of few heads a key
+ * tile that sees more query tiles than the launch's chunk length is cut into parts whose dK / dV meet as FP32
+ * sums (fa4b_attn_bwd_plan).  With
  * dims.mask = FA4B_MASK_NONE every key is visible to every query (a key shard that precedes the query shard);
  * the statistics must then come from the LSE and O of the whole sequence. */
 int fa4b_attn_bwd(const fa4b_attn_bwd_args* a, void* stream);
 
 /* fa4b_attn_bwd_plan / _plan_item: host only.  The work list fa4b_attn_bwd launches for `d` on a device of n_sm
- * multiprocessors (n_sm <= 0: the current device): one CTA per item, items_per_head consecutive items per
- * (batch, kv head), inside a head the key tiles in order and each tile's query range in `parts` nearly equal
- * pieces of at most `chunk` query tiles.  split_rows: leading key rows of every kv head whose dK / dV pass through
- * the FP32 accumulators.  Stands in for the grid half of native_tk_d128_backward_metadata()
- * (tk_fa4/native_gqa_tk_bwd/v509_*bshd.cu:446-522; grid at v509_*bshd.cuh:1561-1565).
- * _plan_item writes {batch * Hkv + kv head, key tile, first query tile, end query tile, parts} of item `index`. */
+ * multiprocessors (n_sm <= 0: the current device): one CTA per item; items_per_head items per (batch, kv head):
+ * the key tiles in order, each tile's query range in `parts` nearly equal pieces of at most `chunk` query tiles
+ * (chunk = S / 128, i.e. no cut, when the launch has about six CTAs per SM without one).  Launch order is
+ * key-tile-major: item i of every head, then item i + 1 of every head.  split_rows: leading key rows of every kv
+ * head whose dK / dV pass through the FP32 accumulators.  Stands in for the grid half of
+ * native_tk_d128_backward_metadata() (tk_fa4/native_gqa_tk_bwd/v509_*bshd.cu:446-522; grid at
+ * v509_*bshd.cuh:1561-1565).  _plan_item writes {batch * Hkv + kv head, key tile, first query tile, end query
+ * tile, parts} of the CTA with block index `index`. */
 typedef struct fa4b_bwd_plan {
   int32_t chunk, items_per_head, split_rows;
   int64_t grid;
