@@ -39,7 +39,7 @@ struct FwdSmem {
   alignas(16) uint8_t k_sf[kStages][(D / 64) * 512];
   alignas(16) uint8_t v_sf[kStages][512];      // MXFP4 route: E8M0 page of the stage's V (row = feature)
   alignas(16) uint8_t p_sf[2][512];            // MXFP4 route: E8M0 page of the P block (row = query row)
-  alignas(8) uint64_t q_full, kv_full[kStages], kv_empty[2][kStages], s_full[2], s_free[2], p_ready[2][2], o_done[2], exp_done[2][4], mma_drained;
+  alignas(8) uint64_t q_full, kv_full[kStages], kv_empty[2][kStages], s_full[2], s_free[2], p_ready[2][2], o_done[2], mma_drained;
   uint32_t tmem_base;
   alignas(8) volatile uint32_t abort_flag;
   uint32_t pad_;
@@ -125,7 +125,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       mbar_init(&s.p_ready[i][0], 4);
       mbar_init(&s.p_ready[i][1], 4);
       mbar_init(&s.o_done[i], 1);
-      for (int w = 0; w < 4; ++w) mbar_init(&s.exp_done[i][w], 1);  // exponential phase of block j over: one warp, phase j
     }
     mbar_init(&s.mma_drained, nb1 ? 2 : 1);
     s.abort_flag = 0;
@@ -279,7 +278,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
     // ---------------------------------------------------------------- softmax (warps 0-3: tile 0, warps 4-7: tile 1)
     const int ti = warp >> 2;
     const int nb = ti ? nb1 : nb0;
-    const int nb_other = ti ? nb0 : nb1;        // blocks of the CTA's other tile (0: there is none)
     const int qt = 2 * pi + ti;                 // global query tile
     const int row = (warp & 3) * 32 + lane;     // query row inside the tile = TMEM lane
     const uint32_t lane_base = tm + ((uint32_t)((warp & 3) * 32) << 16);
@@ -294,16 +292,12 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       tc_fence_after();
       uint32_t x[64];  // raw scores (FP32 bit patterns) of this row against the block's 64 keys
       {
-        uint32_t r0[32], r1[32];
+        uint32_t(&r0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&x[0]);
+        uint32_t(&r1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&x[32]);
         tmem_ld32(lane_base + kColS + 64 * ti, r0);
         tmem_ld32(lane_base + kColS + 64 * ti + 32, r1);
         tmem_ld_wait(r0);
         tmem_ld_wait(r1);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          x[i] = r0[i];
-          x[32 + i] = r1[i];
-        }
       }
       tc_fence_before();
       mbar_arrive_warp(&s.s_free[ti]);  // the next block's Q.K^T may overwrite S now
@@ -342,20 +336,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       const float f = moved ? ex2_approx(mhat - mnew) : 1.0f;
       if (__any_sync(0xffffffffu, moved)) lsum2 = mul2(lsum2, pack2(f, f));
       mhat = mnew;
-      // The two softmax warps of a scheduler (one per tile) share its exponential unit, and left alone they fall
-      // into step: both in their exponentials, then both in their loads, stores and waits.  They take turns
-      // instead -- tile 0's block j, tile 1's block j, tile 0's block j + 1, ... -- so that one warp's exponentials
-      // run under the other's remaining work (measured: 2 % of the kernel; a warp's 64 exponentials take about
-      // 700 cycles with or without the other warp's, and issuing all of them before any sum or conversion, or
-      // starting the second tile half a block late without the hand-over, changed nothing).
-      if (nb_other > 0) {
-        const int w4 = warp & 3;
-        if (ti == 0 ? (j > 0 && j - 1 < nb_other) : (j < nb_other)) {
-          const int ph = ti == 0 ? j - 1 : j;
-          ok = mbar_wait_warp(&s.exp_done[ti ^ 1][w4], ph & 1, &s.abort_flag, p.status, 33, j);
-          if (!ok) break;
-        }
-      }
       // P = 2^(x c2 - mhat + kLift): packed FMA for the exponent, the exponential unit or (6 of 16 columns) the FMA-pipe
       // polynomial for the power, packed add for the sum
       const uint64_t shift2 = pack2(kLift - mhat, kLift - mhat);
@@ -395,7 +375,6 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
           }
         }
       }
-      if (nb_other > 0) mbar_arrive_warp(&s.exp_done[ti][warp & 3]);
       uint32_t p_scales = 0;  // MXFP4 route: the block's two E8M0 bytes
       if constexpr (MX) {
         // MXFP4 of P in 32-key groups: e = ceil(log2 max), step d = 2^e / 6 = RN(4/3) 2^(e-3) and its correctly rounded

@@ -76,9 +76,8 @@ static __device__ __noinline__ bool mbar_wait_teardown(uint64_t* bar, uint32_t p
 // `limit`: the cycle budget of this wait (the kernels use the default; the wait self-test passes a short one)
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
                                           uint32_t where, uint32_t detail = 0, long long limit = kWaitLimitCycles) {
-#pragma unroll 1
-  for (int i = 0; i < 32; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+  // one try parks the thread until the phase completes (or 20 us pass), so the first one nearly always succeeds
+  if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, status, where, detail, limit);
 }
 
@@ -128,9 +127,7 @@ static __device__ __noinline__ bool mbar_wait_warp_slow(uint64_t* bar, uint32_t 
 }
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
                                                uint32_t where, uint32_t detail = 0, long long limit = kWaitLimitCycles) {
-#pragma unroll 1
-  for (int i = 0; i < 32; ++i)
-    if (mbar_try_wait_uniform(bar, parity)) return true;
+  if (mbar_try_wait_uniform(bar, parity)) return true;
   return mbar_wait_warp_slow(bar, parity, abort_flag, status, where, detail, limit);
 }
 // every lane must have issued its own fences before the call; the barrier counts one arrival per warp
