@@ -105,14 +105,15 @@ __host__ __device__ inline BwdItem bwd_item_of(int idx, int n_tiles, int chunk, 
 }
 // Query tiles per work item.  A launch of many (batch, kv head) units needs no cut: in key-tile-major order the long
 // key tiles start first and the short ones fill the tail (cutting costs 2 % there: more CTA set-ups, dK / dV through
-// FP32 sums).  With fewer than about six CTAs per SM the tiles are cut so that the launch has about eight items per
-// SM, at least two query tiles each (a shorter item is mostly set-up).
+// FP32 sums).  With fewer than about six CTAs per SM the tiles are cut so that the launch has about four items per
+// SM (measured best of 3, 4, 6, 8 and 12 on launches of 2, 4 and 8 units at S = 8192), at least two query tiles each
+// (a shorter item is mostly set-up).
 inline int bwd_chunk(const fa4b_attn_dims& d, int n_sm) {
   const long long n = d.S / 128;
   const long long heads = (long long)d.B * d.Hkv;
   if (heads * n >= 6ll * n_sm) return (int)n;
   const long long units = heads * (d.mask == FA4B_MASK_CAUSAL ? n * (n + 1) / 2 : n * n);
-  const long long want = (units + 8ll * n_sm - 1) / (8ll * n_sm);
+  const long long want = (units + 4ll * n_sm - 1) / (4ll * n_sm);
   return (int)std::min<long long>(std::max<long long>(want, 2), n);
 }
 

@@ -569,16 +569,31 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
   if (warp == 20) tmem_dealloc(tm, 512);
 }
 
-// out = bf16(accumulator / 1024) through the caller's strides, for the first `rows_per_head` rows of every head
+// out = bf16(accumulator / 1024) through the caller's strides, for the first `rows_per_head` rows of every head;
+// up to three accumulators (dQ, dK, dV) in one launch, each with its own range of CTAs
+struct ConvertJob {
+  const float* acc;
+  __nv_bfloat16* out;
+  int64_t sb, sh, ss;
+  int64_t n_rows;  // heads * rows_per_head
+  int H, rows_per_head;
+  unsigned first_cta, n_cta;
+};
+struct ConvertJobs {
+  ConvertJob job[3];
+  int n;
+};
 template <int D>
-__global__ void __launch_bounds__(256) accum_convert_kernel(const float* __restrict__ acc, int H, int S, int rows_per_head, int64_t n_rows,
-                                                            __nv_bfloat16* out, int64_t sb, int64_t sh, int64_t ss) {
+__global__ void __launch_bounds__(256) accum_convert_kernel(const ConvertJobs jobs, int S) {
   constexpr int kPerRow = D / 8;
-  for (int64_t c = (int64_t)blockIdx.x * 256 + threadIdx.x; c < n_rows * kPerRow; c += (int64_t)gridDim.x * 256) {
+  int which = 0;
+  while (which + 1 < jobs.n && blockIdx.x >= jobs.job[which + 1].first_cta) ++which;
+  const ConvertJob& jb = jobs.job[which];
+  for (int64_t c = (int64_t)(blockIdx.x - jb.first_cta) * 256 + threadIdx.x; c < jb.n_rows * kPerRow; c += (int64_t)jb.n_cta * 256) {
     const int64_t r = c / kPerRow;
     const int cb = (int)(c % kPerRow) * 8;
-    const int bh = (int)(r / rows_per_head), sidx = (int)(r % rows_per_head);
-    const float* src = acc + ((int64_t)bh * S + sidx) * D + cb;
+    const int bh = (int)(r / jb.rows_per_head), sidx = (int)(r % jb.rows_per_head);
+    const float* src = jb.acc + ((int64_t)bh * S + sidx) * D + cb;
     const float4 a = *reinterpret_cast<const float4*>(src), bq = *reinterpret_cast<const float4*>(src + 4);
     constexpr float inv = 1.0f / 1024.0f;
     const __nv_bfloat162 h0 = __floats2bfloat162_rn(a.x * inv, a.y * inv), h1 = __floats2bfloat162_rn(a.z * inv, a.w * inv);
@@ -588,18 +603,19 @@ __global__ void __launch_bounds__(256) accum_convert_kernel(const float* __restr
     o.y = *reinterpret_cast<const uint32_t*>(&h1);
     o.z = *reinterpret_cast<const uint32_t*>(&h2);
     o.w = *reinterpret_cast<const uint32_t*>(&h3);
-    *reinterpret_cast<uint4*>(out + (int64_t)(bh / H) * sb + (int64_t)(bh % H) * sh + (int64_t)sidx * ss + cb) = o;
+    *reinterpret_cast<uint4*>(jb.out + (int64_t)(bh / jb.H) * jb.sb + (int64_t)(bh % jb.H) * jb.sh + (int64_t)sidx * jb.ss + cb) = o;
   }
 }
 
 template <int D>
-static int convert_rows(const float* acc, int H, int S, int rows_per_head, int64_t n_heads, void* out, const fa4b_strides& st, cudaStream_t stream) {
+static void add_convert_job(ConvertJobs& jobs, const float* acc, int H, int rows_per_head, int64_t n_heads, void* out, const fa4b_strides& st) {
   const int64_t n_rows = n_heads * rows_per_head;
-  if (n_rows == 0) return FA4B_OK;
-  const unsigned grid = (unsigned)std::min<int64_t>((n_rows * (D / 8) + 255) / 256, (int64_t)std::max(sm_count(), 1) * 16);
-  accum_convert_kernel<D><<<grid, 256, 0, stream>>>(acc, H, S, rows_per_head, n_rows, static_cast<__nv_bfloat16*>(out), st.batch, st.head, st.seq);
-  FA4B_CUDA(cudaGetLastError());
-  return FA4B_OK;
+  if (n_rows == 0) return;
+  ConvertJob& jb = jobs.job[jobs.n];
+  jb = ConvertJob{acc, static_cast<__nv_bfloat16*>(out), st.batch, st.head, st.seq, n_rows, H, rows_per_head, 0, 0};
+  jb.first_cta = jobs.n ? jobs.job[jobs.n - 1].first_cta + jobs.job[jobs.n - 1].n_cta : 0;
+  jb.n_cta = (unsigned)std::min<int64_t>((n_rows * (D / 8) + 255) / 256, (int64_t)std::max(sm_count(), 1) * 16);
+  ++jobs.n;
 }
 
 template <int D>
@@ -662,12 +678,19 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   attn_bwd_kernel<D><<<grid, kBwdThreads, smem, st>>>(p, m_kc, m_k8, m_v8, m_qc, m_q8, m_do);
   FA4B_CUDA(cudaGetLastError());
   if (a.ev_after) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_after), st));
+  // one launch rounds what arrived as FP32 sums: dQ, and dK / dV of the key tiles that were cut
+  ConvertJobs jobs{};
+  if (!(a.flags & FA4B_BWD_SKIP_DQ_OUT)) add_convert_job<D>(jobs, p.dq_accum, d.Hq, d.S, (int64_t)nq, a.dq, a.dq_strides);
   if (split_rows) {
-    if (int s = convert_rows<D>(p.dk_accum, d.Hkv, d.S, split_rows, (int64_t)nk, a.dk, a.dk_strides, st)) return s;
-    if (int s = convert_rows<D>(p.dv_accum, d.Hkv, d.S, split_rows, (int64_t)nk, a.dv, a.dv_strides, st)) return s;
+    add_convert_job<D>(jobs, p.dk_accum, d.Hkv, split_rows, (int64_t)nk, a.dk, a.dk_strides);
+    add_convert_job<D>(jobs, p.dv_accum, d.Hkv, split_rows, (int64_t)nk, a.dv, a.dv_strides);
   }
-  if (a.flags & FA4B_BWD_SKIP_DQ_OUT) return FA4B_OK;
-  return convert_rows<D>(p.dq_accum, d.Hq, d.S, d.S, (int64_t)nq, a.dq, a.dq_strides, st);
+  if (jobs.n) {
+    const unsigned cgrid = jobs.job[jobs.n - 1].first_cta + jobs.job[jobs.n - 1].n_cta;
+    accum_convert_kernel<D><<<cgrid, 256, 0, st>>>(jobs, d.S);
+    FA4B_CUDA(cudaGetLastError());
+  }
+  return FA4B_OK;
 }
 
 static int check_out(const void* ptr, const fa4b_strides& s, const char* name) {
