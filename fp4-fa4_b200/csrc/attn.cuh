@@ -117,6 +117,15 @@ inline int bwd_chunk(const fa4b_attn_dims& d, int n_sm) {
   return (int)std::min<long long>(std::max<long long>(want, 2), n);
 }
 
+// (batch, kv head) units per launch group: as many as keep the group's FP32 dQ rows (Hq / Hkv query heads of S x D
+// floats per unit) within 72 MB, a little over half of the 126 MB L2 -- four units at S = 8192, D = 128, four query
+// heads per kv head
+inline int bwd_head_group(const fa4b_attn_dims& d) {
+  const long long per_unit = (long long)(d.Hq / d.Hkv) * d.S * d.D * 4;
+  const long long fit = (72ll << 20) / per_unit;
+  return (int)std::min<long long>(std::max<long long>(fit, 1), (long long)d.B * d.Hkv);
+}
+
 // base to which the layout's transient offsets apply: the caller's separate scratch buffer, or the workspace itself
 inline uint8_t* transient_base(const fa4b_attn_bwd_args& a, const fa4b_attn_ws_layout& l) {
   return a.scratch ? static_cast<uint8_t*>(a.scratch) - l.saved_total : static_cast<uint8_t*>(a.ws);

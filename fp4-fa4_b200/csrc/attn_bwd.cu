@@ -80,6 +80,7 @@ struct BwdParams {
   // work list: every key tile's query range is cut into parts of at most `chunk` query tiles
   int chunk;           // query tiles per work item
   int items_per_head;  // work items of one (batch, kv head)
+  int head_group;      // (batch, kv head) units whose items are launched side by side
   float* dk_accum;     // [B*Hkv, S, D] f32 each: sums of the parts of key tiles that were cut (zeroed before launch)
   float* dv_accum;
 };
@@ -90,13 +91,10 @@ __device__ __forceinline__ float ex2_approx_b(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// The drain warps' reductions go through the same load/store queue as every other warp of their scheduler;
-// 64 of them back to back fill it and the barrier polls, shared-memory accesses and MMA issues of the compute
-// and issuer warps wait behind them (poll latency 115-150 cycles against 16-35 on an idle SM).  So the drain
-// stops for about 60 cycles after every eighth reduction.  With one issuer warp the pauses were worth 10 %
-// (2.61 -> 2.35 ms at the benchmark shape, best at 90 cycles); with one issuer warp per stream they are worth
-// 2 % (2.24 -> 2.19 ms) and the drain itself is the longest loop of the CTA (poll, load, 64 reductions per
-// sub-tile), so longer or more frequent pauses cost time: 120 cycles 2.45 ms, after every 4th 2.64 ms.
+// The drain warps' reductions go through the same load/store queue as every other warp of their scheduler; 64 of
+// them back to back fill it, and the barrier polls, shared-memory accesses and MMA issues of the compute and issuer
+// warps wait behind them.  So the drain stops for about 60 cycles after every eighth reduction (a spin on the cycle
+// counter: a sleep or a chain of dependent shared-memory loads in its place was slower).
 __device__ __forceinline__ void drain_pause() {
   const long long t0 = clock64();
   while (clock64() - t0 < 60) {
@@ -127,16 +125,21 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
 
   const int n_tiles = p.S / 128;
-  // Work item = (key tile, part of the tile's query range, batch and kv head), key-tile-major: the key tiles that
-  // see the most query tiles start first, all heads of a tile side by side.  When the launch has few (batch, kv
-  // head) units a tile's query range is cut into parts of at most `chunk` query tiles, so that the work still
-  // spreads over every SM (kv-head-major order, which keeps a head's FP32 dQ rows in L2 while their partial sums
-  // arrive, measured 8 % slower at B2 Hkv8 S8192 and the same on a launch of two units: the reductions do not
-  // bound the kernel).
+  // Work item = (key tile, part of the tile's query range, batch and kv head).  The (batch, kv head) units run in
+  // groups of `head_group`: inside a group the order is key-tile-major -- the key tiles that see the most query
+  // tiles start first, the group's heads side by side -- and the group is small enough that the FP32 dQ rows its
+  // CTAs add into stay in L2 until their last partial sum has arrived (all heads at once evict and re-fetch every
+  // line several times; one head at a time was slower: its long key tiles start late).  When the launch has few
+  // units a tile's query range is cut into parts of at most `chunk` query tiles, so that the work still spreads
+  // over every SM.
   const int heads_kv = p.B * p.Hkv;
-  const BwdItem item = bwd_item_of((int)blockIdx.x / heads_kv, n_tiles, p.chunk, p.causal != 0);
+  const int per_group = p.items_per_head * p.head_group;
+  const int first_head = ((int)blockIdx.x / per_group) * p.head_group;
+  const int in_group = (int)blockIdx.x % per_group;
+  const int group_heads = min(p.head_group, heads_kv - first_head);  // the last group may be short
+  const BwdItem item = bwd_item_of(in_group / group_heads, n_tiles, p.chunk, p.causal != 0);
   const int kt = item.kt;
-  const int bhk = blockIdx.x % heads_kv;
+  const int bhk = first_head + in_group % group_heads;
   const int b = bhk / p.Hkv, hk = bhk % p.Hkv;
   const int G = p.Hq / p.Hkv;
   const int sub_per_tile = 128 / QT;
@@ -337,8 +340,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         __syncwarp();
         return true;
       };
-      // (One warp serving all streams as their events arrived left each compute group waiting behind the
-      // other's phase and the next S behind the wait for the dQ accumulator.)
       if (stream == 0) {
         for (int it = 0; ok && it < n_it; ++it) ok = pt_phase(it);
       } else if (stream == 1) {
@@ -360,10 +361,8 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     // ------------------------------------------------------------------ dQ drain (warps 16-19)
     // The partial dQ of a sub-tile leaves TMEM for registers and the accumulator is handed back to the
     // issuer at once; the FP32 reductions into the scratch accumulator then run beside the next
-    // sub-tile's MMAs.  (Staging the tile in shared memory for one bulk reduction was slower: with
-    // one 32 KB reduction in flight per SM the reductions ran at 2.4-2.7 TB/s, against 3.2 TB/s here.
-    // Software-pipelining this loop -- the next sub-tile's poll and first TMEM load between the two halves'
-    // reductions -- was slower too: 2.39 against 2.20 ms at the benchmark shape.)
+    // sub-tile's MMAs (staging the tile in shared memory for one bulk reduction, or software-pipelining this
+    // loop, was slower).
     const int w4 = warp & 3;
     const uint32_t lane_base = tm + ((uint32_t)(w4 * 32) << 16);
     const int r = w4 * 32 + lane;  // TMEM lane: d (D = 128) or query row (D = 64)
@@ -405,7 +404,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           for (int i = 0; i < 32; ++i) patch[lane * 33 + i] = __uint_as_float(v[i]);
           __syncwarp();
 #pragma unroll
-          for (int rr = 0; rr < 32; ++rr) atomicAdd(base + (size_t)(w4 * 32 + rr) * D + 32 * hh + lane, patch[rr * 33 + lane]);  // no pauses: at D = 64 the drain has no time to spare (pausing cost 23 %)
+          for (int rr = 0; rr < 32; ++rr) atomicAdd(base + (size_t)(w4 * 32 + rr) * D + 32 * hh + lane, patch[rr * 33 + lane]);  // no pauses: at D = 64 the drain has no time to spare
         }
       }
     }
@@ -654,6 +653,7 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   const int n_tiles = d.S / 128;
   p.chunk = bwd_chunk(d, n_sm);
   p.items_per_head = bwd_items_per_head(n_tiles, p.chunk, p.causal != 0);
+  p.head_group = bwd_head_group(d);
   // rows of every kv head whose key tiles are cut into parts (the tiles that see more than `chunk` query tiles):
   // their dK and dV arrive as FP32 sums
   const int split_rows = n_tiles > p.chunk ? (p.causal ? (n_tiles - p.chunk) * 128 : d.S) : 0;
@@ -736,6 +736,7 @@ extern "C" int fa4b_attn_bwd_plan(const fa4b_attn_dims* d, int32_t n_sm, fa4b_bw
   const bool causal = d->mask == FA4B_MASK_CAUSAL;
   out->chunk = bwd_chunk(*d, n_sm);
   out->items_per_head = bwd_items_per_head(n, out->chunk, causal);
+  out->head_group = bwd_head_group(*d);
   out->grid = (int64_t)d->B * d->Hkv * out->items_per_head;
   out->split_rows = n > out->chunk ? (causal ? (n - out->chunk) * 128 : d->S) : 0;
   return FA4B_OK;
@@ -747,8 +748,11 @@ extern "C" int fa4b_attn_bwd_plan_item(const fa4b_attn_dims* d, int32_t n_sm, in
   FA4B_REQUIRE(out != nullptr && index >= 0 && index < plan.grid, FA4B_BAD_ARG, "item index outside the launch's %lld work items",
                (long long)plan.grid);
   const int64_t heads = (int64_t)d->B * d->Hkv;
-  const BwdItem it = bwd_item_of((int)(index / heads), d->S / 128, plan.chunk, d->mask == FA4B_MASK_CAUSAL);
-  out[0] = (int32_t)(index % heads);
+  const int64_t per_group = (int64_t)plan.items_per_head * plan.head_group;
+  const int64_t first_head = index / per_group * plan.head_group, in_group = index % per_group;
+  const int64_t group_heads = std::min<int64_t>(plan.head_group, heads - first_head);
+  const BwdItem it = bwd_item_of((int)(in_group / group_heads), d->S / 128, plan.chunk, d->mask == FA4B_MASK_CAUSAL);
+  out[0] = (int32_t)(first_head + in_group % group_heads);
   out[1] = it.kt;
   out[2] = it.qt_lo;
   out[3] = it.qt_hi;

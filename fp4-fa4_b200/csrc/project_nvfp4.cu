@@ -10,11 +10,8 @@
 // apply the two global scales and store BF16 rows through small swizzled boxes and TMA stores, beside the next
 // tile's MMAs.
 //
-// Measured at [16384, 4096] x [6144, 4096]^T (launches back to back): 0.194 ms.  Variants that were slower:
-// K steps of 128 values in eight stages (0.29 ms: the issuer's per-stage work no longer fits under two MMAs);
-// three stages with larger store boxes (0.203 ms); four epilogue warps storing straight from registers, 16 bytes
-// per row and instruction (0.252 ms); the scale-page copies on a warp of their own (0.201 ms).  With parts
-// switched off: no scale-page copies -9 %, no accumulator read-out -17 %.
+// (K steps of 128 values in eight stages, three stages with larger store boxes, four epilogue warps storing straight
+// from registers, and scale-page copies on a warp of their own were all slower than this arrangement.)
 #include <algorithm>
 #include <mutex>
 
@@ -26,11 +23,8 @@
 
 namespace fa4b {
 
-#ifndef FA4B_PROJ_STEPK
-#define FA4B_PROJ_STEPK 256
-#endif
 constexpr int kProjThreads = 320;  // warp 0 producer, warp 1 issuer, warps 2-9 epilogue
-constexpr int kProjTileM = 128, kProjTileN = 256, kProjStepK = FA4B_PROJ_STEPK;
+constexpr int kProjTileM = 128, kProjTileN = 256, kProjStepK = 256;
 constexpr int kProjStages = kProjStepK == 256 ? 4 : 8;
 constexpr int kRowBytes = kProjStepK / 2;   // code bytes per row and stage: 128 (128-byte swizzle) or 64
 constexpr int kStepMmas = kProjStepK / 64;  // K64 MMAs, and scale pages per 128 rows, per stage

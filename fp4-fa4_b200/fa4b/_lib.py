@@ -92,7 +92,8 @@ class AttnBwdArgs(C.Structure):
 
 
 class BwdPlan(C.Structure):
-    _fields_ = [("chunk", C.c_int32), ("items_per_head", C.c_int32), ("split_rows", C.c_int32), ("grid", C.c_int64)]
+    _fields_ = [("chunk", C.c_int32), ("items_per_head", C.c_int32), ("split_rows", C.c_int32), ("head_group", C.c_int32),
+                ("grid", C.c_int64)]
 
 
 class Info(C.Structure):

@@ -394,14 +394,15 @@ int fa4b_attn_bwd(const fa4b_attn_bwd_args* a, void* stream);
 /* fa4b_attn_bwd_plan / _plan_item: host only.  The work list fa4b_attn_bwd launches for `d` on a device of n_sm
  * multiprocessors (n_sm <= 0: the current device): one CTA per item; items_per_head items per (batch, kv head):
  * the key tiles in order, each tile's query range in `parts` nearly equal pieces of at most `chunk` query tiles
- * (chunk = S / 128, i.e. no cut, when the launch has about six CTAs per SM without one).  Launch order is
- * key-tile-major: item i of every head, then item i + 1 of every head.  split_rows: leading key rows of every kv
+ * (chunk = S / 128, i.e. no cut, when the launch has about six CTAs per SM without one).  Launch order: the heads
+ * in groups of head_group (as many as keep the group's FP32 dQ rows within about half of L2); inside a group
+ * key-tile-major: item i of every head of the group, then item i + 1.  split_rows: leading key rows of every kv
  * head whose dK / dV pass through the FP32 accumulators.  Stands in for the grid half of
  * native_tk_d128_backward_metadata() (tk_fa4/native_gqa_tk_bwd/v509_*bshd.cu:446-522; grid at
  * v509_*bshd.cuh:1561-1565).  _plan_item writes {batch * Hkv + kv head, key tile, first query tile, end query
  * tile, parts} of the CTA with block index `index`. */
 typedef struct fa4b_bwd_plan {
-  int32_t chunk, items_per_head, split_rows;
+  int32_t chunk, items_per_head, split_rows, head_group;
   int64_t grid;
 } fa4b_bwd_plan;
 int fa4b_attn_bwd_plan(const fa4b_attn_dims* d, int32_t n_sm, fa4b_bwd_plan* out);

@@ -99,25 +99,25 @@ def test_attention_entry_points_reject_a_bad_workspace_before_any_launch():
 
 def test_backward_work_list_tiles_every_key_tile_once():
     """fa4b_attn_bwd_plan / _plan_item (host only): the items of a launch cover, for every (batch, kv head) and key
-    tile, the tile's query range exactly once, in parts no longer than the chunk, key tiles (then parts, then heads)
-    in launch order."""
+    tile, the tile's query range exactly once, in parts no longer than the chunk; launch order: groups of heads, inside
+    a group key tiles, then parts, then the group's heads."""
     h = _lib.lib()
     out = (C.c_int32 * 5)()
     for (B, Hkv, S, n_sm, mask) in ((2, 8, 8192, 148, 0), (1, 2, 8192, 148, 0), (1, 1, 256, 148, 0), (1, 2, 384, 148, 0),
                                     (1, 1, 1024, 148, 0), (1, 1, 512, 148, 1), (16, 8, 4096, 148, 0), (1, 1, 2048, 7, 1),
-                                    (1, 3, 1152, 33, 0)):
+                                    (1, 3, 1152, 33, 0), (1, 6, 8192, 148, 0)):  # the last: head groups of 4 and 2
         d = _lib.AttnDims(B, 4 * Hkv, Hkv, S, 128, 0.0, 0, mask, 0)
         p = _lib.BwdPlan()
         assert h.fa4b_attn_bwd_plan(C.byref(d), n_sm, C.byref(p)) == 0
         n = S // 128
-        assert p.grid == B * Hkv * p.items_per_head and 1 <= p.chunk <= n
+        assert p.grid == B * Hkv * p.items_per_head and 1 <= p.chunk <= n and 1 <= p.head_group <= B * Hkv
         cover, order = {}, []
         for i in range(p.grid):
             assert h.fa4b_attn_bwd_plan_item(C.byref(d), n_sm, i, out) == 0
             bhk, kt, lo, hi, parts = list(out)
             assert 0 < hi - lo <= p.chunk
             cover.setdefault((bhk, kt), []).append((lo, hi, parts))
-            order.append((kt, lo, bhk))
+            order.append((bhk // p.head_group, kt, lo, bhk))
         assert order == sorted(order) and len(cover) == B * Hkv * n
         for (bhk, kt), segs in cover.items():
             first = kt if mask == 0 else 0
@@ -128,7 +128,7 @@ def test_backward_work_list_tiles_every_key_tile_once():
     # the benchmark configuration on 148 SMs, and one eighth of it (what one of eight GPUs holds)
     p = _lib.BwdPlan()
     h.fa4b_attn_bwd_plan(C.byref(_lib.AttnDims(2, 32, 8, 8192, 128, 0.0, 0)), 148, C.byref(p))
-    assert (p.chunk, p.items_per_head, p.grid, p.split_rows) == (64, 64, 1024, 0)  # 6.9 CTAs per SM: no cut
+    assert (p.chunk, p.items_per_head, p.grid, p.split_rows, p.head_group) == (64, 64, 1024, 0, 4)  # 6.9 CTAs per SM: no cut; 4 x 16.8 MB of dQ rows per group
     h.fa4b_attn_bwd_plan(C.byref(_lib.AttnDims(1, 8, 2, 8192, 128, 0.0, 0)), 148, C.byref(p))
     assert (p.chunk, p.grid) == (8, 576)  # about four items per SM
 

@@ -169,7 +169,7 @@ def test_rope_pair_inverse_undoes_the_rotation_within_bf16_rounding():
 
 @pytest.mark.parametrize("shape,seed", [((128, 128), 11), ((256, 512), 12)])
 def test_nvfp4_encode_centric_recipe_matches_its_restatement(shape, seed):
-    # the TK quantiser's default recipe; its oracle is restated from the CUDA source only (parity unpinned)
+    # the TK quantiser's default recipe; its oracle is pinned by hand-worked known answers (tests/test_oracle_pins.py)
     x, gamma = O.make_quantizer_inputs(*shape, seed=seed)
     x[3, 16:32] = 0.0            # an all-zero block: multiplier 448, stored scale E4M3(1/448)
     x[7, :16] *= 1.0e-4          # a tiny block: the multiplier saturates at 448
@@ -189,6 +189,31 @@ def test_nvfp4_encode_centric_recipe_matches_its_restatement(shape, seed):
     # a zero tensor keeps the recipe's E4M3(1/448) scale bytes and zero codes
     z = fa4b.tk_quantize_for_gemm(torch.zeros(128, 128, dtype=torch.bfloat16, device=DEV), return_transpose=False, encode_centric=True)
     assert int(z[0].max()) == 0 and z[1].unique().tolist() == [1] and float(z[4]) == 0.0
+
+
+def test_nvfp4_encode_centric_kernel_on_the_blocks_worked_by_hand():
+    """The known-answer blocks of tests/test_oracle_pins.py (worked from core.cuh:47-60, 103-113 and
+    fused_amax_quantize.cuh:235-256 of the reference) through the kernel: scale bytes and codes as computed by hand,
+    row-wise and in the transposed output."""
+    x = torch.zeros(128, 128)
+    x[0, :16] = torch.tensor([6, -3, 1.5, 0.75, 0.25, 1.25, 1.75, 2.5, 3.5, 5, -0.75, -5, 0, 0.5, 2, 4])
+    x[0, 16:32] = torch.tensor([2688, 1024, 512, -2688] + [0] * 12)
+    x[0, 48:64] = torch.tensor([2.0 ** -10, -(2.0 ** -10), 2.0 ** -12] + [0] * 13)
+    x[1, :16] = torch.tensor([3, 0.375, 0.125, -0.375] + [0] * 12)
+    x[1, 16:32] = torch.tensor([5, 4, 1, 2, -4] + [0] * 11)
+    xb = x.bfloat16()
+    fp4_row, sc_row, fp4_col, sc_col, sg, am = fa4b.tk_quantize_for_gemm(xb.to(DEV), True, True)  # the reference's positional call
+    assert float(am) == 2688.0 and float(sg) == 1.0
+    codes = O.unpack_nibbles(fp4_row.cpu())
+    assert codes[0, :16].tolist() == [7, 13, 3, 2, 0, 2, 4, 4, 6, 6, 10, 14, 0, 1, 4, 6]
+    assert codes[0, 16:32].tolist() == [7, 4, 2, 15] + [0] * 12 and codes[0, 48:64].tolist() == [1, 9, 0] + [0] * 13
+    assert codes[1, :16].tolist() == [7, 2, 0, 10] + [0] * 12 and codes[1, 16:32].tolist() == [7, 6, 2, 4, 14] + [0] * 11
+    scales = O.pages_to_scales(sc_row.cpu())
+    assert scales[0, :4].tolist() == [0x38, 0x7E, 0x01, 0x01] and scales[1, :4].tolist() == [0x30, 0x35, 0x01, 0x01]
+    assert scales[2:].unique().tolist() == [0x01]  # all-zero blocks: E4M3(1 / 448)
+    ref_t = O.nvfp4_quantize_encode_centric(xb.t().contiguous())
+    _same(fp4_col, ref_t.codes, "transposed codes")
+    _same(sc_col, ref_t.pages(), "transposed scale pages")
 
 
 def _wide_range(M, K, seed, lo=-20, hi=20):
