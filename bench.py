@@ -312,6 +312,8 @@ def run_ours(args, rank, world, local_rank):
         init_nccl(device)
     B, Hq, Hkv, S, D = (WORKLOAD[k] for k in ("B", "Hq", "Hkv", "S", "D"))
     G = Hq // Hkv
+    # the launcher pins every rank to one host thread; generating the inputs may use this rank's share of the cores
+    torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))
     # ONE problem of the configured shape for the whole job, partitioned by (batch, kv head): every rank generates the
     # same global tensors from the same seed and keeps its own units; no collective on the data path
     host_global, _ = make_inputs(20260825, "cpu", pin=False)

@@ -142,7 +142,8 @@ int static_ws_pointer(void** out);
 void fill_kernel_info(fa4b_info* out);
 void fill_bwd_info(fa4b_info* out);
 
-int launch_attn_prepare(const fa4b_attn_prepare_args& a, cudaStream_t st);
+// skip_q: publish K and V only (the forward kernel quantises Q itself); the amax words of Q are still taken
+int launch_attn_prepare(const fa4b_attn_prepare_args& a, cudaStream_t st, bool skip_q = false);
 int launch_attn_fwd(const fa4b_attn_fwd_args& a, cudaStream_t st);
 int launch_attn_bwd_preprocess(const fa4b_attn_bwd_args& a, cudaStream_t st);
 int launch_attn_bwd(const fa4b_attn_bwd_args& a, cudaStream_t st);

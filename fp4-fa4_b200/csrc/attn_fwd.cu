@@ -39,6 +39,7 @@ struct FwdSmem {
   alignas(16) uint8_t k_sf[kStages][(D / 64) * 512];
   alignas(16) uint8_t v_sf[kStages][512];      // MXFP4 route: E8M0 page of the stage's V (row = feature)
   alignas(16) uint8_t p_sf[2][512];            // MXFP4 route: E8M0 page of the P block (row = query row)
+  StepTable steps;                             // in-kernel Q quantisation: division table of this head's global scale
   alignas(8) uint64_t q_full, kv_full[kStages], kv_empty[2][kStages], s_full[2], s_free[2], p_ready[2][2], o_done[2], mma_drained;
   uint32_t tmem_base;
   alignas(8) volatile uint32_t abort_flag;
@@ -58,6 +59,16 @@ struct FwdParams {
   int64_t o_sb, o_sh, o_ss;
   float* lse;
   uint32_t* status;
+  // Q quantised inside this kernel (non-NULL q_src): the bf16 queries through their strides, the per-head amax words
+  // (or a unit global scale), and where the operands go for the backward (the workspace's Q sections)
+  const __nv_bfloat16* q_src;
+  int64_t q_sb, q_sh, q_ss;
+  int* q_amax_bits;
+  int unit_global;
+  uint8_t* q_codes_out;
+  uint8_t* q_sf_out;
+  uint8_t* q_fp8_out;
+  float* q_global_out;
 };
 
 
@@ -113,7 +124,8 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
   }
 
   if (t == 0) {
-    mbar_init(&s.q_full, 1);
+    // Q operands: one transaction barrier for the producer's copies, or one arrival per softmax warp that quantises
+    mbar_init(&s.q_full, p.q_src ? (nb1 ? 8 : 4) : 1);
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&s.kv_full[i], 1);
       mbar_init(&s.kv_empty[0][i], 1);  // released by each tile's issuer separately
@@ -143,11 +155,13 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       tma_prefetch_desc(&map_k);
       tma_prefetch_desc(&map_v);
       const int nq = nb1 ? 2 : 1;
-      mbar_expect_tx(&s.q_full, nq * (128 * D / 2 + kPages * 512));
-      for (int i = 0; i < nq; ++i) {
-        const int qt = 2 * pi + i;
-        tma_load_3d(s.q_codes[i], &map_q, 0, qt * 128, bh, &s.q_full);
-        bulk_load(s.q_sf[i], p.q_sf + ((size_t)bh * n_tiles + qt) * kPages * 512, kPages * 512, &s.q_full);
+      if (!p.q_src) {  // published beforehand: codes and scale pages come by copy
+        mbar_expect_tx(&s.q_full, nq * (128 * D / 2 + kPages * 512));
+        for (int i = 0; i < nq; ++i) {
+          const int qt = 2 * pi + i;
+          tma_load_3d(s.q_codes[i], &map_q, 0, qt * 128, bh, &s.q_full);
+          bulk_load(s.q_sf[i], p.q_sf + ((size_t)bh * n_tiles + qt) * kPages * 512, kPages * 512, &s.q_full);
+        }
       }
       int issued = 0;
       for (int j = 0; j < n_stages; ++j) {
@@ -281,7 +295,70 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
     const int qt = 2 * pi + ti;                 // global query tile
     const int row = (warp & 3) * 32 + lane;     // query row inside the tile = TMEM lane
     const uint32_t lane_base = tm + ((uint32_t)((warp & 3) * 32) << 16);
-    const float c2 = p.scale_log2 * p.q_global[bh] * p.k_global[bhk];
+    float q_g = 0.f;
+    if (p.q_src) {
+      // ---- NVFP4 quantisation of this CTA's query rows, one row per thread (the softmax warps have nothing else to do
+      // until the first scores arrive): 16-element blocks along D, E4M3 block scale, FP32 global scale of the head;
+      // codes and scale pages go to shared memory in the layout the producer's copies would have left (and, with
+      // E4M3(4q), to the workspace for the backward).  The arithmetic is publish_heads_kernel's.
+      const float amax = p.unit_global ? kNvfp4GlobalDiv : __int_as_float(p.q_amax_bits[bh]);
+      q_g = amax / kNvfp4GlobalDiv;
+      const float inv6g = 1.0f / (6.0f * q_g);
+      const bool all_zero = !(amax > 0.f);
+      fill_step_table(s.steps, q_g, t);
+      asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight softmax warps
+      if (nb > 0) {
+        const int srow = qt * 128 + row;
+        const __nv_bfloat16* src = p.q_src + (int64_t)b * p.q_sb + (int64_t)h * p.q_sh + (int64_t)srow * p.q_ss;
+        const size_t row_index = (size_t)bh * p.S + srow;
+        uint32_t sw = 0;
+#pragma unroll
+        for (int kb = 0; kb < D / 16; ++kb) {
+          const uint4 lo = __ldg(reinterpret_cast<const uint4*>(src + kb * 16)), hi = __ldg(reinterpret_cast<const uint4*>(src + kb * 16) + 1);
+          const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+          uint64_t xp[8];
+          uint32_t m2 = 0;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            m2 = absmax_bf16x2(m2, w[k]);
+            xp[k] = bf16x2_to_f32x2(w[k]);
+          }
+          const float bamax = fmaxf(bf16_bits_to_f32(m2 & 0xffffu), bf16_bits_to_f32(m2 >> 16));
+          uint32_t c0 = 0, c1 = 0, sbyte = 0;
+          if (!all_zero) {
+            sbyte = nvfp4_scale_byte(bamax, q_g, inv6g);
+            nvfp4_codes16(xp, bamax, s.steps, sbyte, c0, c1);
+          }
+          *reinterpret_cast<uint2*>(&s.q_codes[ti][swizzled_offset((uint32_t)row, (uint32_t)kb * 8u, D / 2)]) = make_uint2(c0, c1);
+          *reinterpret_cast<uint2*>(p.q_codes_out + row_index * (D / 2) + kb * 8) = make_uint2(c0, c1);
+          sw |= sbyte << (8 * (kb & 3));
+          if ((kb & 3) == 3) {  // the four scale bytes of this row in one page are one aligned word
+            *reinterpret_cast<uint32_t*>(&s.q_sf[ti][(kb >> 2) * 512 + page_offset((uint32_t)row, 0)]) = sw;
+            *reinterpret_cast<uint32_t*>(p.q_sf_out + (((size_t)bh * n_tiles + qt) * kPages + (kb >> 2)) * 512 + page_offset((uint32_t)row, 0)) = sw;
+            sw = 0;
+          }
+          uint32_t o8[4];
+          const uint64_t four = pack2(4.f, 4.f);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            float a0, a1, b0, b1;
+            unpack2(mul2(xp[2 * k], four), a0, a1);
+            unpack2(mul2(xp[2 * k + 1], four), b0, b1);
+            o8[k] = cvt_e4m3x4(a0, a1, b0, b1);
+          }
+          *reinterpret_cast<uint4*>(p.q_fp8_out + row_index * D + kb * 16) = make_uint4(o8[0], o8[1], o8[2], o8[3]);
+        }
+        if (pi == 0 && ti == 0 && row == 0) {  // once per head
+          p.q_global_out[bh] = q_g;
+          if (p.unit_global) p.q_amax_bits[bh] = __float_as_int(kNvfp4GlobalDiv);
+        }
+        fence_async_smem();  // the tensor core reads these bytes through the async proxy
+        mbar_arrive_warp(&s.q_full);
+      }
+    } else {
+      q_g = p.q_global[bh];
+    }
+    const float c2 = p.scale_log2 * q_g * p.k_global[bhk];
     float mhat = -INFINITY;
     uint64_t lsum2 = pack2(0.f, 0.f);  // running row sum, as two partial sums
     const uint64_t c2c2 = pack2(c2, c2);
@@ -520,6 +597,14 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   p.o_sb = a.o_strides.batch; p.o_sh = a.o_strides.head; p.o_ss = a.o_strides.seq;
   p.lse = a.lse;
   p.status = reinterpret_cast<uint32_t*>(ws + l.status);
+  if (!a.prepared) {  // launch_attn_fwd has published K and V and taken the amax words; Q is quantised by the kernel
+    p.q_src = static_cast<const __nv_bfloat16*>(a.q);
+    p.q_sb = a.q_strides.batch; p.q_sh = a.q_strides.head; p.q_ss = a.q_strides.seq;
+    p.q_amax_bits = reinterpret_cast<int*>(ws + l.amax_bits);
+    p.unit_global = d.global_scale_mode == FA4B_GLOBAL_ONE;
+    p.q_codes_out = ws + l.q_codes; p.q_sf_out = ws + l.q_scales; p.q_fp8_out = ws + l.q_fp8;
+    p.q_global_out = reinterpret_cast<float*>(ws + l.q_global);
+  }
   FA4B_CUDA(cudaMemsetAsync(p.status, 0, 64, st));
   const int smem = (int)sizeof(FwdSmem<D>) + 1024;
   static std::mutex mu;
@@ -552,8 +637,9 @@ int launch_attn_fwd(const fa4b_attn_fwd_args& a, cudaStream_t st) {
                    a.o_strides.seq % 8 == 0,
                FA4B_BAD_ALIGN, "o: base must be 16-byte aligned and strides multiples of 8 elements");
   if (!a.prepared) {
+    // amax of Q and K (per-head recipe) and the publication of K and V; the forward kernel quantises Q itself
     fa4b_attn_prepare_args pa{a.dims, a.q, a.q_strides, a.k, a.k_strides, a.v, a.v_strides, a.ws};
-    if (int s = launch_attn_prepare(pa, st)) return s;
+    if (int s = launch_attn_prepare(pa, st, /*skip_q=*/true)) return s;
   }
   if (a.dims.pv_format == FA4B_PV_MXFP4_E8M0) return a.dims.D == 128 ? fwd_impl<128, true>(a, st) : fwd_impl<64, true>(a, st);
   return a.dims.D == 128 ? fwd_impl<128, false>(a, st) : fwd_impl<64, false>(a, st);

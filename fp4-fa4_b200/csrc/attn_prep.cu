@@ -351,7 +351,7 @@ static HeadView view(const void* p, const fa4b_strides& s, int H) {
 }
 
 template <int D>
-static int prepare_impl(const fa4b_attn_prepare_args& a, cudaStream_t st) {
+static int prepare_impl(const fa4b_attn_prepare_args& a, cudaStream_t st, bool skip_q) {
   const fa4b_attn_dims& d = a.dims;
   const fa4b_attn_ws_layout l = make_ws_layout(d);
   uint8_t* ws = static_cast<uint8_t*>(a.ws);
@@ -381,7 +381,8 @@ static int prepare_impl(const fa4b_attn_prepare_args& a, cudaStream_t st) {
   // one publication launch: Q and K codes, pages, global scales and E4M3 copies, and E4M3 V.  With a unit global
   // scale and phase ALL this is the only launch in front of the forward kernel.
   const bool unit_here = unit && a.phase == FA4B_PREPARE_ALL;
-  publish_heads_kernel<D><<<dim3(d.S / 128, nq + nk + (mx ? 0 : nk)), 256, 0, st>>>(sq, sk, sv, nq, nk, d.S, unit_here ? 1 : 0);
+  const int nq_pub = skip_q ? 0 : nq;  // the kernel numbers its CTAs Q heads, K heads, V heads
+  publish_heads_kernel<D><<<dim3(d.S / 128, nq_pub + nk + (mx ? 0 : nk)), 256, 0, st>>>(sq, sk, sv, nq_pub, nk, d.S, unit_here ? 1 : 0);
   FA4B_CUDA(cudaGetLastError());
   if (mx) {
     // the V section of the cache holds the MXFP4 codes, then (1024-aligned) the scale pages
@@ -391,7 +392,7 @@ static int prepare_impl(const fa4b_attn_prepare_args& a, cudaStream_t st) {
   return FA4B_OK;
 }
 
-int launch_attn_prepare(const fa4b_attn_prepare_args& a, cudaStream_t st) {
+int launch_attn_prepare(const fa4b_attn_prepare_args& a, cudaStream_t st, bool skip_q) {
   if (int s = check_dims(a.dims)) return s;
   if (int s = check_view(a.q, a.q_strides, "q")) return s;
   if (int s = check_view(a.k, a.k_strides, "k")) return s;
@@ -399,7 +400,7 @@ int launch_attn_prepare(const fa4b_attn_prepare_args& a, cudaStream_t st) {
   FA4B_REQUIRE(a.phase >= FA4B_PREPARE_ALL && a.phase <= FA4B_PREPARE_QUANTIZE, FA4B_BAD_ARG, "unknown prepare phase %d", a.phase);
   FA4B_REQUIRE(a.ws != nullptr && (reinterpret_cast<uintptr_t>(a.ws) & 1023) == 0, FA4B_BAD_ALIGN,
                "workspace must be non-NULL and 1024-byte aligned");
-  return a.dims.D == 128 ? prepare_impl<128>(a, st) : prepare_impl<64>(a, st);
+  return a.dims.D == 128 ? prepare_impl<128>(a, st, skip_q) : prepare_impl<64>(a, st, skip_q);
 }
 
 template <int D>

@@ -309,8 +309,11 @@ int fa4b_attn_prepare(const fa4b_attn_prepare_args* a, void* stream);
 /* fa4b_attn_fwd: O and LSE (natural log, [B,Hq,S] f32).  Replaces
  * forward_hao_direct_fp8pv / forward_hao_direct_fp4pv
  * (tk_fa4/fp4_fa4_fwd/hao_direct_host.inc:263-275, 511-521;
- * hao_direct_fp4pv_host.inc:1141-1237).  Calls fa4b_attn_prepare first unless
- * `prepared` is non-zero.  The MXFP4 P.V route quantises P to MXFP4 in 32-key groups (E8M0, ceil) inside the
+ * hao_direct_fp4pv_host.inc:1141-1237).  Unless `prepared` is non-zero the call
+ * publishes the operands itself: one statistics launch for the per-head amax of Q and K (none at the unit global
+ * scale), one launch that publishes K and V, and the forward kernel quantises its own query rows to NVFP4 (16-element
+ * blocks, E4M3 block scales, the head's FP32 global scale) before its first Q.K^T, leaving codes, scale pages and
+ * E4M3(4q) in `ws` for the backward -- byte for byte what fa4b_attn_prepare writes.  The MXFP4 P.V route quantises P to MXFP4 in 32-key groups (E8M0, ceil) inside the
  * kernel, takes the row sum over the represented P, and is forward only (fa4b_attn_bwd returns FA4B_UNSUPPORTED). */
 typedef struct fa4b_attn_fwd_args {
   fa4b_attn_dims dims;
