@@ -312,9 +312,12 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         const __nv_bfloat16* src = p.q_src + (int64_t)b * p.q_sb + (int64_t)h * p.q_sh + (int64_t)srow * p.q_ss;
         const size_t row_index = (size_t)bh * p.S + srow;
         uint32_t sw = 0;
+        uint4 raw[D / 8];  // the whole row in flight before the first block is worked on
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) raw[c] = __ldg(reinterpret_cast<const uint4*>(src) + c);
 #pragma unroll
         for (int kb = 0; kb < D / 16; ++kb) {
-          const uint4 lo = __ldg(reinterpret_cast<const uint4*>(src + kb * 16)), hi = __ldg(reinterpret_cast<const uint4*>(src + kb * 16) + 1);
+          const uint4 lo = raw[2 * kb], hi = raw[2 * kb + 1];
           const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
           uint64_t xp[8];
           uint32_t m2 = 0;
