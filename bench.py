@@ -80,15 +80,32 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle samples during the timed region (read-only)."""
+    """SM clock and throttle-reason samples during the timed region (read-only NVML queries every
+    10 ms from a host thread; nvidia-smi every 100 ms when the NVML binding is missing)."""
 
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.nvml, self.stop_flag = index, [], None, None, threading.Event()
+
+    def _nvml_handle(self):
+        import pynvml as N
+
+        N.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+        uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        return N, N.nvmlDeviceGetHandleByUUID(uuid)
 
     def start(self):
+        try:
+            self.nvml = self._nvml_handle()
+            self.nvml[0].nvmlDeviceGetClockInfo(self.nvml[1], self.nvml[0].NVML_CLOCK_SM)
+            threading.Thread(target=self._poll, daemon=True).start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -96,22 +113,39 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        N, h = self.nvml
+        bits = (N.nvmlClocksEventReasonHwSlowdown, N.nvmlClocksEventReasonHwThermalSlowdown,
+                N.nvmlClocksEventReasonSwThermalSlowdown, N.nvmlClocksEventReasonSwPowerCap)
+        top = N.nvmlDeviceGetMaxClockInfo(h, N.NVML_CLOCK_SM)
+        while not self.stop_flag.is_set():
+            try:
+                mask = N.nvmlDeviceGetCurrentClocksEventReasons(h)
+                self.rows.append([str(N.nvmlDeviceGetClockInfo(h, N.NVML_CLOCK_SM)), str(top)] +
+                                 ["active" if mask & b else "not active" for b in bits])
+            except Exception:
+                pass
+            time.sleep(0.01)
+
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
+        if self.nvml is None and self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source available"]}
+        if self.nvml is not None:
+            self.stop_flag.set()
+        else:
+            time.sleep(0.15)
+            self.proc.terminate()
         rows = [r for r in self.rows if len(r) >= 6 and r[0].isdigit()]
         if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         sm = sorted(int(r[0]) for r in rows)
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows)}
+        reasons = [n for i, n in enumerate(self.NAMES) if any(r[2 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows),
+                "source": "nvml, 10 ms" if self.nvml is not None else "nvidia-smi, 100 ms"}
 
 
 def make_inputs(seed, device, pin=False):

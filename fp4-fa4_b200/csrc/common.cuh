@@ -53,11 +53,20 @@ __device__ __forceinline__ uint32_t cvt_e5m2x2(float lo, float hi) {
   asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
   return r;
 }
+// four f32 -> four bytes of one register (a in bits 0-7): the two conversions write its halves, nothing merges them afterwards
 __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
-  return cvt_e4m3x2(a, b) | (cvt_e4m3x2(c, d) << 16);
+  uint32_t r;
+  asm("{ .reg .b16 lo, hi; cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1; cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3; mov.b32 %0, {lo, hi}; }"
+      : "=r"(r)
+      : "f"(a), "f"(b), "f"(c), "f"(d));
+  return r;
 }
 __device__ __forceinline__ uint32_t cvt_e5m2x4(float a, float b, float c, float d) {
-  return cvt_e5m2x2(a, b) | (cvt_e5m2x2(c, d) << 16);
+  uint32_t r;
+  asm("{ .reg .b16 lo, hi; cvt.rn.satfinite.e5m2x2.f32 lo, %2, %1; cvt.rn.satfinite.e5m2x2.f32 hi, %4, %3; mov.b32 %0, {lo, hi}; }"
+      : "=r"(r)
+      : "f"(a), "f"(b), "f"(c), "f"(d));
+  return r;
 }
 __device__ __forceinline__ float e4m3_to_f32(uint32_t byte) {
   uint32_t h2;
@@ -180,26 +189,35 @@ __device__ __forceinline__ float absmax3(float m, uint64_t pair) {
   asm("{ .reg .f32 aa, bb; abs.f32 aa, %2; abs.f32 bb, %3; max.f32 %0, %1, aa, bb; }" : "=f"(r) : "f"(m), "f"(a), "f"(b));
   return r;
 }
+// four packed f32 pairs -> eight E2M1 codes in one word (element 0 in the low nibble of byte 0); the four
+// conversions write the bytes of one register, so no masks or merges follow them
+__device__ __forceinline__ uint32_t e2m1_pack8(uint64_t q0, uint64_t q1, uint64_t q2, uint64_t q3) {
+  uint32_t r;
+  asm("{ .reg .b8 t0, t1, t2, t3; .reg .f32 a0, a1, b0, b1, c0, c1, d0, d1;\n\t"
+      "mov.b64 {a0, a1}, %1; mov.b64 {b0, b1}, %2; mov.b64 {c0, c1}, %3; mov.b64 {d0, d1}, %4;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t0, a1, a0;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t1, b1, b0;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t2, c1, c0;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t3, d1, d0;\n\t"
+      "mov.b32 %0, {t0, t1, t2, t3}; }"
+      : "=r"(r)
+      : "l"(q0), "l"(q1), "l"(q2), "l"(q3));
+  return r;
+}
 // eight packed f32 pairs -> sixteen E2M1 codes (two words)
 __device__ __forceinline__ void e2m1_pack16(const uint64_t (&q)[8], uint32_t& lo, uint32_t& hi) {
-  uint32_t b[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    float a, c;
-    unpack2(q[i], a, c);
-    b[i] = cvt_e2m1x2(a, c);
-  }
-  // byte merges as permutes: three operations per word
-  lo = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
-  hi = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
+  lo = e2m1_pack8(q[0], q[1], q[2], q[3]);
+  hi = e2m1_pack8(q[4], q[5], q[6], q[7]);
 }
 // NVFP4 scale byte E4M3(clamp(bamax / 6 / g)) from one multiplication by inv6g ~ 1 / (6 g).  The
 // product is within 3 ulp of the twice-rounded quotient; every E4M3 rounding boundary has zero low
 // 19 significand bits, so a product more than 16 ulp away from such a pattern rounds to the same
-// byte, and the rare closer one takes the two divisions.
+// byte, and the rare closer one takes the two divisions.  A zero (or vanishing) product is byte 0
+// either way and stays on the short path: all-zero blocks are common.
 __device__ __forceinline__ uint32_t nvfp4_scale_byte(float bamax, float g, float inv6g) {
   float s = bamax * inv6g;
-  if (((__float_as_uint(s) + 16u) & 0x7FFFFu) <= 32u) s = (bamax / 6.0f) / g;
+  const uint32_t u = __float_as_uint(s) + 16u;
+  if ((u & 0x7FFFFu) <= 32u && u > 32u) s = (bamax / 6.0f) / g;
   return cvt_e4m3x2(s, 0.f) & 0xffu;
 }
 // per-tensor table over the 127 scale bytes: step d = max(E4M3(byte) g, FLT_MIN) and r = RN(1 / d)
@@ -241,12 +259,28 @@ __device__ __forceinline__ void nvfp4_codes16(const uint64_t (&x)[8], float bama
 // Encode-centric recipe of the TK quantiser (TK_quantisation/nvfp4_v6/core.cuh:47-60, 86-101;
 // fused_amax_quantize.cuh:235-256): the block's multiplier M = E4M3(6 / (bamax * S_enc)) is what is rounded, the
 // stored scale is E4M3(1 / M), and every element is one multiplication by M * S_enc before the E2M1 rounding.
-__device__ __forceinline__ void nvfp4_codes16_encode(const uint64_t (&x)[8], float bamax, float s_enc, uint32_t& sb, uint32_t& lo, uint32_t& hi) {
-  const uint32_t mbyte = bamax <= 1.0e-9f ? 0x7eu : (cvt_e4m3x2(fminf(6.0f / (bamax * s_enc), 3.4028235e38f), 0.f) & 0xffu);
-  const float m = e4m3_to_f32(mbyte);
-  const float coeff = m * s_enc;
-  sb = cvt_e4m3x2(1.0f / m, 0.f) & 0xffu;
-  const uint64_t c2 = pack2(coeff, coeff);
+// Per-tensor table over the 127 multiplier bytes: .x = M * S_enc, .y = the stored scale byte (as an integer's bits).
+struct EncodeTable {
+  float2 e[128];
+};
+__device__ __forceinline__ void fill_encode_table(EncodeTable& tab, float s_enc, int t) {
+  if (t < 128) {
+    const float m = (t < 127) ? e4m3_to_f32((uint32_t)t) : 0.f;
+    tab.e[t] = make_float2(m * s_enc, __uint_as_float(cvt_e4m3x2(1.0f / m, 0.f) & 0xffu));
+  }
+}
+// The multiplier byte from an approximate quotient (two instructions, within 2 ulp for the magnitudes a block can
+// have); the quotient that lands within 16 ulp of an E4M3 rounding boundary (zero low 19 bits) is divided properly.
+__device__ __forceinline__ void nvfp4_codes16_encode(const uint64_t (&x)[8], float bamax, float s_enc, const EncodeTable& tab, uint32_t& sb,
+                                                     uint32_t& lo, uint32_t& hi) {
+  const float v = bamax * s_enc;
+  float u = fminf(__fdividef(6.0f, v), 3.4028235e38f);
+  const uint32_t ub = __float_as_uint(u) + 16u;
+  if ((ub & 0x7FFFFu) <= 32u || !(v >= 1.0e-30f)) u = fminf(6.0f / v, 3.4028235e38f);
+  const uint32_t mbyte = bamax <= 1.0e-9f ? 0x7eu : (cvt_e4m3x2(u, 0.f) & 0xffu);
+  const float2 e = tab.e[mbyte];
+  sb = __float_as_uint(e.y);
+  const uint64_t c2 = pack2(e.x, e.x);
   uint64_t q[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) q[i] = mul2(x[i], c2);

@@ -261,13 +261,14 @@ struct Nvfp4Params {
 // W2D: one scale per 16 x 16 tile (learned projection weights): every 1 x 16 group of the tile, in either
 // orientation, carries the scale of the tile's amax, so the transposed output is the byte-for-byte transpose of
 // the row-wise one.
-template <bool NORM, bool COL, bool W2D = false>
+template <bool NORM, bool COL, bool W2D = false, bool ENC = false>
 __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
   __shared__ __align__(16) __nv_bfloat16 tile[kTile * kPitch];
   __shared__ __align__(16) uint8_t sc_row[2 * 512];
   __shared__ __align__(16) uint8_t sc_col[COL ? 2 * 512 : 16];
   __shared__ __align__(16) uint8_t cb_col[COL ? kTile * 80 : 16];  // [128 columns][64 code bytes + pad]
-  __shared__ StepTable steps;
+  __shared__ StepTable steps;       // decode-centric recipes: division table of this tensor's global scale
+  __shared__ EncodeTable enc_steps;  // encode-centric recipe: multiplier table
   __shared__ float tile_amax[W2D ? 64 : 1];
 
   const int t = threadIdx.x;
@@ -276,13 +277,14 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
   const int64_t row0 = (int64_t)(gridDim.y - 1 - blockIdx.y) * kTile, col0 = (int64_t)(gridDim.x - 1 - blockIdx.x) * kTile;
   const float amax = *p.amax;
   const float g = amax / kNvfp4GlobalDiv;
-  const float inv6g = 1.0f / (6.0f * g);
+  const bool all_zero = !(amax > 0.f);
+  const float inv6g = all_zero ? 0.f : 1.0f / (6.0f * g);  // an all-zero tensor: every scale byte and code 0
   // encode-centric recipe: S_enc = 2688 / amax, 1 for an all-zero tensor (core.cuh:103-113)
-  const bool enc = !W2D && p.recipe == FA4B_RECIPE_ENCODE_CENTRIC;
   float s_enc = fminf(kNvfp4GlobalDiv / amax, 3.4028235e38f);
   if (amax == 0.f || s_enc == 0.f) s_enc = 1.0f;
   if (blockIdx.x == 0 && blockIdx.y == 0 && t == 0) *p.global_scale = g;
-  fill_step_table(steps, g, t);
+  if (ENC) fill_encode_table(enc_steps, s_enc, t);
+  else fill_step_table(steps, g, t);
 
   // ---- stage the tile (and apply the norm) -------------------------------------
 #pragma unroll
@@ -325,7 +327,6 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
     __syncthreads();
   }
 
-  const bool all_zero = !(amax > 0.f);
   // ---- row-wise 1x16 blocks: 512 segments of two blocks, two segments per thread -----------
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -349,10 +350,10 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
       }
       const int kb = (c32 >> 4) + h;
       const float bamax = W2D ? tile_amax[(r >> 4) * 8 + kb] : m;
-      uint32_t sbyte = 0;
-      if (enc) {
-        nvfp4_codes16_encode(x, bamax, s_enc, sbyte, codes[2 * h], codes[2 * h + 1]);
-      } else if (!all_zero) {
+      uint32_t sbyte;
+      if (ENC) {
+        nvfp4_codes16_encode(x, bamax, s_enc, enc_steps, sbyte, codes[2 * h], codes[2 * h + 1]);
+      } else {
         sbyte = nvfp4_scale_byte(bamax, g, inv6g);
         nvfp4_codes16(x, bamax, steps, sbyte, codes[2 * h], codes[2 * h + 1]);
       }
@@ -379,10 +380,10 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
           if (!W2D) m = absmax3(m, x[k]);
         }
         const float bamax = W2D ? tile_amax[rb * 8 + (c >> 4)] : m;
-        uint32_t lo = 0, hi = 0, sbyte = 0;
-        if (enc) {
-          nvfp4_codes16_encode(x, bamax, s_enc, sbyte, lo, hi);
-        } else if (!all_zero) {
+        uint32_t lo, hi, sbyte;
+        if (ENC) {
+          nvfp4_codes16_encode(x, bamax, s_enc, enc_steps, sbyte, lo, hi);
+        } else {
           sbyte = nvfp4_scale_byte(bamax, g, inv6g);
           nvfp4_codes16(x, bamax, steps, sbyte, lo, hi);
         }
@@ -538,6 +539,14 @@ static int launch_nvfp4(const Nvfp4Params& p, bool norm, cudaStream_t st, bool w
   if (weight_tiles) {
     if (col) nvfp4_tile_kernel<false, true, true><<<grid, 256, 0, st>>>(p);
     else nvfp4_tile_kernel<false, false, true><<<grid, 256, 0, st>>>(p);
+  } else if (p.recipe == FA4B_RECIPE_ENCODE_CENTRIC) {
+    if (norm) {
+      if (col) nvfp4_tile_kernel<true, true, false, true><<<grid, 256, 0, st>>>(p);
+      else nvfp4_tile_kernel<true, false, false, true><<<grid, 256, 0, st>>>(p);
+    } else {
+      if (col) nvfp4_tile_kernel<false, true, false, true><<<grid, 256, 0, st>>>(p);
+      else nvfp4_tile_kernel<false, false, false, true><<<grid, 256, 0, st>>>(p);
+    }
   } else if (norm) {
     if (col) nvfp4_tile_kernel<true, true><<<grid, 256, 0, st>>>(p);
     else nvfp4_tile_kernel<true, false><<<grid, 256, 0, st>>>(p);
