@@ -256,13 +256,68 @@ struct Nvfp4Params {
   uint8_t* codes_col;
   uint8_t* scales_col;
   int recipe;  // FA4B_RECIPE_*
+  // GRADS staging: columns [0, n0) come from x, [n0, n1) from x1, [n1, cols) from x2 (each with its own row stride); the
+  // first two ranges are heads of D features that turn back through the rotation of row % S
+  const __nv_bfloat16* x1;
+  const __nv_bfloat16* x2;
+  int64_t ld1, ld2, n0, n1;
+  const __nv_bfloat16* rope_cos;
+  const __nv_bfloat16* rope_sin;
+  int S, D;
 };
+
+// One bf16 pair (x, y) turned by the angle of (cos, sin) in packed bf16 arithmetic, out = fma(perp, sin, mul(pair, cos))
+// with perp = (-y, x): the numbers of apply_rope_pair (tk_fa4/lowp_fa4_bwd/projection_fp4_epilogue.cuh:447-479).
+__device__ __forceinline__ uint32_t rope_word(uint32_t w, uint32_t c16, uint32_t s16) {
+  const uint32_t cc = c16 * 0x00010001u, s2 = s16 * 0x00010001u;
+  const uint32_t perp = ((w << 16) | (w >> 16)) ^ 0x00008000u;
+  const __nv_bfloat162 r = __hfma2(*reinterpret_cast<const __nv_bfloat162*>(&perp), *reinterpret_cast<const __nv_bfloat162*>(&s2),
+                                   __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&w), *reinterpret_cast<const __nv_bfloat162*>(&cc)));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+// Eight gradient features of (row, col) of the [dQ | dK | dV] matrix, dQ and dK turned back through the rotation.
+__device__ __forceinline__ uint4 load_grad_chunk(const Nvfp4Params& p, int64_t row, int64_t col) {
+  const __nv_bfloat16* src = col < p.n0 ? p.x + row * p.ld + col : (col < p.n1 ? p.x1 + row * p.ld1 + (col - p.n0) : p.x2 + row * p.ld2 + (col - p.n1));
+  uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+  if (col < p.n1) {
+    const int s = (int)(row % p.S), d8 = (int)((col < p.n0 ? col : col - p.n0) % p.D) >> 3;
+    const uint2 cv = __ldg(reinterpret_cast<const uint2*>(p.rope_cos + (int64_t)s * (p.D / 2) + d8 * 4));
+    const uint2 sv = __ldg(reinterpret_cast<const uint2*>(p.rope_sin + (int64_t)s * (p.D / 2) + d8 * 4));
+    v.x = rope_word(v.x, cv.x & 0xffffu, (sv.x & 0xffffu) ^ 0x8000u);
+    v.y = rope_word(v.y, cv.x >> 16, (sv.x >> 16) ^ 0x8000u);
+    v.z = rope_word(v.z, cv.y & 0xffffu, (sv.y & 0xffffu) ^ 0x8000u);
+    v.w = rope_word(v.w, cv.y >> 16, (sv.y >> 16) ^ 0x8000u);
+  }
+  return v;
+}
+
+// amax of the rotated gradient matrix (the values the tile kernel will stage), eight features per thread and step
+__global__ void __launch_bounds__(256) grads_amax_kernel(const Nvfp4Params p, float* __restrict__ amax) {
+  const int64_t per_row = p.cols / 8, n_chunks = p.rows * per_row;
+  __nv_bfloat162 acc = __float2bfloat162_rn(0.f);
+  for (int64_t c = (int64_t)blockIdx.x * 256 + threadIdx.x; c < n_chunks; c += (int64_t)gridDim.x * 256) {
+    const uint4 v = load_grad_chunk(p, c / per_row, (c % per_row) * 8);
+    acc = absmax2(absmax2(absmax2(absmax2(acc, v.x), v.y), v.z), v.w);
+  }
+  float m = warp_max(fmaxf(__bfloat162float(acc.x), __bfloat162float(acc.y)));
+  __shared__ float wm[8];
+  if ((threadIdx.x & 31) == 0) wm[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    m = warp_max(threadIdx.x < 8 ? wm[threadIdx.x] : 0.f);
+    if (threadIdx.x == 0) atomicMax(reinterpret_cast<int*>(amax), __float_as_int(m));
+  }
+}
 
 // W2D: one scale per 16 x 16 tile (learned projection weights): every 1 x 16 group of the tile, in either
 // orientation, carries the scale of the tile's amax, so the transposed output is the byte-for-byte transpose of
 // the row-wise one.
-template <bool NORM, bool COL, bool W2D = false, bool ENC = false>
+// STAGE: what the tile is as it lands in shared memory -- the matrix itself, the RMSNorm of it, or the
+// [dQ | dK | dV] gradient matrix gathered from three tensors with the inverse rotation applied.
+enum { kStagePlain = 0, kStageNorm = 1, kStageGrads = 2 };
+template <int STAGE, bool COL, bool W2D = false, bool ENC = false>
 __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
+  constexpr bool NORM = STAGE == kStageNorm;
   __shared__ __align__(16) __nv_bfloat16 tile[kTile * kPitch];
   __shared__ __align__(16) uint8_t sc_row[2 * 512];
   __shared__ __align__(16) uint8_t sc_col[COL ? 2 * 512 : 16];
@@ -291,7 +346,7 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
   for (int i = 0; i < 8; ++i) {
     const int chunk = t + i * 256;  // 2048 chunks of 8 bf16
     const int r = chunk >> 4, c8 = (chunk & 15) * 8;
-    uint4 v = __ldg(reinterpret_cast<const uint4*>(p.x + (row0 + r) * p.ld + col0 + c8));
+    uint4 v = STAGE == kStageGrads ? load_grad_chunk(p, row0 + r, col0 + c8) : __ldg(reinterpret_cast<const uint4*>(p.x + (row0 + r) * p.ld + col0 + c8));
     if (NORM) {
       const float inv = __ldg(p.inv_rms + row0 + r);
       const uint4 gv = __ldg(reinterpret_cast<const uint4*>(p.gamma + col0 + c8));
@@ -503,6 +558,17 @@ static int check_matrix(const void* x, int64_t rows, int64_t cols, int64_t ld) {
 
 using namespace fa4b;
 
+template <int STAGE, bool W2D>
+static void launch_nvfp4_stage(const Nvfp4Params& p, dim3 grid, cudaStream_t st) {
+  const bool col = p.codes_col != nullptr, enc = !W2D && p.recipe == FA4B_RECIPE_ENCODE_CENTRIC;
+  if (col) {
+    if (enc) nvfp4_tile_kernel<STAGE, true, W2D, !W2D><<<grid, 256, 0, st>>>(p);
+    else nvfp4_tile_kernel<STAGE, true, W2D, false><<<grid, 256, 0, st>>>(p);
+  } else {
+    if (enc) nvfp4_tile_kernel<STAGE, false, W2D, !W2D><<<grid, 256, 0, st>>>(p);
+    else nvfp4_tile_kernel<STAGE, false, W2D, false><<<grid, 256, 0, st>>>(p);
+  }
+}
 extern "C" {
 
 const char* fa4b_last_error(void) { return fa4b::last_error(); }
@@ -533,27 +599,12 @@ int fa4b_amax(const void* x, int64_t n, float* amax, void* stream) {
   return FA4B_OK;
 }
 
-static int launch_nvfp4(const Nvfp4Params& p, bool norm, cudaStream_t st, bool weight_tiles = false) {
+static int launch_nvfp4(const Nvfp4Params& p, int stage, cudaStream_t st, bool weight_tiles = false) {
   dim3 grid((unsigned)(p.cols / 128), (unsigned)(p.rows / 128));
-  const bool col = p.codes_col != nullptr;
-  if (weight_tiles) {
-    if (col) nvfp4_tile_kernel<false, true, true><<<grid, 256, 0, st>>>(p);
-    else nvfp4_tile_kernel<false, false, true><<<grid, 256, 0, st>>>(p);
-  } else if (p.recipe == FA4B_RECIPE_ENCODE_CENTRIC) {
-    if (norm) {
-      if (col) nvfp4_tile_kernel<true, true, false, true><<<grid, 256, 0, st>>>(p);
-      else nvfp4_tile_kernel<true, false, false, true><<<grid, 256, 0, st>>>(p);
-    } else {
-      if (col) nvfp4_tile_kernel<false, true, false, true><<<grid, 256, 0, st>>>(p);
-      else nvfp4_tile_kernel<false, false, false, true><<<grid, 256, 0, st>>>(p);
-    }
-  } else if (norm) {
-    if (col) nvfp4_tile_kernel<true, true><<<grid, 256, 0, st>>>(p);
-    else nvfp4_tile_kernel<true, false><<<grid, 256, 0, st>>>(p);
-  } else {
-    if (col) nvfp4_tile_kernel<false, true><<<grid, 256, 0, st>>>(p);
-    else nvfp4_tile_kernel<false, false><<<grid, 256, 0, st>>>(p);
-  }
+  if (weight_tiles) launch_nvfp4_stage<kStagePlain, true>(p, grid, st);
+  else if (stage == kStageNorm) launch_nvfp4_stage<kStageNorm, false>(p, grid, st);
+  else if (stage == kStageGrads) launch_nvfp4_stage<kStageGrads, false>(p, grid, st);
+  else launch_nvfp4_stage<kStagePlain, false>(p, grid, st);
   FA4B_CUDA(cudaGetLastError());
   return FA4B_OK;
 }
@@ -577,12 +628,50 @@ static int quant_nvfp4_impl(const fa4b_quant_nvfp4_args* a, void* stream, bool w
   FA4B_REQUIRE(a->recipe == FA4B_RECIPE_DECODE_CENTRIC || (a->recipe == FA4B_RECIPE_ENCODE_CENTRIC && !weight_tiles), FA4B_UNSUPPORTED,
                "recipe %d (the 16 x 16 weight recipe is decode-centric only)", a->recipe);
   p.recipe = a->recipe;
-  return launch_nvfp4(p, false, st, weight_tiles);
+  return launch_nvfp4(p, kStagePlain, st, weight_tiles);
 }
 
 int fa4b_quant_nvfp4(const fa4b_quant_nvfp4_args* a, void* stream) { return quant_nvfp4_impl(a, stream, false); }
 
 int fa4b_quant_nvfp4_weight(const fa4b_quant_nvfp4_args* a, void* stream) { return quant_nvfp4_impl(a, stream, true); }
+
+int fa4b_pack_qkv_grads(const fa4b_pack_qkv_grads_args* a, void* stream) {
+  FA4B_REQUIRE(a != nullptr, FA4B_BAD_ARG, "args is NULL");
+  FA4B_REQUIRE(a->dq && a->dk && a->dv && a->rope_cos && a->rope_sin, FA4B_BAD_ARG, "fa4b_pack_qkv_grads: an input pointer is NULL");
+  FA4B_REQUIRE(a->amax && a->global_scale && a->codes_row && a->scales_row, FA4B_BAD_ARG, "fa4b_pack_qkv_grads: an output pointer is NULL");
+  FA4B_REQUIRE((a->codes_col == nullptr) == (a->scales_col == nullptr), FA4B_BAD_ARG, "codes_col and scales_col go together");
+  FA4B_REQUIRE(a->B > 0 && a->S > 0 && a->Hq > 0 && a->Hkv > 0 && (a->D == 64 || a->D == 128), FA4B_BAD_SHAPE,
+               "B, S, Hq, Hkv must be positive and D 64 or 128");
+  const int64_t rows = a->B * a->S, n0 = a->Hq * a->D, n1 = n0 + a->Hkv * a->D, cols = n1 + a->Hkv * a->D;
+  FA4B_REQUIRE(rows % 128 == 0 && cols % 128 == 0, FA4B_BAD_SHAPE, "B*S=%lld and (Hq+2Hkv)*D=%lld must be multiples of 128", (long long)rows,
+               (long long)cols);
+  FA4B_REQUIRE(a->ld_q >= n0 && a->ld_k >= n1 - n0 && a->ld_v >= cols - n1 && (a->ld_q | a->ld_k | a->ld_v) % 8 == 0, FA4B_BAD_ALIGN,
+               "row strides must cover a token's heads and be multiples of 8 elements");
+  FA4B_REQUIRE(((reinterpret_cast<uintptr_t>(a->dq) | reinterpret_cast<uintptr_t>(a->dk) | reinterpret_cast<uintptr_t>(a->dv) |
+                 reinterpret_cast<uintptr_t>(a->codes_row) | reinterpret_cast<uintptr_t>(a->scales_row) | reinterpret_cast<uintptr_t>(a->codes_col) |
+                 reinterpret_cast<uintptr_t>(a->scales_col)) & 15) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(a->rope_cos) | reinterpret_cast<uintptr_t>(a->rope_sin)) & 7) == 0,
+               FA4B_BAD_ALIGN, "gradients and outputs must be 16-byte aligned, rope tables 8-byte aligned");
+  FA4B_REQUIRE(a->recipe == FA4B_RECIPE_DECODE_CENTRIC || a->recipe == FA4B_RECIPE_ENCODE_CENTRIC, FA4B_UNSUPPORTED, "recipe %d", a->recipe);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Nvfp4Params p{};
+  p.x = static_cast<const __nv_bfloat16*>(a->dq); p.x1 = static_cast<const __nv_bfloat16*>(a->dk); p.x2 = static_cast<const __nv_bfloat16*>(a->dv);
+  p.ld = a->ld_q; p.ld1 = a->ld_k; p.ld2 = a->ld_v;
+  p.n0 = n0; p.n1 = n1; p.rows = rows; p.cols = cols;
+  p.rope_cos = static_cast<const __nv_bfloat16*>(a->rope_cos); p.rope_sin = static_cast<const __nv_bfloat16*>(a->rope_sin);
+  p.S = (int)a->S; p.D = (int)a->D;
+  p.amax = a->amax; p.global_scale = a->global_scale;
+  p.codes_row = a->codes_row; p.scales_row = a->scales_row;
+  p.codes_col = a->codes_col; p.scales_col = a->scales_col;
+  p.recipe = a->recipe;
+  if (!a->amax_is_input) {
+    FA4B_CUDA(cudaMemsetAsync(a->amax, 0, sizeof(float), st));
+    const int grid = (int)std::min<int64_t>((int64_t)std::max(sm_count(), 1) * 8, (rows * (cols / 8) + 255) / 256);
+    grads_amax_kernel<<<grid, 256, 0, st>>>(p, a->amax);
+    FA4B_CUDA(cudaGetLastError());
+  }
+  return launch_nvfp4(p, kStageGrads, st);
+}
 
 int fa4b_rmsnorm_quant_nvfp4(const fa4b_rmsnorm_quant_nvfp4_args* a, void* stream) {
   FA4B_REQUIRE(a != nullptr, FA4B_BAD_ARG, "args is NULL");
@@ -611,7 +700,7 @@ int fa4b_rmsnorm_quant_nvfp4(const fa4b_rmsnorm_quant_nvfp4_args* a, void* strea
   p.codes_col = a->codes_col; p.scales_col = a->scales_col;
   FA4B_REQUIRE(a->recipe == FA4B_RECIPE_DECODE_CENTRIC || a->recipe == FA4B_RECIPE_ENCODE_CENTRIC, FA4B_UNSUPPORTED, "recipe %d", a->recipe);
   p.recipe = a->recipe;
-  return launch_nvfp4(p, true, st);
+  return launch_nvfp4(p, kStageNorm, st);
 }
 
 size_t fa4b_rmsnorm_bwd_workspace_bytes(int64_t cols) { return cols > 0 ? (size_t)kRmsBwdParts * (size_t)cols * sizeof(float) : 0; }
@@ -703,11 +792,7 @@ __global__ void __launch_bounds__(256) rope_pair_kernel(__nv_bfloat16* __restric
       const uint32_t c16 = (cw[k >> 1] >> (16 * (k & 1))) & 0xffffu;
       uint32_t s16 = (sw[k >> 1] >> (16 * (k & 1))) & 0xffffu;
       if (inverse) s16 ^= 0x8000u;
-      const uint32_t cc = c16 * 0x00010001u, s2 = s16 * 0x00010001u;
-      const uint32_t perp = ((w[k] << 16) | (w[k] >> 16)) ^ 0x00008000u;  // (x, y) -> (-y, x)
-      const __nv_bfloat162 r = __hfma2(*reinterpret_cast<const __nv_bfloat162*>(&perp), *reinterpret_cast<const __nv_bfloat162*>(&s2),
-                                       __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]), *reinterpret_cast<const __nv_bfloat162*>(&cc)));
-      w[k] = *reinterpret_cast<const uint32_t*>(&r);
+      w[k] = rope_word(w[k], c16, s16);
     }
     *px = make_uint4(w[0], w[1], w[2], w[3]);
   }

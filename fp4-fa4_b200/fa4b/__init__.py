@@ -15,6 +15,7 @@ from .quantizers import (  # noqa: F401
     project_qkv_publish,
     project_dout_publish,
     rope_pair_,
+    pack_qkv_grads,
     prepare_nvfp4_projection_weight_dual,
     rmsnorm_backward_bf16,
     tk_fused_norm_quantize,
@@ -22,6 +23,6 @@ from .quantizers import (  # noqa: F401
 )
 
 __all__ = [
-    "amax", "dequant_mxfp4", "dequant_nvfp4", "mxfp4_quantize_for_gemm", "prepare_nvfp4_projection_weight", "project_nvfp4", "project_qkv_publish", "project_dout_publish", "rope_pair_", "prepare_nvfp4_projection_weight_dual", "rmsnorm_backward_bf16", "tk_fused_norm_quantize",
+    "amax", "dequant_mxfp4", "dequant_nvfp4", "mxfp4_quantize_for_gemm", "prepare_nvfp4_projection_weight", "project_nvfp4", "project_qkv_publish", "project_dout_publish", "rope_pair_", "pack_qkv_grads", "prepare_nvfp4_projection_weight_dual", "rmsnorm_backward_bf16", "tk_fused_norm_quantize",
     "tk_quantize_for_gemm",
 ]

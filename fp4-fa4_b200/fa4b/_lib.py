@@ -38,6 +38,14 @@ class RopePairArgs(C.Structure):
                 ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p), ("inverse", C.c_int)]
 
 
+class PackQkvGradsArgs(C.Structure):
+    _fields_ = [("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p), ("ld_q", C.c_int64), ("ld_k", C.c_int64), ("ld_v", C.c_int64),
+                ("B", C.c_int64), ("S", C.c_int64), ("Hq", C.c_int64), ("Hkv", C.c_int64), ("D", C.c_int64),
+                ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p), ("amax", C.c_void_p), ("amax_is_input", C.c_int),
+                ("global_scale", C.c_void_p), ("codes_row", C.c_void_p), ("scales_row", C.c_void_p),
+                ("codes_col", C.c_void_p), ("scales_col", C.c_void_p), ("recipe", C.c_int)]
+
+
 class RmsnormQuantArgs(C.Structure):
     _fields_ = [("x", C.c_void_p), ("gamma", C.c_void_p), ("rows", C.c_int64), ("cols", C.c_int64), ("ld", C.c_int64),
                 ("eps", C.c_float), ("inv_rms", C.c_void_p), ("y_out", C.c_void_p), ("amax", C.c_void_p),
@@ -103,7 +111,7 @@ class Info(C.Structure):
 
 
 EXPORTS = (
-    "fa4b_status_string", "fa4b_last_error", "fa4b_query", "fa4b_amax", "fa4b_quant_nvfp4", "fa4b_quant_nvfp4_weight", "fa4b_project_nvfp4", "fa4b_project_qkv_publish", "fa4b_project_dout_publish", "fa4b_rope_pair",
+    "fa4b_status_string", "fa4b_last_error", "fa4b_query", "fa4b_amax", "fa4b_quant_nvfp4", "fa4b_quant_nvfp4_weight", "fa4b_project_nvfp4", "fa4b_project_qkv_publish", "fa4b_project_dout_publish", "fa4b_rope_pair", "fa4b_pack_qkv_grads",
     "fa4b_rmsnorm_quant_nvfp4", "fa4b_quant_mxfp4", "fa4b_dequant_nvfp4", "fa4b_dequant_mxfp4",
     "fa4b_attn_workspace_bytes", "fa4b_attn_ws_layout_query", "fa4b_attn_prepare", "fa4b_attn_fwd",
     "fa4b_attn_fwd_static", "fa4b_attn_bwd_preprocess", "fa4b_attn_bwd", "fa4b_attn_bwd_plan", "fa4b_attn_bwd_plan_item", "fa4b_attn_check_status", "fa4b_attn_merge", "fa4b_attn_accumulate", "fa4b_rmsnorm_bwd", "fa4b_rmsnorm_bwd_workspace_bytes", "fa4b_microgate", "fa4b_tensor_peak", "fa4b_wait_selftest",

@@ -18,7 +18,7 @@ import torch
 
 from . import attention
 from . import _lib
-from .quantizers import (prepare_nvfp4_projection_weight_dual, project_dout_publish, project_nvfp4, project_qkv_publish, rope_pair_,
+from .quantizers import (pack_qkv_grads, prepare_nvfp4_projection_weight_dual, project_dout_publish, project_nvfp4, project_qkv_publish, rope_pair_,
                          tk_quantize_for_gemm)
 
 
@@ -165,10 +165,9 @@ class LowpFA4AttentionBlock:
         else:
             attention.attn_backward(o_rows.view(B, S, Hq, D).permute(0, 2, 1, 3), lse, do_rows.view(B, S, Hq, D).permute(0, 2, 1, 3), ws,
                                     out=grads)
-        rope_pair_(dq, rope_cos, rope_sin, inverse=True)
-        rope_pair_(dk, rope_cos, rope_sin, inverse=True)
-        # QKV projection: dX = dQKV . Wqkv, dWqkv = dQKV^T . X
-        g_r, g_rp, g_c, g_cp, g_g, _ = tk_quantize_for_gemm(dqkv, return_transpose=True, encode_centric=False)
+        # QKV projection: dX = dQKV . Wqkv, dWqkv = dQKV^T . X; the inverse rotation of dQ and dK happens while the
+        # gradients are packed
+        g_r, g_rp, g_c, g_cp, g_g, _ = pack_qkv_grads(dq, dk, dv, rope_cos, rope_sin, return_transpose=True, encode_centric=False)
         dx = project_nvfp4((g_r, g_rp, g_g), self.w_qkv_t, status=self._slot(dy.device, 4)).view(B, S, self.hidden)
         dwqkv = project_nvfp4((g_c, g_cp, g_g), saved["x_cols"], status=self._slot(dy.device, 5))                               # [(Hq + 2 Hkv) D, hidden]
         return dx, dwqkv[:Hq * D], dwqkv[Hq * D:(Hq + Hkv) * D], dwqkv[(Hq + Hkv) * D:], dwo

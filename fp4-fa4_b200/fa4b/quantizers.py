@@ -201,6 +201,39 @@ def rope_pair_(x: torch.Tensor, rope_cos: torch.Tensor, rope_sin: torch.Tensor, 
     return x
 
 
+def pack_qkv_grads(dq: torch.Tensor, dk: torch.Tensor, dv: torch.Tensor, rope_cos: torch.Tensor, rope_sin: torch.Tensor,
+                   return_transpose: bool = True, encode_centric: bool = False, *, amax_in: torch.Tensor | None = None):
+    """The NVFP4 operand of the QKV projection's backward GEMMs from the attention gradients ``dq [B,S,Hq,D]``,
+    ``dk``, ``dv [B,S,Hkv,D]`` (bf16; token-major, a token's heads contiguous -- column ranges of one
+    ``[B*S, (Hq+2Hkv)D]`` buffer qualify): ``[dQ | dK | dV]`` with dQ and dK turned back through the pair-native
+    rotation, as the 6-tuple of :func:`tk_quantize_for_gemm` (``rows = B*S``, ``cols = (Hq+2Hkv)D``).  One pass over
+    the gradients (two when the amax is not given) instead of two in-place rotations, a statistics pass and the
+    quantiser; the results are byte-identical.  The producer behind
+    ``b300_pack_gqa_d128_hierarchical_qkv_gradient_nvfp4_tiles`` (tk_fa4/interface.py:4864-4912;
+    tk_fa4/lowp_fa4_bwd/gqa_d128_hierarchical_qkv_nvfp4_quantize.cuh), which takes its global scale as an input
+    like ``amax_in`` here."""
+    for name, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+        if t.ndim != 4 or t.dtype != torch.bfloat16 or not t.is_cuda or t.stride(3) != 1 or t.stride(2) != t.shape[3] or (t.shape[0] > 1 and t.stride(0) != t.shape[1] * t.stride(1)):
+            raise ValueError(f"{name} must be a CUDA bfloat16 [B,S,H,D] tensor, a token's heads contiguous and batches token-major")
+    B, S, Hq, D = dq.shape
+    Hkv = dk.shape[2]
+    if tuple(dk.shape) != (B, S, Hkv, D) or tuple(dv.shape) != (B, S, Hkv, D):
+        raise ValueError("dk and dv must be [B,S,Hkv,D] with the batch, length and head size of dq")
+    for name, t in (("rope_cos", rope_cos), ("rope_sin", rope_sin)):
+        if t.dtype != torch.bfloat16 or tuple(t.shape) != (S, D // 2) or not t.is_contiguous() or t.device != dq.device:
+            raise ValueError(f"{name} must be a contiguous bfloat16 [S, D/2] tensor on the device of dq")
+    rows, cols = B * S, (Hq + 2 * Hkv) * D
+    if rows % 128 or cols % 128:
+        raise ValueError(f"B*S={rows} and (Hq+2Hkv)*D={cols} must be multiples of 128")
+    fp4_row, sc_row, fp4_col, sc_col = _alloc_outputs(rows, cols, return_transpose, dq.device)
+    am = torch.empty(1, dtype=torch.float32, device=dq.device) if amax_in is None else amax_in
+    sg = torch.empty(1, dtype=torch.float32, device=dq.device)
+    a = _lib.PackQkvGradsArgs(ptr(dq), ptr(dk), ptr(dv), dq.stride(1), dk.stride(1), dv.stride(1), B, S, Hq, Hkv, D, ptr(rope_cos), ptr(rope_sin),
+                              ptr(am), int(amax_in is not None), ptr(sg), ptr(fp4_row), ptr(sc_row), ptr(fp4_col), ptr(sc_col), int(bool(encode_centric)))
+    check(lib().fa4b_pack_qkv_grads(C.byref(a), C.c_void_p(current_stream())), "fa4b_pack_qkv_grads")
+    return fp4_row, sc_row, fp4_col, sc_col, sg, am
+
+
 def tk_fused_norm_quantize(input: torch.Tensor, gamma: torch.Tensor, epsilon: float = 1e-6, with_silu: bool = False,
                            return_transpose: bool = True, *, return_normalized: bool = False, encode_centric: bool = True):
     """Fused RMSNorm + NVFP4: returns ``(fp4_row, sc_row, fp4_col, sc_col, sg,

@@ -170,6 +170,44 @@ typedef struct fa4b_rope_pair_args {
 } fa4b_rope_pair_args;
 int fa4b_rope_pair(const fa4b_rope_pair_args* a, void* stream);
 
+/* ---- fa4b_pack_qkv_grads --------------------------------------------------
+ * The operand of the QKV projection's backward GEMMs from the attention
+ * gradients in one pass: the token-major matrix [dQ | dK | dV] of
+ * [B*S, (Hq + 2 Hkv) D] bf16 is gathered from the three gradient tensors
+ * (rows are tokens, batch-major; row strides in elements, so the three may be
+ * column ranges of one buffer), dQ and dK turn back through the pair-native
+ * rotation of their token (the arithmetic of fa4b_rope_pair with inverse != 0),
+ * and the result is written as NVFP4 rows and, optionally, transposed NVFP4
+ * (outputs as in fa4b_quant_nvfp4 with rows = B*S, cols = (Hq + 2 Hkv) D).
+ * Byte for byte what fa4b_rope_pair on dQ and dK followed by fa4b_quant_nvfp4
+ * of the concatenation produce; the rotated bf16 matrix is never written.
+ * amax: written (one extra read of the gradients) unless amax_is_input != 0 --
+ * the reference's producer always takes a global scale decided beforehand.
+ * Replaces the producer kernel of
+ * tk_fa4/lowp_fa4_bwd/gqa_d128_hierarchical_qkv_nvfp4_quantize.cuh:1-140 behind
+ * b300_pack_gqa_d128_hierarchical_qkv_gradient_nvfp4_tiles
+ * (tk_fa4/interface.py:4864-4912) for row-major dQ, and its D = 64 sibling
+ * b300_project_gqa_d64_paired_qkv_gradient_nvfp4 (tk_fa4/interface.py:4712).
+ * B*S and (Hq + 2 Hkv) D must be multiples of 128; D is 64 or 128. */
+typedef struct fa4b_pack_qkv_grads_args {
+  const void* dq;          /* bf16, token row t at dq + t * ld_q: Hq heads of D   */
+  const void* dk;          /* bf16, Hkv heads of D per token                      */
+  const void* dv;
+  int64_t ld_q, ld_k, ld_v;
+  int64_t B, S, Hq, Hkv, D;
+  const void* rope_cos;    /* bf16 [S, D/2] */
+  const void* rope_sin;
+  float* amax;
+  int amax_is_input;
+  float* global_scale;
+  uint8_t* codes_row;
+  uint8_t* scales_row;
+  uint8_t* codes_col;      /* NULL = no transposed output */
+  uint8_t* scales_col;
+  int recipe;              /* FA4B_RECIPE_* */
+} fa4b_pack_qkv_grads_args;
+int fa4b_pack_qkv_grads(const fa4b_pack_qkv_grads_args* a, void* stream);
+
 /* ---- fa4b_rmsnorm_quant_nvfp4 -------------------------------------------
  * y = bf16((x * inv_rms[row]) * gamma[col]), inv_rms = 1/sqrt(mean x^2 + eps);
  * then fa4b_quant_nvfp4 of y with amax over the bf16 y.  Replaces

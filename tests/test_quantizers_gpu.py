@@ -167,6 +167,63 @@ def test_rope_pair_inverse_undoes_the_rotation_within_bf16_rounding():
     assert float(((n0 - n1).abs() / n0.clamp_min(1e-3)).max()) < 2e-2
 
 
+@pytest.mark.parametrize("B,S,Hq,Hkv,D,encode_centric", [(2, 256, 4, 2, 128, False), (1, 384, 8, 2, 128, True), (2, 128, 6, 2, 64, False),
+                                                          (1, 256, 2, 1, 64, True)])
+def test_pack_qkv_grads_is_the_oracle_of_rotation_then_quantisation_and_the_separate_passes(B, S, Hq, Hkv, D, encode_centric):
+    """[dQ | dK | dV] -> inverse rotation -> NVFP4 rows and transposed, in one pass: equal byte for byte to the oracle's
+    rotation followed by its quantiser, and to the three separate device passes; from three tensors and from the
+    column ranges of one buffer; with the amax computed and supplied."""
+    g = torch.Generator().manual_seed(100 + S + Hq)
+    N = (Hq + 2 * Hkv) * D
+    buf = (torch.randn(B * S, N, generator=g) * torch.logspace(-3, 0, N)[None, :]).bfloat16()   # dynamic range across the heads
+    dq = buf[:, :Hq * D].view(B, S, Hq, D)
+    dk = buf[:, Hq * D:(Hq + Hkv) * D].view(B, S, Hkv, D)
+    dv = buf[:, (Hq + Hkv) * D:].view(B, S, Hkv, D)
+    cos, sin = O.rope_tables(S, D)
+    rotated = torch.cat([O.rope_pair_reference(dq, cos, sin, inverse=True).reshape(B * S, -1),
+                         O.rope_pair_reference(dk, cos, sin, inverse=True).reshape(B * S, -1), dv.reshape(B * S, -1)], dim=1)
+    quantise = O.nvfp4_quantize_encode_centric if encode_centric else O.nvfp4_quantize
+    ref, ref_t = quantise(rotated), quantise(rotated.t().contiguous())
+    cd, sd = cos.to(DEV), sin.to(DEV)
+    dbuf = buf.to(DEV)
+    views = (dbuf[:, :Hq * D].view(B, S, Hq, D), dbuf[:, Hq * D:(Hq + Hkv) * D].view(B, S, Hkv, D), dbuf[:, (Hq + Hkv) * D:].view(B, S, Hkv, D))
+    separate = tuple(t.contiguous() for t in views)
+    for name, (a, b, c) in (("views of one buffer", views), ("three tensors", separate)):
+        out = fa4b.pack_qkv_grads(a, b, c, cd, sd, return_transpose=True, encode_centric=encode_centric)
+        assert float(out[5]) == float(rotated.float().abs().amax()), name
+        assert float(out[4]) == float(ref.global_scale), name
+        _same(out[0], ref.codes, f"{name}: row codes")
+        _same(out[1], ref.pages(), f"{name}: row scale pages")
+        _same(out[2], ref_t.codes, f"{name}: transposed codes")
+        _same(out[3], ref_t.pages(), f"{name}: transposed scale pages")
+    assert torch.equal(dbuf.cpu(), buf)  # the gradients themselves are left alone
+    # the passes it replaces
+    two = dbuf.clone()
+    fa4b.rope_pair_(two[:, :Hq * D].view(B, S, Hq, D), cd, sd, inverse=True)
+    fa4b.rope_pair_(two[:, Hq * D:(Hq + Hkv) * D].view(B, S, Hkv, D), cd, sd, inverse=True)
+    sep = fa4b.tk_quantize_for_gemm(two, return_transpose=True, encode_centric=encode_centric)
+    # a supplied amax (the reference's delayed global scale) and a row-only call
+    am = sep[5].clone()
+    given = fa4b.pack_qkv_grads(*views, cd, sd, return_transpose=False, encode_centric=encode_centric, amax_in=am)
+    assert given[2] is None and given[3] is None
+    for i, what in ((0, "row codes"), (1, "row scale pages")):
+        _same(given[i], sep[i], f"supplied amax: {what}")
+    for i, what in ((0, "row codes"), (1, "row scale pages"), (2, "transposed codes"), (3, "transposed scale pages")):
+        _same(out[i], sep[i], f"separate passes: {what}")
+
+
+def test_pack_qkv_grads_rejects_bad_layouts():
+    cos, sin = (t.to(DEV) for t in O.rope_tables(128, 128))
+    dq = torch.zeros(1, 128, 2, 128, dtype=torch.bfloat16, device=DEV)
+    dkv = torch.zeros(1, 128, 1, 128, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ValueError):
+        fa4b.pack_qkv_grads(dq.permute(0, 2, 1, 3), dkv, dkv, cos, sin)            # head-major view
+    with pytest.raises(ValueError):
+        fa4b.pack_qkv_grads(dq, dkv, dkv, cos[:64].contiguous(), sin)                # table of another length
+    with pytest.raises(ValueError):
+        fa4b.pack_qkv_grads(dq[:, :64], dkv[:, :64], dkv[:, :64], cos[:64].contiguous(), sin[:64].contiguous())  # 64 tokens
+
+
 @pytest.mark.parametrize("shape,seed", [((128, 128), 11), ((256, 512), 12)])
 def test_nvfp4_encode_centric_recipe_matches_its_restatement(shape, seed):
     # the TK quantiser's default recipe; its oracle is pinned by hand-worked known answers (tests/test_oracle_pins.py)
