@@ -223,15 +223,13 @@ __device__ __forceinline__ uint32_t nvfp4_scale_byte(float bamax, float g, float
 // per-tensor table over the 127 scale bytes: step d = max(E4M3(byte) g, FLT_MIN) and r = RN(1 / d)
 // (r = 0 marks a step whose significand is all ones: divide).  128 threads fill it.
 struct StepTable {
-  float d[128];
-  float r[128];
+  float2 e[128];  // .x = d, .y = r: one shared-memory read per block
 };
 __device__ __forceinline__ void fill_step_table(StepTable& tab, float g, int t) {
   if (t < 128) {
     const float dec = (t < 127) ? e4m3_to_f32((uint32_t)t) : 0.f;
     const float d = fmaxf(dec * g, kFltMin);
-    tab.d[t] = d;
-    tab.r[t] = significand_all_ones(d) ? 0.f : __frcp_rn(d);
+    tab.e[t] = make_float2(d, significand_all_ones(d) ? 0.f : __frcp_rn(d));
   }
 }
 // sixteen values (eight packed pairs, largest magnitude `bamax`) divided by the step of scale byte
@@ -239,7 +237,8 @@ __device__ __forceinline__ void fill_step_table(StepTable& tab, float g, int t) 
 // size) divides: inf - inf in the correction would lose the sign that saturation keeps.
 __device__ __forceinline__ void nvfp4_codes16(const uint64_t (&x)[8], float bamax, const StepTable& tab, uint32_t sb, uint32_t& lo,
                                               uint32_t& hi) {
-  const float d = tab.d[sb], r = tab.r[sb];
+  const float2 e = tab.e[sb];
+  const float d = e.x, r = e.y;
   uint64_t q[8];
   if (r != 0.f && bamax * r < 1.0e38f) {
     const uint64_t r2 = pack2(r, r), nd2 = pack2(-d, -d);

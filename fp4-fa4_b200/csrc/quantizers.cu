@@ -382,45 +382,56 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
     __syncthreads();
   }
 
-  // ---- row-wise 1x16 blocks: 512 segments of two blocks, two segments per thread -----------
+  // ---- row-wise 1x16 blocks: a thread takes half a row (four blocks).  The 32 lanes of a warp are 32 consecutive
+  // rows at one column offset, and a 272-byte row pitch puts eight consecutive rows in eight different groups of four
+  // banks: every 16-byte read is conflict-free.
+  {
+    const int r = t & 127, half = t >> 7;
+    uint32_t sword = 0;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int seg = t + i * 256;
-    const int r = seg >> 2, c32 = (seg & 3) * 32;
-    uint32_t w[16];
+    for (int i = 0; i < 2; ++i) {  // 32 columns (two blocks) at a time
+      const int c32 = half * 64 + i * 32;
+      uint32_t w[16];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint4 v = *reinterpret_cast<const uint4*>(&tile[r * kPitch + c32 + 8 * j]);
-      w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
-    }
-    uint32_t codes[4] = {0, 0, 0, 0};
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {  // the two 16-element blocks of the segment
-      float m = 0.f;
-      uint64_t x[8];
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        x[k] = bf16x2_to_f32x2(w[8 * h + k]);
-        if (!W2D) m = absmax3(m, x[k]);  // on the unpacked values: one three-input maximum per pair
+      for (int j = 0; j < 4; ++j) {
+        const uint4 v = *reinterpret_cast<const uint4*>(&tile[r * kPitch + c32 + 8 * j]);
+        w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
       }
-      const int kb = (c32 >> 4) + h;
-      const float bamax = W2D ? tile_amax[(r >> 4) * 8 + kb] : m;
-      uint32_t sbyte;
-      if (ENC) {
-        nvfp4_codes16_encode(x, bamax, s_enc, enc_steps, sbyte, codes[2 * h], codes[2 * h + 1]);
-      } else {
-        sbyte = nvfp4_scale_byte(bamax, g, inv6g);
-        nvfp4_codes16(x, bamax, steps, sbyte, codes[2 * h], codes[2 * h + 1]);
+      uint32_t codes[4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float m = 0.f;
+        uint64_t x[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          x[k] = bf16x2_to_f32x2(w[8 * h + k]);
+          if (!W2D) m = absmax3(m, x[k]);  // on the unpacked values: one three-input maximum per pair
+        }
+        const int kb = (c32 >> 4) + h;
+        const float bamax = W2D ? tile_amax[(r >> 4) * 8 + kb] : m;
+        uint32_t sbyte;
+        if (ENC) {
+          nvfp4_codes16_encode(x, bamax, s_enc, enc_steps, sbyte, codes[2 * h], codes[2 * h + 1]);
+        } else {
+          sbyte = nvfp4_scale_byte(bamax, g, inv6g);
+          nvfp4_codes16(x, bamax, steps, sbyte, codes[2 * h], codes[2 * h + 1]);
+        }
+        sword |= sbyte << (8 * (2 * i + h));
       }
-      sc_row[(kb >> 2) * 512 + page_offset(r, kb)] = (uint8_t)sbyte;
+      *reinterpret_cast<uint4*>(p.codes_row + (row0 + r) * (p.cols / 2) + (col0 + c32) / 2) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
     }
-    *reinterpret_cast<uint4*>(p.codes_row + (row0 + r) * (p.cols / 2) + (col0 + c32) / 2) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+    // the four scale bytes of this half row are one aligned word of page `half`
+    *reinterpret_cast<uint32_t*>(&sc_row[half * 512 + page_offset(r, 0)]) = sword;
   }
-  // ---- column-wise 16x1 blocks (transposed output): a thread takes two adjacent columns ------
+  // ---- column-wise 16x1 blocks (transposed output): a thread takes two adjacent columns and two consecutive
+  // blocks of 16 rows; the code bytes wait in shared memory with their 8-byte slots permuted by the column so that
+  // the 16 lanes of a half warp write 32 different banks
   if (COL) {
+    const int cp = t & 63, rb0 = (t >> 6) * 2;
+    uint32_t spair[2] = {0, 0};
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      const int cp = t & 63, rb = (t >> 6) + 4 * i;  // column pair, block of 16 rows
+      const int rb = rb0 + i;
       uint32_t w[16];
 #pragma unroll
       for (int k = 0; k < 16; ++k) w[k] = *reinterpret_cast<const uint32_t*>(&tile[(rb * 16 + k) * kPitch + 2 * cp]);
@@ -442,11 +453,15 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
           sbyte = nvfp4_scale_byte(bamax, g, inv6g);
           nvfp4_codes16(x, bamax, steps, sbyte, lo, hi);
         }
-        *reinterpret_cast<uint2*>(&cb_col[c * 80 + rb * 8]) = make_uint2(lo, hi);
-        // transposed tensor: row = c (within this tile's 128 columns), kblock = rb (within 8)
-        sc_col[(rb >> 2) * 512 + page_offset(c, rb)] = (uint8_t)sbyte;
+        *reinterpret_cast<uint2*>(&cb_col[c * 80 + ((rb ^ ((c >> 3) & 3)) * 8)]) = make_uint2(lo, hi);
+        spair[h] |= sbyte << (8 * i);
       }
     }
+    // transposed tensor: row = c (within this tile's 128 columns), kblock = rb (within 8); two consecutive blocks
+    // are two adjacent bytes of a page
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+      *reinterpret_cast<uint16_t*>(&sc_col[(rb0 >> 2) * 512 + page_offset(2 * cp + h, rb0)]) = (uint16_t)spair[h];
   }
   __syncthreads();
   // ---- write the staged scale pages and transposed codes ------------------------------
@@ -462,11 +477,11 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
   }
   if (COL) {
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int chunk = t + i * 256;  // 512 chunks of 16 bytes
-      const int c = chunk >> 2, q = chunk & 3;
-      *reinterpret_cast<uint4*>(p.codes_col + (col0 + c) * (p.rows / 2) + row0 / 2 + q * 16) =
-          *reinterpret_cast<const uint4*>(&cb_col[c * 80 + q * 16]);
+    for (int i = 0; i < 4; ++i) {
+      const int chunk = t + i * 256;  // 1024 slots of 8 bytes: the 16 row pairs of block rb of column c
+      const int c = chunk >> 3, rb = chunk & 7;
+      *reinterpret_cast<uint2*>(p.codes_col + (col0 + c) * (p.rows / 2) + row0 / 2 + rb * 8) =
+          *reinterpret_cast<const uint2*>(&cb_col[c * 80 + ((rb ^ ((c >> 3) & 3)) * 8)]);
     }
   }
 }
