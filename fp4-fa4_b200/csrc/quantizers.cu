@@ -7,6 +7,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "tc_sm100.cuh"
 
 namespace fa4b {
 
@@ -240,7 +241,6 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_reduce_kernel(const float* __
 
 // ------------------------------------------------------------------ NVFP4 tile kernel
 constexpr int kTile = 128;
-constexpr int kPitch = kTile + 8;  // bf16 elements; 272-byte rows keep 16-byte alignment
 
 struct Nvfp4Params {
   const __nv_bfloat16* x;
@@ -312,24 +312,51 @@ __global__ void __launch_bounds__(256) grads_amax_kernel(const Nvfp4Params p, fl
 // W2D: one scale per 16 x 16 tile (learned projection weights): every 1 x 16 group of the tile, in either
 // orientation, carries the scale of the tile's amax, so the transposed output is the byte-for-byte transpose of
 // the row-wise one.
-// STAGE: what the tile is as it lands in shared memory -- the matrix itself, the RMSNorm of it, or the
-// [dQ | dK | dV] gradient matrix gathered from three tensors with the inverse rotation applied.
+// STAGE: what the tile is as it lands in shared memory -- the matrix itself (a TMA load), the RMSNorm of it, or the
+// [dQ | dK | dV] gradient matrix gathered from three tensors with the inverse rotation applied (both through
+// registers).
 enum { kStagePlain = 0, kStageNorm = 1, kStageGrads = 2 };
+
+// Shared memory of one 128 x 128 tile.  Every buffer that a TMA copy touches carries the swizzle of its tensor map,
+// and the thread mappings below are chosen so that each warp-wide access meets every bank at most once (twice for
+// the 8-byte writes of transposed codes).
+struct TileSmem {
+  alignas(1024) uint8_t tile[2][128 * 128];  // bf16 columns [0, 64) and [64, 128): 128-byte rows, 128B swizzle
+  alignas(1024) uint8_t out_row[128 * 64];   // row-wise codes: a 64-byte row per tile row, 64B swizzle
+  alignas(1024) uint8_t out_col[128 * 64];   // transposed codes: a 64-byte row per tile column, 64B swizzle
+  alignas(16) uint8_t sc_row[2 * 512];
+  alignas(16) uint8_t sc_col[2 * 512];
+  union {
+    StepTable steps;        // decode-centric recipes: division table of this tensor's global scale
+    EncodeTable enc_steps;  // encode-centric recipe: multiplier table
+  };
+  float tile_amax[64];
+  alignas(8) uint64_t bar;
+  volatile uint32_t abort_flag;
+};
+constexpr int kTileSmemBytes = (int)sizeof(TileSmem) + 1024;
+
+// status of the quantizer kernels' waits (word 0 != 0: a tile load did not arrive; words 1-3 as in the attention kernels)
+__device__ uint32_t g_quant_status[4];
+
 template <int STAGE, bool COL, bool W2D = false, bool ENC = false>
-__global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
-  constexpr bool NORM = STAGE == kStageNorm;
-  __shared__ __align__(16) __nv_bfloat16 tile[kTile * kPitch];
-  __shared__ __align__(16) uint8_t sc_row[2 * 512];
-  __shared__ __align__(16) uint8_t sc_col[COL ? 2 * 512 : 16];
-  __shared__ __align__(16) uint8_t cb_col[COL ? kTile * 80 : 16];  // [128 columns][64 code bytes + pad]
-  __shared__ StepTable steps;       // decode-centric recipes: division table of this tensor's global scale
-  __shared__ EncodeTable enc_steps;  // encode-centric recipe: multiplier table
-  __shared__ float tile_amax[W2D ? 64 : 1];
+__global__ void __launch_bounds__(256, 4) nvfp4_tile_kernel(const Nvfp4Params p, const __grid_constant__ CUtensorMap map_x,
+                                                         const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col) {
+  extern __shared__ uint8_t tile_smem_raw[];
+  TileSmem& s = *reinterpret_cast<TileSmem*>(tile_smem_raw + ((1024u - (smem_u32(tile_smem_raw) & 1023u)) & 1023u));
 
   const int t = threadIdx.x;
   // tiles run from the end of the matrix to its start: the statistics pass that precedes this kernel
   // read the matrix front to back, so its last part is the part still in L2
   const int64_t row0 = (int64_t)(gridDim.y - 1 - blockIdx.y) * kTile, col0 = (int64_t)(gridDim.x - 1 - blockIdx.x) * kTile;
+  if (STAGE == kStagePlain && t == 0) {
+    s.abort_flag = 0u;
+    mbar_init(&s.bar, 1);
+    fence_barrier_init();
+    mbar_expect_tx(&s.bar, 2 * 128 * 128);
+    tma_load_2d(s.tile[0], &map_x, (int)col0, (int)row0, &s.bar);
+    tma_load_2d(s.tile[1], &map_x, (int)col0 + 64, (int)row0, &s.bar);
+  }
   const float amax = *p.amax;
   const float g = amax / kNvfp4GlobalDiv;
   const bool all_zero = !(amax > 0.f);
@@ -338,63 +365,75 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
   float s_enc = fminf(kNvfp4GlobalDiv / amax, 3.4028235e38f);
   if (amax == 0.f || s_enc == 0.f) s_enc = 1.0f;
   if (blockIdx.x == 0 && blockIdx.y == 0 && t == 0) *p.global_scale = g;
-  if (ENC) fill_encode_table(enc_steps, s_enc, t);
-  else fill_step_table(steps, g, t);
+  if (ENC) fill_encode_table(s.enc_steps, s_enc, t);
+  else fill_step_table(s.steps, g, t);
 
-  // ---- stage the tile (and apply the norm) -------------------------------------
+  // ---- stage the tile -----------------------------------------------------------
+  if (STAGE != kStagePlain) {
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int chunk = t + i * 256;  // 2048 chunks of 8 bf16
-    const int r = chunk >> 4, c8 = (chunk & 15) * 8;
-    uint4 v = STAGE == kStageGrads ? load_grad_chunk(p, row0 + r, col0 + c8) : __ldg(reinterpret_cast<const uint4*>(p.x + (row0 + r) * p.ld + col0 + c8));
-    if (NORM) {
-      const float inv = __ldg(p.inv_rms + row0 + r);
-      const uint4 gv = __ldg(reinterpret_cast<const uint4*>(p.gamma + col0 + c8));
-      uint32_t w[4] = {v.x, v.y, v.z, v.w};
-      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+    for (int i = 0; i < 8; ++i) {
+      const int chunk = t + i * 256;  // 2048 chunks of 8 bf16
+      const int r = chunk >> 4, c8 = (chunk & 15) * 8;
+      uint4 v;
+      if (STAGE == kStageGrads) {
+        v = load_grad_chunk(p, row0 + r, col0 + c8);
+      } else {
+        v = __ldg(reinterpret_cast<const uint4*>(p.x + (row0 + r) * p.ld + col0 + c8));
+        const float inv = __ldg(p.inv_rms + row0 + r);
+        const uint4 gv = __ldg(reinterpret_cast<const uint4*>(p.gamma + col0 + c8));
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float a = (bf16_bits_to_f32(w[k] & 0xffffu) * inv) * bf16_bits_to_f32(gw[k] & 0xffffu);
-        const float b = (bf16_bits_to_f32(w[k] >> 16) * inv) * bf16_bits_to_f32(gw[k] >> 16);
-        const __nv_bfloat162 y = __floats2bfloat162_rn(a, b);
-        w[k] = *reinterpret_cast<const uint32_t*>(&y);
+        for (int k = 0; k < 4; ++k) {
+          const float a = (bf16_bits_to_f32(w[k] & 0xffffu) * inv) * bf16_bits_to_f32(gw[k] & 0xffffu);
+          const float b = (bf16_bits_to_f32(w[k] >> 16) * inv) * bf16_bits_to_f32(gw[k] >> 16);
+          const __nv_bfloat162 y = __floats2bfloat162_rn(a, b);
+          w[k] = *reinterpret_cast<const uint32_t*>(&y);
+        }
+        v = make_uint4(w[0], w[1], w[2], w[3]);
+        if (p.y_out) *reinterpret_cast<uint4*>(p.y_out + (row0 + r) * p.cols + col0 + c8) = v;
       }
-      v = make_uint4(w[0], w[1], w[2], w[3]);
-      if (p.y_out) *reinterpret_cast<uint4*>(p.y_out + (row0 + r) * p.cols + col0 + c8) = v;
+      *reinterpret_cast<uint4*>(&s.tile[c8 >> 6][swizzled_offset((uint32_t)r, (uint32_t)(c8 & 63) * 2u, 128)]) = v;
     }
-    *reinterpret_cast<uint4*>(&tile[r * kPitch + c8]) = v;
   }
-  __syncthreads();
+  __syncthreads();  // tables (and the staged tile, or the barrier's initialisation) visible
+  if (STAGE == kStagePlain) {
+    if (!mbar_wait(&s.bar, 0, &s.abort_flag, g_quant_status, 1, (uint32_t)blockIdx.y)) {
+      if (t == 0) mbar_wait_teardown(&s.bar, 0);  // the copies may still be on their way into this CTA's memory
+      __syncthreads();
+      return;
+    }
+  }
   if (W2D) {  // four threads per 16 x 16 tile, four rows each
     const int id = t >> 2, r0 = (id >> 3) * 16 + (t & 3) * 4, c0 = (id & 7) * 16;
     uint32_t m2 = 0;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      const uint4 a = *reinterpret_cast<const uint4*>(&tile[(r0 + k) * kPitch + c0]);
-      const uint4 b = *reinterpret_cast<const uint4*>(&tile[(r0 + k) * kPitch + c0 + 8]);
+      const uint8_t* half = s.tile[c0 >> 6];
+      const uint4 a = *reinterpret_cast<const uint4*>(half + swizzled_offset((uint32_t)(r0 + k), (uint32_t)(c0 & 63) * 2u, 128));
+      const uint4 b = *reinterpret_cast<const uint4*>(half + swizzled_offset((uint32_t)(r0 + k), (uint32_t)(c0 & 63) * 2u + 16u, 128));
       m2 = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(m2, a.x), a.y), a.z), a.w);
       m2 = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(m2, b.x), b.y), b.z), b.w);
     }
     float m = fmaxf(bf16_bits_to_f32(m2 & 0xffffu), bf16_bits_to_f32(m2 >> 16));
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-    if ((t & 3) == 0) tile_amax[id] = m;
+    if ((t & 3) == 0) s.tile_amax[id] = m;
     __syncthreads();
   }
 
-  // ---- row-wise 1x16 blocks: a thread takes half a row (four blocks).  The 32 lanes of a warp are 32 consecutive
-  // rows at one column offset, and a 272-byte row pitch puts eight consecutive rows in eight different groups of four
-  // banks: every 16-byte read is conflict-free.
+  // ---- row-wise 1x16 blocks: a thread takes half a row (four blocks of one 128-byte swizzled row).  The 32 lanes of a
+  // warp are 32 consecutive rows, so the eight lanes of a quarter warp read eight different 16-byte chunks.
   {
     const int r = t & 127, half = t >> 7;
+    const uint8_t* src = s.tile[half] + r * 128;
     uint32_t sword = 0;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {  // 32 columns (two blocks) at a time
-      const int c32 = half * 64 + i * 32;
       uint32_t w[16];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const uint4 v = *reinterpret_cast<const uint4*>(&tile[r * kPitch + c32 + 8 * j]);
+        const uint4 v = *reinterpret_cast<const uint4*>(src + (((4 * i + j) ^ (r & 7)) << 4));
         w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
       }
       uint32_t codes[4];
@@ -407,34 +446,39 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
           x[k] = bf16x2_to_f32x2(w[8 * h + k]);
           if (!W2D) m = absmax3(m, x[k]);  // on the unpacked values: one three-input maximum per pair
         }
-        const int kb = (c32 >> 4) + h;
-        const float bamax = W2D ? tile_amax[(r >> 4) * 8 + kb] : m;
+        const int kb = half * 4 + 2 * i + h;
+        const float bamax = W2D ? s.tile_amax[(r >> 4) * 8 + kb] : m;
         uint32_t sbyte;
         if (ENC) {
-          nvfp4_codes16_encode(x, bamax, s_enc, enc_steps, sbyte, codes[2 * h], codes[2 * h + 1]);
+          nvfp4_codes16_encode(x, bamax, s_enc, s.enc_steps, sbyte, codes[2 * h], codes[2 * h + 1]);
         } else {
           sbyte = nvfp4_scale_byte(bamax, g, inv6g);
-          nvfp4_codes16(x, bamax, steps, sbyte, codes[2 * h], codes[2 * h + 1]);
+          nvfp4_codes16(x, bamax, s.steps, sbyte, codes[2 * h], codes[2 * h + 1]);
         }
         sword |= sbyte << (8 * (2 * i + h));
       }
-      *reinterpret_cast<uint4*>(p.codes_row + (row0 + r) * (p.cols / 2) + (col0 + c32) / 2) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+      *reinterpret_cast<uint4*>(&s.out_row[swizzled_offset((uint32_t)r, (uint32_t)(half * 32 + i * 16), 64)]) =
+          make_uint4(codes[0], codes[1], codes[2], codes[3]);
     }
     // the four scale bytes of this half row are one aligned word of page `half`
-    *reinterpret_cast<uint32_t*>(&sc_row[half * 512 + page_offset(r, 0)]) = sword;
+    *reinterpret_cast<uint32_t*>(&s.sc_row[half * 512 + page_offset(r, 0)]) = sword;
   }
-  // ---- column-wise 16x1 blocks (transposed output): a thread takes two adjacent columns and two consecutive
-  // blocks of 16 rows; the code bytes wait in shared memory with their 8-byte slots permuted by the column so that
-  // the 16 lanes of a half warp write 32 different banks
+  // ---- column-wise 16x1 blocks (transposed output): a thread takes two adjacent columns (one 32-bit word per tile
+  // row) and two consecutive blocks of 16 rows; the 32 lanes of a warp read 32 consecutive words of a row
   if (COL) {
     const int cp = t & 63, rb0 = (t >> 6) * 2;
+    const uint8_t* src = s.tile[cp >> 5] + (cp & 3) * 4;
+    uint32_t xoff[8];  // the 16-byte chunk of this column pair in a row with (row & 7) == j
+#pragma unroll
+    for (int j = 0; j < 8; ++j) xoff[j] = (uint32_t)((((cp & 31) >> 2) ^ j) << 4);
     uint32_t spair[2] = {0, 0};
+    uint32_t ccodes[2][4];  // per column: the 32 rows of this thread's two blocks, 16 bytes
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       const int rb = rb0 + i;
       uint32_t w[16];
 #pragma unroll
-      for (int k = 0; k < 16; ++k) w[k] = *reinterpret_cast<const uint32_t*>(&tile[(rb * 16 + k) * kPitch + 2 * cp]);
+      for (int k = 0; k < 16; ++k) w[k] = *reinterpret_cast<const uint32_t*>(src + (rb * 16 + k) * 128 + xoff[k & 7]);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {  // low halves: column 2cp, high halves: column 2cp + 1
         const int c = 2 * cp + h;
@@ -445,45 +489,47 @@ __global__ void __launch_bounds__(256) nvfp4_tile_kernel(const Nvfp4Params p) {
           x[k] = h ? pack2u(w[2 * k] & 0xFFFF0000u, w[2 * k + 1] & 0xFFFF0000u) : pack2u(w[2 * k] << 16, w[2 * k + 1] << 16);
           if (!W2D) m = absmax3(m, x[k]);
         }
-        const float bamax = W2D ? tile_amax[rb * 8 + (c >> 4)] : m;
+        const float bamax = W2D ? s.tile_amax[rb * 8 + (c >> 4)] : m;
         uint32_t lo, hi, sbyte;
         if (ENC) {
-          nvfp4_codes16_encode(x, bamax, s_enc, enc_steps, sbyte, lo, hi);
+          nvfp4_codes16_encode(x, bamax, s_enc, s.enc_steps, sbyte, lo, hi);
         } else {
           sbyte = nvfp4_scale_byte(bamax, g, inv6g);
-          nvfp4_codes16(x, bamax, steps, sbyte, lo, hi);
+          nvfp4_codes16(x, bamax, s.steps, sbyte, lo, hi);
         }
-        *reinterpret_cast<uint2*>(&cb_col[c * 80 + ((rb ^ ((c >> 3) & 3)) * 8)]) = make_uint2(lo, hi);
+        ccodes[h][2 * i] = lo;
+        ccodes[h][2 * i + 1] = hi;
         spair[h] |= sbyte << (8 * i);
       }
     }
     // transposed tensor: row = c (within this tile's 128 columns), kblock = rb (within 8); two consecutive blocks
     // are two adjacent bytes of a page
 #pragma unroll
-    for (int h = 0; h < 2; ++h)
-      *reinterpret_cast<uint16_t*>(&sc_col[(rb0 >> 2) * 512 + page_offset(2 * cp + h, rb0)]) = (uint16_t)spair[h];
-  }
-  __syncthreads();
-  // ---- write the staged scale pages and transposed codes ------------------------------
-  if (t < 64) {
-    const int page = t >> 5, off = (t & 31) * 16;
-    uint8_t* dst = p.scales_row + ((row0 / 128) * (p.cols / 64) + col0 / 64 + page) * 512 + off;
-    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&sc_row[page * 512 + off]);
-  } else if (COL && t < 128) {
-    const int u = t - 64;
-    const int page = u >> 5, off = (u & 31) * 16;
-    uint8_t* dst = p.scales_col + ((col0 / 128) * (p.rows / 64) + row0 / 64 + page) * 512 + off;
-    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&sc_col[page * 512 + off]);
-  }
-  if (COL) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int chunk = t + i * 256;  // 1024 slots of 8 bytes: the 16 row pairs of block rb of column c
-      const int c = chunk >> 3, rb = chunk & 7;
-      *reinterpret_cast<uint2*>(p.codes_col + (col0 + c) * (p.rows / 2) + row0 / 2 + rb * 8) =
-          *reinterpret_cast<const uint2*>(&cb_col[c * 80 + ((rb ^ ((c >> 3) & 3)) * 8)]);
+    for (int h = 0; h < 2; ++h) {
+      *reinterpret_cast<uint4*>(&s.out_col[swizzled_offset((uint32_t)(2 * cp + h), (uint32_t)rb0 * 8u, 64)]) =
+          make_uint4(ccodes[h][0], ccodes[h][1], ccodes[h][2], ccodes[h][3]);
+      *reinterpret_cast<uint16_t*>(&s.sc_col[(rb0 >> 2) * 512 + page_offset(2 * cp + h, rb0)]) = (uint16_t)spair[h];
     }
   }
+  fence_async_smem();  // the code planes are read by TMA stores
+  __syncthreads();
+  // ---- codes leave as TMA stores, the scale pages as 16-byte words ------------------------------
+  if (t == 0) {
+    tma_store_2d(&map_row, s.out_row, (int)(col0 / 2), (int)row0);
+    if (COL) tma_store_2d(&map_col, s.out_col, (int)(row0 / 2), (int)col0);
+    tma_store_commit();
+  } else if (t >= 64 && t < 128) {
+    const int u = t - 64;
+    const int page = u >> 5, off = (u & 31) * 16;
+    uint8_t* dst = p.scales_row + ((row0 / 128) * (p.cols / 64) + col0 / 64 + page) * 512 + off;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&s.sc_row[page * 512 + off]);
+  } else if (COL && t >= 128 && t < 192) {
+    const int u = t - 128;
+    const int page = u >> 5, off = (u & 31) * 16;
+    uint8_t* dst = p.scales_col + ((col0 / 128) * (p.rows / 64) + row0 / 64 + page) * 512 + off;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&s.sc_col[page * 512 + off]);
+  }
+  if (t == 0) tma_store_wait_read();  // shared memory stays allocated until the stores have read it
 }
 
 // ------------------------------------------------------------------ MXFP4
@@ -573,17 +619,43 @@ static int check_matrix(const void* x, int64_t rows, int64_t cols, int64_t ld) {
 
 using namespace fa4b;
 
-template <int STAGE, bool W2D>
-static void launch_nvfp4_stage(const Nvfp4Params& p, dim3 grid, cudaStream_t st) {
-  const bool col = p.codes_col != nullptr, enc = !W2D && p.recipe == FA4B_RECIPE_ENCODE_CENTRIC;
-  if (col) {
-    if (enc) nvfp4_tile_kernel<STAGE, true, W2D, !W2D><<<grid, 256, 0, st>>>(p);
-    else nvfp4_tile_kernel<STAGE, true, W2D, false><<<grid, 256, 0, st>>>(p);
-  } else {
-    if (enc) nvfp4_tile_kernel<STAGE, false, W2D, !W2D><<<grid, 256, 0, st>>>(p);
-    else nvfp4_tile_kernel<STAGE, false, W2D, false><<<grid, 256, 0, st>>>(p);
-  }
+struct TileMaps {
+  CUtensorMap x, row, col;
+};
+template <int STAGE, bool COL, bool W2D, bool ENC>
+static int launch_nvfp4_kernel(const Nvfp4Params& p, const TileMaps& m, dim3 grid, cudaStream_t st) {
+  FA4B_CUDA(cudaFuncSetAttribute(nvfp4_tile_kernel<STAGE, COL, W2D, ENC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileSmemBytes));
+  nvfp4_tile_kernel<STAGE, COL, W2D, ENC><<<grid, 256, kTileSmemBytes, st>>>(p, m.x, m.row, m.col);
+  return FA4B_OK;
 }
+template <int STAGE, bool W2D>
+static int launch_nvfp4_stage(const Nvfp4Params& p, const TileMaps& m, dim3 grid, cudaStream_t st) {
+  const bool col = p.codes_col != nullptr, enc = !W2D && p.recipe == FA4B_RECIPE_ENCODE_CENTRIC;
+  if (col) return enc ? launch_nvfp4_kernel<STAGE, true, W2D, !W2D>(p, m, grid, st) : launch_nvfp4_kernel<STAGE, true, W2D, false>(p, m, grid, st);
+  return enc ? launch_nvfp4_kernel<STAGE, false, W2D, !W2D>(p, m, grid, st) : launch_nvfp4_kernel<STAGE, false, W2D, false>(p, m, grid, st);
+}
+// The tensor maps of one call: the bf16 matrix in boxes of 64 columns x 128 rows (plain staging only), the two code
+// planes in boxes of 64 bytes x 128 rows.
+static int launch_nvfp4(const Nvfp4Params& p, int stage, cudaStream_t st, bool weight_tiles = false) {
+  dim3 grid((unsigned)(p.cols / 128), (unsigned)(p.rows / 128));
+  TileMaps m;
+  if (int s = make_tensor_map(&m.row, p.codes_row, 1, (uint64_t)p.cols / 2, (uint64_t)p.rows, 0, (uint64_t)p.cols / 2, 0, 64, 128)) return s;
+  m.col = m.row;
+  m.x = m.row;
+  if (p.codes_col)
+    if (int s = make_tensor_map(&m.col, p.codes_col, 1, (uint64_t)p.rows / 2, (uint64_t)p.cols, 0, (uint64_t)p.rows / 2, 0, 64, 128)) return s;
+  if (stage == kStagePlain)
+    if (int s = make_tensor_map(&m.x, p.x, 2, (uint64_t)p.cols, (uint64_t)p.rows, 0, (uint64_t)p.ld * 2, 0, 64, 128)) return s;
+  int r;
+  if (weight_tiles) r = launch_nvfp4_stage<kStagePlain, true>(p, m, grid, st);
+  else if (stage == kStageNorm) r = launch_nvfp4_stage<kStageNorm, false>(p, m, grid, st);
+  else if (stage == kStageGrads) r = launch_nvfp4_stage<kStageGrads, false>(p, m, grid, st);
+  else r = launch_nvfp4_stage<kStagePlain, false>(p, m, grid, st);
+  if (r) return r;
+  FA4B_CUDA(cudaGetLastError());
+  return FA4B_OK;
+}
+
 extern "C" {
 
 const char* fa4b_last_error(void) { return fa4b::last_error(); }
@@ -614,16 +686,6 @@ int fa4b_amax(const void* x, int64_t n, float* amax, void* stream) {
   return FA4B_OK;
 }
 
-static int launch_nvfp4(const Nvfp4Params& p, int stage, cudaStream_t st, bool weight_tiles = false) {
-  dim3 grid((unsigned)(p.cols / 128), (unsigned)(p.rows / 128));
-  if (weight_tiles) launch_nvfp4_stage<kStagePlain, true>(p, grid, st);
-  else if (stage == kStageNorm) launch_nvfp4_stage<kStageNorm, false>(p, grid, st);
-  else if (stage == kStageGrads) launch_nvfp4_stage<kStageGrads, false>(p, grid, st);
-  else launch_nvfp4_stage<kStagePlain, false>(p, grid, st);
-  FA4B_CUDA(cudaGetLastError());
-  return FA4B_OK;
-}
-
 static int quant_nvfp4_impl(const fa4b_quant_nvfp4_args* a, void* stream, bool weight_tiles) {
   FA4B_REQUIRE(a != nullptr, FA4B_BAD_ARG, "args is NULL");
   if (int s = check_matrix(a->x, a->rows, a->cols, a->ld)) return s;
@@ -647,6 +709,19 @@ static int quant_nvfp4_impl(const fa4b_quant_nvfp4_args* a, void* stream, bool w
 }
 
 int fa4b_quant_nvfp4(const fa4b_quant_nvfp4_args* a, void* stream) { return quant_nvfp4_impl(a, stream, false); }
+
+int fa4b_quant_check_status(void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint32_t host[4] = {0, 0, 0, 0};
+  FA4B_CUDA(cudaMemcpyFromSymbolAsync(host, g_quant_status, sizeof(host), 0, cudaMemcpyDeviceToHost, st));
+  FA4B_CUDA(cudaStreamSynchronize(st));
+  if (host[0] == 0) return FA4B_OK;
+  const uint32_t zero[4] = {0, 0, 0, 0};
+  FA4B_CUDA(cudaMemcpyToSymbolAsync(g_quant_status, zero, sizeof(zero), 0, cudaMemcpyHostToDevice, st));
+  FA4B_CUDA(cudaStreamSynchronize(st));
+  set_error("a quantizer tile load did not arrive within the wait limit (site %u, block %u, tile row %u)", host[1], host[2], host[3]);
+  return FA4B_TIMEOUT;
+}
 
 int fa4b_quant_nvfp4_weight(const fa4b_quant_nvfp4_args* a, void* stream) { return quant_nvfp4_impl(a, stream, true); }
 

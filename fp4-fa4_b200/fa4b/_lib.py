@@ -111,7 +111,7 @@ class Info(C.Structure):
 
 
 EXPORTS = (
-    "fa4b_status_string", "fa4b_last_error", "fa4b_query", "fa4b_amax", "fa4b_quant_nvfp4", "fa4b_quant_nvfp4_weight", "fa4b_project_nvfp4", "fa4b_project_qkv_publish", "fa4b_project_dout_publish", "fa4b_rope_pair", "fa4b_pack_qkv_grads",
+    "fa4b_status_string", "fa4b_last_error", "fa4b_query", "fa4b_amax", "fa4b_quant_nvfp4", "fa4b_quant_check_status", "fa4b_quant_nvfp4_weight", "fa4b_project_nvfp4", "fa4b_project_qkv_publish", "fa4b_project_dout_publish", "fa4b_rope_pair", "fa4b_pack_qkv_grads",
     "fa4b_rmsnorm_quant_nvfp4", "fa4b_quant_mxfp4", "fa4b_dequant_nvfp4", "fa4b_dequant_mxfp4",
     "fa4b_attn_workspace_bytes", "fa4b_attn_ws_layout_query", "fa4b_attn_prepare", "fa4b_attn_fwd",
     "fa4b_attn_fwd_static", "fa4b_attn_bwd_preprocess", "fa4b_attn_bwd", "fa4b_attn_bwd_plan", "fa4b_attn_bwd_plan_item", "fa4b_attn_check_status", "fa4b_attn_merge", "fa4b_attn_accumulate", "fa4b_rmsnorm_bwd", "fa4b_rmsnorm_bwd_workspace_bytes", "fa4b_microgate", "fa4b_tensor_peak", "fa4b_wait_selftest",

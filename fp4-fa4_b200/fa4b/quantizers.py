@@ -67,6 +67,12 @@ def tk_quantize_for_gemm(input: torch.Tensor, return_transpose: bool = True, enc
     return fp4_row, sc_row, fp4_col, sc_col, sg, am
 
 
+def check_status() -> None:
+    """Synchronise the current stream and raise if a quantizer kernel's bounded wait for its tile ran out since the
+    last check (``fa4b_quant_check_status``; the kernels record the event instead of spinning)."""
+    check(lib().fa4b_quant_check_status(C.c_void_p(current_stream())), "fa4b_quant_check_status")
+
+
 def prepare_nvfp4_projection_weight(tensor: torch.Tensor):
     """Learned projection weight ``[N,K]`` with 16x16 NVFP4 scaling: ``(payload [N,K/2], scales
     [N/128,K/64,512], global [1])`` (b300_prepare_nvfp4_projection_weight, tk_fa4/interface.py:1221-1244)."""

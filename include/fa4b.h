@@ -101,6 +101,17 @@ typedef struct fa4b_quant_nvfp4_args {
 } fa4b_quant_nvfp4_args;
 int fa4b_quant_nvfp4(const fa4b_quant_nvfp4_args* a, void* stream);
 
+/* ---- fa4b_quant_check_status ----------------------------------------------
+ * The NVFP4 quantizer kernels (fa4b_quant_nvfp4, fa4b_quant_nvfp4_weight,
+ * fa4b_rmsnorm_quant_nvfp4, fa4b_pack_qkv_grads) wait for the TMA load of
+ * their tile with a cycle limit; a wait that runs out is recorded in a status
+ * word on the device instead of spinning.  This call synchronises the stream,
+ * reads that word, clears it and returns FA4B_TIMEOUT if it was set (the
+ * outputs of the affected call are then incomplete), FA4B_OK otherwise.  No
+ * reference counterpart: the reference's quantizers spin without a limit
+ * (TK_quantisation/nvfp4_v6/fused_amax_quantize.cuh:130-179). */
+int fa4b_quant_check_status(void* stream);
+
 /* ---- fa4b_quant_nvfp4_weight --------------------------------------------
  * The same outputs for a learned projection weight: one scale per 16 x 16
  * tile (the E4M3 byte of the tile's amax), stored once per 1 x 16 group of

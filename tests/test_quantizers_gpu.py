@@ -212,6 +212,20 @@ def test_pack_qkv_grads_is_the_oracle_of_rotation_then_quantisation_and_the_sepa
         _same(out[i], sep[i], f"separate passes: {what}")
 
 
+def test_quantizer_wait_status_is_clear_after_every_kind_of_call():
+    """The tile kernels wait for their TMA load with a cycle limit and record a wait that ran out; after ordinary
+    calls of every staging kind the record is clear."""
+    from fa4b import quantizers as Q
+
+    x, gamma = O.make_quantizer_inputs(256, 512, seed=9)
+    xd, gd = x.to(DEV), gamma.to(DEV)
+    fa4b.tk_quantize_for_gemm(xd, True, True)
+    fa4b.tk_quantize_for_gemm(xd, False, False)
+    fa4b.tk_fused_norm_quantize(xd, gd, 1e-6)
+    fa4b.prepare_nvfp4_projection_weight_dual(xd)
+    Q.check_status()
+
+
 def test_pack_qkv_grads_rejects_bad_layouts():
     cos, sin = (t.to(DEV) for t in O.rope_tables(128, 128))
     dq = torch.zeros(1, 128, 2, 128, dtype=torch.bfloat16, device=DEV)
