@@ -53,7 +53,16 @@ __device__ __forceinline__ __nv_bfloat162 absmax2(__nv_bfloat162 acc, uint32_t w
 __global__ void __launch_bounds__(256) amax_kernel(const uint4* __restrict__ x, int64_t n_vec, const __nv_bfloat16* tail,
                                                    int n_tail, float* __restrict__ amax) {
   __nv_bfloat162 acc = __float2bfloat162_rn(0.f);
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * blockDim.x) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n_vec; i += 4 * stride) {  // four independent loads in flight per thread
+    const uint4 v0 = __ldg(x + i), v1 = __ldg(x + i + stride), v2 = __ldg(x + i + 2 * stride), v3 = __ldg(x + i + 3 * stride);
+    acc = absmax2(absmax2(absmax2(absmax2(acc, v0.x), v0.y), v0.z), v0.w);
+    acc = absmax2(absmax2(absmax2(absmax2(acc, v1.x), v1.y), v1.z), v1.w);
+    acc = absmax2(absmax2(absmax2(absmax2(acc, v2.x), v2.y), v2.z), v2.w);
+    acc = absmax2(absmax2(absmax2(absmax2(acc, v3.x), v3.y), v3.z), v3.w);
+  }
+  for (; i < n_vec; i += stride) {
     const uint4 v = __ldg(x + i);
     acc = absmax2(absmax2(absmax2(absmax2(acc, v.x), v.y), v.z), v.w);
   }
