@@ -561,7 +561,7 @@ def run_ours(args, rank, world, local_rank):
                           f"a rank's inputs are {in_bytes >> 20} MiB: consecutive steps read different copies ({n_rot} copies, {n_rot * in_bytes >> 20} MiB > 2x L2)"),
                    "flops": "6 causal matmuls = 12*B*Hq*D*S(S+1)/2", "includes": "Q/K/V quantisation and dO/statistics publication"},
         "clocks": clocks,
-        "e2e": {"value": flops_job * args.steps / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
+        "e2e": {"value": (flops_job * args.steps / (e2e_ms * 1e-3) / 1e12) if e2e_ms == e2e_ms else None, "unit": UNIT,
                 "h2d_bytes_per_step": nbytes_in, "d2h_bytes_per_step": nbytes_out,
                 "returns": "O, dQ, dK, dV to pinned host memory every step (third stream, overlapped with the next step)",
                 "check": e2e_check},
