@@ -35,6 +35,11 @@ struct FwdSmem {
   alignas(1024) uint8_t k_codes[kStages][128 * D / 2];
   alignas(1024) uint8_t v[kStages][128 * D];   // E4M3 [keys][D]; MXFP4 route: codes [D][64 bytes] in the first half
   alignas(1024) uint8_t p_mx[2][128 * 32];     // MXFP4 route: P codes of one 64-key block per tile, [row][32 bytes]
+  // in-kernel Q quantisation: the tile's bf16 rows as boxes of [128 rows][128 bytes] (128-byte swizzle pattern), filled
+  // by coalesced loads; at D = 128 a thread's E4M3 row then takes the place of the first half of its own bf16 row
+  // (that box is the source of a TMA store), at D = 64 the E4M3 rows have a buffer of their own
+  alignas(1024) uint8_t q_stage[2][128 * 2 * D];
+  alignas(1024) uint8_t q8_stage[2][D == 128 ? 1024 : 128 * D];
   alignas(16) uint8_t q_sf[2][(D / 64) * 512];
   alignas(16) uint8_t k_sf[kStages][(D / 64) * 512];
   alignas(16) uint8_t v_sf[kStages][512];      // MXFP4 route: E8M0 page of the stage's V (row = feature)
@@ -94,7 +99,7 @@ __device__ __forceinline__ void ex2_pair(uint64_t e2, int pair, float& lo, float
 template <int D, bool MX>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                const __grid_constant__ CUtensorMap map_v) {
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_q8) {
   extern __shared__ uint8_t raw[];
   // aligned by offsetting the shared array itself, so that accesses stay shared-space loads and stores
   FwdSmem<D>& s = *reinterpret_cast<FwdSmem<D>*>(raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u));
@@ -215,6 +220,17 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
         if (leader) {
 #pragma unroll
           for (int pg = 0; pg < kPages; ++pg) tmem_cp_page(col_sfq + 4 * pg, make_page_desc(smem_u32(s.q_sf[ti] + 512 * pg)));
+          if (p.q_src && ti == 0) {
+            // the quantised queries of both tiles leave for the workspace (the backward's operands) as bulk copies
+            // from the buffers the softmax warps filled; this thread waits for their reads before it exits
+            for (int i = 0; i < (nb1 ? 2 : 1); ++i) {
+              const int qt = 2 * pi + i;
+              tma_store_3d(&map_q, s.q_codes[i], 0, qt * 128, bh);
+              tma_store_2d(&map_q8, D == 128 ? s.q_stage[i] : s.q8_stage[i], 0, bh * p.S + qt * 128);
+              bulk_store(p.q_sf_out + ((size_t)bh * n_tiles + qt) * kPages * 512, s.q_sf[i], kPages * 512);
+            }
+            tma_store_commit();
+          }
         }
         __syncwarp();
       }
@@ -286,6 +302,7 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       // every tensor-core operation of this CTA has finished before TMEM is freed
       if (leader) mma_commit(&s.mma_drained);
       if (leader) mbar_wait_teardown(&s.mma_drained, 0);
+      if (leader && p.q_src && ti == 0) tma_store_wait_read();  // the query copies have read their shared-memory sources
       __syncwarp();
     }
   } else {
@@ -308,48 +325,65 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       fill_step_table(s.steps, q_g, t);
       asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight softmax warps
       if (nb > 0) {
-        const int srow = qt * 128 + row;
-        const __nv_bfloat16* src = p.q_src + (int64_t)b * p.q_sb + (int64_t)h * p.q_sh + (int64_t)srow * p.q_ss;
-        const size_t row_index = (size_t)bh * p.S + srow;
+        // the tile's rows come in by coalesced loads of its 128 threads (a row is D / 8 chunks of 16 bytes) ...
+        constexpr int kChunks = D / 8;
+        const __nv_bfloat16* tile_src = p.q_src + (int64_t)b * p.q_sb + (int64_t)h * p.q_sh + (int64_t)(qt * 128) * p.q_ss;
+        uint4 raw[kChunks];
+#pragma unroll
+        for (int i = 0; i < kChunks; ++i) {
+          const int chunk = row + i * 128;
+          raw[i] = __ldg(reinterpret_cast<const uint4*>(tile_src + (int64_t)(chunk / kChunks) * p.q_ss) + chunk % kChunks);
+        }
+#pragma unroll
+        for (int i = 0; i < kChunks; ++i) {
+          const int chunk = row + i * 128, r = chunk / kChunks, c = chunk % kChunks;
+          *reinterpret_cast<uint4*>(&s.q_stage[ti][(c >> 3) * (128 * 128) + swizzled_offset((uint32_t)r, (uint32_t)(c & 7) * 16u, 128)]) = raw[i];
+        }
+        asm volatile("bar.sync %0, 128;" ::"r"(2 + ti) : "memory");  // the four warps of this tile
+        // ... and each thread takes its own row back (conflict-free: the eight lanes of a quarter warp are eight rows)
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c)
+          raw[c] = *reinterpret_cast<const uint4*>(&s.q_stage[ti][(c >> 3) * (128 * 128) + swizzled_offset((uint32_t)row, (uint32_t)(c & 7) * 16u, 128)]);
+        uint8_t* q8 = D == 128 ? s.q_stage[ti] : s.q8_stage[ti];
         uint32_t sw = 0;
-        uint4 raw[D / 8];  // the whole row in flight before the first block is worked on
 #pragma unroll
-        for (int c = 0; c < D / 8; ++c) raw[c] = __ldg(reinterpret_cast<const uint4*>(src) + c);
+        for (int kb2 = 0; kb2 < D / 32; ++kb2) {  // two 16-element blocks at a time: 16 bytes of codes
+          uint32_t cw[4] = {0, 0, 0, 0};
 #pragma unroll
-        for (int kb = 0; kb < D / 16; ++kb) {
-          const uint4 lo = raw[2 * kb], hi = raw[2 * kb + 1];
-          const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-          uint64_t xp[8];
-          uint32_t m2 = 0;
+          for (int hb = 0; hb < 2; ++hb) {
+            const int kb = 2 * kb2 + hb;
+            const uint4 lo = raw[2 * kb], hi = raw[2 * kb + 1];
+            const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            uint64_t xp[8];
+            uint32_t m2 = 0;
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            m2 = absmax_bf16x2(m2, w[k]);
-            xp[k] = bf16x2_to_f32x2(w[k]);
+            for (int k = 0; k < 8; ++k) {
+              m2 = absmax_bf16x2(m2, w[k]);
+              xp[k] = bf16x2_to_f32x2(w[k]);
+            }
+            const float bamax = fmaxf(bf16_bits_to_f32(m2 & 0xffffu), bf16_bits_to_f32(m2 >> 16));
+            uint32_t sbyte = 0;
+            if (!all_zero) {
+              sbyte = nvfp4_scale_byte(bamax, q_g, inv6g);
+              nvfp4_codes16(xp, bamax, s.steps, sbyte, cw[2 * hb], cw[2 * hb + 1]);
+            }
+            sw |= sbyte << (8 * (kb & 3));
+            uint32_t o8[4];
+            const uint64_t four = pack2(4.f, 4.f);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              float a0, a1, b0, b1;
+              unpack2(mul2(xp[2 * k], four), a0, a1);
+              unpack2(mul2(xp[2 * k + 1], four), b0, b1);
+              o8[k] = cvt_e4m3x4(a0, a1, b0, b1);
+            }
+            *reinterpret_cast<uint4*>(&q8[swizzled_offset((uint32_t)row, (uint32_t)kb * 16u, D)]) = make_uint4(o8[0], o8[1], o8[2], o8[3]);
           }
-          const float bamax = fmaxf(bf16_bits_to_f32(m2 & 0xffffu), bf16_bits_to_f32(m2 >> 16));
-          uint32_t c0 = 0, c1 = 0, sbyte = 0;
-          if (!all_zero) {
-            sbyte = nvfp4_scale_byte(bamax, q_g, inv6g);
-            nvfp4_codes16(xp, bamax, s.steps, sbyte, c0, c1);
-          }
-          *reinterpret_cast<uint2*>(&s.q_codes[ti][swizzled_offset((uint32_t)row, (uint32_t)kb * 8u, D / 2)]) = make_uint2(c0, c1);
-          *reinterpret_cast<uint2*>(p.q_codes_out + row_index * (D / 2) + kb * 8) = make_uint2(c0, c1);
-          sw |= sbyte << (8 * (kb & 3));
-          if ((kb & 3) == 3) {  // the four scale bytes of this row in one page are one aligned word
-            *reinterpret_cast<uint32_t*>(&s.q_sf[ti][(kb >> 2) * 512 + page_offset((uint32_t)row, 0)]) = sw;
-            *reinterpret_cast<uint32_t*>(p.q_sf_out + (((size_t)bh * n_tiles + qt) * kPages + (kb >> 2)) * 512 + page_offset((uint32_t)row, 0)) = sw;
+          *reinterpret_cast<uint4*>(&s.q_codes[ti][swizzled_offset((uint32_t)row, (uint32_t)kb2 * 16u, D / 2)]) = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+          if ((kb2 & 1) == 1) {  // the four scale bytes of this row in one page are one aligned word
+            *reinterpret_cast<uint32_t*>(&s.q_sf[ti][(kb2 >> 1) * 512 + page_offset((uint32_t)row, 0)]) = sw;
             sw = 0;
           }
-          uint32_t o8[4];
-          const uint64_t four = pack2(4.f, 4.f);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            float a0, a1, b0, b1;
-            unpack2(mul2(xp[2 * k], four), a0, a1);
-            unpack2(mul2(xp[2 * k + 1], four), b0, b1);
-            o8[k] = cvt_e4m3x4(a0, a1, b0, b1);
-          }
-          *reinterpret_cast<uint4*>(p.q_fp8_out + row_index * D + kb * 16) = make_uint4(o8[0], o8[1], o8[2], o8[3]);
         }
         if (pi == 0 && ti == 0 && row == 0) {  // once per head
           p.q_global_out[bh] = q_g;
@@ -579,7 +613,7 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   uint8_t* ws = static_cast<uint8_t*>(a.ws);
   // K and V operands may come from a second cache of the same layout (another sequence shard)
   uint8_t* kvws = a.kv_ws ? static_cast<uint8_t*>(const_cast<void*>(a.kv_ws)) : ws;
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mq8;
   const uint64_t S = d.S;
   if (int s = make_tensor_map(&mq, ws + l.q_codes, 1, D / 2, S, (uint64_t)d.B * d.Hq, D / 2, S * (D / 2), D / 2, 128)) return s;
   if (int s = make_tensor_map(&mk, kvws + l.k_codes, 1, D / 2, S, (uint64_t)d.B * d.Hkv, D / 2, S * (D / 2), D / 2, 128)) return s;
@@ -588,6 +622,8 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   } else {
     if (int s = make_tensor_map(&mv, kvws + l.v_fp8, 1, D, S, (uint64_t)d.B * d.Hkv, D, S * D, D, 128)) return s;
   }
+  // E4M3 queries [B*Hq*S][D]: the kernel's own quantisation writes them as boxes of 128 rows
+  if (int s = make_tensor_map(&mq8, ws + l.q_fp8, 1, D, S * d.B * d.Hq, 0, D, 0, D, 128)) return s;
   FwdParams p{};
   p.B = d.B; p.Hq = d.Hq; p.Hkv = d.Hkv; p.S = d.S;
   p.scale_log2 = resolve_scale(d) * kLog2e;
@@ -623,7 +659,7 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   }
   const unsigned grid = (unsigned)(d.B * d.Hq * ((d.S / 128 + 1) / 2));
   if (a.ev_before) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_before), st));
-  attn_fwd_kernel<D, MX><<<grid, kFwdThreads, smem, st>>>(p, mq, mk, mv);
+  attn_fwd_kernel<D, MX><<<grid, kFwdThreads, smem, st>>>(p, mq, mk, mv, mq8);
   FA4B_CUDA(cudaGetLastError());
   if (a.ev_after) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_after), st));
   return FA4B_OK;
