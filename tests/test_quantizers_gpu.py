@@ -226,6 +226,24 @@ def test_quantizer_wait_status_is_clear_after_every_kind_of_call():
     Q.check_status()
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
+def test_quantizer_and_projection_on_a_second_device_of_the_same_process():
+    """Per-device kernel attributes (shared-memory opt-in) and per-device caches: the same process quantises and
+    projects on cuda:0 and then on cuda:1, with identical bytes."""
+    x, _ = O.make_quantizer_inputs(256, 512, seed=21)
+    w = (torch.randn(256, 512, generator=torch.Generator().manual_seed(22)) * 0.05).bfloat16()
+    outs = []
+    for dev in ("cuda:0", "cuda:1"):
+        with torch.cuda.device(dev):
+            a = fa4b.tk_quantize_for_gemm(x.to(dev), return_transpose=True, encode_centric=False)
+            wq = fa4b.prepare_nvfp4_projection_weight(w.to(dev))
+            y = fa4b.project_nvfp4((a[0], a[1], a[4]), wq)
+            torch.cuda.synchronize(dev)
+            outs.append([t.cpu() for t in a[:4]] + [y.cpu()])
+    for t0, t1 in zip(*outs):
+        assert torch.equal(t0, t1)
+
+
 def test_pack_qkv_grads_rejects_bad_layouts():
     cos, sin = (t.to(DEV) for t in O.rope_tables(128, 128))
     dq = torch.zeros(1, 128, 2, 128, dtype=torch.bfloat16, device=DEV)
