@@ -244,6 +244,34 @@ def test_quantizer_and_projection_on_a_second_device_of_the_same_process():
         assert torch.equal(t0, t1)
 
 
+def test_pack_qkv_grads_at_the_layer_shape_equals_the_separate_passes():
+    """Llama-3-8B layer shape (B2, S8192, Hq32, Hkv8, D128: a [16384, 6144] gradient matrix): the one-pass packer and
+    the rotation + quantiser passes it replaces write the same bytes; the transposed plane is the row plane of the
+    transposed matrix (checked on a slab through the decode utility)."""
+    from fa4b import quantizers as Q
+
+    B, S, Hq, Hkv, D = 2, 8192, 32, 8, 128
+    g = torch.Generator(device=DEV).manual_seed(77)
+    N = (Hq + 2 * Hkv) * D
+    buf = (torch.randn(B * S, N, device=DEV, generator=g) * 0.02).bfloat16()
+    views = (buf[:, :Hq * D].view(B, S, Hq, D), buf[:, Hq * D:(Hq + Hkv) * D].view(B, S, Hkv, D), buf[:, (Hq + Hkv) * D:].view(B, S, Hkv, D))
+    cos, sin = (t.to(DEV) for t in O.rope_tables(S, D))
+    fused = fa4b.pack_qkv_grads(*views, cos, sin, return_transpose=True, encode_centric=False)
+    two = buf.clone()
+    fa4b.rope_pair_(two[:, :Hq * D].view(B, S, Hq, D), cos, sin, inverse=True)
+    fa4b.rope_pair_(two[:, Hq * D:(Hq + Hkv) * D].view(B, S, Hkv, D), cos, sin, inverse=True)
+    sep = fa4b.tk_quantize_for_gemm(two, return_transpose=True, encode_centric=False)
+    Q.check_status()
+    assert float(fused[5]) == float(sep[5]) and float(fused[4]) == float(sep[4])
+    for i, what in ((0, "row codes"), (1, "row scale pages"), (2, "transposed codes"), (3, "transposed scale pages")):
+        assert torch.equal(fused[i], sep[i]), what
+    # a slab of the transposed plane decodes to the transpose of the same slab of the row plane's source, block for block
+    rows = fa4b.dequant_nvfp4(fused[0][:256].contiguous(), fused[1][:2].contiguous(), fused[4])          # [256, N]
+    cols = fa4b.dequant_nvfp4(fused[2][:, :128].contiguous(), fused[3][:, :4].contiguous(), fused[4])    # [N, 256]
+    ref = two[:256].float()
+    assert O.rel_l2(ref.cpu(), rows.float().cpu()) < 0.12 and O.rel_l2(ref.t().cpu(), cols.float().cpu()) < 0.12
+
+
 def test_pack_qkv_grads_rejects_bad_layouts():
     cos, sin = (t.to(DEV) for t in O.rope_tables(128, 128))
     dq = torch.zeros(1, 128, 2, 128, dtype=torch.bfloat16, device=DEV)
