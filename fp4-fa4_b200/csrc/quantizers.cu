@@ -348,6 +348,131 @@ constexpr int kTileSmemBytes = (int)sizeof(TileSmem) + 1024;
 // status of the quantizer kernels' waits (word 0 != 0: a tile load did not arrive; words 1-3 as in the attention kernels)
 __device__ uint32_t g_quant_status[4];
 
+// The buffers one tile is worked in.
+struct TileBuffers {
+  const uint8_t* tile0;    // bf16 columns [0, 64): 128-byte rows, 128B swizzle
+  const uint8_t* tile1;    // bf16 columns [64, 128)
+  uint8_t* out_row;        // row-wise codes: a 64-byte row per tile row, 64B swizzle
+  uint8_t* out_col;        // transposed codes: a 64-byte row per tile column, 64B swizzle
+  uint8_t* sc_row;         // two scale pages of the row-wise codes
+  uint8_t* sc_col;         // two scale pages of the transposed codes
+  const StepTable* steps;
+  const EncodeTable* enc_steps;
+  float* tile_amax;        // W2D: amax of the 64 16 x 16 tiles
+};
+
+// W2D: amax of every 16 x 16 tile of the staged tile, four threads per tile, four rows each (ends with a block-wide barrier)
+__device__ __forceinline__ void tile_amax_pass(const TileBuffers& tb, int t) {
+  const int id = t >> 2, r0 = (id >> 3) * 16 + (t & 3) * 4, c0 = (id & 7) * 16;
+  uint32_t m2 = 0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const uint8_t* half = ((c0 >> 6) ? tb.tile1 : tb.tile0);
+    const uint4 a = *reinterpret_cast<const uint4*>(half + swizzled_offset((uint32_t)(r0 + k), (uint32_t)(c0 & 63) * 2u, 128));
+    const uint4 b = *reinterpret_cast<const uint4*>(half + swizzled_offset((uint32_t)(r0 + k), (uint32_t)(c0 & 63) * 2u + 16u, 128));
+    m2 = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(m2, a.x), a.y), a.z), a.w);
+    m2 = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(m2, b.x), b.y), b.z), b.w);
+  }
+  float m = fmaxf(bf16_bits_to_f32(m2 & 0xffffu), bf16_bits_to_f32(m2 >> 16));
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+  if ((t & 3) == 0) tb.tile_amax[id] = m;
+  __syncthreads();
+}
+
+// Row pass and column pass of one staged tile: codes and scale pages into the shared-memory buffers.
+template <bool COL, bool W2D, bool ENC>
+__device__ __forceinline__ void tile_passes(const TileBuffers& tb, int t, float g, float inv6g, float s_enc) {
+  // ---- row-wise 1x16 blocks: a thread takes half a row (four blocks of one 128-byte swizzled row).  The 32 lanes of a
+  // warp are 32 consecutive rows, so the eight lanes of a quarter warp read eight different 16-byte chunks.
+  {
+    const int r = t & 127, half = t >> 7;
+    const uint8_t* src = ((half) ? tb.tile1 : tb.tile0) + r * 128;
+    uint32_t sword = 0;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {  // 32 columns (two blocks) at a time
+      uint32_t w[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 v = *reinterpret_cast<const uint4*>(src + (((4 * i + j) ^ (r & 7)) << 4));
+        w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+      }
+      uint32_t codes[4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float m = 0.f;
+        uint64_t x[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          x[k] = bf16x2_to_f32x2(w[8 * h + k]);
+          if (!W2D) m = absmax3(m, x[k]);  // on the unpacked values: one three-input maximum per pair
+        }
+        const int kb = half * 4 + 2 * i + h;
+        const float bamax = W2D ? tb.tile_amax[(r >> 4) * 8 + kb] : m;
+        uint32_t sbyte;
+        if (ENC) {
+          nvfp4_codes16_encode(x, bamax, s_enc, (*tb.enc_steps), sbyte, codes[2 * h], codes[2 * h + 1]);
+        } else {
+          sbyte = nvfp4_scale_byte(bamax, g, inv6g);
+          nvfp4_codes16(x, bamax, (*tb.steps), sbyte, codes[2 * h], codes[2 * h + 1]);
+        }
+        sword |= sbyte << (8 * (2 * i + h));
+      }
+      *reinterpret_cast<uint4*>(&tb.out_row[swizzled_offset((uint32_t)r, (uint32_t)(half * 32 + i * 16), 64)]) =
+          make_uint4(codes[0], codes[1], codes[2], codes[3]);
+    }
+    // the four scale bytes of this half row are one aligned word of page `half`
+    *reinterpret_cast<uint32_t*>(&tb.sc_row[half * 512 + page_offset(r, 0)]) = sword;
+  }
+  // ---- column-wise 16x1 blocks (transposed output): a thread takes two adjacent columns (one 32-bit word per tile
+  // row) and two consecutive blocks of 16 rows; the 32 lanes of a warp read 32 consecutive words of a row
+  if (COL) {
+    const int cp = t & 63, rb0 = (t >> 6) * 2;
+    const uint8_t* src = ((cp >> 5) ? tb.tile1 : tb.tile0) + (cp & 3) * 4;
+    uint32_t xoff[8];  // the 16-byte chunk of this column pair in a row with (row & 7) == j
+#pragma unroll
+    for (int j = 0; j < 8; ++j) xoff[j] = (uint32_t)((((cp & 31) >> 2) ^ j) << 4);
+    uint32_t spair[2] = {0, 0};
+    uint32_t ccodes[2][4];  // per column: the 32 rows of this thread's two blocks, 16 bytes
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int rb = rb0 + i;
+      uint32_t w[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) w[k] = *reinterpret_cast<const uint32_t*>(src + (rb * 16 + k) * 128 + xoff[k & 7]);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {  // low halves: column 2cp, high halves: column 2cp + 1
+        const int c = 2 * cp + h;
+        uint64_t x[8];
+        float m = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          x[k] = h ? pack2u(w[2 * k] & 0xFFFF0000u, w[2 * k + 1] & 0xFFFF0000u) : pack2u(w[2 * k] << 16, w[2 * k + 1] << 16);
+          if (!W2D) m = absmax3(m, x[k]);
+        }
+        const float bamax = W2D ? tb.tile_amax[rb * 8 + (c >> 4)] : m;
+        uint32_t lo, hi, sbyte;
+        if (ENC) {
+          nvfp4_codes16_encode(x, bamax, s_enc, (*tb.enc_steps), sbyte, lo, hi);
+        } else {
+          sbyte = nvfp4_scale_byte(bamax, g, inv6g);
+          nvfp4_codes16(x, bamax, (*tb.steps), sbyte, lo, hi);
+        }
+        ccodes[h][2 * i] = lo;
+        ccodes[h][2 * i + 1] = hi;
+        spair[h] |= sbyte << (8 * i);
+      }
+    }
+    // transposed tensor: row = c (within this tile's 128 columns), kblock = rb (within 8); two consecutive blocks
+    // are two adjacent bytes of a page
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      *reinterpret_cast<uint4*>(&tb.out_col[swizzled_offset((uint32_t)(2 * cp + h), (uint32_t)rb0 * 8u, 64)]) =
+          make_uint4(ccodes[h][0], ccodes[h][1], ccodes[h][2], ccodes[h][3]);
+      *reinterpret_cast<uint16_t*>(&tb.sc_col[(rb0 >> 2) * 512 + page_offset(2 * cp + h, rb0)]) = (uint16_t)spair[h];
+    }
+  }}
+
 template <int STAGE, bool COL, bool W2D = false, bool ENC = false>
 __global__ void __launch_bounds__(256, 4) nvfp4_tile_kernel(const Nvfp4Params p, const __grid_constant__ CUtensorMap map_x,
                                                          const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col) {
@@ -413,113 +538,12 @@ __global__ void __launch_bounds__(256, 4) nvfp4_tile_kernel(const Nvfp4Params p,
       return;
     }
   }
-  if (W2D) {  // four threads per 16 x 16 tile, four rows each
-    const int id = t >> 2, r0 = (id >> 3) * 16 + (t & 3) * 4, c0 = (id & 7) * 16;
-    uint32_t m2 = 0;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const uint8_t* half = s.tile[c0 >> 6];
-      const uint4 a = *reinterpret_cast<const uint4*>(half + swizzled_offset((uint32_t)(r0 + k), (uint32_t)(c0 & 63) * 2u, 128));
-      const uint4 b = *reinterpret_cast<const uint4*>(half + swizzled_offset((uint32_t)(r0 + k), (uint32_t)(c0 & 63) * 2u + 16u, 128));
-      m2 = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(m2, a.x), a.y), a.z), a.w);
-      m2 = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(m2, b.x), b.y), b.z), b.w);
-    }
-    float m = fmaxf(bf16_bits_to_f32(m2 & 0xffffu), bf16_bits_to_f32(m2 >> 16));
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-    if ((t & 3) == 0) s.tile_amax[id] = m;
-    __syncthreads();
-  }
-
-  // ---- row-wise 1x16 blocks: a thread takes half a row (four blocks of one 128-byte swizzled row).  The 32 lanes of a
-  // warp are 32 consecutive rows, so the eight lanes of a quarter warp read eight different 16-byte chunks.
-  {
-    const int r = t & 127, half = t >> 7;
-    const uint8_t* src = s.tile[half] + r * 128;
-    uint32_t sword = 0;
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {  // 32 columns (two blocks) at a time
-      uint32_t w[16];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint4 v = *reinterpret_cast<const uint4*>(src + (((4 * i + j) ^ (r & 7)) << 4));
-        w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
-      }
-      uint32_t codes[4];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        float m = 0.f;
-        uint64_t x[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          x[k] = bf16x2_to_f32x2(w[8 * h + k]);
-          if (!W2D) m = absmax3(m, x[k]);  // on the unpacked values: one three-input maximum per pair
-        }
-        const int kb = half * 4 + 2 * i + h;
-        const float bamax = W2D ? s.tile_amax[(r >> 4) * 8 + kb] : m;
-        uint32_t sbyte;
-        if (ENC) {
-          nvfp4_codes16_encode(x, bamax, s_enc, s.enc_steps, sbyte, codes[2 * h], codes[2 * h + 1]);
-        } else {
-          sbyte = nvfp4_scale_byte(bamax, g, inv6g);
-          nvfp4_codes16(x, bamax, s.steps, sbyte, codes[2 * h], codes[2 * h + 1]);
-        }
-        sword |= sbyte << (8 * (2 * i + h));
-      }
-      *reinterpret_cast<uint4*>(&s.out_row[swizzled_offset((uint32_t)r, (uint32_t)(half * 32 + i * 16), 64)]) =
-          make_uint4(codes[0], codes[1], codes[2], codes[3]);
-    }
-    // the four scale bytes of this half row are one aligned word of page `half`
-    *reinterpret_cast<uint32_t*>(&s.sc_row[half * 512 + page_offset(r, 0)]) = sword;
-  }
-  // ---- column-wise 16x1 blocks (transposed output): a thread takes two adjacent columns (one 32-bit word per tile
-  // row) and two consecutive blocks of 16 rows; the 32 lanes of a warp read 32 consecutive words of a row
-  if (COL) {
-    const int cp = t & 63, rb0 = (t >> 6) * 2;
-    const uint8_t* src = s.tile[cp >> 5] + (cp & 3) * 4;
-    uint32_t xoff[8];  // the 16-byte chunk of this column pair in a row with (row & 7) == j
-#pragma unroll
-    for (int j = 0; j < 8; ++j) xoff[j] = (uint32_t)((((cp & 31) >> 2) ^ j) << 4);
-    uint32_t spair[2] = {0, 0};
-    uint32_t ccodes[2][4];  // per column: the 32 rows of this thread's two blocks, 16 bytes
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int rb = rb0 + i;
-      uint32_t w[16];
-#pragma unroll
-      for (int k = 0; k < 16; ++k) w[k] = *reinterpret_cast<const uint32_t*>(src + (rb * 16 + k) * 128 + xoff[k & 7]);
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {  // low halves: column 2cp, high halves: column 2cp + 1
-        const int c = 2 * cp + h;
-        uint64_t x[8];
-        float m = 0.f;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          x[k] = h ? pack2u(w[2 * k] & 0xFFFF0000u, w[2 * k + 1] & 0xFFFF0000u) : pack2u(w[2 * k] << 16, w[2 * k + 1] << 16);
-          if (!W2D) m = absmax3(m, x[k]);
-        }
-        const float bamax = W2D ? s.tile_amax[rb * 8 + (c >> 4)] : m;
-        uint32_t lo, hi, sbyte;
-        if (ENC) {
-          nvfp4_codes16_encode(x, bamax, s_enc, s.enc_steps, sbyte, lo, hi);
-        } else {
-          sbyte = nvfp4_scale_byte(bamax, g, inv6g);
-          nvfp4_codes16(x, bamax, s.steps, sbyte, lo, hi);
-        }
-        ccodes[h][2 * i] = lo;
-        ccodes[h][2 * i + 1] = hi;
-        spair[h] |= sbyte << (8 * i);
-      }
-    }
-    // transposed tensor: row = c (within this tile's 128 columns), kblock = rb (within 8); two consecutive blocks
-    // are two adjacent bytes of a page
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      *reinterpret_cast<uint4*>(&s.out_col[swizzled_offset((uint32_t)(2 * cp + h), (uint32_t)rb0 * 8u, 64)]) =
-          make_uint4(ccodes[h][0], ccodes[h][1], ccodes[h][2], ccodes[h][3]);
-      *reinterpret_cast<uint16_t*>(&s.sc_col[(rb0 >> 2) * 512 + page_offset(2 * cp + h, rb0)]) = (uint16_t)spair[h];
-    }
-  }
+  TileBuffers tb;
+  tb.tile0 = s.tile[0]; tb.tile1 = s.tile[1];
+  tb.out_row = s.out_row; tb.out_col = s.out_col; tb.sc_row = s.sc_row; tb.sc_col = s.sc_col;
+  tb.steps = &s.steps; tb.enc_steps = &s.enc_steps; tb.tile_amax = s.tile_amax;
+  if (W2D) tile_amax_pass(tb, t);
+  tile_passes<COL, W2D, ENC>(tb, t, g, inv6g, s_enc);
   fence_async_smem();  // the code planes are read by TMA stores
   __syncthreads();
   // ---- codes leave as TMA stores, the scale pages as 16-byte words ------------------------------
