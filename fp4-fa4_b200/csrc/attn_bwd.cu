@@ -52,7 +52,7 @@ struct BwdSmem {
   alignas(16) float dstat[kBwdStages][C::QT];
   alignas(16) float dq_patch[D == 64 ? 4 : 1][D == 64 ? 32 * 33 : 1];  // D = 64: per drain warp, 32 x 32 transposition patch
   alignas(16) float c2[16];  // per query head of the group: global scales * softmax scale * log2(e)
-  alignas(8) uint64_t kv_full, in_full[kBwdStages], in_empty[kBwdStages], st_full[2], dp_full[2], pt_ready[2], ds_ready[2], dq_full, dq_free,
+  alignas(8) uint64_t kv_full, in_full[kBwdStages], in_empty[kBwdStages], st_full[2], dp_full[2], dv_done[2], pt_ready[2], ds_ready[2], dq_full, dq_free,
       acc_done, mma_drained;
   uint32_t tmem_base;
   alignas(8) volatile uint32_t abort_flag;
@@ -166,6 +166,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     for (int i = 0; i < 2; ++i) {  // one set per compute group
       mbar_init(&s.st_full[i], 1);
       mbar_init(&s.dp_full[i], 1);
+      mbar_init(&s.dv_done[i], 1);
       mbar_init(&s.pt_ready[i], 8);  // one arrival per compute warp
       mbar_init(&s.ds_ready[i], 8);
     }
@@ -281,7 +282,8 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         __syncwarp();
       };
       // The two compute groups alternate sub-tiles and each runs  P(it); dS(it).  Per sub-tile:
-      //   pt_ready(it) -> dV(it), then dP(it) into the group's buffer (P has been read out of it)
+      //   pt_ready(it) -> dP(it) into the group's buffer (P has been read out of it), committed on its own because the
+      //                   group's dS step waits for it, then dV(it), whose completion the group observes before ds_ready
       //   ds_ready(it) -> S(it+2) into the same buffer (dS has been read out of it), dK(it); dQ(it)
       // Each stream runs in sub-tile order (the dQ drain relies on that order).
       auto pt_phase = [&](int it) -> bool {
@@ -294,10 +296,11 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           const uint64_t dd = d_do0 + st * kQ816, pt = d_pt0 + g * kPt16;
           const uint32_t acc = it > 0 ? 1u : 0u;
 #pragma unroll
-          for (int k = 0; k < QT / 32; ++k) mma_f8_ss(tm + C::colDV, pt + 2 * k, dd + kRow32D * k, id_dv, k > 0 ? 1u : acc);
-#pragma unroll
           for (int k = 0; k < D / 32; ++k) mma_f8_ss(tm + C::colX + g * QT, d_v8 + 2 * k, dd + 2 * k, id_dp, k > 0);
-          mma_commit(&s.dp_full[g]);
+          mma_commit(&s.dp_full[g]);  // the group waits for dP; dV follows behind it
+#pragma unroll
+          for (int k = 0; k < QT / 32; ++k) mma_f8_ss(tm + C::colDV, pt + 2 * k, dd + kRow32D * k, id_dv, k > 0 ? 1u : acc);
+          mma_commit(&s.dv_done[g]);
         }
         __syncwarp();
         return true;
@@ -508,6 +511,8 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           *reinterpret_cast<uint4*>(dst_row + ((uint32_t)(half * CW + c0 + 16 * i) ^ swz)) =
               make_uint4(dk4[4 * i], dk4[4 * i + 1], dk4[4 * i + 2], dk4[4 * i + 3]);
       }
+      // dV of this sub-tile has read P^T and dO by now: ds_ready hands both buffers on
+      if (!mbar_wait_warp(&s.dv_done[grp], (it >> 1) & 1, &s.abort_flag, p.status, 145, it)) return false;
       fence_async_smem();
       tc_fence_before();
       mbar_arrive_warp(&s.ds_ready[grp]);
