@@ -119,11 +119,17 @@ inline int bwd_chunk(const fa4b_attn_dims& d, int n_sm) {
 
 // (batch, kv head) units per launch group: as many as keep the group's FP32 dQ rows (Hq / Hkv query heads of S x D
 // floats per unit) within 72 MB, a little over half of the 126 MB L2 -- four units at S = 8192, D = 128, four query
-// heads per kv head
+// heads per kv head.  The same count serves the f16 sums (half the bytes): eight units per group measured slower.
 inline int bwd_head_group(const fa4b_attn_dims& d) {
   const long long per_unit = (long long)(d.Hq / d.Hkv) * d.S * d.D * 4;
   const long long fit = (72ll << 20) / per_unit;
   return (int)std::min<long long>(std::max<long long>(fit, 1), (long long)d.B * d.Hkv);
+}
+
+// Whether a backward call keeps its dQ sums as f16 (see BwdParams::dq_half) instead of FP32: when this one call forms
+// the whole sum (no FA4B_BWD_KEEP_DQ_ACCUM / FA4B_BWD_SKIP_DQ_OUT) and the caller has not asked for FP32 sums.
+inline bool bwd_dq_half(const fa4b_attn_dims&, int flags) {
+  return !(flags & (FA4B_BWD_KEEP_DQ_ACCUM | FA4B_BWD_SKIP_DQ_OUT | FA4B_BWD_DQ_SUMS_FP32));
 }
 
 // base to which the layout's transient offsets apply: the caller's separate scratch buffer, or the workspace itself

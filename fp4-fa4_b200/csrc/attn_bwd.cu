@@ -71,7 +71,12 @@ struct BwdParams {
   const float* k_global;
   const float* lstat;
   const float* dstat;
-  float* dq_accum;  // [B*Hq, S, D] f32, zeroed before launch
+  float* dq_accum;  // [B*Hq, S, D] f32, zeroed before launch; or (dq_half) packed f16 pairs, see below
+  // dq_half: the dQ sums are kept as f16 (32 * dQ), two per 32-bit word, so that a drain warp's reduction still
+  // covers 128 contiguous bytes but twice the values.  D = 128 (a drain lane holds one feature of 64 query rows):
+  // word ((bh * S / 2 + q / 2) * D + d) holds row q (even) in its low half and row q + 1 in its high half.
+  // D = 64 (a drain lane holds one query row): plain rows, word ((bh * S + q) * D / 2 + d / 2).
+  int dq_half;
   __nv_bfloat16* dk;
   int64_t dk_sb, dk_sh, dk_ss;
   __nv_bfloat16* dv;
@@ -85,6 +90,9 @@ struct BwdParams {
   float* dv_accum;
 };
 
+
+// f16 dQ sums hold the accumulator's value (1024 dQ) times this: 32 dQ, finite up to |dQ| = 2047
+constexpr float kDqHalfScale = 1.0f / 32.0f;
 
 __device__ __forceinline__ float ex2_approx_b(float x) {
   float y;
@@ -382,7 +390,23 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       tmem_ld_wait(v1);
       tc_fence_before();
       mbar_arrive_warp(&s.dq_free);  // the next dQ may overwrite the accumulator now
-      if (D == 128) {
+      if (D == 128 && p.dq_half) {
+        // lane = d, registers i, i + 1 = two adjacent query rows: one coalesced 128-byte f16x2 reduction per row pair
+        // (half the reductions and half the bytes of the FP32 form)
+        uint32_t* words = reinterpret_cast<uint32_t*>(p.dq_accum) + ((size_t)bh * p.S + (size_t)qs * QT) * (D / 2) + r;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const uint32_t(&v)[32] = hh ? v1 : v0;
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const __half2 h2 = __floats2half2_rn(__uint_as_float(v[i]) * kDqHalfScale, __uint_as_float(v[i + 1]) * kDqHalfScale);
+            asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(words + (size_t)((32 * hh + i) >> 1) * D),
+                         "r"(*reinterpret_cast<const uint32_t*>(&h2))
+                         : "memory");
+            if ((i & 15) == 14) drain_pause();
+          }
+        }
+      } else if (D == 128) {
         // lane = d, register i = query row: one coalesced 128-byte reduction per row
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -394,6 +418,22 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
           atomicAdd(base + (size_t)(32 + i) * D + r, __uint_as_float(v1[i]));
           if ((i & 7) == 7) drain_pause();
         }
+      } else if (p.dq_half) {
+        // lane = query row, registers 2 j, 2 j + 1 = two adjacent features: the row's 32 f16 pairs pass through this
+        // warp's shared-memory patch so that every reduction covers the 128 contiguous bytes of one row
+        uint32_t* words = reinterpret_cast<uint32_t*>(p.dq_accum) + ((size_t)bh * p.S + (size_t)qs * QT + w4 * 32) * (D / 2) + lane;
+        uint32_t* patch = reinterpret_cast<uint32_t*>(s.dq_patch[w4]);
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const uint32_t(&v)[32] = j < 16 ? v0 : v1;
+          const __half2 h2 = __floats2half2_rn(__uint_as_float(v[(2 * j) & 31]) * kDqHalfScale, __uint_as_float(v[(2 * j + 1) & 31]) * kDqHalfScale);
+          patch[lane * 33 + j] = *reinterpret_cast<const uint32_t*>(&h2);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int rr = 0; rr < 32; ++rr)
+          asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(words + (size_t)rr * (D / 2)), "r"(patch[rr * 33 + lane]) : "memory");
       } else {
         // lane = query row, register i = feature: transpose 32 x 32 blocks through this warp's shared-memory patch
         // so that every reduction instruction covers 128 contiguous bytes of one row (vector reductions of 16 bytes
@@ -582,6 +622,7 @@ struct ConvertJob {
   int64_t n_rows;  // heads * rows_per_head
   int H, rows_per_head;
   unsigned first_cta, n_cta;
+  int half_pairs;  // the accumulator holds f16 pairs of adjacent rows (BwdParams::dq_half)
 };
 struct ConvertJobs {
   ConvertJob job[3];
@@ -593,6 +634,55 @@ __global__ void __launch_bounds__(256) accum_convert_kernel(const ConvertJobs jo
   int which = 0;
   while (which + 1 < jobs.n && blockIdx.x >= jobs.job[which + 1].first_cta) ++which;
   const ConvertJob& jb = jobs.job[which];
+  if (jb.half_pairs && D == 64) {
+    // plain f16 rows: one thread converts eight features of one row
+    const uint32_t* acc = reinterpret_cast<const uint32_t*>(jb.acc);
+    constexpr float inv = 1.0f / (1024.0f * kDqHalfScale);
+    for (int64_t c = (int64_t)(blockIdx.x - jb.first_cta) * 256 + threadIdx.x; c < jb.n_rows * kPerRow; c += (int64_t)jb.n_cta * 256) {
+      const int64_t r = c / kPerRow;
+      const int cb = (int)(c % kPerRow) * 8;
+      const int bh = (int)(r / jb.rows_per_head), sidx = (int)(r % jb.rows_per_head);
+      const uint4 a = *reinterpret_cast<const uint4*>(acc + (((int64_t)bh * S + sidx) * D + cb) / 2);
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        const __nv_bfloat162 h = __floats2bfloat162_rn(f.x * inv, f.y * inv);
+        o[i] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(jb.out + (int64_t)(bh / jb.H) * jb.sb + (int64_t)(bh % jb.H) * jb.sh + (int64_t)sidx * jb.ss + cb) =
+          make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    return;
+  }
+  if (jb.half_pairs) {
+    // one thread: eight features of a pair of rows -- eight words in, two 16-byte stores out
+    const uint32_t* acc = reinterpret_cast<const uint32_t*>(jb.acc);
+    const int pairs_per_head = jb.rows_per_head / 2;
+    constexpr float inv = 1.0f / (1024.0f * kDqHalfScale);
+    for (int64_t c = (int64_t)(blockIdx.x - jb.first_cta) * 256 + threadIdx.x; c < jb.n_rows / 2 * kPerRow; c += (int64_t)jb.n_cta * 256) {
+      const int64_t pr = c / kPerRow;
+      const int cb = (int)(c % kPerRow) * 8;
+      const int bh = (int)(pr / pairs_per_head), pidx = (int)(pr % pairs_per_head);
+      const uint32_t* src = acc + ((int64_t)bh * (S / 2) + pidx) * D + cb;
+      const uint4 a = *reinterpret_cast<const uint4*>(src), bq = *reinterpret_cast<const uint4*>(src + 4);
+      const uint32_t w[8] = {a.x, a.y, a.z, a.w, bq.x, bq.y, bq.z, bq.w};
+      uint32_t even[4], odd[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w[2 * i]));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w[2 * i + 1]));
+        const __nv_bfloat162 e = __floats2bfloat162_rn(f0.x * inv, f1.x * inv), o = __floats2bfloat162_rn(f0.y * inv, f1.y * inv);
+        even[i] = *reinterpret_cast<const uint32_t*>(&e);
+        odd[i] = *reinterpret_cast<const uint32_t*>(&o);
+      }
+      __nv_bfloat16* dst = jb.out + (int64_t)(bh / jb.H) * jb.sb + (int64_t)(bh % jb.H) * jb.sh + (int64_t)(2 * pidx) * jb.ss + cb;
+      *reinterpret_cast<uint4*>(dst) = make_uint4(even[0], even[1], even[2], even[3]);
+      *reinterpret_cast<uint4*>(dst + jb.ss) = make_uint4(odd[0], odd[1], odd[2], odd[3]);
+    }
+    return;
+  }
   for (int64_t c = (int64_t)(blockIdx.x - jb.first_cta) * 256 + threadIdx.x; c < jb.n_rows * kPerRow; c += (int64_t)jb.n_cta * 256) {
     const int64_t r = c / kPerRow;
     const int cb = (int)(c % kPerRow) * 8;
@@ -612,13 +702,14 @@ __global__ void __launch_bounds__(256) accum_convert_kernel(const ConvertJobs jo
 }
 
 template <int D>
-static void add_convert_job(ConvertJobs& jobs, const float* acc, int H, int rows_per_head, int64_t n_heads, void* out, const fa4b_strides& st) {
+static void add_convert_job(ConvertJobs& jobs, const float* acc, int H, int rows_per_head, int64_t n_heads, void* out, const fa4b_strides& st,
+                            bool half_pairs = false) {
   const int64_t n_rows = n_heads * rows_per_head;
   if (n_rows == 0) return;
   ConvertJob& jb = jobs.job[jobs.n];
-  jb = ConvertJob{acc, static_cast<__nv_bfloat16*>(out), st.batch, st.head, st.seq, n_rows, H, rows_per_head, 0, 0};
+  jb = ConvertJob{acc, static_cast<__nv_bfloat16*>(out), st.batch, st.head, st.seq, n_rows, H, rows_per_head, 0, 0, half_pairs ? 1 : 0};
   jb.first_cta = jobs.n ? jobs.job[jobs.n - 1].first_cta + jobs.job[jobs.n - 1].n_cta : 0;
-  jb.n_cta = (unsigned)std::min<int64_t>((n_rows * (D / 8) + 255) / 256, (int64_t)std::max(sm_count(), 1) * 16);
+  jb.n_cta = (unsigned)std::min<int64_t>(((half_pairs && D == 128 ? n_rows / 2 : n_rows) * (D / 8) + 255) / 256, (int64_t)std::max(sm_count(), 1) * 16);
   ++jobs.n;
 }
 
@@ -658,12 +749,14 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   const int n_tiles = d.S / 128;
   p.chunk = bwd_chunk(d, n_sm);
   p.items_per_head = bwd_items_per_head(n_tiles, p.chunk, p.causal != 0);
+  // f16 dQ sums: only where one call forms the whole sum (a sum kept across calls stays FP32), at D = 128
+  p.dq_half = bwd_dq_half(d, a.flags) ? 1 : 0;
   p.head_group = bwd_head_group(d);
   // rows of every kv head whose key tiles are cut into parts (the tiles that see more than `chunk` query tiles):
   // their dK and dV arrive as FP32 sums
   const int split_rows = n_tiles > p.chunk ? (p.causal ? (n_tiles - p.chunk) * 128 : d.S) : 0;
   FA4B_CUDA(cudaMemsetAsync(p.status, 0, 16, st));
-  if (!(a.flags & FA4B_BWD_KEEP_DQ_ACCUM)) FA4B_CUDA(cudaMemsetAsync(p.dq_accum, 0, nq * S * D * sizeof(float), st));
+  if (!(a.flags & FA4B_BWD_KEEP_DQ_ACCUM)) FA4B_CUDA(cudaMemsetAsync(p.dq_accum, 0, nq * S * D * (p.dq_half ? 2 : 4), st));
   if (split_rows)
     FA4B_CUDA(cudaMemset2DAsync(p.dk_accum, S * D * sizeof(float), 0, (size_t)split_rows * D * sizeof(float), 2 * nk, st));
   const int smem = (int)sizeof(BwdSmem<D>) + 1024;
@@ -685,7 +778,7 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   if (a.ev_after) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_after), st));
   // one launch rounds what arrived as FP32 sums: dQ, and dK / dV of the key tiles that were cut
   ConvertJobs jobs{};
-  if (!(a.flags & FA4B_BWD_SKIP_DQ_OUT)) add_convert_job<D>(jobs, p.dq_accum, d.Hq, d.S, (int64_t)nq, a.dq, a.dq_strides);
+  if (!(a.flags & FA4B_BWD_SKIP_DQ_OUT)) add_convert_job<D>(jobs, p.dq_accum, d.Hq, d.S, (int64_t)nq, a.dq, a.dq_strides, p.dq_half != 0);
   if (split_rows) {
     add_convert_job<D>(jobs, p.dk_accum, d.Hkv, split_rows, (int64_t)nk, a.dk, a.dk_strides);
     add_convert_job<D>(jobs, p.dv_accum, d.Hkv, split_rows, (int64_t)nk, a.dv, a.dv_strides);

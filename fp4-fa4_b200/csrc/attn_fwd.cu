@@ -453,6 +453,15 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       // P = 2^(x c2 - mhat + kLift): packed FMA for the exponent, the exponential unit or (6 of 16 columns) the FMA-pipe
       // polynomial for the power, packed add for the sum
       const uint64_t shift2 = pack2(kLift - mhat, kLift - mhat);
+      if constexpr (!MX) {
+        // The store of the previous block's P was left in flight so that its latency runs under the maximum pass
+        // above: it has landed now, and that block's P.V may be issued.
+        if (j > 0) {
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive_warp(&s.p_ready[ti][(j - 1) & 1]);
+        }
+      }
       uint32_t pa[8], pb[8];  // FP8 route: P as E4M3 words; MXFP4 route: pa = the block's 64 E2M1 codes
       float pf[MX ? 64 : 1];  // MXFP4 route: the un-quantised probabilities, quantised per 32 keys below
       if (diag) {
@@ -560,13 +569,20 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
           *reinterpret_cast<uint4*>(&s.p_mx[ti][swizzled_offset(row, 16, 32)]) = make_uint4(pa[4], pa[5], pa[6], pa[7]);
           *reinterpret_cast<uint16_t*>(&s.p_sf[ti][page_offset(row, 0)]) = (uint16_t)p_scales;
           fence_async_smem();
+          tc_fence_before();
+          mbar_arrive_warp(&s.p_ready[ti][j & 1]);
         } else {
+          // completion is observed in the next iteration, or after the loop
           tmem_st8(lane_base + kColP + 16 * ti, pa);
           tmem_st8(lane_base + kColP + 16 * ti + 8, pb);
-          tmem_st_wait();
         }
+      }
+    }
+    if constexpr (!MX) {
+      if (ok) {
+        tmem_st_wait();
         tc_fence_before();
-        mbar_arrive_warp(&s.p_ready[ti][j & 1]);
+        mbar_arrive_warp(&s.p_ready[ti][(nb - 1) & 1]);
       }
     }
     float lsum;

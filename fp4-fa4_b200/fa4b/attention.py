@@ -249,10 +249,13 @@ def attn_merge(o_acc: torch.Tensor, lse_acc: torch.Tensor, o_part: torch.Tensor,
                                 C.c_void_p(current_stream())), "fa4b_attn_merge")
 
 
-def attn_backward(o, lse, dout, ws: Workspace, preprocessed: bool = False, events=(None, None), out=None):
+def attn_backward(o, lse, dout, ws: Workspace, preprocessed: bool = False, events=(None, None), out=None,
+                  dq_sums_fp32: bool = False):
     """dQ ``[B,Hq,S,D]``, dK, dV ``[B,Hkv,S,D]`` bf16, replaying the operands the forward cached in ``ws``.
     ``out=(dq, dk, dv)`` supplies the destinations: bf16 views of those shapes with any strides (e.g. the column
-    ranges of one ``[B*S, (Hq + 2 Hkv) D]`` buffer)."""
+    ranges of one ``[B*S, (Hq + 2 Hkv) D]`` buffer).  At D = 128 the key tiles' partial dQ sums meet as f16 pairs
+    (half the reduction traffic of FP32 sums; the sums of two runs differ in the last bits of bf16);
+    ``dq_sums_fp32`` keeps them in FP32."""
     for t, n in ((o, "o"), (dout, "dout")):
         _check_bhsd(t, n)
     d = ws.dims
@@ -267,12 +270,13 @@ def attn_backward(o, lse, dout, ws: Workspace, preprocessed: bool = False, event
             if tuple(t.shape) != (d.B, h, d.S, d.D):
                 raise ValueError(f"{n} must be shaped {(d.B, h, d.S, d.D)}, got {tuple(t.shape)}")
     a = _lib.AttnBwdArgs(d, ptr(o), _strides(o), ptr(dout), _strides(dout), ptr(lse), ptr(dq), _strides(dq), ptr(dk), _strides(dk),
-                         ptr(dv), _strides(dv), ptr(ws.buf), int(preprocessed), _ev(events[0]), _ev(events[1]), 0, 0, ptr(ws.scratch))
+                         ptr(dv), _strides(dv), ptr(ws.buf), int(preprocessed), _ev(events[0]), _ev(events[1]), 0,
+                         BWD_DQ_SUMS_FP32 if dq_sums_fp32 else 0, ptr(ws.scratch))
     check(lib().fa4b_attn_bwd(C.byref(a), C.c_void_p(current_stream())), "fa4b_attn_bwd")
     return dq, dk, dv
 
 
-BWD_KEEP_DQ_ACCUM, BWD_SKIP_DQ_OUT = 1, 2
+BWD_KEEP_DQ_ACCUM, BWD_SKIP_DQ_OUT, BWD_DQ_SUMS_FP32 = 1, 2, 4
 
 
 def attn_backward_prepared(ws: Workspace, kv_ws: Workspace | None = None, causal: bool = True, keep_dq_accum: bool = False,

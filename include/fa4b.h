@@ -50,7 +50,11 @@ enum { FA4B_MX_CEIL = 0, FA4B_MX_RTE_MANTISSA = 1, FA4B_MX_FLOOR = 2 };
  * TK_quantisation/nvfp4_v6/fused_amax_quantize.cuh:235-256) */
 enum { FA4B_RECIPE_DECODE_CENTRIC = 0, FA4B_RECIPE_ENCODE_CENTRIC = 1 };
 /* fa4b_attn_bwd flags: a sequence-sharded run folds several key shards into one query shard's dQ */
-enum { FA4B_BWD_KEEP_DQ_ACCUM = 1 /* do not zero the accumulator first */, FA4B_BWD_SKIP_DQ_OUT = 2 /* do not convert it into dq */ };
+enum {
+  FA4B_BWD_KEEP_DQ_ACCUM = 1 /* do not zero the accumulator first */,
+  FA4B_BWD_SKIP_DQ_OUT = 2 /* do not convert it into dq */,
+  FA4B_BWD_DQ_SUMS_FP32 = 4 /* keep the partial dQ sums in FP32 where the call would keep them as f16 pairs */
+};
 enum { FA4B_PREPARE_ALL = 0, FA4B_PREPARE_AMAX = 1, FA4B_PREPARE_QUANTIZE = 2 };
 enum { FA4B_LAYOUT_BHSD = 0, FA4B_LAYOUT_BSHD = 1 };
 
@@ -424,7 +428,7 @@ typedef struct fa4b_attn_bwd_args {
   void* ev_after;
   const void* kv_ws;    /* optional: a second operand cache of the same dims whose K and V sections are used instead
                            of `ws`'s (the keys of another sequence shard); the queries, dO and statistics stay `ws`'s */
-  int32_t flags;        /* FA4B_BWD_*: how this call treats the FP32 dQ accumulator */
+  int32_t flags;        /* FA4B_BWD_*: how this call treats the dQ accumulator */
   void* scratch;        /* optional, 1024-byte aligned: the transient section of the layout (total - saved_total
                            bytes) as a buffer of its own; `ws` then only needs its first saved_total bytes.  NULL:
                            the transient section is the tail of `ws` */
@@ -435,7 +439,11 @@ int fa4b_attn_bwd_preprocess(const fa4b_attn_bwd_args* a, void* stream);
  * backward_nvfp4_score_e4m3_qkv_e5m2_dout_bshd_precleared_dq_out
  * (tk_fa4/native_gqa_tk_bwd/v509_*bshd.cu:406-444) and the D64 kernel v416.
  * Runs the preprocess step itself unless `preprocessed` is set.  Uses the
- * transient section's FP32 accumulators as scratch (dQ zeroed here unless FA4B_BWD_KEEP_DQ_ACCUM).  One CTA per
+ * transient section's accumulators as scratch (dQ zeroed here unless FA4B_BWD_KEEP_DQ_ACCUM).  The partial dQ sums of
+ * the key tiles meet in the dQ accumulator as f16 pairs (32 dQ per value: half the reduction traffic of FP32 sums, the
+ * reference's v420 adds them as bf16; dQ of two runs then differs by the order of those roundings, about 1e-3
+ * relative) when one call forms the whole sum; FA4B_BWD_DQ_SUMS_FP32 asks for FP32 sums, and a sum carried across
+ * calls (FA4B_BWD_KEEP_DQ_ACCUM, FA4B_BWD_SKIP_DQ_OUT) is always FP32.  One CTA per
  * (key tile, part of the tile's query range, batch and kv head), key-tile-major; in a launch of few heads a key
  * tile that sees more query tiles than the launch's chunk length is cut into parts whose dK / dV meet as FP32
  * sums (fa4b_attn_bwd_plan).  With

@@ -10,6 +10,9 @@ from fa4b import attention
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
+# dQ of two runs of the same problem: the key tiles' partial sums meet as f16 pairs in an order that differs from run
+# to run (7.5e-4 measured at S = 2048 ... 8192); with dq_sums_fp32 the difference is FP32 summation order only
+DQ_RERUN_TOL = 4e-3
 
 
 def _pages(scales):  # [B,H,S,D/16] bytes -> [B,H,S/128,D/64,512]
@@ -187,7 +190,7 @@ def test_partition_by_batch_and_kv_head_reproduces_the_unsharded_run():
     assert torch.equal(parallel.unshard_q_like(parts["lse"], B, Hq), lse)
     _assert_dkv_reproduce(ws.dims, parallel.unshard_kv_like(parts["dk"], B, Hkv), dk, "dk")
     _assert_dkv_reproduce(ws.dims, parallel.unshard_kv_like(parts["dv"], B, Hkv), dv, "dv")
-    assert O.rel_l2(dq.float().cpu(), parallel.unshard_q_like(parts["dq"], B, Hq).float().cpu()) < 1e-3
+    assert O.rel_l2(dq.float().cpu(), parallel.unshard_q_like(parts["dq"], B, Hq).float().cpu()) < DQ_RERUN_TOL
 
 
 @pytest.mark.parametrize("B,Hq,Hkv,S,D", [(1, 4, 1, 256, 128), (1, 4, 4, 512, 64), (2, 8, 2, 384, 128)])
@@ -293,7 +296,7 @@ def test_full_size_properties_at_the_benchmark_shape():
     ws.check_status()
     _assert_dkv_reproduce(ws.dims, dk2, dk, "dk")
     _assert_dkv_reproduce(ws.dims, dv2, dv, "dv")
-    assert O.rel_l2(dq.float().cpu(), dq2.float().cpu()) < 1e-3
+    assert O.rel_l2(dq.float().cpu(), dq2.float().cpu()) < DQ_RERUN_TOL
     dq0, dk0, dv0 = attention.attn_backward(o, lse, torch.zeros_like(dod), ws)
     ws.check_status()
     assert not dq0.any() and not dk0.any() and not dv0.any()
@@ -320,7 +323,7 @@ def test_forward_and_backward_replay_from_a_cuda_graph():
         assert torch.equal(o, o_ref) and torch.equal(lse, lse_ref)
         _assert_dkv_reproduce(ws.dims, dk, grads_ref[1], "dk")
         _assert_dkv_reproduce(ws.dims, dv, grads_ref[2], "dv")
-        assert O.rel_l2(grads_ref[0].float().cpu(), dq.float().cpu()) < 1e-3
+        assert O.rel_l2(grads_ref[0].float().cpu(), dq.float().cpu()) < DQ_RERUN_TOL
     ws_g.check_status()
 
 
@@ -380,3 +383,22 @@ def test_backward_block_calls_against_oracle_and_the_single_kernel():
         acc[:, :, :h], acc[:, :, h:] = lo, hi
     assert O.rel_l2(dq_ref.float().cpu(), torch.cat([dq0, dq1], dim=2).float().cpu()) < 2e-3
     assert O.rel_l2(dk_ref.float().cpu(), dk_acc.cpu()) < 4e-3 and O.rel_l2(dv_ref.float().cpu(), dv_acc.cpu()) < 4e-3
+
+
+@pytest.mark.parametrize("D,S", [(128, 2048), (64, 1024)])
+def test_dq_partial_sums_as_f16_pairs_or_fp32(D, S):
+    """The default backward adds the key tiles' partial dQ sums as f16 pairs (half the reduction traffic); both that
+    form and the FP32 form requested by dq_sums_fp32 stay within the dQ tolerance, the FP32 form an order of
+    magnitude closer to the oracle, and dK / dV do not depend on the choice."""
+    q, k, v, do = O.make_attention_inputs(1, 4, 1, S, D, seed=11, do_std=0.01)
+    fwd = O.attn_forward(q, k, v)
+    want = O.attn_backward(q, k, v, fwd.o, fwd.lse, do)
+    o, lse, ws = attention.attn_forward(q.to(DEV), k.to(DEV), v.to(DEV))
+    dq16, dk16, dv16 = attention.attn_backward(o, lse, do.to(DEV), ws)
+    dq32, dk32, dv32 = attention.attn_backward(o, lse, do.to(DEV), ws, dq_sums_fp32=True)
+    ws.check_status()
+    e16, e32 = O.rel_l2(want[0], dq16.float().cpu()), O.rel_l2(want[0], dq32.float().cpu())
+    assert e32 < 1e-3 and e16 < 4e-3, (e16, e32)
+    assert O.rel_l2(dq32.float().cpu(), dq16.float().cpu()) < DQ_RERUN_TOL
+    _assert_dkv_reproduce(ws.dims, dk16, dk32, "dk")
+    _assert_dkv_reproduce(ws.dims, dv16, dv32, "dv")

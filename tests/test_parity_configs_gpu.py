@@ -67,7 +67,7 @@ def test_custom_op_saves_only_the_operand_section_and_checks_it_on_the_way_back(
     # the same backward with the transient section as a caller-owned buffer, through the Python operator
     ws = attention.Workspace(attention.make_dims(q, k, None, "e4m3_fp8"), layout, saved)
     dq2, dk2, dv2 = attention.attn_backward(o, lse, do, ws.with_scratch(attention.alloc_scratch(ws.dims, DEV)))
-    assert torch.equal(dk2, dk) and torch.equal(dv2, dv) and O.rel_l2(dq.float().cpu(), dq2.float().cpu()) < 1e-3
+    assert torch.equal(dk2, dk) and torch.equal(dv2, dv) and O.rel_l2(dq.float().cpu(), dq2.float().cpu()) < 4e-3  # f16 partial sums, other order
 
 
 def test_wrapper_mxfp4_route_forward():
