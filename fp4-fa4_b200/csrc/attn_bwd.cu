@@ -52,7 +52,7 @@ struct BwdSmem {
   alignas(16) float dstat[kBwdStages][C::QT];
   alignas(16) float dq_patch[D == 64 ? 4 : 1][D == 64 ? 32 * 33 : 1];  // D = 64: per drain warp, 32 x 32 transposition patch
   alignas(16) float c2[16];  // per query head of the group: global scales * softmax scale * log2(e)
-  alignas(8) uint64_t kv_full, in_full[kBwdStages], in_empty[kBwdStages], st_full[2], dp_full[2], dv_done[2], pt_ready[2], ds_ready[2], dq_full, dq_free,
+  alignas(8) uint64_t kv_full, in_full[kBwdStages], in_empty[kBwdStages], st_full[2], dp_full[2], dv_done[2], pt_ready[2], s_read[2], x_free[2], ds_ready[2], dq_full, dq_free,
       acc_done, mma_drained;
   uint32_t tmem_base;
   alignas(8) volatile uint32_t abort_flag;
@@ -176,6 +176,8 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       mbar_init(&s.dp_full[i], 1);
       mbar_init(&s.dv_done[i], 1);
       mbar_init(&s.pt_ready[i], 8);  // one arrival per compute warp
+      mbar_init(&s.x_free[i], 8);
+      mbar_init(&s.s_read[i], 8);
       mbar_init(&s.ds_ready[i], 8);
     }
     mbar_init(&s.dq_full, 1);
@@ -298,14 +300,20 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         const uint32_t st = stage_of(it), g = it & 1;
         // dO of the stage arrives through the async proxy: this thread observes its barrier itself
         if (!mbar_wait_warp(&s.in_full[st], (it / kBwdStages) & 1, &s.abort_flag, p.status, 126, it)) return false;
+        // dP^T as soon as the scores have been read out of the group's buffer: it forms while the group computes P
+        if (!mbar_wait_warp(&s.s_read[g], (it >> 1) & 1, &s.abort_flag, p.status, 129, it)) return false;
+        tc_fence_after();
+        const uint64_t dd = d_do0 + st * kQ816, pt = d_pt0 + g * kPt16;
+        if (leader) {
+#pragma unroll
+          for (int k = 0; k < D / 32; ++k) mma_f8_ss(tm + C::colX + g * QT, d_v8 + 2 * k, dd + 2 * k, id_dp, k > 0);
+          mma_commit(&s.dp_full[g]);
+        }
+        __syncwarp();
         if (!mbar_wait_warp(&s.pt_ready[g], (it >> 1) & 1, &s.abort_flag, p.status, 122, it)) return false;
         tc_fence_after();
         if (leader) {
-          const uint64_t dd = d_do0 + st * kQ816, pt = d_pt0 + g * kPt16;
           const uint32_t acc = it > 0 ? 1u : 0u;
-#pragma unroll
-          for (int k = 0; k < D / 32; ++k) mma_f8_ss(tm + C::colX + g * QT, d_v8 + 2 * k, dd + 2 * k, id_dp, k > 0);
-          mma_commit(&s.dp_full[g]);  // the group waits for dP; dV follows behind it
 #pragma unroll
           for (int k = 0; k < QT / 32; ++k) mma_f8_ss(tm + C::colDV, pt + 2 * k, dd + kRow32D * k, id_dv, k > 0 ? 1u : acc);
           mma_commit(&s.dv_done[g]);
@@ -315,10 +323,15 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       };
       auto ds_phase = [&](int it) -> bool {
         const uint32_t st = stage_of(it), g = it & 1;
+        // the group's next scores as soon as dP^T of this sub-tile has been read out of the group's buffer: they
+        // form while the group still computes dS
+        if (it + 2 < n_it) {
+          if (!mbar_wait_warp(&s.x_free[g], (it >> 1) & 1, &s.abort_flag, p.status, 128, it)) return false;
+          tc_fence_after();
+          fire_s(it + 2);
+        }
         if (!mbar_wait_warp(&s.ds_ready[g], (it >> 1) & 1, &s.abort_flag, p.status, 123, it)) return false;
         tc_fence_after();
-        // the group's next scores first: its threads are about to wait for them
-        if (it + 2 < n_it) fire_s(it + 2);
         const uint32_t acc = it > 0 ? 1u : 0u;
         const uint64_t q8 = d_q80 + st * kQ816, ds = d_ds0 + g * kPt16;
         if (leader) {
@@ -485,6 +498,10 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         uint32_t v[32];
         tmem_ld32(lane_base + C::colX + grp * QT + half * CW + c0, v);
         tmem_ld_wait(v);
+        if (c0 + 32 >= CW) {  // the last read of the scores: dP^T of this sub-tile may take the buffer
+          tc_fence_before();
+          mbar_arrive_warp(&s.s_read[grp]);
+        }
         // LSE, and E4M3 rounds 2^8.0x back to 256.  The masked variant is a separate, warp-uniform
         // path so that the common one carries no compare/select per element.
         if (diag) {
@@ -535,6 +552,10 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         uint32_t v[32];
         tmem_ld32(lane_base + C::colX + grp * QT + half * CW + c0, v);
         tmem_ld_wait(v);
+        if (c0 + 32 >= CW) {  // the last read of the group's buffer for this sub-tile: S of the next one may take it
+          tc_fence_before();
+          mbar_arrive_warp(&s.x_free[grp]);
+        }
         uint32_t dk4[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
