@@ -51,6 +51,9 @@ struct BwdSmem {
   alignas(16) float lstat[kBwdStages][C::QT];
   alignas(16) float dstat[kBwdStages][C::QT];
   alignas(16) float dq_patch[D == 64 ? 4 : 1][D == 64 ? 32 * 33 : 1];  // D = 64: per drain warp, 32 x 32 transposition patch
+  // D = 128, f16 dQ sums: per drain warp the sub-tile's 32 row pairs x 32 features as words, in the accumulator's own
+  // order, two buffers: the source of one bulk reduction per warp and sub-tile
+  alignas(128) uint32_t dq_tile[D == 128 ? 2 : 1][D == 128 ? 4 : 1][D == 128 ? 32 * 32 : 4];
   alignas(16) float c2[16];  // per query head of the group: global scales * softmax scale * log2(e)
   alignas(8) uint64_t kv_full, in_full[kBwdStages], in_empty[kBwdStages], st_full[2], dp_full[2], dv_done[2], pt_ready[2], s_read[2], x_free[2], ds_ready[2], dq_full, dq_free,
       acc_done, mma_drained;
@@ -73,8 +76,10 @@ struct BwdParams {
   const float* dstat;
   float* dq_accum;  // [B*Hq, S, D] f32, zeroed before launch; or (dq_half) packed f16 pairs, see below
   // dq_half: the dQ sums are kept as f16 (32 * dQ), two per 32-bit word, so that a drain warp's reduction still
-  // covers 128 contiguous bytes but twice the values.  D = 128 (a drain lane holds one feature of 64 query rows):
-  // word ((bh * S / 2 + q / 2) * D + d) holds row q (even) in its low half and row q + 1 in its high half.
+  // moves 128 contiguous bytes but twice the values.  D = 128 (a drain lane holds one feature of 64 query rows): a
+  // word holds row q (even) in its low half and row q + 1 in its high half; the 32 x 128 words of a sub-tile of 64
+  // query rows form one block, ordered (feature / 32, row pair, feature % 32) so that what one drain warp adds is
+  // contiguous: word ((bh * S / 2 + q / 64 * 32) * D + d / 32 * 1024 + q % 64 / 2 * 32 + d % 32).
   // D = 64 (a drain lane holds one query row): plain rows, word ((bh * S + q) * D / 2 + d / 2).
   int dq_half;
   __nv_bfloat16* dk;
@@ -390,6 +395,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     const int w4 = warp & 3;
     const uint32_t lane_base = tm + ((uint32_t)(w4 * 32) << 16);
     const int r = w4 * 32 + lane;  // TMEM lane: d (D = 128) or query row (D = 64)
+    const bool bulk = D == 128 && p.dq_half;
     for (int it = 0; it < n_it; ++it) {
       if (!mbar_wait_warp(&s.dq_full, it & 1, &s.abort_flag, p.status, 130, it)) break;
       tc_fence_after();
@@ -404,20 +410,32 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       tc_fence_before();
       mbar_arrive_warp(&s.dq_free);  // the next dQ may overwrite the accumulator now
       if (D == 128 && p.dq_half) {
-        // lane = d, registers i, i + 1 = two adjacent query rows: one coalesced 128-byte f16x2 reduction per row pair
-        // (half the reductions and half the bytes of the FP32 form)
-        uint32_t* words = reinterpret_cast<uint32_t*>(p.dq_accum) + ((size_t)bh * p.S + (size_t)qs * QT) * (D / 2) + r;
+        // lane = d, registers i, i + 1 = two adjacent query rows -> one f16x2 word per row pair.  The accumulator keeps
+        // a warp's 32 row pairs x 32 features of a sub-tile as 4 contiguous KB, so each warp stages them in shared memory
+        // and sends them as ONE bulk reduction: the copy engine carries the traffic, and the load/store queue that every
+        // warp of the SM shares sees 32 shared-memory stores per thread instead of 32 global reductions (which held it
+        // up for the compute warps' accesses).  No warp waits for another.
+        uint32_t* tile = s.dq_tile[it & 1][w4];
+        // this warp's reduction of two sub-tiles ago has finished reading the buffer
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        __syncwarp();
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           const uint32_t(&v)[32] = hh ? v1 : v0;
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             const __half2 h2 = __floats2half2_rn(__uint_as_float(v[i]) * kDqHalfScale, __uint_as_float(v[i + 1]) * kDqHalfScale);
-            asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(words + (size_t)((32 * hh + i) >> 1) * D),
-                         "r"(*reinterpret_cast<const uint32_t*>(&h2))
-                         : "memory");
-            if ((i & 15) == 14) drain_pause();
+            tile[((32 * hh + i) >> 1) * 32 + lane] = *reinterpret_cast<const uint32_t*>(&h2);
           }
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          uint32_t* words = reinterpret_cast<uint32_t*>(p.dq_accum) + ((size_t)bh * p.S + (size_t)qs * QT) * (D / 2) + w4 * (32 * 32);
+          asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.f16 [%0], [%1], %2;" ::"l"(words), "r"(smem_u32(tile)),
+                       "r"(32 * 32 * 4)
+                       : "memory");
+          tma_store_commit();
         }
       } else if (D == 128) {
         // lane = d, register i = query row: one coalesced 128-byte reduction per row
@@ -464,6 +482,8 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         }
       }
     }
+    // the bulk reductions of this CTA have completed before its shared memory is given up
+    if (bulk && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   } else {
     // ------------------------------------------------------------------ compute (warps 0-15)
     constexpr int CW = QT / 2;                   // query columns per thread
@@ -686,7 +706,7 @@ __global__ void __launch_bounds__(256) accum_convert_kernel(const ConvertJobs jo
       const int64_t pr = c / kPerRow;
       const int cb = (int)(c % kPerRow) * 8;
       const int bh = (int)(pr / pairs_per_head), pidx = (int)(pr % pairs_per_head);
-      const uint32_t* src = acc + ((int64_t)bh * (S / 2) + pidx) * D + cb;
+      const uint32_t* src = acc + ((int64_t)bh * (S / 2) + pidx / 32 * 32) * D + (cb / 32) * 1024 + (pidx % 32) * 32 + cb % 32;
       const uint4 a = *reinterpret_cast<const uint4*>(src), bq = *reinterpret_cast<const uint4*>(src + 4);
       const uint32_t w[8] = {a.x, a.y, a.z, a.w, bq.x, bq.y, bq.z, bq.w};
       uint32_t even[4], odd[4];
@@ -750,6 +770,7 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   if (int s = make_tensor_map(&m_qc, ws + l.q_codes, 1, D / 2, S, nq, D / 2, S * (D / 2), D / 2, C::QT)) return s;
   if (int s = make_tensor_map(&m_q8, ws + l.q_fp8, 1, D, S, nq, D, S * D, D, C::QT)) return s;
   if (int s = make_tensor_map(&m_do, tws + l.do_fp8, 1, D, S, nq, D, S * D, D, C::QT)) return s;
+
   const int n_sm = sm_count();
   FA4B_REQUIRE(n_sm > 0, FA4B_CUDA_ERROR, "could not read the multiprocessor count of the current device");
   BwdParams p{};
