@@ -1,7 +1,8 @@
 // Causal GQA backward.  One CTA owns a 128-key tile of one kv head: dK and dV of
 // that tile accumulate in TMEM over every query head of the group and every
-// query tile at or after the key tile; dQ contributions leave through FP32
-// reductions into a scratch accumulator that a second kernel rounds to bf16.
+// query tile at or after the key tile; dQ contributions leave as reductions
+// (f16 pairs through the copy engine, or FP32) into a scratch accumulator that a
+// second kernel rounds to bf16.
 //
 // Per query sub-tile (QT = 64 rows at D = 128, 128 rows at D = 64) five MMAs:
 //   S^T  = Knvfp4 . Qnvfp4^T            block-scaled FP4   -> TMEM St  [key, q]
@@ -13,9 +14,13 @@
 // computed by two groups of eight warps (two threads per key row each); group 0 takes the even
 // sub-tiles and group 1 the odd ones, so one group's exponentials overlap the other group's waits.
 // Each group owns one TMEM buffer that first holds S^T and then, once P has been read out of it,
-// dP^T of the same sub-tile.
+// dP^T of the same sub-tile.  A group's chain S^T -> P -> dP^T -> dS -> next S^T sets the kernel's rate (two
+// sub-tiles are in flight; a third group's buffer does not fit the 512 TMEM columns beside a 64-column dQ
+// accumulator), so both tensor-core round trips of the chain are taken off it: dP^T is issued as soon as the
+// group has READ the scores out of the buffer (it forms while the group computes P) and the next S^T as soon as
+// it has READ dP^T (it forms while the group computes dS).
 //
-// Warps: 0-7 compute group 0, 8-15 compute group 1, 16-19 drain dQ, 20 TMA producer, 21 MMA issuer.
+// Warps: 0-7 compute group 0, 8-15 compute group 1, 16-19 drain dQ, 20 TMA producer, 21-23 MMA issuers.
 #include <cstdlib>
 #include <mutex>
 
@@ -297,9 +302,11 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         __syncwarp();
       };
       // The two compute groups alternate sub-tiles and each runs  P(it); dS(it).  Per sub-tile:
-      //   pt_ready(it) -> dP(it) into the group's buffer (P has been read out of it), committed on its own because the
-      //                   group's dS step waits for it, then dV(it), whose completion the group observes before ds_ready
-      //   ds_ready(it) -> S(it+2) into the same buffer (dS has been read out of it), dK(it); dQ(it)
+      //   s_read(it)   -> dP(it) into the group's buffer (the scores have been read out of it), committed on its own
+      //                   because the group's dS step waits for it
+      //   pt_ready(it) -> dV(it), whose completion the group observes before ds_ready
+      //   x_free(it)   -> S(it+2) into the same buffer (dP has been read out of it)
+      //   ds_ready(it) -> dK(it); dQ(it)
       // Each stream runs in sub-tile order (the dQ drain relies on that order).
       auto pt_phase = [&](int it) -> bool {
         const uint32_t st = stage_of(it), g = it & 1;
@@ -389,9 +396,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
   } else if (warp >= 16) {
     // ------------------------------------------------------------------ dQ drain (warps 16-19)
     // The partial dQ of a sub-tile leaves TMEM for registers and the accumulator is handed back to the
-    // issuer at once; the FP32 reductions into the scratch accumulator then run beside the next
-    // sub-tile's MMAs (staging the tile in shared memory for one bulk reduction, or software-pipelining this
-    // loop, was slower).
+    // issuer at once; the reductions into the scratch accumulator then run beside the next sub-tile's MMAs.
     const int w4 = warp & 3;
     const uint32_t lane_base = tm + ((uint32_t)(w4 * 32) << 16);
     const int r = w4 * 32 + lane;  // TMEM lane: d (D = 128) or query row (D = 64)
