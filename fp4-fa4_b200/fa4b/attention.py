@@ -285,7 +285,8 @@ def attn_backward_prepared(ws: Workspace, kv_ws: Workspace | None = None, causal
     (:func:`attn_bwd_preprocess` has run on it with the LSE and O of the whole sequence), keys and values from
     ``kv_ws`` (default ``ws``).  Returns ``(dq | None, dk, dv)``: dK and dV of this block alone (bf16); the query
     gradient accumulates in ``ws``'s FP32 scratch across calls with ``keep_dq_accum`` and is only converted into
-    ``dq`` when ``write_dq``.  ``out=(dq, dk, dv)`` supplies strided destinations as in :func:`attn_backward`."""
+    ``dq`` when ``write_dq`` (a sum over several calls starts with ``write_dq=False``; a single call with the
+    defaults forms its sum as f16 pairs, as :func:`attn_backward` does).  ``out=(dq, dk, dv)`` supplies strided destinations as in :func:`attn_backward`."""
     d = ws.dims
     dims = _lib.AttnDims(d.B, d.Hq, d.Hkv, d.S, d.D, d.softmax_scale, d.pv_format, 0 if causal else 1, d.global_scale_mode)
     dev = ws.buf.device

@@ -332,8 +332,9 @@ typedef struct fa4b_attn_ws_layout {
    * training step has to keep between the two (the reference keeps the same operands, release/routes.json:443-447) */
   size_t q_codes, q_scales, q_global, k_codes, k_scales, k_global;
   size_t v_fp8, k_fp8, q_fp8, amax_bits, status, saved_total;
-  /* transient section [saved_total, total): lives inside one backward call -- E5M2 dO, dstat, lstat, the FP32 dQ
-   * accumulator and the FP32 dK / dV accumulators of key tiles whose query range is split over several CTAs.
+  /* transient section [saved_total, total): lives inside one backward call -- E5M2 dO, dstat, lstat, the dQ
+   * accumulator (FP32-sized; a call that forms the whole sum keeps f16 values in its first half, see fa4b_attn_bwd)
+   * and the FP32 dK / dV accumulators of key tiles whose query range is split over several CTAs.
    * Either the tail of `ws`, or a separate buffer of total - saved_total bytes passed as
    * fa4b_attn_bwd_args.scratch and shared by every layer */
   size_t do_fp8, dstat, lstat, dq_accum, dkv_accum, total;
@@ -443,7 +444,8 @@ int fa4b_attn_bwd_preprocess(const fa4b_attn_bwd_args* a, void* stream);
  * the key tiles meet in the dQ accumulator as f16 pairs (32 dQ per value: half the reduction traffic of FP32 sums, the
  * reference's v420 adds them as bf16; dQ of two runs then differs by the order of those roundings, about 1e-3
  * relative) when one call forms the whole sum; FA4B_BWD_DQ_SUMS_FP32 asks for FP32 sums, and a sum carried across
- * calls (FA4B_BWD_KEEP_DQ_ACCUM, FA4B_BWD_SKIP_DQ_OUT) is always FP32.  One CTA per
+ * calls (FA4B_BWD_KEEP_DQ_ACCUM, FA4B_BWD_SKIP_DQ_OUT) is always FP32: such a sum starts with a call that carries
+ * FA4B_BWD_SKIP_DQ_OUT, never with a call that wrote dq (the accumulator would hold f16 words).  One CTA per
  * (key tile, part of the tile's query range, batch and kv head), key-tile-major; in a launch of few heads a key
  * tile that sees more query tiles than the launch's chunk length is cut into parts whose dK / dV meet as FP32
  * sums (fa4b_attn_bwd_plan).  With
