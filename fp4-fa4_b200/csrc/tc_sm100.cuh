@@ -25,13 +25,13 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// A failed try parks the thread until the phase completes or, at the latest, for the time hint (20 us): with the
-// hardware's default limit waiting warps woke more often and their re-polls took issue slots from working warps
-// (2 % of the forward at B2 Hq32 S8192).
+// A failed try parks the thread until the phase completes or the hardware's time limit passes (a few microseconds).
+// No suspend-time hint: with one, a try is a longer instruction sequence for every waiting warp, which cost the
+// attention kernels 1 % (forward) and 3 % (backward) of their time once their waits had become short.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 20000; selp.u32 %0, 1, 0, p; }"
+      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
@@ -76,7 +76,7 @@ static __device__ __noinline__ bool mbar_wait_teardown(uint64_t* bar, uint32_t p
 // `limit`: the cycle budget of this wait (the kernels use the default; the wait self-test passes a short one)
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status,
                                           uint32_t where, uint32_t detail = 0, long long limit = kWaitLimitCycles) {
-  // one try parks the thread until the phase completes (or 20 us pass), so the first one nearly always succeeds
+  // one try parks the thread until the phase completes (or the hardware's limit passes), so the first one nearly always succeeds
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, status, where, detail, limit);
 }
