@@ -37,9 +37,6 @@ struct BwdCfg {
   static constexpr int kPages = D / 64;
   static constexpr uint32_t colDK = 0, colDV = D, colX = 2 * D, colDQ = 2 * D + 2 * QT;  // colX + g * QT: S^T / dP^T of group g
   static constexpr uint32_t colSfa = colDQ + 64, colSfb = colSfa + 8;
-  // dS8^T buffers per compute group: with two (D = 128, where shared memory allows) a group writes the dS8^T of a
-  // sub-tile without waiting for dK and dQ of its previous one to have read theirs
-  static constexpr int kDstDepth = (D == 128) ? 2 : 1;
   static_assert(colSfb + 8 <= 512, "TMEM budget");
 };
 
@@ -53,16 +50,15 @@ struct BwdSmem {
   alignas(1024) uint8_t q8[kBwdStages][C::QT * D];
   alignas(1024) uint8_t do5[kBwdStages][C::QT * D];
   alignas(1024) uint8_t pt[2][128 * C::QT];   // P8^T  [key][q], rows of QT bytes, swizzled
-  alignas(1024) uint8_t dst[2][C::kDstDepth][128 * C::QT];  // dS8^T [key][q], per group and use
+  alignas(1024) uint8_t dst[2][128 * C::QT];  // dS8^T [key][q]
   alignas(16) uint8_t k_sf[C::kPages * 512];
   alignas(16) uint8_t q_sf[kBwdStages][C::kPages * 512];
   alignas(16) float lstat[kBwdStages][C::QT];
   alignas(16) float dstat[kBwdStages][C::QT];
   alignas(16) float dq_patch[D == 64 ? 4 : 1][D == 64 ? 32 * 33 : 1];  // D = 64: per drain warp, 32 x 32 transposition patch
   // D = 128, f16 dQ sums: per drain warp the sub-tile's 32 row pairs x 32 features as words, in the accumulator's own
-  // order: the source of one bulk reduction per warp and sub-tile (one buffer: the copy engine has read it long
-  // before the next sub-tile's dQ arrives)
-  alignas(128) uint32_t dq_tile[D == 128 ? 4 : 1][D == 128 ? 32 * 32 : 4];
+  // order, two buffers: the source of one bulk reduction per warp and sub-tile
+  alignas(128) uint32_t dq_tile[D == 128 ? 2 : 1][D == 128 ? 4 : 1][D == 128 ? 32 * 32 : 4];
   alignas(16) float c2[16];  // per query head of the group: global scales * softmax scale * log2(e)
   alignas(8) uint64_t kv_full, in_full[kBwdStages], in_empty[kBwdStages], st_full[2], dp_full[2], dv_done[2], pt_ready[2], s_read[2], x_free[2], ds_ready[2], dq_full, dq_free,
       acc_done, mma_drained;
@@ -265,9 +261,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
       const uint64_t d_v8 = make_tile_desc(smem_u32(s.v8), D);
       const uint64_t d_qc0 = make_tile_desc(smem_u32(s.q_codes[0]), D / 2), d_q80 = make_tile_desc(smem_u32(s.q8[0]), D);
       const uint64_t d_do0 = make_tile_desc(smem_u32(s.do5[0]), D);
-      const uint64_t d_pt0 = make_tile_desc(smem_u32(s.pt[0]), QT), d_ds0 = make_tile_desc(smem_u32(s.dst[0][0]), QT);
-      // dS8^T buffer of sub-tile `it`: group it & 1, use (it >> 1) % kDstDepth
-      auto dst_index = [](int it) { return (uint32_t)((it & 1) * C::kDstDepth + ((it >> 1) % C::kDstDepth)); };
+      const uint64_t d_pt0 = make_tile_desc(smem_u32(s.pt[0]), QT), d_ds0 = make_tile_desc(smem_u32(s.dst[0]), QT);
       const uint64_t d_sfq0 = make_page_desc(smem_u32(s.q_sf[0]));
       constexpr uint32_t kQc16 = (QT * D / 2) >> 4, kQ816 = (QT * D) >> 4, kSf16 = (kPages * 512) >> 4, kPt16 = (128 * QT) >> 4;
       constexpr uint32_t kRow32D = (32 * D) >> 4, kRow32Q = (32 * QT) >> 4;
@@ -351,7 +345,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         if (!mbar_wait_warp(&s.ds_ready[g], (it >> 1) & 1, &s.abort_flag, p.status, 123, it)) return false;
         tc_fence_after();
         const uint32_t acc = it > 0 ? 1u : 0u;
-        const uint64_t q8 = d_q80 + st * kQ816, ds = d_ds0 + dst_index(it) * kPt16;
+        const uint64_t q8 = d_q80 + st * kQ816, ds = d_ds0 + g * kPt16;
         if (leader) {
 #pragma unroll
           for (int k = 0; k < QT / 32; ++k) mma_f8_ss(tm + C::colDK, ds + 2 * k, q8 + kRow32D * k, id_dk, k > 0 ? 1u : acc);
@@ -366,7 +360,7 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         if (!mbar_wait_warp(&s.ds_ready[g], (it >> 1) & 1, &s.abort_flag, p.status, 127, it)) return false;
         if (it > 0 && !mbar_wait_warp(&s.dq_free, (it - 1) & 1, &s.abort_flag, p.status, 124, it)) return false;
         tc_fence_after();
-        const uint64_t ds = d_ds0 + dst_index(it) * kPt16;
+        const uint64_t ds = d_ds0 + g * kPt16;
         if (leader) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) {  // 128 keys, 32 per step
@@ -426,9 +420,9 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
         // and sends them as ONE bulk reduction: the copy engine carries the traffic, and the load/store queue that every
         // warp of the SM shares sees 32 shared-memory stores per thread instead of 32 global reductions (which held it
         // up for the compute warps' accesses).  No warp waits for another.
-        uint32_t* tile = s.dq_tile[w4];
-        // this warp's previous reduction has finished reading the buffer
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        uint32_t* tile = s.dq_tile[it & 1][w4];
+        // this warp's reduction of two sub-tiles ago has finished reading the buffer
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
         __syncwarp();
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
@@ -573,16 +567,13 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     const uint64_t bb = pack2(beta, beta);
     auto do_ds = [&](int it, const uint32_t (&pk)[CW / 4]) -> bool {
       const int st = it % kBwdStages;
-      // dK and dQ of the sub-tile that last used this dS8^T buffer have read it: the release of their input stage is
-      // committed after them (that stage is not released again before this sub-tile's own dK and dQ, so the phase
-      // waited for is the barrier's latest or the one before)
-      constexpr int kBack = 2 * C::kDstDepth;
-      if (it >= kBack && !mbar_wait_warp(&s.in_empty[(it - kBack) % kBwdStages], ((it - kBack) / kBwdStages) & 1, &s.abort_flag, p.status, 144, it))
+      // the release of their input stage is committed after them
+      if (it >= 2 && !mbar_wait_warp(&s.in_empty[(it - 2) % kBwdStages], ((it - 2) / kBwdStages) & 1, &s.abort_flag, p.status, 144, it))
         return false;
       if (!mbar_wait_warp(&s.dp_full[grp], (it >> 1) & 1, &s.abort_flag, p.status, 141, it)) return false;
       tc_fence_after();
       const float* dsm = &s.dstat[st][half * CW];
-      uint8_t* dst_row = &s.dst[grp][(it >> 1) % C::kDstDepth][row_base];
+      uint8_t* dst_row = &s.dst[grp][row_base];
 #pragma unroll
       for (int c0 = 0; c0 < CW; c0 += 32) {
         uint32_t v[32];
