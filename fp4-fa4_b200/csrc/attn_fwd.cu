@@ -45,7 +45,7 @@ struct FwdSmem {
   alignas(16) uint8_t v_sf[kStages][512];      // MXFP4 route: E8M0 page of the stage's V (row = feature)
   alignas(16) uint8_t p_sf[2][512];            // MXFP4 route: E8M0 page of the P block (row = query row)
   StepTable steps;                             // in-kernel Q quantisation: division table of this head's global scale
-  alignas(8) uint64_t q_full, kv_full[kStages], kv_empty[2][kStages], s_full[2], s_free[2], p_ready[2][2], o_done[2], mma_drained;
+  alignas(8) uint64_t q_raw, q_full, kv_full[kStages], kv_empty[2][kStages], s_full[2], s_free[2], p_ready[2][2], o_done[2], mma_drained;
   uint32_t tmem_base;
   alignas(8) volatile uint32_t abort_flag;
   uint32_t pad_;
@@ -74,6 +74,7 @@ struct FwdParams {
   uint8_t* q_sf_out;
   uint8_t* q_fp8_out;
   float* q_global_out;
+  int q_tma;  // the bf16 query tiles arrive by TMA (map_qsrc) instead of through the softmax threads' loads
 };
 
 
@@ -99,7 +100,8 @@ __device__ __forceinline__ void ex2_pair(uint64_t e2, int pair, float& lo, float
 template <int D, bool MX>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_q8) {
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_q8,
+                const __grid_constant__ CUtensorMap map_qsrc) {
   extern __shared__ uint8_t raw[];
   // aligned by offsetting the shared array itself, so that accesses stay shared-space loads and stores
   FwdSmem<D>& s = *reinterpret_cast<FwdSmem<D>*>(raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u));
@@ -144,8 +146,19 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       mbar_init(&s.o_done[i], 1);
     }
     mbar_init(&s.mma_drained, nb1 ? 2 : 1);
+    mbar_init(&s.q_raw, 1);
     s.abort_flag = 0;
     fence_barrier_init();
+    if (p.q_src && p.q_tma) {
+      // the bf16 query rows of this CTA's tiles start on their way at once, as boxes of 128 rows x 64 features in the
+      // layout the quantisation reads (their latency runs under the rest of the set-up)
+      const int nq = nb1 ? 2 : 1;
+      mbar_expect_tx(&s.q_raw, nq * 128 * D * 2);
+      for (int i = 0; i < nq; ++i)
+#pragma unroll
+        for (int bx = 0; bx < D / 64; ++bx)
+          tma_load_4d(&s.q_stage[i][bx * (128 * 128)], &map_qsrc, bx * 64, (2 * pi + i) * 128, h, b, &s.q_raw);
+    }
   }
   if (warp == 8) tmem_alloc(&s.tmem_base, 512);
   tc_fence_before();
@@ -189,6 +202,7 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       // tensor core's arrivals on the stage barriers must have landed too (nobody else waits for
       // the last ones)
       mbar_wait_teardown(&s.q_full, 0);
+      if (p.q_src && p.q_tma) mbar_wait_teardown(&s.q_raw, 0);
       for (int j = issued > kStages ? issued - kStages : 0; j < issued; ++j) {
         mbar_wait_teardown(&s.kv_full[j % kStages], (j / kStages) & 1);
         if (issued == n_stages && !s.abort_flag) {
@@ -325,21 +339,26 @@ attn_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap map_q, co
       fill_step_table(s.steps, q_g, t);
       asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight softmax warps
       if (nb > 0) {
-        // the tile's rows come in by coalesced loads of its 128 threads (a row is D / 8 chunks of 16 bytes) ...
         constexpr int kChunks = D / 8;
-        const __nv_bfloat16* tile_src = p.q_src + (int64_t)b * p.q_sb + (int64_t)h * p.q_sh + (int64_t)(qt * 128) * p.q_ss;
         uint4 raw[kChunks];
+        if (p.q_tma) {
+          // the tile's rows were asked for by TMA when the CTA started
+          mbar_wait_warp(&s.q_raw, 0, &s.abort_flag, p.status, 33);
+        } else {
+          // the tile's rows come in by coalesced loads of its 128 threads (a row is D / 8 chunks of 16 bytes) ...
+          const __nv_bfloat16* tile_src = p.q_src + (int64_t)b * p.q_sb + (int64_t)h * p.q_sh + (int64_t)(qt * 128) * p.q_ss;
 #pragma unroll
-        for (int i = 0; i < kChunks; ++i) {
-          const int chunk = row + i * 128;
-          raw[i] = __ldg(reinterpret_cast<const uint4*>(tile_src + (int64_t)(chunk / kChunks) * p.q_ss) + chunk % kChunks);
-        }
+          for (int i = 0; i < kChunks; ++i) {
+            const int chunk = row + i * 128;
+            raw[i] = __ldg(reinterpret_cast<const uint4*>(tile_src + (int64_t)(chunk / kChunks) * p.q_ss) + chunk % kChunks);
+          }
 #pragma unroll
-        for (int i = 0; i < kChunks; ++i) {
-          const int chunk = row + i * 128, r = chunk / kChunks, c = chunk % kChunks;
-          *reinterpret_cast<uint4*>(&s.q_stage[ti][(c >> 3) * (128 * 128) + swizzled_offset((uint32_t)r, (uint32_t)(c & 7) * 16u, 128)]) = raw[i];
+          for (int i = 0; i < kChunks; ++i) {
+            const int chunk = row + i * 128, r = chunk / kChunks, c = chunk % kChunks;
+            *reinterpret_cast<uint4*>(&s.q_stage[ti][(c >> 3) * (128 * 128) + swizzled_offset((uint32_t)r, (uint32_t)(c & 7) * 16u, 128)]) = raw[i];
+          }
+          asm volatile("bar.sync %0, 128;" ::"r"(2 + ti) : "memory");  // the four warps of this tile
         }
-        asm volatile("bar.sync %0, 128;" ::"r"(2 + ti) : "memory");  // the four warps of this tile
         // ... and each thread takes its own row back (conflict-free: the eight lanes of a quarter warp are eight rows)
 #pragma unroll
         for (int c = 0; c < kChunks; ++c)
@@ -640,6 +659,7 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   }
   // E4M3 queries [B*Hq*S][D]: the kernel's own quantisation writes them as boxes of 128 rows
   if (int s = make_tensor_map(&mq8, ws + l.q_fp8, 1, D, S * d.B * d.Hq, 0, D, 0, D, 128)) return s;
+  CUtensorMap mqs = mq8;
   FwdParams p{};
   p.B = d.B; p.Hq = d.Hq; p.Hkv = d.Hkv; p.S = d.S;
   p.scale_log2 = resolve_scale(d) * kLog2e;
@@ -659,6 +679,11 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
     p.unit_global = d.global_scale_mode == FA4B_GLOBAL_ONE;
     p.q_codes_out = ws + l.q_codes; p.q_sf_out = ws + l.q_scales; p.q_fp8_out = ws + l.q_fp8;
     p.q_global_out = reinterpret_cast<float*>(ws + l.q_global);
+    // bf16 queries [B][Hq][S][D] through the caller's strides; a view the tensor-map encoder refuses is loaded by threads
+    p.q_tma = make_tensor_map_4d_bf16(&mqs, a.q, D, S, d.Hq, d.B, (uint64_t)a.q_strides.seq * 2, (uint64_t)a.q_strides.head * 2,
+                                      (uint64_t)a.q_strides.batch * 2, 64, 128) == FA4B_OK
+                  ? 1
+                  : 0;
   }
   FA4B_CUDA(cudaMemsetAsync(p.status, 0, 64, st));
   const int smem = (int)sizeof(FwdSmem<D>) + 1024;
@@ -675,7 +700,7 @@ static int fwd_impl(const fa4b_attn_fwd_args& a, cudaStream_t st) {
   }
   const unsigned grid = (unsigned)(d.B * d.Hq * ((d.S / 128 + 1) / 2));
   if (a.ev_before) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_before), st));
-  attn_fwd_kernel<D, MX><<<grid, kFwdThreads, smem, st>>>(p, mq, mk, mv, mq8);
+  attn_fwd_kernel<D, MX><<<grid, kFwdThreads, smem, st>>>(p, mq, mk, mv, mq8, mqs);
   FA4B_CUDA(cudaGetLastError());
   if (a.ev_after) FA4B_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(a.ev_after), st));
   return FA4B_OK;

@@ -46,6 +46,25 @@ int make_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, uint64_t
   return FA4B_OK;
 }
 
+int make_tensor_map_4d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows, uint64_t d2, uint64_t d3,
+                            uint64_t row_stride_bytes, uint64_t d2_stride_bytes, uint64_t d3_stride_bytes, uint32_t box_inner,
+                            uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr || box_inner * 2 != 128) return FA4B_CUDA_ERROR;
+  // a dimension of extent 1 carries no stride of its own: give it the next inner one's span so that the encoder's
+  // checks (multiples of 16, non-decreasing is not required) pass whatever the caller's view says
+  cuuint64_t dims[4] = {inner, rows, d2, d3};
+  cuuint64_t strides[3] = {row_stride_bytes, d2 > 1 ? d2_stride_bytes : row_stride_bytes * rows,
+                           d3 > 1 ? d3_stride_bytes : (d2 > 1 ? d2_stride_bytes * d2 : row_stride_bytes * rows)};
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] == 0 || (strides[i] & 15) != 0 || strides[i] >= (1ull << 40)) return FA4B_BAD_ALIGN;
+  cuuint32_t box[4] = {box_inner, box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FA4B_OK : FA4B_CUDA_ERROR;
+}
+
 struct GateSmem {
   alignas(1024) uint8_t a[128 * 128];
   alignas(1024) uint8_t b[128 * 128];

@@ -158,6 +158,13 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int x, int y, int z, int w, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
 // TMA store of one box from shared memory (bulk async-group completion)
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(smem_u32(smem_src)), "r"(x),
@@ -325,5 +332,12 @@ __device__ __forceinline__ void tmem_cp_page(uint32_t taddr, uint64_t sdesc) {
 // width in bytes.
 int make_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t rows, uint64_t outer,
                     uint64_t row_stride_bytes, uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_rows);
+
+// bf16 tensor [d3][d2][rows][inner] whose three outer strides (in bytes, multiples of 16) are free; the box is
+// box_inner x box_rows x 1 x 1 with the 128-byte swizzle (box_inner = 64).  Returns a status without setting the
+// error text when the driver refuses the strides: the caller then takes its path without TMA.
+int make_tensor_map_4d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows, uint64_t d2, uint64_t d3,
+                            uint64_t row_stride_bytes, uint64_t d2_stride_bytes, uint64_t d3_stride_bytes, uint32_t box_inner,
+                            uint32_t box_rows);
 
 }  // namespace fa4b
