@@ -151,7 +151,8 @@ void fill_bwd_info(fa4b_info* out);
 // skip_q: publish K and V only (the forward kernel quantises Q itself); the amax words of Q are still taken
 int launch_attn_prepare(const fa4b_attn_prepare_args& a, cudaStream_t st, bool skip_q = false);
 int launch_attn_fwd(const fa4b_attn_fwd_args& a, cudaStream_t st);
-int launch_attn_bwd_preprocess(const fa4b_attn_bwd_args& a, cudaStream_t st);
+// zero_dq: the launch also clears the dQ accumulator of the backward call it belongs to
+int launch_attn_bwd_preprocess(const fa4b_attn_bwd_args& a, cudaStream_t st, bool zero_dq = false);
 int launch_attn_bwd(const fa4b_attn_bwd_args& a, cudaStream_t st);
 int launch_attn_accumulate(float* acc, const void* part, int64_t n, void* out, cudaStream_t st);
 int launch_attn_merge(float* o_acc, float* lse_acc, const void* o_part, const float* lse_part, int64_t n_rows, int D, void* o_out,

@@ -761,8 +761,9 @@ static void add_convert_job(ConvertJobs& jobs, const float* acc, int H, int rows
   ++jobs.n;
 }
 
+// dq_zeroed: the preprocess launch of this call has cleared the dQ accumulator
 template <int D>
-static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
+static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st, bool dq_zeroed) {
   using C = BwdCfg<D>;
   const fa4b_attn_dims& d = a.dims;
   const fa4b_attn_ws_layout l = make_ws_layout(d);
@@ -805,7 +806,7 @@ static int bwd_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   // their dK and dV arrive as FP32 sums
   const int split_rows = n_tiles > p.chunk ? (p.causal ? (n_tiles - p.chunk) * 128 : d.S) : 0;
   FA4B_CUDA(cudaMemsetAsync(p.status, 0, 16, st));
-  if (!(a.flags & FA4B_BWD_KEEP_DQ_ACCUM)) FA4B_CUDA(cudaMemsetAsync(p.dq_accum, 0, nq * S * D * (p.dq_half ? 2 : 4), st));
+  if (!(a.flags & FA4B_BWD_KEEP_DQ_ACCUM) && !dq_zeroed) FA4B_CUDA(cudaMemsetAsync(p.dq_accum, 0, nq * S * D * (p.dq_half ? 2 : 4), st));
   if (split_rows)
     FA4B_CUDA(cudaMemset2DAsync(p.dk_accum, S * D * sizeof(float), 0, (size_t)split_rows * D * sizeof(float), 2 * nk, st));
   const int smem = (int)sizeof(BwdSmem<D>) + 1024;
@@ -858,10 +859,11 @@ int launch_attn_bwd(const fa4b_attn_bwd_args& a, cudaStream_t st) {
     if (int s = check_out(a.dq, a.dq_strides, "dq")) return s;
   if (int s = check_out(a.dk, a.dk_strides, "dk")) return s;
   if (int s = check_out(a.dv, a.dv_strides, "dv")) return s;
+  const bool zero_in_preprocess = !a.preprocessed && !(a.flags & FA4B_BWD_KEEP_DQ_ACCUM);
   if (!a.preprocessed) {
-    if (int s = launch_attn_bwd_preprocess(a, st)) return s;
+    if (int s = launch_attn_bwd_preprocess(a, st, zero_in_preprocess)) return s;
   }
-  return a.dims.D == 128 ? bwd_impl<128>(a, st) : bwd_impl<64>(a, st);
+  return a.dims.D == 128 ? bwd_impl<128>(a, st, zero_in_preprocess) : bwd_impl<64>(a, st, zero_in_preprocess);
 }
 
 void fill_bwd_info(fa4b_info* out) {

@@ -201,14 +201,19 @@ __global__ void __launch_bounds__(256) v_to_mx_kernel(HeadView x, int S, uint8_t
 
 __device__ __forceinline__ float e5m2_to_f32(uint32_t byte) { return __half2float(__ushort_as_half((unsigned short)(byte << 8))); }
 
-// dO5 = E5M2(4 dO); dstat = -4 sum_d O * float(dO5); lstat = 8 - LSE * log2e
+// dO5 = E5M2(4 dO); dstat = -4 sum_d O * float(dO5); lstat = 8 - LSE * log2e.  With `zero16` > 0 the launch also
+// clears the backward's dQ accumulator, zero16 16-byte words per thread (the accumulator is a whole number of such
+// rounds: 2 or 4 bytes per element of O), in place of a memset of its own between this kernel and the backward.
 template <int D>
 __global__ void __launch_bounds__(256) bwd_preprocess_kernel(HeadView o, HeadView dout, const float* __restrict__ lse, int S,
                                                              int64_t n_rows, uint8_t* __restrict__ do_fp8,
-                                                             float* __restrict__ dstat, float* __restrict__ lstat) {
+                                                             float* __restrict__ dstat, float* __restrict__ lstat,
+                                                             uint4* __restrict__ zero_base, int zero16) {
   constexpr int kLanes = D / 8;  // threads per row, 8 elements each
   const int64_t row = (int64_t)blockIdx.x * (256 / kLanes) + threadIdx.x / kLanes;
   const int c = threadIdx.x % kLanes;
+  for (int k = 0; k < zero16; ++k)
+    zero_base[((int64_t)k * gridDim.x + blockIdx.x) * 256 + threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
   float acc = 0.f;
   if (row < n_rows) {
     const int bh = (int)(row / S), s = (int)(row % S);
@@ -404,20 +409,22 @@ int launch_attn_prepare(const fa4b_attn_prepare_args& a, cudaStream_t st, bool s
 }
 
 template <int D>
-static int preprocess_impl(const fa4b_attn_bwd_args& a, cudaStream_t st) {
+static int preprocess_impl(const fa4b_attn_bwd_args& a, cudaStream_t st, bool zero_dq) {
   const fa4b_attn_dims& d = a.dims;
   const fa4b_attn_ws_layout l = make_ws_layout(d);
   uint8_t* ws = transient_base(a, l);
   const int64_t n_rows = (int64_t)d.B * d.Hq * d.S;
   constexpr int kRowsPerCta = 256 / (D / 8);
+  // n_rows is a multiple of 128 (S is): every CTA is full, and one 16-byte word per thread covers two bytes per element
+  const int zero16 = zero_dq ? (bwd_dq_half(d, a.flags) ? 1 : 2) : 0;
   bwd_preprocess_kernel<D><<<(unsigned)((n_rows + kRowsPerCta - 1) / kRowsPerCta), 256, 0, st>>>(
       view(a.o, a.o_strides, d.Hq), view(a.dout, a.do_strides, d.Hq), a.lse, d.S, n_rows, ws + l.do_fp8,
-      reinterpret_cast<float*>(ws + l.dstat), reinterpret_cast<float*>(ws + l.lstat));
+      reinterpret_cast<float*>(ws + l.dstat), reinterpret_cast<float*>(ws + l.lstat), reinterpret_cast<uint4*>(ws + l.dq_accum), zero16);
   FA4B_CUDA(cudaGetLastError());
   return FA4B_OK;
 }
 
-int launch_attn_bwd_preprocess(const fa4b_attn_bwd_args& a, cudaStream_t st) {
+int launch_attn_bwd_preprocess(const fa4b_attn_bwd_args& a, cudaStream_t st, bool zero_dq) {
   if (int s = check_dims(a.dims)) return s;
   if (int s = check_view(a.o, a.o_strides, "o")) return s;
   if (int s = check_view(a.dout, a.do_strides, "dout")) return s;
@@ -425,7 +432,7 @@ int launch_attn_bwd_preprocess(const fa4b_attn_bwd_args& a, cudaStream_t st) {
   FA4B_REQUIRE(a.ws != nullptr && (reinterpret_cast<uintptr_t>(a.ws) & 1023) == 0, FA4B_BAD_ALIGN,
                "workspace must be non-NULL and 1024-byte aligned");
   FA4B_REQUIRE((reinterpret_cast<uintptr_t>(a.scratch) & 1023) == 0, FA4B_BAD_ALIGN, "scratch must be 1024-byte aligned");
-  return a.dims.D == 128 ? preprocess_impl<128>(a, st) : preprocess_impl<64>(a, st);
+  return a.dims.D == 128 ? preprocess_impl<128>(a, st, zero_dq) : preprocess_impl<64>(a, st, zero_dq);
 }
 
 }  // namespace fa4b
