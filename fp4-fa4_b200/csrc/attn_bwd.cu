@@ -196,6 +196,12 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
     mbar_init(&s.mma_drained, 3);
     s.abort_flag = 0;
     fence_barrier_init();
+    // the key tile's operands start on their way at once: their latency runs under the rest of the set-up
+    mbar_expect_tx(&s.kv_full, 128 * D / 2 + kPages * 512 + 2 * 128 * D);
+    tma_load_3d(s.k_codes, &map_kc, 0, kt * 128, bhk, &s.kv_full);
+    bulk_load(s.k_sf, p.k_sf + ((size_t)bhk * n_tiles + kt) * kPages * 512, kPages * 512, &s.kv_full);
+    tma_load_3d(s.k8, &map_k8, 0, kt * 128, bhk, &s.kv_full);
+    tma_load_3d(s.v8, &map_v8, 0, kt * 128, bhk, &s.kv_full);
   }
   if (t < 16) s.c2[t] = (t < G) ? p.k_global[bhk] * p.scale * kLog2e * p.q_global[b * p.Hq + hk * G + t] : 0.f;
   if (warp == 20) tmem_alloc(&s.tmem_base, 512);
@@ -207,11 +213,6 @@ attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap map_kc, c
   if (warp == 20) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
-      mbar_expect_tx(&s.kv_full, 128 * D / 2 + kPages * 512 + 2 * 128 * D);
-      tma_load_3d(s.k_codes, &map_kc, 0, kt * 128, bhk, &s.kv_full);
-      bulk_load(s.k_sf, p.k_sf + ((size_t)bhk * n_tiles + kt) * kPages * 512, kPages * 512, &s.kv_full);
-      tma_load_3d(s.k8, &map_k8, 0, kt * 128, bhk, &s.kv_full);
-      tma_load_3d(s.v8, &map_v8, 0, kt * 128, bhk, &s.kv_full);
       int issued = 0;
       for (int it = 0; it < n_it; ++it) {
         const int st = it % kBwdStages;
