@@ -31,6 +31,15 @@ def test_query_reports_build_facts():
     assert 0 < info.wait_limit <= 1 << 24
 
 
+def test_backward_flags_agree_between_the_header_and_the_python_side():
+    from fa4b import attention
+
+    header = (ROOT / "include" / "fa4b.h").read_text()
+    values = {m.group(1): int(m.group(2)) for m in re.finditer(r"(FA4B_BWD_[A-Z0-9_]+) = (\d+)", header)}
+    assert values == {"FA4B_BWD_KEEP_DQ_ACCUM": 1, "FA4B_BWD_SKIP_DQ_OUT": 2, "FA4B_BWD_DQ_SUMS_FP32": 4}
+    assert (attention.BWD_KEEP_DQ_ACCUM, attention.BWD_SKIP_DQ_OUT, attention.BWD_DQ_SUMS_FP32) == (1, 2, 4)
+
+
 def test_status_strings():
     h = _lib.lib()
     assert h.fa4b_status_string(0) == b"ok"
